@@ -1,0 +1,14 @@
+"""symm_mem_recipes_b200: symmetric-memory collectives and fused
+compute+collective kernels for NVIDIA B200 (sm_100a).
+
+One process per GPU (`torch.distributed`, backend "nccl") for the plumbing;
+all cross-GPU bytes of the ops move by loads, stores and `multimem`
+instructions issued from this package's own kernels on peer-mapped memory.
+"""
+from . import errors  # noqa: F401
+from .parallel import symm_mem  # noqa: F401
+from . import ops  # noqa: F401
+from .ops import (all_reduce, barrier_test, multimem_all_reduce_, one_shot_all_reduce,  # noqa: F401
+                  two_shot_all_reduce_)
+
+__version__ = "0.1.0"

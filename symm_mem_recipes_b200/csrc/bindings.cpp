@@ -1,0 +1,320 @@
+// Python bindings (pybind11 through torch/extension.h).  This is the only
+// translation unit that sees framework headers; everything it calls takes raw
+// pointers and a stream.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <cuda_runtime_api.h>
+#include <torch/extension.h>
+
+#include <map>
+#include <memory>
+#include <mutex>
+
+#include "kernels/launch.h"
+#include "oracle/cpu_reference.h"
+#include "symm/allocator.h"
+#include "symm/host_backend.h"
+#include "symm/ipc.h"
+
+namespace py = pybind11;
+using namespace smr;
+
+namespace {
+
+void rt_check(int e, const char* what) {
+  TORCH_CHECK(e == 0, what, ": ", cudaGetErrorString((cudaError_t)e));
+}
+
+// ---- per-device status record ----------------------------------------------
+std::mutex g_status_mu;
+std::map<int, Status*> g_status;
+
+Status* status_for(int device) {
+  std::lock_guard<std::mutex> lock(g_status_mu);
+  auto it = g_status.find(device);
+  if (it != g_status.end()) return it->second;
+  c10::cuda::CUDAGuard guard(device);
+  Status* s = nullptr;
+  rt_check(cudaMalloc(reinterpret_cast<void**>(&s), sizeof(Status)), "cudaMalloc(status)");
+  rt_check(cudaMemset(s, 0, sizeof(Status)), "cudaMemset(status)");
+  g_status[device] = s;
+  return s;
+}
+
+// Synchronises the device, returns (code, rank, block, peer, where, aux) and
+// clears the record.
+py::tuple read_status(int device) {
+  Status* s = status_for(device);
+  c10::cuda::CUDAGuard guard(device);
+  Status h{};
+  rt_check(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+  rt_check(cudaMemcpy(&h, s, sizeof(Status), cudaMemcpyDeviceToHost), "cudaMemcpy(status)");
+  if (h.code != 0) rt_check(cudaMemset(s, 0, sizeof(Status)), "cudaMemset(status)");
+  return py::make_tuple(h.code, h.rank, h.block, h.peer, h.where, h.aux);
+}
+
+cudaStream_t current_stream(int device) { return c10::cuda::getCurrentCUDAStream(device).stream(); }
+
+PeerView view_of(const CudaSymmAllocation& a) {
+  TORCH_CHECK(a.rendezvoused(), "symmetric allocation has not been rendezvoused");
+  PeerView pv;
+  pv.buffers = a.buffers_dev();
+  pv.pads = a.pads_dev();
+  pv.multicast = a.multicast_ptr();
+  pv.rank = a.rank();
+  pv.world_size = a.world_size();
+  return pv;
+}
+
+torch::Tensor cuda_view(const std::shared_ptr<CudaSymmAllocation>& a, int rank,
+                        std::vector<int64_t> sizes, torch::ScalarType dtype, int64_t offset_bytes,
+                        bool multicast) {
+  int64_t numel = 1;
+  for (auto s : sizes) numel *= s;
+  int64_t bytes = numel * (int64_t)c10::elementSize(dtype);
+  TORCH_CHECK(offset_bytes >= 0 && (size_t)(offset_bytes + bytes) <= a->payload_bytes(),
+              "view exceeds the symmetric allocation");
+  char* base;
+  if (multicast) {
+    TORCH_CHECK(a->multicast_ptr() != nullptr, "allocation has no multicast mapping");
+    base = static_cast<char*>(a->multicast_ptr());
+  } else if (rank < 0 || !a->rendezvoused()) {
+    base = static_cast<char*>(a->local_ptr());
+  } else {
+    base = static_cast<char*>(a->peer_ptr(rank));
+  }
+  auto opts = torch::TensorOptions().dtype(dtype).device(torch::kCUDA, a->device());
+  // The deleter keeps the allocation alive for as long as a view exists.
+  return torch::from_blob(base + offset_bytes, sizes, [a](void*) {}, opts);
+}
+
+torch::Tensor cuda_pad_view(const std::shared_ptr<CudaSymmAllocation>& a, int rank) {
+  char* base = (rank < 0 || !a->rendezvoused()) ? static_cast<char*>(a->local_ptr())
+                                                : static_cast<char*>(a->peer_ptr(rank));
+  auto opts = torch::TensorOptions().dtype(torch::kInt32).device(torch::kCUDA, a->device());
+  return torch::from_blob(base + a->pad_offset(), {(int64_t)kSignalPadSlots}, [a](void*) {}, opts);
+}
+
+torch::Tensor host_view(const std::shared_ptr<HostSymmAllocation>& a, int rank,
+                        std::vector<int64_t> sizes, torch::ScalarType dtype, int64_t offset_bytes) {
+  int64_t numel = 1;
+  for (auto s : sizes) numel *= s;
+  int64_t bytes = numel * (int64_t)c10::elementSize(dtype);
+  TORCH_CHECK(offset_bytes >= 0 && (size_t)(offset_bytes + bytes) <= a->payload_bytes(),
+              "view exceeds the symmetric allocation");
+  char* base = (rank < 0 || !a->rendezvoused()) ? static_cast<char*>(a->local_ptr())
+                                                : static_cast<char*>(a->peer_ptr(rank));
+  auto opts = torch::TensorOptions().dtype(dtype).device(torch::kCPU);
+  return torch::from_blob(base + offset_bytes, sizes, [a](void*) {}, opts);
+}
+
+torch::Tensor host_pad_view(const std::shared_ptr<HostSymmAllocation>& a, int rank) {
+  char* base = (rank < 0 || !a->rendezvoused()) ? static_cast<char*>(a->local_ptr())
+                                                : static_cast<char*>(a->peer_ptr(rank));
+  auto opts = torch::TensorOptions().dtype(torch::kInt32).device(torch::kCPU);
+  return torch::from_blob(base + a->pad_offset(), {(int64_t)kSignalPadSlots}, [a](void*) {}, opts);
+}
+
+const uint16_t* bf16_ptr(const torch::Tensor& t) {
+  TORCH_CHECK(t.scalar_type() == torch::kBFloat16 && t.is_contiguous() && t.device().is_cpu(),
+              "expected a contiguous CPU bf16 tensor");
+  return reinterpret_cast<const uint16_t*>(t.data_ptr());
+}
+
+// Host all-reduce over shared memory: barrier, then the oracle's arithmetic.
+// algo: 0 one-shot (ordered bf16), 1 two-shot (ordered bf16, in place),
+//       2 "multimem" stand-in (fp32 accumulate, in place).
+py::tuple host_all_reduce(const std::shared_ptr<HostSymmAllocation>& a, int64_t offset_bytes,
+                          torch::Tensor out, int64_t numel, int algo, uint64_t timeout_ns) {
+  TORCH_CHECK(a->rendezvoused(), "symmetric allocation has not been rendezvoused");
+  const int ws = a->world_size(), rank = a->rank();
+  int peer = -1;
+  uint32_t code;
+  {
+    py::gil_scoped_release nogil;
+    code = a->barrier(0, timeout_ns, &peer);
+  }
+  if (code != kOk) return py::make_tuple(code, rank, 0, peer, (int)kWhereOneShotEntry, 0);
+  std::vector<const uint16_t*> srcs(ws);
+  for (int r = 0; r < ws; ++r)
+    srcs[r] = reinterpret_cast<const uint16_t*>(static_cast<char*>(a->peer_ptr(r)) + offset_bytes);
+  if (algo == 0) {
+    TORCH_CHECK(out.numel() == numel, "output size mismatch");
+    ordered_sum_bf16(srcs.data(), ws, reinterpret_cast<uint16_t*>(out.data_ptr()), (size_t)numel);
+    return py::make_tuple(0, rank, 0, 0, 0, 0);
+  }
+  // in-place algorithms: reduce own slice, publish to every peer, exit barrier
+  size_t n_vec = (size_t)numel / 8, q = n_vec / ws, rem = n_vec % ws;
+  size_t begin = (size_t)rank * q + std::min((size_t)rank, rem);
+  size_t end = begin + q + ((size_t)rank < rem ? 1 : 0);
+  std::vector<uint16_t> tmp((end - begin) * 8);
+  std::vector<const uint16_t*> sl(ws);
+  for (int r = 0; r < ws; ++r) sl[r] = srcs[r] + begin * 8;
+  if (algo == 1) ordered_sum_bf16(sl.data(), ws, tmp.data(), tmp.size());
+  else fp32_sum_bf16(sl.data(), ws, tmp.data(), tmp.size());
+  for (int r = 0; r < ws; ++r)
+    memcpy(const_cast<uint16_t*>(srcs[r]) + begin * 8, tmp.data(), tmp.size() * 2);
+  {
+    py::gil_scoped_release nogil;
+    code = a->barrier(0, timeout_ns, &peer);
+  }
+  return py::make_tuple(code, rank, 0, peer, (int)kWhereTwoShotExit, 0);
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.doc() = "symm_mem_recipes_b200 native module (sm_100a kernels + symmetric memory runtime)";
+  m.attr("SIGNAL_PAD_BYTES") = (int)kSignalPadBytes;
+  m.attr("BLOCK_SLOTS") = (int)kBlockSlots;
+  m.attr("CHANNEL_SLOTS") = (int)kChannelSlots;
+  m.attr("FLAG_SLOTS_BASE") = (int)kFlagSlotsBase;
+  m.attr("MAX_WORLD_SIZE") = (int)kMaxWorldSize;
+
+  py::class_<FdChannel, std::shared_ptr<FdChannel>>(m, "FdChannel")
+      .def(py::init<const std::string&>())
+      .def_property_readonly("name", &FdChannel::name)
+      .def("send_fd", &FdChannel::send_fd, py::call_guard<py::gil_scoped_release>())
+      .def("recv_fd",
+           [](const FdChannel& c, int timeout_ms) {
+             FdMessage msg;
+             {
+               py::gil_scoped_release nogil;
+               msg = c.recv_fd(timeout_ms);
+             }
+             return py::make_tuple(msg.fd, msg.src_rank, msg.tag);
+           });
+
+  py::class_<CudaSymmAllocation, std::shared_ptr<CudaSymmAllocation>>(m, "CudaSymmAllocation")
+      .def(py::init<int, size_t>())
+      .def_property_readonly("device", &CudaSymmAllocation::device)
+      .def_property_readonly("payload_bytes", &CudaSymmAllocation::payload_bytes)
+      .def_property_readonly("block_bytes", &CudaSymmAllocation::block_bytes)
+      .def_property_readonly("pad_offset", &CudaSymmAllocation::pad_offset)
+      .def_property_readonly("rank", &CudaSymmAllocation::rank)
+      .def_property_readonly("world_size", &CudaSymmAllocation::world_size)
+      .def_property_readonly("rendezvoused", &CudaSymmAllocation::rendezvoused)
+      .def_property_readonly("local_ptr", [](const CudaSymmAllocation& a) { return (uintptr_t)a.local_ptr(); })
+      .def_property_readonly("multicast_ptr", [](const CudaSymmAllocation& a) { return (uintptr_t)a.multicast_ptr(); })
+      .def_property_readonly("buffer_ptrs_dev", [](const CudaSymmAllocation& a) { return (uintptr_t)a.buffers_dev(); })
+      .def_property_readonly("signal_pad_ptrs_dev", [](const CudaSymmAllocation& a) { return (uintptr_t)a.pads_dev(); })
+      .def("peer_ptr", [](const CudaSymmAllocation& a, int r) { return (uintptr_t)a.peer_ptr(r); })
+      .def("begin_rendezvous", &CudaSymmAllocation::begin_rendezvous)
+      .def("exchange_and_map", &CudaSymmAllocation::exchange_and_map, py::call_guard<py::gil_scoped_release>())
+      .def("multicast_create_and_add", &CudaSymmAllocation::multicast_create_and_add,
+           py::call_guard<py::gil_scoped_release>())
+      .def("multicast_bind_and_map", &CudaSymmAllocation::multicast_bind_and_map)
+      .def("multicast_teardown", &CudaSymmAllocation::multicast_teardown)
+      .def("finish_rendezvous", &CudaSymmAllocation::finish_rendezvous)
+      .def("release", &CudaSymmAllocation::release)
+      .def_static("multicast_supported", &CudaSymmAllocation::multicast_supported);
+  m.def("cuda_view", &cuda_view, py::arg("alloc"), py::arg("rank"), py::arg("sizes"), py::arg("dtype"),
+        py::arg("offset_bytes"), py::arg("multicast") = false);
+  m.def("cuda_pad_view", &cuda_pad_view);
+
+  py::class_<HostSymmAllocation, std::shared_ptr<HostSymmAllocation>>(m, "HostSymmAllocation")
+      .def(py::init<const std::string&, size_t>())
+      .def_property_readonly("shm_name", &HostSymmAllocation::shm_name)
+      .def_property_readonly("payload_bytes", &HostSymmAllocation::payload_bytes)
+      .def_property_readonly("block_bytes", &HostSymmAllocation::block_bytes)
+      .def_property_readonly("pad_offset", &HostSymmAllocation::pad_offset)
+      .def_property_readonly("rank", &HostSymmAllocation::rank)
+      .def_property_readonly("world_size", &HostSymmAllocation::world_size)
+      .def_property_readonly("rendezvoused", &HostSymmAllocation::rendezvoused)
+      .def_property_readonly("local_ptr", [](const HostSymmAllocation& a) { return (uintptr_t)a.local_ptr(); })
+      .def("rendezvous", &HostSymmAllocation::rendezvous)
+      .def("release", &HostSymmAllocation::release)
+      .def("barrier",
+           [](HostSymmAllocation& a, uint32_t slot_base, uint64_t timeout_ns) {
+             int peer = -1;
+             uint32_t code;
+             {
+               py::gil_scoped_release nogil;
+               code = a.barrier(slot_base, timeout_ns, &peer);
+             }
+             return py::make_tuple(code, peer);
+           });
+  m.def("host_view", &host_view);
+  m.def("host_pad_view", &host_pad_view);
+  m.def("host_all_reduce", &host_all_reduce);
+
+  // ---- status ----
+  m.def("read_status", &read_status);
+
+  // ---- device ops ----
+  m.def("barrier_test", [](const std::shared_ptr<CudaSymmAllocation>& a, int blocks, int threads,
+                           uint64_t timeout_ns) {
+    c10::cuda::CUDAGuard guard(a->device());
+    rt_check(launch_barrier_test(view_of(*a), blocks, threads, timeout_ns, status_for(a->device()),
+                                 current_stream(a->device())), "barrier_test");
+  });
+  m.def("channel_barrier", [](const std::shared_ptr<CudaSymmAllocation>& a, int channel,
+                              uint64_t timeout_ns) {
+    c10::cuda::CUDAGuard guard(a->device());
+    rt_check(launch_channel_barrier(view_of(*a), channel, timeout_ns, status_for(a->device()),
+                                    current_stream(a->device())), "channel_barrier");
+  });
+  m.def("wait_flag", [](torch::Tensor flag, uint32_t target, uint64_t timeout_ns) {
+    TORCH_CHECK(flag.is_cuda() && flag.element_size() == 4, "flag must be a 32-bit CUDA tensor");
+    int dev = flag.get_device();
+    c10::cuda::CUDAGuard guard(dev);
+    rt_check(launch_wait_flag(reinterpret_cast<const uint32_t*>(flag.data_ptr()), target, timeout_ns, 0,
+                              status_for(dev), current_stream(dev)), "wait_flag");
+  });
+  m.def("one_shot_all_reduce", [](const std::shared_ptr<CudaSymmAllocation>& a, int64_t offset_bytes,
+                                  torch::Tensor out, int64_t numel, int max_blocks, bool exit_barrier,
+                                  uint64_t timeout_ns) {
+    TORCH_CHECK(out.is_cuda() && out.is_contiguous() && out.scalar_type() == torch::kBFloat16 &&
+                out.numel() == numel, "bad output tensor");
+    c10::cuda::CUDAGuard guard(a->device());
+    rt_check(launch_one_shot_all_reduce(view_of(*a), (size_t)offset_bytes, out.data_ptr(), (size_t)numel,
+                                        max_blocks, exit_barrier, timeout_ns, status_for(a->device()),
+                                        current_stream(a->device())), "one_shot_all_reduce");
+  });
+  m.def("two_shot_all_reduce", [](const std::shared_ptr<CudaSymmAllocation>& a, int64_t offset_bytes,
+                                  int64_t numel, int max_blocks, uint64_t timeout_ns) {
+    c10::cuda::CUDAGuard guard(a->device());
+    rt_check(launch_two_shot_all_reduce(view_of(*a), (size_t)offset_bytes, (size_t)numel, max_blocks,
+                                        timeout_ns, status_for(a->device()),
+                                        current_stream(a->device())), "two_shot_all_reduce");
+  });
+  m.def("multimem_all_reduce", [](const std::shared_ptr<CudaSymmAllocation>& a, int64_t offset_bytes,
+                                  int64_t numel, int max_blocks, uint64_t timeout_ns) {
+    c10::cuda::CUDAGuard guard(a->device());
+    rt_check(launch_multimem_all_reduce(view_of(*a), (size_t)offset_bytes, (size_t)numel, max_blocks,
+                                        timeout_ns, status_for(a->device()),
+                                        current_stream(a->device())), "multimem_all_reduce");
+  });
+
+  // ---- oracles (CPU tensors) ----
+  m.def("oracle_ordered_sum_bf16", [](std::vector<torch::Tensor> srcs) {
+    TORCH_CHECK(!srcs.empty(), "need at least one source");
+    std::vector<const uint16_t*> p;
+    for (auto& t : srcs) p.push_back(bf16_ptr(t));
+    torch::Tensor out = torch::empty_like(srcs[0]);
+    ordered_sum_bf16(p.data(), (int)p.size(), reinterpret_cast<uint16_t*>(out.data_ptr()), (size_t)out.numel());
+    return out;
+  });
+  m.def("oracle_fp32_sum_bf16", [](std::vector<torch::Tensor> srcs) {
+    TORCH_CHECK(!srcs.empty(), "need at least one source");
+    std::vector<const uint16_t*> p;
+    for (auto& t : srcs) p.push_back(bf16_ptr(t));
+    torch::Tensor out = torch::empty_like(srcs[0]);
+    fp32_sum_bf16(p.data(), (int)p.size(), reinterpret_cast<uint16_t*>(out.data_ptr()), (size_t)out.numel());
+    return out;
+  });
+  m.def("oracle_gemm_nt_bf16", [](torch::Tensor a, torch::Tensor b) {
+    TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.size(1) == b.size(1), "A[M,K], B[N,K]");
+    torch::Tensor c = torch::empty({a.size(0), b.size(0)}, a.options());
+    gemm_nt_bf16(bf16_ptr(a), bf16_ptr(b), reinterpret_cast<uint16_t*>(c.data_ptr()), (int)a.size(0),
+                 (int)b.size(0), (int)a.size(1));
+    return c;
+  });
+  m.def("oracle_gemv_f32", [](torch::Tensor x, torch::Tensor w) {
+    TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && x.size(1) == w.size(0), "x[B,K], w[K,N]");
+    torch::Tensor y = torch::empty({x.size(0), w.size(1)}, x.options().dtype(torch::kFloat32));
+    gemv_f32(bf16_ptr(x), bf16_ptr(w), y.data_ptr<float>(), (int)x.size(0), (int)x.size(1), (int)w.size(1));
+    return y;
+  });
+}

@@ -1,0 +1,243 @@
+// Barrier and all-reduce kernels over symmetric memory (bf16).
+//
+//  * one-shot:  every rank reads all WS peer buffers and sums them, in rank
+//    order 0..WS-1 starting from +0 with bf16 adds.  Same arithmetic, hence
+//    same bits on every rank, as
+//    symm_mem_recipes/triton_one_shot_all_reduce.py:59-93; the loads are issued
+//    starting at the rank's own neighbour so that the WS-1 links are busy at
+//    once (upstream loads peer 0 first on every rank, :86-88).
+//  * two-shot:  rank r reduces slice r (reduce-scatter by peer loads) and
+//    stores the result into slice r of every peer (all-gather by peer stores).
+//  * multimem:  rank r reduces slice r inside the NVSwitch
+//    (multimem.ld_reduce, fp32 accumulate) and broadcasts it (multimem.st).
+//
+// None of them has a counterpart launch parameter that must change between
+// calls: barriers return the pad to zero, so a captured graph replays.
+#include <cuda_runtime.h>
+
+#include "../device/barrier.cuh"
+#include "../device/multimem.cuh"
+#include "../device/vec.cuh"
+#include "launch.h"
+
+namespace smr {
+
+namespace {
+
+constexpr int kArThreads = 512;
+
+__global__ void barrier_test_kernel(PeerView pv, uint64_t timeout_ns, Status* st) {
+  blockwise_barrier(pv.pads, flat_block_id(), pv.rank, pv.world_size, timeout_ns, st, kWhereTest);
+}
+
+// One CTA; slot = kBlockSlots + channel * WS + sender.
+__global__ void channel_barrier_kernel(PeerView pv, int channel, uint64_t timeout_ns, Status* st) {
+  int t = threadIdx.x;
+  if (t < pv.world_size) {
+    barrier_signal_wait(pv.pads, kBlockSlots + (uint32_t)channel * (uint32_t)pv.world_size,
+                        pv.rank, pv.world_size, t, timeout_ns, st, (uint32_t)channel,
+                        kWhereBarrierKernel);
+  }
+}
+
+__global__ void wait_flag_kernel(const uint32_t* flag, uint32_t target, uint64_t timeout_ns,
+                                 int rank, Status* st) {
+  if (threadIdx.x == 0) {
+    if (!wait_ge_acquire_sys(flag, target, timeout_ns)) {
+      report_status(st, kTimeoutFlag, rank, blockIdx.x, 0, kWhereTest, target);
+    }
+  }
+}
+
+template <int WS>
+__global__ void __launch_bounds__(kArThreads)
+one_shot_all_reduce_kernel(PeerView pv, size_t offset_bytes, Vec16* __restrict__ out,
+                           size_t n_vec, bool exit_barrier, uint64_t timeout_ns, Status* st) {
+  const int rank = pv.rank;
+  if (!blockwise_barrier(pv.pads, blockIdx.x, rank, WS, timeout_ns, st, kWhereOneShotEntry))
+    return;
+
+  const Vec16* src[WS];
+#pragma unroll
+  for (int r = 0; r < WS; ++r)
+    src[r] = reinterpret_cast<const Vec16*>(static_cast<const char*>(pv.buffers[r]) + offset_bytes);
+
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += stride) {
+    Vec16 v[WS];
+    // issue order staggered by rank; register slot = source rank
+#pragma unroll
+    for (int j = 0; j < WS; ++j) {
+      int r = (rank + 1 + j) % WS;
+#pragma unroll
+      for (int k = 0; k < WS; ++k)
+        if (k == r) v[k] = ld_16(src[k] + i);
+    }
+    Vec16 acc = {0u, 0u, 0u, 0u};
+#pragma unroll
+    for (int r = 0; r < WS; ++r) acc = add_bf16x8(acc, v[r]);
+    st_16(out + i, acc);
+  }
+
+  if (exit_barrier) {
+    // proves that every peer has finished reading this rank's buffer
+    blockwise_barrier(pv.pads, blockIdx.x, rank, WS, timeout_ns, st, kWhereOneShotExit);
+  }
+}
+
+// Slice of 16-byte vectors owned by `r`: [begin, end)
+__device__ __forceinline__ void slice_of(size_t n_vec, int ws, int r, size_t& begin, size_t& end) {
+  size_t q = n_vec / ws, rem = n_vec % ws;
+  begin = (size_t)r * q + ((size_t)r < rem ? (size_t)r : rem);
+  end = begin + q + ((size_t)r < rem ? 1 : 0);
+}
+
+template <int WS>
+__global__ void __launch_bounds__(kArThreads)
+two_shot_all_reduce_kernel(PeerView pv, size_t offset_bytes, size_t n_vec, uint64_t timeout_ns,
+                           Status* st) {
+  const int rank = pv.rank;
+  if (!blockwise_barrier(pv.pads, blockIdx.x, rank, WS, timeout_ns, st, kWhereTwoShotEntry))
+    return;
+
+  Vec16* buf[WS];
+#pragma unroll
+  for (int r = 0; r < WS; ++r)
+    buf[r] = reinterpret_cast<Vec16*>(static_cast<char*>(pv.buffers[r]) + offset_bytes);
+
+  size_t begin, end;
+  slice_of(n_vec, WS, rank, begin, end);
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = begin + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < end; i += stride) {
+    Vec16 v[WS];
+#pragma unroll
+    for (int j = 0; j < WS; ++j) {
+      int r = (rank + 1 + j) % WS;
+#pragma unroll
+      for (int k = 0; k < WS; ++k)
+        if (k == r) v[k] = ld_16(buf[k] + i);
+    }
+    Vec16 acc = {0u, 0u, 0u, 0u};
+#pragma unroll
+    for (int r = 0; r < WS; ++r) acc = add_bf16x8(acc, v[r]);
+    // Element i of every peer is read by this thread only (above), so the
+    // in-place push cannot overtake a reader.
+#pragma unroll
+    for (int j = 0; j < WS; ++j) {
+      int r = (rank + 1 + j) % WS;
+#pragma unroll
+      for (int k = 0; k < WS; ++k)
+        if (k == r) st_16(buf[k] + i, acc);
+    }
+  }
+  // All pushes of all ranks have landed once every CTA has passed this.
+  blockwise_barrier(pv.pads, blockIdx.x, rank, WS, timeout_ns, st, kWhereTwoShotExit);
+}
+
+__global__ void __launch_bounds__(kArThreads)
+multimem_all_reduce_kernel(PeerView pv, size_t offset_bytes, size_t n_vec, uint64_t timeout_ns,
+                           Status* st) {
+  const int rank = pv.rank, ws = pv.world_size;
+  if (!blockwise_barrier(pv.pads, blockIdx.x, rank, ws, timeout_ns, st, kWhereMultimemEntry))
+    return;
+  Vec16* mc = reinterpret_cast<Vec16*>(static_cast<char*>(pv.multicast) + offset_bytes);
+  size_t begin, end;
+  slice_of(n_vec, ws, rank, begin, end);
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  size_t i = begin + (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  // two independent reductions in flight per thread
+  for (; i + stride < end; i += 2 * stride) {
+    Vec16 a = multimem_ld_reduce_bf16x8(mc + i);
+    Vec16 b = multimem_ld_reduce_bf16x8(mc + i + stride);
+    multimem_st_16(mc + i, a);
+    multimem_st_16(mc + i + stride, b);
+  }
+  if (i < end) {
+    Vec16 a = multimem_ld_reduce_bf16x8(mc + i);
+    multimem_st_16(mc + i, a);
+  }
+  blockwise_barrier(pv.pads, blockIdx.x, rank, ws, timeout_ns, st, kWhereMultimemExit);
+}
+
+int blocks_for(size_t n_vec, int max_blocks) {
+  size_t b = (n_vec + kArThreads - 1) / kArThreads;
+  if (b < 1) b = 1;
+  if (b > (size_t)max_blocks) b = max_blocks;
+  return (int)b;
+}
+
+int last_error() { return (int)cudaGetLastError(); }
+
+}  // namespace
+
+int launch_barrier_test(const PeerView& pv, int num_blocks, int threads, uint64_t timeout_ns,
+                        Status* status, cudaStream_t stream) {
+  if (num_blocks < 1 || (uint32_t)num_blocks * pv.world_size > kBlockSlots) return cudaErrorInvalidValue;
+  if (threads < pv.world_size) return cudaErrorInvalidValue;
+  barrier_test_kernel<<<num_blocks, threads, 0, stream>>>(pv, timeout_ns, status);
+  return last_error();
+}
+
+int launch_channel_barrier(const PeerView& pv, int channel, uint64_t timeout_ns, Status* status,
+                           cudaStream_t stream) {
+  if (channel < 0 || (uint32_t)(channel + 1) * pv.world_size > kChannelSlots) return cudaErrorInvalidValue;
+  channel_barrier_kernel<<<1, 32, 0, stream>>>(pv, channel, timeout_ns, status);
+  return last_error();
+}
+
+int launch_wait_flag(const uint32_t* flag, uint32_t target, uint64_t timeout_ns, int rank,
+                     Status* status, cudaStream_t stream) {
+  wait_flag_kernel<<<1, 32, 0, stream>>>(flag, target, timeout_ns, rank, status);
+  return last_error();
+}
+
+#define SMR_DISPATCH_WS(ws, ...)                      \
+  switch (ws) {                                       \
+    case 1: { constexpr int WS = 1; __VA_ARGS__; break; } \
+    case 2: { constexpr int WS = 2; __VA_ARGS__; break; } \
+    case 4: { constexpr int WS = 4; __VA_ARGS__; break; } \
+    case 8: { constexpr int WS = 8; __VA_ARGS__; break; } \
+    default: return cudaErrorInvalidValue;            \
+  }
+
+int launch_one_shot_all_reduce(const PeerView& pv, size_t offset_bytes, void* out, size_t numel,
+                               int max_blocks, bool exit_barrier, uint64_t timeout_ns,
+                               Status* status, cudaStream_t stream) {
+  if (numel % 8 != 0 || offset_bytes % 16 != 0) return cudaErrorInvalidValue;
+  size_t n_vec = numel / 8;
+  if ((uint32_t)max_blocks * pv.world_size > kBlockSlots) max_blocks = kBlockSlots / pv.world_size;
+  int blocks = blocks_for(n_vec, max_blocks);
+  SMR_DISPATCH_WS(pv.world_size,
+                  one_shot_all_reduce_kernel<WS><<<blocks, kArThreads, 0, stream>>>(
+                      pv, offset_bytes, static_cast<Vec16*>(out), n_vec, exit_barrier, timeout_ns,
+                      status));
+  return last_error();
+}
+
+int launch_two_shot_all_reduce(const PeerView& pv, size_t offset_bytes, size_t numel,
+                               int max_blocks, uint64_t timeout_ns, Status* status,
+                               cudaStream_t stream) {
+  if (numel % 8 != 0 || offset_bytes % 16 != 0) return cudaErrorInvalidValue;
+  size_t n_vec = numel / 8;
+  if ((uint32_t)max_blocks * pv.world_size > kBlockSlots) max_blocks = kBlockSlots / pv.world_size;
+  int blocks = blocks_for((n_vec + pv.world_size - 1) / pv.world_size, max_blocks);
+  SMR_DISPATCH_WS(pv.world_size,
+                  two_shot_all_reduce_kernel<WS><<<blocks, kArThreads, 0, stream>>>(
+                      pv, offset_bytes, n_vec, timeout_ns, status));
+  return last_error();
+}
+
+int launch_multimem_all_reduce(const PeerView& pv, size_t offset_bytes, size_t numel,
+                               int max_blocks, uint64_t timeout_ns, Status* status,
+                               cudaStream_t stream) {
+  if (numel % 8 != 0 || offset_bytes % 16 != 0) return cudaErrorInvalidValue;
+  if (pv.multicast == nullptr) return cudaErrorNotSupported;
+  size_t n_vec = numel / 8;
+  if ((uint32_t)max_blocks * pv.world_size > kBlockSlots) max_blocks = kBlockSlots / pv.world_size;
+  int blocks = blocks_for((n_vec + pv.world_size - 1) / pv.world_size, max_blocks);
+  multimem_all_reduce_kernel<<<blocks, kArThreads, 0, stream>>>(pv, offset_bytes, n_vec,
+                                                                 timeout_ns, status);
+  return last_error();
+}
+
+}  // namespace smr

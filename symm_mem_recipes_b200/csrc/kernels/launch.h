@@ -1,0 +1,43 @@
+// C launchers of every kernel in the library.  They take raw device pointers
+// and a stream, include no framework header, and return a cudaError_t-style
+// int (0 = launched).  The Python bindings and the C ABI both go through them.
+#pragma once
+#include <cuda_runtime_api.h>
+#include <stdint.h>
+
+#include "../device/status.h"
+
+namespace smr {
+
+// Pointers a kernel needs to reach its peers; all tables live in device memory.
+struct PeerView {
+  void* const* buffers;        // [world_size] payload base of every rank (mapped locally)
+  uint32_t* const* pads;       // [world_size] signal-pad base of every rank
+  void* multicast;             // multicast payload base or nullptr
+  int rank;
+  int world_size;
+};
+
+// ---- barrier ---------------------------------------------------------------
+int launch_barrier_test(const PeerView& pv, int num_blocks, int threads, uint64_t timeout_ns,
+                        Status* status, cudaStream_t stream);
+int launch_channel_barrier(const PeerView& pv, int channel, uint64_t timeout_ns, Status* status,
+                           cudaStream_t stream);
+// Waits on a flag nothing sets unless `*flag >= target`; used to prove that a
+// timed-out wait returns an error status and leaves the device usable.
+int launch_wait_flag(const uint32_t* flag, uint32_t target, uint64_t timeout_ns, int rank,
+                     Status* status, cudaStream_t stream);
+
+// ---- all-reduce (bf16) -----------------------------------------------------
+// `offset_bytes` is the offset of the tensor inside the symmetric payload.
+int launch_one_shot_all_reduce(const PeerView& pv, size_t offset_bytes, void* out, size_t numel,
+                               int max_blocks, bool exit_barrier, uint64_t timeout_ns,
+                               Status* status, cudaStream_t stream);
+int launch_two_shot_all_reduce(const PeerView& pv, size_t offset_bytes, size_t numel,
+                               int max_blocks, uint64_t timeout_ns, Status* status,
+                               cudaStream_t stream);
+int launch_multimem_all_reduce(const PeerView& pv, size_t offset_bytes, size_t numel,
+                               int max_blocks, uint64_t timeout_ns, Status* status,
+                               cudaStream_t stream);
+
+}  // namespace smr

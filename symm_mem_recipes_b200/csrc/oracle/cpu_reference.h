@@ -1,0 +1,41 @@
+// CPU oracles: the arithmetic contract of every kernel, in plain C++.
+//
+//  * ordered bf16 sum: acc = +0; acc = bf16(acc + x_r) for r = 0..WS-1, one
+//    round-to-nearest-even per add.  Bit-for-bit what the one-shot and
+//    two-shot kernels (and symm_mem_recipes/triton_one_shot_all_reduce.py:84-89)
+//    compute.
+//  * fp32 sum: accumulate in fp32 in rank order, round to bf16 once (what the
+//    NVSwitch does for multimem.ld_reduce with .acc::f32, up to its own
+//    summation order).
+//  * GEMM / GEMV: fp32 accumulate over K, round to bf16 once.
+#pragma once
+#include <stddef.h>
+#include <stdint.h>
+
+namespace smr {
+
+inline float bf16_to_f32(uint16_t v) {
+  uint32_t u = (uint32_t)v << 16;
+  float f;
+  __builtin_memcpy(&f, &u, 4);
+  return f;
+}
+// round to nearest even; NaN stays NaN
+inline uint16_t f32_to_bf16(float f) {
+  uint32_t u;
+  __builtin_memcpy(&u, &f, 4);
+  if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x40u);
+  u += 0x7fffu + ((u >> 16) & 1u);
+  return (uint16_t)(u >> 16);
+}
+
+// out[i] = ordered bf16 sum over srcs[0..n_src)
+void ordered_sum_bf16(const uint16_t* const* srcs, int n_src, uint16_t* out, size_t numel);
+// out[i] = bf16( sum_r float(srcs[r][i]) )
+void fp32_sum_bf16(const uint16_t* const* srcs, int n_src, uint16_t* out, size_t numel);
+// C[M,N] = A[M,K] * B[N,K]^T, bf16 in, fp32 accumulate, bf16 out (row-major)
+void gemm_nt_bf16(const uint16_t* a, const uint16_t* b, uint16_t* c, int M, int N, int K);
+// y[B,N] (fp32) = x[B,K] * w[K,N]
+void gemv_f32(const uint16_t* x, const uint16_t* w, float* y, int B, int K, int N);
+
+}  // namespace smr

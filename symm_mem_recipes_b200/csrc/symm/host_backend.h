@@ -1,0 +1,59 @@
+// Symmetric memory on the CPU: POSIX shared memory blocks (payload + signal
+// pad) mapped by every rank of the host, and the same barrier / all-reduce
+// protocols executed with host atomics.  It exists so that the allocator API,
+// the rendezvous, the dispatcher and the barrier state machine can be tested
+// with `gloo` ranks on a machine without a GPU.
+#pragma once
+#include <stdint.h>
+
+#include <string>
+#include <vector>
+
+#include "../device/pad_layout.h"
+#include "../device/status.h"
+
+namespace smr {
+
+class HostSymmAllocation {
+ public:
+  // Creates /dev/shm/<name> of payload + pad bytes, zero-filled.
+  HostSymmAllocation(const std::string& shm_name, size_t payload_bytes);
+  ~HostSymmAllocation();
+  HostSymmAllocation(const HostSymmAllocation&) = delete;
+  HostSymmAllocation& operator=(const HostSymmAllocation&) = delete;
+
+  const std::string& shm_name() const { return name_; }
+  size_t payload_bytes() const { return payload_bytes_; }
+  size_t pad_offset() const { return pad_offset_; }
+  size_t block_bytes() const { return block_bytes_; }
+  void* local_ptr() const { return base_; }
+
+  // Maps the peers' blocks by name (names[rank] must be this block's name).
+  void rendezvous(int rank, const std::vector<std::string>& names);
+  bool rendezvoused() const { return rendezvoused_; }
+  int rank() const { return rank_; }
+  int world_size() const { return world_size_; }
+  void* peer_ptr(int r) const { return peers_.at(r); }
+  uint32_t* peer_pad(int r) const {
+    return reinterpret_cast<uint32_t*>(static_cast<char*>(peers_.at(r)) + pad_offset_);
+  }
+  void release();
+
+  // Same slot protocol as the device barrier; `slot_base` selects block or
+  // channel slots.  Returns a StatusCode (kOk on success) and fills `peer`.
+  uint32_t barrier(uint32_t slot_base, uint64_t timeout_ns, int* failed_peer);
+
+ private:
+  std::string name_;
+  size_t payload_bytes_, pad_offset_, block_bytes_;
+  void* base_ = nullptr;
+  int rank_ = -1, world_size_ = 0;
+  std::vector<void*> peers_;
+  bool rendezvoused_ = false, released_ = false;
+};
+
+// Barrier protocol on bare pads (used by the multi-threaded protocol tests).
+uint32_t host_barrier_signal_wait(uint32_t* const* pads, uint32_t slot_base, int rank,
+                                  int world_size, uint64_t timeout_ns, int* failed_peer);
+
+}  // namespace smr

@@ -1,0 +1,3 @@
+from .all_reduce import (all_reduce, choose_algo, multimem_all_reduce_,  # noqa: F401
+                         one_shot_all_reduce, two_shot_all_reduce_)
+from .barrier import barrier_test, wait_flag  # noqa: F401

@@ -1,0 +1,112 @@
+"""bf16 all-reduce over symmetric memory: one-shot, two-shot, multimem and a
+size-based dispatcher.
+
+`one_shot_all_reduce(tensor)` keeps the contract of
+symm_mem_recipes/triton_one_shot_all_reduce.py:96-125: bf16, numel % 8 == 0,
+symmetric input, a fresh local output, and the same bits on every rank
+(ordered bf16 sum).  The in-place variants have no upstream counterpart.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .._ext import C
+from ..errors import SymmMemError, raise_for_status
+from ..parallel import symm_mem
+from .config import DEFAULT_ALL_REDUCE, AllReduceConfig
+
+_ALGOS = ("auto", "one_shot", "two_shot", "multimem")
+
+
+def _prepare(t: torch.Tensor):
+    if t.dtype != torch.bfloat16:
+        raise SymmMemError("only bfloat16 is supported")
+    if t.numel() % 8 != 0:
+        raise SymmMemError("the number of elements must be a multiple of 8 (128-bit accesses)")
+    if not t.is_contiguous():
+        raise SymmMemError("the tensor must be contiguous")
+    rec, offset = symm_mem._find_record(t)
+    hdl = symm_mem.rendezvous(t)
+    if offset % 16 != 0:
+        raise SymmMemError("the tensor must start on a 16-byte boundary of its allocation")
+    return hdl, offset
+
+
+def one_shot_all_reduce(t: torch.Tensor, *, exit_barrier: bool = False,
+                        out: Optional[torch.Tensor] = None,
+                        config: AllReduceConfig = DEFAULT_ALL_REDUCE) -> torch.Tensor:
+    """Sum of `t` over all ranks, returned as a new local tensor.
+
+    As upstream, there is no trailing barrier by default: do not overwrite `t`
+    until every peer is known to have finished (the next collective on the same
+    group proves it), or pass `exit_barrier=True`.
+    """
+    hdl, offset = _prepare(t)
+    if out is None:
+        out = torch.empty_like(t)
+    t_ns = config.timeout_ms * 1_000_000
+    if hdl.kind == "cuda":
+        C.one_shot_all_reduce(hdl.native, offset, out, t.numel(), config.one_shot_max_blocks,
+                              exit_barrier, t_ns)
+    else:
+        raise_for_status(C.host_all_reduce(hdl.native, offset, out, t.numel(), 0, t_ns))
+        if exit_barrier:
+            hdl.barrier(channel=1, timeout_ms=config.timeout_ms)
+    return out
+
+
+def two_shot_all_reduce_(t: torch.Tensor, *, config: AllReduceConfig = DEFAULT_ALL_REDUCE) -> torch.Tensor:
+    """In place: rank r reduces slice r from all peers (ordered bf16 sum) and
+    stores it into slice r of every peer.  Returns `t`."""
+    hdl, offset = _prepare(t)
+    t_ns = config.timeout_ms * 1_000_000
+    if hdl.kind == "cuda":
+        C.two_shot_all_reduce(hdl.native, offset, t.numel(), config.two_shot_max_blocks, t_ns)
+    else:
+        raise_for_status(C.host_all_reduce(hdl.native, offset, t, t.numel(), 1, t_ns))
+    return t
+
+
+def multimem_all_reduce_(t: torch.Tensor, *, config: AllReduceConfig = DEFAULT_ALL_REDUCE) -> torch.Tensor:
+    """In place through the NVSwitch: multimem.ld_reduce (fp32 accumulate, one
+    bf16 rounding) of slice r, multimem.st of the result.  Returns `t`."""
+    hdl, offset = _prepare(t)
+    t_ns = config.timeout_ms * 1_000_000
+    if hdl.kind == "cuda":
+        if hdl.world_size == 1:
+            return t
+        if not hdl.has_multicast:
+            raise SymmMemError("this allocation has no multicast mapping (NVLS unavailable)")
+        C.multimem_all_reduce(hdl.native, offset, t.numel(), config.multimem_max_blocks, t_ns)
+    else:
+        raise_for_status(C.host_all_reduce(hdl.native, offset, t, t.numel(), 2, t_ns))
+    return t
+
+
+def choose_algo(nbytes: int, world_size: int, has_multicast: bool,
+                config: AllReduceConfig = DEFAULT_ALL_REDUCE) -> str:
+    """The dispatcher's decision, exposed for tests and benchmarks."""
+    if world_size == 1 or nbytes <= config.one_shot_max_bytes:
+        return "one_shot"
+    return "multimem" if has_multicast else "two_shot"
+
+
+def all_reduce(t: torch.Tensor, algo: str = "auto", *,
+               config: AllReduceConfig = DEFAULT_ALL_REDUCE) -> torch.Tensor:
+    """All-reduce of a symmetric bf16 tensor; the result is returned in `t`
+    itself for the in-place algorithms and copied into `t` for one-shot, so the
+    caller always reads the sum from the returned tensor (`t`)."""
+    if algo not in _ALGOS:
+        raise SymmMemError(f"algo must be one of {_ALGOS}")
+    if algo == "auto":
+        hdl = symm_mem.rendezvous(t)
+        algo = choose_algo(t.numel() * t.element_size(), hdl.world_size, hdl.has_multicast, config)
+    if algo == "one_shot":
+        out = one_shot_all_reduce(t, exit_barrier=True, config=config)
+        t.copy_(out)
+        return t
+    if algo == "two_shot":
+        return two_shot_all_reduce_(t, config=config)
+    return multimem_all_reduce_(t, config=config)

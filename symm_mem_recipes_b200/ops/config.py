@@ -1,0 +1,29 @@
+"""Per-op configuration: one dataclass per op, overridable by `SMR_*`
+environment variables (the upstream recipes use module constants and a plain
+dict of tile sizes: symm_mem_recipes/triton_one_shot_all_reduce.py:97-100,
+symm_mem_recipes/triton_all_gather_matmul.py:380-388)."""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+
+
+def _env_int(name: str, default: int) -> int:
+    v = os.environ.get(name)
+    return int(v) if v not in (None, "") else default
+
+
+@dataclass
+class AllReduceConfig:
+    # Message sizes (bytes) up to which each algorithm is picked by `algo="auto"`.
+    one_shot_max_bytes: int = _env_int("SMR_AR_ONE_SHOT_MAX_BYTES", 256 * 1024)
+    # Above one-shot: multimem when a multicast mapping exists, else two-shot.
+    # CTA caps.  Upstream caps its one-shot kernel at 24 CTAs of 512 threads
+    # (triton_one_shot_all_reduce.py:97-109); large messages want more.
+    one_shot_max_blocks: int = _env_int("SMR_AR_ONE_SHOT_MAX_BLOCKS", 32)
+    two_shot_max_blocks: int = _env_int("SMR_AR_TWO_SHOT_MAX_BLOCKS", 64)
+    multimem_max_blocks: int = _env_int("SMR_AR_MULTIMEM_MAX_BLOCKS", 32)
+    timeout_ms: int = _env_int("SMR_TIMEOUT_MS", 10000)
+
+
+DEFAULT_ALL_REDUCE = AllReduceConfig()

@@ -1,0 +1,44 @@
+"""Out-of-band exchange between ranks through a torch.distributed Store.
+
+The rendezvous of a symmetric allocation needs a few small host-side messages
+(socket names, sizes, phase barriers).  They go through the process group's
+Store (TCPStore under torchrun), never through the GPU, so the same code
+serves `nccl` and `gloo` groups.
+"""
+from __future__ import annotations
+
+import pickle
+from datetime import timedelta
+
+import torch.distributed as dist
+
+
+def _store_of(group) -> "dist.Store":
+    c10d = dist.distributed_c10d
+    if group is None or group is dist.group.WORLD:
+        return c10d._get_default_store()
+    return c10d._get_process_group_store(group)
+
+
+class StoreExchange:
+    """all_gather / barrier of picklable objects among the ranks of a group."""
+
+    def __init__(self, group=None, namespace: str = "smr", timeout_s: float = 120.0):
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world_size = dist.get_world_size(group)
+        name = "world" if group is None else getattr(group, "group_name", str(id(group)))
+        self.store = dist.PrefixStore(f"{namespace}/{name}", _store_of(group))
+        self.timeout = timedelta(seconds=timeout_s)
+        self._seq = 0
+
+    def all_gather(self, obj) -> list:
+        seq = self._seq
+        self._seq += 1
+        self.store.set(f"{seq}/{self.rank}", pickle.dumps(obj))
+        keys = [f"{seq}/{r}" for r in range(self.world_size)]
+        self.store.wait(keys, self.timeout)
+        return [pickle.loads(self.store.get(k)) for k in keys]
+
+    def barrier(self) -> None:
+        self.all_gather(None)

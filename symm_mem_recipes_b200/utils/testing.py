@@ -1,0 +1,90 @@
+"""Helpers for multi-rank tests: run a function as N ranks of one host.
+
+CPU tests use backend "gloo"; GPU tests use "nccl" with one GPU per rank.  The
+rendezvous address is always 127.0.0.1.
+"""
+from __future__ import annotations
+
+import os
+import socket
+import traceback
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def free_port() -> int:
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _entry(rank: int, world_size: int, backend: str, port: int, fn, args, errq):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["RANK"] = str(rank)
+    os.environ["LOCAL_RANK"] = str(rank)
+    os.environ["WORLD_SIZE"] = str(world_size)
+    ok = False
+    try:
+        if backend == "nccl":
+            torch.cuda.set_device(rank)
+            dist.init_process_group("nccl", rank=rank, world_size=world_size,
+                                    device_id=torch.device("cuda", rank))
+        else:
+            dist.init_process_group(backend, rank=rank, world_size=world_size)
+        fn(rank, world_size, *args)
+        ok = True
+    except BaseException:  # noqa: BLE001 - reported to the parent
+        errq.put((rank, traceback.format_exc()))
+    finally:
+        # Orderly teardown even after a failure: every rank unbinds its
+        # multicast memory only after meeting the others (or a short timeout).
+        try:
+            from symm_mem_recipes_b200.parallel import symm_mem
+            symm_mem.shutdown()
+        except BaseException:  # noqa: BLE001
+            if ok:
+                errq.put((rank, traceback.format_exc()))
+        try:
+            dist.destroy_process_group()
+        except BaseException:  # noqa: BLE001
+            pass
+
+
+def spawn_ranks(fn, world_size: int, backend: str = "gloo", args=(), timeout_s: float = 300.0) -> None:
+    """Run `fn(rank, world_size, *args)` in `world_size` fresh processes and
+    raise in the parent if any rank failed or the deadline passed."""
+    ctx = mp.get_context("spawn")
+    errq = ctx.Queue()
+    port = free_port()
+    procs = [ctx.Process(target=_entry, args=(r, world_size, backend, port, fn, args, errq))
+             for r in range(world_size)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout_s)
+    hung = [p for p in procs if p.is_alive()]
+    for p in hung:
+        p.terminate()
+        p.join(10)
+    errors = []
+    while not errq.empty():
+        errors.append(errq.get())
+    if hung:
+        errors.append((-1, f"{len(hung)} rank(s) did not finish within {timeout_s} s"))
+    bad_exit = [(i, p.exitcode) for i, p in enumerate(procs) if p.exitcode not in (0, None)]
+    if errors or bad_exit:
+        msg = "\n".join(f"--- rank {r} ---\n{tb}" for r, tb in errors)
+        raise RuntimeError(f"rank failure(s); exit codes {bad_exit}\n{msg}")
+
+
+def seeded_normal_bf16(numel: int, rank: int, device="cpu", std: float = 1.0, seed: int = 42) -> torch.Tensor:
+    """bf16 N(0, std) values that depend only on (seed, rank): every process
+    can regenerate any rank's input (upstream seeds with 42 + rank,
+    symm_mem_recipes/triton_all_gather_matmul.py:364)."""
+    g = torch.Generator(device="cpu")
+    g.manual_seed(seed + rank)
+    t = (torch.randn(numel, generator=g, dtype=torch.float32) * std).to(torch.bfloat16)
+    return t.to(device)
