@@ -85,15 +85,25 @@ torch::Tensor cuda_view(const std::shared_ptr<CudaSymmAllocation>& a, int rank,
     base = static_cast<char*>(a->peer_ptr(rank));
   }
   auto opts = torch::TensorOptions().dtype(dtype).device(torch::kCUDA, a->device());
-  // The deleter keeps the allocation alive for as long as a view exists.
-  return torch::from_blob(base + offset_bytes, sizes, [a](void*) {}, opts);
+  // The deleter keeps the allocation alive for as long as a view exists.  A
+  // peer or multicast mapping reports the peer's device to the pointer query;
+  // target_device pins the view to the device that maps it.
+  return at::for_blob(base + offset_bytes, sizes)
+      .deleter([a](void*) {})
+      .options(opts)
+      .target_device(c10::Device(c10::kCUDA, a->device()))
+      .make_tensor();
 }
 
 torch::Tensor cuda_pad_view(const std::shared_ptr<CudaSymmAllocation>& a, int rank) {
   char* base = (rank < 0 || !a->rendezvoused()) ? static_cast<char*>(a->local_ptr())
                                                 : static_cast<char*>(a->peer_ptr(rank));
   auto opts = torch::TensorOptions().dtype(torch::kInt32).device(torch::kCUDA, a->device());
-  return torch::from_blob(base + a->pad_offset(), {(int64_t)kSignalPadSlots}, [a](void*) {}, opts);
+  return at::for_blob(base + a->pad_offset(), {(int64_t)kSignalPadSlots})
+      .deleter([a](void*) {})
+      .options(opts)
+      .target_device(c10::Device(c10::kCUDA, a->device()))
+      .make_tensor();
 }
 
 torch::Tensor host_view(const std::shared_ptr<HostSymmAllocation>& a, int rank,
@@ -286,6 +296,57 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                                         timeout_ns, status_for(a->device()),
                                         current_stream(a->device())), "multimem_all_reduce");
   });
+
+  // a: own shard (or all of A when alloc is None), b: [N, K], c: [M, N]
+  m.def("ag_matmul", [](torch::Tensor a, torch::Tensor b, torch::Tensor c,
+                        std::shared_ptr<CudaSymmAllocation> alloc, int64_t shard_offset,
+                        c10::optional<torch::Tensor> a_out, c10::optional<torch::Tensor> flags,
+                        int block_n, int num_sms, int n_copy, uint64_t timeout_ns) {
+    auto ok2d = [](const torch::Tensor& t) {
+      return t.is_cuda() && t.dim() == 2 && t.is_contiguous() && t.scalar_type() == torch::kBFloat16;
+    };
+    TORCH_CHECK(ok2d(a) && ok2d(b) && ok2d(c), "a, b, c must be contiguous 2-D bf16 CUDA tensors");
+    TORCH_CHECK(a.size(1) == b.size(1), "A[*, K] and B[N, K] disagree on K");
+    int dev = a.get_device();
+    c10::cuda::CUDAGuard guard(dev);
+    cudaStream_t stream = current_stream(dev);
+    AgMatmulArgs args{};
+    args.a_local = a.data_ptr();
+    args.b = b.data_ptr();
+    args.c = c.data_ptr();
+    args.N = (int)b.size(0);
+    args.K = (int)a.size(1);
+    args.block_n = block_n;
+    args.num_sms = num_sms;
+    args.timeout_ns = timeout_ns;
+    args.status = status_for(dev);
+    if (alloc && n_copy > 0) {
+      TORCH_CHECK(a_out.has_value() && flags.has_value(), "a_out and flags are required with communication");
+      PeerView pv = view_of(*alloc);
+      args.n_copy = n_copy;
+      args.rank = pv.rank;
+      args.world_size = pv.world_size;
+      args.rows_per_rank = (int)a.size(0);
+      args.M = args.rows_per_rank * pv.world_size;
+      args.buffers = pv.buffers;
+      args.shard_offset = (size_t)shard_offset;
+      TORCH_CHECK(ok2d(*a_out) && a_out->size(0) == args.M && a_out->size(1) == args.K, "a_out must be [M, K] bf16");
+      args.a_out = a_out->data_ptr();
+      int n_blocks = (args.M + 127) / 128;
+      TORCH_CHECK(flags->is_cuda() && flags->element_size() == 4 && flags->numel() >= n_blocks, "flags too small");
+      args.flags = reinterpret_cast<uint32_t*>(flags->data_ptr());
+      args.pads = pv.pads;
+      args.barrier_block_base = 1024;
+      rt_check(cudaMemsetAsync(args.flags, 0, sizeof(uint32_t) * n_blocks, stream), "cudaMemsetAsync(flags)");
+    } else {
+      args.n_copy = 0;
+      args.M = (int)a.size(0);
+    }
+    TORCH_CHECK(c.size(0) == args.M && c.size(1) == args.N, "c must be [M, N]");
+    rt_check(launch_ag_matmul(args, stream), "ag_matmul");
+  }, py::arg("a"), py::arg("b"), py::arg("c"), py::arg("alloc"), py::arg("shard_offset"),
+     py::arg("a_out"), py::arg("flags"), py::arg("block_n"), py::arg("num_sms"), py::arg("n_copy"),
+     py::arg("timeout_ns"));
 
   // ---- oracles (CPU tensors) ----
   m.def("oracle_ordered_sum_bf16", [](std::vector<torch::Tensor> srcs) {

@@ -40,4 +40,27 @@ int launch_multimem_all_reduce(const PeerView& pv, size_t offset_bytes, size_t n
                                int max_blocks, uint64_t timeout_ns, Status* status,
                                cudaStream_t stream);
 
+// ---- all_gather_matmul (tcgen05 GEMM + in-kernel all-gather) ---------------
+struct AgMatmulArgs {
+  const void* a_local;   // own A shard [rows_per_rank, K] (or all of A [M, K] when n_copy == 0)
+  const void* b;         // [N, K] bf16, K-major
+  void* c;               // [M, N] bf16
+  int M, N, K;
+  int block_n;           // 128, 192, 224 or 256
+  int num_sms;           // CTAs to launch at most (copiers included)
+  // communication; n_copy == 0 turns it off (GEMM over a_local only)
+  int n_copy;            // copier CTAs
+  int rank, world_size;
+  int rows_per_rank;     // multiple of 128
+  void* const* buffers;  // device table: symmetric payload base of every rank
+  size_t shard_offset;   // offset of the A shard inside the payload
+  void* a_out;           // local gathered A [M, K]
+  uint32_t* flags;       // local [ceil(M/128)], zeroed (stream-ordered) before the launch
+  uint32_t* const* pads; // signal pads
+  uint32_t barrier_block_base;
+  uint64_t timeout_ns;
+  Status* status;
+};
+int launch_ag_matmul(const AgMatmulArgs& args, cudaStream_t stream);
+
 }  // namespace smr

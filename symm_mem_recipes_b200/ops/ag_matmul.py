@@ -1,0 +1,145 @@
+"""all_gather_matmul: C = all_gather(A_shard) @ B^T with the gather running
+inside the GEMM kernel.
+
+API and behaviour follow
+symm_mem_recipes/triton_all_gather_matmul.py:219-319
+(`all_gather_matmul_tma_persistent(a_shard, b, a_out, c_out, configs,
+mm_only)`): A is sharded on rows (tokens), B is given as [N, K], the fully
+gathered A is a side output, and `mm_only=True` runs the GEMM alone.  The
+NCCL + cuBLAS composition of :322-326 is `reference_all_gather_matmul`.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from .._ext import C
+from ..errors import SymmMemError
+from ..parallel import symm_mem
+
+_BLOCK_NS = (256, 224, 192, 128)
+
+
+def _env_int(name: str, default: int) -> int:
+    v = os.environ.get(name)
+    return int(v) if v not in (None, "") else default
+
+
+@dataclass
+class AgMatmulConfig:
+    """Tile / scheduling knobs (upstream: a dict of BLOCK_SIZE_M/N/K,
+    GROUP_SIZE_M, num_stages, num_warps; triton_all_gather_matmul.py:380-388).
+    The M tile is 128 and the K tile 64; the stage count follows from BLOCK_N."""
+    block_n: int = _env_int("SMR_AGMM_BLOCK_N", 0)        # 0 = pick per shape
+    n_copy: int = _env_int("SMR_AGMM_COPY_CTAS", 8)       # CTAs that run the all-gather
+    num_sms: int = _env_int("SMR_AGMM_NUM_SMS", 0)        # 0 = all SMs of the device
+    timeout_ms: int = _env_int("SMR_TIMEOUT_MS", 10000)
+
+
+DEFAULT_CONFIG = AgMatmulConfig()
+_sm_count: dict[int, int] = {}
+_flags: dict[int, torch.Tensor] = {}
+
+
+def _num_sms(device: torch.device) -> int:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _sm_count:
+        _sm_count[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return _sm_count[idx]
+
+
+def choose_block_n(M: int, N: int, gemm_ctas: int) -> int:
+    """Smallest modelled time: waves of the static tile schedule times the tile
+    width; ties go to the wider tile (fewer A re-reads)."""
+    best, best_cost = _BLOCK_NS[0], None
+    m_blocks = -(-M // 128)
+    for bn in _BLOCK_NS:
+        tiles = m_blocks * (-(-N // bn))
+        waves = -(-tiles // max(gemm_ctas, 1))
+        cost = waves * bn
+        if best_cost is None or cost < best_cost:
+            best, best_cost = bn, cost
+    return best
+
+
+def _check_2d_bf16(name: str, t: torch.Tensor) -> None:
+    if t.dim() != 2 or t.dtype != torch.bfloat16 or not t.is_cuda or not t.is_contiguous():
+        raise SymmMemError(f"{name} must be a contiguous 2-D bfloat16 CUDA tensor")
+
+
+def matmul(a: torch.Tensor, b: torch.Tensor, c_out: Optional[torch.Tensor] = None,
+           config: AgMatmulConfig = DEFAULT_CONFIG) -> torch.Tensor:
+    """C[M, N] = A[M, K] @ B[N, K]^T on the tcgen05 kernel, no communication."""
+    _check_2d_bf16("a", a)
+    _check_2d_bf16("b", b)
+    M, K = a.shape
+    N = b.shape[0]
+    if b.shape[1] != K or N % 8 or K % 8:
+        raise SymmMemError("need B[N, K] with N and K multiples of 8")
+    if c_out is None:
+        c_out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+    sms = config.num_sms or _num_sms(a.device)
+    bn = config.block_n or choose_block_n(M, N, sms)
+    C.ag_matmul(a, b, c_out, None, 0, None, None, bn, sms, 0, config.timeout_ms * 1_000_000)
+    return c_out
+
+
+def all_gather_matmul(a_shard: torch.Tensor, b: torch.Tensor, a_out: Optional[torch.Tensor] = None,
+                      c_out: Optional[torch.Tensor] = None, config: AgMatmulConfig = DEFAULT_CONFIG,
+                      mm_only: bool = False) -> torch.Tensor:
+    """`a_shard` [M/WS, K] must live in symmetric memory; `b` is [N, K];
+    returns `c_out` [M, N] and fills `a_out` [M, K] with the gathered A.
+
+    `mm_only=True` skips the gather and multiplies `a_out` (or `a_shard` when
+    no `a_out` is given) as it is, to time the GEMM alone.
+    """
+    _check_2d_bf16("a_shard", a_shard)
+    _check_2d_bf16("b", b)
+    if mm_only:
+        return matmul(a_out if a_out is not None else a_shard, b, c_out, config)
+    rec, offset = symm_mem._find_record(a_shard)
+    hdl = symm_mem.rendezvous(a_shard)
+    ws = hdl.world_size
+    rows, K = a_shard.shape
+    M, N = rows * ws, b.shape[0]
+    if b.shape[1] != K or N % 8 or K % 8:
+        raise SymmMemError("need B[N, K] with N and K multiples of 8")
+    if a_out is None:
+        a_out = torch.empty(M, K, dtype=torch.bfloat16, device=a_shard.device)
+    if c_out is None:
+        c_out = torch.empty(M, N, dtype=torch.bfloat16, device=a_shard.device)
+    if tuple(a_out.shape) != (M, K) or tuple(c_out.shape) != (M, N):
+        raise SymmMemError("a_out must be [M, K] and c_out [M, N] with M = rows * world_size")
+    if ws == 1:
+        matmul(a_shard, b, c_out, config)
+        a_out.copy_(a_shard)
+        return c_out
+    if rows % 128:
+        raise SymmMemError("rows per rank must be a multiple of 128 (the M tile and flag granularity)")
+    if offset % 16:
+        raise SymmMemError("a_shard must start on a 16-byte boundary of its allocation")
+    sms = config.num_sms or _num_sms(a_shard.device)
+    n_copy = max(1, min(config.n_copy, sms // 4))
+    bn = config.block_n or choose_block_n(M, N, sms - n_copy)
+    dev_idx = a_shard.device.index
+    n_blocks = M // 128
+    flags = _flags.get(dev_idx)
+    if flags is None or flags.numel() < n_blocks:
+        flags = torch.zeros(max(n_blocks, 1024), dtype=torch.int32, device=a_shard.device)
+        _flags[dev_idx] = flags
+    C.ag_matmul(a_shard, b, c_out, hdl.native, offset, a_out, flags, bn, sms, n_copy,
+                config.timeout_ms * 1_000_000)
+    return c_out
+
+
+def reference_all_gather_matmul(a_shard: torch.Tensor, b: torch.Tensor, group=None) -> torch.Tensor:
+    """The library baseline: NCCL all-gather, then cuBLAS (upstream's
+    `all_gather_matmul`, triton_all_gather_matmul.py:322-326).  `b` is [N, K]."""
+    ws = dist.get_world_size(group)
+    a = torch.empty(a_shard.shape[0] * ws, a_shard.shape[1], dtype=a_shard.dtype, device=a_shard.device)
+    dist.all_gather_into_tensor(a, a_shard, group=group)
+    return torch.matmul(a, b.t())

@@ -1,0 +1,102 @@
+"""tcgen05 GEMM and the fused all-gather + GEMM against fp32 references."""
+import pytest
+import torch
+
+from symm_mem_recipes_b200.utils.testing import spawn_ranks
+
+
+def _ref(a, b):
+    return a.float() @ b.float().t()
+
+
+def _close(c, ref, K):
+    # fp32 accumulation in another order plus one bf16 rounding
+    err = (c.float() - ref).abs()
+    tol = ref.abs() * 2.0 ** -7 + 1e-3 * (K ** 0.5) * 0.02
+    return bool((err <= tol).all()), float(err.max())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("block_n", [128, 192, 224, 256])
+@pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 256), (200, 328, 96), (640, 1000, 1024)])
+def test_matmul_small(block_n, shape):
+    from symm_mem_recipes_b200.ops.ag_matmul import AgMatmulConfig, matmul
+    from symm_mem_recipes_b200.parallel import symm_mem
+
+    M, N, K = shape
+    torch.manual_seed(M + N + K)
+    a = (torch.randn(M, K, device="cuda") * 0.5).to(torch.bfloat16)
+    b = (torch.randn(N, K, device="cuda") * 0.5).to(torch.bfloat16)
+    c = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    matmul(a, b, c, AgMatmulConfig(block_n=block_n, timeout_ms=2000))
+    symm_mem.check_status("cuda")
+    ok, err = _close(c, _ref(a, b), K)
+    assert ok, f"max abs error {err}"
+
+
+@pytest.mark.gpu
+def test_matmul_llama70b_shape_vs_cublas():
+    from symm_mem_recipes_b200.ops.ag_matmul import matmul
+    from symm_mem_recipes_b200.parallel import symm_mem
+
+    M, N, K = 4096, 3584, 8192
+    torch.manual_seed(0)
+    a = (torch.randn(M, K, device="cuda") * 0.02).to(torch.bfloat16)
+    b = (torch.randn(N, K, device="cuda") * 0.02).to(torch.bfloat16)
+    c = matmul(a, b)
+    symm_mem.check_status("cuda")
+    ref = torch.matmul(a, b.t())
+    assert torch.allclose(c.float(), ref.float(), rtol=2e-2, atol=2e-3)
+
+
+def _agmm_worker(rank, world_size, rows, N, K, n_copy):
+    import symm_mem_recipes_b200 as smr
+    from symm_mem_recipes_b200.ops.ag_matmul import AgMatmulConfig
+    from symm_mem_recipes_b200.parallel import symm_mem
+
+    dev = torch.device("cuda", rank)
+    torch.manual_seed(42 + rank)
+    a_shard = symm_mem.empty(rows, K, dtype=torch.bfloat16, device=dev)
+    a_shard.copy_((torch.randn(rows, K, device=dev) * 0.02).to(torch.bfloat16))
+    torch.manual_seed(7)
+    b = (torch.randn(N, K, device=dev) * 0.02).to(torch.bfloat16)
+    M = rows * world_size
+    a_out = torch.zeros(M, K, dtype=torch.bfloat16, device=dev)
+    c_out = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
+    cfg = AgMatmulConfig(n_copy=n_copy, timeout_ms=5000)
+    failures = []
+    for it in range(3):
+        smr.all_gather_matmul(a_shard, b, a_out, c_out, cfg)
+        symm_mem.check_status(dev)
+        ref_a = torch.empty_like(a_out)
+        torch.distributed.all_gather_into_tensor(ref_a, a_shard)
+        if not torch.equal(a_out, ref_a):
+            failures.append(f"iteration {it}: a_out differs from the all-gather")
+        ref = ref_a.float() @ b.float().t()
+        if not torch.allclose(c_out.float(), ref, rtol=2e-2, atol=2e-3):
+            failures.append(f"iteration {it}: c_out max err {(c_out.float() - ref).abs().max().item()}")
+        # new data every iteration: stale flags or stale a_out would show
+        a_shard.copy_((torch.randn(rows, K, device=dev) * 0.02).to(torch.bfloat16))
+        a_out.zero_()
+        torch.cuda.synchronize()
+        torch.distributed.barrier()
+    c_lib = smr.reference_all_gather_matmul(a_shard, b)
+    c_mm = smr.all_gather_matmul(a_shard, b, a_out=ref_a, mm_only=True)
+    symm_mem.check_status(dev)
+    if c_mm.shape != c_lib.shape:
+        failures.append("mm_only shape mismatch")
+    torch.cuda.synchronize()
+    assert not failures, failures
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu(2)
+@pytest.mark.parametrize("rows,N,K,n_copy", [(128, 256, 256, 1), (256, 512, 1024, 3), (2048, 3584, 8192, 8)])
+def test_all_gather_matmul_2gpu(rows, N, K, n_copy):
+    spawn_ranks(_agmm_worker, 2, "nccl", (rows, N, K, n_copy))
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu(8)
+def test_all_gather_matmul_8gpu():
+    spawn_ranks(_agmm_worker, 8, "nccl", (2048, 3584, 8192, 8))

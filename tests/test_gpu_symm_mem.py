@@ -1,0 +1,136 @@
+"""Allocator, rendezvous, barrier and all-reduce on real GPUs.
+
+World of one runs in-process; worlds of 2/4/8 run one process per GPU over
+NCCL.  Every all-reduce result is compared with the CPU oracle (bit-exact for
+the ordered-sum algorithms, one bf16 ulp for the in-switch reduction).
+"""
+import pytest
+import torch
+
+from symm_mem_recipes_b200.utils.testing import seeded_normal_bf16, spawn_ranks
+
+
+@pytest.mark.gpu
+def test_world_of_one_all_paths():
+    import symm_mem_recipes_b200 as smr
+    from symm_mem_recipes_b200.parallel import symm_mem
+
+    torch.cuda.set_device(0)
+    t = symm_mem.empty(8192, dtype=torch.bfloat16, device="cuda")
+    assert int(t.float().abs().sum()) == 0           # zero-filled
+    t.copy_(seeded_normal_bf16(8192, 0, "cuda"))
+    hdl = symm_mem.rendezvous(t)
+    assert (hdl.rank, hdl.world_size) == (0, 1)
+    out = smr.one_shot_all_reduce(t, exit_barrier=True)
+    assert torch.equal(out, t)
+    before = t.clone()
+    smr.two_shot_all_reduce_(t)
+    assert torch.equal(t, before)
+    smr.barrier_test(hdl, num_blocks=32)
+    hdl.barrier()
+    hdl.check()
+    assert int(hdl.get_signal_pad().abs().sum()) == 0
+    view = hdl.get_buffer(0, (16,), torch.bfloat16, storage_offset=64)
+    assert torch.equal(view, t[64:80])
+
+
+@pytest.mark.gpu
+def test_bounded_wait_reports_and_device_survives():
+    """A flag that nothing sets: the kernel gives up after ~20 ms, records a
+    timeout status and returns; the context stays usable."""
+    from symm_mem_recipes_b200 import ops
+    from symm_mem_recipes_b200.errors import SymmMemTimeout
+    from symm_mem_recipes_b200.parallel import symm_mem
+
+    torch.cuda.set_device(0)
+    flag = torch.zeros(4, dtype=torch.int32, device="cuda")
+    ops.wait_flag(flag, 1, timeout_ms=20)
+    with pytest.raises(SymmMemTimeout) as e:
+        symm_mem.check_status("cuda:0")
+    assert e.value.code == 3
+    symm_mem.check_status("cuda:0")                  # record was cleared
+    flag.fill_(1)
+    ops.wait_flag(flag, 1, timeout_ms=20)            # satisfied at once
+    symm_mem.check_status("cuda:0")
+    x = torch.ones(1024, device="cuda")
+    assert float(x.sum()) == 1024.0
+
+
+def _ar_worker(rank, world_size, numel):
+    import symm_mem_recipes_b200 as smr
+    from symm_mem_recipes_b200._ext import C
+    from symm_mem_recipes_b200.parallel import symm_mem
+
+    dev = torch.device("cuda", rank)
+    failures = []
+    t = symm_mem.empty(numel, dtype=torch.bfloat16, device=dev)
+    hdl = symm_mem.rendezvous(t)
+    srcs = [seeded_normal_bf16(numel, r) for r in range(world_size)]
+    ordered = C.oracle_ordered_sum_bf16(srcs)
+    fp32 = torch.stack([s.float() for s in srcs]).sum(0)
+
+    # pointer-table round trip: every rank reads every peer's payload
+    t.copy_(srcs[rank].to(dev))
+    hdl.barrier()
+    for r in range(world_size):
+        peer = hdl.get_buffer(r, (numel,), torch.bfloat16).cpu()
+        if not torch.equal(peer, srcs[r]):
+            failures.append(f"peer view of rank {r} differs")
+    hdl.barrier()
+
+    out = smr.one_shot_all_reduce(t, exit_barrier=True)
+    hdl.check()
+    if not torch.equal(out.cpu().view(torch.int16), ordered.view(torch.int16)):
+        failures.append("one_shot differs from the ordered-sum oracle")
+
+    smr.two_shot_all_reduce_(t)
+    hdl.check()
+    if not torch.equal(t.cpu().view(torch.int16), ordered.view(torch.int16)):
+        failures.append("two_shot differs from the ordered-sum oracle")
+
+    if hdl.has_multicast:
+        hdl.barrier()
+        t.copy_(srcs[rank].to(dev))
+        hdl.barrier()
+        smr.multimem_all_reduce_(t)
+        hdl.check()
+        got = t.cpu().float()
+        # one rounding of the fp32 sum: within one bf16 ulp of it
+        tol = fp32.abs() * 2.0 ** -7 + 1e-6
+        if not bool(((got - fp32).abs() <= tol).all()):
+            failures.append("multimem differs from the fp32-accumulate oracle")
+        mc = hdl.get_multicast_buffer((8,), torch.bfloat16)
+        assert mc.data_ptr() == hdl.multicast_ptr
+    elif world_size > 1:
+        failures.append("no multicast mapping on an NVSwitch machine")
+
+    # barrier stress: the pad must be all zero afterwards
+    for blocks in (1, 7, 32, 148):
+        for _ in range(50):
+            smr.barrier_test(hdl, num_blocks=blocks)
+    hdl.barrier()
+    hdl.check()
+    if int(hdl.get_signal_pad().abs().sum()) != 0:
+        failures.append("signal pad is not zero after the barrier stress")
+    hdl.barrier()
+    torch.cuda.synchronize()
+    assert not failures, failures
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu(2)
+@pytest.mark.parametrize("numel", [8192, 1 << 20])
+def test_all_reduce_2gpu(numel):
+    spawn_ranks(_ar_worker, 2, "nccl", (numel,))
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu(4)
+def test_all_reduce_4gpu():
+    spawn_ranks(_ar_worker, 4, "nccl", (1 << 16,))
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu(8)
+def test_all_reduce_8gpu():
+    spawn_ranks(_ar_worker, 8, "nccl", (1 << 18,))
