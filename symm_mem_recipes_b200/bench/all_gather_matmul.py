@@ -1,0 +1,105 @@
+"""all_gather_matmul benchmark with the flags and the four timings of the
+upstream driver (symm_mem_recipes/triton_all_gather_matmul.py:329-427):
+cuBLAS mm only, this package's mm only, cuBLAS + NCCL, fused.
+
+    torchrun --nnodes 1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        -m symm_mem_recipes_b200.bench.all_gather_matmul --M 16384 --N 3584 --K 8192
+
+M is the gathered row count; N and K are the per-rank weight dims.  Median of
+`--iters` timed calls after `--warmup`, L2 flushed before each, CUDA events,
+maximum over ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--M", type=int, default=4096)
+    ap.add_argument("--N", type=int, default=6656)
+    ap.add_argument("--K", type=int, default=16384)
+    ap.add_argument("--BLOCK_SIZE_N", "--block-n", dest="block_n", type=int, default=0)
+    ap.add_argument("--copy-ctas", default="4", help="comma-separated list to sweep")
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--iters", type=int, default=25)
+    ap.add_argument("--out", default=None)
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29512")
+    dist.init_process_group("nccl", device_id=dev, rank=rank, world_size=world)
+
+    import symm_mem_recipes_b200 as smr
+    from symm_mem_recipes_b200.ops.ag_matmul import AgMatmulConfig
+    from symm_mem_recipes_b200.parallel import symm_mem
+    from symm_mem_recipes_b200.utils.benchmark import benchmark_with_event
+
+    M, N, K = args.M, args.N, args.K
+    assert M % world == 0
+    torch.manual_seed(42 + rank)
+    a_shard = symm_mem.empty(M // world, K, dtype=torch.bfloat16, device=dev)
+    a_shard.copy_((torch.randn(M // world, K, device=dev) * 0.02).to(torch.bfloat16))
+    a = (torch.randn(M, K, device=dev) * 0.02).to(torch.bfloat16)
+    b = (torch.randn(N, K, device=dev) * 0.02).to(torch.bfloat16)
+    bt = b.t()
+    c = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+    a_out = symm_mem.empty(M, K, dtype=torch.bfloat16, device=dev)       # push (broadcast) path
+    a_out_plain = torch.empty(M, K, dtype=torch.bfloat16, device=dev)    # pull path
+    symm_mem.rendezvous(a_shard)
+    symm_mem.rendezvous(a_out)
+    flops = 2.0 * M * N * K
+    lines = []
+
+    def emit(name, us, **extra):
+        rec = {"op": "all_gather_matmul", "impl": name, "world_size": world, "M": M, "N": N, "K": K,
+               "us": round(us, 1), "tflops": round(flops / us / 1e6, 1), **extra}
+        if rank == 0:
+            s = json.dumps(rec)
+            print(s, flush=True)
+            lines.append(s)
+
+    c0 = smr.reference_all_gather_matmul(a_shard, b)
+    c1 = smr.all_gather_matmul(a_shard, b, a_out, c)
+    symm_mem.check_status(dev)
+    assert torch.allclose(c0.float(), c1.float(), rtol=2e-2, atol=2e-3), "fused != NCCL + cuBLAS"
+
+    bench = dict(warmup_iters=args.warmup, benchmark_iters=args.iters, flush_l2=True)
+    emit("cublas_mm_only", benchmark_with_event(lambda: torch.matmul(a, bt, out=c), **bench))
+    cfg0 = AgMatmulConfig(block_n=args.block_n)
+    emit("smr_mm_only", benchmark_with_event(lambda: smr.matmul(a, b, c, cfg0), **bench))
+    emit("cublas_plus_nccl", benchmark_with_event(lambda: smr.reference_all_gather_matmul(a_shard, b), **bench))
+    gathered = torch.empty(M, K, dtype=torch.bfloat16, device=dev)
+    emit("nccl_all_gather_only",
+         benchmark_with_event(lambda: dist.all_gather_into_tensor(gathered, a_shard), **bench))
+    for n_copy in [int(x) for x in args.copy_ctas.split(",") if x]:
+        cfg = AgMatmulConfig(block_n=args.block_n, n_copy=n_copy)
+        us = benchmark_with_event(lambda: smr.all_gather_matmul(a_shard, b, a_out, c, cfg), **bench)
+        emit("smr_fused", us, copy_ctas=n_copy, gather="push")
+        symm_mem.check_status(dev)
+    if os.environ.get("SMR_BENCH_PULL", "0") == "1":
+        cfg = AgMatmulConfig(block_n=args.block_n, n_copy=16)
+        us = benchmark_with_event(lambda: smr.all_gather_matmul(a_shard, b, a_out_plain, c, cfg), **bench)
+        emit("smr_fused", us, copy_ctas=16, gather="pull")
+        symm_mem.check_status(dev)
+    if args.out and rank == 0:
+        with open(args.out, "a") as f:
+            f.write("\n".join(lines) + "\n")
+    symm_mem.shutdown()
+    dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

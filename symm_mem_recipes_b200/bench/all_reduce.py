@@ -1,0 +1,128 @@
+"""All-reduce sweep: latency (µs) and bus bandwidth per message size for the
+one-shot, two-shot and multimem kernels, against NCCL and (optionally) the
+upstream Triton kernel.
+
+    torchrun --nnodes 1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        -m symm_mem_recipes_b200.bench.all_reduce --min-bytes 4096 --max-bytes 268435456
+
+Mirrors the upstream driver (symm_mem_recipes/triton_one_shot_all_reduce.py:128-164),
+which times one 16 KiB message; here every power of two in the range is timed.
+Device-side CUDA events, maximum over ranks, one JSON line per (size, impl).
+busBW = 2 (WS-1)/WS * bytes / time.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--min-bytes", type=int, default=4096)
+    ap.add_argument("--max-bytes", type=int, default=256 * 1024 * 1024)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--iters", type=int, default=50)
+    ap.add_argument("--algos", default="one_shot,two_shot,multimem,auto")
+    ap.add_argument("--one-shot-limit", type=int, default=8 * 1024 * 1024,
+                    help="largest message timed with the one-shot kernels")
+    ap.add_argument("--with-reference-triton", action="store_true")
+    ap.add_argument("--timing", default="graph", choices=["graph", "event"],
+                    help="graph: CUDA-graph replay (device time per call) up to --graph-limit bytes")
+    ap.add_argument("--graph-limit", type=int, default=4 * 1024 * 1024)
+    ap.add_argument("--out", default=None, help="also append the JSON lines to this file")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29511")
+    dist.init_process_group("nccl", device_id=dev, rank=rank, world_size=world)
+
+    import symm_mem_recipes_b200 as smr
+    from symm_mem_recipes_b200.ops.config import AllReduceConfig
+    from symm_mem_recipes_b200.parallel import symm_mem
+    from symm_mem_recipes_b200.utils.benchmark import benchmark_with_event, benchmark_with_graph
+
+    max_numel = args.max_bytes // 2
+    torch.manual_seed(42 + rank)
+    buf = symm_mem.empty(max_numel, dtype=torch.bfloat16, device=dev)
+    buf.normal_()
+    hdl = symm_mem.rendezvous(buf)
+    plain = torch.randn(max_numel, device=dev).to(torch.bfloat16)
+    cfg = AllReduceConfig()
+    ref_fn = ref_buf = None
+    if args.with_reference_triton:
+        try:
+            sys.path.insert(0, os.getcwd())
+            from baseline.reference_triton import load_reference_one_shot
+            ref_fn, ref_alloc = load_reference_one_shot()
+            ref_buf = ref_alloc(min(max_numel, args.one_shot_limit // 2), dev)
+            ref_buf.normal_()
+        except Exception as e:  # noqa: BLE001
+            if rank == 0:
+                print(json.dumps({"impl": "reference_triton", "unavailable": f"{type(e).__name__}: {e}"}))
+            ref_fn = None
+
+    lines = []
+
+    def emit(rec):
+        if rank == 0:
+            s = json.dumps(rec)
+            print(s, flush=True)
+            lines.append(s)
+
+    algos = [a for a in args.algos.split(",") if a]
+    nbytes = args.min_bytes
+    while nbytes <= args.max_bytes:
+        numel = nbytes // 2
+        t = buf[:numel]
+        iters = args.iters if nbytes <= (16 << 20) else max(10, args.iters // 4)
+        warm = args.warmup if nbytes <= (16 << 20) else 5
+        impls = {}
+        impls["nccl"] = lambda: dist.all_reduce(plain[:numel])
+        for a in algos:
+            if a == "one_shot" and nbytes <= args.one_shot_limit:
+                out = torch.empty_like(t)
+                impls["one_shot"] = lambda out=out: smr.one_shot_all_reduce(t, out=out, config=cfg)
+            elif a == "two_shot" and world > 1:
+                impls["two_shot"] = lambda: smr.two_shot_all_reduce_(t, config=cfg)
+            elif a == "multimem" and world > 1 and hdl.has_multicast:
+                impls["multimem"] = lambda: smr.multimem_all_reduce_(t, config=cfg)
+            elif a == "auto":
+                impls["auto:" + smr.ops.choose_algo(nbytes, world, hdl.has_multicast, cfg)] = \
+                    lambda: smr.all_reduce(t, config=cfg)
+        if ref_fn is not None and numel <= ref_buf.numel():
+            rt = ref_buf[:numel]
+            impls["reference_triton"] = lambda: ref_fn(rt)
+        for name, fn in impls.items():
+            if args.timing == "graph" and nbytes <= args.graph_limit:
+                # device time per call; the eager number would mostly be CPU launch cost
+                us = benchmark_with_graph(fn, calls_per_graph=20, warmup_iters=5, replays=10)
+                how = "graph"
+            else:
+                us = benchmark_with_event(fn, warm, iters, flush_l2=False)
+                how = "event"
+            buf.normal_()   # in-place algorithms grow the values; refresh
+            emit({"op": "all_reduce", "impl": name, "world_size": world, "bytes": nbytes, "timing": how,
+                  "us": round(us, 2), "alg_gbs": round(nbytes / us / 1e3, 2),
+                  "bus_gbs": round(2 * (world - 1) / world * nbytes / us / 1e3, 2)})
+        hdl.check()
+        nbytes *= 2
+    if args.out and rank == 0:
+        with open(args.out, "a") as f:
+            f.write("\n".join(lines) + "\n")
+    symm_mem.shutdown()
+    dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

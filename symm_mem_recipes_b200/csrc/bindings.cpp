@@ -297,9 +297,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                                         current_stream(a->device())), "multimem_all_reduce");
   });
 
-  // a: own shard (or all of A when alloc is None), b: [N, K], c: [M, N]
-  m.def("ag_matmul", [](torch::Tensor a, torch::Tensor b, torch::Tensor c,
-                        std::shared_ptr<CudaSymmAllocation> alloc, int64_t shard_offset,
+  // a: own shard (or all of A when mode == 0), b: [N, K], c: [M, N]
+  // mode 1 (pull): `shard_alloc` holds a; a_out is an ordinary tensor.
+  // mode 2 (push): `aout_alloc` holds a_out; a is any CUDA tensor.
+  m.def("ag_matmul", [](torch::Tensor a, torch::Tensor b, torch::Tensor c, int mode,
+                        std::shared_ptr<CudaSymmAllocation> shard_alloc, int64_t shard_offset,
+                        std::shared_ptr<CudaSymmAllocation> aout_alloc, int64_t aout_offset,
                         c10::optional<torch::Tensor> a_out, c10::optional<torch::Tensor> flags,
                         int block_n, int num_sms, int n_copy, uint64_t timeout_ns) {
     auto ok2d = [](const torch::Tensor& t) {
@@ -320,33 +323,79 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     args.num_sms = num_sms;
     args.timeout_ns = timeout_ns;
     args.status = status_for(dev);
-    if (alloc && n_copy > 0) {
-      TORCH_CHECK(a_out.has_value() && flags.has_value(), "a_out and flags are required with communication");
-      PeerView pv = view_of(*alloc);
+    args.mode = mode;
+    if (mode != 0) {
+      TORCH_CHECK(mode == 1 || mode == 2, "mode must be 0, 1 or 2");
+      const CudaSymmAllocation* sym = mode == 1 ? shard_alloc.get() : aout_alloc.get();
+      TORCH_CHECK(sym != nullptr && a_out.has_value(), "communication needs a symmetric allocation and a_out");
+      PeerView pv = view_of(*sym);
       args.n_copy = n_copy;
       args.rank = pv.rank;
       args.world_size = pv.world_size;
       args.rows_per_rank = (int)a.size(0);
       args.M = args.rows_per_rank * pv.world_size;
-      args.buffers = pv.buffers;
-      args.shard_offset = (size_t)shard_offset;
+      args.pads = pv.pads;
+      args.barrier_block_base = 1024;
       TORCH_CHECK(ok2d(*a_out) && a_out->size(0) == args.M && a_out->size(1) == args.K, "a_out must be [M, K] bf16");
       args.a_out = a_out->data_ptr();
       int n_blocks = (args.M + 127) / 128;
-      TORCH_CHECK(flags->is_cuda() && flags->element_size() == 4 && flags->numel() >= n_blocks, "flags too small");
-      args.flags = reinterpret_cast<uint32_t*>(flags->data_ptr());
-      args.pads = pv.pads;
-      args.barrier_block_base = 1024;
-      rt_check(cudaMemsetAsync(args.flags, 0, sizeof(uint32_t) * n_blocks, stream), "cudaMemsetAsync(flags)");
+      if (mode == 1) {
+        TORCH_CHECK(flags.has_value() && flags->is_cuda() && flags->element_size() == 4 &&
+                    flags->numel() >= n_blocks, "flags too small");
+        args.buffers = pv.buffers;
+        args.shard_offset = (size_t)shard_offset;
+        args.flags = reinterpret_cast<uint32_t*>(flags->data_ptr());
+        rt_check(cudaMemsetAsync(args.flags, 0, sizeof(uint32_t) * n_blocks, stream), "cudaMemsetAsync(flags)");
+      } else {
+        TORCH_CHECK((char*)a_out->data_ptr() == (char*)aout_alloc->local_ptr() + aout_offset,
+                    "a_out does not sit at aout_offset of its allocation");
+        args.aout_buffers = pv.buffers;
+        args.aout_mc = pv.multicast;
+        args.aout_offset = (size_t)aout_offset;
+        args.local_pad = aout_alloc->peer_pad(pv.rank);
+      }
     } else {
       args.n_copy = 0;
       args.M = (int)a.size(0);
     }
     TORCH_CHECK(c.size(0) == args.M && c.size(1) == args.N, "c must be [M, N]");
     rt_check(launch_ag_matmul(args, stream), "ag_matmul");
-  }, py::arg("a"), py::arg("b"), py::arg("c"), py::arg("alloc"), py::arg("shard_offset"),
-     py::arg("a_out"), py::arg("flags"), py::arg("block_n"), py::arg("num_sms"), py::arg("n_copy"),
-     py::arg("timeout_ns"));
+  }, py::arg("a"), py::arg("b"), py::arg("c"), py::arg("mode"), py::arg("shard_alloc"),
+     py::arg("shard_offset"), py::arg("aout_alloc"), py::arg("aout_offset"), py::arg("a_out"),
+     py::arg("flags"), py::arg("block_n"), py::arg("num_sms"), py::arg("n_copy"), py::arg("timeout_ns"));
+
+  m.def("gemv_batch_tile", &gemv_batch_tile);
+  m.def("gemv_workspace_bytes", [](int batch_tile, int N, int world_size) {
+    return gemv_workspace_bytes(batch_tile, N, world_size, nullptr, nullptr, nullptr);
+  });
+  m.def("gemv_all_reduce", [](torch::Tensor x, torch::Tensor w, torch::Tensor out,
+                              const std::shared_ptr<CudaSymmAllocation>& workspace, int64_t ws_offset,
+                              uint64_t timeout_ns) {
+    auto ok2d = [](const torch::Tensor& t) {
+      return t.is_cuda() && t.dim() == 2 && t.is_contiguous() && t.scalar_type() == torch::kBFloat16;
+    };
+    TORCH_CHECK(ok2d(x) && ok2d(w) && ok2d(out), "x, w, out must be contiguous 2-D bf16 CUDA tensors");
+    TORCH_CHECK(x.size(1) == w.size(0) && out.size(0) == x.size(0) && out.size(1) == w.size(1),
+                "need x[B, K], w[K, N], out[B, N]");
+    int dev = x.get_device();
+    c10::cuda::CUDAGuard guard(dev);
+    GemvArgs args{};
+    args.x = x.data_ptr();
+    args.w = w.data_ptr();
+    args.out = out.data_ptr();
+    args.batch = (int)x.size(0);
+    args.K = (int)x.size(1);
+    args.N = (int)w.size(1);
+    args.pv = view_of(*workspace);
+    args.ws_offset = (size_t)ws_offset;
+    args.timeout_ns = timeout_ns;
+    args.status = status_for(dev);
+    int bt = gemv_batch_tile(args.batch);
+    TORCH_CHECK(bt > 0, "batch must be between 1 and 16");
+    TORCH_CHECK(gemv_workspace_bytes(bt, args.N, args.pv.world_size, nullptr, nullptr, nullptr) + (size_t)ws_offset
+                    <= workspace->payload_bytes(), "workspace too small");
+    rt_check(launch_gemv_all_reduce(args, current_stream(dev)), "gemv_all_reduce");
+  });
 
   // ---- oracles (CPU tensors) ----
   m.def("oracle_ordered_sum_bf16", [](std::vector<torch::Tensor> srcs) {

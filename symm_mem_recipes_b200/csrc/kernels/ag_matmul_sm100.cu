@@ -8,13 +8,25 @@
 // to Blackwell:
 //
 //  * grid = n_copy "copier" CTAs + (SMs - n_copy) GEMM CTAs, one per SM.
-//  * copier CTA: one thread pulls the peers' shards, 128-row block by block,
-//    with untiled TMA bulk copies peer-HBM -> shared memory -> local a_out,
-//    keeping the whole 200 KB of shared memory in flight over NVLink, and
-//    publishes one flag per block (st.release.gpu) once its writes are done.
-//    Peers are visited in the order rank+1, rank+2, ... (upstream :43-44), the
-//    own shard last.  An entry barrier over the signal pad proves the peers'
-//    shards are ready, an exit barrier that they may be overwritten.
+//  * copier CTA, PUSH mode (a_out in symmetric memory; the default): every
+//    rank broadcasts its OWN shard, 128-row block by block, into the a_out of
+//    all ranks with `multimem.st` on the NVLink multicast address, so a shard
+//    leaves its GPU once and the NVSwitch fans it out (plain peer stores when
+//    there is no multicast mapping).  After a block it adds 1 to that block's
+//    arrival counter on every rank (red.release.sys); the counter of call
+//    number e reads e, so nothing is reset between calls.  An entry barrier
+//    over the signal pad proves that every rank has finished reading the
+//    a_out of the previous call.
+//  * copier CTA, PULL mode (a_out is an ordinary tensor, as upstream): one
+//    thread pulls the peers' shards with untiled TMA bulk copies peer-HBM ->
+//    shared memory -> local a_out and publishes one flag per block once its
+//    writes are done; entry barrier = the peers' shards are ready, exit
+//    barrier = they may be overwritten (upstream :56, :250).
+//  * M is visited so that the k-th block of every shard is consumed before
+//    the (k+1)-th of any: own shard's block first (never waits), then the
+//    same block of rank+1, rank+2, ... (upstream pivots by rank, :157-163).
+//    All senders deliver their k-th blocks at about the same time, so this
+//    order keeps the GEMM behind the arrivals.
 //  * GEMM CTA, warp-specialised:
 //      warp 0   TMA producer: waits for the block's flag (remote blocks
 //               only), then loads A [128 x 64] and B [BN x 64] tiles with the
@@ -33,6 +45,7 @@
 
 #include "../device/barrier.cuh"
 #include "../device/mbarrier.cuh"
+#include "../device/multimem.cuh"
 #include "../device/tcgen05.cuh"
 #include "../device/tma.cuh"
 #include "../device/vec.cuh"
@@ -62,7 +75,14 @@ struct AgMatmulParams {
   int rank, world_size;
   int blocks_per_rank;   // 128-row blocks per shard
   int n_copy;            // copier CTAs (0 = no communication)
-  uint32_t* flags;       // [n_blocks_m] local, zeroed before launch; 1 = block landed
+  int mode;              // 0 none, 1 pull, 2 push
+  uint32_t* flags;       // [n_blocks_m] arrival flags read by the GEMM CTAs (local memory)
+  uint32_t flag_target;  // pull: 1 (flags zeroed before launch); push: filled from the epoch
+  uint32_t* header;      // push: [0] epoch, [1] CTAs done (local, in the a_out signal pad)
+  const char* a_local;   // own shard
+  void* const* aout_buffers;   // push: payload base of the a_out allocation on every rank
+  void* aout_mc;         // push: multicast payload base of the a_out allocation, or nullptr
+  size_t aout_offset;    // push: offset of a_out inside that payload
   void* const* buffers;  // device table [WS]: symmetric payload base of every rank (peer-mapped)
   size_t shard_offset;   // offset of the A shard inside the payload
   char* a_out;           // local gathered A [M, K]
@@ -88,8 +108,8 @@ struct SmemLayout {
 
 // ---------------------------------------------------------------------------
 // Copier: thread 0 of a copier CTA.
-// Work items: remote blocks in arrival order, then the own shard; copier i
-// takes items i, i + n_copy, ...
+// Work items in the order the GEMM consumes them (block k of every shard,
+// then block k+1); copier i takes items i, i + n_copy, ...
 // ---------------------------------------------------------------------------
 template <int BN, int STAGES>
 __device__ void copier_thread(const AgMatmulParams& p, int copier, uint8_t* ring, uint64_t* cbar) {
@@ -108,9 +128,9 @@ __device__ void copier_thread(const AgMatmulParams& p, int copier, uint8_t* ring
   auto chunk_src_dst = [&](uint64_t c, const char*& src, char*& dst, uint32_t& bytes, int& gblock) {
     int item = copier + (int)(c / chunks_per_block) * p.n_copy;
     uint32_t ch = (uint32_t)(c % chunks_per_block);
-    int step = item / bpr;                     // 0 .. WS-1; WS-1 = own shard
-    int blk = item % bpr;
-    int peer = (p.rank + 1 + step) % p.world_size;
+    int blk = item / p.world_size;             // block k of every shard before block k+1
+    int step = item % p.world_size;            // 0 = own shard (side output only)
+    int peer = (p.rank + step) % p.world_size;
     size_t off = (size_t)ch * kCopyChunk;
     size_t left = block_bytes - off;
     bytes = (uint32_t)(left < kCopyChunk ? left : kCopyChunk);
@@ -183,6 +203,95 @@ __device__ void copier_thread(const AgMatmulParams& p, int copier, uint8_t* ring
   // refill of chunk (index - NBUF + kStoreLag).
 }
 
+// ---------------------------------------------------------------------------
+// Push copier: the whole CTA broadcasts blocks `copier, copier + n_copy, ...`
+// of the OWN shard into every rank's a_out and bumps the arrival counters.
+// Thread 0 streams the shard from local HBM into a shared-memory ring with TMA
+// bulk loads (the ring, ~200 KB, is what is in flight); all threads then move
+// each chunk from shared memory to the multicast address with multimem.st.
+// ---------------------------------------------------------------------------
+constexpr uint32_t kPushChunk = 32768;
+
+template <int BN, int STAGES>
+__device__ void copier_push(const AgMatmulParams& p, int copier, uint8_t* ring, uint64_t* cbar) {
+  using L = SmemLayout<BN, STAGES>;
+  constexpr uint32_t NBUF = L::kRingBytes / kPushChunk;
+  static_assert(NBUF >= 3 && NBUF <= 32, "ring size");
+  const size_t block_bytes = (size_t)kBM * p.K * 2;
+  const uint32_t chunks_per_block = (uint32_t)((block_bytes + kPushChunk - 1) / kPushChunk);
+  const int tid = threadIdx.x;
+  int my_blocks = 0;
+  for (int b = copier; b < p.blocks_per_rank; b += p.n_copy) ++my_blocks;
+  const uint32_t total_chunks = (uint32_t)my_blocks * chunks_per_block;
+
+  auto chunk_of = [&](uint32_t c, const char*& src, size_t& dst_off, uint32_t& bytes, int& gblk) {
+    int blk = copier + (int)(c / chunks_per_block) * p.n_copy;
+    size_t off = (size_t)(c % chunks_per_block) * kPushChunk;
+    size_t left = block_bytes - off;
+    bytes = (uint32_t)(left < kPushChunk ? left : kPushChunk);
+    src = p.a_local + (size_t)blk * block_bytes + off;
+    gblk = p.rank * p.blocks_per_rank + blk;
+    dst_off = p.aout_offset + (size_t)gblk * block_bytes + off;
+  };
+  auto issue = [&](uint32_t c) {
+    const char* src; size_t dst_off; uint32_t bytes; int gblk;
+    chunk_of(c, src, dst_off, bytes, gblk);
+    uint32_t b = c % NBUF;
+    mbar_arrive_expect_tx(&cbar[b], bytes);
+    bulk_load(ring + (size_t)b * kPushChunk, src, bytes, &cbar[b]);
+  };
+
+  if (tid == 0)
+    for (uint32_t c = 0; c < total_chunks && c < NBUF - 1; ++c) issue(c);
+  bool ok = true;
+  for (uint32_t c = 0; c < total_chunks; ++c) {
+    // buffer (c-1) % NBUF was released by the __syncthreads that ended iteration c-1
+    if (tid == 0 && c + NBUF - 1 < total_chunks) issue(c + NBUF - 1);
+    const char* src; size_t dst_off; uint32_t bytes; int gblk;
+    chunk_of(c, src, dst_off, bytes, gblk);
+    const uint32_t b = c % NBUF;
+    if (!mbar_wait(&cbar[b], (c / NBUF) & 1u, p.timeout_ns)) {
+      if (tid == 0)
+        report_status(p.status, kTimeoutMbarrier, p.rank, blockIdx.x, 0, kWhereCopierEntry, c);
+      ok = false;
+    }
+    if (!__syncthreads_and(ok)) {
+      for (int i = 0; i < 100; ++i) __nanosleep(1000);   // let the bulk loads in flight land
+      return;
+    }
+    const Vec16* sv = reinterpret_cast<const Vec16*>(ring + (size_t)b * kPushChunk);
+    const uint32_t vecs = bytes / 16;
+    if (p.aout_mc != nullptr) {
+      Vec16* dst = reinterpret_cast<Vec16*>(static_cast<char*>(p.aout_mc) + dst_off);
+#pragma unroll 4
+      for (uint32_t i = tid; i < vecs; i += kGemmThreads) multimem_st_16(dst + i, sv[i]);
+    } else {
+      for (int s = 1; s <= p.world_size; ++s) {        // own a_out last
+        int peer = (p.rank + s) % p.world_size;
+        Vec16* dst = reinterpret_cast<Vec16*>(static_cast<char*>(p.aout_buffers[peer]) + dst_off);
+#pragma unroll 4
+        for (uint32_t i = tid; i < vecs; i += kGemmThreads) st_16(dst + i, sv[i]);
+      }
+    }
+    __syncthreads();   // chunk consumed: its buffer may be refilled; stores precede the release
+    if ((c % chunks_per_block) == chunks_per_block - 1 && tid < p.world_size)
+      red_add_release_sys(p.pads[tid] + kFlagSlotsBase + 2 + gblk, 1u);
+  }
+}
+
+// Position `mi` of the M schedule -> 128-row block of the gathered A.
+__device__ __forceinline__ int scheduled_block(const AgMatmulParams& p, int mi, bool& local) {
+  if (p.mode == 0) {
+    local = true;
+    return mi;
+  }
+  int k = mi / p.world_size, step = mi % p.world_size;
+  int src = p.rank + step;
+  if (src >= p.world_size) src -= p.world_size;
+  local = (step == 0);
+  return src * p.blocks_per_rank + k;
+}
+
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 ag_matmul_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
@@ -202,20 +311,39 @@ ag_matmul_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
+  // push mode: this call's number, the value every arrival counter will reach
+  uint32_t flag_target = p.flag_target;
+  if (p.mode == 2) flag_target = ld_relaxed_gpu(&p.header[0]) + 1u;
+
   // ======================= copier CTAs =======================
   if ((int)blockIdx.x < p.n_copy) {
     if (threadIdx.x == 0) {
       for (int i = 0; i < 32; ++i) mbar_init(&copy_bar[i], 1);
       mbar_fence_init();
     }
-    // entry: every peer's shard is written (their earlier kernels are done)
+    // entry: every peer has entered this call, i.e. its shard is written and
+    // it no longer reads the a_out of the previous call
     bool ok = blockwise_barrier(p.pads, p.barrier_block_base + blockIdx.x, p.rank, p.world_size,
                                 p.timeout_ns, p.status, kWhereCopierEntry);
-    if (ok && threadIdx.x == 0) copier_thread<BN, STAGES>(p, (int)blockIdx.x, smem, copy_bar);
-    // exit: every peer has finished reading this rank's shard
-    if (ok)
+    if (ok && p.mode == 2) {
+      copier_push<BN, STAGES>(p, (int)blockIdx.x, smem, copy_bar);
+    } else if (ok) {
+      if (threadIdx.x == 0) copier_thread<BN, STAGES>(p, (int)blockIdx.x, smem, copy_bar);
+      // exit: every peer has finished reading this rank's shard
       blockwise_barrier(p.pads, p.barrier_block_base + blockIdx.x, p.rank, p.world_size,
                         p.timeout_ns, p.status, kWhereCopierExit);
+    }
+    if (p.mode == 2) {
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        uint32_t done = atomicAdd(&p.header[1], 1u);
+        if (done == gridDim.x - 1) {
+          p.header[1] = 0u;
+          __threadfence();
+          st_release_gpu(&p.header[0], flag_target);
+        }
+      }
+    }
     return;
   }
 
@@ -256,18 +384,16 @@ ag_matmul_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
       uint32_t stage = 0, phase = 0;
       for (int t = gemm_cta; t < total_tiles && !failed; t += n_gemm) {
         int mi = t / p.n_tiles_n, ni = t % p.n_tiles_n;
-        // visit M in arrival order: own shard first, then rank+1, ...
-        int mblk = mi + p.rank * p.blocks_per_rank;
-        if (mblk >= p.n_blocks_m) mblk -= p.n_blocks_m;
-        const bool local = (p.n_copy == 0) || (mblk / p.blocks_per_rank == p.rank);
+        bool local;
+        const int mblk = scheduled_block(p, mi, local);
         const CUtensorMap* amap = &tmap_a_out;
         int row0 = mblk * kBM;
-        if (p.n_copy > 0 && local) {
+        if (p.mode != 0 && local) {
           amap = &tmap_a_shard;
           row0 -= p.rank * rows_per_rank;
         }
         if (!local) {
-          if (!wait_ge_acquire_gpu(&p.flags[mblk], 1u, p.timeout_ns)) {
+          if (!wait_ge_acquire_sys(&p.flags[mblk], flag_target, p.timeout_ns)) {
             report_status(p.status, kTimeoutFlag, p.rank, blockIdx.x, mblk, kWhereGemmProgress);
             failed = true;
             break;
@@ -334,8 +460,8 @@ ag_matmul_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
     uint32_t acc = 0, acc_phase = 0;
     for (int t = gemm_cta; t < total_tiles && !failed; t += n_gemm) {
       int mi = t / p.n_tiles_n, ni = t % p.n_tiles_n;
-      int mblk = mi + p.rank * p.blocks_per_rank;
-      if (mblk >= p.n_blocks_m) mblk -= p.n_blocks_m;
+      bool local_unused;
+      const int mblk = scheduled_block(p, mi, local_unused);
       if (!mbar_wait(&tmem_full[acc], acc_phase, p.timeout_ns)) {
         if (lane == 0)
           report_status(p.status, kTimeoutMbarrier, p.rank, blockIdx.x, acc, kWhereGemmTmemFull);
@@ -383,6 +509,15 @@ ag_matmul_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
   __syncthreads();
   tcgen05_fence_after_thread_sync();
   if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+  if (p.mode == 2 && threadIdx.x == 0) {
+    // the last CTA of the grid to finish publishes this call's number
+    uint32_t done = atomicAdd(&p.header[1], 1u);
+    if (done == gridDim.x - 1) {
+      p.header[1] = 0u;
+      __threadfence();
+      st_release_gpu(&p.header[0], flag_target);
+    }
+  }
 }
 
 // row-major bf16 [rows, cols] with a [box_rows x 64] box and 128-byte swizzle
@@ -415,12 +550,14 @@ int launch_variant(const CUtensorMap& ta_shard, const CUtensorMap& ta_out, const
 
 int launch_ag_matmul(const AgMatmulArgs& a, cudaStream_t stream) {
   if (a.N % 8 != 0 || a.K % 8 != 0 || a.M <= 0 || a.N <= 0 || a.K <= 0) return cudaErrorInvalidValue;
-  const bool comm = a.n_copy > 0;
+  const bool comm = a.mode != 0;
   if (comm) {
-    if (a.world_size < 2 || a.rows_per_rank % kBM != 0 || a.rows_per_rank * a.world_size != a.M ||
-        a.buffers == nullptr || a.a_out == nullptr || a.flags == nullptr || a.pads == nullptr)
+    if (a.n_copy < 1 || a.world_size < 2 || a.rows_per_rank % kBM != 0 ||
+        a.rows_per_rank * a.world_size != a.M || a.a_out == nullptr || a.pads == nullptr)
       return cudaErrorInvalidValue;
-    if (((size_t)kBM * a.K * 2) % 16 != 0) return cudaErrorInvalidValue;
+    if (a.mode == 1 && (a.buffers == nullptr || a.flags == nullptr)) return cudaErrorInvalidValue;
+    if (a.mode == 2 && (a.aout_buffers == nullptr || a.local_pad == nullptr)) return cudaErrorInvalidValue;
+    if (a.mode == 2 && (uint32_t)(a.M / kBM) + 2u > kFlagSlots) return cudaErrorInvalidValue;
   }
   int bn = a.block_n;
   if (bn != 128 && bn != 192 && bn != 224 && bn != 256) return cudaErrorInvalidValue;
@@ -434,7 +571,14 @@ int launch_ag_matmul(const AgMatmulArgs& a, cudaStream_t stream) {
   p.world_size = comm ? a.world_size : 1;
   p.blocks_per_rank = comm ? a.rows_per_rank / kBM : p.n_blocks_m;
   p.n_copy = comm ? a.n_copy : 0;
-  p.flags = a.flags;
+  p.mode = comm ? a.mode : 0;
+  p.flags = a.mode == 2 ? a.local_pad + kFlagSlotsBase + 2 : a.flags;
+  p.flag_target = 1u;
+  p.header = a.mode == 2 ? a.local_pad + kFlagSlotsBase : nullptr;
+  p.a_local = static_cast<const char*>(a.a_local);
+  p.aout_buffers = a.aout_buffers;
+  p.aout_mc = a.aout_mc;
+  p.aout_offset = a.aout_offset;
   p.buffers = a.buffers;
   p.shard_offset = a.shard_offset;
   p.a_out = static_cast<char*>(a.a_out);

@@ -145,14 +145,16 @@ multimem_all_reduce_kernel(PeerView pv, size_t offset_bytes, size_t n_vec, uint6
   slice_of(n_vec, ws, rank, begin, end);
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   size_t i = begin + (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  // two independent reductions in flight per thread
-  for (; i + stride < end; i += 2 * stride) {
-    Vec16 a = multimem_ld_reduce_bf16x8(mc + i);
-    Vec16 b = multimem_ld_reduce_bf16x8(mc + i + stride);
-    multimem_st_16(mc + i, a);
-    multimem_st_16(mc + i + stride, b);
+  // four independent in-switch reductions in flight per thread
+  constexpr int U = 4;
+  for (; i + (U - 1) * stride < end; i += U * stride) {
+    Vec16 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) v[u] = multimem_ld_reduce_bf16x8(mc + i + u * stride);
+#pragma unroll
+    for (int u = 0; u < U; ++u) multimem_st_16(mc + i + u * stride, v[u]);
   }
-  if (i < end) {
+  for (; i < end; i += stride) {
     Vec16 a = multimem_ld_reduce_bf16x8(mc + i);
     multimem_st_16(mc + i, a);
   }

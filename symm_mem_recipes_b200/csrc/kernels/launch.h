@@ -48,19 +48,46 @@ struct AgMatmulArgs {
   int M, N, K;
   int block_n;           // 128, 192, 224 or 256
   int num_sms;           // CTAs to launch at most (copiers included)
-  // communication; n_copy == 0 turns it off (GEMM over a_local only)
+  // communication: mode 0 = none (GEMM over a_local only),
+  //   1 = pull (a_out ordinary memory; the A shards are symmetric and copier
+  //       CTAs fetch the peers' shards),
+  //   2 = push (a_out symmetric; copier CTAs broadcast the own shard).
+  int mode;
   int n_copy;            // copier CTAs
   int rank, world_size;
   int rows_per_rank;     // multiple of 128
-  void* const* buffers;  // device table: symmetric payload base of every rank
-  size_t shard_offset;   // offset of the A shard inside the payload
   void* a_out;           // local gathered A [M, K]
+  uint32_t* const* pads; // signal pads of the symmetric allocation in use
+  // pull
+  void* const* buffers;  // device table: payload base of the A-shard allocation on every rank
+  size_t shard_offset;   // offset of the A shard inside that payload
   uint32_t* flags;       // local [ceil(M/128)], zeroed (stream-ordered) before the launch
-  uint32_t* const* pads; // signal pads
+  // push
+  void* const* aout_buffers;  // device table: payload base of the a_out allocation on every rank
+  void* aout_mc;              // its multicast base or nullptr
+  size_t aout_offset;         // offset of a_out inside that payload
+  uint32_t* local_pad;        // this rank's signal pad of the a_out allocation
   uint32_t barrier_block_base;
   uint64_t timeout_ns;
   Status* status;
 };
 int launch_ag_matmul(const AgMatmulArgs& args, cudaStream_t stream);
+
+// ---- fused GEMV + all-reduce (decode) -------------------------------------
+struct GemvArgs {
+  const void* x;      // [batch, K] bf16, batch <= 16
+  const void* w;      // [K, N] bf16
+  void* out;          // [batch, N] bf16
+  int batch, K, N;
+  PeerView pv;        // of the symmetric workspace
+  size_t ws_offset;   // offset of the workspace inside the payload
+  uint64_t timeout_ns;
+  Status* status;
+};
+// Bytes of symmetric workspace for a batch tile (1, 2, 4, 8 or 16), N columns.
+size_t gemv_workspace_bytes(int batch_tile, int N, int world_size, size_t* flags_offset,
+                            size_t* inbox_offset, int* max_tiles);
+int gemv_batch_tile(int batch);   // smallest supported tile >= batch, -1 if none
+int launch_gemv_all_reduce(const GemvArgs& args, cudaStream_t stream);
 
 }  // namespace smr

@@ -3,3 +3,4 @@ from .all_reduce import (all_reduce, choose_algo, multimem_all_reduce_,  # noqa:
 from .barrier import barrier_test, wait_flag  # noqa: F401
 from .ag_matmul import (AgMatmulConfig, all_gather_matmul, matmul,  # noqa: F401
                                 reference_all_gather_matmul)
+from .gemv_all_reduce import gemv_all_reduce, reference_gemv_all_reduce  # noqa: F401

@@ -35,7 +35,7 @@ class AgMatmulConfig:
     GROUP_SIZE_M, num_stages, num_warps; triton_all_gather_matmul.py:380-388).
     The M tile is 128 and the K tile 64; the stage count follows from BLOCK_N."""
     block_n: int = _env_int("SMR_AGMM_BLOCK_N", 0)        # 0 = pick per shape
-    n_copy: int = _env_int("SMR_AGMM_COPY_CTAS", 8)       # CTAs that run the all-gather
+    n_copy: int = _env_int("SMR_AGMM_COPY_CTAS", 4)       # CTAs that run the all-gather
     num_sms: int = _env_int("SMR_AGMM_NUM_SMS", 0)        # 0 = all SMs of the device
     timeout_ms: int = _env_int("SMR_TIMEOUT_MS", 10000)
 
@@ -84,15 +84,38 @@ def matmul(a: torch.Tensor, b: torch.Tensor, c_out: Optional[torch.Tensor] = Non
         c_out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
     sms = config.num_sms or _num_sms(a.device)
     bn = config.block_n or choose_block_n(M, N, sms)
-    C.ag_matmul(a, b, c_out, None, 0, None, None, bn, sms, 0, config.timeout_ms * 1_000_000)
+    C.ag_matmul(a, b, c_out, 0, None, 0, None, 0, None, None, bn, sms, 0, config.timeout_ms * 1_000_000)
     return c_out
+
+
+_gather_buffers: dict[tuple, torch.Tensor] = {}
+
+
+def gather_buffer(M: int, K: int, device: torch.device, group=None) -> torch.Tensor:
+    """The symmetric [M, K] buffer that `all_gather_matmul` gathers into when
+    the caller passes no `a_out`.  Allocated and rendezvoused at first use
+    (collective: every rank must reach it), then reused."""
+    key = (M, K, device.index, symm_mem._group_key(group))
+    t = _gather_buffers.get(key)
+    if t is None:
+        t = symm_mem.empty(M, K, dtype=torch.bfloat16, device=device)
+        symm_mem.rendezvous(t, group)
+        _gather_buffers[key] = t
+    return t
 
 
 def all_gather_matmul(a_shard: torch.Tensor, b: torch.Tensor, a_out: Optional[torch.Tensor] = None,
                       c_out: Optional[torch.Tensor] = None, config: AgMatmulConfig = DEFAULT_CONFIG,
-                      mm_only: bool = False) -> torch.Tensor:
-    """`a_shard` [M/WS, K] must live in symmetric memory; `b` is [N, K];
-    returns `c_out` [M, N] and fills `a_out` [M, K] with the gathered A.
+                      mm_only: bool = False, group=None) -> torch.Tensor:
+    """`a_shard` is this rank's [M/WS, K] rows of A; `b` is [N, K]; returns
+    `c_out` [M, N] = all_gather(A) @ B^T and leaves the gathered A in `a_out`.
+
+    Where the gathered A lands decides how it is gathered:
+      * `a_out` in symmetric memory (`symm_mem.empty`), or None (an internal
+        symmetric buffer, see `gather_buffer`): every rank broadcasts its own
+        shard through the NVSwitch (push).  This is the fast path.
+      * `a_out` an ordinary tensor, as in the upstream API: `a_shard` must be
+        in symmetric memory and the kernel pulls the peers' shards.
 
     `mm_only=True` skips the gather and multiplies `a_out` (or `a_shard` when
     no `a_out` is given) as it is, to time the GEMM alone.
@@ -101,38 +124,49 @@ def all_gather_matmul(a_shard: torch.Tensor, b: torch.Tensor, a_out: Optional[to
     _check_2d_bf16("b", b)
     if mm_only:
         return matmul(a_out if a_out is not None else a_shard, b, c_out, config)
-    rec, offset = symm_mem._find_record(a_shard)
-    hdl = symm_mem.rendezvous(a_shard)
-    ws = hdl.world_size
     rows, K = a_shard.shape
-    M, N = rows * ws, b.shape[0]
+    N = b.shape[0]
     if b.shape[1] != K or N % 8 or K % 8:
         raise SymmMemError("need B[N, K] with N and K multiples of 8")
-    if a_out is None:
-        a_out = torch.empty(M, K, dtype=torch.bfloat16, device=a_shard.device)
+    ws = dist.get_world_size(group) if dist.is_initialized() else 1
+    M = rows * ws
     if c_out is None:
         c_out = torch.empty(M, N, dtype=torch.bfloat16, device=a_shard.device)
-    if tuple(a_out.shape) != (M, K) or tuple(c_out.shape) != (M, N):
-        raise SymmMemError("a_out must be [M, K] and c_out [M, N] with M = rows * world_size")
     if ws == 1:
+        # nothing to gather: the shard is the gathered A; copy only on request
         matmul(a_shard, b, c_out, config)
-        a_out.copy_(a_shard)
+        if a_out is not None:
+            a_out.copy_(a_shard)
         return c_out
     if rows % 128:
         raise SymmMemError("rows per rank must be a multiple of 128 (the M tile and flag granularity)")
-    if offset % 16:
-        raise SymmMemError("a_shard must start on a 16-byte boundary of its allocation")
+    if a_out is None:
+        a_out = gather_buffer(M, K, a_shard.device, group)
+    if tuple(a_out.shape) != (M, K) or tuple(c_out.shape) != (M, N):
+        raise SymmMemError("a_out must be [M, K] and c_out [M, N] with M = rows * world_size")
     sms = config.num_sms or _num_sms(a_shard.device)
     n_copy = max(1, min(config.n_copy, sms // 4))
     bn = config.block_n or choose_block_n(M, N, sms - n_copy)
+    t_ns = config.timeout_ms * 1_000_000
+    if symm_mem.is_symm_mem_tensor(a_out):
+        _, aout_offset = symm_mem._find_record(a_out)
+        hdl = symm_mem.rendezvous(a_out, group)
+        if aout_offset % 16:
+            raise SymmMemError("a_out must start on a 16-byte boundary of its allocation")
+        C.ag_matmul(a_shard, b, c_out, 2, None, 0, hdl.native, aout_offset, a_out, None,
+                    bn, sms, n_copy, t_ns)
+        return c_out
+    _, offset = symm_mem._find_record(a_shard)
+    hdl = symm_mem.rendezvous(a_shard, group)
+    if offset % 16:
+        raise SymmMemError("a_shard must start on a 16-byte boundary of its allocation")
     dev_idx = a_shard.device.index
     n_blocks = M // 128
     flags = _flags.get(dev_idx)
     if flags is None or flags.numel() < n_blocks:
         flags = torch.zeros(max(n_blocks, 1024), dtype=torch.int32, device=a_shard.device)
         _flags[dev_idx] = flags
-    C.ag_matmul(a_shard, b, c_out, hdl.native, offset, a_out, flags, bn, sms, n_copy,
-                config.timeout_ms * 1_000_000)
+    C.ag_matmul(a_shard, b, c_out, 1, hdl.native, offset, None, 0, a_out, flags, bn, sms, n_copy, t_ns)
     return c_out
 
 

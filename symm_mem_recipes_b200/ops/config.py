@@ -21,8 +21,8 @@ class AllReduceConfig:
     # CTA caps.  Upstream caps its one-shot kernel at 24 CTAs of 512 threads
     # (triton_one_shot_all_reduce.py:97-109); large messages want more.
     one_shot_max_blocks: int = _env_int("SMR_AR_ONE_SHOT_MAX_BLOCKS", 32)
-    two_shot_max_blocks: int = _env_int("SMR_AR_TWO_SHOT_MAX_BLOCKS", 64)
-    multimem_max_blocks: int = _env_int("SMR_AR_MULTIMEM_MAX_BLOCKS", 32)
+    two_shot_max_blocks: int = _env_int("SMR_AR_TWO_SHOT_MAX_BLOCKS", 128)
+    multimem_max_blocks: int = _env_int("SMR_AR_MULTIMEM_MAX_BLOCKS", 128)
     timeout_ms: int = _env_int("SMR_TIMEOUT_MS", 10000)
 
 

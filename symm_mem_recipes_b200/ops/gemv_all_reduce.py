@@ -1,0 +1,67 @@
+"""Fused GEMV + all-reduce for tensor-parallel decode.
+
+    out[b, :] = sum over ranks of x_r[b, :] @ W_r          (b <= 16)
+
+Row-parallel linear layer at decode time (for example the Llama-3-70B
+down-projection at TP8: x [b, 3584], W [3584, 8192] per rank).  One kernel
+streams the weight shard and reduces the partials across ranks through peer
+stores; see csrc/kernels/gemv_allreduce.cu.  There is no upstream counterpart;
+the library baseline is `reference_gemv_all_reduce` (cuBLAS + NCCL).
+"""
+from __future__ import annotations
+
+import os
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from .._ext import C
+from ..errors import SymmMemError
+from ..parallel import symm_mem
+
+_workspaces: dict[tuple, torch.Tensor] = {}
+_TIMEOUT_MS = int(os.environ.get("SMR_TIMEOUT_MS", "10000"))
+
+
+def _workspace(batch_tile: int, N: int, device: torch.device, group) -> torch.Tensor:
+    """Symmetric scratch (inboxes, flags, epoch) for one (batch tile, N):
+    allocated and rendezvoused at the first call, which is therefore
+    collective; all ranks must make the same sequence of first calls."""
+    ws = dist.get_world_size(group) if dist.is_initialized() else 1
+    key = (batch_tile, N, device.index, symm_mem._group_key(group))
+    t = _workspaces.get(key)
+    if t is None:
+        nbytes = C.gemv_workspace_bytes(batch_tile, N, ws)
+        t = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+        symm_mem.rendezvous(t, group)
+        _workspaces[key] = t
+    return t
+
+
+def gemv_all_reduce(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
+                    group=None, timeout_ms: int = _TIMEOUT_MS) -> torch.Tensor:
+    """`x` [B, K] and `w` [K, N] are this rank's (ordinary) tensors; returns the
+    all-reduced [B, N] in bf16, bitwise identical on every rank."""
+    if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[0]:
+        raise SymmMemError("need x[B, K] and w[K, N]")
+    B, N = x.shape[0], w.shape[1]
+    if not 1 <= B <= 16:
+        raise SymmMemError("batch must be between 1 and 16 (decode); use matmul_reduce_scatter for prefill")
+    if N % 8:
+        raise SymmMemError("N must be a multiple of 8")
+    if out is None:
+        out = torch.empty(B, N, dtype=torch.bfloat16, device=x.device)
+    bt = C.gemv_batch_tile(B)
+    wsp = _workspace(bt, N, x.device, group)
+    hdl = symm_mem.rendezvous(wsp, group)
+    C.gemv_all_reduce(x.contiguous(), w, out, hdl.native, 0, int(timeout_ms) * 1_000_000)
+    return out
+
+
+def reference_gemv_all_reduce(x: torch.Tensor, w: torch.Tensor, group=None) -> torch.Tensor:
+    """Library baseline: cuBLAS GEMM, then NCCL all-reduce (bf16)."""
+    y = torch.matmul(x, w)
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(y, group=group)
+    return y

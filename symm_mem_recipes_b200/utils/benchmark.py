@@ -124,6 +124,41 @@ def benchmark_with_profiler(target_fn: Callable[[], None], event_key_regex: str,
     return float(statistics.median(times))
 
 
+def benchmark_with_graph(target_fn: Callable[[], None], calls_per_graph: int = 20,
+                         warmup_iters: int = 5, replays: int = 10, all_ranks_max: bool = True) -> float:
+    """Device time per call (µs) with the CPU launch cost taken out: the call
+    is captured `calls_per_graph` times into one CUDA graph and the graph is
+    replayed; the median replay time is divided by the number of calls.  This
+    is how small-message latencies are reported (upstream gets kernel-only
+    time from the profiler instead: utils.py:10-82).  Every op of this package
+    is capturable because no launch parameter changes between calls."""
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        for _ in range(warmup_iters):
+            target_fn()
+    stream.synchronize()
+    _barrier()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        for _ in range(calls_per_graph):
+            target_fn()
+    torch.cuda.synchronize()
+    _barrier()
+    graph.replay()
+    torch.cuda.synchronize()
+    begins = [torch.cuda.Event(enable_timing=True) for _ in range(replays)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(replays)]
+    for i in range(replays):
+        begins[i].record()
+        graph.replay()
+        ends[i].record()
+    torch.cuda.synchronize()
+    us = statistics.median(b.elapsed_time(e) * 1000.0 / calls_per_graph for b, e in zip(begins, ends))
+    del graph
+    return max_over_ranks(us) if all_ranks_max else us
+
+
 class ClockSampler:
     """Samples SM clock, power and throttle reasons of one GPU with nvidia-smi
     while a timed region runs (read-only; changes no GPU setting)."""

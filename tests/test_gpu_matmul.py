@@ -49,7 +49,7 @@ def test_matmul_llama70b_shape_vs_cublas():
     assert torch.allclose(c.float(), ref.float(), rtol=2e-2, atol=2e-3)
 
 
-def _agmm_worker(rank, world_size, rows, N, K, n_copy):
+def _agmm_worker(rank, world_size, rows, N, K, n_copy, mode):
     import symm_mem_recipes_b200 as smr
     from symm_mem_recipes_b200.ops.ag_matmul import AgMatmulConfig
     from symm_mem_recipes_b200.parallel import symm_mem
@@ -61,13 +61,21 @@ def _agmm_worker(rank, world_size, rows, N, K, n_copy):
     torch.manual_seed(7)
     b = (torch.randn(N, K, device=dev) * 0.02).to(torch.bfloat16)
     M = rows * world_size
-    a_out = torch.zeros(M, K, dtype=torch.bfloat16, device=dev)
+    if mode == "push":          # gathered A lands in symmetric memory: shards are broadcast
+        a_out = symm_mem.empty(M, K, dtype=torch.bfloat16, device=dev)
+    elif mode == "pull":        # ordinary a_out, as in the upstream API: shards are fetched
+        a_out = torch.zeros(M, K, dtype=torch.bfloat16, device=dev)
+    else:                       # internal symmetric buffer
+        from symm_mem_recipes_b200.ops.ag_matmul import gather_buffer
+        a_out = None
     c_out = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
     cfg = AgMatmulConfig(n_copy=n_copy, timeout_ms=5000)
     failures = []
     for it in range(3):
         smr.all_gather_matmul(a_shard, b, a_out, c_out, cfg)
         symm_mem.check_status(dev)
+        if a_out is None:
+            a_out = gather_buffer(M, K, dev)
         ref_a = torch.empty_like(a_out)
         torch.distributed.all_gather_into_tensor(ref_a, a_shard)
         if not torch.equal(a_out, ref_a):
@@ -78,6 +86,8 @@ def _agmm_worker(rank, world_size, rows, N, K, n_copy):
         # new data every iteration: stale flags or stale a_out would show
         a_shard.copy_((torch.randn(rows, K, device=dev) * 0.02).to(torch.bfloat16))
         a_out.zero_()
+        if mode == "internal":
+            a_out = None
         torch.cuda.synchronize()
         torch.distributed.barrier()
     c_lib = smr.reference_all_gather_matmul(a_shard, b)
@@ -91,12 +101,20 @@ def _agmm_worker(rank, world_size, rows, N, K, n_copy):
 
 @pytest.mark.gpu
 @pytest.mark.multigpu(2)
-@pytest.mark.parametrize("rows,N,K,n_copy", [(128, 256, 256, 1), (256, 512, 1024, 3), (2048, 3584, 8192, 8)])
-def test_all_gather_matmul_2gpu(rows, N, K, n_copy):
-    spawn_ranks(_agmm_worker, 2, "nccl", (rows, N, K, n_copy))
+@pytest.mark.parametrize("mode", ["push", "pull", "internal"])
+@pytest.mark.parametrize("rows,N,K,n_copy", [(128, 256, 256, 1), (256, 512, 1024, 3), (2048, 3584, 8192, 4)])
+def test_all_gather_matmul_2gpu(rows, N, K, n_copy, mode):
+    spawn_ranks(_agmm_worker, 2, "nccl", (rows, N, K, n_copy, mode))
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu(2)
+def test_all_gather_matmul_push_without_multicast(monkeypatch):
+    monkeypatch.setenv("SMR_DISABLE_MULTICAST", "1")     # plain peer stores instead of multimem.st
+    spawn_ranks(_agmm_worker, 2, "nccl", (256, 512, 1024, 2, "push"))
 
 
 @pytest.mark.gpu
 @pytest.mark.multigpu(8)
 def test_all_gather_matmul_8gpu():
-    spawn_ranks(_agmm_worker, 8, "nccl", (2048, 3584, 8192, 8))
+    spawn_ranks(_agmm_worker, 8, "nccl", (2048, 3584, 8192, 4, "push"))
