@@ -26,7 +26,7 @@ def main() -> int:
     ap.add_argument("--N", type=int, default=6656)
     ap.add_argument("--K", type=int, default=16384)
     ap.add_argument("--BLOCK_SIZE_N", "--block-n", dest="block_n", type=int, default=0)
-    ap.add_argument("--copy-ctas", default="4", help="comma-separated list to sweep")
+    ap.add_argument("--copy-ctas", default="", help="pull mode: comma-separated copier-CTA counts to time")
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--iters", type=int, default=25)
     ap.add_argument("--out", default=None)
@@ -83,15 +83,13 @@ def main() -> int:
     gathered = torch.empty(M, K, dtype=torch.bfloat16, device=dev)
     emit("nccl_all_gather_only",
          benchmark_with_event(lambda: dist.all_gather_into_tensor(gathered, a_shard), **bench))
+    us = benchmark_with_event(lambda: smr.all_gather_matmul(a_shard, b, a_out, c, cfg0), **bench)
+    emit("smr_fused", us, gather="push")
+    symm_mem.check_status(dev)
     for n_copy in [int(x) for x in args.copy_ctas.split(",") if x]:
         cfg = AgMatmulConfig(block_n=args.block_n, n_copy=n_copy)
-        us = benchmark_with_event(lambda: smr.all_gather_matmul(a_shard, b, a_out, c, cfg), **bench)
-        emit("smr_fused", us, copy_ctas=n_copy, gather="push")
-        symm_mem.check_status(dev)
-    if os.environ.get("SMR_BENCH_PULL", "0") == "1":
-        cfg = AgMatmulConfig(block_n=args.block_n, n_copy=16)
         us = benchmark_with_event(lambda: smr.all_gather_matmul(a_shard, b, a_out_plain, c, cfg), **bench)
-        emit("smr_fused", us, copy_ctas=16, gather="pull")
+        emit("smr_fused", us, copy_ctas=n_copy, gather="pull")
         symm_mem.check_status(dev)
     if args.out and rank == 0:
         with open(args.out, "a") as f:

@@ -1,0 +1,57 @@
+"""Barrier smoke test and latency: what `python -m symm_mem_recipes.triton_barrier`
+does upstream (symm_mem_recipes/triton_barrier.py:173-200: 32 CTAs that only run
+the barrier; success = it terminates), plus the device time per barrier.
+
+    torchrun --nnodes 1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        -m symm_mem_recipes_b200.bench.barrier
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--blocks", default="1,32,148")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29513")
+    dist.init_process_group("nccl", device_id=dev, rank=rank, world_size=world)
+
+    import symm_mem_recipes_b200 as smr
+    from symm_mem_recipes_b200.parallel import symm_mem
+    from symm_mem_recipes_b200.utils.benchmark import benchmark_with_graph
+
+    t = symm_mem.empty(4096, dtype=torch.int32, device=dev)     # as upstream: 4096 x u32, zero-filled
+    hdl = symm_mem.rendezvous(t)
+    for blocks in [int(b) for b in args.blocks.split(",")]:
+        smr.barrier_test(hdl, num_blocks=blocks)
+        hdl.check()
+        us = benchmark_with_graph(lambda: smr.barrier_test(hdl, num_blocks=blocks), calls_per_graph=50)
+        if rank == 0:
+            print(json.dumps({"op": "blockwise_barrier", "world_size": world, "blocks": blocks,
+                              "us": round(us, 2), "timing": "graph"}), flush=True)
+    us = benchmark_with_graph(lambda: hdl.barrier(0), calls_per_graph=50)
+    hdl.check()
+    pad_sum = int(hdl.get_signal_pad().abs().sum())
+    if rank == 0:
+        print(json.dumps({"op": "channel_barrier", "world_size": world, "us": round(us, 2), "timing": "graph"}))
+        print(json.dumps({"op": "barrier_test", "signal_pad_abs_sum": pad_sum, "ok": pad_sum == 0}))
+    symm_mem.shutdown()
+    dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,82 @@
+"""Single-GPU timing of the tcgen05 GEMM (the `mm_only` arm of the upstream
+driver, symm_mem_recipes/triton_all_gather_matmul.py:394-405) against cuBLAS,
+and of the world-of-one GEMV and all-reduce kernels.  Also the program that
+`ncu` wraps for the per-kernel profiles under profiles/.
+
+    python -m symm_mem_recipes_b200.bench.matmul --M 16384 --N 3584 --K 8192
+    python -m symm_mem_recipes_b200.bench.matmul --op gemv --batch 16
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+
+import torch
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", default="matmul", choices=["matmul", "gemv", "all_reduce"])
+    ap.add_argument("--M", type=int, default=16384)
+    ap.add_argument("--N", type=int, default=3584)
+    ap.add_argument("--K", type=int, default=8192)
+    ap.add_argument("--block-n", type=int, default=0)
+    ap.add_argument("--batch", type=int, default=16)
+    ap.add_argument("--bytes", type=int, default=64 * 1024 * 1024)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--no-cublas", action="store_true")
+    args = ap.parse_args()
+
+    import symm_mem_recipes_b200 as smr
+    from symm_mem_recipes_b200.ops.ag_matmul import AgMatmulConfig, choose_block_n
+    from symm_mem_recipes_b200.parallel import symm_mem
+    from symm_mem_recipes_b200.utils.benchmark import ClockSampler, benchmark_with_event
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    bench = dict(warmup_iters=args.warmup, benchmark_iters=args.iters, flush_l2=True, all_ranks_max=False)
+    out = {"op": args.op}
+    with ClockSampler(0, period_ms=100) as clocks:
+        if args.op == "matmul":
+            M, N, K = args.M, args.N, args.K
+            a = (torch.randn(M, K, device=dev) * 0.02).to(torch.bfloat16)
+            b = (torch.randn(N, K, device=dev) * 0.02).to(torch.bfloat16)
+            c = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+            cfg = AgMatmulConfig(block_n=args.block_n)
+            flops = 2.0 * M * N * K
+            us = benchmark_with_event(lambda: smr.matmul(a, b, c, cfg), **bench)
+            out.update(M=M, N=N, K=K, block_n=args.block_n or choose_block_n(M, N, 148),
+                       smr_us=round(us, 1), smr_tflops=round(flops / us / 1e6, 1))
+            if not args.no_cublas:
+                bt = b.t()
+                us2 = benchmark_with_event(lambda: torch.matmul(a, bt, out=c), **bench)
+                out.update(cublas_us=round(us2, 1), cublas_tflops=round(flops / us2 / 1e6, 1))
+        elif args.op == "gemv":
+            x = (torch.randn(args.batch, args.K, device=dev) * 0.02).to(torch.bfloat16)
+            w = (torch.randn(args.K, args.N, device=dev) * 0.02).to(torch.bfloat16)
+            y = torch.empty(args.batch, args.N, dtype=torch.bfloat16, device=dev)
+            us = benchmark_with_event(lambda: smr.gemv_all_reduce(x, w, y), **bench)
+            out.update(batch=args.batch, K=args.K, N=args.N, smr_us=round(us, 2),
+                       weight_gbs=round(args.K * args.N * 2 / us / 1e3, 1))
+            if not args.no_cublas:
+                us2 = benchmark_with_event(lambda: torch.matmul(x, w), **bench)
+                out.update(cublas_us=round(us2, 2))
+        else:
+            numel = args.bytes // 2
+            t = symm_mem.empty(numel, dtype=torch.bfloat16, device=dev)
+            t.normal_()
+            o = torch.empty_like(t)
+            us = benchmark_with_event(lambda: smr.one_shot_all_reduce(t, out=o), **bench)
+            out.update(bytes=args.bytes, one_shot_us=round(us, 2),
+                       read_write_gbs=round(2 * args.bytes / us / 1e3, 1))
+        symm_mem.check_status(dev)
+    out["clocks"] = clocks.summary()
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -304,7 +304,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                         std::shared_ptr<CudaSymmAllocation> shard_alloc, int64_t shard_offset,
                         std::shared_ptr<CudaSymmAllocation> aout_alloc, int64_t aout_offset,
                         c10::optional<torch::Tensor> a_out, c10::optional<torch::Tensor> flags,
-                        int block_n, int num_sms, int n_copy, uint64_t timeout_ns) {
+                        int block_n, int num_sms, int n_copy, uint64_t timeout_ns, bool cta_pair) {
     auto ok2d = [](const torch::Tensor& t) {
       return t.is_cuda() && t.dim() == 2 && t.is_contiguous() && t.scalar_type() == torch::kBFloat16;
     };
@@ -359,18 +359,23 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       args.M = (int)a.size(0);
     }
     TORCH_CHECK(c.size(0) == args.M && c.size(1) == args.N, "c must be [M, N]");
-    rt_check(launch_ag_matmul(args, stream), "ag_matmul");
+    rt_check(cta_pair && mode != 1 ? launch_ag_matmul_2cta(args, stream) : launch_ag_matmul(args, stream),
+             "ag_matmul");
   }, py::arg("a"), py::arg("b"), py::arg("c"), py::arg("mode"), py::arg("shard_alloc"),
      py::arg("shard_offset"), py::arg("aout_alloc"), py::arg("aout_offset"), py::arg("a_out"),
-     py::arg("flags"), py::arg("block_n"), py::arg("num_sms"), py::arg("n_copy"), py::arg("timeout_ns"));
+     py::arg("flags"), py::arg("block_n"), py::arg("num_sms"), py::arg("n_copy"), py::arg("timeout_ns"),
+     py::arg("cta_pair") = false);
 
   m.def("gemv_batch_tile", &gemv_batch_tile);
   m.def("gemv_workspace_bytes", [](int batch_tile, int N, int world_size) {
     return gemv_workspace_bytes(batch_tile, N, world_size, nullptr, nullptr, nullptr);
   });
+  m.def("gemv_tc_workspace_bytes", [](int N, int K, int world_size, int num_sms) {
+    return gemv_tc_workspace_bytes(N, K, world_size, num_sms, nullptr, nullptr, nullptr, nullptr);
+  });
   m.def("gemv_all_reduce", [](torch::Tensor x, torch::Tensor w, torch::Tensor out,
                               const std::shared_ptr<CudaSymmAllocation>& workspace, int64_t ws_offset,
-                              uint64_t timeout_ns) {
+                              uint64_t timeout_ns, bool tensor_core, int num_sms) {
     auto ok2d = [](const torch::Tensor& t) {
       return t.is_cuda() && t.dim() == 2 && t.is_contiguous() && t.scalar_type() == torch::kBFloat16;
     };
@@ -392,9 +397,45 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     args.status = status_for(dev);
     int bt = gemv_batch_tile(args.batch);
     TORCH_CHECK(bt > 0, "batch must be between 1 and 16");
+    if (tensor_core) {
+      TORCH_CHECK(gemv_tc_workspace_bytes(args.N, args.K, args.pv.world_size, num_sms, nullptr, nullptr, nullptr,
+                                          nullptr) <= workspace->payload_bytes(), "workspace too small");
+      rt_check(launch_gemv_all_reduce_tc(args, num_sms, current_stream(dev)), "gemv_all_reduce (tcgen05)");
+      return;
+    }
     TORCH_CHECK(gemv_workspace_bytes(bt, args.N, args.pv.world_size, nullptr, nullptr, nullptr) + (size_t)ws_offset
                     <= workspace->payload_bytes(), "workspace too small");
     rt_check(launch_gemv_all_reduce(args, current_stream(dev)), "gemv_all_reduce");
+  }, py::arg("x"), py::arg("w"), py::arg("out"), py::arg("workspace"), py::arg("ws_offset"),
+     py::arg("timeout_ns"), py::arg("tensor_core") = false, py::arg("num_sms") = 148);
+
+  m.def("matmul_rs_workspace_bytes", &matmul_rs_workspace_bytes);
+  m.def("matmul_reduce_scatter", [](torch::Tensor a, torch::Tensor b, torch::Tensor out,
+                                    const std::shared_ptr<CudaSymmAllocation>& workspace, int num_sms,
+                                    uint64_t timeout_ns) {
+    auto ok2d = [](const torch::Tensor& t) {
+      return t.is_cuda() && t.dim() == 2 && t.is_contiguous() && t.scalar_type() == torch::kBFloat16;
+    };
+    TORCH_CHECK(ok2d(a) && ok2d(b) && ok2d(out), "a, b, out must be contiguous 2-D bf16 CUDA tensors");
+    TORCH_CHECK(a.size(1) == b.size(1), "A[M, K] and B[N, K] disagree on K");
+    int dev = a.get_device();
+    c10::cuda::CUDAGuard guard(dev);
+    MatmulRsArgs args{};
+    args.a = a.data_ptr();
+    args.b = b.data_ptr();
+    args.out = out.data_ptr();
+    args.M = (int)a.size(0);
+    args.N = (int)b.size(0);
+    args.K = (int)a.size(1);
+    args.pv = view_of(*workspace);
+    TORCH_CHECK(out.size(0) * args.pv.world_size == args.M && out.size(1) == args.N, "out must be [M / WS, N]");
+    TORCH_CHECK(matmul_rs_workspace_bytes(args.M, args.N) <= workspace->payload_bytes(), "workspace too small");
+    args.inbox_offset = 0;
+    args.local_pad = workspace->peer_pad(args.pv.rank);
+    args.num_sms = num_sms;
+    args.timeout_ns = timeout_ns;
+    args.status = status_for(dev);
+    rt_check(launch_matmul_reduce_scatter(args, current_stream(dev)), "matmul_reduce_scatter");
   });
 
   // ---- oracles (CPU tensors) ----

@@ -1,0 +1,392 @@
+// all_gather_matmul with tcgen05 `cta_group::2`: two CTAs on neighbouring SMs
+// (a cluster of 2) share one 256 x BN tile.  Each CTA stages ITS OWN 128 rows
+// of A and ITS OWN half of the B tile (BN/2 rows) with ordinary TMA loads — no
+// cluster-multicast qualifier anywhere — and the leader CTA's single MMA thread
+// issues `tcgen05.mma.cta_group::2`, which reads A and B from both CTAs'
+// shared memory and writes each CTA's 128 accumulator rows into that CTA's own
+// TMEM.  Per flop every SM pulls half as many B bytes out of L2 as the 1-CTA
+// kernel in ag_matmul_sm100.cu, which is what that kernel is bound by.
+//
+// Hand-offs inside the pair:
+//   full[s]        leader only.  The leader's producer arrives with the byte
+//                  count of BOTH CTAs' loads; both CTAs' TMA loads complete on
+//                  the leader's barrier (`.cta_group::2` form of the load).
+//   empty[s]       both CTAs; `tcgen05.commit ... multicast::cluster` from the
+//                  leader's MMA thread frees the stage in both.
+//   tmem_full[b]   both CTAs; same multicast commit.
+//   tmem_empty[b]  leader only, 8 arrivals: the four epilogue warps of each CTA
+//                  (the peer's arrive through a shared::cluster address).
+// The two 128-row blocks of a pair are two consecutive positions of the M
+// schedule, not necessarily neighbours in memory: each CTA loads, waits for and
+// stores its own block.  Gather modes: none and push (see ag_matmul_sm100.cu);
+// the pull mode stays on the 1-CTA kernel.
+#include "ag_matmul_common.cuh"
+
+namespace smr {
+
+using namespace agmm;
+
+namespace {
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of `smem_addr` (a shared::cta address) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// 2-D tile load whose completion bytes land on a barrier that may sit in the
+// peer CTA of the pair (address in the shared::cluster window).
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map,
+                                                 uint32_t bar_cluster_addr, int32_t x, int32_t y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr),
+        "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+               ::"r"(smem_u32(smem_dst)), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_ss_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                                  uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// One arrival on the barrier at this offset in BOTH CTAs of the pair once all
+// MMAs issued so far have completed.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  const uint16_t mask = 3;
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(smem_u32(bar)), "h"(mask) : "memory");
+}
+
+template <int BN, int STAGES>
+struct PairSmem {
+  static constexpr uint32_t kABytes = kBM * kBK * 2;
+  static constexpr uint32_t kBBytes = (BN / 2) * kBK * 2;     // this CTA's half of the B tile
+  static constexpr uint32_t kStageBytes = kABytes + kBBytes;
+  static constexpr uint32_t kRingBytes = kStageBytes * STAGES;
+  static constexpr uint32_t kBarOffset = kRingBytes;
+  static constexpr uint32_t kNumBars = 2 * STAGES + 4;
+  static constexpr uint32_t kMiscOffset = kBarOffset + 8 * kNumBars;
+  static constexpr uint32_t kTotal = kMiscOffset + 16 + 1024;
+  static_assert(kStageBytes % 1024 == 0, "stage bases must stay 1024-byte aligned");
+};
+
+template <int BN, int STAGES>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
+                      const __grid_constant__ CUtensorMap tmap_a_out,
+                      const __grid_constant__ CUtensorMap tmap_b, const AgMatmulParams p) {
+  using L = PairSmem<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  // same offset in both CTAs: the dynamic window starts at the same shared address
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + STAGES;
+  uint64_t* tmem_full = bars + 2 * STAGES;
+  uint64_t* tmem_empty = bars + 2 * STAGES + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kMiscOffset);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t cta_rank = cluster_ctarank();
+  const bool leader = cta_rank == 0;
+
+  uint32_t epoch = 0, flag_target = p.flag_target;
+  if (p.mode == 2) {
+    epoch = ld_relaxed_gpu(&p.header[0]) + 1u;
+    flag_target = epoch * (uint32_t)p.pieces;
+  }
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tmem_full[b], 1);
+      mbar_init(&tmem_empty[b], 8);   // 4 epilogue warps x 2 CTAs (used in the leader)
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a_shard);
+    tma_prefetch_desc(&tmap_a_out);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tcgen05_fence_before_thread_sync();
+  __syncthreads();
+  cluster_sync_all();                 // barriers of both CTAs initialised, TMEM allocated
+  tcgen05_fence_after_thread_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int pair = (int)blockIdx.x >> 1;
+  const int n_pairs = (int)gridDim.x >> 1;
+  const int n_pair_rows = (p.n_blocks_m + 1) >> 1;         // 256-row tiles along M
+  const int total_tiles = n_pair_rows * p.n_tiles_n;
+  const int k_blocks = (p.K + kBK - 1) / kBK;
+  const int rows_per_rank = p.blocks_per_rank * kBM;
+  bool failed = false;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs) ----------------
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      for (int t = pair; t < total_tiles && !failed; t += n_pairs) {
+        const int mi = (t / p.n_tiles_n) * 2 + (int)cta_rank, ni = t % p.n_tiles_n;
+        bool local = true;
+        const CUtensorMap* amap = &tmap_a_out;
+        int row0;
+        if (mi < p.n_blocks_m) {
+          const int mblk = scheduled_block(p, mi, local);
+          row0 = mblk * kBM;
+          if (p.mode != 0 && local) {
+            amap = &tmap_a_shard;
+            row0 -= p.rank * rows_per_rank;
+          }
+          if (!local) {
+            if (!wait_ge_acquire_sys(&p.flags[mblk], flag_target, p.timeout_ns)) {
+              report_status(p.status, kTimeoutFlag, p.rank, blockIdx.x, mblk, kWhereGemmProgress);
+              failed = true;
+              break;
+            }
+            fence_proxy_async();
+          }
+        } else {
+          row0 = p.n_blocks_m * kBM;   // odd tail: rows past M read as zero
+        }
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.timeout_ns)) {
+            report_status(p.status, kTimeoutMbarrier, p.rank, blockIdx.x, stage, kWhereGemmEmpty);
+            failed = true;
+            break;
+          }
+          uint8_t* sa = smem + (size_t)stage * L::kStageBytes;
+          uint8_t* sb = sa + L::kABytes;
+          if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2u * L::kStageBytes);
+          const uint32_t full_leader = map_to_cta(smem_u32(&full_bar[stage]), 0);
+          tma_load_2d_pair(sa, amap, full_leader, kb * kBK, row0);
+          tma_load_2d_pair(sb, &tmap_b, full_leader, kb * kBK, ni * BN + (int)cta_rank * (BN / 2));
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader CTA only) ----------------
+    if (leader && lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16_f32(2 * kBM, BN);
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+      for (int t = pair; t < total_tiles && !failed; t += n_pairs) {
+        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, p.timeout_ns)) {
+          report_status(p.status, kTimeoutMbarrier, p.rank, blockIdx.x, acc, kWhereGemmTmemEmpty);
+          failed = true;
+          break;
+        }
+        tcgen05_fence_after_thread_sync();
+        const uint32_t d_tmem = tmem_base + acc * 256u;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, p.timeout_ns)) {
+            report_status(p.status, kTimeoutMbarrier, p.rank, blockIdx.x, stage, kWhereGemmFull);
+            failed = true;
+            break;
+          }
+          tcgen05_fence_after_thread_sync();
+          const uint32_t sa = smem_u32(smem + (size_t)stage * L::kStageBytes);
+          const uint64_t da = umma_smem_desc_sw128(sa);
+          const uint64_t db = umma_smem_desc_sw128(sa + L::kABytes);
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k)
+            umma_bf16_ss_pair(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc,
+                              (kb | k) != 0 ? 1u : 0u);
+          umma_commit_pair(&empty_bar[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (failed) break;
+        umma_commit_pair(&tmem_full[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5 of both CTAs) ----------------
+    const int quarter = warp & 3;
+    uint32_t acc = 0, acc_phase = 0;
+    const int etid = (int)threadIdx.x - 64;
+    int next_piece = (int)blockIdx.x, round = 0;
+    const int all_pieces = p.blocks_per_rank * p.pieces;
+    if (p.mode == 2 && !push_entry_barrier(p, (int)blockIdx.x, etid)) failed = true;
+    for (int t = pair; t < total_tiles && !failed; t += n_pairs) {
+      const int mi = (t / p.n_tiles_n) * 2 + (int)cta_rank, ni = t % p.n_tiles_n;
+      bool local_unused;
+      const bool valid = mi < p.n_blocks_m;
+      const int mblk = valid ? scheduled_block(p, mi, local_unused) : 0;
+      if (p.mode == 2) {
+        next_piece = push_pieces(p, next_piece, (int)gridDim.x,
+                                 pieces_needed_through_round(p, round + 1, n_pairs, 2), etid);
+        ++round;
+      }
+      if (!mbar_wait(&tmem_full[acc], acc_phase, p.timeout_ns)) {
+        if (lane == 0)
+          report_status(p.status, kTimeoutMbarrier, p.rank, blockIdx.x, acc, kWhereGemmTmemFull);
+        failed = true;
+        break;
+      }
+      tcgen05_fence_after_thread_sync();
+      const int row = mblk * kBM + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + acc * 256u + ((uint32_t)(quarter * 32) << 16);
+      __nv_bfloat16* crow = p.c + (size_t)row * p.N + (size_t)ni * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(taddr + (uint32_t)(c * 32), r);
+        tmem_ld_wait();
+        const int col0 = ni * BN + c * 32;
+        if (valid && row < p.M) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            if (col0 + v * 8 < p.N) {
+              Vec16 o;
+              o.x = pack_bf16x2(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
+              o.y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+              o.z = pack_bf16x2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+              o.w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+              st_16(crow + c * 32 + v * 8, o);
+            }
+          }
+        }
+      }
+      tcgen05_fence_before_thread_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc]), 0));
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+    if (p.mode == 2 && !failed) push_pieces(p, next_piece, (int)gridDim.x, all_pieces, etid);
+  }
+
+  // ---------------- teardown ----------------
+  if (__any_sync(0xffffffffu, failed)) {
+    for (int i = 0; i < 100; ++i) __nanosleep(1000);
+  }
+  tcgen05_fence_before_thread_sync();
+  __syncthreads();
+  cluster_sync_all();   // the peer may still read this CTA's smem / signal its barriers until here
+  tcgen05_fence_after_thread_sync();
+  if (warp == 1) tmem_dealloc_pair(tmem_base, kTmemCols);
+  if (p.mode == 2 && threadIdx.x == 0) {
+    uint32_t done = atomicAdd(&p.header[1], 1u);
+    if (done == gridDim.x - 1) {
+      p.header[1] = 0u;
+      __threadfence();
+      st_release_gpu(&p.header[0], epoch);
+    }
+  }
+}
+
+template <int BN, int STAGES>
+int launch_pair_variant(const CUtensorMap& ta_shard, const CUtensorMap& ta_out, const CUtensorMap& tb,
+                        const AgMatmulParams& p, int grid, cudaStream_t stream) {
+  using L = PairSmem<BN, STAGES>;
+  static_assert(L::kTotal <= 232448, "shared memory budget exceeded");
+  auto kern = ag_matmul_2cta_kernel<BN, STAGES>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::kTotal);
+  if (e != cudaSuccess) return (int)e;
+  kern<<<grid, kGemmThreads, L::kTotal, stream>>>(ta_shard, ta_out, tb, p);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+int launch_ag_matmul_2cta(const AgMatmulArgs& a, cudaStream_t stream) {
+  if (a.N % 8 != 0 || a.K % 8 != 0 || a.M <= 0 || a.N <= 0 || a.K <= 0) return cudaErrorInvalidValue;
+  if (a.mode != 0 && a.mode != 2) return cudaErrorInvalidValue;   // pull mode: 1-CTA kernel
+  const bool comm = a.mode == 2;
+  if (comm) {
+    if (a.world_size < 2 || a.rows_per_rank % kBM != 0 || a.rows_per_rank * a.world_size != a.M ||
+        a.a_out == nullptr || a.pads == nullptr || a.aout_buffers == nullptr || a.local_pad == nullptr)
+      return cudaErrorInvalidValue;
+    if ((uint32_t)(a.M / kBM) + 2u > kFlagSlots) return cudaErrorInvalidValue;
+  }
+  const int bn = a.block_n;
+  if (bn != 128 && bn != 192 && bn != 224 && bn != 256) return cudaErrorInvalidValue;
+
+  AgMatmulParams p{};
+  p.c = static_cast<__nv_bfloat16*>(a.c);
+  p.M = a.M; p.N = a.N; p.K = a.K;
+  p.n_tiles_n = (a.N + bn - 1) / bn;
+  p.n_blocks_m = (a.M + kBM - 1) / kBM;
+  p.rank = comm ? a.rank : 0;
+  p.world_size = comm ? a.world_size : 1;
+  p.blocks_per_rank = comm ? a.rows_per_rank / kBM : p.n_blocks_m;
+  p.n_copy = 0;
+  p.mode = a.mode;
+  p.lead = 0;
+  p.pieces = 1;
+  if (comm) {
+    p.lead = p.blocks_per_rank < 4 ? p.blocks_per_rank : 4;
+    size_t block_vecs = (size_t)kBM * a.K * 2 / 16;
+    p.pieces = block_vecs >= 8192 ? 16 : (block_vecs >= 1024 ? 4 : 1);
+  }
+  p.flags = comm ? a.local_pad + kFlagSlotsBase + 2 : nullptr;
+  p.flag_target = 1u;
+  p.header = comm ? a.local_pad + kFlagSlotsBase : nullptr;
+  p.a_local = static_cast<const char*>(a.a_local);
+  p.aout_buffers = a.aout_buffers;
+  p.aout_mc = a.aout_mc;
+  p.aout_offset = a.aout_offset;
+  p.a_out = static_cast<char*>(a.a_out);
+  p.pads = a.pads;
+  p.barrier_block_base = a.barrier_block_base;
+  p.timeout_ns = a.timeout_ns;
+  p.status = a.status;
+
+  CUtensorMap ta_shard, ta_out, tb;
+  int rows_local = comm ? a.rows_per_rank : a.M;
+  if (make_tmap(&ta_shard, a.a_local, (uint64_t)rows_local, (uint64_t)a.K, kBM)) return cudaErrorInvalidValue;
+  if (make_tmap(&ta_out, comm ? a.a_out : a.a_local, (uint64_t)a.M, (uint64_t)a.K, kBM)) return cudaErrorInvalidValue;
+  if (make_tmap(&tb, a.b, (uint64_t)a.N, (uint64_t)a.K, (uint32_t)(bn / 2))) return cudaErrorInvalidValue;
+
+  const int total_tiles = ((p.n_blocks_m + 1) / 2) * p.n_tiles_n;
+  int pairs = a.num_sms / 2;
+  if (pairs > total_tiles) pairs = total_tiles;
+  if (pairs < 1) return cudaErrorInvalidValue;
+  const int grid = 2 * pairs;
+  switch (bn) {
+    case 128: return launch_pair_variant<128, 8>(ta_shard, ta_out, tb, p, grid, stream);
+    case 192: return launch_pair_variant<192, 7>(ta_shard, ta_out, tb, p, grid, stream);
+    case 224: return launch_pair_variant<224, 7>(ta_shard, ta_out, tb, p, grid, stream);
+    default:  return launch_pair_variant<256, 6>(ta_shard, ta_out, tb, p, grid, stream);
+  }
+}
+
+}  // namespace smr

@@ -1,0 +1,198 @@
+// Pieces shared by the 1-CTA and the 2-CTA (cta_group::2) all_gather_matmul
+// kernels: parameters, the M schedule, the epilogue-warp push of the own shard
+// and the tensor-map builder.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "../device/barrier.cuh"
+#include "../device/mbarrier.cuh"
+#include "../device/multimem.cuh"
+#include "../device/tcgen05.cuh"
+#include "../device/tma.cuh"
+#include "../device/vec.cuh"
+#include "../symm/driver_api.h"
+#include "launch.h"
+
+namespace smr {
+namespace agmm {
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;           // 64 bf16 = 128 bytes = one swizzle row
+constexpr int kUmmaK = 16;
+constexpr int kGemmThreads = 192; // 6 warps
+constexpr int kEpiWarp0 = 2;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kCopyChunk = 16384;   // bytes per bulk copy
+constexpr int kStoreLag = 2;             // bulk stores allowed to still read smem
+constexpr int kFlagLag = 6;              // chunks after which a block's writes are drained
+
+struct AgMatmulParams {
+  __nv_bfloat16* c;      // [M, N]
+  int M, N, K;
+  int n_tiles_n;         // ceil(N / BN)
+  int n_blocks_m;        // ceil(M / 128)
+  // gather
+  int rank, world_size;
+  int blocks_per_rank;   // 128-row blocks per shard
+  int n_copy;            // copier CTAs (0 = no communication)
+  int mode;              // 0 none, 1 pull, 2 push
+  int lead;              // own blocks scheduled before the first remote one
+  int pieces;            // push: pieces per 128-row block (arrivals per block and call)
+  uint32_t* flags;       // [n_blocks_m] arrival flags read by the GEMM CTAs (local memory)
+  uint32_t flag_target;  // pull: 1 (flags zeroed before launch); push: filled from the epoch
+  uint32_t* header;      // push: [0] epoch, [1] CTAs done (local, in the a_out signal pad)
+  const char* a_local;   // own shard
+  void* const* aout_buffers;   // push: payload base of the a_out allocation on every rank
+  void* aout_mc;         // push: multicast payload base of the a_out allocation, or nullptr
+  size_t aout_offset;    // push: offset of a_out inside that payload
+  void* const* buffers;  // device table [WS]: symmetric payload base of every rank (peer-mapped)
+  size_t shard_offset;   // offset of the A shard inside the payload
+  char* a_out;           // local gathered A [M, K]
+  uint32_t* const* pads; // signal pads (entry / exit barrier of the copiers)
+  uint32_t barrier_block_base;     // first blockwise-barrier slot id used by copiers
+  uint64_t timeout_ns;
+  Status* status;
+};
+
+// ---------------------------------------------------------------------------
+// Push, run by the 128 epilogue threads of every GEMM CTA before their first
+// tile: entry barrier, then pieces `cta, cta + n_ctas, ...` of the OWN shard
+// are broadcast into every rank's a_out and the arrival counters bumped.
+// `etid` is the thread's index among the 128; named barrier 1 joins them.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void epilogue_group_sync() {
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+}
+
+// Entry barrier of the push mode, among the CTAs with this index on every rank.
+__device__ inline bool push_entry_barrier(const AgMatmulParams& p, int cta, int etid) {
+  __shared__ int entry_ok;
+  if (etid == 0) entry_ok = 1;
+  epilogue_group_sync();
+  if (etid < p.world_size) {
+    if (!barrier_signal_wait(p.pads, (p.barrier_block_base + (uint32_t)cta) * (uint32_t)p.world_size,
+                             p.rank, p.world_size, etid, p.timeout_ns, p.status,
+                             p.barrier_block_base + (uint32_t)cta, kWhereCopierEntry))
+      entry_ok = 0;
+  }
+  epilogue_group_sync();
+  return entry_ok != 0;
+}
+
+// Broadcast this CTA's pieces `next, next + n_ctas, ...` while they are below
+// `limit` (an index into the piece sequence of the shard).  Returns the first
+// piece not pushed.
+__device__ inline int push_pieces(const AgMatmulParams& p, int next, int n_ctas, int limit, int etid) {
+  constexpr int U = 8;
+  const size_t block_vecs = (size_t)kBM * p.K * 2 / 16;
+  const size_t piece_vecs = (block_vecs + p.pieces - 1) / p.pieces;
+  int piece = next;
+  for (; piece < limit; piece += n_ctas) {
+    const int blk = piece / p.pieces, sub = piece - blk * p.pieces;
+    const int gblk = p.rank * p.blocks_per_rank + blk;
+    const size_t v0 = (size_t)sub * piece_vecs;
+    const size_t v1 = v0 + piece_vecs < block_vecs ? v0 + piece_vecs : block_vecs;
+    const Vec16* src = reinterpret_cast<const Vec16*>(p.a_local) + (size_t)blk * block_vecs;
+    const size_t dst_off = p.aout_offset + (size_t)gblk * block_vecs * 16;
+    if (p.aout_mc != nullptr) {
+      Vec16* dst = reinterpret_cast<Vec16*>(static_cast<char*>(p.aout_mc) + dst_off);
+      for (size_t i = v0 + etid; i < v1; i += (size_t)128 * U) {
+        Vec16 v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          if (i + (size_t)u * 128 < v1) v[u] = ld_16_nc(src + i + (size_t)u * 128);
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          if (i + (size_t)u * 128 < v1) multimem_st_16(dst + i + (size_t)u * 128, v[u]);
+      }
+    } else {
+      for (size_t i = v0 + etid; i < v1; i += (size_t)128 * U) {
+        Vec16 v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          if (i + (size_t)u * 128 < v1) v[u] = ld_16_nc(src + i + (size_t)u * 128);
+        for (int s2 = 1; s2 <= p.world_size; ++s2) {      // own a_out last
+          int peer = (p.rank + s2) % p.world_size;
+          Vec16* dst = reinterpret_cast<Vec16*>(static_cast<char*>(p.aout_buffers[peer]) + dst_off);
+#pragma unroll
+          for (int u = 0; u < U; ++u)
+            if (i + (size_t)u * 128 < v1) st_16(dst + i + (size_t)u * 128, v[u]);
+        }
+      }
+    }
+    epilogue_group_sync();   // the group's stores precede the releases below
+    if (etid < p.world_size)
+      red_add_release_sys(p.pads[etid] + kFlagSlotsBase + 2 + gblk, 1u);
+  }
+  return piece;
+}
+
+// Position `mi` of the M schedule -> 128-row block of the gathered A.
+//   mi < lead                      own block mi
+//   then groups k = 0 .. : block k of rank+1 .. rank+WS-1, then own block
+//   lead + k while own blocks remain.
+__device__ __forceinline__ int scheduled_block(const AgMatmulParams& p, int mi, bool& local) {
+  if (p.mode == 0) {
+    local = true;
+    return mi;
+  }
+  const int ws = p.world_size, bpr = p.blocks_per_rank;
+  int step, k;
+  if (mi < p.lead) {
+    step = 0; k = mi;
+  } else {
+    int q = mi - p.lead;
+    const int full = bpr - p.lead;             // groups that still carry an own block
+    if (q < full * ws) {
+      int g = q / ws, s2 = q - g * ws;
+      if (s2 < ws - 1) { step = s2 + 1; k = g; }
+      else { step = 0; k = g + p.lead; }
+    } else {
+      q -= full * ws;
+      int g = q / (ws - 1), s2 = q - g * (ws - 1);
+      step = s2 + 1; k = full + g;
+    }
+  }
+  int src = p.rank + step;
+  if (src >= ws) src -= ws;
+  local = (step == 0);
+  return src * bpr + k;
+}
+
+// Pieces of the own shard that every rank must have pushed before any CTA may
+// block on the tiles of rounds <= `round` (round j = tiles j*G .. (j+1)*G-1 of
+// the static schedule): all pieces of the remote blocks those tiles read.
+// `n_units` tiles run concurrently (CTAs, or CTA pairs); a tile covers
+// `pos_per_tile` consecutive schedule positions (1, or 2 for a CTA pair).
+__device__ __forceinline__ int pieces_needed_through_round(const AgMatmulParams& p, int round,
+                                                           int n_units, int pos_per_tile = 1) {
+  const int ws = p.world_size, bpr = p.blocks_per_rank;
+  long long tiles = (long long)(round + 1) * n_units;
+  int mi_end = (int)((tiles + p.n_tiles_n - 1) / p.n_tiles_n) * pos_per_tile;   // positions touched: [0, mi_end)
+  if (mi_end > p.n_blocks_m) mi_end = p.n_blocks_m;
+  if (mi_end <= p.lead) return 0;
+  int q = mi_end - 1 - p.lead;
+  const int full = bpr - p.lead;
+  int k_max = q < full * ws ? q / ws : full + (q - full * ws) / (ws - 1);
+  if (k_max >= bpr) k_max = bpr - 1;
+  return (k_max + 1) * p.pieces;
+}
+
+// row-major bf16 [rows, cols] with a [box_rows x 64] box and 128-byte swizzle
+inline int make_tmap(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  const DriverApi& d = DriverApi::get();
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 2};
+  cuuint32_t box[2] = {(cuuint32_t)kBK, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = d.cuTensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base),
+                                        dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+
+}  // namespace agmm
+}  // namespace smr

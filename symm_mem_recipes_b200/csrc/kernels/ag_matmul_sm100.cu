@@ -8,25 +8,33 @@
 // to Blackwell:
 //
 //  * grid = n_copy "copier" CTAs + (SMs - n_copy) GEMM CTAs, one per SM.
-//  * copier CTA, PUSH mode (a_out in symmetric memory; the default): every
-//    rank broadcasts its OWN shard, 128-row block by block, into the a_out of
-//    all ranks with `multimem.st` on the NVLink multicast address, so a shard
-//    leaves its GPU once and the NVSwitch fans it out (plain peer stores when
-//    there is no multicast mapping).  After a block it adds 1 to that block's
-//    arrival counter on every rank (red.release.sys); the counter of call
-//    number e reads e, so nothing is reset between calls.  An entry barrier
-//    over the signal pad proves that every rank has finished reading the
-//    a_out of the previous call.
-//  * copier CTA, PULL mode (a_out is an ordinary tensor, as upstream): one
-//    thread pulls the peers' shards with untiled TMA bulk copies peer-HBM ->
+//  * PUSH mode (a_out in symmetric memory; the default): no SM is set aside
+//    for communication.  Every rank broadcasts its OWN shard into the a_out
+//    of all ranks with `multimem.st` on the NVLink multicast address, so a
+//    shard leaves its GPU once and the NVSwitch fans it out (plain peer stores
+//    when there is no multicast mapping).  The shard is cut into pieces of
+//    1/16 of a 128-row block, dealt round-robin to ALL GEMM CTAs, whose four
+//    epilogue warps push them in the time they would otherwise idle waiting
+//    for an accumulator: before the epilogue of its j-th tile a CTA pushes its
+//    pieces of every block that some tile of round j+1 reads, so the data is
+//    on the wire one tile-time ahead of need and no CTA can block while it
+//    holds a piece a peer waits for.  One SM sustains only ~30 GB/s of NVLink
+//    stores (measured); spread over 148 SMs the gather costs no SM at all.
+//    After a piece, the block's arrival counter on every rank gets +1
+//    (red.release.sys); the counter of call number e reads pieces * e, so
+//    nothing is reset between calls.  An entry barrier over the signal pad, run by
+//    the epilogue warps, proves that every rank has finished reading the a_out
+//    of the previous call.
+//  * PULL mode (a_out is an ordinary tensor, as upstream): n_copy copier
+//    CTAs are set aside; in each, one thread pulls the peers' shards with untiled TMA bulk copies peer-HBM ->
 //    shared memory -> local a_out and publishes one flag per block once its
 //    writes are done; entry barrier = the peers' shards are ready, exit
 //    barrier = they may be overwritten (upstream :56, :250).
-//  * M is visited so that the k-th block of every shard is consumed before
-//    the (k+1)-th of any: own shard's block first (never waits), then the
-//    same block of rank+1, rank+2, ... (upstream pivots by rank, :157-163).
-//    All senders deliver their k-th blocks at about the same time, so this
-//    order keeps the GEMM behind the arrivals.
+//  * M schedule: a few blocks of the own shard first (they never wait and
+//    cover the start-up of the gather), then, for k = 0, 1, ...: block k of
+//    rank+1, rank+2, ... and one more own block (upstream pivots by rank,
+//    :157-163).  All senders deliver their k-th blocks at about the same
+//    time, so this order keeps the GEMM behind the arrivals.
 //  * GEMM CTA, warp-specialised:
 //      warp 0   TMA producer: waits for the block's flag (remote blocks
 //               only), then loads A [128 x 64] and B [BN x 64] tiles with the
@@ -40,57 +48,13 @@
 //    records a Status, lets copies in flight land, frees TMEM and returns.
 //
 // With n_copy = 0 the kernel is a plain persistent GEMM (upstream's `mm_only`).
-#include <cuda.h>
-#include <cuda_runtime.h>
-
-#include "../device/barrier.cuh"
-#include "../device/mbarrier.cuh"
-#include "../device/multimem.cuh"
-#include "../device/tcgen05.cuh"
-#include "../device/tma.cuh"
-#include "../device/vec.cuh"
-#include "../symm/driver_api.h"
-#include "launch.h"
+#include "ag_matmul_common.cuh"
 
 namespace smr {
 
+using namespace agmm;
+
 namespace {
-
-constexpr int kBM = 128;
-constexpr int kBK = 64;           // 64 bf16 = 128 bytes = one swizzle row
-constexpr int kUmmaK = 16;
-constexpr int kGemmThreads = 192; // 6 warps
-constexpr int kEpiWarp0 = 2;
-constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kCopyChunk = 16384;   // bytes per bulk copy
-constexpr int kStoreLag = 2;             // bulk stores allowed to still read smem
-constexpr int kFlagLag = 6;              // chunks after which a block's writes are drained
-
-struct AgMatmulParams {
-  __nv_bfloat16* c;      // [M, N]
-  int M, N, K;
-  int n_tiles_n;         // ceil(N / BN)
-  int n_blocks_m;        // ceil(M / 128)
-  // gather
-  int rank, world_size;
-  int blocks_per_rank;   // 128-row blocks per shard
-  int n_copy;            // copier CTAs (0 = no communication)
-  int mode;              // 0 none, 1 pull, 2 push
-  uint32_t* flags;       // [n_blocks_m] arrival flags read by the GEMM CTAs (local memory)
-  uint32_t flag_target;  // pull: 1 (flags zeroed before launch); push: filled from the epoch
-  uint32_t* header;      // push: [0] epoch, [1] CTAs done (local, in the a_out signal pad)
-  const char* a_local;   // own shard
-  void* const* aout_buffers;   // push: payload base of the a_out allocation on every rank
-  void* aout_mc;         // push: multicast payload base of the a_out allocation, or nullptr
-  size_t aout_offset;    // push: offset of a_out inside that payload
-  void* const* buffers;  // device table [WS]: symmetric payload base of every rank (peer-mapped)
-  size_t shard_offset;   // offset of the A shard inside the payload
-  char* a_out;           // local gathered A [M, K]
-  uint32_t* const* pads; // signal pads (entry / exit barrier of the copiers)
-  uint32_t barrier_block_base;     // first blockwise-barrier slot id used by copiers
-  uint64_t timeout_ns;
-  Status* status;
-};
 
 template <int BN, int STAGES>
 struct SmemLayout {
@@ -203,95 +167,6 @@ __device__ void copier_thread(const AgMatmulParams& p, int copier, uint8_t* ring
   // refill of chunk (index - NBUF + kStoreLag).
 }
 
-// ---------------------------------------------------------------------------
-// Push copier: the whole CTA broadcasts blocks `copier, copier + n_copy, ...`
-// of the OWN shard into every rank's a_out and bumps the arrival counters.
-// Thread 0 streams the shard from local HBM into a shared-memory ring with TMA
-// bulk loads (the ring, ~200 KB, is what is in flight); all threads then move
-// each chunk from shared memory to the multicast address with multimem.st.
-// ---------------------------------------------------------------------------
-constexpr uint32_t kPushChunk = 32768;
-
-template <int BN, int STAGES>
-__device__ void copier_push(const AgMatmulParams& p, int copier, uint8_t* ring, uint64_t* cbar) {
-  using L = SmemLayout<BN, STAGES>;
-  constexpr uint32_t NBUF = L::kRingBytes / kPushChunk;
-  static_assert(NBUF >= 3 && NBUF <= 32, "ring size");
-  const size_t block_bytes = (size_t)kBM * p.K * 2;
-  const uint32_t chunks_per_block = (uint32_t)((block_bytes + kPushChunk - 1) / kPushChunk);
-  const int tid = threadIdx.x;
-  int my_blocks = 0;
-  for (int b = copier; b < p.blocks_per_rank; b += p.n_copy) ++my_blocks;
-  const uint32_t total_chunks = (uint32_t)my_blocks * chunks_per_block;
-
-  auto chunk_of = [&](uint32_t c, const char*& src, size_t& dst_off, uint32_t& bytes, int& gblk) {
-    int blk = copier + (int)(c / chunks_per_block) * p.n_copy;
-    size_t off = (size_t)(c % chunks_per_block) * kPushChunk;
-    size_t left = block_bytes - off;
-    bytes = (uint32_t)(left < kPushChunk ? left : kPushChunk);
-    src = p.a_local + (size_t)blk * block_bytes + off;
-    gblk = p.rank * p.blocks_per_rank + blk;
-    dst_off = p.aout_offset + (size_t)gblk * block_bytes + off;
-  };
-  auto issue = [&](uint32_t c) {
-    const char* src; size_t dst_off; uint32_t bytes; int gblk;
-    chunk_of(c, src, dst_off, bytes, gblk);
-    uint32_t b = c % NBUF;
-    mbar_arrive_expect_tx(&cbar[b], bytes);
-    bulk_load(ring + (size_t)b * kPushChunk, src, bytes, &cbar[b]);
-  };
-
-  if (tid == 0)
-    for (uint32_t c = 0; c < total_chunks && c < NBUF - 1; ++c) issue(c);
-  bool ok = true;
-  for (uint32_t c = 0; c < total_chunks; ++c) {
-    // buffer (c-1) % NBUF was released by the __syncthreads that ended iteration c-1
-    if (tid == 0 && c + NBUF - 1 < total_chunks) issue(c + NBUF - 1);
-    const char* src; size_t dst_off; uint32_t bytes; int gblk;
-    chunk_of(c, src, dst_off, bytes, gblk);
-    const uint32_t b = c % NBUF;
-    if (!mbar_wait(&cbar[b], (c / NBUF) & 1u, p.timeout_ns)) {
-      if (tid == 0)
-        report_status(p.status, kTimeoutMbarrier, p.rank, blockIdx.x, 0, kWhereCopierEntry, c);
-      ok = false;
-    }
-    if (!__syncthreads_and(ok)) {
-      for (int i = 0; i < 100; ++i) __nanosleep(1000);   // let the bulk loads in flight land
-      return;
-    }
-    const Vec16* sv = reinterpret_cast<const Vec16*>(ring + (size_t)b * kPushChunk);
-    const uint32_t vecs = bytes / 16;
-    if (p.aout_mc != nullptr) {
-      Vec16* dst = reinterpret_cast<Vec16*>(static_cast<char*>(p.aout_mc) + dst_off);
-#pragma unroll 4
-      for (uint32_t i = tid; i < vecs; i += kGemmThreads) multimem_st_16(dst + i, sv[i]);
-    } else {
-      for (int s = 1; s <= p.world_size; ++s) {        // own a_out last
-        int peer = (p.rank + s) % p.world_size;
-        Vec16* dst = reinterpret_cast<Vec16*>(static_cast<char*>(p.aout_buffers[peer]) + dst_off);
-#pragma unroll 4
-        for (uint32_t i = tid; i < vecs; i += kGemmThreads) st_16(dst + i, sv[i]);
-      }
-    }
-    __syncthreads();   // chunk consumed: its buffer may be refilled; stores precede the release
-    if ((c % chunks_per_block) == chunks_per_block - 1 && tid < p.world_size)
-      red_add_release_sys(p.pads[tid] + kFlagSlotsBase + 2 + gblk, 1u);
-  }
-}
-
-// Position `mi` of the M schedule -> 128-row block of the gathered A.
-__device__ __forceinline__ int scheduled_block(const AgMatmulParams& p, int mi, bool& local) {
-  if (p.mode == 0) {
-    local = true;
-    return mi;
-  }
-  int k = mi / p.world_size, step = mi % p.world_size;
-  int src = p.rank + step;
-  if (src >= p.world_size) src -= p.world_size;
-  local = (step == 0);
-  return src * p.blocks_per_rank + k;
-}
-
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 ag_matmul_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
@@ -312,37 +187,26 @@ ag_matmul_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
   const int lane = threadIdx.x & 31;
 
   // push mode: this call's number, the value every arrival counter will reach
-  uint32_t flag_target = p.flag_target;
-  if (p.mode == 2) flag_target = ld_relaxed_gpu(&p.header[0]) + 1u;
+  uint32_t epoch = 0, flag_target = p.flag_target;
+  if (p.mode == 2) {
+    epoch = ld_relaxed_gpu(&p.header[0]) + 1u;
+    flag_target = epoch * (uint32_t)p.pieces;
+  }
 
-  // ======================= copier CTAs =======================
+  // ======================= copier CTAs (pull mode only) =======================
   if ((int)blockIdx.x < p.n_copy) {
     if (threadIdx.x == 0) {
       for (int i = 0; i < 32; ++i) mbar_init(&copy_bar[i], 1);
       mbar_fence_init();
     }
-    // entry: every peer has entered this call, i.e. its shard is written and
-    // it no longer reads the a_out of the previous call
+    // entry: every peer's shard is written (its earlier kernels are done)
     bool ok = blockwise_barrier(p.pads, p.barrier_block_base + blockIdx.x, p.rank, p.world_size,
                                 p.timeout_ns, p.status, kWhereCopierEntry);
-    if (ok && p.mode == 2) {
-      copier_push<BN, STAGES>(p, (int)blockIdx.x, smem, copy_bar);
-    } else if (ok) {
+    if (ok) {
       if (threadIdx.x == 0) copier_thread<BN, STAGES>(p, (int)blockIdx.x, smem, copy_bar);
       // exit: every peer has finished reading this rank's shard
       blockwise_barrier(p.pads, p.barrier_block_base + blockIdx.x, p.rank, p.world_size,
                         p.timeout_ns, p.status, kWhereCopierExit);
-    }
-    if (p.mode == 2) {
-      __syncthreads();
-      if (threadIdx.x == 0) {
-        uint32_t done = atomicAdd(&p.header[1], 1u);
-        if (done == gridDim.x - 1) {
-          p.header[1] = 0u;
-          __threadfence();
-          st_release_gpu(&p.header[0], flag_target);
-        }
-      }
     }
     return;
   }
@@ -458,10 +322,21 @@ ag_matmul_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
     // ---------------- epilogue (warps 2..5) ----------------
     const int quarter = warp & 3;           // TMEM lanes [32*quarter, +32)
     uint32_t acc = 0, acc_phase = 0;
+    // push mode: this CTA's pieces of the own shard go out just ahead of need,
+    // one round of tiles in advance, so the epilogue warps never sit on data a
+    // peer is waiting for
+    const int etid = (int)threadIdx.x - 64;
+    int next_piece = gemm_cta, round = 0;
+    const int all_pieces = p.blocks_per_rank * p.pieces;
+    if (p.mode == 2 && !push_entry_barrier(p, gemm_cta, etid)) failed = true;
     for (int t = gemm_cta; t < total_tiles && !failed; t += n_gemm) {
       int mi = t / p.n_tiles_n, ni = t % p.n_tiles_n;
       bool local_unused;
       const int mblk = scheduled_block(p, mi, local_unused);
+      if (p.mode == 2) {
+        next_piece = push_pieces(p, next_piece, n_gemm, pieces_needed_through_round(p, round + 1, n_gemm), etid);
+        ++round;
+      }
       if (!mbar_wait(&tmem_full[acc], acc_phase, p.timeout_ns)) {
         if (lane == 0)
           report_status(p.status, kTimeoutMbarrier, p.rank, blockIdx.x, acc, kWhereGemmTmemFull);
@@ -498,6 +373,7 @@ ag_matmul_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
+    if (p.mode == 2 && !failed) push_pieces(p, next_piece, n_gemm, all_pieces, etid);
   }
 
   // ---------------- teardown ----------------
@@ -515,23 +391,9 @@ ag_matmul_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
     if (done == gridDim.x - 1) {
       p.header[1] = 0u;
       __threadfence();
-      st_release_gpu(&p.header[0], flag_target);
+      st_release_gpu(&p.header[0], epoch);
     }
   }
-}
-
-// row-major bf16 [rows, cols] with a [box_rows x 64] box and 128-byte swizzle
-int make_tmap(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
-  const DriverApi& d = DriverApi::get();
-  cuuint64_t dims[2] = {cols, rows};
-  cuuint64_t strides[1] = {cols * 2};
-  cuuint32_t box[2] = {(cuuint32_t)kBK, box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = d.cuTensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base),
-                                        dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
 template <int BN, int STAGES>
@@ -552,7 +414,7 @@ int launch_ag_matmul(const AgMatmulArgs& a, cudaStream_t stream) {
   if (a.N % 8 != 0 || a.K % 8 != 0 || a.M <= 0 || a.N <= 0 || a.K <= 0) return cudaErrorInvalidValue;
   const bool comm = a.mode != 0;
   if (comm) {
-    if (a.n_copy < 1 || a.world_size < 2 || a.rows_per_rank % kBM != 0 ||
+    if ((a.mode == 1 && a.n_copy < 1) || a.world_size < 2 || a.rows_per_rank % kBM != 0 ||
         a.rows_per_rank * a.world_size != a.M || a.a_out == nullptr || a.pads == nullptr)
       return cudaErrorInvalidValue;
     if (a.mode == 1 && (a.buffers == nullptr || a.flags == nullptr)) return cudaErrorInvalidValue;
@@ -570,8 +432,15 @@ int launch_ag_matmul(const AgMatmulArgs& a, cudaStream_t stream) {
   p.rank = comm ? a.rank : 0;
   p.world_size = comm ? a.world_size : 1;
   p.blocks_per_rank = comm ? a.rows_per_rank / kBM : p.n_blocks_m;
-  p.n_copy = comm ? a.n_copy : 0;
+  p.n_copy = a.mode == 1 ? a.n_copy : 0;
   p.mode = comm ? a.mode : 0;
+  p.lead = 0;
+  p.pieces = 1;
+  if (a.mode == 2) {
+    p.lead = p.blocks_per_rank < 4 ? p.blocks_per_rank : 4;
+    size_t block_vecs = (size_t)kBM * a.K * 2 / 16;
+    p.pieces = block_vecs >= 8192 ? 16 : (block_vecs >= 1024 ? 4 : 1);
+  }
   p.flags = a.mode == 2 ? a.local_pad + kFlagSlotsBase + 2 : a.flags;
   p.flag_target = 1u;
   p.header = a.mode == 2 ? a.local_pad + kFlagSlotsBase : nullptr;

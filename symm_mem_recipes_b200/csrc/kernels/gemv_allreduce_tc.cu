@@ -1,0 +1,333 @@
+// Fused GEMV + all-reduce on the tensor cores (tcgen05), for decode batches
+// 1..16.  Same contract as gemv_allreduce.cu:
+//     out[b, n] = sum over ranks r of  x_r[b, :] . W_r[:, n]
+//
+// The product is computed transposed ("swap A/B") so that the skinny batch
+// becomes the MMA's N dimension (16) and 128 output columns fill its M:
+//     D[128 n, 16 b] (TMEM, fp32) += W^T[128 n, 16 k] * x^T[16 k, 16 b]
+// W is stored [K, N] with N contiguous, i.e. the A operand is "MN-major": TMA
+// loads [64 k x 64 n] boxes with the 128-byte swizzle and the shared-memory
+// descriptor says MN-major (8-row k groups 1024 B apart, 64-column n groups
+// 8192 B apart).  x is the K-major B operand, one [16 x 64] box per k step.
+// One thread streams the weights through an 8-stage TMA ring (144 KB in
+// flight per SM) — the op is bound by HBM, the MMA work is negligible.
+//
+// Grid = (N / 128 column tiles) x (K splits), chosen to fill the SMs.  Every
+// CTA pushes its fp32 partial [b, 128] into the inbox slot (rank, split) of
+// every rank, raises that slot's flag for its tile (st.release.sys), waits
+// (bounded) for all WS x splits flags of the tile and reduces its share of the
+// tile's columns in slot order, so every rank produces the same bits.
+// Epoch / parity handling as in gemv_allreduce.cu: nothing is reset between
+// calls and the kernel can be replayed from a CUDA graph.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "../device/barrier.cuh"
+#include "../device/mbarrier.cuh"
+#include "../device/tcgen05.cuh"
+#include "../device/tma.cuh"
+#include "../device/vec.cuh"
+#include "../symm/driver_api.h"
+#include "launch.h"
+
+namespace smr {
+
+namespace {
+
+constexpr int kTileN = 128;      // output columns per CTA = MMA M
+constexpr int kBatchN = 16;      // MMA N: the batch, zero-padded by TMA
+constexpr int kBK = 64;
+constexpr int kUmmaK = 16;
+constexpr int kStages = 8;
+constexpr int kThreads = 192;
+constexpr uint32_t kWBytes = 2 * 64 * kBK * 2;        // two [64 k x 64 n] boxes
+constexpr uint32_t kXBytes = kBatchN * kBK * 2;
+constexpr uint32_t kStageBytes = kWBytes + kXBytes;   // 18432 = 18 * 1024
+constexpr uint32_t kRingBytes = kStageBytes * kStages;
+constexpr uint32_t kBarOffset = kRingBytes;
+constexpr uint32_t kNumBars = 2 * kStages + 1;
+constexpr uint32_t kMiscOffset = kBarOffset + 8 * kNumBars;
+constexpr uint32_t kSmemTotal = kMiscOffset + 16 + 1024;
+constexpr int kFlagStride = 32;   // flag slots per tile (>= WS * splits)
+constexpr uint32_t kTmemCols = 32;
+
+struct GemvTcParams {
+  __nv_bfloat16* out;     // [batch, N]
+  int batch, K, N;
+  int rank, world_size;
+  int ksplit;
+  void* const* buffers;   // workspace payload base of every rank
+  size_t flags_offset;    // [2 parity][tiles][kFlagStride] u32
+  size_t inbox_offset;    // [2 parity][WS * ksplit][16][N] fp32
+  int tiles;
+  uint64_t timeout_ns;
+  Status* status;
+};
+
+// MN-major, 128-byte swizzle: 8-row k groups 1024 B apart (SBO), 64-element
+// n groups 8192 B apart (LBO).
+__device__ __forceinline__ uint64_t umma_smem_desc_mn_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)(8192u >> 4) << 16;
+  d |= (uint64_t)(1024u >> 4) << 32;
+  d |= (uint64_t)1u << 46;
+  d |= (uint64_t)2u << 61;
+  return d;
+}
+
+__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+
+__device__ __forceinline__ void group_sync_128() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemv_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+               const GemvTcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kBarOffset);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + kStages;
+  uint64_t* tmem_full = bars + 2 * kStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kMiscOffset);
+  __shared__ int flags_ok;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = (int)blockIdx.x / p.ksplit, kh = (int)blockIdx.x % p.ksplit;
+  const int n0 = tile * kTileN;
+  const int rank = p.rank, ws = p.world_size;
+  const int slots = ws * p.ksplit;                       // partials per output element
+  const int my_slot = rank * p.ksplit + kh;
+
+  char* my_ws = static_cast<char*>(p.buffers[rank]);
+  uint32_t* header = reinterpret_cast<uint32_t*>(my_ws);   // [0] epoch, [1] CTAs done
+  const uint32_t epoch = ld_relaxed_gpu(&header[0]) + 1u;
+  const uint32_t parity = epoch & 1u;
+
+  const int kb_total = (p.K + kBK - 1) / kBK;
+  const int kb_per = (kb_total + p.ksplit - 1) / p.ksplit;
+  const int kb0 = kh * kb_per;
+  const int kb1 = kb0 + kb_per < kb_total ? kb0 + kb_per : kb_total;
+  const int n_kb = kb1 > kb0 ? kb1 - kb0 : 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(tmem_full, 1);
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_w);
+    tma_prefetch_desc(&tmap_x);
+    flags_ok = 1;
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish_alloc_permit();
+  }
+  tcgen05_fence_before_thread_sync();
+  __syncthreads();
+  tcgen05_fence_after_thread_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  bool failed = false;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      for (int i = 0; i < n_kb; ++i) {
+        const int kb = kb0 + i;
+        if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.timeout_ns)) {
+          report_status(p.status, kTimeoutMbarrier, rank, blockIdx.x, stage, kWhereGemmEmpty);
+          failed = true;
+          break;
+        }
+        uint8_t* sw = smem + (size_t)stage * kStageBytes;
+        mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
+        tma_load_2d(sw, &tmap_w, &full_bar[stage], n0, kb * kBK);               // n 0..63
+        tma_load_2d(sw + 8192, &tmap_w, &full_bar[stage], n0 + 64, kb * kBK);   // n 64..127
+        tma_load_2d(sw + kWBytes, &tmap_x, &full_bar[stage], kb * kBK, 0);
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // kind::f16, bf16 x bf16 -> fp32, A MN-major (bit 15), B K-major, M = 128, N = 16
+      constexpr uint32_t idesc = umma_idesc_bf16_f32(kTileN, kBatchN) | (1u << 15);
+      uint32_t stage = 0, phase = 0;
+      for (int i = 0; i < n_kb; ++i) {
+        if (!mbar_wait(&full_bar[stage], phase, p.timeout_ns)) {
+          report_status(p.status, kTimeoutMbarrier, rank, blockIdx.x, stage, kWhereGemmFull);
+          failed = true;
+          break;
+        }
+        tcgen05_fence_after_thread_sync();
+        const uint32_t sw = smem_u32(smem + (size_t)stage * kStageBytes);
+        const uint64_t da = umma_smem_desc_mn_sw128(sw);
+        const uint64_t db = umma_smem_desc_sw128(sw + kWBytes);
+#pragma unroll
+        for (int k = 0; k < kBK / kUmmaK; ++k) {
+          // A: +16 k rows = +2048 B; B: +16 k elements inside the 128-byte row = +32 B
+          umma_bf16_ss(tmem_base, da + (uint64_t)(k * (2048 >> 4)), db + (uint64_t)(2 * k), idesc,
+                       (i | k) != 0 ? 1u : 0u);
+        }
+        umma_commit(&empty_bar[stage]);
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
+      }
+      if (!failed) umma_commit(tmem_full);
+    }
+  } else {
+    // ---------------- epilogue + all-reduce (warps 2..5, 128 threads) ----------------
+    const int quarter = warp & 3;
+    const int etid = (int)threadIdx.x - 64;
+    const int col = quarter * 32 + lane;                 // column of the tile owned by this thread
+    uint32_t acc[16];
+    if (n_kb > 0) {
+      if (!mbar_wait(tmem_full, 0, p.timeout_ns)) {
+        if (lane == 0) report_status(p.status, kTimeoutMbarrier, rank, blockIdx.x, 0, kWhereGemmTmemFull);
+        failed = true;
+      } else {
+        tcgen05_fence_after_thread_sync();
+        tmem_ld_32x32b_x16(tmem_base + ((uint32_t)(quarter * 32) << 16), acc);
+        tmem_ld_wait();
+      }
+    } else {
+#pragma unroll
+      for (int b = 0; b < 16; ++b) acc[b] = 0u;
+    }
+    const size_t slot_stride = (size_t)kBatchN * p.N;                   // floats per slot
+    const size_t parity_off = (size_t)parity * slots * slot_stride;
+    if (!failed && n0 + col < p.N) {
+      const size_t off = parity_off + (size_t)my_slot * slot_stride + n0 + col;
+      for (int j = 1; j <= ws; ++j) {                                   // own inbox last
+        int peer = rank + j;
+        if (peer >= ws) peer -= ws;
+        float* inbox = reinterpret_cast<float*>(static_cast<char*>(p.buffers[peer]) + p.inbox_offset) + off;
+#pragma unroll
+        for (int b = 0; b < 16; ++b)
+          if (b < p.batch) inbox[(size_t)b * p.N] = __uint_as_float(acc[b]);
+      }
+    }
+    group_sync_128();   // the group's pushes precede the releases below
+    const size_t flag_idx = ((size_t)parity * p.tiles + tile) * kFlagStride;
+    if (etid < ws && !failed) {
+      uint32_t* peer_flags = reinterpret_cast<uint32_t*>(static_cast<char*>(p.buffers[etid]) + p.flags_offset);
+      st_release_sys(peer_flags + flag_idx + my_slot, epoch);
+    }
+    if (etid < slots) {
+      const uint32_t* mine = reinterpret_cast<const uint32_t*>(my_ws + p.flags_offset) + flag_idx + etid;
+      Deadline d(p.timeout_ns);
+      while (ld_acquire_sys(mine) != epoch) {
+        if (!d.alive()) {
+          report_status(p.status, kTimeoutFlag, rank, tile, etid, kWhereGemvArrive, epoch);
+          flags_ok = 0;
+          break;
+        }
+      }
+    }
+    group_sync_128();
+    if (flags_ok && !failed) {
+      // this CTA reduces its share of the tile's columns: 128 / ksplit of them
+      const int share = kTileN / p.ksplit;
+      const int c0 = n0 + kh * share;
+      const float* inbox = reinterpret_cast<const float*>(my_ws + p.inbox_offset) + parity_off;
+      for (int item = etid; item < p.batch * share; item += 128) {
+        const int b = item / share, c = c0 + item % share;
+        if (c >= p.N) continue;
+        float s = 0.f;
+        for (int sl = 0; sl < slots; ++sl)
+          s += __ldcv(inbox + (size_t)sl * slot_stride + (size_t)b * p.N + c);
+        p.out[(size_t)b * p.N + c] = __float2bfloat16(s);
+      }
+    }
+  }
+
+  if (__any_sync(0xffffffffu, failed)) {
+    for (int i = 0; i < 100; ++i) __nanosleep(1000);
+  }
+  tcgen05_fence_before_thread_sync();
+  __syncthreads();
+  tcgen05_fence_after_thread_sync();
+  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+  if (threadIdx.x == 0) {
+    __threadfence();
+    uint32_t done = atomicAdd(&header[1], 1u);
+    if (done == gridDim.x - 1) {
+      header[1] = 0u;
+      __threadfence();
+      st_release_gpu(&header[0], epoch);
+    }
+  }
+}
+
+int encode(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint32_t box_inner,
+           uint32_t box_outer) {
+  const DriverApi& d = DriverApi::get();
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {inner * 2};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = d.cuTensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base),
+                                        dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 1;
+}
+
+int pick_ksplit(int N, int K, int num_sms) {
+  int tiles = (N + kTileN - 1) / kTileN;
+  int ks = num_sms / tiles;
+  if (ks < 1) ks = 1;
+  if (ks > 4) ks = 4;
+  while (ks > 1 && (kTileN % ks != 0 || (K + kBK - 1) / kBK < ks)) --ks;
+  return ks;
+}
+
+}  // namespace
+
+size_t gemv_tc_workspace_bytes(int N, int K, int world_size, int num_sms, size_t* flags_offset,
+                               size_t* inbox_offset, int* tiles, int* ksplit) {
+  int t = (N + kTileN - 1) / kTileN;
+  int ks = pick_ksplit(N, K, num_sms);
+  size_t flags_off = 256;
+  size_t flags_bytes = (size_t)2 * t * kFlagStride * 4;
+  size_t inbox_off = (flags_off + flags_bytes + 255) & ~(size_t)255;
+  size_t inbox_bytes = (size_t)2 * world_size * ks * kBatchN * N * 4;
+  if (flags_offset) *flags_offset = flags_off;
+  if (inbox_offset) *inbox_offset = inbox_off;
+  if (tiles) *tiles = t;
+  if (ksplit) *ksplit = ks;
+  return inbox_off + inbox_bytes;
+}
+
+int launch_gemv_all_reduce_tc(const GemvArgs& a, int num_sms, cudaStream_t stream) {
+  if (a.batch < 1 || a.batch > kBatchN || a.N % 8 != 0 || a.K % 8 != 0 || a.ws_offset != 0)
+    return cudaErrorInvalidValue;
+  GemvTcParams p{};
+  p.out = static_cast<__nv_bfloat16*>(a.out);
+  p.batch = a.batch; p.K = a.K; p.N = a.N;
+  p.rank = a.pv.rank; p.world_size = a.pv.world_size;
+  p.buffers = a.pv.buffers;
+  p.timeout_ns = a.timeout_ns;
+  p.status = a.status;
+  gemv_tc_workspace_bytes(a.N, a.K, a.pv.world_size, num_sms, &p.flags_offset, &p.inbox_offset, &p.tiles,
+                          &p.ksplit);
+  if (p.world_size * p.ksplit > kFlagStride) return cudaErrorInvalidValue;
+  CUtensorMap tw, tx;
+  if (encode(&tw, a.w, (uint64_t)a.N, (uint64_t)a.K, 64, kBK)) return cudaErrorInvalidValue;
+  if (encode(&tx, a.x, (uint64_t)a.K, (uint64_t)a.batch, kBK, kBatchN)) return cudaErrorInvalidValue;
+  cudaError_t e = cudaFuncSetAttribute(gemv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)kSmemTotal);
+  if (e != cudaSuccess) return (int)e;
+  gemv_tc_kernel<<<p.tiles * p.ksplit, kThreads, kSmemTotal, stream>>>(tw, tx, p);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace smr

@@ -72,6 +72,8 @@ struct AgMatmulArgs {
   Status* status;
 };
 int launch_ag_matmul(const AgMatmulArgs& args, cudaStream_t stream);
+// Same contract on CTA pairs (tcgen05 cta_group::2, 256 x BN tiles); modes 0 and 2 only.
+int launch_ag_matmul_2cta(const AgMatmulArgs& args, cudaStream_t stream);
 
 // ---- fused GEMV + all-reduce (decode) -------------------------------------
 struct GemvArgs {
@@ -89,5 +91,25 @@ size_t gemv_workspace_bytes(int batch_tile, int N, int world_size, size_t* flags
                             size_t* inbox_offset, int* max_tiles);
 int gemv_batch_tile(int batch);   // smallest supported tile >= batch, -1 if none
 int launch_gemv_all_reduce(const GemvArgs& args, cudaStream_t stream);
+// Tensor-core (tcgen05, swap A/B) variant; its workspace layout differs.
+size_t gemv_tc_workspace_bytes(int N, int K, int world_size, int num_sms, size_t* flags_offset,
+                               size_t* inbox_offset, int* tiles, int* ksplit);
+int launch_gemv_all_reduce_tc(const GemvArgs& args, int num_sms, cudaStream_t stream);
+
+// ---- fused GEMM + reduce-scatter (prefill, row-parallel linear) --------------
+struct MatmulRsArgs {
+  const void* a;      // [M, K] bf16: all tokens, this rank's slice of the reduction dim
+  const void* b;      // [N, K] bf16
+  void* out;          // [M / WS, N] bf16: this rank's rows of the sum
+  int M, N, K;
+  PeerView pv;        // of the symmetric workspace (inbox)
+  size_t inbox_offset;
+  uint32_t* local_pad;
+  int num_sms;
+  uint64_t timeout_ns;
+  Status* status;
+};
+size_t matmul_rs_workspace_bytes(int M, int N);
+int launch_matmul_reduce_scatter(const MatmulRsArgs& args, cudaStream_t stream);
 
 }  // namespace smr

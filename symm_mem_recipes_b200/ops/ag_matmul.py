@@ -35,8 +35,10 @@ class AgMatmulConfig:
     GROUP_SIZE_M, num_stages, num_warps; triton_all_gather_matmul.py:380-388).
     The M tile is 128 and the K tile 64; the stage count follows from BLOCK_N."""
     block_n: int = _env_int("SMR_AGMM_BLOCK_N", 0)        # 0 = pick per shape
-    n_copy: int = _env_int("SMR_AGMM_COPY_CTAS", 4)       # CTAs that run the all-gather
+    n_copy: int = _env_int("SMR_AGMM_COPY_CTAS", 16)      # pull mode only: CTAs set aside for the gather
     num_sms: int = _env_int("SMR_AGMM_NUM_SMS", 0)        # 0 = all SMs of the device
+    # tcgen05 cta_group::2: two SMs share a 256 x BLOCK_N tile (not used by the pull mode)
+    cta_pair: bool = bool(_env_int("SMR_AGMM_CTA_PAIR", 0))
     timeout_ms: int = _env_int("SMR_TIMEOUT_MS", 10000)
 
 
@@ -52,14 +54,16 @@ def _num_sms(device: torch.device) -> int:
     return _sm_count[idx]
 
 
-def choose_block_n(M: int, N: int, gemm_ctas: int) -> int:
+def choose_block_n(M: int, N: int, gemm_ctas: int, cta_pair: bool = False) -> int:
     """Smallest modelled time: waves of the static tile schedule times the tile
-    width; ties go to the wider tile (fewer A re-reads)."""
+    width; ties go to the wider tile (fewer A re-reads).  With `cta_pair` a
+    tile is 256 rows and runs on two CTAs."""
     best, best_cost = _BLOCK_NS[0], None
-    m_blocks = -(-M // 128)
+    m_blocks = -(-M // (256 if cta_pair else 128))
+    units = gemm_ctas // 2 if cta_pair else gemm_ctas
     for bn in _BLOCK_NS:
         tiles = m_blocks * (-(-N // bn))
-        waves = -(-tiles // max(gemm_ctas, 1))
+        waves = -(-tiles // max(units, 1))
         cost = waves * bn
         if best_cost is None or cost < best_cost:
             best, best_cost = bn, cost
@@ -83,8 +87,9 @@ def matmul(a: torch.Tensor, b: torch.Tensor, c_out: Optional[torch.Tensor] = Non
     if c_out is None:
         c_out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
     sms = config.num_sms or _num_sms(a.device)
-    bn = config.block_n or choose_block_n(M, N, sms)
-    C.ag_matmul(a, b, c_out, 0, None, 0, None, 0, None, None, bn, sms, 0, config.timeout_ms * 1_000_000)
+    bn = config.block_n or choose_block_n(M, N, sms, config.cta_pair)
+    C.ag_matmul(a, b, c_out, 0, None, 0, None, 0, None, None, bn, sms, 0, config.timeout_ms * 1_000_000,
+                config.cta_pair)
     return c_out
 
 
@@ -145,17 +150,20 @@ def all_gather_matmul(a_shard: torch.Tensor, b: torch.Tensor, a_out: Optional[to
     if tuple(a_out.shape) != (M, K) or tuple(c_out.shape) != (M, N):
         raise SymmMemError("a_out must be [M, K] and c_out [M, N] with M = rows * world_size")
     sms = config.num_sms or _num_sms(a_shard.device)
-    n_copy = max(1, min(config.n_copy, sms // 4))
-    bn = config.block_n or choose_block_n(M, N, sms - n_copy)
     t_ns = config.timeout_ms * 1_000_000
     if symm_mem.is_symm_mem_tensor(a_out):
+        # push: every CTA is a GEMM CTA, the epilogue warps broadcast the shard
+        bn = config.block_n or choose_block_n(M, N, sms, config.cta_pair)
+        n_copy = 0
         _, aout_offset = symm_mem._find_record(a_out)
         hdl = symm_mem.rendezvous(a_out, group)
         if aout_offset % 16:
             raise SymmMemError("a_out must start on a 16-byte boundary of its allocation")
         C.ag_matmul(a_shard, b, c_out, 2, None, 0, hdl.native, aout_offset, a_out, None,
-                    bn, sms, n_copy, t_ns)
+                    bn, sms, n_copy, t_ns, config.cta_pair)
         return c_out
+    n_copy = max(1, min(config.n_copy, sms // 4))
+    bn = config.block_n or choose_block_n(M, N, sms - n_copy)
     _, offset = symm_mem._find_record(a_shard)
     hdl = symm_mem.rendezvous(a_shard, group)
     if offset % 16:

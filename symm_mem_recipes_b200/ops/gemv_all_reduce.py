@@ -19,20 +19,25 @@ import torch.distributed as dist
 from .._ext import C
 from ..errors import SymmMemError
 from ..parallel import symm_mem
+from .ag_matmul import _num_sms
 
 _workspaces: dict[tuple, torch.Tensor] = {}
 _TIMEOUT_MS = int(os.environ.get("SMR_TIMEOUT_MS", "10000"))
 
 
-def _workspace(batch_tile: int, N: int, device: torch.device, group) -> torch.Tensor:
-    """Symmetric scratch (inboxes, flags, epoch) for one (batch tile, N):
-    allocated and rendezvoused at the first call, which is therefore
+def _workspace(batch_tile: int, N: int, K: int, device: torch.device, group, tensor_core: bool,
+               sms: int) -> torch.Tensor:
+    """Symmetric scratch (inboxes, flags, epoch) for one (kernel, batch tile,
+    N, K): allocated and rendezvoused at the first call, which is therefore
     collective; all ranks must make the same sequence of first calls."""
     ws = dist.get_world_size(group) if dist.is_initialized() else 1
-    key = (batch_tile, N, device.index, symm_mem._group_key(group))
+    key = (tensor_core, batch_tile, N, K, device.index, symm_mem._group_key(group))
     t = _workspaces.get(key)
     if t is None:
-        nbytes = C.gemv_workspace_bytes(batch_tile, N, ws)
+        if tensor_core:
+            nbytes = C.gemv_tc_workspace_bytes(N, K, ws, sms)
+        else:
+            nbytes = C.gemv_workspace_bytes(batch_tile, N, ws)
         t = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
         symm_mem.rendezvous(t, group)
         _workspaces[key] = t
@@ -40,9 +45,12 @@ def _workspace(batch_tile: int, N: int, device: torch.device, group) -> torch.Te
 
 
 def gemv_all_reduce(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
-                    group=None, timeout_ms: int = _TIMEOUT_MS) -> torch.Tensor:
+                    group=None, timeout_ms: int = _TIMEOUT_MS, algo: Optional[str] = None) -> torch.Tensor:
     """`x` [B, K] and `w` [K, N] are this rank's (ordinary) tensors; returns the
-    all-reduced [B, N] in bf16, bitwise identical on every rank."""
+    all-reduced [B, N] in bf16, bitwise identical on every rank.
+
+    `algo`: "tc" = tcgen05 kernel (weights streamed by TMA, swap-A/B MMA);
+    "simt" = CUDA-core kernel.  Default from SMR_GEMV_ALGO, else "tc"."""
     if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[0]:
         raise SymmMemError("need x[B, K] and w[K, N]")
     B, N = x.shape[0], w.shape[1]
@@ -52,10 +60,15 @@ def gemv_all_reduce(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor
         raise SymmMemError("N must be a multiple of 8")
     if out is None:
         out = torch.empty(B, N, dtype=torch.bfloat16, device=x.device)
-    bt = C.gemv_batch_tile(B)
-    wsp = _workspace(bt, N, x.device, group)
+    algo = algo or os.environ.get("SMR_GEMV_ALGO", "tc")
+    if algo not in ("tc", "simt"):
+        raise SymmMemError('algo must be "tc" or "simt"')
+    tensor_core = algo == "tc" and x.shape[1] % 8 == 0
+    sms = _num_sms(x.device)
+    bt = 16 if tensor_core else C.gemv_batch_tile(B)
+    wsp = _workspace(bt, N, x.shape[1], x.device, group, tensor_core, sms)
     hdl = symm_mem.rendezvous(wsp, group)
-    C.gemv_all_reduce(x.contiguous(), w, out, hdl.native, 0, int(timeout_ms) * 1_000_000)
+    C.gemv_all_reduce(x.contiguous(), w, out, hdl.native, 0, int(timeout_ms) * 1_000_000, tensor_core, sms)
     return out
 
 

@@ -15,9 +15,19 @@ import torch.multiprocessing as mp
 
 
 def free_port() -> int:
-    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
-        s.bind(("127.0.0.1", 0))
-        return s.getsockname()[1]
+    """A port that is free now, drawn at random from a range the kernel does
+    not hand out as ephemeral ports (so nothing grabs it before rank 0 binds)."""
+    import random
+
+    for _ in range(64):
+        port = random.randint(20000, 29999)
+        with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
+            try:
+                s.bind(("127.0.0.1", port))
+                return port
+            except OSError:
+                continue
+    raise RuntimeError("no free port found")
 
 
 def _entry(rank: int, world_size: int, backend: str, port: int, fn, args, errq):
@@ -61,10 +71,16 @@ def spawn_ranks(fn, world_size: int, backend: str = "gloo", args=(), timeout_s: 
     port = free_port()
     procs = [ctx.Process(target=_entry, args=(r, world_size, backend, port, fn, args, errq))
              for r in range(world_size)]
+    import time
+
     for p in procs:
         p.start()
-    for p in procs:
-        p.join(timeout_s)
+    deadline = time.monotonic() + timeout_s
+    while time.monotonic() < deadline and any(p.is_alive() for p in procs):
+        if any(p.exitcode not in (0, None) for p in procs):
+            # a rank died: give the others a moment to notice, then stop waiting
+            deadline = min(deadline, time.monotonic() + 30.0)
+        time.sleep(0.05)
     hung = [p for p in procs if p.is_alive()]
     for p in hung:
         p.terminate()

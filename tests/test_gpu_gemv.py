@@ -12,7 +12,7 @@ def _inputs(rank, B, K, N):
     return x, w
 
 
-def _gemv_worker(rank, world_size, B, K, N):
+def _gemv_worker(rank, world_size, B, K, N, algo="tc"):
     import symm_mem_recipes_b200 as smr
     from symm_mem_recipes_b200.parallel import symm_mem
 
@@ -26,7 +26,7 @@ def _gemv_worker(rank, world_size, B, K, N):
     x, w = x.to(dev), w.to(dev)
     out = None
     for it in range(4):          # repeated calls exercise the epoch / parity logic
-        out = smr.gemv_all_reduce(x, w)
+        out = smr.gemv_all_reduce(x, w, algo=algo)
         symm_mem.check_status(dev)
         err = (out.double().cpu() - ref).abs()
         tol = ref.abs() * 2.0 ** -7 + 2e-2
@@ -45,17 +45,19 @@ def _gemv_worker(rank, world_size, B, K, N):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("algo", ["tc", "simt"])
 @pytest.mark.parametrize("B,K,N", [(1, 512, 256), (4, 3584, 8192), (16, 3584, 8192), (3, 1000, 328), (8, 256, 64)])
-def test_gemv_world_of_one(B, K, N):
+def test_gemv_world_of_one(B, K, N, algo):
     torch.cuda.set_device(0)
-    _gemv_worker(0, 1, B, K, N)
+    _gemv_worker(0, 1, B, K, N, algo)
 
 
 @pytest.mark.gpu
 @pytest.mark.multigpu(2)
+@pytest.mark.parametrize("algo", ["tc", "simt"])
 @pytest.mark.parametrize("B", [1, 4, 16])
-def test_gemv_all_reduce_2gpu(B):
-    spawn_ranks(_gemv_worker, 2, "nccl", (B, 3584, 8192))
+def test_gemv_all_reduce_2gpu(B, algo):
+    spawn_ranks(_gemv_worker, 2, "nccl", (B, 3584, 8192, algo))
 
 
 @pytest.mark.gpu

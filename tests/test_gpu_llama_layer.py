@@ -1,0 +1,81 @@
+"""The TP decoder layer: fused forward vs the NCCL + cuBLAS forward vs fp32."""
+import pytest
+import torch
+
+from symm_mem_recipes_b200.utils.testing import spawn_ranks
+
+
+def _layer_worker(rank, world_size):
+    from symm_mem_recipes_b200.models.llama_tp_layer import (LlamaTPConfig, LlamaTPDecoderLayer,
+                                                              full_precision_reference)
+    from symm_mem_recipes_b200.parallel import symm_mem
+
+    dev = torch.device("cuda", rank)
+    cfg = LlamaTPConfig.tiny(world_size)
+    layer = LlamaTPDecoderLayer(cfg, dev, seed=11)
+    batch, seq = 2, 128 * world_size
+    rows = batch * seq // world_size
+    g = torch.Generator().manual_seed(5)
+    x_full = (torch.randn(batch * seq, cfg.hidden, generator=g) * 0.5).to(torch.bfloat16)
+    x_shard = x_full[rank * rows:(rank + 1) * rows].to(dev)
+    failures = []
+    y = layer.forward(x_shard, batch, seq, barrier_between_phases=True)
+    symm_mem.check_status(dev)
+    y_lib = layer.forward_reference(x_shard, batch, seq)
+    if not torch.allclose(y.float(), y_lib.float(), rtol=5e-2, atol=5e-2):
+        failures.append(f"fused vs NCCL+cuBLAS: {(y.float() - y_lib.float()).abs().max().item()}")
+    # fp32 reference from every rank's weights (regenerated from their seeds on the CPU)
+    weights = []
+    for r in range(world_size):
+        gw = torch.Generator().manual_seed(11 + r)
+        H, D = cfg.hidden, cfg.head_dim
+
+        def w(*shape):
+            return (torch.randn(*shape, generator=gw) * 0.02).to(torch.bfloat16)
+
+        w_qkv = w((layer.hq + 2 * layer.hkv) * D, H)
+        w_o = w(H, layer.hq * D)
+        w_gu = w(2 * layer.ffn_local, H)
+        w_down = w(H, layer.ffn_local)
+        weights.append((w_qkv, w_o, w_gu, w_down, layer.norm1.cpu(), layer.norm2.cpu()))
+    if not torch.equal(weights[rank][0], layer.w_qkv.cpu()):
+        failures.append("weight regeneration does not match")
+    ref = full_precision_reference(weights, cfg, x_full, batch, seq)[rank * rows:(rank + 1) * rows]
+    err = (y.float().cpu() - ref).abs().max().item()
+    if err > 0.1:
+        failures.append(f"fused vs fp32 reference: {err}")
+
+    # decode: fused GEMV + all-reduce vs cuBLAS + NCCL
+    B, smax = 4, 16
+    xd = (torch.randn(B, cfg.hidden, generator=torch.Generator().manual_seed(9)) * 0.5).to(torch.bfloat16).to(dev)
+    kc = torch.zeros(B, smax, layer.hkv, cfg.head_dim, dtype=torch.bfloat16, device=dev)
+    vc = torch.zeros_like(kc)
+    kc2, vc2 = kc.clone(), vc.clone()
+    for pos in range(3):
+        yd = layer.decode(xd, kc, vc, pos, fused=True)
+        yr = layer.decode(xd, kc2, vc2, pos, fused=False)
+        symm_mem.check_status(dev)
+        if not torch.allclose(yd.float(), yr.float(), rtol=5e-2, atol=5e-2):
+            failures.append(f"decode pos {pos}: {(yd.float() - yr.float()).abs().max().item()}")
+    torch.cuda.synchronize()
+    assert not failures, failures
+
+
+@pytest.mark.gpu
+def test_layer_world_of_one():
+    from symm_mem_recipes_b200.models.llama_tp_layer import smoke
+
+    torch.cuda.set_device(0)
+    smoke(torch.device("cuda", 0))
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu(2)
+def test_layer_2gpu():
+    spawn_ranks(_layer_worker, 2, "nccl")
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu(4)
+def test_layer_4gpu():
+    spawn_ranks(_layer_worker, 4, "nccl")

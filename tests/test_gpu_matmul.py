@@ -17,9 +17,10 @@ def _close(c, ref, K):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("cta_pair", [False, True])
 @pytest.mark.parametrize("block_n", [128, 192, 224, 256])
 @pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 256), (200, 328, 96), (640, 1000, 1024)])
-def test_matmul_small(block_n, shape):
+def test_matmul_small(block_n, shape, cta_pair):
     from symm_mem_recipes_b200.ops.ag_matmul import AgMatmulConfig, matmul
     from symm_mem_recipes_b200.parallel import symm_mem
 
@@ -28,28 +29,29 @@ def test_matmul_small(block_n, shape):
     a = (torch.randn(M, K, device="cuda") * 0.5).to(torch.bfloat16)
     b = (torch.randn(N, K, device="cuda") * 0.5).to(torch.bfloat16)
     c = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
-    matmul(a, b, c, AgMatmulConfig(block_n=block_n, timeout_ms=2000))
+    matmul(a, b, c, AgMatmulConfig(block_n=block_n, timeout_ms=2000, cta_pair=cta_pair))
     symm_mem.check_status("cuda")
     ok, err = _close(c, _ref(a, b), K)
     assert ok, f"max abs error {err}"
 
 
 @pytest.mark.gpu
-def test_matmul_llama70b_shape_vs_cublas():
-    from symm_mem_recipes_b200.ops.ag_matmul import matmul
+@pytest.mark.parametrize("cta_pair", [False, True])
+def test_matmul_llama70b_shape_vs_cublas(cta_pair):
+    from symm_mem_recipes_b200.ops.ag_matmul import AgMatmulConfig, matmul
     from symm_mem_recipes_b200.parallel import symm_mem
 
     M, N, K = 4096, 3584, 8192
     torch.manual_seed(0)
     a = (torch.randn(M, K, device="cuda") * 0.02).to(torch.bfloat16)
     b = (torch.randn(N, K, device="cuda") * 0.02).to(torch.bfloat16)
-    c = matmul(a, b)
+    c = matmul(a, b, config=AgMatmulConfig(cta_pair=cta_pair, timeout_ms=2000))
     symm_mem.check_status("cuda")
     ref = torch.matmul(a, b.t())
     assert torch.allclose(c.float(), ref.float(), rtol=2e-2, atol=2e-3)
 
 
-def _agmm_worker(rank, world_size, rows, N, K, n_copy, mode):
+def _agmm_worker(rank, world_size, rows, N, K, n_copy, mode, cta_pair=False):
     import symm_mem_recipes_b200 as smr
     from symm_mem_recipes_b200.ops.ag_matmul import AgMatmulConfig
     from symm_mem_recipes_b200.parallel import symm_mem
@@ -69,7 +71,7 @@ def _agmm_worker(rank, world_size, rows, N, K, n_copy, mode):
         from symm_mem_recipes_b200.ops.ag_matmul import gather_buffer
         a_out = None
     c_out = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
-    cfg = AgMatmulConfig(n_copy=n_copy, timeout_ms=5000)
+    cfg = AgMatmulConfig(n_copy=n_copy, timeout_ms=5000, cta_pair=cta_pair)
     failures = []
     for it in range(3):
         smr.all_gather_matmul(a_shard, b, a_out, c_out, cfg)
@@ -105,6 +107,13 @@ def _agmm_worker(rank, world_size, rows, N, K, n_copy, mode):
 @pytest.mark.parametrize("rows,N,K,n_copy", [(128, 256, 256, 1), (256, 512, 1024, 3), (2048, 3584, 8192, 4)])
 def test_all_gather_matmul_2gpu(rows, N, K, n_copy, mode):
     spawn_ranks(_agmm_worker, 2, "nccl", (rows, N, K, n_copy, mode))
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu(2)
+@pytest.mark.parametrize("rows,N,K", [(128, 256, 256), (384, 512, 1024), (2048, 3584, 8192)])
+def test_all_gather_matmul_cta_pair_2gpu(rows, N, K):
+    spawn_ranks(_agmm_worker, 2, "nccl", (rows, N, K, 0, "push", True))
 
 
 @pytest.mark.gpu
