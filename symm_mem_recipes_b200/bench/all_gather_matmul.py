@@ -20,7 +20,7 @@ import torch
 import torch.distributed as dist
 
 
-def main() -> int:
+def main(argv=None, standalone: bool = True) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--M", type=int, default=4096)
     ap.add_argument("--N", type=int, default=6656)
@@ -30,16 +30,11 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--iters", type=int, default=25)
     ap.add_argument("--out", default=None)
-    args = ap.parse_args()
+    args = ap.parse_args(argv)
 
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-    os.environ.setdefault("MASTER_PORT", "29512")
-    dist.init_process_group("nccl", device_id=dev, rank=rank, world_size=world)
+    from symm_mem_recipes_b200.bench._common import finish, init_distributed
+
+    rank, local_rank, world, dev = init_distributed()
 
     import symm_mem_recipes_b200 as smr
     from symm_mem_recipes_b200.ops.ag_matmul import AgMatmulConfig
@@ -94,8 +89,8 @@ def main() -> int:
     if args.out and rank == 0:
         with open(args.out, "a") as f:
             f.write("\n".join(lines) + "\n")
-    symm_mem.shutdown()
-    dist.destroy_process_group()
+    if standalone:
+        finish()
     return 0
 
 

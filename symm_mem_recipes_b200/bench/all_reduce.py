@@ -21,7 +21,7 @@ import torch
 import torch.distributed as dist
 
 
-def main() -> int:
+def main(argv=None, standalone: bool = True) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--min-bytes", type=int, default=4096)
     ap.add_argument("--max-bytes", type=int, default=256 * 1024 * 1024)
@@ -35,16 +35,11 @@ def main() -> int:
                     help="graph: CUDA-graph replay (device time per call) up to --graph-limit bytes")
     ap.add_argument("--graph-limit", type=int, default=4 * 1024 * 1024)
     ap.add_argument("--out", default=None, help="also append the JSON lines to this file")
-    args = ap.parse_args()
+    args = ap.parse_args(argv)
 
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-    os.environ.setdefault("MASTER_PORT", "29511")
-    dist.init_process_group("nccl", device_id=dev, rank=rank, world_size=world)
+    from symm_mem_recipes_b200.bench._common import finish, init_distributed
+
+    rank, local_rank, world, dev = init_distributed()
 
     import symm_mem_recipes_b200 as smr
     from symm_mem_recipes_b200.ops.config import AllReduceConfig
@@ -119,8 +114,8 @@ def main() -> int:
     if args.out and rank == 0:
         with open(args.out, "a") as f:
             f.write("\n".join(lines) + "\n")
-    symm_mem.shutdown()
-    dist.destroy_process_group()
+    if standalone:
+        finish()
     return 0
 
 

@@ -16,18 +16,13 @@ import torch
 import torch.distributed as dist
 
 
-def main() -> int:
+def main(argv=None, standalone: bool = True) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--blocks", default="1,32,148")
-    args = ap.parse_args()
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-    os.environ.setdefault("MASTER_PORT", "29513")
-    dist.init_process_group("nccl", device_id=dev, rank=rank, world_size=world)
+    args = ap.parse_args(argv)
+    from symm_mem_recipes_b200.bench._common import finish, init_distributed
+
+    rank, local_rank, world, dev = init_distributed()
 
     import symm_mem_recipes_b200 as smr
     from symm_mem_recipes_b200.parallel import symm_mem
@@ -48,8 +43,8 @@ def main() -> int:
     if rank == 0:
         print(json.dumps({"op": "channel_barrier", "world_size": world, "us": round(us, 2), "timing": "graph"}))
         print(json.dumps({"op": "barrier_test", "signal_pad_abs_sum": pad_sum, "ok": pad_sum == 0}))
-    symm_mem.shutdown()
-    dist.destroy_process_group()
+    if standalone:
+        finish()
     return 0
 
 

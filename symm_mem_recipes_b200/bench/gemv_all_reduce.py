@@ -20,21 +20,16 @@ import torch
 import torch.distributed as dist
 
 
-def main() -> int:
+def main(argv=None, standalone: bool = True) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--K", type=int, default=3584)
     ap.add_argument("--N", type=int, default=8192)
     ap.add_argument("--batches", default="1,4,16")
     ap.add_argument("--out", default=None)
-    args = ap.parse_args()
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-    os.environ.setdefault("MASTER_PORT", "29514")
-    dist.init_process_group("nccl", device_id=dev, rank=rank, world_size=world)
+    args = ap.parse_args(argv)
+    from symm_mem_recipes_b200.bench._common import finish, init_distributed
+
+    rank, local_rank, world, dev = init_distributed()
 
     import symm_mem_recipes_b200 as smr
     from symm_mem_recipes_b200.parallel import symm_mem
@@ -77,8 +72,8 @@ def main() -> int:
     if args.out and rank == 0:
         with open(args.out, "a") as f:
             f.write("\n".join(lines) + "\n")
-    symm_mem.shutdown()
-    dist.destroy_process_group()
+    if standalone:
+        finish()
     return 0
 
 

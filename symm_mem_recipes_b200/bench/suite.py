@@ -1,0 +1,52 @@
+"""Runs every multi-GPU benchmark of the package in ONE set of processes
+(start-up of a torchrun job costs more than most of the benchmarks).
+
+    torchrun --nnodes 1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        -m symm_mem_recipes_b200.bench.suite --out-dir gpurun_out --tag ws8
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--out-dir", default=".")
+    ap.add_argument("--tag", default="")
+    ap.add_argument("--only", default="barrier,all_reduce,all_gather_matmul,gemv,layer")
+    ap.add_argument("--with-reference-triton", action="store_true")
+    ap.add_argument("--ar-max-bytes", type=int, default=256 * 1024 * 1024)
+    args = ap.parse_args()
+    from symm_mem_recipes_b200.bench import (all_gather_matmul, all_reduce, barrier, gemv_all_reduce,
+                                             llama_layer)
+    from symm_mem_recipes_b200.bench._common import finish, init_distributed
+
+    rank, _, world, _ = init_distributed()
+    tag = args.tag or f"ws{world}"
+    only = set(args.only.split(","))
+
+    def out(name):
+        return os.path.join(args.out_dir, f"{name}_{tag}.jsonl")
+
+    if "barrier" in only:
+        barrier.main([], standalone=False)
+    if "all_reduce" in only:
+        argv = ["--max-bytes", str(args.ar_max_bytes), "--out", out("all_reduce")]
+        if args.with_reference_triton:
+            argv.append("--with-reference-triton")
+        all_reduce.main(argv, standalone=False)
+    if "all_gather_matmul" in only:
+        all_gather_matmul.main(["--M", "16384", "--N", "3584", "--K", "8192", "--out", out("agmm")],
+                               standalone=False)
+    if "gemv" in only:
+        gemv_all_reduce.main(["--out", out("gemv")], standalone=False)
+    if "layer" in only:
+        llama_layer.main(["--out", out("layer")], standalone=False)
+    finish()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

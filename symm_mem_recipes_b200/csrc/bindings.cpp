@@ -9,7 +9,9 @@
 
 #include <map>
 #include <memory>
+#include <atomic>
 #include <mutex>
+#include <thread>
 
 #include "kernels/launch.h"
 #include "oracle/cpu_reference.h"
@@ -248,6 +250,58 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("host_view", &host_view);
   m.def("host_pad_view", &host_pad_view);
   m.def("host_all_reduce", &host_all_reduce);
+
+  // Barrier protocol hammered by threads: `world_size` threads act as ranks over
+  // private pads, each running `iters` barriers on each of `blocks` block ids.
+  // `dead_rank` >= 0 never arrives.  Returns (codes per rank, sum of |pad|, max
+  // counter skew seen), so a test can check completion, the all-zero pad and
+  // that no rank ever ran ahead of a rank that had not arrived.
+  m.def("host_barrier_stress", [](int world_size, int blocks, int iters, uint64_t timeout_ns, int dead_rank) {
+    TORCH_CHECK(world_size >= 1 && world_size <= kMaxWorldSize && blocks >= 1 &&
+                (uint32_t)blocks * world_size <= kBlockSlots, "bad stress configuration");
+    std::vector<std::vector<uint32_t>> pads(world_size, std::vector<uint32_t>(kSignalPadSlots, 0u));
+    std::vector<uint32_t*> pad_ptrs(world_size);
+    for (int r = 0; r < world_size; ++r) pad_ptrs[r] = pads[r].data();
+    std::vector<uint32_t> codes(world_size, 0);
+    std::vector<std::atomic<int64_t>> progress(world_size);
+    for (auto& c : progress) c.store(0);
+    std::atomic<int64_t> max_skew{0};
+    {
+      py::gil_scoped_release nogil;
+      std::vector<std::thread> threads;
+      for (int r = 0; r < world_size; ++r) {
+        if (r == dead_rank) continue;
+        threads.emplace_back([&, r] {
+          for (int it = 0; it < iters && codes[r] == 0; ++it) {
+            for (int b = 0; b < blocks; ++b) {
+              progress[r].fetch_add(1);
+              int peer = -1;
+              uint32_t code = host_barrier_signal_wait(pad_ptrs.data(), (uint32_t)b * world_size, r, world_size,
+                                                       timeout_ns, &peer);
+              if (code != kOk) {
+                codes[r] = code;
+                break;
+              }
+              // after a barrier nobody can be more than one barrier behind me
+              int64_t mine = progress[r].load();
+              for (int q = 0; q < world_size; ++q) {
+                if (q == dead_rank) continue;
+                int64_t skew = mine - progress[q].load();
+                int64_t cur = max_skew.load();
+                while (skew > cur && !max_skew.compare_exchange_weak(cur, skew)) {
+                }
+              }
+            }
+          }
+        });
+      }
+      for (auto& t : threads) t.join();
+    }
+    uint64_t pad_sum = 0;
+    for (auto& pad : pads)
+      for (uint32_t v : pad) pad_sum += v;
+    return py::make_tuple(codes, pad_sum, max_skew.load());
+  });
 
   // ---- status ----
   m.def("read_status", &read_status);

@@ -204,15 +204,24 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     }
     const size_t slot_stride = (size_t)kBatchN * p.N;                   // floats per slot
     const size_t parity_off = (size_t)parity * slots * slot_stride;
-    if (!failed && n0 + col < p.N) {
-      const size_t off = parity_off + (size_t)my_slot * slot_stride + n0 + col;
-      for (int j = 1; j <= ws; ++j) {                                   // own inbox last
-        int peer = rank + j;
-        if (peer >= ws) peer -= ws;
-        float* inbox = reinterpret_cast<float*>(static_cast<char*>(p.buffers[peer]) + p.inbox_offset) + off;
+    // transpose through shared memory (the ring is idle once the last MMA has
+    // completed) so that the pushes are 16-byte stores of 4 consecutive columns
+    float* part = reinterpret_cast<float*>(smem);                       // [16][128]
 #pragma unroll
-        for (int b = 0; b < 16; ++b)
-          if (b < p.batch) inbox[(size_t)b * p.N] = __uint_as_float(acc[b]);
+    for (int b = 0; b < 16; ++b) part[b * kTileN + col] = __uint_as_float(acc[b]);
+    group_sync_128();
+    if (!failed) {
+      const size_t off = parity_off + (size_t)my_slot * slot_stride + n0;
+      for (int item = etid; item < p.batch * (kTileN / 4); item += 128) {
+        const int b = item / (kTileN / 4), c4 = (item % (kTileN / 4)) * 4;
+        if (n0 + c4 >= p.N) continue;                                   // N % 8 == 0
+        const Vec16 v = *reinterpret_cast<const Vec16*>(&part[b * kTileN + c4]);
+        for (int j = 1; j <= ws; ++j) {                                 // own inbox last
+          int peer = rank + j;
+          if (peer >= ws) peer -= ws;
+          float* inbox = reinterpret_cast<float*>(static_cast<char*>(p.buffers[peer]) + p.inbox_offset);
+          st_16(inbox + off + (size_t)b * p.N + c4, v);
+        }
       }
     }
     group_sync_128();   // the group's pushes precede the releases below
@@ -238,13 +247,27 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
       const int share = kTileN / p.ksplit;
       const int c0 = n0 + kh * share;
       const float* inbox = reinterpret_cast<const float*>(my_ws + p.inbox_offset) + parity_off;
-      for (int item = etid; item < p.batch * share; item += 128) {
-        const int b = item / share, c = c0 + item % share;
+      for (int item = etid; item < p.batch * (share / 4); item += 128) {
+        const int b = item / (share / 4), c = c0 + (item % (share / 4)) * 4;
         if (c >= p.N) continue;
-        float s = 0.f;
-        for (int sl = 0; sl < slots; ++sl)
-          s += __ldcv(inbox + (size_t)sl * slot_stride + (size_t)b * p.N + c);
-        p.out[(size_t)b * p.N + c] = __float2bfloat16(s);
+        const float* src = inbox + (size_t)b * p.N + c;
+        float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int sl0 = 0; sl0 < slots; sl0 += 8) {                      // 8 independent loads in flight
+          Vec16 v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            if (sl0 + u < slots) v[u] = ld_16_stream(src + (size_t)(sl0 + u) * slot_stride);
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            if (sl0 + u < slots) {
+              s4.x += __uint_as_float(v[u].x); s4.y += __uint_as_float(v[u].y);
+              s4.z += __uint_as_float(v[u].z); s4.w += __uint_as_float(v[u].w);
+            }
+        }
+        uint2 o;
+        o.x = pack_bf16x2(s4.x, s4.y);
+        o.y = pack_bf16x2(s4.z, s4.w);
+        *reinterpret_cast<uint2*>(p.out + (size_t)b * p.N + c) = o;
       }
     }
   }

@@ -38,7 +38,7 @@ class AgMatmulConfig:
     n_copy: int = _env_int("SMR_AGMM_COPY_CTAS", 16)      # pull mode only: CTAs set aside for the gather
     num_sms: int = _env_int("SMR_AGMM_NUM_SMS", 0)        # 0 = all SMs of the device
     # tcgen05 cta_group::2: two SMs share a 256 x BLOCK_N tile (not used by the pull mode)
-    cta_pair: bool = bool(_env_int("SMR_AGMM_CTA_PAIR", 0))
+    cta_pair: bool = bool(_env_int("SMR_AGMM_CTA_PAIR", 1))
     timeout_ms: int = _env_int("SMR_TIMEOUT_MS", 10000)
 
 
@@ -55,19 +55,14 @@ def _num_sms(device: torch.device) -> int:
 
 
 def choose_block_n(M: int, N: int, gemm_ctas: int, cta_pair: bool = False) -> int:
-    """Smallest modelled time: waves of the static tile schedule times the tile
-    width; ties go to the wider tile (fewer A re-reads).  With `cta_pair` a
-    tile is 256 rows and runs on two CTAs."""
-    best, best_cost = _BLOCK_NS[0], None
-    m_blocks = -(-M // (256 if cta_pair else 128))
-    units = gemm_ctas // 2 if cta_pair else gemm_ctas
-    for bn in _BLOCK_NS:
-        tiles = m_blocks * (-(-N // bn))
-        waves = -(-tiles // max(units, 1))
-        cost = waves * bn
-        if best_cost is None or cost < best_cost:
-            best, best_cost = bn, cost
-    return best
+    """Measured on B200: a tcgen05.mma of M = 128 rows per CTA takes the same
+    time for every N <= 256, so the widest tile is the efficient one; narrower
+    tiles only pay off when N itself is narrow (less zero padding streamed)."""
+    del M, gemm_ctas, cta_pair
+    for bn in sorted(_BLOCK_NS):
+        if N <= bn:
+            return bn
+    return 256
 
 
 def _check_2d_bf16(name: str, t: torch.Tensor) -> None:

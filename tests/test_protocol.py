@@ -1,0 +1,56 @@
+"""The signal-pad barrier protocol compiled for the host and hammered by
+threads acting as ranks, plus the pure-Python pieces (dispatcher, config)."""
+import pytest
+
+from symm_mem_recipes_b200._ext import C
+
+
+@pytest.mark.parametrize("world_size,blocks", [(2, 1), (4, 8), (8, 32)])
+def test_barrier_completes_and_restores_the_pad(world_size, blocks):
+    codes, pad_sum, skew = C.host_barrier_stress(world_size, blocks, 200, 5_000_000_000, -1)
+    assert list(codes) == [0] * world_size
+    assert pad_sum == 0            # zero-pad invariant: re-entrant without any host-side epoch
+    assert skew <= 1               # nobody got past a barrier a peer had not reached
+
+
+def test_barrier_with_a_dead_rank_times_out_everywhere():
+    codes, _, _ = C.host_barrier_stress(4, 2, 10, 100_000_000, 2)
+    live = [c for r, c in enumerate(codes) if r != 2]
+    assert all(c in (1, 2) for c in live)    # send or wait timed out, nobody hung
+
+
+def test_dispatcher_thresholds():
+    from symm_mem_recipes_b200.ops import choose_algo
+    from symm_mem_recipes_b200.ops.config import AllReduceConfig
+
+    cfg = AllReduceConfig(one_shot_max_bytes=1 << 18)
+    assert choose_algo(4096, 8, True, cfg) == "one_shot"
+    assert choose_algo(1 << 18, 8, True, cfg) == "one_shot"
+    assert choose_algo((1 << 18) + 16, 8, True, cfg) == "multimem"
+    assert choose_algo(1 << 26, 8, False, cfg) == "two_shot"
+    assert choose_algo(1 << 26, 1, False, cfg) == "one_shot"   # nothing to reduce
+
+
+def test_block_n_choice():
+    from symm_mem_recipes_b200.ops.ag_matmul import choose_block_n
+
+    assert choose_block_n(16384, 3584, 148) == 256
+    assert choose_block_n(256, 128, 148) == 128
+    assert choose_block_n(256, 200, 148) == 224
+
+
+def test_gemv_workspace_sizes_grow_with_world():
+    a = C.gemv_tc_workspace_bytes(8192, 3584, 1, 148)
+    b = C.gemv_tc_workspace_bytes(8192, 3584, 8, 148)
+    assert b > a > 0
+    assert C.matmul_rs_workspace_bytes(32768, 8192) == 32768 * 8192 * 2
+
+
+def test_status_decoding():
+    from symm_mem_recipes_b200.errors import SymmMemTimeout, raise_for_status
+
+    raise_for_status((0, 0, 0, 0, 0, 0))
+    with pytest.raises(SymmMemTimeout) as e:
+        raise_for_status((2, 3, 7, 5, 10, 0))
+    assert (e.value.rank, e.value.block, e.value.peer) == (3, 7, 5)
+    assert "never arrived" in str(e.value)
