@@ -140,10 +140,15 @@ def main() -> int:
         ms = sum(b_.elapsed_time(e_) for b_, e_ in zip(begins, ends)) / steps
         return max_over_ranks(ms, dev), wall
 
-    for _ in range(max(args.warmup, 3)):
-        step()
-    with ClockSampler(local_rank) as clocks:
+    # nvidia-smi needs a moment to start: the sampler runs from the warm-up on, and the
+    # timed region is repeated (same K steps, not reported) until it has seen the GPU under load
+    with ClockSampler(local_rank, period_ms=50) as clocks:
+        for _ in range(max(args.warmup, 3)):
+            step()
         ms_per_step, wall = timed(step, args.steps)
+        t_end = time.perf_counter() + 3.0
+        while clocks.samples_under_load() < 3 and time.perf_counter() < t_end:
+            timed(step, args.steps)
     symm_mem.check_status(dev)
 
     # ---- end to end: H2D of the step's input, public API, D2H of a checksum ----

@@ -199,20 +199,37 @@ class ClockSampler:
                 self._proc.kill()
         return False
 
+    def samples_under_load(self) -> int:
+        """Samples so far that show the GPU busy (power well above idle)."""
+        n = 0
+        for line in list(self._lines):
+            parts = [p.strip() for p in line.split(",")]
+            try:
+                if len(parts) >= 3 and float(parts[2]) > 300.0:
+                    n += 1
+            except ValueError:
+                continue
+        return n
+
     def summary(self) -> dict:
-        sm, smax, reasons = [], 0.0, set()
+        sm, idle, smax, reasons = [], [], 0.0, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in self._lines:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 7:
                 continue
             try:
-                sm.append(float(parts[0]))
+                clk, power = float(parts[0]), float(parts[2])
                 smax = max(smax, float(parts[1]))
             except ValueError:
                 continue
+            if power <= 300.0:          # idle sample (before / after the kernels): not "under load"
+                idle.append(clk)
+                continue
+            sm.append(clk)
             for name, val in zip(names, parts[3:7]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": smax or None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+        return {"sm_mhz": statistics.median(sm) if sm else (statistics.median(idle) if idle else None),
+                "sm_max_mhz": smax or None, "samples_under_load": len(sm), "samples_idle": len(idle),
+                "reasons": sorted(reasons)}
