@@ -354,3 +354,97 @@ int launch_gemv_all_reduce_tc(const GemvArgs& a, int num_sms, cudaStream_t strea
 }
 
 }  // namespace smr
+
+// ---------------------------------------------------------------------------
+// Allocation-free C entry point (see gemv_noalloc.h).  The scratch that the
+// kernel above normally finds in a symmetric workspace lives in this array;
+// offset 0 holds the one-entry "workspace base of every rank" table, the
+// workspace itself starts at offset 256.
+// ---------------------------------------------------------------------------
+#include <mutex>
+#include <stdio.h>
+
+#include "gemv_noalloc.h"
+
+namespace {
+
+static __device__ __align__(256) unsigned char g_gemv_noalloc_scratch[SMR_GEMV_NOALLOC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_noalloc_mu;
+unsigned char* g_noalloc_base[kMaxDevices] = {};   // device address of the array, per device
+int g_noalloc_sms[kMaxDevices] = {};
+
+int noalloc_fail(int code, char* err, int err_len, const char* what, const char* detail = "") {
+  if (err != nullptr && err_len > 0) snprintf(err, (size_t)err_len, "smr_gemv_bf16_noalloc: %s%s", what, detail);
+  return code;
+}
+
+}  // namespace
+
+extern "C" int smr_gemv_bf16_noalloc(const void* x, const void* w, void* out, int batch, int K, int N,
+                                     void* stream_ptr, char* err, int err_len) {
+  using namespace smr;
+  if (batch < 1 || batch > SMR_GEMV_NOALLOC_MAX_BATCH)
+    return noalloc_fail(1, err, err_len, "batch must be between 1 and 16");
+  if (N < 8 || N > SMR_GEMV_NOALLOC_MAX_N || N % 8 != 0)
+    return noalloc_fail(1, err, err_len, "N must be a multiple of 8 and at most 8192 (the scratch array is sized for that)");
+  if (K < 8 || K % 8 != 0) return noalloc_fail(1, err, err_len, "K must be a positive multiple of 8");
+  if (x == nullptr || w == nullptr || out == nullptr || ((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) % 16 != 0)
+    return noalloc_fail(2, err, err_len, "x, w and out must be non-null and 16-byte aligned");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return noalloc_fail(3, err, err_len, "cudaGetDevice: ", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return noalloc_fail(3, err, err_len, "device ordinal out of range");
+  unsigned char* base;
+  int sms;
+  {
+    // Once per device, with that device current: the array's name is only a
+    // host-side handle; the kernel needs the address the symbol has on THIS GPU.
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    if (g_noalloc_base[dev] == nullptr) {
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_gemv_noalloc_scratch);
+      if (e != cudaSuccess) return noalloc_fail(3, err, err_len, "cudaGetSymbolAddress: ", cudaGetErrorString(e));
+      void* ws_base = static_cast<unsigned char*>(p) + 256;
+      e = cudaMemcpy(p, &ws_base, sizeof(void*), cudaMemcpyHostToDevice);   // the one-entry base table
+      if (e != cudaSuccess) return noalloc_fail(3, err, err_len, "cudaMemcpy(base table): ", cudaGetErrorString(e));
+      int n = 0;
+      e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+      if (e != cudaSuccess) return noalloc_fail(3, err, err_len, "cudaDeviceGetAttribute: ", cudaGetErrorString(e));
+      g_noalloc_sms[dev] = n;
+      g_noalloc_base[dev] = static_cast<unsigned char*>(p);
+    }
+    base = g_noalloc_base[dev];
+    sms = g_noalloc_sms[dev];
+  }
+
+  GemvTcParams p{};
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.batch = batch; p.K = K; p.N = N;
+  p.rank = 0; p.world_size = 1;
+  p.buffers = reinterpret_cast<void* const*>(base);
+  p.timeout_ns = 2000000000ull;
+  p.status = nullptr;
+  size_t need = gemv_tc_workspace_bytes(N, K, 1, sms, &p.flags_offset, &p.inbox_offset, &p.tiles, &p.ksplit);
+  if (need + 256 > (size_t)SMR_GEMV_NOALLOC_SCRATCH_BYTES)
+    return noalloc_fail(1, err, err_len, "this shape needs more scratch than the static array holds");
+  CUtensorMap tw, tx;
+  try {
+    if (encode(&tw, w, (uint64_t)N, (uint64_t)K, 64, kBK) || encode(&tx, x, (uint64_t)K, (uint64_t)batch, kBK, kBatchN))
+      return noalloc_fail(3, err, err_len, "cuTensorMapEncodeTiled rejected the operands");
+  } catch (const std::exception& ex) {
+    return noalloc_fail(3, err, err_len, "CUDA driver: ", ex.what());
+  }
+  // "CTAs done" must read zero when the kernel starts; an aborted earlier call may have left it set
+  e = cudaMemsetAsync(base + 256 + 4, 0, 4, stream);
+  if (e != cudaSuccess) return noalloc_fail(3, err, err_len, "cudaMemsetAsync: ", cudaGetErrorString(e));
+  e = cudaFuncSetAttribute(gemv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTotal);
+  if (e != cudaSuccess) return noalloc_fail(3, err, err_len, "cudaFuncSetAttribute: ", cudaGetErrorString(e));
+  gemv_tc_kernel<<<p.tiles * p.ksplit, kThreads, kSmemTotal, stream>>>(tw, tx, p);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return noalloc_fail(3, err, err_len, "kernel launch: ", cudaGetErrorString(e));
+  return 0;
+}

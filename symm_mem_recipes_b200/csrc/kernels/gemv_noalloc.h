@@ -1,0 +1,62 @@
+// smr_gemv_bf16_noalloc: a decode GEMV for callers that must not allocate.
+//
+// This entry point has no counterpart in the upstream recipes.  It exists for
+// hosts that drive the GPU from a context in which device allocation is off
+// limits: a serving loop that has handed all of its memory to a pool and
+// forbids cudaMalloc on the hot path, a plugin loaded into someone else's
+// process that may not touch that process's allocator, or code running between
+// the begin and end of a region where allocation would synchronise the device.
+// Such a caller cannot create the symmetric workspace that `gemv_all_reduce`
+// sets up on first use, so the library carries the workspace itself.
+//
+//     out[b, n] = sum_k x[b, k] * w[k, n]      bf16 in, fp32 accumulate, bf16 out
+//
+// on ONE GPU (a world of one: nothing crosses NVLink), computed by the same
+// tcgen05 kernel as `gemv_all_reduce`.  That kernel splits K over several CTAs
+// per column tile and combines the partial sums through scratch memory; here
+// the scratch is a file-scope `static __device__` array of
+// SMR_GEMV_NOALLOC_SCRATCH_BYTES (about 4 MiB) that every GPU loading the
+// library holds until the process exits.
+//
+// What the caller must know:
+//  * Limits: 1 <= batch <= SMR_GEMV_NOALLOC_MAX_BATCH, N <= SMR_GEMV_NOALLOC_MAX_N,
+//    N % 8 == 0, K % 8 == 0, K >= 8.  Anything else is refused with a non-zero
+//    return value and a message in `err` (when `err` is not NULL); nothing is
+//    launched.
+//  * x is [batch, K], w is [K, N], out is [batch, N]; contiguous bf16 in device
+//    memory of the current device, 16-byte aligned.  The caller owns them.
+//  * The first call on each device resolves the device address of the scratch
+//    array (cudaGetSymbolAddress) and writes one pointer into it with a
+//    blocking copy.  Make that first call before any stream capture and outside
+//    any region that must not synchronise.  Later calls only enqueue work on
+//    `stream`.
+//  * No call allocates: no cudaMalloc, no cudaFree, no framework allocator.
+//  * All calls on a device share the one scratch array, which keeps whatever
+//    the previous call left in it.  The kernel's own bookkeeping tolerates
+//    that (and the entry point clears the one counter that must start at
+//    zero), but two calls that overlap in time on the same GPU — different
+//    streams, or two host threads — race on it and produce garbage.  Order
+//    them on one stream or with events.
+//
+// Returns 0 when the kernel was enqueued, otherwise:
+//   1 a size is outside the limits above      2 a pointer is null or misaligned
+//   3 a CUDA call failed (the message names it)
+#pragma once
+#include <stddef.h>
+
+#define SMR_GEMV_NOALLOC_MAX_BATCH 16
+#define SMR_GEMV_NOALLOC_MAX_N 8192
+#define SMR_GEMV_NOALLOC_SCRATCH_BYTES (256 + 16640 + 2 * 4 * 16 * SMR_GEMV_NOALLOC_MAX_N * 4)
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// `stream` is a cudaStream_t passed as a pointer (NULL = the default stream).
+// `err`/`err_len`: optional buffer that receives a NUL-terminated message on failure.
+int smr_gemv_bf16_noalloc(const void* x, const void* w, void* out, int batch, int K, int N,
+                          void* stream, char* err, int err_len);
+
+#ifdef __cplusplus
+}
+#endif
