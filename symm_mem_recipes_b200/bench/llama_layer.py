@@ -65,12 +65,22 @@ def main(argv=None, standalone: bool = True) -> int:
         us_r = benchmark_with_event(lambda: smr.reference_matmul_reduce_scatter(a, b), **bench)
         us_mm = benchmark_with_event(lambda: torch.matmul(a, b.t()), **bench)
         symm_mem.check_status(dev)
+        # phase breakdown from the kernel's own time stamps (one traced call)
+        trace = torch.zeros(148, 4, dtype=torch.int64, device=dev)
+        smr.matmul_reduce_scatter(a, b, out, trace=trace)
+        torch.cuda.synchronize()
+        tr = trace[trace[:, 0] > 0].double()
+        t0 = tr[:, 0].min()
+        phases = {"entered_us": float((tr[:, 1].max() - t0) / 1e3),
+                  "gemm_done_first_us": float((tr[:, 2].min() - t0) / 1e3),
+                  "gemm_done_last_us": float((tr[:, 2].max() - t0) / 1e3),
+                  "reduced_last_us": float((tr[:, 3].max() - t0) / 1e3)}
         wire = T * cfg.hidden * 2 * (world - 1) / world          # bytes leaving each GPU
         emit({"op": "matmul_reduce_scatter", "shape": name, "world_size": world, "M": T, "N": cfg.hidden,
               "K_local": k_local, "matches_library": ok, "smr_fused_us": round(us_f, 1),
               "cublas_plus_nccl_us": round(us_r, 1), "cublas_mm_only_us": round(us_mm, 1),
               "fused_tflops": round(flops / us_f / 1e6, 1), "wire_gbs": round(wire / us_f / 1e3, 1),
-              "speedup": round(us_r / us_f, 3)})
+              "speedup": round(us_r / us_f, 3), "phases": {k: round(v, 1) for k, v in phases.items()}})
         del a, b, out, ref
     # ---- whole layer ----
     if not args.skip_layer:
@@ -79,13 +89,16 @@ def main(argv=None, standalone: bool = True) -> int:
         y = layer.forward(x, args.batch, args.seq)
         symm_mem.check_status(dev)
         y_ref = layer.forward_reference(x, args.batch, args.seq)
-        ok = bool(torch.allclose(y.float(), y_ref.float(), rtol=5e-2, atol=5e-2))
+        # the two forwards round partial sums at different places (bf16 partials summed in fp32 here,
+        # bf16 reduce-scatter in NCCL): compare relative to the output's scale
+        rel = float((y.float() - y_ref.float()).abs().max() / y_ref.float().abs().max())
+        ok = rel < 3e-2
         us_f = benchmark_with_event(lambda: layer.forward(x, args.batch, args.seq), **bench)
         us_r = benchmark_with_event(lambda: layer.forward_reference(x, args.batch, args.seq), **bench)
         symm_mem.check_status(dev)
         emit({"op": "llama70b_layer_prefill", "world_size": world, "batch": args.batch, "seq": args.seq,
-              "matches_library": ok, "smr_fused_us": round(us_f, 1), "nccl_cublas_us": round(us_r, 1),
-              "tokens_per_s_fused": round(T / us_f * 1e6), "speedup": round(us_r / us_f, 3)})
+              "matches_library": ok, "max_rel_diff": round(rel, 5), "smr_fused_us": round(us_f, 1),
+              "nccl_cublas_us": round(us_r, 1), "tokens_per_s_fused": round(T / us_f * 1e6), "speedup": round(us_r / us_f, 3)})
         for B in (1, 4, 16):
             xd = (torch.randn(B, cfg.hidden, device=dev) * 0.5).to(torch.bfloat16)
             if world > 1:

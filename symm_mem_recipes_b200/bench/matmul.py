@@ -27,6 +27,8 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-cublas", action="store_true")
+    ap.add_argument("--eager", action="store_true",
+                    help="gemv: time eager launches with events instead of graph replay (for profilers)")
     args = ap.parse_args()
 
     import symm_mem_recipes_b200 as smr
@@ -74,10 +76,13 @@ def main() -> int:
                 torch.matmul(x, ws_[state["i"]])
 
             fused()
-            us = benchmark_with_graph(fused, calls_per_graph=20, replays=10, all_ranks_max=False)
-            out.update(batch=args.batch, K=K, N=N, smr_us=round(us, 2), timing="graph",
+            if args.eager:
+                us = benchmark_with_event(fused, **bench)
+            else:
+                us = benchmark_with_graph(fused, calls_per_graph=20, replays=10, all_ranks_max=False)
+            out.update(batch=args.batch, K=K, N=N, smr_us=round(us, 2), timing="event" if args.eager else "graph",
                        weight_gbs=round(K * N * 2 / us / 1e3, 1))
-            if not args.no_cublas:
+            if not args.no_cublas and not args.eager:
                 us2 = benchmark_with_graph(lib, calls_per_graph=20, replays=10, all_ranks_max=False)
                 out.update(cublas_us=round(us2, 2))
         else:

@@ -328,14 +328,17 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   });
   m.def("one_shot_all_reduce", [](const std::shared_ptr<CudaSymmAllocation>& a, int64_t offset_bytes,
                                   torch::Tensor out, int64_t numel, int max_blocks, bool exit_barrier,
-                                  uint64_t timeout_ns) {
+                                  uint64_t timeout_ns, bool write_back, bool stagger) {
     TORCH_CHECK(out.is_cuda() && out.is_contiguous() && out.scalar_type() == torch::kBFloat16 &&
                 out.numel() == numel, "bad output tensor");
     c10::cuda::CUDAGuard guard(a->device());
     rt_check(launch_one_shot_all_reduce(view_of(*a), (size_t)offset_bytes, out.data_ptr(), (size_t)numel,
-                                        max_blocks, exit_barrier, timeout_ns, status_for(a->device()),
-                                        current_stream(a->device())), "one_shot_all_reduce");
-  });
+                                        max_blocks, exit_barrier, write_back, stagger, timeout_ns,
+                                        status_for(a->device()), current_stream(a->device())),
+             "one_shot_all_reduce");
+  }, py::arg("alloc"), py::arg("offset_bytes"), py::arg("out"), py::arg("numel"), py::arg("max_blocks"),
+     py::arg("exit_barrier"), py::arg("timeout_ns"), py::arg("write_back") = false,
+     py::arg("stagger") = true);
   m.def("two_shot_all_reduce", [](const std::shared_ptr<CudaSymmAllocation>& a, int64_t offset_bytes,
                                   int64_t numel, int max_blocks, uint64_t timeout_ns) {
     c10::cuda::CUDAGuard guard(a->device());
@@ -466,7 +469,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("matmul_rs_workspace_bytes", &matmul_rs_workspace_bytes);
   m.def("matmul_reduce_scatter", [](torch::Tensor a, torch::Tensor b, torch::Tensor out,
                                     const std::shared_ptr<CudaSymmAllocation>& workspace, int num_sms,
-                                    uint64_t timeout_ns) {
+                                    uint64_t timeout_ns, c10::optional<torch::Tensor> trace) {
     auto ok2d = [](const torch::Tensor& t) {
       return t.is_cuda() && t.dim() == 2 && t.is_contiguous() && t.scalar_type() == torch::kBFloat16;
     };
@@ -485,12 +488,19 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     TORCH_CHECK(out.size(0) * args.pv.world_size == args.M && out.size(1) == args.N, "out must be [M / WS, N]");
     TORCH_CHECK(matmul_rs_workspace_bytes(args.M, args.N) <= workspace->payload_bytes(), "workspace too small");
     args.inbox_offset = 0;
+    for (int r = 0; r < args.pv.world_size; ++r) args.peer_base[r] = workspace->peer_ptr(r);
     args.local_pad = workspace->peer_pad(args.pv.rank);
     args.num_sms = num_sms;
     args.timeout_ns = timeout_ns;
     args.status = status_for(dev);
+    if (trace.has_value()) {
+      TORCH_CHECK(trace->is_cuda() && trace->scalar_type() == torch::kInt64 && trace->numel() >= 4 * num_sms,
+                  "trace must be an int64 CUDA tensor of at least 4 * num_sms elements");
+      args.trace = reinterpret_cast<uint64_t*>(trace->data_ptr());
+    }
     rt_check(launch_matmul_reduce_scatter(args, current_stream(dev)), "matmul_reduce_scatter");
-  });
+  }, py::arg("a"), py::arg("b"), py::arg("out"), py::arg("workspace"), py::arg("num_sms"),
+     py::arg("timeout_ns"), py::arg("trace") = py::none());
 
   // ---- oracles (CPU tensors) ----
   m.def("oracle_ordered_sum_bf16", [](std::vector<torch::Tensor> srcs) {

@@ -78,4 +78,57 @@ __device__ __forceinline__ bool blockwise_barrier(uint32_t* const* pads, uint32_
   return __syncthreads_and(ok) != 0;
 }
 
+// ---------------------------------------------------------------------------
+// Epoch barrier: the low-latency barrier of the all-reduce kernels.
+//
+// blockwise_barrier above pays a remote atomic round trip (CAS to the peer's
+// pad) before it can start waiting.  Here arrival is a plain store: thread
+// t < WS writes this block's barrier count e into slot [16 + rank] of peer t
+// (st.release.sys, one way over NVLink) and polls its OWN slot [16 + t] until
+// it reads a count >= e.  The count lives in the pad (slot [0] of the block's
+// group), is read when the kernel starts and written back when it ends, so no
+// launch parameter changes between calls and a captured graph replays.  A peer
+// can be at most one barrier ahead, hence the signed comparison.
+// ---------------------------------------------------------------------------
+struct EpochBarrier {
+  uint32_t* const* pads;
+  uint32_t* mine;      // this rank's group of kArFlagStride slots for this block id
+  uint32_t slot_base;  // offset of that group inside any rank's pad
+  uint32_t count;      // barriers passed so far by this block id
+  int rank, world_size;
+
+  __device__ __forceinline__ EpochBarrier(uint32_t* const* pads_, uint32_t block_id, int rank_, int ws)
+      : pads(pads_), rank(rank_), world_size(ws) {
+    slot_base = kArFlagBase + block_id * kArFlagStride;
+    mine = pads[rank] + slot_base;
+    count = ld_relaxed_gpu(mine);     // written by the previous kernel of this stream
+  }
+
+  // All threads of the CTA call it.  false on timeout (Status recorded).
+  __device__ __forceinline__ bool sync(uint64_t timeout_ns, Status* st, uint32_t where) {
+    ++count;
+    __syncthreads();   // the CTA's earlier writes precede the release
+    bool ok = true;
+    const uint32_t tid = flat_tid();
+    if (tid < (uint32_t)world_size) {
+      st_release_sys(pads[tid] + slot_base + 16u + (uint32_t)rank, count);
+      const uint32_t* wait = mine + 16u + tid;
+      Deadline d(timeout_ns);
+      while ((int32_t)(ld_acquire_sys(wait) - count) < 0) {
+        if (!d.alive()) {
+          report_status(st, kTimeoutBarrierWait, rank, slot_base, tid, where, count);
+          ok = false;
+          break;
+        }
+      }
+    }
+    return __syncthreads_and(ok) != 0;
+  }
+
+  // Once, by every thread, after the kernel's last sync.
+  __device__ __forceinline__ void finish() {
+    if (flat_tid() == 0) *mine = count;
+  }
+};
+
 }  // namespace smr

@@ -14,6 +14,7 @@
 // None of them has a counterpart launch parameter that must change between
 // calls: barriers return the pad to zero, so a captured graph replays.
 #include <cuda_runtime.h>
+#include <stdlib.h>
 
 #include "../device/barrier.cuh"
 #include "../device/multimem.cuh"
@@ -49,13 +50,58 @@ __global__ void wait_flag_kernel(const uint32_t* flag, uint32_t target, uint64_t
   }
 }
 
-template <int WS>
+// RANK is a template parameter so that the staggered issue order is static:
+// the WS loads of an element go out back to back and are only consumed by the
+// ordered sum (a run-time rotation would make the compiler select on each
+// loaded value right away, which serialises the WS NVLink round trips).
+__device__ __forceinline__ Vec16 ld_16_relaxed_sys(const void* p) {
+  Vec16 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
+template <int WS, int RANK, int VARIANT>
+__global__ void __launch_bounds__(kArThreads)
+one_shot_variant_kernel(PeerView pv, size_t offset_bytes, Vec16* __restrict__ out, size_t n_vec,
+                        uint64_t timeout_ns, Status* st) {
+  // VARIANT bit 0: CAS barrier instead of the epoch barrier; bits 1-2: load flavour
+  if constexpr ((VARIANT & 1) != 0) {
+    if (!blockwise_barrier(pv.pads, blockIdx.x, RANK, WS, timeout_ns, st, kWhereOneShotEntry)) return;
+  }
+  EpochBarrier bar(pv.pads, blockIdx.x, RANK, WS);
+  if constexpr ((VARIANT & 1) == 0) {
+    if (!bar.sync(timeout_ns, st, kWhereOneShotEntry)) return;
+  }
+  const Vec16* src[WS];
+#pragma unroll
+  for (int r = 0; r < WS; ++r)
+    src[r] = reinterpret_cast<const Vec16*>(static_cast<const char*>(pv.buffers[r]) + offset_bytes);
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += stride) {
+    Vec16 v[WS];
+#pragma unroll
+    for (int j = 0; j < WS; ++j) {
+      const int r = (RANK + 1 + j) % WS;
+      if constexpr ((VARIANT >> 1) == 0) v[r] = ld_16(src[r] + i);
+      else if constexpr ((VARIANT >> 1) == 1) v[r] = ld_16_relaxed_sys(src[r] + i);
+      else v[r] = ld_16_nc(src[r] + i);
+    }
+    Vec16 acc = {0u, 0u, 0u, 0u};
+#pragma unroll
+    for (int r = 0; r < WS; ++r) acc = add_bf16x8(acc, v[r]);
+    st_16(out + i, acc);
+  }
+  if constexpr ((VARIANT & 1) == 0) bar.finish();
+}
+
+template <int WS, int RANK, bool STAGGER>
 __global__ void __launch_bounds__(kArThreads)
 one_shot_all_reduce_kernel(PeerView pv, size_t offset_bytes, Vec16* __restrict__ out,
-                           size_t n_vec, bool exit_barrier, uint64_t timeout_ns, Status* st) {
-  const int rank = pv.rank;
-  if (!blockwise_barrier(pv.pads, blockIdx.x, rank, WS, timeout_ns, st, kWhereOneShotEntry))
-    return;
+                           size_t n_vec, bool exit_barrier, bool write_back, uint64_t timeout_ns,
+                           Status* st) {
+  EpochBarrier bar(pv.pads, blockIdx.x, RANK, WS);
+  if (!bar.sync(timeout_ns, st, kWhereOneShotEntry)) return;
 
   const Vec16* src[WS];
 #pragma unroll
@@ -65,13 +111,10 @@ one_shot_all_reduce_kernel(PeerView pv, size_t offset_bytes, Vec16* __restrict__
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += stride) {
     Vec16 v[WS];
-    // issue order staggered by rank; register slot = source rank
 #pragma unroll
     for (int j = 0; j < WS; ++j) {
-      int r = (rank + 1 + j) % WS;
-#pragma unroll
-      for (int k = 0; k < WS; ++k)
-        if (k == r) v[k] = ld_16(src[k] + i);
+      const int r = STAGGER ? (RANK + 1 + j) % WS : j;   // compile-time after unrolling
+      v[r] = ld_16(src[r] + i);
     }
     Vec16 acc = {0u, 0u, 0u, 0u};
 #pragma unroll
@@ -81,8 +124,15 @@ one_shot_all_reduce_kernel(PeerView pv, size_t offset_bytes, Vec16* __restrict__
 
   if (exit_barrier) {
     // proves that every peer has finished reading this rank's buffer
-    blockwise_barrier(pv.pads, blockIdx.x, rank, WS, timeout_ns, st, kWhereOneShotExit);
+    if (bar.sync(timeout_ns, st, kWhereOneShotExit) && write_back) {
+      // in-place form: now the sum may replace this rank's input; every thread
+      // copies back exactly the vectors it produced above
+      Vec16* self = reinterpret_cast<Vec16*>(static_cast<char*>(pv.buffers[RANK]) + offset_bytes);
+      for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += stride)
+        st_16(self + i, ld_16(out + i));
+    }
   }
+  bar.finish();
 }
 
 // Slice of 16-byte vectors owned by `r`: [begin, end)
@@ -92,13 +142,12 @@ __device__ __forceinline__ void slice_of(size_t n_vec, int ws, int r, size_t& be
   end = begin + q + ((size_t)r < rem ? 1 : 0);
 }
 
-template <int WS>
+template <int WS, int RANK>
 __global__ void __launch_bounds__(kArThreads)
 two_shot_all_reduce_kernel(PeerView pv, size_t offset_bytes, size_t n_vec, uint64_t timeout_ns,
                            Status* st) {
-  const int rank = pv.rank;
-  if (!blockwise_barrier(pv.pads, blockIdx.x, rank, WS, timeout_ns, st, kWhereTwoShotEntry))
-    return;
+  EpochBarrier bar(pv.pads, blockIdx.x, RANK, WS);
+  if (!bar.sync(timeout_ns, st, kWhereTwoShotEntry)) return;
 
   Vec16* buf[WS];
 #pragma unroll
@@ -106,16 +155,14 @@ two_shot_all_reduce_kernel(PeerView pv, size_t offset_bytes, size_t n_vec, uint6
     buf[r] = reinterpret_cast<Vec16*>(static_cast<char*>(pv.buffers[r]) + offset_bytes);
 
   size_t begin, end;
-  slice_of(n_vec, WS, rank, begin, end);
+  slice_of(n_vec, WS, RANK, begin, end);
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (size_t i = begin + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < end; i += stride) {
     Vec16 v[WS];
 #pragma unroll
     for (int j = 0; j < WS; ++j) {
-      int r = (rank + 1 + j) % WS;
-#pragma unroll
-      for (int k = 0; k < WS; ++k)
-        if (k == r) v[k] = ld_16(buf[k] + i);
+      const int r = (RANK + 1 + j) % WS;
+      v[r] = ld_16(buf[r] + i);
     }
     Vec16 acc = {0u, 0u, 0u, 0u};
 #pragma unroll
@@ -124,29 +171,28 @@ two_shot_all_reduce_kernel(PeerView pv, size_t offset_bytes, size_t n_vec, uint6
     // in-place push cannot overtake a reader.
 #pragma unroll
     for (int j = 0; j < WS; ++j) {
-      int r = (rank + 1 + j) % WS;
-#pragma unroll
-      for (int k = 0; k < WS; ++k)
-        if (k == r) st_16(buf[k] + i, acc);
+      const int r = (RANK + 1 + j) % WS;
+      st_16(buf[r] + i, acc);
     }
   }
   // All pushes of all ranks have landed once every CTA has passed this.
-  blockwise_barrier(pv.pads, blockIdx.x, rank, WS, timeout_ns, st, kWhereTwoShotExit);
+  bar.sync(timeout_ns, st, kWhereTwoShotExit);
+  bar.finish();
 }
 
 __global__ void __launch_bounds__(kArThreads)
 multimem_all_reduce_kernel(PeerView pv, size_t offset_bytes, size_t n_vec, uint64_t timeout_ns,
                            Status* st) {
   const int rank = pv.rank, ws = pv.world_size;
-  if (!blockwise_barrier(pv.pads, blockIdx.x, rank, ws, timeout_ns, st, kWhereMultimemEntry))
-    return;
+  EpochBarrier bar(pv.pads, blockIdx.x, rank, ws);
+  if (!bar.sync(timeout_ns, st, kWhereMultimemEntry)) return;
   Vec16* mc = reinterpret_cast<Vec16*>(static_cast<char*>(pv.multicast) + offset_bytes);
   size_t begin, end;
   slice_of(n_vec, ws, rank, begin, end);
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   size_t i = begin + (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  // four independent in-switch reductions in flight per thread
-  constexpr int U = 4;
+  // eight independent in-switch reductions in flight per thread
+  constexpr int U = 8;
   for (; i + (U - 1) * stride < end; i += U * stride) {
     Vec16 v[U];
 #pragma unroll
@@ -158,7 +204,8 @@ multimem_all_reduce_kernel(PeerView pv, size_t offset_bytes, size_t n_vec, uint6
     Vec16 a = multimem_ld_reduce_bf16x8(mc + i);
     multimem_st_16(mc + i, a);
   }
-  blockwise_barrier(pv.pads, blockIdx.x, rank, ws, timeout_ns, st, kWhereMultimemExit);
+  bar.sync(timeout_ns, st, kWhereMultimemExit);
+  bar.finish();
 }
 
 int blocks_for(size_t n_vec, int max_blocks) {
@@ -193,26 +240,49 @@ int launch_wait_flag(const uint32_t* flag, uint32_t target, uint64_t timeout_ns,
   return last_error();
 }
 
-#define SMR_DISPATCH_WS(ws, ...)                      \
-  switch (ws) {                                       \
-    case 1: { constexpr int WS = 1; __VA_ARGS__; break; } \
-    case 2: { constexpr int WS = 2; __VA_ARGS__; break; } \
-    case 4: { constexpr int WS = 4; __VA_ARGS__; break; } \
-    case 8: { constexpr int WS = 8; __VA_ARGS__; break; } \
-    default: return cudaErrorInvalidValue;            \
+#define SMR_RANK_CASE(r, ...) case r: { constexpr int RANK = r; __VA_ARGS__; break; }
+#define SMR_DISPATCH_WS_RANK(ws, rank, ...)                                                     \
+  switch (ws) {                                                                                 \
+    case 1: { constexpr int WS = 1; switch (rank) { SMR_RANK_CASE(0, __VA_ARGS__) default: return cudaErrorInvalidValue; } break; } \
+    case 2: { constexpr int WS = 2; switch (rank) { SMR_RANK_CASE(0, __VA_ARGS__) SMR_RANK_CASE(1, __VA_ARGS__) default: return cudaErrorInvalidValue; } break; } \
+    case 4: { constexpr int WS = 4; switch (rank) { SMR_RANK_CASE(0, __VA_ARGS__) SMR_RANK_CASE(1, __VA_ARGS__) SMR_RANK_CASE(2, __VA_ARGS__) SMR_RANK_CASE(3, __VA_ARGS__) default: return cudaErrorInvalidValue; } break; } \
+    case 8: { constexpr int WS = 8; switch (rank) { SMR_RANK_CASE(0, __VA_ARGS__) SMR_RANK_CASE(1, __VA_ARGS__) SMR_RANK_CASE(2, __VA_ARGS__) SMR_RANK_CASE(3, __VA_ARGS__) SMR_RANK_CASE(4, __VA_ARGS__) SMR_RANK_CASE(5, __VA_ARGS__) SMR_RANK_CASE(6, __VA_ARGS__) SMR_RANK_CASE(7, __VA_ARGS__) default: return cudaErrorInvalidValue; } break; } \
+    default: return cudaErrorInvalidValue;                                                      \
   }
 
 int launch_one_shot_all_reduce(const PeerView& pv, size_t offset_bytes, void* out, size_t numel,
-                               int max_blocks, bool exit_barrier, uint64_t timeout_ns,
-                               Status* status, cudaStream_t stream) {
+                               int max_blocks, bool exit_barrier, bool write_back, bool stagger,
+                               uint64_t timeout_ns, Status* status, cudaStream_t stream) {
+  if (write_back && !exit_barrier) return cudaErrorInvalidValue;
   if (numel % 8 != 0 || offset_bytes % 16 != 0) return cudaErrorInvalidValue;
   size_t n_vec = numel / 8;
-  if ((uint32_t)max_blocks * pv.world_size > kBlockSlots) max_blocks = kBlockSlots / pv.world_size;
+  if ((uint32_t)max_blocks > kArMaxBlocks) max_blocks = (int)kArMaxBlocks;
   int blocks = blocks_for(n_vec, max_blocks);
-  SMR_DISPATCH_WS(pv.world_size,
-                  one_shot_all_reduce_kernel<WS><<<blocks, kArThreads, 0, stream>>>(
-                      pv, offset_bytes, static_cast<Vec16*>(out), n_vec, exit_barrier, timeout_ns,
-                      status));
+  static int variant = -1;
+  if (variant < 0) {
+    const char* e = getenv("SMR_AR_ONE_SHOT_VARIANT");
+    variant = e != nullptr ? atoi(e) : 0;
+  }
+  if (variant > 0 && !exit_barrier) {
+    switch (variant) {
+      case 1: SMR_DISPATCH_WS_RANK(pv.world_size, pv.rank, (one_shot_variant_kernel<WS, RANK, 1><<<blocks, kArThreads, 0, stream>>>(pv, offset_bytes, static_cast<Vec16*>(out), n_vec, timeout_ns, status))); break;
+      case 2: SMR_DISPATCH_WS_RANK(pv.world_size, pv.rank, (one_shot_variant_kernel<WS, RANK, 2><<<blocks, kArThreads, 0, stream>>>(pv, offset_bytes, static_cast<Vec16*>(out), n_vec, timeout_ns, status))); break;
+      case 4: SMR_DISPATCH_WS_RANK(pv.world_size, pv.rank, (one_shot_variant_kernel<WS, RANK, 4><<<blocks, kArThreads, 0, stream>>>(pv, offset_bytes, static_cast<Vec16*>(out), n_vec, timeout_ns, status))); break;
+      default: SMR_DISPATCH_WS_RANK(pv.world_size, pv.rank, (one_shot_variant_kernel<WS, RANK, 5><<<blocks, kArThreads, 0, stream>>>(pv, offset_bytes, static_cast<Vec16*>(out), n_vec, timeout_ns, status))); break;
+    }
+    return last_error();
+  }
+  if (stagger) {
+    SMR_DISPATCH_WS_RANK(pv.world_size, pv.rank,
+                         (one_shot_all_reduce_kernel<WS, RANK, true><<<blocks, kArThreads, 0, stream>>>(
+                             pv, offset_bytes, static_cast<Vec16*>(out), n_vec, exit_barrier, write_back,
+                             timeout_ns, status)));
+  } else {
+    SMR_DISPATCH_WS_RANK(pv.world_size, pv.rank,
+                         (one_shot_all_reduce_kernel<WS, RANK, false><<<blocks, kArThreads, 0, stream>>>(
+                             pv, offset_bytes, static_cast<Vec16*>(out), n_vec, exit_barrier, write_back,
+                             timeout_ns, status)));
+  }
   return last_error();
 }
 
@@ -221,11 +291,11 @@ int launch_two_shot_all_reduce(const PeerView& pv, size_t offset_bytes, size_t n
                                cudaStream_t stream) {
   if (numel % 8 != 0 || offset_bytes % 16 != 0) return cudaErrorInvalidValue;
   size_t n_vec = numel / 8;
-  if ((uint32_t)max_blocks * pv.world_size > kBlockSlots) max_blocks = kBlockSlots / pv.world_size;
+  if ((uint32_t)max_blocks > kArMaxBlocks) max_blocks = (int)kArMaxBlocks;
   int blocks = blocks_for((n_vec + pv.world_size - 1) / pv.world_size, max_blocks);
-  SMR_DISPATCH_WS(pv.world_size,
-                  two_shot_all_reduce_kernel<WS><<<blocks, kArThreads, 0, stream>>>(
-                      pv, offset_bytes, n_vec, timeout_ns, status));
+  SMR_DISPATCH_WS_RANK(pv.world_size, pv.rank,
+                       (two_shot_all_reduce_kernel<WS, RANK><<<blocks, kArThreads, 0, stream>>>(
+                           pv, offset_bytes, n_vec, timeout_ns, status)));
   return last_error();
 }
 
@@ -235,7 +305,7 @@ int launch_multimem_all_reduce(const PeerView& pv, size_t offset_bytes, size_t n
   if (numel % 8 != 0 || offset_bytes % 16 != 0) return cudaErrorInvalidValue;
   if (pv.multicast == nullptr) return cudaErrorNotSupported;
   size_t n_vec = numel / 8;
-  if ((uint32_t)max_blocks * pv.world_size > kBlockSlots) max_blocks = kBlockSlots / pv.world_size;
+  if ((uint32_t)max_blocks > kArMaxBlocks) max_blocks = (int)kArMaxBlocks;
   int blocks = blocks_for((n_vec + pv.world_size - 1) / pv.world_size, max_blocks);
   multimem_all_reduce_kernel<<<blocks, kArThreads, 0, stream>>>(pv, offset_bytes, n_vec,
                                                                  timeout_ns, status);

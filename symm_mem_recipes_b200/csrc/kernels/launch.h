@@ -30,9 +30,12 @@ int launch_wait_flag(const uint32_t* flag, uint32_t target, uint64_t timeout_ns,
 
 // ---- all-reduce (bf16) -----------------------------------------------------
 // `offset_bytes` is the offset of the tensor inside the symmetric payload.
+// `stagger`: rank r issues its peer loads starting at rank r+1 (else at rank 0, as upstream).
+// `write_back` (needs exit_barrier): after the exit barrier the sum also replaces this
+// rank's symmetric input, i.e. the in-place form used by the dispatcher.
 int launch_one_shot_all_reduce(const PeerView& pv, size_t offset_bytes, void* out, size_t numel,
-                               int max_blocks, bool exit_barrier, uint64_t timeout_ns,
-                               Status* status, cudaStream_t stream);
+                               int max_blocks, bool exit_barrier, bool write_back, bool stagger,
+                               uint64_t timeout_ns, Status* status, cudaStream_t stream);
 int launch_two_shot_all_reduce(const PeerView& pv, size_t offset_bytes, size_t numel,
                                int max_blocks, uint64_t timeout_ns, Status* status,
                                cudaStream_t stream);
@@ -104,10 +107,12 @@ struct MatmulRsArgs {
   int M, N, K;
   PeerView pv;        // of the symmetric workspace (inbox)
   size_t inbox_offset;
+  void* peer_base[16]; // host copy: workspace payload base of every rank as mapped here
   uint32_t* local_pad;
   int num_sms;
   uint64_t timeout_ns;
   Status* status;
+  uint64_t* trace;     // optional [num_sms][4] %globaltimer stamps per CTA (start, entered, GEMM done, reduced)
 };
 size_t matmul_rs_workspace_bytes(int M, int N);
 int launch_matmul_reduce_scatter(const MatmulRsArgs& args, cudaStream_t stream);

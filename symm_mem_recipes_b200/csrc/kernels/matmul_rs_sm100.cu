@@ -7,11 +7,14 @@
 //  * Tiles are visited by destination rank: rank+1 first, ..., own rows last,
 //    so the links are busy from the first tile and nothing waits on the wire
 //    at the end.
-//  * Epilogue: accumulator -> bf16 -> a shared-memory staging strip of 64
-//    columns -> one 128-byte bulk store (cp.async.bulk, shared -> global) per
-//    row into the DESTINATION rank's inbox [src][row][N].  Full-row packets
-//    cross NVLink, not 16-byte fragments.  When a tile's stores have completed
-//    the destination's arrival counter for that tile gets +1 (red.release.sys).
+//  * Epilogue: accumulator -> bf16 -> a swizzled shared-memory strip of
+//    [128 rows x 64 columns] -> ONE TMA tensor store (cp.async.bulk.tensor,
+//    shared -> global) into the DESTINATION rank's inbox [src][row][N], through
+//    a tensor map built over that peer's memory.  Two strips alternate, so the
+//    next strip is converted while the previous one is on the wire, and whole
+//    128-byte lines cross NVLink.  A tile's arrival counter on the destination
+//    gets +1 (red.release.sys) once the tile's stores have completed, which is
+//    checked one tile later so the epilogue never waits for the wire.
 //  * Reduce: after its GEMM tiles every CTA takes output tiles of its own rank,
 //    waits (bounded) until WS partials have arrived, sums them in rank order in
 //    fp32 and writes bf16.  All ranks thus produce identical bits.
@@ -40,8 +43,13 @@ constexpr int kUmmaK = 16;
 constexpr int kStages = 4;
 constexpr int kThreads = 192;
 constexpr uint32_t kTmemCols = 512;
-constexpr int kStripCols = 64;                         // columns staged at a time
-constexpr uint32_t kStripPitch = kStripCols * 2 + 16;  // bytes; +16 spreads rows over banks
+constexpr int kStripCols = 64;                         // columns staged at a time (128 bytes: one swizzle row)
+constexpr uint32_t kStripBytesOne = kBM * kStripCols * 2;   // 16 KB
+constexpr int kMaxWorld = 8;
+
+struct InboxMaps {
+  CUtensorMap m[kMaxWorld];   // m[d]: this rank's slice [M/WS, N] of rank d's inbox
+};
 
 struct RsParams {
   int M, N, K;
@@ -55,6 +63,7 @@ struct RsParams {
   __nv_bfloat16* out;        // [M/WS, N]
   uint64_t timeout_ns;
   Status* status;
+  uint64_t* trace;           // optional [grid][4] %globaltimer stamps: start, entered, GEMM done, reduced
 };
 
 struct Smem {
@@ -63,13 +72,22 @@ struct Smem {
   static constexpr uint32_t kStageBytes = kABytes + kBBytes;
   static constexpr uint32_t kRingBytes = kStageBytes * kStages;
   static constexpr uint32_t kStripOffset = kRingBytes;
-  static constexpr uint32_t kStripBytes = kBM * kStripPitch;
+  static constexpr uint32_t kStripBytes = 2 * kStripBytesOne;   // two strips alternate
   static constexpr uint32_t kBarOffset = kStripOffset + kStripBytes;
   static constexpr uint32_t kNumBars = 2 * kStages + 4;
   static constexpr uint32_t kMiscOffset = kBarOffset + 8 * kNumBars;
   static constexpr uint32_t kTotal = kMiscOffset + 16 + 1024;
 };
 static_assert(Smem::kTotal <= 232448, "shared memory budget exceeded");
+
+__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// 2-D tile shared -> global through a tensor map (which may describe a peer GPU's memory)
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int32_t x, int32_t y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+               : "memory");
+}
 
 // tile index -> destination rank, 128-row block inside the destination, N tile
 __device__ __forceinline__ void tile_coords(const RsParams& p, int t, int& dest, int& mb, int& ni) {
@@ -81,9 +99,73 @@ __device__ __forceinline__ void tile_coords(const RsParams& p, int t, int& dest,
   ni = rem - mb * p.n_tiles_n;
 }
 
+// Ordered fp32 sum of the WS partials of one [128 x 256] output tile.  16
+// independent 16-byte loads are in flight per thread (the phase is bound by
+// memory latency otherwise): 16 / WS output vectors at a time.  WS = 0 selects
+// the generic loop for other world sizes.
+template <int WS>
+__device__ __forceinline__ void reduce_tile(const RsParams& p, const __nv_bfloat16* inbox, int mb, int ni,
+                                            int rows_per_rank) {
+  const int n0 = ni * kBN;
+  const int vec_per_row = (min(kBN, p.N - n0)) / 8;
+  const int total = kBM * vec_per_row;
+  const size_t src_stride = (size_t)rows_per_rank * p.N;
+  if constexpr (WS == 0) {
+    for (int idx = threadIdx.x; idx < total; idx += kThreads) {
+      const int row = mb * kBM + idx / vec_per_row, cv = idx % vec_per_row;
+      const size_t off = (size_t)row * p.N + n0 + cv * 8;
+      float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int src = 0; src < p.world_size; ++src) {
+        Vec16 v = ld_16_stream(inbox + (size_t)src * src_stride + off);
+        s[0] += bf16lo_to_f32(v.x); s[1] += bf16hi_to_f32(v.x);
+        s[2] += bf16lo_to_f32(v.y); s[3] += bf16hi_to_f32(v.y);
+        s[4] += bf16lo_to_f32(v.z); s[5] += bf16hi_to_f32(v.z);
+        s[6] += bf16lo_to_f32(v.w); s[7] += bf16hi_to_f32(v.w);
+      }
+      Vec16 o;
+      o.x = pack_bf16x2(s[0], s[1]); o.y = pack_bf16x2(s[2], s[3]);
+      o.z = pack_bf16x2(s[4], s[5]); o.w = pack_bf16x2(s[6], s[7]);
+      st_16(p.out + off, o);
+    }
+  } else {
+    constexpr int U = 16 / WS;
+    for (int idx0 = threadIdx.x; idx0 < total; idx0 += kThreads * U) {
+      Vec16 v[U][WS];
+      size_t off[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int idx = idx0 + u * kThreads;
+        const int row = mb * kBM + idx / vec_per_row, cv = idx % vec_per_row;
+        off[u] = (size_t)row * p.N + n0 + cv * 8;
+        if (idx < total) {
+#pragma unroll
+          for (int src = 0; src < WS; ++src) v[u][src] = ld_16_stream(inbox + (size_t)src * src_stride + off[u]);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (idx0 + u * kThreads >= total) break;
+        float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int src = 0; src < WS; ++src) {
+          const Vec16& w = v[u][src];
+          s[0] += bf16lo_to_f32(w.x); s[1] += bf16hi_to_f32(w.x);
+          s[2] += bf16lo_to_f32(w.y); s[3] += bf16hi_to_f32(w.y);
+          s[4] += bf16lo_to_f32(w.z); s[5] += bf16hi_to_f32(w.z);
+          s[6] += bf16lo_to_f32(w.w); s[7] += bf16hi_to_f32(w.w);
+        }
+        Vec16 o;
+        o.x = pack_bf16x2(s[0], s[1]); o.y = pack_bf16x2(s[2], s[3]);
+        o.z = pack_bf16x2(s[4], s[5]); o.w = pack_bf16x2(s[6], s[7]);
+        st_16(p.out + off[u], o);
+      }
+    }
+  }
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 matmul_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const RsParams p) {
+                 const __grid_constant__ InboxMaps inbox_maps, const RsParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* strip = smem + Smem::kStripOffset;
@@ -117,9 +199,11 @@ matmul_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish_alloc_permit();
   }
+  if (p.trace != nullptr && threadIdx.x == 0) p.trace[blockIdx.x * 4 + 0] = globaltimer_ns();
   // every rank has entered this call: its reduce of the previous call is done
   bool entered = blockwise_barrier(p.pads, 1024u + blockIdx.x, p.rank, p.world_size, p.timeout_ns,
                                    p.status, kWhereRsEntry);
+  if (p.trace != nullptr && threadIdx.x == 0) p.trace[blockIdx.x * 4 + 1] = globaltimer_ns();
   tcgen05_fence_before_thread_sync();
   __syncthreads();
   tcgen05_fence_after_thread_sync();
@@ -187,11 +271,12 @@ matmul_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
     }
   } else {
-    // ---------------- epilogue: TMEM -> bf16 strip -> bulk stores to the destination ----------------
+    // ---------------- epilogue: TMEM -> bf16 strip -> TMA store into the destination ----------------
     const int quarter = warp & 3;
+    const int etid = (int)threadIdx.x - 64;
     const int r = quarter * 32 + lane;                  // row of the tile owned by this thread
-    uint8_t* my_strip = strip + (size_t)r * kStripPitch;
-    uint32_t acc = 0, acc_phase = 0;
+    uint32_t acc = 0, acc_phase = 0, strip_ctr = 0;
+    uint32_t* prev_counter = nullptr;                   // tile whose stores are issued but not yet signalled
     for (int t = blockIdx.x; t < total_tiles && !failed; t += gridDim.x) {
       int dest, mb, ni;
       tile_coords(p, t, dest, mb, ni);
@@ -203,50 +288,63 @@ matmul_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
       tcgen05_fence_after_thread_sync();
       const uint32_t taddr = tmem_base + acc * 256u + ((uint32_t)(quarter * 32) << 16);
-      // inbox of the destination: [src = this rank][row in destination][N]
-      __nv_bfloat16* inbox = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(p.buffers[dest]) + p.inbox_offset);
-      __nv_bfloat16* drow = inbox + ((size_t)p.rank * rows_per_rank + (size_t)mb * kBM + r) * p.N;
+      int strips = 0;
 #pragma unroll 1
       for (int sidx = 0; sidx < kBN / kStripCols; ++sidx) {
         const int col0 = ni * kBN + sidx * kStripCols;
         if (col0 >= p.N) break;                          // uniform over the CTA
-        bulk_wait_group_read<0>();                       // my previous row store has left the strip
+        uint32_t v0[32], v1[32];
+        tmem_ld_32x32b_x32(taddr + (uint32_t)(sidx * kStripCols), v0);
+        tmem_ld_32x32b_x32(taddr + (uint32_t)(sidx * kStripCols + 32), v1);
+        tmem_ld_wait();
+        // the store issued two strips ago has finished reading the buffer we are about to fill
+        if (etid == 0) bulk_wait_group_read<1>();
+        epilogue_sync();
+        uint8_t* buf = strip + (size_t)(strip_ctr & 1u) * kStripBytesOne;
+        uint8_t* row = buf + (size_t)r * 128;
 #pragma unroll
-        for (int h = 0; h < kStripCols / 32; ++h) {
-          uint32_t v[32];
-          tmem_ld_32x32b_x32(taddr + (uint32_t)(sidx * kStripCols + h * 32), v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            Vec16 o;
-            o.x = pack_bf16x2(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1]));
-            o.y = pack_bf16x2(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3]));
-            o.z = pack_bf16x2(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5]));
-            o.w = pack_bf16x2(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]));
-            *reinterpret_cast<Vec16*>(my_strip + h * 64 + q * 16) = o;
-          }
+        for (int c = 0; c < 8; ++c) {                    // 16-byte chunk c of the row, 128-byte swizzle
+          const uint32_t* v = c < 4 ? &v0[c * 8] : &v1[(c - 4) * 8];
+          Vec16 o;
+          o.x = pack_bf16x2(__uint_as_float(v[0]), __uint_as_float(v[1]));
+          o.y = pack_bf16x2(__uint_as_float(v[2]), __uint_as_float(v[3]));
+          o.z = pack_bf16x2(__uint_as_float(v[4]), __uint_as_float(v[5]));
+          o.w = pack_bf16x2(__uint_as_float(v[6]), __uint_as_float(v[7]));
+          *reinterpret_cast<Vec16*>(row + ((c ^ (r & 7)) << 4)) = o;
         }
-        fence_proxy_async();                             // strip written by this thread, read by the bulk store
-        int cols = p.N - col0;
-        if (cols > kStripCols) cols = kStripCols;
-        bulk_store(drow + col0, my_strip, (uint32_t)cols * 2u);
-        bulk_commit_group();
+        fence_proxy_async();                             // generic writes to smem, async-proxy read
+        epilogue_sync();
+        if (etid == 0) {
+          tma_store_2d(&inbox_maps.m[dest], buf, col0, mb * kBM);
+          bulk_commit_group();
+        }
+        ++strip_ctr;
+        ++strips;
       }
-      // the accumulator has been read: hand it back before waiting on the wire
+      // the accumulator has been read: hand it back
       tcgen05_fence_before_thread_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
-      bulk_wait_group<0>();                              // my rows have been written at the destination
-      asm volatile("bar.sync 1, 128;" ::: "memory");     // the four epilogue warps
-      if (warp == 2 && lane == 0) {
-        uint32_t* counters = p.pads[dest] + kFlagSlotsBase + 2;
-        fence_proxy_async();
-        red_add_release_sys(&counters[mb * p.n_tiles_n + ni], 1u);
+      if (etid == 0) {
+        if (prev_counter != nullptr) {
+          // everything older than this tile's groups has completed
+          if (strips == 4) bulk_wait_group<4>();
+          else bulk_wait_group<0>();
+          fence_proxy_async();
+          red_add_release_sys(prev_counter, 1u);
+        }
+        prev_counter = p.pads[dest] + kFlagSlotsBase + 2 + mb * p.n_tiles_n + ni;
       }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
-    bulk_wait_group<0>();
+    if (etid == 0) {
+      bulk_wait_group<0>();
+      if (prev_counter != nullptr && !failed) {
+        fence_proxy_async();
+        red_add_release_sys(prev_counter, 1u);
+      }
+    }
   }
 
   // ---------------- GEMM teardown ----------------
@@ -257,6 +355,7 @@ matmul_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   failed = __syncthreads_or(failed) != 0;
   tcgen05_fence_after_thread_sync();
   if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+  if (p.trace != nullptr && threadIdx.x == 0) p.trace[blockIdx.x * 4 + 2] = globaltimer_ns();
 
   // ---------------- reduce the tiles of this rank ----------------
   if (!failed) {
@@ -271,31 +370,18 @@ matmul_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         ok = false;
       }
       if (!__syncthreads_and(ok)) break;
-      const int n0 = ni * kBN;
-      const int vec_per_row = (min(kBN, p.N - n0)) / 8;
-      for (int idx = threadIdx.x; idx < kBM * vec_per_row; idx += kThreads) {
-        const int row = mb * kBM + idx / vec_per_row, cv = idx % vec_per_row;
-        const size_t off = (size_t)row * p.N + n0 + cv * 8;
-        float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int src = 0; src < p.world_size; ++src) {
-          Vec16 v = ld_16_stream(inbox + (size_t)src * rows_per_rank * p.N + off);
-          s[0] += bf16lo_to_f32(v.x); s[1] += bf16hi_to_f32(v.x);
-          s[2] += bf16lo_to_f32(v.y); s[3] += bf16hi_to_f32(v.y);
-          s[4] += bf16lo_to_f32(v.z); s[5] += bf16hi_to_f32(v.z);
-          s[6] += bf16lo_to_f32(v.w); s[7] += bf16hi_to_f32(v.w);
-        }
-        Vec16 o;
-        o.x = pack_bf16x2(s[0], s[1]);
-        o.y = pack_bf16x2(s[2], s[3]);
-        o.z = pack_bf16x2(s[4], s[5]);
-        o.w = pack_bf16x2(s[6], s[7]);
-        st_16(p.out + off, o);
+      switch (p.world_size) {
+        case 2: reduce_tile<2>(p, inbox, mb, ni, rows_per_rank); break;
+        case 4: reduce_tile<4>(p, inbox, mb, ni, rows_per_rank); break;
+        case 8: reduce_tile<8>(p, inbox, mb, ni, rows_per_rank); break;
+        default: reduce_tile<0>(p, inbox, mb, ni, rows_per_rank); break;
       }
     }
   }
 
   // ---------------- the last CTA to finish publishes this call's number ----------------
   __syncthreads();
+  if (p.trace != nullptr && threadIdx.x == 0) p.trace[blockIdx.x * 4 + 3] = globaltimer_ns();
   if (threadIdx.x == 0) {
     uint32_t done = atomicAdd(&header[1], 1u);
     if (done == gridDim.x - 1) {
@@ -319,6 +405,19 @@ int make_tmap(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, 
   return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
+// [rows, cols] bf16 destination with a [128 rows x 64 cols] swizzled box
+int make_store_tmap(CUtensorMap* map, void* base, uint64_t rows, uint64_t cols) {
+  const DriverApi& d = DriverApi::get();
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 2};
+  cuuint32_t box[2] = {(cuuint32_t)kStripCols, (cuuint32_t)kBM};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = d.cuTensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, estr,
+                                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                        CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 1;
+}
+
 }  // namespace
 
 size_t matmul_rs_workspace_bytes(int M, int N) { return (size_t)M * N * 2; }
@@ -339,16 +438,25 @@ int launch_matmul_reduce_scatter(const MatmulRsArgs& a, cudaStream_t stream) {
   p.out = static_cast<__nv_bfloat16*>(a.out);
   p.timeout_ns = a.timeout_ns;
   p.status = a.status;
+  p.trace = a.trace;
   CUtensorMap ta, tb;
   if (make_tmap(&ta, a.a, (uint64_t)a.M, (uint64_t)a.K, kBM)) return cudaErrorInvalidValue;
   if (make_tmap(&tb, a.b, (uint64_t)a.N, (uint64_t)a.K, kBN)) return cudaErrorInvalidValue;
+  if (ws > kMaxWorld) return cudaErrorInvalidValue;
+  InboxMaps maps{};
+  const size_t slice_bytes = (size_t)(a.M / ws) * a.N * 2;
+  for (int d = 0; d < ws; ++d) {
+    // this rank's slice of rank d's inbox, as mapped into this process
+    char* base = static_cast<char*>(a.peer_base[d]) + a.inbox_offset + (size_t)p.rank * slice_bytes;
+    if (make_store_tmap(&maps.m[d], base, (uint64_t)(a.M / ws), (uint64_t)a.N)) return cudaErrorInvalidValue;
+  }
   int total_tiles = ws * p.blocks_per_rank * p.n_tiles_n;
   int grid = a.num_sms < total_tiles ? a.num_sms : total_tiles;
   if (grid < 1 || (uint32_t)(1024 + grid) * (uint32_t)ws > kBlockSlots) return cudaErrorInvalidValue;
   cudaError_t e = cudaFuncSetAttribute(matmul_rs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)Smem::kTotal);
   if (e != cudaSuccess) return (int)e;
-  matmul_rs_kernel<<<grid, kThreads, Smem::kTotal, stream>>>(ta, tb, p);
+  matmul_rs_kernel<<<grid, kThreads, Smem::kTotal, stream>>>(ta, tb, maps, p);
   return (int)cudaGetLastError();
 }
 

@@ -76,6 +76,7 @@ CudaSymmAllocation::CudaSymmAllocation(int device, size_t payload_bytes)
         mgran > gran)
       gran = round_up(mgran, gran);
   }
+  granularity_ = gran;
   pad_offset_ = round_up(payload_bytes_ == 0 ? 16 : payload_bytes_, 256);
   block_bytes_ = round_up(pad_offset_ + kSignalPadBytes, gran);
   SMR_CU_CHECK(d.cuMemCreate(&handle_, block_bytes_, &prop, 0));
@@ -136,7 +137,8 @@ void CudaSymmAllocation::exchange_and_map(const FdChannel& chan,
     SMR_CU_CHECK(r);
     peer_handles_[m.src_rank] = h;
     CUdeviceptr va = 0;
-    SMR_CU_CHECK(d.cuMemAddressReserve(&va, block_bytes_, 0, 0, 0));
+    // aligned to the allocation granularity so that the mapping can use large pages
+    SMR_CU_CHECK(d.cuMemAddressReserve(&va, block_bytes_, granularity_, 0, 0));
     SMR_CU_CHECK(d.cuMemMap(va, block_bytes_, 0, h, 0));
     set_rw_access(va, block_bytes_, device_);
     peer_va_[m.src_rank] = va;
@@ -190,7 +192,7 @@ void CudaSymmAllocation::multicast_bind_and_map() {
   if (mc_handle_ == 0) throw std::runtime_error("no multicast object");
   SMR_CU_CHECK(d.cuMulticastBindMem(mc_handle_, 0, handle_, 0, block_bytes_, 0));
   mc_bound_ = true;
-  SMR_CU_CHECK(d.cuMemAddressReserve(&mc_va_, block_bytes_, 0, 0, 0));
+  SMR_CU_CHECK(d.cuMemAddressReserve(&mc_va_, block_bytes_, granularity_, 0, 0));
   SMR_CU_CHECK(d.cuMemMap(mc_va_, block_bytes_, 0, mc_handle_, 0));
   set_rw_access(mc_va_, block_bytes_, device_);
 }

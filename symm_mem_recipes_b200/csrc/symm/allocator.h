@@ -70,6 +70,7 @@ class CudaSymmAllocation {
  private:
   int device_;
   size_t payload_bytes_, pad_offset_, block_bytes_;
+  size_t granularity_ = 0;   // of the physical allocation; every mapping of it is aligned to this
   CUmemGenericAllocationHandle handle_ = 0;
   CUdeviceptr va_ = 0;
   int rank_ = -1, world_size_ = 0;

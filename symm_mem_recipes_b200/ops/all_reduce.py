@@ -35,25 +35,29 @@ def _prepare(t: torch.Tensor):
 
 
 def one_shot_all_reduce(t: torch.Tensor, *, exit_barrier: bool = False,
-                        out: Optional[torch.Tensor] = None,
+                        out: Optional[torch.Tensor] = None, write_back: bool = False,
                         config: AllReduceConfig = DEFAULT_ALL_REDUCE) -> torch.Tensor:
     """Sum of `t` over all ranks, returned as a new local tensor.
 
     As upstream, there is no trailing barrier by default: do not overwrite `t`
     until every peer is known to have finished (the next collective on the same
-    group proves it), or pass `exit_barrier=True`.
+    group proves it), or pass `exit_barrier=True`.  `write_back=True` (implies
+    the exit barrier) also stores the sum into `t` once all peers have read it.
     """
     hdl, offset = _prepare(t)
     if out is None:
         out = torch.empty_like(t)
     t_ns = config.timeout_ms * 1_000_000
+    exit_barrier = exit_barrier or write_back
     if hdl.kind == "cuda":
         C.one_shot_all_reduce(hdl.native, offset, out, t.numel(), config.one_shot_max_blocks,
-                              exit_barrier, t_ns)
+                              exit_barrier, t_ns, write_back, bool(config.one_shot_stagger))
     else:
         raise_for_status(C.host_all_reduce(hdl.native, offset, out, t.numel(), 0, t_ns))
         if exit_barrier:
             hdl.barrier(channel=1, timeout_ms=config.timeout_ms)
+        if write_back:
+            t.copy_(out)
     return out
 
 
@@ -104,8 +108,7 @@ def all_reduce(t: torch.Tensor, algo: str = "auto", *,
         hdl = symm_mem.rendezvous(t)
         algo = choose_algo(t.numel() * t.element_size(), hdl.world_size, hdl.has_multicast, config)
     if algo == "one_shot":
-        out = one_shot_all_reduce(t, exit_barrier=True, config=config)
-        t.copy_(out)
+        one_shot_all_reduce(t, write_back=True, config=config)
         return t
     if algo == "two_shot":
         return two_shot_all_reduce_(t, config=config)

@@ -40,11 +40,16 @@ def _workspace(M: int, N: int, device: torch.device, group) -> torch.Tensor:
 
 
 def matmul_reduce_scatter(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None,
-                          group=None, num_sms: int = 0, timeout_ms: int = _TIMEOUT_MS) -> torch.Tensor:
+                          group=None, num_sms: int = 0, timeout_ms: int = _TIMEOUT_MS,
+                          trace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """`a` [M, K_local] (all tokens, this rank's slice of the reduction
     dimension), `b` [N, K_local]; returns this rank's [M/WS, N] rows of the sum
     over ranks, bitwise identical to what any other summation site would get
-    (fp32 sum in rank order of bf16 partials)."""
+    (fp32 sum in rank order of bf16 partials).
+
+    `trace`: optional int64 CUDA tensor [num_sms, 4]; every CTA writes its
+    %globaltimer (ns) at kernel start, after the entry barrier, when its GEMM
+    tiles are pushed, and when its share of the reduction is done."""
     if a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[1]:
         raise SymmMemError("need a[M, K] and b[N, K]")
     ws = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -59,7 +64,7 @@ def matmul_reduce_scatter(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.
     wsp = _workspace(M, N, a.device, group)
     hdl = symm_mem.rendezvous(wsp, group)
     C.matmul_reduce_scatter(a, b, out, hdl.native, num_sms or _num_sms(a.device),
-                            int(timeout_ms) * 1_000_000)
+                            int(timeout_ms) * 1_000_000, trace)
     return out
 
 

@@ -29,7 +29,9 @@ def test_world_of_one_all_paths():
     smr.barrier_test(hdl, num_blocks=32)
     hdl.barrier()
     hdl.check()
-    assert int(hdl.get_signal_pad().abs().sum()) == 0
+    from symm_mem_recipes_b200._ext import C
+    # barrier slots are back to zero; the all-reduce epoch counters beyond them only ever grow
+    assert int(hdl.get_signal_pad()[:C.FLAG_SLOTS_BASE].abs().sum()) == 0
     view = hdl.get_buffer(0, (16,), torch.bfloat16, storage_offset=64)
     assert torch.equal(view, t[64:80])
 
@@ -104,14 +106,24 @@ def _ar_worker(rank, world_size, numel):
     elif world_size > 1:
         failures.append("no multicast mapping on an NVSwitch machine")
 
+    # dispatcher: in place, whichever kernel it picks
+    hdl.barrier()
+    t.copy_(srcs[rank].to(dev))
+    hdl.barrier()
+    smr.all_reduce(t, "auto")
+    hdl.check()
+    tol = fp32.abs() * 2.0 ** -5 + 1e-2       # covers ordered-bf16 and in-switch fp32 summation
+    if not bool(((t.cpu().float() - fp32).abs() <= tol).all()):
+        failures.append("all_reduce(auto) is off")
+
     # barrier stress: the pad must be all zero afterwards
     for blocks in (1, 7, 32, 148):
         for _ in range(50):
             smr.barrier_test(hdl, num_blocks=blocks)
     hdl.barrier()
     hdl.check()
-    if int(hdl.get_signal_pad().abs().sum()) != 0:
-        failures.append("signal pad is not zero after the barrier stress")
+    if int(hdl.get_signal_pad()[:C.FLAG_SLOTS_BASE].abs().sum()) != 0:
+        failures.append("barrier slots are not zero after the barrier stress")
     hdl.barrier()
     torch.cuda.synchronize()
     assert not failures, failures
