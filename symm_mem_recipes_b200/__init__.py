@@ -8,8 +8,8 @@ instructions issued from this package's own kernels on peer-mapped memory.
 from . import errors  # noqa: F401
 from .parallel import symm_mem  # noqa: F401
 from . import ops  # noqa: F401
-from .ops import (all_reduce, barrier_test, multimem_all_reduce_, one_shot_all_reduce,  # noqa: F401
-                  two_shot_all_reduce_)
+from .ops import (all_reduce, barrier_test, low_latency_all_reduce, multimem_all_reduce_,  # noqa: F401
+                  one_shot_all_reduce, two_shot_all_reduce_)
 
 from .ops import all_gather_matmul, matmul, reference_all_gather_matmul  # noqa: F401,E402
 from .ops import gemv_all_reduce, reference_gemv_all_reduce  # noqa: F401,E402

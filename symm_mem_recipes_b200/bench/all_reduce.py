@@ -27,7 +27,7 @@ def main(argv=None, standalone: bool = True) -> int:
     ap.add_argument("--max-bytes", type=int, default=256 * 1024 * 1024)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--iters", type=int, default=50)
-    ap.add_argument("--algos", default="one_shot,two_shot,multimem,auto")
+    ap.add_argument("--algos", default="low_latency,one_shot,two_shot,multimem,auto")
     ap.add_argument("--one-shot-limit", type=int, default=8 * 1024 * 1024,
                     help="largest message timed with the one-shot kernels")
     ap.add_argument("--with-reference-triton", action="store_true")
@@ -84,7 +84,11 @@ def main(argv=None, standalone: bool = True) -> int:
         impls = {}
         impls["nccl"] = lambda: dist.all_reduce(plain[:numel])
         for a in algos:
-            if a == "one_shot" and nbytes <= args.one_shot_limit:
+            if a == "low_latency" and nbytes <= 256 * 1024 and world > 1:
+                src_ll = plain[:numel]
+                out_ll = torch.empty_like(src_ll)
+                impls["low_latency"] = lambda s_=src_ll, o_=out_ll: smr.low_latency_all_reduce(s_, out=o_, config=cfg)
+            elif a == "one_shot" and nbytes <= args.one_shot_limit:
                 out = torch.empty_like(t)
                 impls["one_shot"] = lambda out=out: smr.one_shot_all_reduce(t, out=out, config=cfg)
             elif a == "two_shot" and world > 1:

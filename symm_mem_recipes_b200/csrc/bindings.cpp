@@ -339,6 +339,22 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   }, py::arg("alloc"), py::arg("offset_bytes"), py::arg("out"), py::arg("numel"), py::arg("max_blocks"),
      py::arg("exit_barrier"), py::arg("timeout_ns"), py::arg("write_back") = false,
      py::arg("stagger") = true);
+  m.def("ll_all_reduce_workspace_bytes", &ll_all_reduce_workspace_bytes);
+  m.def("ll_all_reduce", [](const std::shared_ptr<CudaSymmAllocation>& workspace, torch::Tensor in,
+                            torch::Tensor out, int64_t capacity_numel, int max_blocks, uint64_t timeout_ns) {
+    auto okt = [](const torch::Tensor& t) {
+      return t.is_cuda() && t.is_contiguous() && t.scalar_type() == torch::kBFloat16;
+    };
+    TORCH_CHECK(okt(in) && okt(out) && in.numel() == out.numel(), "in / out must be contiguous bf16 CUDA tensors");
+    TORCH_CHECK(((uintptr_t)in.data_ptr() | (uintptr_t)out.data_ptr()) % 16 == 0, "in / out must be 16-byte aligned");
+    c10::cuda::CUDAGuard guard(workspace->device());
+    PeerView pv = view_of(*workspace);
+    TORCH_CHECK(ll_all_reduce_workspace_bytes((size_t)capacity_numel, pv.world_size) <= workspace->payload_bytes(),
+                "workspace too small");
+    rt_check(launch_ll_all_reduce(pv, in.data_ptr(), out.data_ptr(), (size_t)in.numel(), (size_t)capacity_numel,
+                                  max_blocks, timeout_ns, status_for(workspace->device()),
+                                  current_stream(workspace->device())), "ll_all_reduce");
+  });
   m.def("two_shot_all_reduce", [](const std::shared_ptr<CudaSymmAllocation>& a, int64_t offset_bytes,
                                   int64_t numel, int max_blocks, uint64_t timeout_ns) {
     c10::cuda::CUDAGuard guard(a->device());

@@ -36,6 +36,12 @@ int launch_wait_flag(const uint32_t* flag, uint32_t target, uint64_t timeout_ns,
 int launch_one_shot_all_reduce(const PeerView& pv, size_t offset_bytes, void* out, size_t numel,
                                int max_blocks, bool exit_barrier, bool write_back, bool stagger,
                                uint64_t timeout_ns, Status* status, cudaStream_t stream);
+// Low-latency (push, tagged words) all-reduce for small messages.  `pv` is the view of a
+// symmetric workspace of ll_all_reduce_workspace_bytes(capacity_numel, WS); `in` / `out` are
+// ordinary device buffers (they may be the same).
+size_t ll_all_reduce_workspace_bytes(size_t max_numel, int world_size);
+int launch_ll_all_reduce(const PeerView& pv, const void* in, void* out, size_t numel, size_t capacity_numel,
+                         int max_blocks, uint64_t timeout_ns, Status* status, cudaStream_t stream);
 int launch_two_shot_all_reduce(const PeerView& pv, size_t offset_bytes, size_t numel,
                                int max_blocks, uint64_t timeout_ns, Status* status,
                                cudaStream_t stream);

@@ -1,5 +1,5 @@
-from .all_reduce import (all_reduce, choose_algo, multimem_all_reduce_,  # noqa: F401
-                         one_shot_all_reduce, two_shot_all_reduce_)
+from .all_reduce import (all_reduce, choose_algo, low_latency_all_reduce,  # noqa: F401
+                         multimem_all_reduce_, one_shot_all_reduce, two_shot_all_reduce_)
 from .barrier import barrier_test, wait_flag  # noqa: F401
 from .ag_matmul import (AgMatmulConfig, all_gather_matmul, matmul,  # noqa: F401
                                 reference_all_gather_matmul)

@@ -17,7 +17,9 @@ from ..errors import SymmMemError, raise_for_status
 from ..parallel import symm_mem
 from .config import DEFAULT_ALL_REDUCE, AllReduceConfig
 
-_ALGOS = ("auto", "one_shot", "two_shot", "multimem")
+_ALGOS = ("auto", "low_latency", "one_shot", "two_shot", "multimem")
+_LL_CAPACITY_NUMEL = 128 * 1024          # elements: messages up to 256 KiB
+_ll_workspaces: dict[tuple, torch.Tensor] = {}
 
 
 def _prepare(t: torch.Tensor):
@@ -61,6 +63,50 @@ def one_shot_all_reduce(t: torch.Tensor, *, exit_barrier: bool = False,
     return out
 
 
+def _ll_workspace(device: torch.device, group) -> torch.Tensor:
+    """Symmetric inbox of the low-latency kernel (about 8 MiB per rank at 8
+    ranks), allocated and rendezvoused at first use: that call is collective."""
+    import torch.distributed as dist
+
+    key = (device.index, symm_mem._group_key(group))
+    w = _ll_workspaces.get(key)
+    if w is None:
+        ws = dist.get_world_size(group) if dist.is_initialized() else 1
+        w = symm_mem.empty(C.ll_all_reduce_workspace_bytes(_LL_CAPACITY_NUMEL, ws), dtype=torch.uint8,
+                           device=device)
+        symm_mem.rendezvous(w, group)
+        _ll_workspaces[key] = w
+    return w
+
+
+def low_latency_all_reduce(t: torch.Tensor, out: Optional[torch.Tensor] = None, group=None,
+                           config: AllReduceConfig = DEFAULT_ALL_REDUCE) -> torch.Tensor:
+    """All-reduce for small bf16 messages (up to 256 KiB) in one NVLink
+    crossing: every rank pushes its data, tagged with the call number, into an
+    inbox on every rank and sums what lands in its own; no barrier, no peer
+    loads.  `t` is ANY contiguous bf16 CUDA tensor (it need not be symmetric);
+    `out` defaults to a new tensor and may be `t` itself.  Same arithmetic as
+    `one_shot_all_reduce` (ordered bf16 sum), hence the same bits on all ranks.
+    No upstream counterpart."""
+    if t.dtype != torch.bfloat16 or not t.is_contiguous() or t.numel() % 8:
+        raise SymmMemError("need a contiguous bfloat16 tensor whose size is a multiple of 8")
+    if t.numel() > _LL_CAPACITY_NUMEL:
+        raise SymmMemError(f"low_latency_all_reduce handles at most {_LL_CAPACITY_NUMEL} elements")
+    if not t.is_cuda:
+        # CPU ranks: same result through the shared-memory one-shot path
+        res = one_shot_all_reduce(t, exit_barrier=True, config=config)
+        if out is None:
+            return res
+        out.copy_(res)
+        return out
+    if out is None:
+        out = torch.empty_like(t)
+    w = _ll_workspace(t.device, group)
+    hdl = symm_mem.rendezvous(w, group)
+    C.ll_all_reduce(hdl.native, t, out, _LL_CAPACITY_NUMEL, config.ll_max_blocks, config.timeout_ms * 1_000_000)
+    return out
+
+
 def two_shot_all_reduce_(t: torch.Tensor, *, config: AllReduceConfig = DEFAULT_ALL_REDUCE) -> torch.Tensor:
     """In place: rank r reduces slice r from all peers (ordered bf16 sum) and
     stores it into slice r of every peer.  Returns `t`."""
@@ -92,7 +138,11 @@ def multimem_all_reduce_(t: torch.Tensor, *, config: AllReduceConfig = DEFAULT_A
 def choose_algo(nbytes: int, world_size: int, has_multicast: bool,
                 config: AllReduceConfig = DEFAULT_ALL_REDUCE) -> str:
     """The dispatcher's decision, exposed for tests and benchmarks."""
-    if world_size == 1 or nbytes <= config.one_shot_max_bytes:
+    if world_size == 1:
+        return "one_shot"
+    if nbytes <= min(config.ll_max_bytes, _LL_CAPACITY_NUMEL * 2):
+        return "low_latency"
+    if nbytes <= config.one_shot_max_bytes:
         return "one_shot"
     return "multimem" if has_multicast else "two_shot"
 
@@ -107,6 +157,11 @@ def all_reduce(t: torch.Tensor, algo: str = "auto", *,
     if algo == "auto":
         hdl = symm_mem.rendezvous(t)
         algo = choose_algo(t.numel() * t.element_size(), hdl.world_size, hdl.has_multicast, config)
+    if algo == "low_latency":
+        if not t.is_cuda:
+            one_shot_all_reduce(t, write_back=True, config=config)
+            return t
+        return low_latency_all_reduce(t, out=t, config=config)
     if algo == "one_shot":
         one_shot_all_reduce(t, write_back=True, config=config)
         return t

@@ -16,6 +16,10 @@ def _env_int(name: str, default: int) -> int:
 @dataclass
 class AllReduceConfig:
     # Message sizes (bytes) up to which each algorithm is picked by `algo="auto"`.
+    # low-latency push kernel (tagged words, no barrier) up to this size ...
+    ll_max_bytes: int = _env_int("SMR_AR_LL_MAX_BYTES", 256 * 1024)
+    ll_max_blocks: int = _env_int("SMR_AR_LL_MAX_BLOCKS", 32)
+    # ... then one-shot (peer loads) up to this size (only when larger than ll_max_bytes)
     one_shot_max_bytes: int = _env_int("SMR_AR_ONE_SHOT_MAX_BYTES", 256 * 1024)
     # Above one-shot: multimem when a multicast mapping exists, else two-shot.
     # CTA caps.  Upstream caps its one-shot kernel at 24 CTAs of 512 threads

@@ -90,6 +90,20 @@ def _ar_worker(rank, world_size, numel):
     if not torch.equal(t.cpu().view(torch.int16), ordered.view(torch.int16)):
         failures.append("two_shot differs from the ordered-sum oracle")
 
+    # low-latency push kernel: plain (non-symmetric) input, several calls, then in place
+    n_ll = min(numel, 65536)
+    plain = srcs[rank][:n_ll].to(dev)
+    ordered_ll = C.oracle_ordered_sum_bf16([s[:n_ll] for s in srcs])
+    for _ in range(3):
+        out_ll = smr.low_latency_all_reduce(plain)
+        hdl.check()
+        if not torch.equal(out_ll.cpu().view(torch.int16), ordered_ll.view(torch.int16)):
+            failures.append("low_latency differs from the ordered-sum oracle")
+    smr.low_latency_all_reduce(plain, out=plain)
+    hdl.check()
+    if not torch.equal(plain.cpu().view(torch.int16), ordered_ll.view(torch.int16)):
+        failures.append("in-place low_latency differs from the ordered-sum oracle")
+
     if hdl.has_multicast:
         hdl.barrier()
         t.copy_(srcs[rank].to(dev))

@@ -23,8 +23,9 @@ def test_dispatcher_thresholds():
     from symm_mem_recipes_b200.ops import choose_algo
     from symm_mem_recipes_b200.ops.config import AllReduceConfig
 
-    cfg = AllReduceConfig(one_shot_max_bytes=1 << 18)
-    assert choose_algo(4096, 8, True, cfg) == "one_shot"
+    cfg = AllReduceConfig(ll_max_bytes=1 << 16, one_shot_max_bytes=1 << 18)
+    assert choose_algo(4096, 8, True, cfg) == "low_latency"
+    assert choose_algo((1 << 16) + 16, 8, True, cfg) == "one_shot"
     assert choose_algo(1 << 18, 8, True, cfg) == "one_shot"
     assert choose_algo((1 << 18) + 16, 8, True, cfg) == "multimem"
     assert choose_algo(1 << 26, 8, False, cfg) == "two_shot"
