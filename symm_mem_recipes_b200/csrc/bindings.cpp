@@ -377,7 +377,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                         std::shared_ptr<CudaSymmAllocation> shard_alloc, int64_t shard_offset,
                         std::shared_ptr<CudaSymmAllocation> aout_alloc, int64_t aout_offset,
                         c10::optional<torch::Tensor> a_out, c10::optional<torch::Tensor> flags,
-                        int block_n, int num_sms, int n_copy, uint64_t timeout_ns, bool cta_pair) {
+                        int block_n, int num_sms, int n_copy, uint64_t timeout_ns, bool cta_pair,
+                        c10::optional<torch::Tensor> tail_scratch) {
     auto ok2d = [](const torch::Tensor& t) {
       return t.is_cuda() && t.dim() == 2 && t.is_contiguous() && t.scalar_type() == torch::kBFloat16;
     };
@@ -432,12 +433,22 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       args.M = (int)a.size(0);
     }
     TORCH_CHECK(c.size(0) == args.M && c.size(1) == args.N, "c must be [M, N]");
+    if (tail_scratch.has_value() && cta_pair) {
+      // first 4 KiB: arrival counters; the rest: fp32 partial accumulators
+      TORCH_CHECK(tail_scratch->is_cuda() && tail_scratch->is_contiguous() && tail_scratch->nbytes() > 8192,
+                  "tail_scratch must be a contiguous CUDA tensor");
+      char* base = static_cast<char*>(tail_scratch->data_ptr());
+      args.tail_counters = reinterpret_cast<uint32_t*>(base);
+      args.tail_counter_slots = 1024;
+      args.tail_scratch = base + 4096;
+      args.tail_scratch_bytes = tail_scratch->nbytes() - 4096;
+    }
     rt_check(cta_pair && mode != 1 ? launch_ag_matmul_2cta(args, stream) : launch_ag_matmul(args, stream),
              "ag_matmul");
   }, py::arg("a"), py::arg("b"), py::arg("c"), py::arg("mode"), py::arg("shard_alloc"),
      py::arg("shard_offset"), py::arg("aout_alloc"), py::arg("aout_offset"), py::arg("a_out"),
      py::arg("flags"), py::arg("block_n"), py::arg("num_sms"), py::arg("n_copy"), py::arg("timeout_ns"),
-     py::arg("cta_pair") = false);
+     py::arg("cta_pair") = false, py::arg("tail_scratch") = py::none());
 
   m.def("gemv_batch_tile", &gemv_batch_tile);
   m.def("gemv_workspace_bytes", [](int batch_tile, int N, int world_size) {

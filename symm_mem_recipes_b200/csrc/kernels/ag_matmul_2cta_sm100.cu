@@ -16,6 +16,12 @@
 //   tmem_full[b]   both CTAs; same multicast commit.
 //   tmem_empty[b]  leader only, 8 arrivals: the four epilogue warps of each CTA
 //                  (the peer's arrive through a shared::cluster address).
+// Tail of the static schedule: when the last wave would fill only a few pairs
+// (896 tiles on 74 pairs leave 8), each of its tiles is cut along K into 2, 4
+// or 8 parts that run on as many pairs at once.  Every part stores its fp32
+// partial accumulator to scratch memory, bumps the tile's arrival counter,
+// waits (bounded) for the other parts and then reduces ITS share of the tile's
+// columns in part order, so the result does not depend on timing.
 // The two 128-row blocks of a pair are two consecutive positions of the M
 // schedule, not necessarily neighbours in memory: each CTA loads, waits for and
 // stores its own block.  Gather modes: none and push (see ag_matmul_sm100.cu);
@@ -100,6 +106,34 @@ struct PairSmem {
   static_assert(kStageBytes % 1024 == 0, "stage bases must stay 1024-byte aligned");
 };
 
+// The i-th piece of work of a pair: a whole tile, or one K part of a tail tile.
+struct PairWork {
+  int tile;        // index into the tile schedule
+  int kb0, kb1;    // K blocks [kb0, kb1)
+  int part;        // -1 = whole tile, else the part's index
+  int tail_idx;    // index of the tile among the tail tiles
+};
+__device__ __forceinline__ bool pair_work(const AgMatmulParams& p, int pair, int n_pairs, int total_tiles,
+                                          int k_blocks, int i, PairWork& w) {
+  const int full_tiles = total_tiles - p.tail_tiles;
+  const int t = pair + i * n_pairs;
+  if (t < full_tiles) {
+    w.tile = t; w.kb0 = 0; w.kb1 = k_blocks; w.part = -1; w.tail_idx = 0;
+    return true;
+  }
+  // at most one unit of tail work per pair, right after its whole tiles
+  const int first_tail_i = (full_tiles - pair + n_pairs - 1) / n_pairs;   // first i with t >= full_tiles
+  if (p.tail_tiles == 0 || i != first_tail_i || pair >= p.tail_tiles * p.tail_splits) return false;
+  const int per = (k_blocks + p.tail_splits - 1) / p.tail_splits;
+  w.tail_idx = pair / p.tail_splits;
+  w.part = pair - w.tail_idx * p.tail_splits;
+  w.tile = full_tiles + w.tail_idx;
+  w.kb0 = w.part * per;
+  w.kb1 = w.kb0 + per < k_blocks ? w.kb0 + per : k_blocks;
+  if (w.kb1 < w.kb0) w.kb1 = w.kb0;
+  return true;
+}
+
 template <int BN, int STAGES>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
@@ -162,7 +196,9 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
     // ---------------- TMA producer (both CTAs) ----------------
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
-      for (int t = pair; t < total_tiles && !failed; t += n_pairs) {
+      PairWork w;
+      for (int wi = 0; !failed && pair_work(p, pair, n_pairs, total_tiles, k_blocks, wi, w); ++wi) {
+        const int t = w.tile;
         const int mi = (t / p.n_tiles_n) * 2 + (int)cta_rank, ni = t % p.n_tiles_n;
         bool local = true;
         const CUtensorMap* amap = &tmap_a_out;
@@ -185,7 +221,7 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
         } else {
           row0 = p.n_blocks_m * kBM;   // odd tail: rows past M read as zero
         }
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.timeout_ns)) {
             report_status(p.status, kTimeoutMbarrier, p.rank, blockIdx.x, stage, kWhereGemmEmpty);
             failed = true;
@@ -206,7 +242,8 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
     if (leader && lane == 0) {
       constexpr uint32_t idesc = umma_idesc_bf16_f32(2 * kBM, BN);
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
-      for (int t = pair; t < total_tiles && !failed; t += n_pairs) {
+      PairWork w;
+      for (int wi = 0; !failed && pair_work(p, pair, n_pairs, total_tiles, k_blocks, wi, w); ++wi) {
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, p.timeout_ns)) {
           report_status(p.status, kTimeoutMbarrier, p.rank, blockIdx.x, acc, kWhereGemmTmemEmpty);
           failed = true;
@@ -214,7 +251,7 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
         }
         tcgen05_fence_after_thread_sync();
         const uint32_t d_tmem = tmem_base + acc * 256u;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, p.timeout_ns)) {
             report_status(p.status, kTimeoutMbarrier, p.rank, blockIdx.x, stage, kWhereGemmFull);
             failed = true;
@@ -227,7 +264,7 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
 #pragma unroll
           for (int k = 0; k < kBK / kUmmaK; ++k)
             umma_bf16_ss_pair(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc,
-                              (kb | k) != 0 ? 1u : 0u);
+                              (kb != w.kb0 || k != 0) ? 1u : 0u);
           umma_commit_pair(&empty_bar[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -245,7 +282,10 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
     int next_piece = (int)blockIdx.x, round = 0;
     const int all_pieces = p.blocks_per_rank * p.pieces;
     if (p.mode == 2 && !push_entry_barrier(p, (int)blockIdx.x, etid)) failed = true;
-    for (int t = pair; t < total_tiles && !failed; t += n_pairs) {
+    __shared__ int tail_ok;
+    PairWork w;
+    for (int wi = 0; !failed && pair_work(p, pair, n_pairs, total_tiles, k_blocks, wi, w); ++wi) {
+      const int t = w.tile;
       const int mi = (t / p.n_tiles_n) * 2 + (int)cta_rank, ni = t % p.n_tiles_n;
       bool local_unused;
       const bool valid = mi < p.n_blocks_m;
@@ -265,6 +305,67 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
       const int row = mblk * kBM + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + acc * 256u + ((uint32_t)(quarter * 32) << 16);
       __nv_bfloat16* crow = p.c + (size_t)row * p.N + (size_t)ni * BN;
+      if (w.part >= 0) {
+        // ---- split-K tail: park the fp32 partial, meet the other parts, reduce my columns ----
+        const int r = quarter * 32 + lane;
+        const size_t blk = (size_t)kBM * BN;                       // floats per CTA block
+        float* mine = p.tail_scratch + (((size_t)w.tail_idx * p.tail_splits + w.part) * 2 + cta_rank) * blk +
+                      (size_t)r * BN;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t v[32];
+          if (w.kb1 > w.kb0) {
+            tmem_ld_32x32b_x32(taddr + (uint32_t)(c * 32), v);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int q = 0; q < 32; ++q) v[q] = 0u;
+          }
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            st_16(mine + c * 32 + q * 4, Vec16{v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]});
+        }
+        tcgen05_fence_before_thread_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc]), 0));
+        __threadfence();
+        if (etid == 0) tail_ok = 1;
+        epilogue_group_sync();
+        uint32_t* counter = p.tail_counters + w.tail_idx * 2 + cta_rank;
+        if (etid == 0) {
+          red_add_release_gpu(counter, 1u);
+          if (!wait_ge_acquire_gpu(counter, (uint32_t)p.tail_splits, p.timeout_ns)) {
+            report_status(p.status, kTimeoutFlag, p.rank, blockIdx.x, w.tail_idx, kWhereGemmTmemFull, w.part);
+            tail_ok = 0;
+          }
+        }
+        epilogue_group_sync();
+        if (!tail_ok) { failed = true; break; }
+        const int cw = BN / p.tail_splits;                         // my share of the tile's columns
+        const float* base = p.tail_scratch + ((size_t)w.tail_idx * p.tail_splits * 2 + cta_rank) * blk +
+                            (size_t)r * BN + (size_t)w.part * cw;
+        for (int c8 = 0; c8 < cw; c8 += 8) {
+          float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          for (int sp = 0; sp < p.tail_splits; ++sp) {             // part order: deterministic
+            const float* src = base + (size_t)sp * 2 * blk + c8;
+            Vec16 lo = ld_16_stream(src), hi = ld_16_stream(src + 4);
+            s[0] += __uint_as_float(lo.x); s[1] += __uint_as_float(lo.y);
+            s[2] += __uint_as_float(lo.z); s[3] += __uint_as_float(lo.w);
+            s[4] += __uint_as_float(hi.x); s[5] += __uint_as_float(hi.y);
+            s[6] += __uint_as_float(hi.z); s[7] += __uint_as_float(hi.w);
+          }
+          const int col = ni * BN + w.part * cw + c8;
+          if (valid && row < p.M && col < p.N) {
+            Vec16 o;
+            o.x = pack_bf16x2(s[0], s[1]); o.y = pack_bf16x2(s[2], s[3]);
+            o.z = pack_bf16x2(s[4], s[5]); o.w = pack_bf16x2(s[6], s[7]);
+            st_16(crow + w.part * cw + c8, o);
+          }
+        }
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -381,6 +482,24 @@ int launch_ag_matmul_2cta(const AgMatmulArgs& a, cudaStream_t stream) {
   if (pairs > total_tiles) pairs = total_tiles;
   if (pairs < 1) return cudaErrorInvalidValue;
   const int grid = 2 * pairs;
+  // split-K tail: only when the last wave fills less than half of the pairs
+  p.tail_tiles = 0;
+  p.tail_splits = 1;
+  const int rem = total_tiles % pairs;
+  const int k_blocks = (a.K + kBK - 1) / kBK;
+  if (a.tail_scratch != nullptr && rem > 0 && rem * 2 <= pairs) {
+    int splits = pairs / rem;
+    splits = splits >= 8 ? 8 : (splits >= 4 ? 4 : 2);
+    const size_t need = (size_t)rem * splits * 2 * kBM * bn * sizeof(float);
+    if (k_blocks >= 2 * splits && need <= a.tail_scratch_bytes && (size_t)rem * 2 <= a.tail_counter_slots) {
+      p.tail_tiles = rem;
+      p.tail_splits = splits;
+      p.tail_scratch = static_cast<float*>(a.tail_scratch);
+      p.tail_counters = a.tail_counters;
+      cudaError_t me = cudaMemsetAsync(a.tail_counters, 0, sizeof(uint32_t) * rem * 2, stream);
+      if (me != cudaSuccess) return (int)me;
+    }
+  }
   switch (bn) {
     case 128: return launch_pair_variant<128, 8>(ta_shard, ta_out, tb, p, grid, stream);
     case 192: return launch_pair_variant<192, 7>(ta_shard, ta_out, tb, p, grid, stream);

@@ -53,6 +53,11 @@ struct AgMatmulParams {
   uint32_t barrier_block_base;     // first blockwise-barrier slot id used by copiers
   uint64_t timeout_ns;
   Status* status;
+  // split-K tail (2-CTA kernel): the tiles of the last, partly filled wave are cut along K
+  int tail_tiles;        // tiles handled that way (0 = none); they are the last ones of the schedule
+  int tail_splits;       // K parts per such tile (2, 4 or 8)
+  float* tail_scratch;   // [tail_tiles][tail_splits][2 CTAs][128 x BN] fp32 partial accumulators
+  uint32_t* tail_counters;   // [tail_tiles][2] arrivals, zeroed before the launch
 };
 
 // ---------------------------------------------------------------------------

@@ -320,8 +320,11 @@ int launch_ll_all_reduce(const PeerView& pv, const void* in, void* out, size_t n
                          int max_blocks, uint64_t timeout_ns, Status* status, cudaStream_t stream) {
   if (numel % 8 != 0 || numel > capacity_numel || capacity_numel % 8 != 0) return cudaErrorInvalidValue;
   size_t n_vec = numel / 8;
-  int blocks = blocks_for(n_vec, max_blocks);
-#define SMR_LL_CASE(n) case n: ll_all_reduce_kernel<n><<<blocks, kArThreads, 0, stream>>>( \
+  // small CTAs on many SMs: one SM sustains only ~30 GB/s of NVLink stores
+  constexpr int kLlThreads = 128;
+  size_t want = (n_vec + kLlThreads - 1) / kLlThreads;
+  int blocks = (int)(want < 1 ? 1 : (want > (size_t)max_blocks ? (size_t)max_blocks : want));
+#define SMR_LL_CASE(n) case n: ll_all_reduce_kernel<n><<<blocks, kLlThreads, 0, stream>>>( \
       pv, static_cast<const Vec16*>(in), static_cast<Vec16*>(out), n_vec, capacity_numel / 8, timeout_ns, status); break;
   switch (pv.world_size) {
     SMR_LL_CASE(1) SMR_LL_CASE(2) SMR_LL_CASE(4) SMR_LL_CASE(8)

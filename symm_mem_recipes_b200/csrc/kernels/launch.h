@@ -79,6 +79,11 @@ struct AgMatmulArgs {
   uint32_t barrier_block_base;
   uint64_t timeout_ns;
   Status* status;
+  // optional scratch of the 2-CTA kernel's split-K tail (nullptr = never split)
+  void* tail_scratch;
+  size_t tail_scratch_bytes;
+  uint32_t* tail_counters;
+  size_t tail_counter_slots;
 };
 int launch_ag_matmul(const AgMatmulArgs& args, cudaStream_t stream);
 // Same contract on CTA pairs (tcgen05 cta_group::2, 256 x BN tiles); modes 0 and 2 only.

@@ -7,14 +7,19 @@
 //  * Tiles are visited by destination rank: rank+1 first, ..., own rows last,
 //    so the links are busy from the first tile and nothing waits on the wire
 //    at the end.
-//  * Epilogue: accumulator -> bf16 -> a swizzled shared-memory strip of
-//    [128 rows x 64 columns] -> ONE TMA tensor store (cp.async.bulk.tensor,
-//    shared -> global) into the DESTINATION rank's inbox [src][row][N], through
-//    a tensor map built over that peer's memory.  Two strips alternate, so the
-//    next strip is converted while the previous one is on the wire, and whole
-//    128-byte lines cross NVLink.  A tile's arrival counter on the destination
-//    gets +1 (red.release.sys) once the tile's stores have completed, which is
-//    checked one tile later so the epilogue never waits for the wire.
+//  * Epilogue: accumulator -> bf16 -> a shared-memory strip of [128 rows x 64
+//    columns] (16 KB, 16-byte chunks XOR-swizzled by row so that the writes do
+//    not collide on banks) -> ONE bulk copy (cp.async.bulk, shared -> global)
+//    of 16 contiguous KB into the DESTINATION rank's inbox.  The inbox is
+//    internal scratch, so it is laid out strip by strip,
+//    [src][row block][N tile][strip][16 KB], exactly as the strips sit in
+//    shared memory: every store is one long contiguous write over NVLink (a
+//    row-major inbox would turn it into 128-byte fragments 16 KB apart, which
+//    measured 400 GB/s).  Two strips alternate, so the next one is converted
+//    while the previous one is on the wire.  A tile's arrival counter on the
+//    destination gets +1 (red.release.sys) once the tile's stores have
+//    completed, which is checked one tile later so the epilogue never waits
+//    for the wire.
 //  * Reduce: after its GEMM tiles every CTA takes output tiles of its own rank,
 //    waits (bounded) until WS partials have arrived, sums them in rank order in
 //    fp32 and writes bf16.  All ranks thus produce identical bits.
@@ -45,11 +50,13 @@ constexpr int kThreads = 192;
 constexpr uint32_t kTmemCols = 512;
 constexpr int kStripCols = 64;                         // columns staged at a time (128 bytes: one swizzle row)
 constexpr uint32_t kStripBytesOne = kBM * kStripCols * 2;   // 16 KB
-constexpr int kMaxWorld = 8;
+constexpr int kStripsPerTile = kBN / kStripCols;       // 4
 
-struct InboxMaps {
-  CUtensorMap m[kMaxWorld];   // m[d]: this rank's slice [M/WS, N] of rank d's inbox
-};
+// Byte offset of a strip inside an inbox: [src][row block][N tile][strip] x 16 KB
+__host__ __device__ __forceinline__ size_t strip_offset(int src, int mb, int ni, int sidx, int blocks_per_rank,
+                                                        int n_tiles_n) {
+  return ((((size_t)src * blocks_per_rank + mb) * n_tiles_n + ni) * kStripsPerTile + sidx) * kStripBytesOne;
+}
 
 struct RsParams {
   int M, N, K;
@@ -82,13 +89,6 @@ static_assert(Smem::kTotal <= 232448, "shared memory budget exceeded");
 
 __device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
-// 2-D tile shared -> global through a tensor map (which may describe a peer GPU's memory)
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int32_t x, int32_t y) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
-               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smem_src)), "r"(x), "r"(y)
-               : "memory");
-}
-
 // tile index -> destination rank, 128-row block inside the destination, N tile
 __device__ __forceinline__ void tile_coords(const RsParams& p, int t, int& dest, int& mb, int& ni) {
   const int per_dest = p.blocks_per_rank * p.n_tiles_n;
@@ -99,73 +99,80 @@ __device__ __forceinline__ void tile_coords(const RsParams& p, int t, int& dest,
   ni = rem - mb * p.n_tiles_n;
 }
 
-// Ordered fp32 sum of the WS partials of one [128 x 256] output tile.  16
-// independent 16-byte loads are in flight per thread (the phase is bound by
-// memory latency otherwise): 16 / WS output vectors at a time.  WS = 0 selects
-// the generic loop for other world sizes.
+// Ordered fp32 sum of the WS partials of one [128 x 256] output tile, read from the
+// strip-major inbox (un-doing the row XOR of the 16-byte chunks) and written row-major.
+// 16 independent 16-byte loads are in flight per thread (the phase is bound by memory
+// latency otherwise): 16 / WS output vectors at a time.  WS = 0: generic loop.
 template <int WS>
-__device__ __forceinline__ void reduce_tile(const RsParams& p, const __nv_bfloat16* inbox, int mb, int ni,
-                                            int rows_per_rank) {
+__device__ __forceinline__ void reduce_tile(const RsParams& p, const char* inbox, int mb, int ni) {
   const int n0 = ni * kBN;
-  const int vec_per_row = (min(kBN, p.N - n0)) / 8;
-  const int total = kBM * vec_per_row;
-  const size_t src_stride = (size_t)rows_per_rank * p.N;
-  if constexpr (WS == 0) {
-    for (int idx = threadIdx.x; idx < total; idx += kThreads) {
-      const int row = mb * kBM + idx / vec_per_row, cv = idx % vec_per_row;
-      const size_t off = (size_t)row * p.N + n0 + cv * 8;
-      float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      for (int src = 0; src < p.world_size; ++src) {
-        Vec16 v = ld_16_stream(inbox + (size_t)src * src_stride + off);
-        s[0] += bf16lo_to_f32(v.x); s[1] += bf16hi_to_f32(v.x);
-        s[2] += bf16lo_to_f32(v.y); s[3] += bf16hi_to_f32(v.y);
-        s[4] += bf16lo_to_f32(v.z); s[5] += bf16hi_to_f32(v.z);
-        s[6] += bf16lo_to_f32(v.w); s[7] += bf16hi_to_f32(v.w);
-      }
-      Vec16 o;
-      o.x = pack_bf16x2(s[0], s[1]); o.y = pack_bf16x2(s[2], s[3]);
-      o.z = pack_bf16x2(s[4], s[5]); o.w = pack_bf16x2(s[6], s[7]);
-      st_16(p.out + off, o);
-    }
-  } else {
-    constexpr int U = 16 / WS;
-    for (int idx0 = threadIdx.x; idx0 < total; idx0 += kThreads * U) {
-      Vec16 v[U][WS];
-      size_t off[U];
+  const int strips = min(kStripsPerTile, (p.N - n0 + kStripCols - 1) / kStripCols);
+  const int total = strips * kBM * 8;                       // 16-byte vectors of the tile
+  const size_t src_stride = (size_t)p.blocks_per_rank * p.n_tiles_n * kStripsPerTile * kStripBytesOne;
+  const char* tile_base = inbox + strip_offset(0, mb, ni, 0, p.blocks_per_rank, p.n_tiles_n);
+  // vector idx -> (strip, row, chunk): consecutive idx walk a strip's bytes in order (coalesced)
+  auto locate = [&](int idx, size_t& in_off, size_t& out_off, bool& in_range) {
+    const int sidx = idx / (kBM * 8), rem = idx - sidx * (kBM * 8);
+    const int row = rem >> 3, pos = rem & 7;                // pos: position inside the swizzled row
+    const int c = pos ^ (row & 7);                          // logical 16-byte chunk
+    in_off = (size_t)sidx * kStripBytesOne + (size_t)rem * 16;
+    const int col = n0 + sidx * kStripCols + c * 8;
+    in_range = col < p.N;
+    out_off = (size_t)(mb * kBM + row) * p.N + col;
+  };
+  constexpr int U = WS == 0 ? 1 : 16 / WS;
+  for (int idx0 = threadIdx.x; idx0 < total; idx0 += kThreads * U) {
+    Vec16 v[U][WS == 0 ? 1 : WS];
+    size_t out_off[U];
+    bool live[U];
+    float s[U][8];
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int idx = idx0 + u * kThreads;
-        const int row = mb * kBM + idx / vec_per_row, cv = idx % vec_per_row;
-        off[u] = (size_t)row * p.N + n0 + cv * 8;
-        if (idx < total) {
+    for (int u = 0; u < U; ++u) {
+      const int idx = idx0 + u * kThreads;
+      size_t in_off = 0;
+      live[u] = false;
+      if (idx < total) locate(idx, in_off, out_off[u], live[u]);
 #pragma unroll
-          for (int src = 0; src < WS; ++src) v[u][src] = ld_16_stream(inbox + (size_t)src * src_stride + off[u]);
+      for (int q = 0; q < 8; ++q) s[u][q] = 0.f;
+      if (live[u]) {
+        if constexpr (WS == 0) {
+          for (int src = 0; src < p.world_size; ++src) {
+            const Vec16 w = ld_16_stream(tile_base + (size_t)src * src_stride + in_off);
+            s[u][0] += bf16lo_to_f32(w.x); s[u][1] += bf16hi_to_f32(w.x);
+            s[u][2] += bf16lo_to_f32(w.y); s[u][3] += bf16hi_to_f32(w.y);
+            s[u][4] += bf16lo_to_f32(w.z); s[u][5] += bf16hi_to_f32(w.z);
+            s[u][6] += bf16lo_to_f32(w.w); s[u][7] += bf16hi_to_f32(w.w);
+          }
+        } else {
+#pragma unroll
+          for (int src = 0; src < WS; ++src) v[u][src] = ld_16_stream(tile_base + (size_t)src * src_stride + in_off);
         }
       }
+    }
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        if (idx0 + u * kThreads >= total) break;
-        float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int u = 0; u < U; ++u) {
+      if (!live[u]) continue;
+      if constexpr (WS != 0) {
 #pragma unroll
         for (int src = 0; src < WS; ++src) {
           const Vec16& w = v[u][src];
-          s[0] += bf16lo_to_f32(w.x); s[1] += bf16hi_to_f32(w.x);
-          s[2] += bf16lo_to_f32(w.y); s[3] += bf16hi_to_f32(w.y);
-          s[4] += bf16lo_to_f32(w.z); s[5] += bf16hi_to_f32(w.z);
-          s[6] += bf16lo_to_f32(w.w); s[7] += bf16hi_to_f32(w.w);
+          s[u][0] += bf16lo_to_f32(w.x); s[u][1] += bf16hi_to_f32(w.x);
+          s[u][2] += bf16lo_to_f32(w.y); s[u][3] += bf16hi_to_f32(w.y);
+          s[u][4] += bf16lo_to_f32(w.z); s[u][5] += bf16hi_to_f32(w.z);
+          s[u][6] += bf16lo_to_f32(w.w); s[u][7] += bf16hi_to_f32(w.w);
         }
-        Vec16 o;
-        o.x = pack_bf16x2(s[0], s[1]); o.y = pack_bf16x2(s[2], s[3]);
-        o.z = pack_bf16x2(s[4], s[5]); o.w = pack_bf16x2(s[6], s[7]);
-        st_16(p.out + off[u], o);
       }
+      Vec16 o;
+      o.x = pack_bf16x2(s[u][0], s[u][1]); o.y = pack_bf16x2(s[u][2], s[u][3]);
+      o.z = pack_bf16x2(s[u][4], s[u][5]); o.w = pack_bf16x2(s[u][6], s[u][7]);
+      st_16(p.out + out_off[u], o);
     }
   }
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
 matmul_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const __grid_constant__ InboxMaps inbox_maps, const RsParams p) {
+                 const RsParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* strip = smem + Smem::kStripOffset;
@@ -315,7 +322,9 @@ matmul_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         fence_proxy_async();                             // generic writes to smem, async-proxy read
         epilogue_sync();
         if (etid == 0) {
-          tma_store_2d(&inbox_maps.m[dest], buf, col0, mb * kBM);
+          char* dst = static_cast<char*>(p.buffers[dest]) + p.inbox_offset +
+                      strip_offset(p.rank, mb, ni, sidx, p.blocks_per_rank, p.n_tiles_n);
+          bulk_store(dst, buf, kStripBytesOne);
           bulk_commit_group();
         }
         ++strip_ctr;
@@ -360,8 +369,7 @@ matmul_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   // ---------------- reduce the tiles of this rank ----------------
   if (!failed) {
     const int my_tiles = p.blocks_per_rank * p.n_tiles_n;
-    const __nv_bfloat16* inbox = reinterpret_cast<const __nv_bfloat16*>(
-        static_cast<const char*>(p.buffers[p.rank]) + p.inbox_offset);
+    const char* inbox = static_cast<const char*>(p.buffers[p.rank]) + p.inbox_offset;
     for (int t = blockIdx.x; t < my_tiles; t += gridDim.x) {
       const int mb = t / p.n_tiles_n, ni = t - mb * p.n_tiles_n;
       bool ok = true;
@@ -371,10 +379,10 @@ matmul_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
       if (!__syncthreads_and(ok)) break;
       switch (p.world_size) {
-        case 2: reduce_tile<2>(p, inbox, mb, ni, rows_per_rank); break;
-        case 4: reduce_tile<4>(p, inbox, mb, ni, rows_per_rank); break;
-        case 8: reduce_tile<8>(p, inbox, mb, ni, rows_per_rank); break;
-        default: reduce_tile<0>(p, inbox, mb, ni, rows_per_rank); break;
+        case 2: reduce_tile<2>(p, inbox, mb, ni); break;
+        case 4: reduce_tile<4>(p, inbox, mb, ni); break;
+        case 8: reduce_tile<8>(p, inbox, mb, ni); break;
+        default: reduce_tile<0>(p, inbox, mb, ni); break;
       }
     }
   }
@@ -405,22 +413,12 @@ int make_tmap(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, 
   return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
-// [rows, cols] bf16 destination with a [128 rows x 64 cols] swizzled box
-int make_store_tmap(CUtensorMap* map, void* base, uint64_t rows, uint64_t cols) {
-  const DriverApi& d = DriverApi::get();
-  cuuint64_t dims[2] = {cols, rows};
-  cuuint64_t strides[1] = {cols * 2};
-  cuuint32_t box[2] = {(cuuint32_t)kStripCols, (cuuint32_t)kBM};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = d.cuTensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, estr,
-                                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                        CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : 1;
-}
-
 }  // namespace
 
-size_t matmul_rs_workspace_bytes(int M, int N) { return (size_t)M * N * 2; }
+size_t matmul_rs_workspace_bytes(int M, int N) {
+  // strip-major inbox: every [128 x 256] tile occupies four 16 KB strips, also at the N edge
+  return (size_t)((M + kBM - 1) / kBM) * ((N + kBN - 1) / kBN) * kStripsPerTile * kStripBytesOne;
+}
 
 int launch_matmul_reduce_scatter(const MatmulRsArgs& a, cudaStream_t stream) {
   const int ws = a.pv.world_size;
@@ -442,21 +440,13 @@ int launch_matmul_reduce_scatter(const MatmulRsArgs& a, cudaStream_t stream) {
   CUtensorMap ta, tb;
   if (make_tmap(&ta, a.a, (uint64_t)a.M, (uint64_t)a.K, kBM)) return cudaErrorInvalidValue;
   if (make_tmap(&tb, a.b, (uint64_t)a.N, (uint64_t)a.K, kBN)) return cudaErrorInvalidValue;
-  if (ws > kMaxWorld) return cudaErrorInvalidValue;
-  InboxMaps maps{};
-  const size_t slice_bytes = (size_t)(a.M / ws) * a.N * 2;
-  for (int d = 0; d < ws; ++d) {
-    // this rank's slice of rank d's inbox, as mapped into this process
-    char* base = static_cast<char*>(a.peer_base[d]) + a.inbox_offset + (size_t)p.rank * slice_bytes;
-    if (make_store_tmap(&maps.m[d], base, (uint64_t)(a.M / ws), (uint64_t)a.N)) return cudaErrorInvalidValue;
-  }
   int total_tiles = ws * p.blocks_per_rank * p.n_tiles_n;
   int grid = a.num_sms < total_tiles ? a.num_sms : total_tiles;
   if (grid < 1 || (uint32_t)(1024 + grid) * (uint32_t)ws > kBlockSlots) return cudaErrorInvalidValue;
   cudaError_t e = cudaFuncSetAttribute(matmul_rs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)Smem::kTotal);
   if (e != cudaSuccess) return (int)e;
-  matmul_rs_kernel<<<grid, kThreads, Smem::kTotal, stream>>>(ta, tb, maps, p);
+  matmul_rs_kernel<<<grid, kThreads, Smem::kTotal, stream>>>(ta, tb, p);
   return (int)cudaGetLastError();
 }
 

@@ -39,11 +39,28 @@ class AgMatmulConfig:
     num_sms: int = _env_int("SMR_AGMM_NUM_SMS", 0)        # 0 = all SMs of the device
     # tcgen05 cta_group::2: two SMs share a 256 x BLOCK_N tile (not used by the pull mode)
     cta_pair: bool = bool(_env_int("SMR_AGMM_CTA_PAIR", 1))
+    # cut the tiles of a thinly filled last wave along K (2-CTA kernel only)
+    split_k_tail: bool = bool(_env_int("SMR_AGMM_SPLIT_K_TAIL", 1))
     timeout_ms: int = _env_int("SMR_TIMEOUT_MS", 10000)
 
 
 DEFAULT_CONFIG = AgMatmulConfig()
 _sm_count: dict[int, int] = {}
+_tail_scratch: dict[int, torch.Tensor] = {}
+_TAIL_SCRATCH_BYTES = 4096 + 37 * 8 * 2 * 128 * 256 * 4     # counters + the largest tail (37 tiles x 8 parts)
+
+
+def _tail_buffer(device: torch.device, config: "AgMatmulConfig"):
+    """Scratch of the split-K tail (fp32 partial accumulators), one per device."""
+    if not (config.cta_pair and config.split_k_tail):
+        return None
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    t = _tail_scratch.get(idx)
+    if t is None:
+        t = torch.empty(_TAIL_SCRATCH_BYTES, dtype=torch.uint8, device=device)
+        _tail_scratch[idx] = t
+    return t
+
 _flags: dict[int, torch.Tensor] = {}
 
 
@@ -84,7 +101,7 @@ def matmul(a: torch.Tensor, b: torch.Tensor, c_out: Optional[torch.Tensor] = Non
     sms = config.num_sms or _num_sms(a.device)
     bn = config.block_n or choose_block_n(M, N, sms, config.cta_pair)
     C.ag_matmul(a, b, c_out, 0, None, 0, None, 0, None, None, bn, sms, 0, config.timeout_ms * 1_000_000,
-                config.cta_pair)
+                config.cta_pair, _tail_buffer(a.device, config))
     return c_out
 
 
@@ -155,7 +172,7 @@ def all_gather_matmul(a_shard: torch.Tensor, b: torch.Tensor, a_out: Optional[to
         if aout_offset % 16:
             raise SymmMemError("a_out must start on a 16-byte boundary of its allocation")
         C.ag_matmul(a_shard, b, c_out, 2, None, 0, hdl.native, aout_offset, a_out, None,
-                    bn, sms, n_copy, t_ns, config.cta_pair)
+                    bn, sms, n_copy, t_ns, config.cta_pair, _tail_buffer(a_shard.device, config))
         return c_out
     n_copy = max(1, min(config.n_copy, sms // 4))
     bn = config.block_n or choose_block_n(M, N, sms - n_copy)

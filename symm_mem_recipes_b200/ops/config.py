@@ -17,8 +17,8 @@ def _env_int(name: str, default: int) -> int:
 class AllReduceConfig:
     # Message sizes (bytes) up to which each algorithm is picked by `algo="auto"`.
     # low-latency push kernel (tagged words, no barrier) up to this size ...
-    ll_max_bytes: int = _env_int("SMR_AR_LL_MAX_BYTES", 256 * 1024)
-    ll_max_blocks: int = _env_int("SMR_AR_LL_MAX_BLOCKS", 32)
+    ll_max_bytes: int = _env_int("SMR_AR_LL_MAX_BYTES", 128 * 1024)
+    ll_max_blocks: int = _env_int("SMR_AR_LL_MAX_BLOCKS", 128)
     # ... then one-shot (peer loads) up to this size (only when larger than ll_max_bytes)
     one_shot_max_bytes: int = _env_int("SMR_AR_ONE_SHOT_MAX_BYTES", 256 * 1024)
     # Above one-shot: multimem when a multicast mapping exists, else two-shot.
@@ -26,7 +26,7 @@ class AllReduceConfig:
     # (triton_one_shot_all_reduce.py:97-109); large messages want more.
     one_shot_max_blocks: int = _env_int("SMR_AR_ONE_SHOT_MAX_BLOCKS", 32)
     two_shot_max_blocks: int = _env_int("SMR_AR_TWO_SHOT_MAX_BLOCKS", 128)
-    multimem_max_blocks: int = _env_int("SMR_AR_MULTIMEM_MAX_BLOCKS", 32)
+    multimem_max_blocks: int = _env_int("SMR_AR_MULTIMEM_MAX_BLOCKS", 16)
     # one-shot: rank r starts its peer loads at rank r+1 (0 = every rank starts at rank 0, as upstream)
     one_shot_stagger: int = _env_int("SMR_AR_ONE_SHOT_STAGGER", 1)
     timeout_ms: int = _env_int("SMR_TIMEOUT_MS", 10000)

@@ -36,6 +36,33 @@ def test_matmul_small(block_n, shape, cta_pair):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("shape,num_sms", [((768, 768, 1024), 8), ((1280, 512, 512), 8), ((768, 768, 4096), 8),
+                                           ((16384, 3584, 1024), 0)])
+def test_matmul_split_k_tail(shape, num_sms):
+    """Tile counts that leave a thin last wave: its tiles are cut along K and
+    reduced through scratch memory; the result must not differ from the plain
+    schedule by more than summation order."""
+    from symm_mem_recipes_b200.ops.ag_matmul import AgMatmulConfig, matmul
+    from symm_mem_recipes_b200.parallel import symm_mem
+
+    M, N, K = shape
+    torch.manual_seed(M + N + K)
+    a = (torch.randn(M, K, device="cuda") * 0.5).to(torch.bfloat16)
+    b = (torch.randn(N, K, device="cuda") * 0.5).to(torch.bfloat16)
+    outs = []
+    for split in (True, False):
+        c = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        for _ in range(2):       # second call reuses the scratch and its counters
+            matmul(a, b, c, AgMatmulConfig(num_sms=num_sms, split_k_tail=split, timeout_ms=2000))
+        symm_mem.check_status("cuda")
+        outs.append(c)
+    ok, err = _close(outs[0], _ref(a, b), K)
+    assert ok, f"split-K tail: max abs error {err}"
+    ok, err = _close(outs[1], _ref(a, b), K)
+    assert ok, f"plain schedule: max abs error {err}"
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("cta_pair", [False, True])
 def test_matmul_llama70b_shape_vs_cublas(cta_pair):
     from symm_mem_recipes_b200.ops.ag_matmul import AgMatmulConfig, matmul

@@ -44,7 +44,8 @@ def test_gemv_workspace_sizes_grow_with_world():
     a = C.gemv_tc_workspace_bytes(8192, 3584, 1, 148)
     b = C.gemv_tc_workspace_bytes(8192, 3584, 8, 148)
     assert b > a > 0
-    assert C.matmul_rs_workspace_bytes(32768, 8192) == 32768 * 8192 * 2
+    assert C.matmul_rs_workspace_bytes(32768, 8192) == 32768 * 8192 * 2      # strip-major, no padding here
+    assert C.matmul_rs_workspace_bytes(256, 328) == 2 * 2 * 4 * 16384          # padded to whole tiles
 
 
 def test_status_decoding():
