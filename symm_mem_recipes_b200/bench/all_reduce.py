@@ -68,6 +68,34 @@ def main(argv=None, standalone: bool = True) -> int:
 
     lines = []
 
+    # correctness gate before timing: every kernel against NCCL at two sizes
+    if world > 1:
+        for check_numel in (4096, 1 << 20):
+            if check_numel > max_numel:
+                continue
+            torch.manual_seed(7 + rank)
+            ref_in = torch.randn(check_numel, device=dev).to(torch.bfloat16)
+            ref = ref_in.clone()
+            dist.all_reduce(ref)
+            tc = buf[:check_numel]
+            results = {}
+            tc.copy_(ref_in); hdl.barrier(); results["one_shot"] = smr.one_shot_all_reduce(tc, exit_barrier=True)
+            tc.copy_(ref_in); hdl.barrier(); results["two_shot"] = smr.two_shot_all_reduce_(tc).clone()
+            if hdl.has_multicast:
+                hdl.barrier(); tc.copy_(ref_in); hdl.barrier()
+                results["multimem"] = smr.multimem_all_reduce_(tc).clone()
+            if check_numel * 2 <= 256 * 1024:
+                results["low_latency"] = smr.low_latency_all_reduce(ref_in)
+            hdl.barrier()
+            hdl.check()
+            scale = float(ref.float().abs().max())
+            for name, got in results.items():
+                err = float((got.float() - ref.float()).abs().max()) / scale
+                if rank == 0:
+                    print(json.dumps({"op": "all_reduce_check", "impl": name, "numel": check_numel,
+                                      "max_rel_err_vs_nccl": round(err, 5), "ok": err < 2e-2}), flush=True)
+        buf.normal_()
+
     def emit(rec):
         if rank == 0:
             s = json.dumps(rec)

@@ -17,10 +17,10 @@ def _env_int(name: str, default: int) -> int:
 class AllReduceConfig:
     # Message sizes (bytes) up to which each algorithm is picked by `algo="auto"`.
     # low-latency push kernel (tagged words, no barrier) up to this size ...
-    ll_max_bytes: int = _env_int("SMR_AR_LL_MAX_BYTES", 128 * 1024)
+    ll_max_bytes: int = _env_int("SMR_AR_LL_MAX_BYTES", 256 * 1024)
     ll_max_blocks: int = _env_int("SMR_AR_LL_MAX_BLOCKS", 128)
     # ... then one-shot (peer loads) up to this size (only when larger than ll_max_bytes)
-    one_shot_max_bytes: int = _env_int("SMR_AR_ONE_SHOT_MAX_BYTES", 256 * 1024)
+    one_shot_max_bytes: int = _env_int("SMR_AR_ONE_SHOT_MAX_BYTES", 0)
     # Above one-shot: multimem when a multicast mapping exists, else two-shot.
     # CTA caps.  Upstream caps its one-shot kernel at 24 CTAs of 512 threads
     # (triton_one_shot_all_reduce.py:97-109); large messages want more.
