@@ -30,6 +30,9 @@ def main(argv=None, standalone: bool = True) -> int:
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--iters", type=int, default=25)
     ap.add_argument("--out", default=None)
+    ap.add_argument("--print-ptxas", "--print_ptx", dest="print_ptxas", action="store_true",
+                    help="print what the compiler made of the kernels (registers, spills, shared memory from "
+                         "`ptxas -v`); upstream's --print_ptx dumps Triton's PTX at this point")
     args = ap.parse_args(argv)
 
     from symm_mem_recipes_b200.bench._common import finish, init_distributed
@@ -86,6 +89,9 @@ def main(argv=None, standalone: bool = True) -> int:
         us = benchmark_with_event(lambda: smr.all_gather_matmul(a_shard, b, a_out_plain, c, cfg), **bench)
         emit("smr_fused", us, copy_ctas=n_copy, gather="pull")
         symm_mem.check_status(dev)
+    if args.print_ptxas and rank == 0:
+        from symm_mem_recipes_b200 import _build
+        print(_build.ptxas_report())
     if args.out and rank == 0:
         with open(args.out, "a") as f:
             f.write("\n".join(lines) + "\n")

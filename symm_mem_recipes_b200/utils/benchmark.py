@@ -90,9 +90,11 @@ def benchmark_with_event(target_fn: Callable[[], None], warmup_iters: int = 200,
 def benchmark_with_profiler(target_fn: Callable[[], None], event_key_regex: str,
                             warmup_iters: int = 200, benchmark_iters: int = 25,
                             profile_ranks: Optional[Sequence[int]] = None,
-                            flush_l2: bool = False) -> float:
+                            flush_l2: bool = False, trace_handler=None) -> float:
     """Median device time (µs) of the kernels whose name matches
-    `event_key_regex`; ranks outside `profile_ranks` (default [0]) return 0."""
+    `event_key_regex`; ranks outside `profile_ranks` (default [0]) return 0.
+    `trace_handler(prof)` is passed to the profiler as `on_trace_ready`
+    (upstream imports an optional `trace_handler` module for this, utils.py:41-44)."""
     flush = globals()["flush_l2"] if flush_l2 else None
     rank = dist.get_rank() if dist.is_initialized() else 0
     if profile_ranks is None:
@@ -110,7 +112,7 @@ def benchmark_with_profiler(target_fn: Callable[[], None], event_key_regex: str,
         return 0.0
     from torch.profiler import ProfilerActivity, profile
 
-    with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA]) as prof:
+    with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA], on_trace_ready=trace_handler) as prof:
         torch.cuda._sleep(int(2e7))   # queue the launches behind a busy GPU (upstream :64)
         for _ in range(benchmark_iters):
             if flush is not None:
