@@ -482,6 +482,8 @@ int launch_ag_matmul_2cta(const AgMatmulArgs& a, cudaStream_t stream) {
   if (pairs > total_tiles) pairs = total_tiles;
   if (pairs < 1) return cudaErrorInvalidValue;
   const int grid = 2 * pairs;
+  // the entry barrier of CTA i uses block slot (barrier_block_base + i): it must stay inside the block-slot region
+  if (comm && ((size_t)a.barrier_block_base + grid) * a.world_size > kBlockSlots) return cudaErrorInvalidValue;
   // split-K tail: only when the last wave fills less than half of the pairs
   p.tail_tiles = 0;
   p.tail_splits = 1;

@@ -7,7 +7,7 @@
 // order shards arrive, own shard first, :157-174).  How it does it is specific
 // to Blackwell:
 //
-//  * grid = n_copy "copier" CTAs + (SMs - n_copy) GEMM CTAs, one per SM.
+//  * grid = one GEMM CTA per SM (in pull mode n_copy of them are "copier" CTAs instead).
 //  * PUSH mode (a_out in symmetric memory; the default): no SM is set aside
 //    for communication.  Every rank broadcasts its OWN shard into the a_out
 //    of all ranks with `multimem.st` on the NVLink multicast address, so a
@@ -22,14 +22,16 @@
 //    stores (measured); spread over 148 SMs the gather costs no SM at all.
 //    After a piece, the block's arrival counter on every rank gets +1
 //    (red.release.sys); the counter of call number e reads pieces * e, so
-//    nothing is reset between calls.  An entry barrier over the signal pad, run by
-//    the epilogue warps, proves that every rank has finished reading the a_out
-//    of the previous call.
-//  * PULL mode (a_out is an ordinary tensor, as upstream): n_copy copier
-//    CTAs are set aside; in each, one thread pulls the peers' shards with untiled TMA bulk copies peer-HBM ->
-//    shared memory -> local a_out and publishes one flag per block once its
-//    writes are done; entry barrier = the peers' shards are ready, exit
-//    barrier = they may be overwritten (upstream :56, :250).
+//    nothing is reset between calls.  An entry barrier over the signal pad,
+//    run by the epilogue warps, proves that every rank has finished reading
+//    the a_out of the previous call.
+//  * PULL mode (a_out is an ordinary tensor, as upstream): n_copy copier CTAs
+//    are set aside; in each, one thread pulls the peers' shards with untiled
+//    TMA bulk copies peer-HBM -> shared memory -> local a_out and publishes
+//    one flag per block once its writes are done; entry barrier = the peers'
+//    shards are ready, exit barrier = they may be overwritten (upstream :56,
+//    :250).  One SM moves only ~14 GB/s this way (measured), so this mode
+//    needs many copier CTAs and is slower than the push mode.
 //  * M schedule: a few blocks of the own shard first (they never wait and
 //    cover the start-up of the gather), then, for k = 0, 1, ...: block k of
 //    rank+1, rank+2, ... and one more own block (upstream pivots by rank,
@@ -469,6 +471,8 @@ int launch_ag_matmul(const AgMatmulArgs& a, cudaStream_t stream) {
   if (gemm_ctas < 1) return cudaErrorInvalidValue;
   if (gemm_ctas > total_tiles) gemm_ctas = total_tiles;
   int grid = gemm_ctas + p.n_copy;
+  // the entry barriers use block slots (barrier_block_base + CTA index): stay inside the block-slot region
+  if (comm && ((size_t)a.barrier_block_base + grid) * a.world_size > kBlockSlots) return cudaErrorInvalidValue;
 
   switch (bn) {
     case 128: return launch_variant<128, 6>(ta_shard, ta_out, tb, p, grid, stream);
