@@ -2,7 +2,7 @@
 (start-up of a torchrun job costs more than most of the benchmarks).
 
     torchrun --nnodes 1 --nproc-per-node 8 --master-addr 127.0.0.1 \
-        -m symm_mem_recipes_b200.bench.suite --out-dir gpurun_out --tag ws8
+        -m symm_mem_recipes_b200.bench.suite --out-dir results --tag ws8
 """
 from __future__ import annotations
 

@@ -418,7 +418,7 @@ template <int BN, int STAGES>
 int launch_pair_variant(const CUtensorMap& ta_shard, const CUtensorMap& ta_out, const CUtensorMap& tb,
                         const AgMatmulParams& p, int grid, cudaStream_t stream) {
   using L = PairSmem<BN, STAGES>;
-  static_assert(L::kTotal <= 232448, "shared memory budget exceeded");
+  static_assert(L::kTotal <= 232448, "shared memory limit exceeded");
   auto kern = ag_matmul_2cta_kernel<BN, STAGES>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::kTotal);
   if (e != cudaSuccess) return (int)e;

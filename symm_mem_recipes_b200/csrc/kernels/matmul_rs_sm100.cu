@@ -85,7 +85,7 @@ struct Smem {
   static constexpr uint32_t kMiscOffset = kBarOffset + 8 * kNumBars;
   static constexpr uint32_t kTotal = kMiscOffset + 16 + 1024;
 };
-static_assert(Smem::kTotal <= 232448, "shared memory budget exceeded");
+static_assert(Smem::kTotal <= 232448, "shared memory limit exceeded");
 
 __device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
