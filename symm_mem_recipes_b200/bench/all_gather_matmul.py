@@ -26,6 +26,13 @@ def main(argv=None, standalone: bool = True) -> int:
     ap.add_argument("--N", type=int, default=6656)
     ap.add_argument("--K", type=int, default=16384)
     ap.add_argument("--BLOCK_SIZE_N", "--block-n", dest="block_n", type=int, default=0)
+    # accepted for command-line compatibility with the upstream driver (:330-339); the M tile (128 per
+    # CTA), the K tile (64), the stage count and the warp roles are fixed by the kernel design
+    ap.add_argument("--BLOCK_SIZE_M", type=int, default=128, help="fixed: 128 rows per CTA (256 per CTA pair)")
+    ap.add_argument("--BLOCK_SIZE_K", type=int, default=64, help="fixed: one 128-byte swizzle row")
+    ap.add_argument("--GROUP_SIZE_M", type=int, default=1, help="ignored: tiles are scheduled N-fastest")
+    ap.add_argument("--num_stages", type=int, default=0, help="ignored: follows from the tile (4-8 stages)")
+    ap.add_argument("--num_warps", type=int, default=6, help="fixed: TMA, MMA and four epilogue warps")
     ap.add_argument("--copy-ctas", default="", help="pull mode: comma-separated copier-CTA counts to time")
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--iters", type=int, default=25)

@@ -68,6 +68,15 @@ def main(argv=None, standalone: bool = True) -> int:
 
     lines = []
 
+    # the upstream driver's own check (triton_one_shot_all_reduce.py:145-154): all ones in, world size out
+    ones = buf[:8192]
+    ones.fill_(1)
+    hdl.barrier()
+    ones_ok = bool(smr.one_shot_all_reduce(ones, exit_barrier=True).eq(world).all())
+    hdl.check()
+    if rank == 0:
+        print(json.dumps({"op": "all_reduce_check", "impl": "one_shot", "input": "ones[8192]",
+                          "output_equals_world_size": ones_ok}), flush=True)
     # correctness gate before timing: every kernel against NCCL at two sizes
     if world > 1:
         for check_numel in (4096, 1 << 20):
