@@ -450,6 +450,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
      py::arg("flags"), py::arg("block_n"), py::arg("num_sms"), py::arg("n_copy"), py::arg("timeout_ns"),
      py::arg("cta_pair") = false, py::arg("tail_scratch") = py::none());
 
+  m.def("check_push_schedule", &check_push_schedule);
+  m.def("check_pair_work", &check_pair_work);
   m.def("gemv_batch_tile", &gemv_batch_tile);
   m.def("gemv_workspace_bytes", [](int batch_tile, int N, int world_size) {
     return gemv_workspace_bytes(batch_tile, N, world_size, nullptr, nullptr, nullptr);

@@ -106,34 +106,6 @@ struct PairSmem {
   static_assert(kStageBytes % 1024 == 0, "stage bases must stay 1024-byte aligned");
 };
 
-// The i-th piece of work of a pair: a whole tile, or one K part of a tail tile.
-struct PairWork {
-  int tile;        // index into the tile schedule
-  int kb0, kb1;    // K blocks [kb0, kb1)
-  int part;        // -1 = whole tile, else the part's index
-  int tail_idx;    // index of the tile among the tail tiles
-};
-__device__ __forceinline__ bool pair_work(const AgMatmulParams& p, int pair, int n_pairs, int total_tiles,
-                                          int k_blocks, int i, PairWork& w) {
-  const int full_tiles = total_tiles - p.tail_tiles;
-  const int t = pair + i * n_pairs;
-  if (t < full_tiles) {
-    w.tile = t; w.kb0 = 0; w.kb1 = k_blocks; w.part = -1; w.tail_idx = 0;
-    return true;
-  }
-  // at most one unit of tail work per pair, right after its whole tiles
-  const int first_tail_i = (full_tiles - pair + n_pairs - 1) / n_pairs;   // first i with t >= full_tiles
-  if (p.tail_tiles == 0 || i != first_tail_i || pair >= p.tail_tiles * p.tail_splits) return false;
-  const int per = (k_blocks + p.tail_splits - 1) / p.tail_splits;
-  w.tail_idx = pair / p.tail_splits;
-  w.part = pair - w.tail_idx * p.tail_splits;
-  w.tile = full_tiles + w.tail_idx;
-  w.kb0 = w.part * per;
-  w.kb1 = w.kb0 + per < k_blocks ? w.kb0 + per : k_blocks;
-  if (w.kb1 < w.kb0) w.kb1 = w.kb0;
-  return true;
-}
-
 template <int BN, int STAGES>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,

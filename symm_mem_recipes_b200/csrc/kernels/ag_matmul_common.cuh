@@ -137,7 +137,7 @@ __device__ inline int push_pieces(const AgMatmulParams& p, int next, int n_ctas,
 //   mi < lead                      own block mi
 //   then groups k = 0 .. : block k of rank+1 .. rank+WS-1, then own block
 //   lead + k while own blocks remain.
-__device__ __forceinline__ int scheduled_block(const AgMatmulParams& p, int mi, bool& local) {
+__host__ __device__ __forceinline__ int scheduled_block(const AgMatmulParams& p, int mi, bool& local) {
   if (p.mode == 0) {
     local = true;
     return mi;
@@ -170,7 +170,7 @@ __device__ __forceinline__ int scheduled_block(const AgMatmulParams& p, int mi, 
 // the static schedule): all pieces of the remote blocks those tiles read.
 // `n_units` tiles run concurrently (CTAs, or CTA pairs); a tile covers
 // `pos_per_tile` consecutive schedule positions (1, or 2 for a CTA pair).
-__device__ __forceinline__ int pieces_needed_through_round(const AgMatmulParams& p, int round,
+__host__ __device__ __forceinline__ int pieces_needed_through_round(const AgMatmulParams& p, int round,
                                                            int n_units, int pos_per_tile = 1) {
   const int ws = p.world_size, bpr = p.blocks_per_rank;
   long long tiles = (long long)(round + 1) * n_units;
@@ -182,6 +182,35 @@ __device__ __forceinline__ int pieces_needed_through_round(const AgMatmulParams&
   int k_max = q < full * ws ? q / ws : full + (q - full * ws) / (ws - 1);
   if (k_max >= bpr) k_max = bpr - 1;
   return (k_max + 1) * p.pieces;
+}
+
+// The i-th piece of work of a CTA pair in the 2-CTA kernel: a whole tile, or
+// one K part of a tile of the split-K tail.
+struct PairWork {
+  int tile;        // index into the tile schedule
+  int kb0, kb1;    // K blocks [kb0, kb1)
+  int part;        // -1 = whole tile, else the part's index
+  int tail_idx;    // index of the tile among the tail tiles
+};
+__host__ __device__ __forceinline__ bool pair_work(const AgMatmulParams& p, int pair, int n_pairs,
+                                                   int total_tiles, int k_blocks, int i, PairWork& w) {
+  const int full_tiles = total_tiles - p.tail_tiles;
+  const int t = pair + i * n_pairs;
+  if (t < full_tiles) {
+    w.tile = t; w.kb0 = 0; w.kb1 = k_blocks; w.part = -1; w.tail_idx = 0;
+    return true;
+  }
+  // at most one unit of tail work per pair, right after its whole tiles
+  const int first_tail_i = (full_tiles - pair + n_pairs - 1) / n_pairs;   // first i with t >= full_tiles
+  if (p.tail_tiles == 0 || i != first_tail_i || pair >= p.tail_tiles * p.tail_splits) return false;
+  const int per = (k_blocks + p.tail_splits - 1) / p.tail_splits;
+  w.tail_idx = pair / p.tail_splits;
+  w.part = pair - w.tail_idx * p.tail_splits;
+  w.tile = full_tiles + w.tail_idx;
+  w.kb0 = w.part * per;
+  w.kb1 = w.kb0 + per < k_blocks ? w.kb0 + per : k_blocks;
+  if (w.kb1 < w.kb0) w.kb1 = w.kb0;
+  return true;
 }
 
 // row-major bf16 [rows, cols] with a [box_rows x 64] box and 128-byte swizzle

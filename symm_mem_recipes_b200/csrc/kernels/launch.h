@@ -89,6 +89,11 @@ int launch_ag_matmul(const AgMatmulArgs& args, cudaStream_t stream);
 // Same contract on CTA pairs (tcgen05 cta_group::2, 256 x BN tiles); modes 0 and 2 only.
 int launch_ag_matmul_2cta(const AgMatmulArgs& args, cudaStream_t stream);
 
+// Host-side checks of the kernels' scheduling arithmetic (schedule_check.cu); 0 = invariants hold.
+int check_push_schedule(int world_size, int rank, int blocks_per_rank, int n_tiles_n, int n_units,
+                        int pos_per_tile, int pieces);
+int check_pair_work(int total_tiles, int n_pairs, int k_blocks, int tail_tiles, int tail_splits);
+
 // ---- fused GEMV + all-reduce (decode) -------------------------------------
 struct GemvArgs {
   const void* x;      // [batch, K] bf16, batch <= 16

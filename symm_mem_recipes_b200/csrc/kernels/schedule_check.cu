@@ -1,0 +1,83 @@
+// Host-side self-checks of the scheduling arithmetic that the fused kernels
+// rely on for progress: the M schedule, the just-in-time push of the own
+// shard, and the split-K tail.  The functions under test are the very ones
+// the kernels call (`__host__ __device__` in ag_matmul_common.cuh); the checks
+// run on the CPU and need no GPU.
+#include <vector>
+
+#include "ag_matmul_common.cuh"
+
+namespace smr {
+
+using namespace agmm;
+
+// 0 = all invariants hold, otherwise a code saying which one failed:
+//  1 the M schedule is not a permutation of the blocks / `local` is wrong
+//  2 a tile could wait for a piece that no CTA has been told to push yet
+//  3 not every piece is pushed by the end
+int check_push_schedule(int world_size, int rank, int blocks_per_rank, int n_tiles_n, int n_units,
+                        int pos_per_tile, int pieces) {
+  AgMatmulParams p{};
+  p.mode = 2;
+  p.world_size = world_size;
+  p.rank = rank;
+  p.blocks_per_rank = blocks_per_rank;
+  p.n_blocks_m = world_size * blocks_per_rank;
+  p.n_tiles_n = n_tiles_n;
+  p.lead = blocks_per_rank < 4 ? blocks_per_rank : 4;
+  p.pieces = pieces;
+  // 1. permutation + locality
+  std::vector<int> seen(p.n_blocks_m, 0);
+  for (int mi = 0; mi < p.n_blocks_m; ++mi) {
+    bool local = false;
+    int blk = scheduled_block(p, mi, local);
+    if (blk < 0 || blk >= p.n_blocks_m || seen[blk]++) return 1;
+    if (local != (blk / blocks_per_rank == rank)) return 1;
+  }
+  // 2. before any CTA blocks in the epilogue of round j, every piece of every remote block that a tile
+  //    of rounds <= j reads has been assigned for pushing (pieces with index < the limit of round j)
+  const int m_tiles = (p.n_blocks_m + pos_per_tile - 1) / pos_per_tile;
+  const int total_tiles = m_tiles * n_tiles_n;
+  const int rounds = (total_tiles + n_units - 1) / n_units;
+  for (int j = 0; j < rounds; ++j) {
+    const int limit = pieces_needed_through_round(p, j + 1, n_units, pos_per_tile);
+    const long long t_end = (long long)(j + 1) * n_units;
+    for (int t = 0; t < total_tiles && t < t_end; ++t) {
+      for (int c = 0; c < pos_per_tile; ++c) {
+        const int mi = (t / n_tiles_n) * pos_per_tile + c;
+        if (mi >= p.n_blocks_m) continue;
+        bool local = false;
+        const int blk = scheduled_block(p, mi, local);
+        if (local) continue;
+        const int k = blk % blocks_per_rank;          // index of the block inside its shard
+        if ((k + 1) * pieces > limit) return 2;
+      }
+    }
+  }
+  // 3. the last limit covers the whole shard
+  if (pieces_needed_through_round(p, rounds, n_units, pos_per_tile) < blocks_per_rank * pieces) return 3;
+  return 0;
+}
+
+// 0 = every (tile, K block) is computed exactly once and every pair gets at most one tail unit.
+int check_pair_work(int total_tiles, int n_pairs, int k_blocks, int tail_tiles, int tail_splits) {
+  AgMatmulParams p{};
+  p.tail_tiles = tail_tiles;
+  p.tail_splits = tail_splits;
+  std::vector<int> cover((size_t)total_tiles * k_blocks, 0);
+  for (int pair = 0; pair < n_pairs; ++pair) {
+    int tail_units = 0;
+    PairWork w;
+    for (int i = 0; pair_work(p, pair, n_pairs, total_tiles, k_blocks, i, w); ++i) {
+      if (w.tile < 0 || w.tile >= total_tiles || w.kb0 < 0 || w.kb1 > k_blocks) return 1;
+      if (w.part >= 0 && ++tail_units > 1) return 2;
+      for (int kb = w.kb0; kb < w.kb1; ++kb) cover[(size_t)w.tile * k_blocks + kb]++;
+      if (i > total_tiles) return 3;
+    }
+  }
+  for (int v : cover)
+    if (v != 1) return 4;
+  return 0;
+}
+
+}  // namespace smr
