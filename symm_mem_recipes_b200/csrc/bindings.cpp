@@ -498,7 +498,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("matmul_rs_workspace_bytes", &matmul_rs_workspace_bytes);
   m.def("matmul_reduce_scatter", [](torch::Tensor a, torch::Tensor b, torch::Tensor out,
                                     const std::shared_ptr<CudaSymmAllocation>& workspace, int num_sms,
-                                    uint64_t timeout_ns, c10::optional<torch::Tensor> trace) {
+                                    uint64_t timeout_ns, c10::optional<torch::Tensor> trace, bool deep_strips) {
     auto ok2d = [](const torch::Tensor& t) {
       return t.is_cuda() && t.dim() == 2 && t.is_contiguous() && t.scalar_type() == torch::kBFloat16;
     };
@@ -527,9 +527,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                   "trace must be an int64 CUDA tensor of at least 4 * num_sms elements");
       args.trace = reinterpret_cast<uint64_t*>(trace->data_ptr());
     }
+    args.deep_strips = deep_strips;
     rt_check(launch_matmul_reduce_scatter(args, current_stream(dev)), "matmul_reduce_scatter");
   }, py::arg("a"), py::arg("b"), py::arg("out"), py::arg("workspace"), py::arg("num_sms"),
-     py::arg("timeout_ns"), py::arg("trace") = py::none());
+     py::arg("timeout_ns"), py::arg("trace") = py::none(), py::arg("deep_strips") = false);
 
   // ---- oracles (CPU tensors) ----
   m.def("oracle_ordered_sum_bf16", [](std::vector<torch::Tensor> srcs) {

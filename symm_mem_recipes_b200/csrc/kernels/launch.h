@@ -129,6 +129,7 @@ struct MatmulRsArgs {
   uint64_t timeout_ns;
   Status* status;
   uint64_t* trace;     // optional [num_sms][4] %globaltimer stamps per CTA (start, entered, GEMM done, reduced)
+  bool deep_strips;    // 3-stage ring and five epilogue strips on the wire instead of 4 stages and two
 };
 size_t matmul_rs_workspace_bytes(int M, int N);
 int launch_matmul_reduce_scatter(const MatmulRsArgs& args, cudaStream_t stream);

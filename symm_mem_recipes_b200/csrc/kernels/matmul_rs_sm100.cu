@@ -45,7 +45,6 @@ constexpr int kBM = 128;
 constexpr int kBN = 256;
 constexpr int kBK = 64;
 constexpr int kUmmaK = 16;
-constexpr int kStages = 4;
 constexpr int kThreads = 192;
 constexpr uint32_t kTmemCols = 512;
 constexpr int kStripCols = 64;                         // columns staged at a time (128 bytes: one swizzle row)
@@ -73,19 +72,20 @@ struct RsParams {
   uint64_t* trace;           // optional [grid][4] %globaltimer stamps: start, entered, GEMM done, reduced
 };
 
+template <int kStages, int kNStrips>
 struct Smem {
   static constexpr uint32_t kABytes = kBM * kBK * 2;
   static constexpr uint32_t kBBytes = kBN * kBK * 2;
   static constexpr uint32_t kStageBytes = kABytes + kBBytes;
   static constexpr uint32_t kRingBytes = kStageBytes * kStages;
   static constexpr uint32_t kStripOffset = kRingBytes;
-  static constexpr uint32_t kStripBytes = 2 * kStripBytesOne;   // two strips alternate
+  static constexpr uint32_t kStripBytes = kNStrips * kStripBytesOne;   // strips in flight on the wire
   static constexpr uint32_t kBarOffset = kStripOffset + kStripBytes;
   static constexpr uint32_t kNumBars = 2 * kStages + 4;
   static constexpr uint32_t kMiscOffset = kBarOffset + 8 * kNumBars;
   static constexpr uint32_t kTotal = kMiscOffset + 16 + 1024;
 };
-static_assert(Smem::kTotal <= 232448, "shared memory limit exceeded");
+static_assert(Smem<4, 2>::kTotal <= 232448 && Smem<3, 5>::kTotal <= 232448, "shared memory limit exceeded");
 
 __device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
@@ -170,9 +170,14 @@ __device__ __forceinline__ void reduce_tile(const RsParams& p, const char* inbox
   }
 }
 
+// kStages: depth of the operand ring; kNStrips: epilogue strips that may be on the wire at once.
+// <4, 2> is the default; <3, 5> trades a stage for three more strips in flight (short-K shapes,
+// where the wire, not the main loop, is the limit).
+template <int kStages, int kNStrips>
 __global__ void __launch_bounds__(kThreads, 1)
 matmul_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const RsParams p) {
+  using Smem = smr::Smem<kStages, kNStrips>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* strip = smem + Smem::kStripOffset;
@@ -305,9 +310,9 @@ matmul_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         tmem_ld_32x32b_x32(taddr + (uint32_t)(sidx * kStripCols + 32), v1);
         tmem_ld_wait();
         // the store issued two strips ago has finished reading the buffer we are about to fill
-        if (etid == 0) bulk_wait_group_read<1>();
+        if (etid == 0) bulk_wait_group_read<kNStrips - 1>();
         epilogue_sync();
-        uint8_t* buf = strip + (size_t)(strip_ctr & 1u) * kStripBytesOne;
+        uint8_t* buf = strip + (size_t)(strip_ctr % (uint32_t)kNStrips) * kStripBytesOne;
         uint8_t* row = buf + (size_t)r * 128;
 #pragma unroll
         for (int c = 0; c < 8; ++c) {                    // 16-byte chunk c of the row, 128-byte swizzle
@@ -443,10 +448,19 @@ int launch_matmul_reduce_scatter(const MatmulRsArgs& a, cudaStream_t stream) {
   int total_tiles = ws * p.blocks_per_rank * p.n_tiles_n;
   int grid = a.num_sms < total_tiles ? a.num_sms : total_tiles;
   if (grid < 1 || (uint32_t)(1024 + grid) * (uint32_t)ws > kBlockSlots) return cudaErrorInvalidValue;
-  cudaError_t e = cudaFuncSetAttribute(matmul_rs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)Smem::kTotal);
-  if (e != cudaSuccess) return (int)e;
-  matmul_rs_kernel<<<grid, kThreads, Smem::kTotal, stream>>>(ta, tb, p);
+  if (a.deep_strips) {
+    auto kern = matmul_rs_kernel<3, 5>;
+    constexpr int smem = (int)Smem<3, 5>::kTotal;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    kern<<<grid, kThreads, smem, stream>>>(ta, tb, p);
+  } else {
+    auto kern = matmul_rs_kernel<4, 2>;
+    constexpr int smem = (int)Smem<4, 2>::kTotal;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    kern<<<grid, kThreads, smem, stream>>>(ta, tb, p);
+  }
   return (int)cudaGetLastError();
 }
 
