@@ -250,6 +250,68 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("host_view", &host_view);
   m.def("host_pad_view", &host_pad_view);
   m.def("host_all_reduce", &host_all_reduce);
+  m.def("host_ll_all_reduce", [](const std::shared_ptr<HostSymmAllocation>& workspace, torch::Tensor in,
+                                 torch::Tensor out, int64_t capacity_numel, uint64_t timeout_ns) {
+    TORCH_CHECK(workspace->rendezvoused(), "workspace has not been rendezvoused");
+    TORCH_CHECK(in.numel() == out.numel() && in.numel() % 8 == 0 && in.numel() <= capacity_numel, "bad sizes");
+    const int ws = workspace->world_size();
+    TORCH_CHECK(256 + (size_t)2 * ws * (capacity_numel / 8) * 32 <= workspace->payload_bytes(), "workspace too small");
+    std::vector<void*> bases(ws);
+    for (int r = 0; r < ws; ++r) bases[r] = workspace->peer_ptr(r);
+    int peer = -1;
+    uint32_t code;
+    const uint16_t* src = bf16_ptr(in);
+    uint16_t* dst = reinterpret_cast<uint16_t*>(out.data_ptr());
+    {
+      py::gil_scoped_release nogil;
+      code = host_ll_all_reduce(bases.data(), workspace->rank(), ws, src, dst, (size_t)in.numel(),
+                                (size_t)capacity_numel, timeout_ns, &peer);
+    }
+    return py::make_tuple(code, workspace->rank(), 0, peer, (int)kWhereOneShotEntry, 0);
+  });
+  // Epoch barrier hammered by threads (same protocol as the device EpochBarrier): returns
+  // (codes per rank, max skew seen).
+  m.def("host_epoch_barrier_stress", [](int world_size, int blocks, int iters, uint64_t timeout_ns) {
+    TORCH_CHECK(world_size >= 1 && world_size <= kMaxWorldSize && blocks >= 1 && (uint32_t)blocks <= kArMaxBlocks,
+                "bad stress configuration");
+    std::vector<std::vector<uint32_t>> pads(world_size, std::vector<uint32_t>(kSignalPadSlots, 0u));
+    std::vector<uint32_t*> pad_ptrs(world_size);
+    for (int r = 0; r < world_size; ++r) pad_ptrs[r] = pads[r].data();
+    std::vector<uint32_t> codes(world_size, 0);
+    std::vector<std::atomic<int64_t>> progress(world_size);
+    for (auto& c : progress) c.store(0);
+    std::atomic<int64_t> max_skew{0};
+    {
+      py::gil_scoped_release nogil;
+      std::vector<std::thread> threads;
+      for (int r = 0; r < world_size; ++r) {
+        threads.emplace_back([&, r] {
+          std::vector<uint32_t> counts(blocks, 0);
+          for (int it = 0; it < iters && codes[r] == 0; ++it) {
+            for (int b = 0; b < blocks; ++b) {
+              progress[r].fetch_add(1);
+              int peer = -1;
+              uint32_t code = host_epoch_barrier(pad_ptrs.data(), (uint32_t)b, r, world_size, &counts[b],
+                                                 timeout_ns, &peer);
+              if (code != kOk) {
+                codes[r] = code;
+                break;
+              }
+              int64_t mine = progress[r].load();
+              for (int q = 0; q < world_size; ++q) {
+                int64_t skew = mine - progress[q].load();
+                int64_t cur = max_skew.load();
+                while (skew > cur && !max_skew.compare_exchange_weak(cur, skew)) {
+                }
+              }
+            }
+          }
+        });
+      }
+      for (auto& t : threads) t.join();
+    }
+    return py::make_tuple(codes, max_skew.load());
+  });
 
   // Barrier protocol hammered by threads: `world_size` threads act as ranks over
   // private pads, each running `iters` barriers on each of `blocks` block ids.

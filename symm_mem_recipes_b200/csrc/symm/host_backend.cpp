@@ -113,6 +113,93 @@ uint32_t host_barrier_signal_wait(uint32_t* const* pads, uint32_t slot_base, int
   return kOk;
 }
 
+uint32_t host_epoch_barrier(uint32_t* const* pads, uint32_t block_id, int rank, int world_size,
+                            uint32_t* count, uint64_t timeout_ns, int* failed_peer) {
+  const uint64_t deadline = now_ns() + timeout_ns;
+  const uint32_t base = kArFlagBase + block_id * kArFlagStride;
+  const uint32_t c = ++*count;
+  for (int peer = 0; peer < world_size; ++peer)
+    __atomic_store_n(pads[peer] + base + 16u + (uint32_t)rank, c, __ATOMIC_RELEASE);
+  for (int peer = 0; peer < world_size; ++peer) {
+    const uint32_t* wait = pads[rank] + base + 16u + (uint32_t)peer;
+    for (uint32_t spins = 0;; ++spins) {
+      // a peer can be one barrier ahead, never behind once it has arrived: signed comparison
+      if ((int32_t)(__atomic_load_n(wait, __ATOMIC_ACQUIRE) - c) >= 0) break;
+      if ((spins & 255u) == 255u) {
+        if (now_ns() > deadline) {
+          if (failed_peer) *failed_peer = peer;
+          return kTimeoutBarrierWait;
+        }
+        sched_yield();
+      }
+    }
+  }
+  return kOk;
+}
+
+uint32_t host_ll_all_reduce(void* const* workspaces, int rank, int world_size, const uint16_t* in,
+                            uint16_t* out, size_t numel, size_t capacity_numel, uint64_t timeout_ns,
+                            int* failed_peer) {
+  const uint64_t deadline = now_ns() + timeout_ns;
+  char* my_ws = static_cast<char*>(workspaces[rank]);
+  uint32_t* header = reinterpret_cast<uint32_t*>(my_ws);
+  const uint32_t tag = header[0] + 1u;                    // this call's number
+  const size_t cap_vec = capacity_numel / 8, n_vec = numel / 8;
+  const size_t parity_off = 256 + (size_t)(tag & 1u) * world_size * cap_vec * 32;
+  // push: every 8 bytes on the "wire" = 4 bytes of data + the tag
+  for (size_t i = 0; i < n_vec; ++i) {
+    uint32_t x[4];
+    memcpy(x, in + i * 8, 16);
+    for (int j = 1; j <= world_size; ++j) {               // own inbox last
+      const int peer = (rank + j) % world_size;
+      uint64_t* dst = reinterpret_cast<uint64_t*>(static_cast<char*>(workspaces[peer]) + parity_off +
+                                                  ((size_t)rank * cap_vec + i) * 32);
+      for (int q = 0; q < 4; ++q)
+        __atomic_store_n(dst + q, (uint64_t)x[q] | ((uint64_t)tag << 32), __ATOMIC_RELAXED);
+    }
+  }
+  // poll the own inbox, sum in rank order (bf16 adds from +0: same bits on every rank)
+  for (size_t i = 0; i < n_vec; ++i) {
+    uint16_t acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int r = 0; r < world_size; ++r) {
+      const uint64_t* src = reinterpret_cast<const uint64_t*>(my_ws + parity_off + ((size_t)r * cap_vec + i) * 32);
+      uint32_t w[4];
+      for (int q = 0; q < 4; ++q) {
+        for (uint32_t spins = 0;; ++spins) {
+          const uint64_t v = __atomic_load_n(src + q, __ATOMIC_RELAXED);
+          if ((uint32_t)(v >> 32) == tag) {
+            w[q] = (uint32_t)v;
+            break;
+          }
+          if ((spins & 255u) == 255u) {
+            if (now_ns() > deadline) {
+              if (failed_peer) *failed_peer = r;
+              return kTimeoutFlag;
+            }
+            sched_yield();
+          }
+        }
+      }
+      uint16_t h[8];
+      memcpy(h, w, 16);
+      for (int e = 0; e < 8; ++e) {
+        uint32_t a = (uint32_t)acc[e] << 16, b = (uint32_t)h[e] << 16;
+        float fa, fb;
+        memcpy(&fa, &a, 4);
+        memcpy(&fb, &b, 4);
+        float f = fa + fb;
+        uint32_t u;
+        memcpy(&u, &f, 4);
+        if ((u & 0x7fffffffu) <= 0x7f800000u) u += 0x7fffu + ((u >> 16) & 1u);   // round to nearest even
+        acc[e] = (uint16_t)(u >> 16);
+      }
+    }
+    memcpy(out + i * 8, acc, 16);
+  }
+  header[0] = tag;                                         // single-threaded per rank: no "last CTA" needed
+  return kOk;
+}
+
 uint32_t HostSymmAllocation::barrier(uint32_t slot_base, uint64_t timeout_ns, int* failed_peer) {
   if (!rendezvoused_) throw std::runtime_error("barrier on an allocation that is not rendezvoused");
   std::vector<uint32_t*> pads(world_size_);

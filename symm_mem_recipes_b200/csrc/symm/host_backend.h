@@ -56,4 +56,18 @@ class HostSymmAllocation {
 uint32_t host_barrier_signal_wait(uint32_t* const* pads, uint32_t slot_base, int rank,
                                   int world_size, uint64_t timeout_ns, int* failed_peer);
 
+// Epoch barrier of the all-reduce kernels (store the barrier count into the peers' slots, poll
+// the own ones), same slot layout as the device version: group of kArFlagStride slots per
+// block id at kArFlagBase, [0] = own count, [16 + s] = last count announced by rank s.
+// `count` is the caller's running barrier count for this block id.
+uint32_t host_epoch_barrier(uint32_t* const* pads, uint32_t block_id, int rank, int world_size,
+                            uint32_t* count, uint64_t timeout_ns, int* failed_peer);
+
+// Low-latency all-reduce protocol on host memory (see ll_all_reduce_kernel): tagged 8-byte
+// words pushed into every rank's inbox, two parities, call number in the workspace header.
+// `workspaces[r]` is rank r's workspace base as mapped here.  Returns a StatusCode.
+uint32_t host_ll_all_reduce(void* const* workspaces, int rank, int world_size, const uint16_t* in,
+                            uint16_t* out, size_t numel, size_t capacity_numel, uint64_t timeout_ns,
+                            int* failed_peer);
+
 }  // namespace smr

@@ -68,7 +68,7 @@ def _ll_workspace(device: torch.device, group) -> torch.Tensor:
     ranks), allocated and rendezvoused at first use: that call is collective."""
     import torch.distributed as dist
 
-    key = (device.index, symm_mem._group_key(group))
+    key = (device.type, device.index, symm_mem._group_key(group))
     w = _ll_workspaces.get(key)
     if w is None:
         ws = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -92,17 +92,15 @@ def low_latency_all_reduce(t: torch.Tensor, out: Optional[torch.Tensor] = None, 
         raise SymmMemError("need a contiguous bfloat16 tensor whose size is a multiple of 8")
     if t.numel() > _LL_CAPACITY_NUMEL:
         raise SymmMemError(f"low_latency_all_reduce handles at most {_LL_CAPACITY_NUMEL} elements")
-    if not t.is_cuda:
-        # CPU ranks: same result through the shared-memory one-shot path
-        res = one_shot_all_reduce(t, exit_barrier=True, config=config)
-        if out is None:
-            return res
-        out.copy_(res)
-        return out
     if out is None:
         out = torch.empty_like(t)
     w = _ll_workspace(t.device, group)
     hdl = symm_mem.rendezvous(w, group)
+    if not t.is_cuda:
+        # CPU ranks: the same protocol (tagged words, two parities) over shared memory
+        raise_for_status(C.host_ll_all_reduce(hdl.native, t, out, _LL_CAPACITY_NUMEL,
+                                              config.timeout_ms * 1_000_000))
+        return out
     C.ll_all_reduce(hdl.native, t, out, _LL_CAPACITY_NUMEL, config.ll_max_blocks, config.timeout_ms * 1_000_000)
     return out
 
@@ -158,9 +156,6 @@ def all_reduce(t: torch.Tensor, algo: str = "auto", *,
         hdl = symm_mem.rendezvous(t)
         algo = choose_algo(t.numel() * t.element_size(), hdl.world_size, hdl.has_multicast, config)
     if algo == "low_latency":
-        if not t.is_cuda:
-            one_shot_all_reduce(t, write_back=True, config=config)
-            return t
         return low_latency_all_reduce(t, out=t, config=config)
     if algo == "one_shot":
         one_shot_all_reduce(t, write_back=True, config=config)

@@ -46,6 +46,28 @@ def test_all_reduce_gloo_ws4():
     spawn_ranks(_all_reduce_worker, 4, "gloo", ("one_shot",))
 
 
+def _low_latency_worker(rank, world_size):
+    """The tagged-word protocol over shared memory: sizes change from call to
+    call, parities alternate, the last call is in place."""
+    import symm_mem_recipes_b200 as smr
+    from symm_mem_recipes_b200._ext import C
+
+    for call, numel in enumerate([8192, 64, 8192, 131072, 1024, 1024, 1024]):
+        srcs = [seeded_normal_bf16(numel, r, seed=100 + call) for r in range(world_size)]
+        mine = srcs[rank].clone()              # an ordinary tensor: the input need not be symmetric
+        ref = C.oracle_ordered_sum_bf16(srcs)
+        if call % 2:
+            out = smr.low_latency_all_reduce(mine, out=mine)   # in place
+        else:
+            out = smr.low_latency_all_reduce(mine)
+        assert torch.equal(out.view(torch.int16), ref.view(torch.int16)), f"call {call}"
+
+
+@pytest.mark.parametrize("world_size", [2, 4])
+def test_low_latency_all_reduce_gloo(world_size):
+    spawn_ranks(_low_latency_worker, world_size, "gloo")
+
+
 def _peer_view_worker(rank, world_size):
     from symm_mem_recipes_b200.parallel import symm_mem
 

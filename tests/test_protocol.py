@@ -19,6 +19,13 @@ def test_barrier_with_a_dead_rank_times_out_everywhere():
     assert all(c in (1, 2) for c in live)    # send or wait timed out, nobody hung
 
 
+@pytest.mark.parametrize("world_size,blocks", [(2, 1), (4, 8), (8, 24)])
+def test_epoch_barrier_keeps_ranks_in_step(world_size, blocks):
+    codes, skew = C.host_epoch_barrier_stress(world_size, blocks, 300, 5_000_000_000)
+    assert list(codes) == [0] * world_size
+    assert skew <= 1
+
+
 def test_dispatcher_thresholds():
     from symm_mem_recipes_b200.ops import choose_algo
     from symm_mem_recipes_b200.ops.config import AllReduceConfig
