@@ -441,11 +441,16 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                         c10::optional<torch::Tensor> a_out, c10::optional<torch::Tensor> flags,
                         int block_n, int num_sms, int n_copy, uint64_t timeout_ns, bool cta_pair,
                         c10::optional<torch::Tensor> tail_scratch) {
-    auto ok2d = [](const torch::Tensor& t) {
-      return t.is_cuda() && t.dim() == 2 && t.is_contiguous() && t.scalar_type() == torch::kBFloat16;
+    const auto dtype = a.scalar_type();
+    const bool fp8 = dtype == at::kFloat8_e4m3fn;
+    TORCH_CHECK(fp8 || dtype == torch::kBFloat16, "a must be bfloat16 or float8_e4m3fn");
+    auto ok2d = [dtype](const torch::Tensor& t) {
+      return t.is_cuda() && t.dim() == 2 && t.is_contiguous() && t.scalar_type() == dtype;
     };
-    TORCH_CHECK(ok2d(a) && ok2d(b) && ok2d(c), "a, b, c must be contiguous 2-D bf16 CUDA tensors");
+    TORCH_CHECK(ok2d(a) && ok2d(b) && ok2d(c), "a, b, c must be contiguous 2-D CUDA tensors of one dtype");
     TORCH_CHECK(a.size(1) == b.size(1), "A[*, K] and B[N, K] disagree on K");
+    TORCH_CHECK(!fp8 || (cta_pair && mode != 1),
+                "float8_e4m3fn runs on the CTA-pair kernel: a_out must be symmetric memory (push) or absent");
     int dev = a.get_device();
     c10::cuda::CUDAGuard guard(dev);
     cudaStream_t stream = current_stream(dev);
@@ -455,6 +460,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     args.c = c.data_ptr();
     args.N = (int)b.size(0);
     args.K = (int)a.size(1);
+    args.elem_bytes = fp8 ? 1 : 2;
     args.block_n = block_n;
     args.num_sms = num_sms;
     args.timeout_ns = timeout_ns;
@@ -472,7 +478,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       args.M = args.rows_per_rank * pv.world_size;
       args.pads = pv.pads;
       args.barrier_block_base = 1024;
-      TORCH_CHECK(ok2d(*a_out) && a_out->size(0) == args.M && a_out->size(1) == args.K, "a_out must be [M, K] bf16");
+      TORCH_CHECK(ok2d(*a_out) && a_out->size(0) == args.M && a_out->size(1) == args.K, "a_out must be [M, K] of a's dtype");
       args.a_out = a_out->data_ptr();
       int n_blocks = (args.M + 127) / 128;
       if (mode == 1) {

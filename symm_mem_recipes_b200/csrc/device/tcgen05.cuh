@@ -55,6 +55,12 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16_f32(int m, int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+// Instruction descriptor for kind::f8f6f4 with e4m3 A and B (format code 0 in
+// both operand fields, both K-major) and an fp32 accumulator.
+__host__ __device__ constexpr uint32_t umma_idesc_e4m3_f32(int m, int n) {
+  return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
 // ---- MMA ---------------------------------------------------------------------
 // D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread.
 __device__ __forceinline__ void umma_bf16_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,

@@ -84,6 +84,19 @@ __device__ __forceinline__ void umma_bf16_ss_pair(uint32_t tmem_d, uint64_t desc
       ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Same for fp8 (e4m3) operands: kind::f8f6f4 multiplies 32 elements of K per
+// instruction, i.e. the same 32 bytes of every shared-memory row as kind::f16.
+__device__ __forceinline__ void umma_e4m3_ss_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                                  uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
+      "}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // One arrival on the barrier at this offset in BOTH CTAs of the pair once all
 // MMAs issued so far have completed.
 __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
@@ -106,7 +119,10 @@ struct PairSmem {
   static_assert(kStageBytes % 1024 == 0, "stage bases must stay 1024-byte aligned");
 };
 
-template <int BN, int STAGES>
+// kFp8: A, B, C (and the gathered A) hold e4m3 bytes.  All byte geometry stays
+// (128-byte rows, 16 KB A stage, 32 bytes of K per MMA); a K block is then 128
+// elements instead of 64 and the epilogue packs four outputs per 32-bit word.
+template <int BN, int STAGES, bool kFp8>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
                       const __grid_constant__ CUtensorMap tmap_a_out,
@@ -160,7 +176,8 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
   const int n_pairs = (int)gridDim.x >> 1;
   const int n_pair_rows = (p.n_blocks_m + 1) >> 1;         // 256-row tiles along M
   const int total_tiles = n_pair_rows * p.n_tiles_n;
-  const int k_blocks = (p.K + kBK - 1) / kBK;
+  constexpr int kBKE = kFp8 ? 2 * kBK : kBK;                // elements of K per 128-byte row
+  const int k_blocks = (p.K + kBKE - 1) / kBKE;
   const int rows_per_rank = p.blocks_per_rank * kBM;
   bool failed = false;
 
@@ -203,8 +220,8 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
           uint8_t* sb = sa + L::kABytes;
           if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2u * L::kStageBytes);
           const uint32_t full_leader = map_to_cta(smem_u32(&full_bar[stage]), 0);
-          tma_load_2d_pair(sa, amap, full_leader, kb * kBK, row0);
-          tma_load_2d_pair(sb, &tmap_b, full_leader, kb * kBK, ni * BN + (int)cta_rank * (BN / 2));
+          tma_load_2d_pair(sa, amap, full_leader, kb * kBKE, row0);
+          tma_load_2d_pair(sb, &tmap_b, full_leader, kb * kBKE, ni * BN + (int)cta_rank * (BN / 2));
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -212,7 +229,7 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
   } else if (warp == 1) {
     // ---------------- MMA issuer (leader CTA only) ----------------
     if (leader && lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16_f32(2 * kBM, BN);
+      constexpr uint32_t idesc = kFp8 ? umma_idesc_e4m3_f32(2 * kBM, BN) : umma_idesc_bf16_f32(2 * kBM, BN);
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       PairWork w;
       for (int wi = 0; !failed && pair_work(p, pair, n_pairs, total_tiles, k_blocks, wi, w); ++wi) {
@@ -234,9 +251,14 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
           const uint64_t da = umma_smem_desc_sw128(sa);
           const uint64_t db = umma_smem_desc_sw128(sa + L::kABytes);
 #pragma unroll
-          for (int k = 0; k < kBK / kUmmaK; ++k)
-            umma_bf16_ss_pair(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc,
-                              (kb != w.kb0 || k != 0) ? 1u : 0u);
+          for (int k = 0; k < kBK / kUmmaK; ++k) {
+            if constexpr (kFp8)
+              umma_e4m3_ss_pair(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc,
+                                (kb != w.kb0 || k != 0) ? 1u : 0u);
+            else
+              umma_bf16_ss_pair(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc,
+                                (kb != w.kb0 || k != 0) ? 1u : 0u);
+          }
           umma_commit_pair(&empty_bar[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -277,6 +299,7 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
       const int row = mblk * kBM + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + acc * 256u + ((uint32_t)(quarter * 32) << 16);
       __nv_bfloat16* crow = p.c + (size_t)row * p.N + (size_t)ni * BN;
+      uint8_t* crow8 = reinterpret_cast<uint8_t*>(p.c) + (size_t)row * p.N + (size_t)ni * BN;   // kFp8
       if (w.part >= 0) {
         // ---- split-K tail: park the fp32 partial, meet the other parts, reduce my columns ----
         const int r = quarter * 32 + lane;
@@ -328,10 +351,15 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
           }
           const int col = ni * BN + w.part * cw + c8;
           if (valid && row < p.M && col < p.N) {
-            Vec16 o;
-            o.x = pack_bf16x2(s[0], s[1]); o.y = pack_bf16x2(s[2], s[3]);
-            o.z = pack_bf16x2(s[4], s[5]); o.w = pack_bf16x2(s[6], s[7]);
-            st_16(crow + w.part * cw + c8, o);
+            if constexpr (kFp8) {
+              st_8(crow8 + w.part * cw + c8, pack_e4m3x4(s[0], s[1], s[2], s[3]),
+                   pack_e4m3x4(s[4], s[5], s[6], s[7]));
+            } else {
+              Vec16 o;
+              o.x = pack_bf16x2(s[0], s[1]); o.y = pack_bf16x2(s[2], s[3]);
+              o.z = pack_bf16x2(s[4], s[5]); o.w = pack_bf16x2(s[6], s[7]);
+              st_16(crow + w.part * cw + c8, o);
+            }
           }
         }
         acc ^= 1;
@@ -344,7 +372,26 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
         tmem_ld_32x32b_x32(taddr + (uint32_t)(c * 32), r);
         tmem_ld_wait();
         const int col0 = ni * BN + c * 32;
-        if (valid && row < p.M) {
+        if constexpr (kFp8) {
+          if (valid && row < p.M) {
+#pragma unroll
+            for (int v = 0; v < 2; ++v) {
+              if (col0 + v * 16 < p.N) {
+                Vec16 o;
+                const uint32_t* q = r + v * 16;
+                o.x = pack_e4m3x4(__uint_as_float(q[0]), __uint_as_float(q[1]),
+                                  __uint_as_float(q[2]), __uint_as_float(q[3]));
+                o.y = pack_e4m3x4(__uint_as_float(q[4]), __uint_as_float(q[5]),
+                                  __uint_as_float(q[6]), __uint_as_float(q[7]));
+                o.z = pack_e4m3x4(__uint_as_float(q[8]), __uint_as_float(q[9]),
+                                  __uint_as_float(q[10]), __uint_as_float(q[11]));
+                o.w = pack_e4m3x4(__uint_as_float(q[12]), __uint_as_float(q[13]),
+                                  __uint_as_float(q[14]), __uint_as_float(q[15]));
+                st_16(crow8 + c * 32 + v * 16, o);
+              }
+            }
+          }
+        } else if (valid && row < p.M) {
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
             if (col0 + v * 8 < p.N) {
@@ -386,12 +433,12 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
   }
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool kFp8>
 int launch_pair_variant(const CUtensorMap& ta_shard, const CUtensorMap& ta_out, const CUtensorMap& tb,
                         const AgMatmulParams& p, int grid, cudaStream_t stream) {
   using L = PairSmem<BN, STAGES>;
   static_assert(L::kTotal <= 232448, "shared memory limit exceeded");
-  auto kern = ag_matmul_2cta_kernel<BN, STAGES>;
+  auto kern = ag_matmul_2cta_kernel<BN, STAGES, kFp8>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::kTotal);
   if (e != cudaSuccess) return (int)e;
   kern<<<grid, kGemmThreads, L::kTotal, stream>>>(ta_shard, ta_out, tb, p);
@@ -401,7 +448,11 @@ int launch_pair_variant(const CUtensorMap& ta_shard, const CUtensorMap& ta_out, 
 }  // namespace
 
 int launch_ag_matmul_2cta(const AgMatmulArgs& a, cudaStream_t stream) {
-  if (a.N % 8 != 0 || a.K % 8 != 0 || a.M <= 0 || a.N <= 0 || a.K <= 0) return cudaErrorInvalidValue;
+  if (a.elem_bytes != 0 && a.elem_bytes != 1 && a.elem_bytes != 2) return cudaErrorInvalidValue;
+  const bool fp8 = a.elem_bytes == 1;
+  const int es = fp8 ? 1 : 2;
+  const int align = 16 / es;                                       // elements per 16 bytes
+  if (a.N % align != 0 || a.K % align != 0 || a.M <= 0 || a.N <= 0 || a.K <= 0) return cudaErrorInvalidValue;
   if (a.mode != 0 && a.mode != 2) return cudaErrorInvalidValue;   // pull mode: 1-CTA kernel
   const bool comm = a.mode == 2;
   if (comm) {
@@ -416,6 +467,7 @@ int launch_ag_matmul_2cta(const AgMatmulArgs& a, cudaStream_t stream) {
   AgMatmulParams p{};
   p.c = static_cast<__nv_bfloat16*>(a.c);
   p.M = a.M; p.N = a.N; p.K = a.K;
+  p.elem_bytes = es;
   p.n_tiles_n = (a.N + bn - 1) / bn;
   p.n_blocks_m = (a.M + kBM - 1) / kBM;
   p.rank = comm ? a.rank : 0;
@@ -427,7 +479,7 @@ int launch_ag_matmul_2cta(const AgMatmulArgs& a, cudaStream_t stream) {
   p.pieces = 1;
   if (comm) {
     p.lead = p.blocks_per_rank < 4 ? p.blocks_per_rank : 4;
-    size_t block_vecs = (size_t)kBM * a.K * 2 / 16;
+    size_t block_vecs = (size_t)kBM * a.K * es / 16;
     p.pieces = block_vecs >= 8192 ? 16 : (block_vecs >= 1024 ? 4 : 1);
   }
   p.flags = comm ? a.local_pad + kFlagSlotsBase + 2 : nullptr;
@@ -445,9 +497,10 @@ int launch_ag_matmul_2cta(const AgMatmulArgs& a, cudaStream_t stream) {
 
   CUtensorMap ta_shard, ta_out, tb;
   int rows_local = comm ? a.rows_per_rank : a.M;
-  if (make_tmap(&ta_shard, a.a_local, (uint64_t)rows_local, (uint64_t)a.K, kBM)) return cudaErrorInvalidValue;
-  if (make_tmap(&ta_out, comm ? a.a_out : a.a_local, (uint64_t)a.M, (uint64_t)a.K, kBM)) return cudaErrorInvalidValue;
-  if (make_tmap(&tb, a.b, (uint64_t)a.N, (uint64_t)a.K, (uint32_t)(bn / 2))) return cudaErrorInvalidValue;
+  if (make_tmap(&ta_shard, a.a_local, (uint64_t)rows_local, (uint64_t)a.K, kBM, es)) return cudaErrorInvalidValue;
+  if (make_tmap(&ta_out, comm ? a.a_out : a.a_local, (uint64_t)a.M, (uint64_t)a.K, kBM, es))
+    return cudaErrorInvalidValue;
+  if (make_tmap(&tb, a.b, (uint64_t)a.N, (uint64_t)a.K, (uint32_t)(bn / 2), es)) return cudaErrorInvalidValue;
 
   const int total_tiles = ((p.n_blocks_m + 1) / 2) * p.n_tiles_n;
   int pairs = a.num_sms / 2;
@@ -460,12 +513,14 @@ int launch_ag_matmul_2cta(const AgMatmulArgs& a, cudaStream_t stream) {
   p.tail_tiles = 0;
   p.tail_splits = 1;
   const int rem = total_tiles % pairs;
-  const int k_blocks = (a.K + kBK - 1) / kBK;
+  const int k_blocks = (a.K * es + 127) / 128;                    // one K block = 128 bytes of a row
   if (a.tail_scratch != nullptr && rem > 0 && rem * 2 <= pairs) {
     int splits = pairs / rem;
     splits = splits >= 8 ? 8 : (splits >= 4 ? 4 : 2);
+    // every part reduces BN / splits columns in vectors of 8
+    while (splits > 1 && bn % (8 * splits) != 0) splits >>= 1;
     const size_t need = (size_t)rem * splits * 2 * kBM * bn * sizeof(float);
-    if (k_blocks >= 2 * splits && need <= a.tail_scratch_bytes && (size_t)rem * 2 <= a.tail_counter_slots) {
+    if (splits >= 2 && k_blocks >= 2 * splits && need <= a.tail_scratch_bytes && (size_t)rem * 2 <= a.tail_counter_slots) {
       p.tail_tiles = rem;
       p.tail_splits = splits;
       p.tail_scratch = static_cast<float*>(a.tail_scratch);
@@ -474,11 +529,19 @@ int launch_ag_matmul_2cta(const AgMatmulArgs& a, cudaStream_t stream) {
       if (me != cudaSuccess) return (int)me;
     }
   }
+  if (fp8) {
+    switch (bn) {
+      case 128: return launch_pair_variant<128, 8, true>(ta_shard, ta_out, tb, p, grid, stream);
+      case 192: return launch_pair_variant<192, 7, true>(ta_shard, ta_out, tb, p, grid, stream);
+      case 224: return launch_pair_variant<224, 7, true>(ta_shard, ta_out, tb, p, grid, stream);
+      default:  return launch_pair_variant<256, 6, true>(ta_shard, ta_out, tb, p, grid, stream);
+    }
+  }
   switch (bn) {
-    case 128: return launch_pair_variant<128, 8>(ta_shard, ta_out, tb, p, grid, stream);
-    case 192: return launch_pair_variant<192, 7>(ta_shard, ta_out, tb, p, grid, stream);
-    case 224: return launch_pair_variant<224, 7>(ta_shard, ta_out, tb, p, grid, stream);
-    default:  return launch_pair_variant<256, 6>(ta_shard, ta_out, tb, p, grid, stream);
+    case 128: return launch_pair_variant<128, 8, false>(ta_shard, ta_out, tb, p, grid, stream);
+    case 192: return launch_pair_variant<192, 7, false>(ta_shard, ta_out, tb, p, grid, stream);
+    case 224: return launch_pair_variant<224, 7, false>(ta_shard, ta_out, tb, p, grid, stream);
+    default:  return launch_pair_variant<256, 6, false>(ta_shard, ta_out, tb, p, grid, stream);
   }
 }
 

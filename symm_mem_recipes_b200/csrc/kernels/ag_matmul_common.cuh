@@ -28,8 +28,9 @@ constexpr int kStoreLag = 2;             // bulk stores allowed to still read sm
 constexpr int kFlagLag = 6;              // chunks after which a block's writes are drained
 
 struct AgMatmulParams {
-  __nv_bfloat16* c;      // [M, N]
+  __nv_bfloat16* c;      // [M, N]; one byte per element when elem_bytes == 1
   int M, N, K;
+  int elem_bytes;        // 2 = bf16 in and out; 1 = fp8 e4m3 in and out (2-CTA kernel only)
   int n_tiles_n;         // ceil(N / BN)
   int n_blocks_m;        // ceil(M / 128)
   // gather
@@ -90,7 +91,7 @@ __device__ inline bool push_entry_barrier(const AgMatmulParams& p, int cta, int 
 // piece not pushed.
 __device__ inline int push_pieces(const AgMatmulParams& p, int next, int n_ctas, int limit, int etid) {
   constexpr int U = 8;
-  const size_t block_vecs = (size_t)kBM * p.K * 2 / 16;
+  const size_t block_vecs = (size_t)kBM * p.K * p.elem_bytes / 16;
   const size_t piece_vecs = (block_vecs + p.pieces - 1) / p.pieces;
   int piece = next;
   for (; piece < limit; piece += n_ctas) {
@@ -213,14 +214,17 @@ __host__ __device__ __forceinline__ bool pair_work(const AgMatmulParams& p, int 
   return true;
 }
 
-// row-major bf16 [rows, cols] with a [box_rows x 64] box and 128-byte swizzle
-inline int make_tmap(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+// row-major [rows, cols] of bf16 (or of 1-byte elements) with a box of
+// `box_rows` rows x 128 bytes and the 128-byte swizzle
+inline int make_tmap(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                     int elem_bytes = 2) {
   const DriverApi& d = DriverApi::get();
   cuuint64_t dims[2] = {cols, rows};
-  cuuint64_t strides[1] = {cols * 2};
-  cuuint32_t box[2] = {(cuuint32_t)kBK, box_rows};
+  cuuint64_t strides[1] = {cols * (cuuint64_t)elem_bytes};
+  cuuint32_t box[2] = {(cuuint32_t)(128 / elem_bytes), box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = d.cuTensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base),
+  const CUtensorMapDataType dt = elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  CUresult r = d.cuTensorMapEncodeTiled(map, dt, 2, const_cast<void*>(base),
                                         dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);

@@ -425,10 +425,12 @@ int launch_ag_matmul(const AgMatmulArgs& a, cudaStream_t stream) {
   }
   int bn = a.block_n;
   if (bn != 128 && bn != 192 && bn != 224 && bn != 256) return cudaErrorInvalidValue;
+  if (a.elem_bytes != 0 && a.elem_bytes != 2) return cudaErrorInvalidValue;   // fp8: 2-CTA kernel
 
   AgMatmulParams p{};
   p.c = static_cast<__nv_bfloat16*>(a.c);
   p.M = a.M; p.N = a.N; p.K = a.K;
+  p.elem_bytes = 2;
   p.n_tiles_n = (a.N + bn - 1) / bn;
   p.n_blocks_m = (a.M + kBM - 1) / kBM;
   p.rank = comm ? a.rank : 0;

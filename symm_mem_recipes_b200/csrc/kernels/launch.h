@@ -55,6 +55,9 @@ struct AgMatmulArgs {
   const void* b;         // [N, K] bf16, K-major
   void* c;               // [M, N] bf16
   int M, N, K;
+  // 0 or 2: bf16.  1: A, B, C and a_out hold fp8 e4m3 (fp32 accumulation, no scale factors,
+  // as upstream's FP8_OUTPUT path); 2-CTA kernel, modes 0 and 2; N and K multiples of 16.
+  int elem_bytes;
   int block_n;           // 128, 192, 224 or 256
   int num_sms;           // CTAs to launch at most (copiers included)
   // communication: mode 0 = none (GEMM over a_local only),

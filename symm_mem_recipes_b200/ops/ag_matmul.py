@@ -7,6 +7,12 @@ symm_mem_recipes/triton_all_gather_matmul.py:219-319
 mm_only)`): A is sharded on rows (tokens), B is given as [N, K], the fully
 gathered A is a side output, and `mm_only=True` runs the GEMM alone.  The
 NCCL + cuBLAS composition of :322-326 is `reference_all_gather_matmul`.
+
+Dtypes: bfloat16, or float8_e4m3fn for A, B and C at once (upstream's
+`FP8_OUTPUT` path, :123 and :311: the output takes the dtype of `a_shard`;
+fp32 accumulation, no scale factors).  The fp8 form runs on the CTA-pair
+kernel, so its gathered A lives in symmetric memory (push), and N and K are
+multiples of 16.
 """
 from __future__ import annotations
 
@@ -82,22 +88,38 @@ def choose_block_n(M: int, N: int, gemm_ctas: int, cta_pair: bool = False) -> in
     return 256
 
 
-def _check_2d_bf16(name: str, t: torch.Tensor) -> None:
-    if t.dim() != 2 or t.dtype != torch.bfloat16 or not t.is_cuda or not t.is_contiguous():
-        raise SymmMemError(f"{name} must be a contiguous 2-D bfloat16 CUDA tensor")
+_DTYPES = (torch.bfloat16, torch.float8_e4m3fn)
+
+
+def _check_2d(name: str, t: torch.Tensor, dtype: Optional[torch.dtype] = None) -> None:
+    if t.dim() != 2 or t.dtype not in _DTYPES or not t.is_cuda or not t.is_contiguous():
+        raise SymmMemError(f"{name} must be a contiguous 2-D bfloat16 or float8_e4m3fn CUDA tensor")
+    if dtype is not None and t.dtype != dtype:
+        raise SymmMemError(f"{name} is {t.dtype}, expected {dtype}: A, B and C share one dtype")
+
+
+def _check_nk(N: int, K: int, b: torch.Tensor, dtype: torch.dtype) -> None:
+    align = 16 // dtype.itemsize       # elements per 16 bytes (TMA row pitch, vector stores)
+    if b.shape[1] != K or N % align or K % align:
+        raise SymmMemError(f"need B[N, K] with N and K multiples of {align}")
+
+
+def _check_fp8_config(dtype: torch.dtype, config: "AgMatmulConfig") -> None:
+    if dtype == torch.float8_e4m3fn and not config.cta_pair:
+        raise SymmMemError("float8_e4m3fn needs the CTA-pair kernel (config.cta_pair)")
 
 
 def matmul(a: torch.Tensor, b: torch.Tensor, c_out: Optional[torch.Tensor] = None,
            config: AgMatmulConfig = DEFAULT_CONFIG) -> torch.Tensor:
     """C[M, N] = A[M, K] @ B[N, K]^T on the tcgen05 kernel, no communication."""
-    _check_2d_bf16("a", a)
-    _check_2d_bf16("b", b)
+    _check_2d("a", a)
+    _check_2d("b", b, a.dtype)
+    _check_fp8_config(a.dtype, config)
     M, K = a.shape
     N = b.shape[0]
-    if b.shape[1] != K or N % 8 or K % 8:
-        raise SymmMemError("need B[N, K] with N and K multiples of 8")
+    _check_nk(N, K, b, a.dtype)
     if c_out is None:
-        c_out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+        c_out = torch.empty(M, N, dtype=a.dtype, device=a.device)
     sms = config.num_sms or _num_sms(a.device)
     bn = config.block_n or choose_block_n(M, N, sms, config.cta_pair)
     C.ag_matmul(a, b, c_out, 0, None, 0, None, 0, None, None, bn, sms, 0, config.timeout_ms * 1_000_000,
@@ -108,14 +130,15 @@ def matmul(a: torch.Tensor, b: torch.Tensor, c_out: Optional[torch.Tensor] = Non
 _gather_buffers: dict[tuple, torch.Tensor] = {}
 
 
-def gather_buffer(M: int, K: int, device: torch.device, group=None) -> torch.Tensor:
+def gather_buffer(M: int, K: int, device: torch.device, group=None,
+                  dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
     """The symmetric [M, K] buffer that `all_gather_matmul` gathers into when
     the caller passes no `a_out`.  Allocated and rendezvoused at first use
     (collective: every rank must reach it), then reused."""
-    key = (M, K, device.index, symm_mem._group_key(group))
+    key = (M, K, device.index, symm_mem._group_key(group), dtype)
     t = _gather_buffers.get(key)
     if t is None:
-        t = symm_mem.empty(M, K, dtype=torch.bfloat16, device=device)
+        t = symm_mem.empty(M, K, dtype=dtype, device=device)
         symm_mem.rendezvous(t, group)
         _gather_buffers[key] = t
     return t
@@ -137,18 +160,18 @@ def all_gather_matmul(a_shard: torch.Tensor, b: torch.Tensor, a_out: Optional[to
     `mm_only=True` skips the gather and multiplies `a_out` (or `a_shard` when
     no `a_out` is given) as it is, to time the GEMM alone.
     """
-    _check_2d_bf16("a_shard", a_shard)
-    _check_2d_bf16("b", b)
+    _check_2d("a_shard", a_shard)
+    _check_2d("b", b, a_shard.dtype)
+    _check_fp8_config(a_shard.dtype, config)
     if mm_only:
         return matmul(a_out if a_out is not None else a_shard, b, c_out, config)
     rows, K = a_shard.shape
     N = b.shape[0]
-    if b.shape[1] != K or N % 8 or K % 8:
-        raise SymmMemError("need B[N, K] with N and K multiples of 8")
+    _check_nk(N, K, b, a_shard.dtype)
     ws = dist.get_world_size(group) if dist.is_initialized() else 1
     M = rows * ws
     if c_out is None:
-        c_out = torch.empty(M, N, dtype=torch.bfloat16, device=a_shard.device)
+        c_out = torch.empty(M, N, dtype=a_shard.dtype, device=a_shard.device)
     if ws == 1:
         # nothing to gather: the shard is the gathered A; copy only on request
         matmul(a_shard, b, c_out, config)
@@ -158,7 +181,7 @@ def all_gather_matmul(a_shard: torch.Tensor, b: torch.Tensor, a_out: Optional[to
     if rows % 128:
         raise SymmMemError("rows per rank must be a multiple of 128 (the M tile and flag granularity)")
     if a_out is None:
-        a_out = gather_buffer(M, K, a_shard.device, group)
+        a_out = gather_buffer(M, K, a_shard.device, group, a_shard.dtype)
     if tuple(a_out.shape) != (M, K) or tuple(c_out.shape) != (M, N):
         raise SymmMemError("a_out must be [M, K] and c_out [M, N] with M = rows * world_size")
     sms = config.num_sms or _num_sms(a_shard.device)
@@ -174,6 +197,9 @@ def all_gather_matmul(a_shard: torch.Tensor, b: torch.Tensor, a_out: Optional[to
         C.ag_matmul(a_shard, b, c_out, 2, None, 0, hdl.native, aout_offset, a_out, None,
                     bn, sms, n_copy, t_ns, config.cta_pair, _tail_buffer(a_shard.device, config))
         return c_out
+    if a_shard.dtype != torch.bfloat16:
+        raise SymmMemError("the pull mode (a_out in ordinary memory) is bfloat16 only; allocate a_out with "
+                           "symm_mem.empty, or pass None")
     n_copy = max(1, min(config.n_copy, sms // 4))
     bn = config.block_n or choose_block_n(M, N, sms - n_copy)
     _, offset = symm_mem._find_record(a_shard)
@@ -195,5 +221,9 @@ def reference_all_gather_matmul(a_shard: torch.Tensor, b: torch.Tensor, group=No
     `all_gather_matmul`, triton_all_gather_matmul.py:322-326).  `b` is [N, K]."""
     ws = dist.get_world_size(group)
     a = torch.empty(a_shard.shape[0] * ws, a_shard.shape[1], dtype=a_shard.dtype, device=a_shard.device)
+    if a_shard.dtype == torch.float8_e4m3fn:
+        # no fp8 reduction is involved: gather the bytes; the product is taken in bf16 and cast
+        dist.all_gather_into_tensor(a.view(torch.uint8), a_shard.view(torch.uint8), group=group)
+        return torch.matmul(a.to(torch.bfloat16), b.to(torch.bfloat16).t()).to(torch.float8_e4m3fn)
     dist.all_gather_into_tensor(a, a_shard, group=group)
     return torch.matmul(a, b.t())
