@@ -459,7 +459,7 @@ int launch_ag_matmul_2cta(const AgMatmulArgs& a, cudaStream_t stream) {
     if (a.world_size < 2 || a.rows_per_rank % kBM != 0 || a.rows_per_rank * a.world_size != a.M ||
         a.a_out == nullptr || a.pads == nullptr || a.aout_buffers == nullptr || a.local_pad == nullptr)
       return cudaErrorInvalidValue;
-    if ((uint32_t)(a.M / kBM) + 2u > kFlagSlots) return cudaErrorInvalidValue;
+    if ((uint32_t)(a.M / kBM) + 2u > kFusedFlagSlots) return cudaErrorInvalidValue;
   }
   const int bn = a.block_n;
   if (bn != 128 && bn != 192 && bn != 224 && bn != 256) return cudaErrorInvalidValue;

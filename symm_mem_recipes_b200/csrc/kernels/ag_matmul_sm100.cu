@@ -421,7 +421,7 @@ int launch_ag_matmul(const AgMatmulArgs& a, cudaStream_t stream) {
       return cudaErrorInvalidValue;
     if (a.mode == 1 && (a.buffers == nullptr || a.flags == nullptr)) return cudaErrorInvalidValue;
     if (a.mode == 2 && (a.aout_buffers == nullptr || a.local_pad == nullptr)) return cudaErrorInvalidValue;
-    if (a.mode == 2 && (uint32_t)(a.M / kBM) + 2u > kFlagSlots) return cudaErrorInvalidValue;
+    if (a.mode == 2 && (uint32_t)(a.M / kBM) + 2u > kFusedFlagSlots) return cudaErrorInvalidValue;
   }
   int bn = a.block_n;
   if (bn != 128 && bn != 192 && bn != 224 && bn != 256) return cudaErrorInvalidValue;

@@ -433,7 +433,7 @@ int launch_matmul_reduce_scatter(const MatmulRsArgs& a, cudaStream_t stream) {
   p.rank = a.pv.rank; p.world_size = ws;
   p.blocks_per_rank = a.M / ws / kBM;
   p.n_tiles_n = (a.N + kBN - 1) / kBN;
-  if ((uint32_t)(p.blocks_per_rank * p.n_tiles_n) + 2u > kFlagSlots) return cudaErrorInvalidValue;
+  if ((uint32_t)(p.blocks_per_rank * p.n_tiles_n) + 2u > kFusedFlagSlots) return cudaErrorInvalidValue;
   p.buffers = a.pv.buffers;
   p.inbox_offset = a.inbox_offset;
   p.pads = a.pv.pads;
