@@ -26,6 +26,7 @@ import torch.distributed as dist
 from .._ext import C
 from ..errors import SymmMemError
 from ..parallel import symm_mem
+from ..utils.trace import traced
 
 _BLOCK_NS = (256, 224, 192, 128)
 
@@ -109,6 +110,7 @@ def _check_fp8_config(dtype: torch.dtype, config: "AgMatmulConfig") -> None:
         raise SymmMemError("float8_e4m3fn needs the CTA-pair kernel (config.cta_pair)")
 
 
+@traced("smr.matmul")
 def matmul(a: torch.Tensor, b: torch.Tensor, c_out: Optional[torch.Tensor] = None,
            config: AgMatmulConfig = DEFAULT_CONFIG) -> torch.Tensor:
     """C[M, N] = A[M, K] @ B[N, K]^T on the tcgen05 kernel, no communication."""
@@ -144,6 +146,7 @@ def gather_buffer(M: int, K: int, device: torch.device, group=None,
     return t
 
 
+@traced("smr.all_gather_matmul")
 def all_gather_matmul(a_shard: torch.Tensor, b: torch.Tensor, a_out: Optional[torch.Tensor] = None,
                       c_out: Optional[torch.Tensor] = None, config: AgMatmulConfig = DEFAULT_CONFIG,
                       mm_only: bool = False, group=None) -> torch.Tensor:

@@ -15,6 +15,7 @@ import torch
 from .._ext import C
 from ..errors import SymmMemError, raise_for_status
 from ..parallel import symm_mem
+from ..utils.trace import traced
 from .config import DEFAULT_ALL_REDUCE, AllReduceConfig
 
 _ALGOS = ("auto", "low_latency", "one_shot", "two_shot", "multimem")
@@ -36,6 +37,7 @@ def _prepare(t: torch.Tensor):
     return hdl, offset
 
 
+@traced("smr.one_shot_all_reduce")
 def one_shot_all_reduce(t: torch.Tensor, *, exit_barrier: bool = False,
                         out: Optional[torch.Tensor] = None, write_back: bool = False,
                         config: AllReduceConfig = DEFAULT_ALL_REDUCE) -> torch.Tensor:
@@ -79,6 +81,7 @@ def _ll_workspace(device: torch.device, group) -> torch.Tensor:
     return w
 
 
+@traced("smr.low_latency_all_reduce")
 def low_latency_all_reduce(t: torch.Tensor, out: Optional[torch.Tensor] = None, group=None,
                            config: AllReduceConfig = DEFAULT_ALL_REDUCE) -> torch.Tensor:
     """All-reduce for small bf16 messages (up to 256 KiB) in one NVLink
@@ -105,6 +108,7 @@ def low_latency_all_reduce(t: torch.Tensor, out: Optional[torch.Tensor] = None, 
     return out
 
 
+@traced("smr.two_shot_all_reduce_")
 def two_shot_all_reduce_(t: torch.Tensor, *, config: AllReduceConfig = DEFAULT_ALL_REDUCE) -> torch.Tensor:
     """In place: rank r reduces slice r from all peers (ordered bf16 sum) and
     stores it into slice r of every peer.  Returns `t`."""
@@ -117,6 +121,7 @@ def two_shot_all_reduce_(t: torch.Tensor, *, config: AllReduceConfig = DEFAULT_A
     return t
 
 
+@traced("smr.multimem_all_reduce_")
 def multimem_all_reduce_(t: torch.Tensor, *, config: AllReduceConfig = DEFAULT_ALL_REDUCE) -> torch.Tensor:
     """In place through the NVSwitch: multimem.ld_reduce (fp32 accumulate, one
     bf16 rounding) of slice r, multimem.st of the result.  Returns `t`."""

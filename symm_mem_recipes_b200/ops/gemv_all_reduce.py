@@ -19,6 +19,7 @@ import torch.distributed as dist
 from .._ext import C
 from ..errors import SymmMemError
 from ..parallel import symm_mem
+from ..utils.trace import traced
 from .ag_matmul import _num_sms
 
 _workspaces: dict[tuple, torch.Tensor] = {}
@@ -44,6 +45,7 @@ def _workspace(batch_tile: int, N: int, K: int, device: torch.device, group, ten
     return t
 
 
+@traced("smr.gemv_all_reduce")
 def gemv_all_reduce(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
                     group=None, timeout_ms: int = _TIMEOUT_MS, algo: Optional[str] = None) -> torch.Tensor:
     """`x` [B, K] and `w` [K, N] are this rank's (ordinary) tensors; returns the

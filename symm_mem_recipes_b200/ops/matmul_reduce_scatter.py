@@ -21,6 +21,7 @@ import torch.distributed as dist
 from .._ext import C
 from ..errors import SymmMemError
 from ..parallel import symm_mem
+from ..utils.trace import traced
 from .ag_matmul import _num_sms, matmul
 
 _workspaces: dict[tuple, torch.Tensor] = {}
@@ -39,6 +40,7 @@ def _workspace(M: int, N: int, device: torch.device, group) -> torch.Tensor:
     return t
 
 
+@traced("smr.matmul_reduce_scatter")
 def matmul_reduce_scatter(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None,
                           group=None, num_sms: int = 0, timeout_ms: int = _TIMEOUT_MS,
                           trace: Optional[torch.Tensor] = None, deep_strips: Optional[bool] = None) -> torch.Tensor:

@@ -4,6 +4,8 @@ import json
 import subprocess
 import sys
 
+import torch
+
 from symm_mem_recipes_b200.utils.benchmark import ClockSampler
 
 
@@ -60,3 +62,33 @@ def test_ptxas_report_lists_the_kernels():
     report = _build.ptxas_report()
     if report:          # present whenever the module was built in this tree
         assert "registers" in report
+
+
+def test_nvtx_tracing_is_free_when_off_and_balanced_when_on(monkeypatch):
+    from symm_mem_recipes_b200.utils import trace
+
+    def op(t, k=1):
+        if k < 0:
+            raise ValueError("boom")
+        return t + k
+
+    assert trace.traced("smr.op", enabled=False)(op) is op        # off: the very same function
+    events = []
+    monkeypatch.setattr(trace, "_push", lambda msg: events.append(("push", msg)))
+    monkeypatch.setattr(trace, "_pop", lambda: events.append(("pop",)))
+    wrapped = trace.traced("smr.op", enabled=True)(op)
+    assert wrapped.__name__ == "op"
+    assert int(wrapped(torch.zeros(2, 3), k=2).sum()) == 12
+    assert events == [("push", "smr.op (2, 3)"), ("pop",)]
+    events.clear()
+    try:
+        wrapped(torch.zeros(1), k=-1)
+    except ValueError:
+        pass
+    assert events == [("push", "smr.op (1,)"), ("pop",)]          # popped on the error path too
+    events.clear()
+    with trace.nvtx_range("phase", enabled=True):
+        pass
+    with trace.nvtx_range("quiet", enabled=False):
+        pass
+    assert events == [("push", "phase"), ("pop",)]

@@ -1,0 +1,55 @@
+"""The Markdown renderer of the benchmark JSON lines (no GPU involved)."""
+import json
+
+from symm_mem_recipes_b200.bench import report
+
+LINES = [
+    'some log line that is not JSON',
+    '{"op": "all_reduce", "impl": "nccl", "world_size": 8, "bytes": 4096, "timing": "graph", "us": 28.81}',
+    '{"op": "all_reduce", "impl": "low_latency", "world_size": 8, "bytes": 4096, "timing": "graph", "us": 5.4}',
+    '{"op": "all_reduce", "impl": "reference_triton", "world_size": 8, "bytes": 4096, "timing": "graph", "us": 7.96}',
+    '{"op": "all_reduce", "impl": "auto:low_latency", "world_size": 8, "bytes": 4096, "timing": "graph", "us": 5.5}',
+    '{"op": "all_reduce", "impl": "nccl", "world_size": 8, "bytes": 67108864, "timing": "event", "us": 279.04}',
+    '{"op": "all_reduce", "impl": "multimem", "world_size": 8, "bytes": 67108864, "timing": "event", "us": 166.38}',
+    '{"op": "all_gather_matmul", "impl": "cublas_plus_nccl", "world_size": 8, "M": 16384, "N": 3584, "K": 8192, "us": 1341.5}',
+    '{"op": "all_gather_matmul", "impl": "smr_fused", "world_size": 8, "M": 16384, "N": 3584, "K": 8192, "us": 772.1, "gather": "push"}',
+    '{"op": "gemv_all_reduce", "impl": "smr_fused", "world_size": 8, "batch": 1, "K": 3584, "N": 8192, "us": 22.6}',
+    '{"op": "gemv_all_reduce", "impl": "cublas_plus_nccl", "world_size": 8, "batch": 1, "K": 3584, "N": 8192, "us": 39.52}',
+    '{"op": "llama70b_layer_decode", "world_size": 8, "batch": 1, "smr_fused_us": 197.2, "nccl_cublas_us": 237.6, "speedup": 1.205}',
+    '{"truncated": ',
+]
+PEAKS = {"bf16_tflops": 1647.3, "bf16_tflops_sustained": 1411.0, "hbm_gbs": 6541.5}
+
+
+def test_report_tables(tmp_path):
+    f = tmp_path / "r.jsonl"
+    f.write_text("\n".join(LINES) + "\n")
+    recs = report.read_records([str(f)])
+    assert len(recs) == 11                       # the log line and the truncated object are skipped
+    text = report.render(recs, PEAKS)
+    # all-reduce: best of this package and both speed-ups
+    row = [ln for ln in text.splitlines() if ln.startswith("| 8 | 4 KiB")][0]
+    assert "5.40" in row and "5.34x" in row and "1.47x" in row
+    # bus bandwidth of the 64 MiB row: 2 * 7/8 * 64 MiB / 166.38 µs = 705.9 GB/s = 78.4 % of 900
+    row = [ln for ln in text.splitlines() if ln.startswith("| 8 | 64 MiB")][0]
+    assert "705.9" in row and "78.4 %" in row
+    # fused all_gather_matmul against the library composition, and its roofline line
+    assert "1.74x" in text
+    assert "584 µs of math" in text and "224 MiB of remote A" in text
+    # GEMV: the 56 MiB weight shard at the measured HBM rate is 9.0 µs
+    row = [ln for ln in text.splitlines() if ln.startswith("| 8 | 3584 x 8192 | 1 |")][0]
+    assert "1.75x" in row and "9.0" in row
+    assert "decode batch 1" in text and "1.21x" in text
+
+
+def test_report_cli_without_peaks(tmp_path, capsys):
+    f = tmp_path / "r.jsonl"
+    f.write_text("\n".join(LINES) + "\n")
+    out = tmp_path / "t.md"
+    assert report.main([str(f), "--out", str(out)]) == 0
+    text = out.read_text()
+    assert "of measured" not in text and "### all-reduce" in text
+    empty = tmp_path / "e.jsonl"
+    empty.write_text(json.dumps({"no": "op"}) + "\n")
+    assert report.main([str(empty)]) == 0
+    assert "no benchmark records" in capsys.readouterr().out
