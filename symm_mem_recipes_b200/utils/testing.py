@@ -104,3 +104,27 @@ def seeded_normal_bf16(numel: int, rank: int, device="cpu", std: float = 1.0, se
     g.manual_seed(seed + rank)
     t = (torch.randn(numel, generator=g, dtype=torch.float32) * std).to(torch.bfloat16)
     return t.to(device)
+
+
+def guarded_empty(shape, dtype: torch.dtype, device, guard_bytes: int = 4096, fill: int = 0xA5):
+    """An output buffer between two canary regions.  Returns `(tensor, intact)`:
+    `tensor` is contiguous, 256-byte aligned and filled with the canary pattern
+    too (every element must be overwritten by the op under test); `intact()`
+    is true while no byte of the guard regions before and after it has changed.
+    Stands in for a memory checker in the kernel tests: a store past either end
+    of the output shows up on the host."""
+    numel = 1
+    for s in shape:
+        numel *= int(s)
+    nbytes = numel * dtype.itemsize
+    assert guard_bytes % 256 == 0
+    raw = torch.full((guard_bytes + (nbytes + 255) // 256 * 256 + guard_bytes,), fill, dtype=torch.uint8,
+                     device=device)
+    tensor = raw[guard_bytes:guard_bytes + nbytes].view(dtype).view(*shape)
+
+    def intact() -> bool:
+        front = bool((raw[:guard_bytes] == fill).all())
+        back = bool((raw[guard_bytes + nbytes:] == fill).all())
+        return front and back
+
+    return tensor, intact

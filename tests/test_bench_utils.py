@@ -92,3 +92,21 @@ def test_nvtx_tracing_is_free_when_off_and_balanced_when_on(monkeypatch):
     with trace.nvtx_range("quiet", enabled=False):
         pass
     assert events == [("push", "phase"), ("pop",)]
+
+
+def test_guarded_empty_detects_stores_outside():
+    from symm_mem_recipes_b200.utils.testing import guarded_empty
+
+    t, intact = guarded_empty((5, 24), torch.bfloat16, "cpu", guard_bytes=256)
+    assert t.shape == (5, 24) and t.is_contiguous() and t.data_ptr() % 16 == 0
+    t.zero_()
+    assert intact()
+    flat = t.view(-1)
+    # one element past the end / before the start, through the underlying storage
+    past = torch.as_strided(flat, (1,), (1,), storage_offset=flat.storage_offset() + flat.numel())
+    past.fill_(1.0)
+    assert not intact()
+    t2, intact2 = guarded_empty((8,), torch.float32, "cpu", guard_bytes=256)
+    before = torch.as_strided(t2, (1,), (1,), storage_offset=t2.storage_offset() - 1)
+    before.fill_(3.0)
+    assert not intact2()

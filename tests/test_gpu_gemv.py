@@ -2,7 +2,7 @@
 import pytest
 import torch
 
-from symm_mem_recipes_b200.utils.testing import spawn_ranks
+from symm_mem_recipes_b200.utils.testing import guarded_empty, spawn_ranks
 
 
 def _inputs(rank, B, K, N):
@@ -24,10 +24,13 @@ def _gemv_worker(rank, world_size, B, K, N, algo="tc"):
         ref += x.double() @ w.double()
     x, w = _inputs(rank, B, K, N)
     x, w = x.to(dev), w.to(dev)
-    out = None
+    out, intact = guarded_empty((B, N), torch.bfloat16, dev)     # canaries before and after the output
     for it in range(4):          # repeated calls exercise the epoch / parity logic
-        out = smr.gemv_all_reduce(x, w, algo=algo)
+        out.fill_(float("nan"))
+        smr.gemv_all_reduce(x, w, out, algo=algo)
         symm_mem.check_status(dev)
+        if not intact():
+            failures.append(f"call {it}: the kernel stored outside its output")
         err = (out.double().cpu() - ref).abs()
         tol = ref.abs() * 2.0 ** -7 + 2e-2
         if not bool((err <= tol).all()):

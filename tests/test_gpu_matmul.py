@@ -2,7 +2,7 @@
 import pytest
 import torch
 
-from symm_mem_recipes_b200.utils.testing import spawn_ranks
+from symm_mem_recipes_b200.utils.testing import guarded_empty, spawn_ranks
 
 
 def _ref(a, b):
@@ -28,11 +28,13 @@ def test_matmul_small(block_n, shape, cta_pair):
     torch.manual_seed(M + N + K)
     a = (torch.randn(M, K, device="cuda") * 0.5).to(torch.bfloat16)
     b = (torch.randn(N, K, device="cuda") * 0.5).to(torch.bfloat16)
-    c = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    c, intact = guarded_empty((M, N), torch.bfloat16, "cuda")    # canaries before and after the output
+    c.fill_(float("nan"))
     matmul(a, b, c, AgMatmulConfig(block_n=block_n, timeout_ms=2000, cta_pair=cta_pair))
     symm_mem.check_status("cuda")
     ok, err = _close(c, _ref(a, b), K)
     assert ok, f"max abs error {err}"
+    assert intact(), "the kernel stored outside its output"
 
 
 @pytest.mark.gpu
