@@ -178,14 +178,22 @@ def layer_tables(recs: list[dict]) -> Optional[str]:
              "outbound GB/s", "speed-up"], rows))
     if pre or dec:
         rows = []
-        for r in {(r["world_size"], r["batch"], r["seq"]): r for r in pre}.values():
-            rows.append([str(r["world_size"]), f"prefill {r['batch']} x {r['seq']}", _fmt(r["smr_fused_us"]),
+        for r in {(r["world_size"], r["batch"], r["seq"], r.get("fused_glue", False)): r for r in pre}.values():
+            glue = ", single-pass norm / RoPE / SiLU kernels" if r.get("fused_glue") else ""
+            rows.append([str(r["world_size"]), f"prefill {r['batch']} x {r['seq']}{glue}", _fmt(r["smr_fused_us"]),
                          _fmt(r["nccl_cublas_us"]), f"{r['speedup']:.2f}x"])
         for r in {(r["world_size"], r["batch"]): r for r in dec}.values():
             rows.append([str(r["world_size"]), f"decode batch {r['batch']}", _fmt(r["smr_fused_us"]),
                          _fmt(r["nccl_cublas_us"]), f"{r['speedup']:.2f}x"])
         parts.append("### Llama-3-70B TP decoder layer\n\n" + _table(
             ["WS", "step", "this package µs", "NCCL + cuBLAS µs", "speed-up"], rows))
+    for r in recs:
+        if r.get("op") == "llama70b_layer_prefill_phases":
+            total = sum(r["us"].values())
+            rows = [[k, _fmt(v), _fmt(100.0 * v / total) + " %"] for k, v in r["us"].items()]
+            glue = "single-pass glue kernels" if r.get("fused_glue") else "PyTorch glue"
+            parts.append(f"### prefill phases, WS {r['world_size']}, {glue} (rank 0)\n\n" +
+                         _table(["phase", "µs", "share"], rows))
     return "\n\n".join(parts) if parts else None
 
 

@@ -600,7 +600,68 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   }, py::arg("a"), py::arg("b"), py::arg("out"), py::arg("workspace"), py::arg("num_sms"),
      py::arg("timeout_ns"), py::arg("trace") = py::none(), py::arg("deep_strips") = false);
 
+  // ---- rank-local layer glue ----
+  m.def("rms_norm", [](torch::Tensor x, c10::optional<torch::Tensor> residual, torch::Tensor w,
+                       c10::optional<torch::Tensor> sum_out, torch::Tensor out, double eps) {
+    auto ok = [](const torch::Tensor& t) {
+      return t.is_cuda() && t.is_contiguous() && t.scalar_type() == torch::kBFloat16;
+    };
+    TORCH_CHECK(ok(x) && ok(w) && ok(out) && x.dim() == 2 && w.dim() == 1 && w.size(0) == x.size(1) &&
+                out.sizes() == x.sizes(), "rms_norm: x[rows, H], w[H], out[rows, H], contiguous bf16 on the GPU");
+    TORCH_CHECK(!residual.has_value() || (ok(*residual) && residual->sizes() == x.sizes()), "residual must match x");
+    TORCH_CHECK(!sum_out.has_value() || (residual.has_value() && ok(*sum_out) && sum_out->sizes() == x.sizes()),
+                "sum_out needs a residual and must match x");
+    int dev = x.get_device();
+    c10::cuda::CUDAGuard guard(dev);
+    rt_check(launch_rms_norm(x.data_ptr(), residual ? residual->data_ptr() : nullptr, w.data_ptr(),
+                             sum_out ? sum_out->data_ptr() : nullptr, out.data_ptr(), (int)x.size(0),
+                             (int)x.size(1), (float)eps, current_stream(dev)), "rms_norm");
+  }, py::arg("x"), py::arg("residual"), py::arg("w"), py::arg("sum_out"), py::arg("out"), py::arg("eps"));
+  m.def("rope_inplace", [](torch::Tensor qkv, int n_heads, int head_dim, int seq, int pos0, double theta,
+                           int num_sms) {
+    TORCH_CHECK(qkv.is_cuda() && qkv.is_contiguous() && qkv.dim() == 2 && qkv.scalar_type() == torch::kBFloat16,
+                "rope_inplace: qkv[tokens, row] contiguous bf16 on the GPU");
+    int dev = qkv.get_device();
+    c10::cuda::CUDAGuard guard(dev);
+    rt_check(launch_rope_inplace(qkv.data_ptr(), qkv.size(0), (int)qkv.size(1), n_heads, head_dim, seq, pos0,
+                                 (float)theta, num_sms, current_stream(dev)), "rope_inplace");
+  });
+  m.def("silu_mul", [](torch::Tensor gate_up, torch::Tensor out, int num_sms) {
+    auto ok = [](const torch::Tensor& t) {
+      return t.is_cuda() && t.is_contiguous() && t.dim() == 2 && t.scalar_type() == torch::kBFloat16;
+    };
+    TORCH_CHECK(ok(gate_up) && ok(out) && gate_up.size(1) == 2 * out.size(1) && gate_up.size(0) == out.size(0),
+                "silu_mul: gate_up[rows, 2F], out[rows, F], contiguous bf16 on the GPU");
+    int dev = gate_up.get_device();
+    c10::cuda::CUDAGuard guard(dev);
+    rt_check(launch_silu_mul(gate_up.data_ptr(), out.data_ptr(), gate_up.size(0), (int)out.size(1), num_sms,
+                             current_stream(dev)), "silu_mul");
+  });
+
   // ---- oracles (CPU tensors) ----
+  m.def("oracle_rms_norm_bf16", [](torch::Tensor x, c10::optional<torch::Tensor> residual, torch::Tensor w,
+                                   double eps) {
+    TORCH_CHECK(x.dim() == 2 && w.dim() == 1 && w.size(0) == x.size(1), "x[rows, H], w[H]");
+    torch::Tensor out = torch::empty_like(x), sum = torch::empty_like(x);
+    rms_norm_bf16(bf16_ptr(x), residual ? bf16_ptr(*residual) : nullptr, bf16_ptr(w),
+                  residual ? reinterpret_cast<uint16_t*>(sum.data_ptr()) : nullptr,
+                  reinterpret_cast<uint16_t*>(out.data_ptr()), (int)x.size(0), (int)x.size(1), (float)eps);
+    return std::make_pair(out, residual ? sum : x);
+  });
+  m.def("oracle_rope_bf16", [](torch::Tensor qkv, int n_heads, int head_dim, int seq, int pos0, double theta) {
+    TORCH_CHECK(qkv.dim() == 2 && (int64_t)n_heads * head_dim <= qkv.size(1) && head_dim % 2 == 0, "qkv[tokens, row]");
+    bf16_ptr(qkv);   // dtype / device / contiguity check
+    torch::Tensor out = qkv.clone();
+    rope_bf16(reinterpret_cast<uint16_t*>(out.data_ptr()), out.size(0), (int)out.size(1), n_heads, head_dim, seq,
+              pos0, (float)theta);
+    return out;
+  });
+  m.def("oracle_silu_mul_bf16", [](torch::Tensor gu) {
+    TORCH_CHECK(gu.dim() == 2 && gu.size(1) % 2 == 0, "gate_up[rows, 2F]");
+    torch::Tensor out = torch::empty({gu.size(0), gu.size(1) / 2}, gu.options());
+    silu_mul_bf16(bf16_ptr(gu), reinterpret_cast<uint16_t*>(out.data_ptr()), gu.size(0), (int)gu.size(1) / 2);
+    return out;
+  });
   m.def("oracle_ordered_sum_bf16", [](std::vector<torch::Tensor> srcs) {
     TORCH_CHECK(!srcs.empty(), "need at least one source");
     std::vector<const uint16_t*> p;

@@ -137,4 +137,16 @@ struct MatmulRsArgs {
 size_t matmul_rs_workspace_bytes(int M, int N);
 int launch_matmul_reduce_scatter(const MatmulRsArgs& args, cudaStream_t stream);
 
+// ---- rank-local layer glue (layer_glue.cu): bf16 data, fp32 math, one pass each ----
+// out[rows, H] = RMSNorm(x (+ residual)) * w.  With `residual`, `sum_out` (optional) receives
+// bf16(x + residual).  Outputs must not alias inputs.  H % 8 == 0, 16-byte aligned pointers.
+int launch_rms_norm(const void* x, const void* residual, const void* w, void* sum_out, void* out, int rows, int H,
+                    float eps, cudaStream_t stream);
+// Rotary embedding in place on heads [0, n_heads) of every row (`row_stride` elements per row);
+// token t is at position pos0 + t % seq.  head_dim % 16 == 0.
+int launch_rope_inplace(void* qkv, long long tokens, int row_stride, int n_heads, int head_dim, int seq, int pos0,
+                        float theta, int num_sms, cudaStream_t stream);
+// out[rows, F] = SiLU(gate_up[:, :F]) * gate_up[:, F:].  F % 8 == 0.
+int launch_silu_mul(const void* gate_up, void* out, long long rows, int F, int num_sms, cudaStream_t stream);
+
 }  // namespace smr

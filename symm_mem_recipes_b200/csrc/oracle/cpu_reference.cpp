@@ -1,5 +1,6 @@
 #include "cpu_reference.h"
 
+#include <cmath>
 #include <vector>
 
 namespace smr {
@@ -44,6 +45,55 @@ void gemv_f32(const uint16_t* x, const uint16_t* w, float* y, int B, int K, int 
       for (int n = 0; n < N; ++n) yr[n] += xv * bf16_to_f32(wr[n]);
     }
   }
+}
+
+void rms_norm_bf16(const uint16_t* x, const uint16_t* residual, const uint16_t* w, uint16_t* sum_out,
+                   uint16_t* out, int rows, int H, float eps) {
+  std::vector<float> s((size_t)H);
+  for (int r = 0; r < rows; ++r) {
+    const size_t o = (size_t)r * H;
+    double ss = 0.0;
+    for (int i = 0; i < H; ++i) {
+      float v = bf16_to_f32(x[o + i]);
+      if (residual != nullptr) {
+        uint16_t sum = f32_to_bf16(v + bf16_to_f32(residual[o + i]));
+        if (sum_out != nullptr) sum_out[o + i] = sum;
+        v = bf16_to_f32(sum);
+      }
+      s[i] = v;
+      ss += (double)v * v;
+    }
+    const float scale = 1.0f / std::sqrt((float)(ss / H) + eps);
+    for (int i = 0; i < H; ++i) {
+      const float n = bf16_to_f32(f32_to_bf16(s[i] * scale));
+      out[o + i] = f32_to_bf16(n * bf16_to_f32(w[i]));
+    }
+  }
+}
+
+void rope_bf16(uint16_t* qkv, long long tokens, int row_stride, int n_heads, int D, int seq, int pos0, float theta) {
+  const int half = D / 2;
+  for (long long t = 0; t < tokens; ++t) {
+    const double pos = (double)(pos0 + (int)(t % seq));
+    for (int h = 0; h < n_heads; ++h) {
+      uint16_t* base = qkv + t * row_stride + (long long)h * D;
+      for (int i = 0; i < half; ++i) {
+        const double ang = pos * std::pow((double)theta, -2.0 * i / D);
+        const float cs = (float)std::cos(ang), sn = (float)std::sin(ang);
+        const float x1 = bf16_to_f32(base[i]), x2 = bf16_to_f32(base[i + half]);
+        base[i] = f32_to_bf16(x1 * cs - x2 * sn);
+        base[i + half] = f32_to_bf16(x2 * cs + x1 * sn);
+      }
+    }
+  }
+}
+
+void silu_mul_bf16(const uint16_t* gu, uint16_t* out, long long rows, int F) {
+  for (long long r = 0; r < rows; ++r)
+    for (int c = 0; c < F; ++c) {
+      const float g = bf16_to_f32(gu[r * 2 * F + c]), u = bf16_to_f32(gu[r * 2 * F + F + c]);
+      out[r * F + c] = f32_to_bf16(g / (1.0f + std::exp(-g)) * u);
+    }
 }
 
 }  // namespace smr

@@ -8,6 +8,8 @@
 //    NVSwitch does for multimem.ld_reduce with .acc::f32, up to its own
 //    summation order).
 //  * GEMM / GEMV: fp32 accumulate over K, round to bf16 once.
+//  * RMSNorm, rotary embedding, SiLU-mul: fp32 math on bf16 data, rounding
+//    where the kernels round.
 #pragma once
 #include <stddef.h>
 #include <stdint.h>
@@ -37,5 +39,16 @@ void fp32_sum_bf16(const uint16_t* const* srcs, int n_src, uint16_t* out, size_t
 void gemm_nt_bf16(const uint16_t* a, const uint16_t* b, uint16_t* c, int M, int N, int K);
 // y[B,N] (fp32) = x[B,K] * w[K,N]
 void gemv_f32(const uint16_t* x, const uint16_t* w, float* y, int B, int K, int N);
+
+// Layer glue (kernels/layer_glue.cu), same rounding points as the kernels:
+// s = x (+ r, rounded to bf16, stored to sum_out when given);
+// out = bf16( bf16(s * rsqrt(mean(s^2) + eps)) * w )
+void rms_norm_bf16(const uint16_t* x, const uint16_t* residual, const uint16_t* w, uint16_t* sum_out,
+                   uint16_t* out, int rows, int H, float eps);
+// in place: heads [0, n_heads) of every row of `row_stride` elements, pairs (i, i + D/2),
+// angle = (pos0 + t % seq) * theta^(-2i/D)
+void rope_bf16(uint16_t* qkv, long long tokens, int row_stride, int n_heads, int D, int seq, int pos0, float theta);
+// out[T, F] = bf16( silu(gu[:, :F]) * gu[:, F:] )
+void silu_mul_bf16(const uint16_t* gu, uint16_t* out, long long rows, int F);
 
 }  // namespace smr

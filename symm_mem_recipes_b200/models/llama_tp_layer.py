@@ -17,11 +17,17 @@ projections use the fused GEMV + all-reduce.
 collectives and cuBLAS and are the baseline the fused layer is timed against.
 The upstream recipes stop at the single fused op; this module is how the ops
 compose in the workload they were written for (Llama-3-70B at TP8: hidden
-8192, 64 query / 8 KV heads of 128, FFN 28672).  Norms, RoPE, attention and
-the activation are ordinary PyTorch ops: they are rank-local.
+8192, 64 query / 8 KV heads of 128, FFN 28672).  Attention is PyTorch's
+scaled_dot_product_attention (rank-local).  Norms, RoPE and the activation are
+PyTorch compositions by default; `fused_glue=True` (or SMR_FUSED_GLUE=1) swaps
+in the single-pass kernels of `ops.layer_glue`: RMSNorm writes straight into
+the symmetric buffer the next all_gather_matmul reads (and folds in the
+residual add before it), RoPE rotates Q and K in place inside the QKV buffer,
+SiLU(gate) * up is one pass.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Optional
 
@@ -74,8 +80,9 @@ class LlamaTPDecoderLayer:
     reference forward passes.  Plain object, inference only."""
 
     def __init__(self, cfg: LlamaTPConfig, device: torch.device, group=None, seed: int = 0,
-                 dtype: torch.dtype = torch.bfloat16):
+                 dtype: torch.dtype = torch.bfloat16, fused_glue: Optional[bool] = None):
         self.cfg, self.device, self.group = cfg, device, group
+        self.fused_glue = (os.environ.get("SMR_FUSED_GLUE", "0") == "1") if fused_glue is None else bool(fused_glue)
         self.ws = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         ws = self.ws
@@ -100,6 +107,28 @@ class LlamaTPDecoderLayer:
         self.norm1 = (1.0 + 0.1 * torch.randn(H, generator=gn)).to(dtype).to(device)
         self.norm2 = (1.0 + 0.1 * torch.randn(H, generator=gn)).to(dtype).to(device)
         self._sym: dict[tuple, torch.Tensor] = {}
+        # set to a list to get (phase name, CUDA event) pairs appended by `forward` (see `phase_times_us`)
+        self.phase_marks: Optional[list] = None
+
+    def _mark(self, name: str) -> None:
+        if self.phase_marks is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self.phase_marks.append((name, ev))
+
+    def phase_times_us(self, x_shard: torch.Tensor, batch: int, seq: int, iters: int = 5) -> dict:
+        """Device time of every phase of `forward` (CUDA events between the
+        phases, mean over `iters` calls after one warm-up), in µs."""
+        self.forward(x_shard, batch, seq)
+        totals: dict[str, float] = {}
+        for _ in range(iters):
+            self.phase_marks = []
+            self.forward(x_shard, batch, seq)
+            marks, self.phase_marks = self.phase_marks, None
+            torch.cuda.synchronize(self.device)
+            for (_, e0), (name, e1) in zip(marks[:-1], marks[1:]):
+                totals[name] = totals.get(name, 0.0) + e0.elapsed_time(e1) * 1e3 / iters
+        return totals
 
     # ---- symmetric staging for the gather inputs ----
     def _symmetric(self, tag: str, rows: int) -> torch.Tensor:
@@ -112,21 +141,28 @@ class LlamaTPDecoderLayer:
         return t
 
     # ---- rank-local attention on [T, (hq + 2 hkv) * D] ----
-    def _attention(self, qkv: torch.Tensor, batch: int, seq: int) -> torch.Tensor:
+    def _attention(self, qkv: torch.Tensor, batch: int, seq: int, glue: bool = False) -> torch.Tensor:
         D, hq, hkv = self.cfg.head_dim, self.hq, self.hkv
+        if glue:
+            ops.rope_(qkv, hq + hkv, D, seq, self.cfg.rope_theta)      # Q and K heads, in place
         q, k, v = qkv.split([hq * D, hkv * D, hkv * D], dim=-1)
         q = q.view(batch, seq, hq, D)
         k = k.view(batch, seq, hkv, D)
         v = v.view(batch, seq, hkv, D)
-        pos = torch.arange(seq, device=qkv.device)[None, :].expand(batch, seq)
-        q, k = _rope(q, pos, self.cfg.rope_theta), _rope(k, pos, self.cfg.rope_theta)
+        if not glue:
+            pos = torch.arange(seq, device=qkv.device)[None, :].expand(batch, seq)
+            q, k = _rope(q, pos, self.cfg.rope_theta), _rope(k, pos, self.cfg.rope_theta)
         o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
                                            is_causal=True, enable_gqa=True)
         return o.transpose(1, 2).reshape(batch * seq, hq * D).contiguous()
 
-    def _mlp_act(self, gu: torch.Tensor) -> torch.Tensor:
-        gate, up = gu.split(self.ffn_local, dim=-1)
+    @staticmethod
+    def _mlp_act_torch(gu: torch.Tensor, ffn_local: int) -> torch.Tensor:
+        gate, up = gu.split(ffn_local, dim=-1)
         return (F.silu(gate.float()) * up.float()).to(gu.dtype).contiguous()
+
+    def _mlp_act(self, gu: torch.Tensor) -> torch.Tensor:
+        return ops.silu_mul(gu) if self.fused_glue else self._mlp_act_torch(gu, self.ffn_local)
 
     # ------------------------------------------------------------------
     def forward(self, x_shard: torch.Tensor, batch: int, seq: int, barrier_between_phases: bool = False
@@ -136,19 +172,38 @@ class LlamaTPDecoderLayer:
         rows = x_shard.shape[0]
         assert rows * self.ws == batch * seq
         h = self._symmetric("attn_in", rows)
-        h.copy_(_rms_norm(x_shard, self.norm1, cfg.eps))
+        self._mark("start")
+        if self.fused_glue:
+            ops.rms_norm(x_shard, self.norm1, cfg.eps, out=h)
+        else:
+            h.copy_(_rms_norm(x_shard, self.norm1, cfg.eps))
+        self._mark("norm1")
         qkv = ops.all_gather_matmul(h, self.w_qkv, group=self.group)
-        attn = self._attention(qkv, batch, seq)
+        self._mark("qkv_all_gather_matmul")
+        attn = self._attention(qkv, batch, seq, glue=self.fused_glue)
+        self._mark("rope_attention")
         if barrier_between_phases:
             symm_mem.rendezvous(h, self.group).barrier(channel=1)
-        x1 = x_shard + ops.matmul_reduce_scatter(attn, self.w_o, group=self.group)
         h2 = self._symmetric("mlp_in", rows)
-        h2.copy_(_rms_norm(x1, self.norm2, cfg.eps))
+        o = ops.matmul_reduce_scatter(attn, self.w_o, group=self.group)
+        self._mark("o_proj_reduce_scatter")
+        if self.fused_glue:
+            _, x1 = ops.rms_norm(x_shard, self.norm2, cfg.eps, out=h2, residual=o)    # x1 = x_shard + o
+        else:
+            x1 = x_shard + o
+            h2.copy_(_rms_norm(x1, self.norm2, cfg.eps))
+        self._mark("residual_norm2")
         gu = ops.all_gather_matmul(h2, self.w_gate_up, group=self.group)
+        self._mark("gate_up_all_gather_matmul")
         act = self._mlp_act(gu)
+        self._mark("silu_mul")
         if barrier_between_phases:
             symm_mem.rendezvous(h2, self.group).barrier(channel=2)
-        return x1 + ops.matmul_reduce_scatter(act, self.w_down, group=self.group)
+        d = ops.matmul_reduce_scatter(act, self.w_down, group=self.group)
+        self._mark("down_proj_reduce_scatter")
+        y = x1 + d
+        self._mark("residual")
+        return y
 
     def forward_reference(self, x_shard: torch.Tensor, batch: int, seq: int) -> torch.Tensor:
         """The same layer from NCCL all-gather / reduce-scatter and cuBLAS."""
@@ -172,7 +227,7 @@ class LlamaTPDecoderLayer:
         attn = self._attention(h @ self.w_qkv.t(), batch, seq)
         x1 = x_shard + scatter(attn @ self.w_o.t())
         h2 = gather(_rms_norm(x1, self.norm2, cfg.eps))
-        act = self._mlp_act(h2 @ self.w_gate_up.t())
+        act = self._mlp_act_torch(h2 @ self.w_gate_up.t(), self.ffn_local)
         return x1 + scatter(act @ self.w_down.t())
 
     # ------------------------------------------------------------------
@@ -188,17 +243,23 @@ class LlamaTPDecoderLayer:
                 return ops.gemv_all_reduce(act, w_t, group=self.group)
             return ops.reference_gemv_all_reduce(act, w_t, group=self.group)
 
-        qkv = _rms_norm(x, self.norm1, cfg.eps) @ self.w_qkv.t()
+        glue = fused and self.fused_glue
+        norm = (lambda t, w: ops.rms_norm(t, w, cfg.eps)) if glue else (lambda t, w: _rms_norm(t, w, cfg.eps))
+        qkv = norm(x, self.norm1) @ self.w_qkv.t()
+        if glue:
+            ops.rope_(qkv, hq + hkv, D, 1, cfg.rope_theta, pos0=pos)
         q, k, v = qkv.split([hq * D, hkv * D, hkv * D], dim=-1)
-        p = torch.full((B, 1), pos, device=x.device)
-        q = _rope(q.view(B, 1, hq, D), p, cfg.rope_theta)
-        k = _rope(k.view(B, 1, hkv, D), p, cfg.rope_theta)
+        q, k = q.view(B, 1, hq, D), k.view(B, 1, hkv, D)
+        if not glue:
+            p = torch.full((B, 1), pos, device=x.device)
+            q, k = _rope(q, p, cfg.rope_theta), _rope(k, p, cfg.rope_theta)
         k_cache[:, pos] = k[:, 0]
         v_cache[:, pos] = v.view(B, hkv, D)
         o = F.scaled_dot_product_attention(q.transpose(1, 2), k_cache[:, : pos + 1].transpose(1, 2),
                                            v_cache[:, : pos + 1].transpose(1, 2), enable_gqa=True)
         x1 = x + row_parallel(o.transpose(1, 2).reshape(B, hq * D).contiguous(), self.w_o_t)
-        act = self._mlp_act(_rms_norm(x1, self.norm2, cfg.eps) @ self.w_gate_up.t())
+        gu = norm(x1, self.norm2) @ self.w_gate_up.t()
+        act = ops.silu_mul(gu) if glue else LlamaTPDecoderLayer._mlp_act_torch(gu, self.ffn_local)
         return x1 + row_parallel(act, self.w_down_t)
 
 

@@ -1,0 +1,71 @@
+"""Rank-local glue of a decoder layer as single-pass CUDA kernels: RMSNorm
+(optionally fused with the residual add before it), rotary embedding in place
+on the QKV buffer, and SiLU(gate) * up.  bf16 data, fp32 math.
+
+No upstream counterpart.  They exist because the PyTorch compositions
+(`x.float()...`, `torch.cat`, `F.silu(g.float()) * u.float()`) make five to
+ten passes with fp32 temporaries over tensors as large as the GEMM outputs,
+which at Llama-70B prefill sizes costs more than the o-projection GEMM.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .._ext import C
+from ..errors import SymmMemError
+from ..utils.trace import traced
+from .ag_matmul import _num_sms
+
+
+def _check(name: str, t: torch.Tensor, dim: int) -> None:
+    if t.dim() != dim or t.dtype != torch.bfloat16 or not t.is_cuda or not t.is_contiguous():
+        raise SymmMemError(f"{name} must be a contiguous {dim}-D bfloat16 CUDA tensor")
+
+
+@traced("smr.rms_norm")
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: Optional[torch.Tensor] = None,
+             residual: Optional[torch.Tensor] = None, sum_out: Optional[torch.Tensor] = None):
+    """`out = bf16(bf16(s * rsqrt(mean(s^2) + eps)) * weight)` per row of `s`,
+    where `s = x`, or `bf16(x + residual)` when a residual is given (then `s`
+    itself is written to `sum_out` if provided).  `out` may be a symmetric
+    buffer, so the result lands where `all_gather_matmul` reads it.  Returns
+    `out`, or `(out, sum_out)` with a residual."""
+    _check("x", x, 2)
+    _check("weight", weight, 1)
+    if x.shape[1] % 8 or weight.shape[0] != x.shape[1]:
+        raise SymmMemError("need x[rows, H], weight[H] with H a multiple of 8")
+    if out is None:
+        out = torch.empty_like(x)
+    if residual is not None and sum_out is None:
+        sum_out = torch.empty_like(x)
+    if residual is None and sum_out is not None:
+        raise SymmMemError("sum_out is only written when a residual is given")
+    C.rms_norm(x, residual, weight, sum_out, out, float(eps))
+    return out if residual is None else (out, sum_out)
+
+
+@traced("smr.rope_")
+def rope_(qkv: torch.Tensor, n_heads: int, head_dim: int, seq: int, theta: float, pos0: int = 0) -> torch.Tensor:
+    """Rotate heads `[0, n_heads)` of every row of `qkv` [tokens, row] in place
+    (Llama pairing `(i, i + head_dim/2)`); token `t` is at position
+    `pos0 + t % seq`.  With the Q heads followed by the K heads at the start of
+    the row, `n_heads = q_heads + kv_heads` rotates both and leaves V alone."""
+    _check("qkv", qkv, 2)
+    if head_dim % 16 or n_heads * head_dim > qkv.shape[1] or qkv.shape[1] % 8:
+        raise SymmMemError("need head_dim % 16 == 0, n_heads * head_dim <= row length, row length % 8 == 0")
+    C.rope_inplace(qkv, int(n_heads), int(head_dim), int(seq), int(pos0), float(theta), _num_sms(qkv.device))
+    return qkv
+
+
+@traced("smr.silu_mul")
+def silu_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """`out[rows, F] = SiLU(gate_up[:, :F]) * gate_up[:, F:]`."""
+    _check("gate_up", gate_up, 2)
+    if gate_up.shape[1] % 16:
+        raise SymmMemError("gate_up must be [rows, 2F] with F a multiple of 8")
+    if out is None:
+        out = torch.empty(gate_up.shape[0], gate_up.shape[1] // 2, dtype=torch.bfloat16, device=gate_up.device)
+    C.silu_mul(gate_up, out, _num_sms(gate_up.device))
+    return out

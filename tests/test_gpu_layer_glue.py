@@ -1,0 +1,87 @@
+"""RMSNorm, rotary embedding and SiLU-mul kernels against their CPU oracles
+(same rounding points) and, through the decoder layer, against fp32.
+
+Marked `first_run`: compiled for sm_100a, CPU oracles tested, first run on
+hardware pending (opt in with SMR_TEST_FIRST_RUN=1).
+"""
+import pytest
+import torch
+
+pytestmark = [pytest.mark.gpu, pytest.mark.first_run]
+
+
+def _ulp_close(got, ref, extra_abs=1e-6):
+    # fast-math exp / rsqrt / sincos may flip the final bf16 rounding: one ulp
+    err = (got.float().cpu() - ref.float()).abs()
+    return bool((err <= ref.float().abs() * 2.0 ** -7 + extra_abs).all()), float(err.max())
+
+
+@pytest.mark.parametrize("rows,H", [(1, 8), (37, 512), (300, 8192), (5, 16384 + 8)])
+def test_rms_norm(rows, H):
+    from symm_mem_recipes_b200 import ops
+    from symm_mem_recipes_b200._ext import C
+    from symm_mem_recipes_b200.utils.testing import guarded_empty
+
+    g = torch.Generator().manual_seed(rows + H)
+    x = (torch.randn(rows, H, generator=g) * 0.7).to(torch.bfloat16)
+    r = (torch.randn(rows, H, generator=g) * 0.3).to(torch.bfloat16)
+    w = (1.0 + 0.1 * torch.randn(H, generator=g)).to(torch.bfloat16)
+    ref, _ = C.oracle_rms_norm_bf16(x, None, w, 1e-5)
+    out, intact = guarded_empty((rows, H), torch.bfloat16, "cuda")
+    ops.rms_norm(x.cuda(), w.cuda(), 1e-5, out=out)
+    ok, err = _ulp_close(out, ref)
+    assert ok and intact(), err
+    ref2, sum2 = C.oracle_rms_norm_bf16(x, r, w, 1e-5)
+    out2, s2 = ops.rms_norm(x.cuda(), w.cuda(), 1e-5, residual=r.cuda())
+    assert torch.equal(s2.cpu(), sum2)
+    ok, err = _ulp_close(out2, ref2)
+    assert ok, err
+
+
+@pytest.mark.parametrize("batch,seq,hq,hkv,D,pos0", [(2, 24, 4, 1, 64, 0), (1, 2048, 8, 1, 128, 0), (4, 1, 8, 1, 128, 1777)])
+def test_rope(batch, seq, hq, hkv, D, pos0):
+    from symm_mem_recipes_b200 import ops
+    from symm_mem_recipes_b200._ext import C
+
+    g = torch.Generator().manual_seed(seq + D)
+    qkv = torch.randn(batch * seq, (hq + 2 * hkv) * D, generator=g).to(torch.bfloat16)
+    ref = C.oracle_rope_bf16(qkv, hq + hkv, D, seq, pos0, 500000.0)
+    got = ops.rope_(qkv.cuda(), hq + hkv, D, seq, 500000.0, pos0=pos0)
+    # fp32 angles (the oracle's are fp64): up to ~2e-4 rad at position 2048
+    ok, err = _ulp_close(got, ref, extra_abs=4e-3)
+    assert ok, err
+    assert torch.equal(got[:, (hq + hkv) * D:].cpu(), qkv[:, (hq + hkv) * D:])     # V untouched
+
+
+@pytest.mark.parametrize("rows,F", [(1, 8), (19, 48), (4096, 3584)])
+def test_silu_mul(rows, F):
+    from symm_mem_recipes_b200 import ops
+    from symm_mem_recipes_b200._ext import C
+    from symm_mem_recipes_b200.utils.testing import guarded_empty
+
+    g = torch.Generator().manual_seed(rows + F)
+    gu = (torch.randn(rows, 2 * F, generator=g) * 3.0).to(torch.bfloat16)
+    ref = C.oracle_silu_mul_bf16(gu)
+    out, intact = guarded_empty((rows, F), torch.bfloat16, "cuda")
+    ops.silu_mul(gu.cuda(), out)
+    ok, err = _ulp_close(out, ref)
+    assert ok and intact(), err
+
+
+def test_layer_with_fused_glue_matches_fp32():
+    from symm_mem_recipes_b200.models.llama_tp_layer import (LlamaTPConfig, LlamaTPDecoderLayer,
+                                                             full_precision_reference)
+
+    dev = torch.device("cuda", 0)
+    cfg = LlamaTPConfig.tiny(1)
+    layer = LlamaTPDecoderLayer(cfg, dev, seed=1, fused_glue=True)
+    batch, seq = 2, 128
+    torch.manual_seed(3)
+    x = (torch.randn(batch * seq, cfg.hidden, device=dev) * 0.5).to(torch.bfloat16)
+    y = layer.forward(x, batch, seq)
+    y_plain = LlamaTPDecoderLayer(cfg, dev, seed=1, fused_glue=False).forward(x, batch, seq)
+    weights = [(layer.w_qkv.cpu(), layer.w_o.cpu(), layer.w_gate_up.cpu(), layer.w_down.cpu(),
+                layer.norm1.cpu(), layer.norm2.cpu())]
+    ref = full_precision_reference(weights, cfg, x.cpu(), batch, seq)
+    assert (y.float().cpu() - ref).abs().max().item() < 0.1
+    assert (y.float() - y_plain.float()).abs().max().item() < 0.1

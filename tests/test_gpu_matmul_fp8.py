@@ -3,21 +3,16 @@ follows `a_shard`, as upstream's FP8_OUTPUT switch does,
 symm_mem_recipes/triton_all_gather_matmul.py:123, 311).
 
 The fp8 instantiations of the CTA-pair kernel have been compiled for sm_100a
-but have not yet had a first run on hardware, so these tests are opt-in:
-set SMR_TEST_FP8=1.  Every case runs in a child process.
+but have not yet had a first run on hardware, so these tests carry the
+`first_run` marker (opt in with SMR_TEST_FIRST_RUN=1).  Every case runs in a
+child process.
 """
-import os
-
 import pytest
 import torch
 
 from symm_mem_recipes_b200.utils.testing import spawn_ranks
 
-pytestmark = [
-    pytest.mark.gpu,
-    pytest.mark.skipif(os.environ.get("SMR_TEST_FP8") != "1",
-                       reason="fp8 kernels await their first run on hardware; opt in with SMR_TEST_FP8=1"),
-]
+pytestmark = [pytest.mark.gpu, pytest.mark.first_run]
 
 FP8 = torch.float8_e4m3fn
 

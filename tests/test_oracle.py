@@ -44,3 +44,67 @@ def test_gemv():
     w = (torch.randn(96, 40) * 0.1).to(torch.bfloat16)
     ref = x.float() @ w.float()
     assert torch.allclose(C.oracle_gemv_f32(x, w), ref, rtol=1e-4, atol=1e-5)
+
+
+# ---- layer glue: the oracles restate the kernels' rounding points; PyTorch restates the layer's math ----
+def _glue_inputs(rows, H, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    x = (torch.randn(rows, H, generator=g) * 0.7).to(torch.bfloat16)
+    r = (torch.randn(rows, H, generator=g) * 0.3).to(torch.bfloat16)
+    w = (1.0 + 0.1 * torch.randn(H, generator=g)).to(torch.bfloat16)
+    return x, r, w
+
+
+def test_rms_norm_oracle_matches_the_layer_math():
+    from symm_mem_recipes_b200._ext import C
+    from symm_mem_recipes_b200.models.llama_tp_layer import _rms_norm
+
+    x, r, w = _glue_inputs(37, 512)
+    out, s = C.oracle_rms_norm_bf16(x, None, w, 1e-5)
+    assert s.data_ptr() == x.data_ptr() or torch.equal(s, x)
+    ref = _rms_norm(x, w, 1e-5)
+    # the same rounding points; the mean is summed in another order, which may flip a rounding
+    diff = (out.float() - ref.float()).abs()
+    assert float((diff > 0).float().mean()) < 0.01
+    assert bool((diff <= ref.float().abs() * 2.0 ** -7 + 1e-6).all())
+    out2, s2 = C.oracle_rms_norm_bf16(x, r, w, 1e-5)
+    assert torch.equal(s2, x + r)
+    ref2 = _rms_norm(x + r, w, 1e-5)
+    diff2 = (out2.float() - ref2.float()).abs()
+    assert bool((diff2 <= ref2.float().abs() * 2.0 ** -7 + 1e-6).all())
+
+
+def test_rope_oracle_matches_the_layer_math():
+    from symm_mem_recipes_b200._ext import C
+    from symm_mem_recipes_b200.models.llama_tp_layer import _rope
+
+    batch, seq, hq, hkv, D = 2, 24, 4, 1, 64
+    g = torch.Generator().manual_seed(3)
+    qkv = (torch.randn(batch * seq, (hq + 2 * hkv) * D, generator=g)).to(torch.bfloat16)
+    out = C.oracle_rope_bf16(qkv, hq + hkv, D, seq, 0, 500000.0)
+    pos = torch.arange(seq)[None, :].expand(batch, seq)
+    q, k, v = qkv.split([hq * D, hkv * D, hkv * D], dim=-1)
+    ref_q = _rope(q.reshape(batch, seq, hq, D), pos, 500000.0).reshape(batch * seq, hq * D)
+    ref_k = _rope(k.reshape(batch, seq, hkv, D), pos, 500000.0).reshape(batch * seq, hkv * D)
+    got_q, got_k, got_v = out.split([hq * D, hkv * D, hkv * D], dim=-1)
+    assert torch.equal(got_v, v)                                   # V is not rotated
+    for got, ref in ((got_q, ref_q), (got_k, ref_k)):
+        assert bool(((got.float() - ref.float()).abs() <= 2.0 ** -7 * ref.float().abs() + 2e-3).all())
+    # decode form: one token per sequence at position 17
+    one = qkv[:batch].clone()
+    dec = C.oracle_rope_bf16(one, hq + hkv, D, 1, 17, 500000.0)
+    p17 = torch.full((batch, 1), 17)
+    ref17 = _rope(one[:, : hq * D].reshape(batch, 1, hq, D), p17, 500000.0).reshape(batch, hq * D)
+    assert bool(((dec[:, : hq * D].float() - ref17.float()).abs() <= 2.0 ** -7 * ref17.float().abs() + 2e-3).all())
+
+
+def test_silu_mul_oracle_matches_the_layer_math():
+    from symm_mem_recipes_b200._ext import C
+
+    g = torch.Generator().manual_seed(5)
+    gu = (torch.randn(19, 2 * 48, generator=g) * 3.0).to(torch.bfloat16)
+    out = C.oracle_silu_mul_bf16(gu)
+    gate, up = gu.split(48, dim=-1)
+    ref = (torch.nn.functional.silu(gate.float()) * up.float()).to(torch.bfloat16)
+    diff = (out.float() - ref.float()).abs()
+    assert bool((diff <= ref.float().abs() * 2.0 ** -7 + 1e-6).all())
