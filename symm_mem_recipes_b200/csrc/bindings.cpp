@@ -566,7 +566,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("matmul_rs_workspace_bytes", &matmul_rs_workspace_bytes);
   m.def("matmul_reduce_scatter", [](torch::Tensor a, torch::Tensor b, torch::Tensor out,
                                     const std::shared_ptr<CudaSymmAllocation>& workspace, int num_sms,
-                                    uint64_t timeout_ns, c10::optional<torch::Tensor> trace, bool deep_strips) {
+                                    uint64_t timeout_ns, c10::optional<torch::Tensor> trace, bool deep_strips,
+                                    bool cta_pair) {
     auto ok2d = [](const torch::Tensor& t) {
       return t.is_cuda() && t.dim() == 2 && t.is_contiguous() && t.scalar_type() == torch::kBFloat16;
     };
@@ -596,9 +597,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       args.trace = reinterpret_cast<uint64_t*>(trace->data_ptr());
     }
     args.deep_strips = deep_strips;
+    args.cta_pair = cta_pair;
     rt_check(launch_matmul_reduce_scatter(args, current_stream(dev)), "matmul_reduce_scatter");
   }, py::arg("a"), py::arg("b"), py::arg("out"), py::arg("workspace"), py::arg("num_sms"),
-     py::arg("timeout_ns"), py::arg("trace") = py::none(), py::arg("deep_strips") = false);
+     py::arg("timeout_ns"), py::arg("trace") = py::none(), py::arg("deep_strips") = false,
+     py::arg("cta_pair") = false);
 
   // ---- rank-local layer glue ----
   m.def("rms_norm", [](torch::Tensor x, c10::optional<torch::Tensor> residual, torch::Tensor w,

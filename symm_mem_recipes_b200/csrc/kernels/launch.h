@@ -133,9 +133,12 @@ struct MatmulRsArgs {
   Status* status;
   uint64_t* trace;     // optional [num_sms][4] %globaltimer stamps per CTA (start, entered, GEMM done, reduced)
   bool deep_strips;    // 3-stage ring and five epilogue strips on the wire instead of 4 stages and two
+  bool cta_pair;       // tcgen05 cta_group::2 main loop (256 x 256 tiles on CTA pairs), 5 stages, four strips
 };
 size_t matmul_rs_workspace_bytes(int M, int N);
+// Dispatches on `cta_pair` / `deep_strips`; same workspace layout and result bits for every variant.
 int launch_matmul_reduce_scatter(const MatmulRsArgs& args, cudaStream_t stream);
+int launch_matmul_reduce_scatter_2cta(const MatmulRsArgs& args, cudaStream_t stream);
 
 // ---- rank-local layer glue (layer_glue.cu): bf16 data, fp32 math, one pass each ----
 // out[rows, H] = RMSNorm(x (+ residual)) * w.  With `residual`, `sum_out` (optional) receives

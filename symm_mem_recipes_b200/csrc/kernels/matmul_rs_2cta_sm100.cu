@@ -1,0 +1,346 @@
+// Fused GEMM + reduce-scatter on CTA pairs (tcgen05 `cta_group::2`): the main
+// loop of ag_matmul_2cta_sm100.cu under the epilogue and reduction of
+// matmul_rs_sm100.cu.  No upstream counterpart.
+//
+// A pair of CTAs on neighbouring SMs multiplies one [256 x 256] tile: each CTA
+// stages its own 128 rows of A and its own half of the B tile (ordinary TMA
+// loads, no multicast qualifier), the leader's MMA thread issues one
+// `tcgen05.mma.cta_group::2` per 16 elements of K, and each CTA finds its 128
+// accumulator rows in its own TMEM.  Per flop an SM pulls half as many B bytes
+// from L2 as in the 1-CTA kernel, and a stage is 32 KB instead of 48 KB, which
+// pays for five stages AND four 16 KB epilogue strips on the wire.
+//
+// The two row blocks of a pair are consecutive entries of the list of
+// (destination, row block) pairs in visiting order (destination rank+1 first,
+// own rows last), so they may belong to different destinations; each CTA
+// converts, ships and signals its own block exactly as the 1-CTA kernel does.
+// With an odd number of row blocks the last pair's second CTA multiplies
+// zero rows (out-of-range TMA coordinates read as zero) and ships nothing.
+//
+// Barriers inside the pair: as in ag_matmul_2cta_sm100.cu (full[] on the
+// leader, empty[] / tmem_full[] by multicast commit, tmem_empty[] on the leader
+// with 8 arrivals).
+#include "../device/tcgen05_pair.cuh"
+#include "matmul_rs_common.cuh"
+
+namespace smr {
+
+using namespace rs;
+
+namespace {
+
+template <int kStages, int kNStrips>
+struct PairRsSmem {
+  static constexpr uint32_t kABytes = kBM * kBK * 2;
+  static constexpr uint32_t kBBytes = (kBN / 2) * kBK * 2;       // this CTA's half of the B tile
+  static constexpr uint32_t kStageBytes = kABytes + kBBytes;
+  static constexpr uint32_t kRingBytes = kStageBytes * kStages;
+  static constexpr uint32_t kStripOffset = kRingBytes;
+  static constexpr uint32_t kStripBytes = kNStrips * kStripBytesOne;
+  static constexpr uint32_t kBarOffset = kStripOffset + kStripBytes;
+  static constexpr uint32_t kNumBars = 2 * kStages + 4;
+  static constexpr uint32_t kMiscOffset = kBarOffset + 8 * kNumBars;
+  static constexpr uint32_t kTotal = kMiscOffset + 16 + 1024;
+  static_assert(kStageBytes % 1024 == 0, "stage bases must stay 1024-byte aligned");
+};
+static_assert(PairRsSmem<5, 4>::kTotal <= 232448, "shared memory limit exceeded");
+
+// Entry `rb` of the visiting order -> destination rank and row block inside it.
+__device__ __forceinline__ void row_block_coords(const RsParams& p, int rb, int& dest, int& mb) {
+  const int step = rb / p.blocks_per_rank;
+  mb = rb - step * p.blocks_per_rank;
+  dest = p.rank + 1 + step;
+  if (dest >= p.world_size) dest -= p.world_size;
+}
+
+template <int kStages, int kNStrips>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+matmul_rs_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                      const RsParams p) {
+  using L = PairRsSmem<kStages, kNStrips>;
+  extern __shared__ uint8_t smem_raw[];
+  // same offset in both CTAs: the dynamic window starts at the same shared address
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* strip = smem + L::kStripOffset;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + kStages;
+  uint64_t* tmem_full = bars + 2 * kStages;
+  uint64_t* tmem_empty = bars + 2 * kStages + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kMiscOffset);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t cta_rank = cluster_ctarank();
+  const bool leader = cta_rank == 0;
+  uint32_t* header = p.local_pad + kFlagSlotsBase;        // [0] epoch, [1] CTAs done
+  const uint32_t epoch = ld_relaxed_gpu(&header[0]) + 1u;
+  const uint32_t target = epoch * (uint32_t)p.world_size;
+  uint32_t* my_counters = p.local_pad + kFlagSlotsBase + 2;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tmem_full[b], 1);
+      mbar_init(&tmem_empty[b], 8);   // 4 epilogue warps x 2 CTAs (used in the leader)
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, kTmemCols);
+    tmem_relinquish_pair();
+  }
+  if (p.trace != nullptr && threadIdx.x == 0) p.trace[blockIdx.x * 4 + 0] = globaltimer_ns();
+  // every rank has entered this call: its reduce of the previous call is done
+  bool entered = blockwise_barrier(p.pads, 1024u + blockIdx.x, p.rank, p.world_size, p.timeout_ns,
+                                   p.status, kWhereRsEntry);
+  if (p.trace != nullptr && threadIdx.x == 0) p.trace[blockIdx.x * 4 + 1] = globaltimer_ns();
+  tcgen05_fence_before_thread_sync();
+  __syncthreads();
+  cluster_sync_all();                 // barriers of both CTAs initialised, TMEM allocated
+  tcgen05_fence_after_thread_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int pair = (int)blockIdx.x >> 1;
+  const int n_pairs = (int)gridDim.x >> 1;
+  const int n_rb = p.world_size * p.blocks_per_rank;       // 128-row blocks over all destinations
+  const int total_tiles = ((n_rb + 1) >> 1) * p.n_tiles_n;
+  const int k_blocks = (p.K + kBK - 1) / kBK;
+  const int rows_per_rank = p.blocks_per_rank * kBM;
+  bool failed = !entered;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs) ----------------
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      for (int t = pair; t < total_tiles && !failed; t += n_pairs) {
+        const int pr = t / p.n_tiles_n, ni = t - pr * p.n_tiles_n;
+        const int rb = 2 * pr + (int)cta_rank;
+        int row0 = p.M;                                    // past the end: reads as zero
+        if (rb < n_rb) {
+          int dest, mb;
+          row_block_coords(p, rb, dest, mb);
+          row0 = dest * rows_per_rank + mb * kBM;
+        }
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.timeout_ns)) {
+            report_status(p.status, kTimeoutMbarrier, p.rank, blockIdx.x, stage, kWhereGemmEmpty);
+            failed = true;
+            break;
+          }
+          uint8_t* sa = smem + (size_t)stage * L::kStageBytes;
+          if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2u * L::kStageBytes);
+          const uint32_t full_leader = map_to_cta(smem_u32(&full_bar[stage]), 0);
+          tma_load_2d_pair(sa, &tmap_a, full_leader, kb * kBK, row0);
+          tma_load_2d_pair(sa + L::kABytes, &tmap_b, full_leader, kb * kBK, ni * kBN + (int)cta_rank * (kBN / 2));
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader CTA only) ----------------
+    if (leader && lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16_f32(2 * kBM, kBN);
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+      for (int t = pair; t < total_tiles && !failed; t += n_pairs) {
+        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, p.timeout_ns)) {
+          report_status(p.status, kTimeoutMbarrier, p.rank, blockIdx.x, acc, kWhereGemmTmemEmpty);
+          failed = true;
+          break;
+        }
+        tcgen05_fence_after_thread_sync();
+        const uint32_t d_tmem = tmem_base + acc * 256u;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, p.timeout_ns)) {
+            report_status(p.status, kTimeoutMbarrier, p.rank, blockIdx.x, stage, kWhereGemmFull);
+            failed = true;
+            break;
+          }
+          tcgen05_fence_after_thread_sync();
+          const uint32_t sa = smem_u32(smem + (size_t)stage * L::kStageBytes);
+          const uint64_t da = umma_smem_desc_sw128(sa);
+          const uint64_t db = umma_smem_desc_sw128(sa + L::kABytes);
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k)
+            umma_bf16_ss_pair(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc,
+                              (kb | k) != 0 ? 1u : 0u);
+          umma_commit_pair(&empty_bar[stage]);
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+        if (failed) break;
+        umma_commit_pair(&tmem_full[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    // ------- epilogue (warps 2..5 of both CTAs): TMEM -> bf16 strip -> bulk store into the destination -------
+    const int quarter = warp & 3;
+    const int etid = (int)threadIdx.x - 64;
+    const int r = quarter * 32 + lane;                  // row of this CTA's block owned by this thread
+    uint32_t acc = 0, acc_phase = 0, strip_ctr = 0;
+    uint32_t* prev_counter = nullptr;                   // tile whose stores are issued but not yet signalled
+    for (int t = pair; t < total_tiles && !failed; t += n_pairs) {
+      const int pr = t / p.n_tiles_n, ni = t - pr * p.n_tiles_n;
+      const int rb = 2 * pr + (int)cta_rank;
+      const bool valid = rb < n_rb;
+      int dest = 0, mb = 0;
+      if (valid) row_block_coords(p, rb, dest, mb);
+      if (!mbar_wait(&tmem_full[acc], acc_phase, p.timeout_ns)) {
+        if (lane == 0)
+          report_status(p.status, kTimeoutMbarrier, p.rank, blockIdx.x, acc, kWhereGemmTmemFull);
+        failed = true;
+        break;
+      }
+      tcgen05_fence_after_thread_sync();
+      const uint32_t taddr = tmem_base + acc * 256u + ((uint32_t)(quarter * 32) << 16);
+      int strips = 0;
+      if (valid) {
+#pragma unroll 1
+        for (int sidx = 0; sidx < kStripsPerTile; ++sidx) {
+          const int col0 = ni * kBN + sidx * kStripCols;
+          if (col0 >= p.N) break;                          // uniform over the CTA
+          uint32_t v0[32], v1[32];
+          tmem_ld_32x32b_x32(taddr + (uint32_t)(sidx * kStripCols), v0);
+          tmem_ld_32x32b_x32(taddr + (uint32_t)(sidx * kStripCols + 32), v1);
+          tmem_ld_wait();
+          // the store issued kNStrips strips ago has finished reading the buffer we are about to fill
+          if (etid == 0) bulk_wait_group_read<kNStrips - 1>();
+          epilogue_sync();
+          uint8_t* buf = strip + (size_t)(strip_ctr % (uint32_t)kNStrips) * kStripBytesOne;
+          uint8_t* row = buf + (size_t)r * 128;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {                    // 16-byte chunk c of the row, XOR-swizzled by row
+            const uint32_t* v = c < 4 ? &v0[c * 8] : &v1[(c - 4) * 8];
+            Vec16 o;
+            o.x = pack_bf16x2(__uint_as_float(v[0]), __uint_as_float(v[1]));
+            o.y = pack_bf16x2(__uint_as_float(v[2]), __uint_as_float(v[3]));
+            o.z = pack_bf16x2(__uint_as_float(v[4]), __uint_as_float(v[5]));
+            o.w = pack_bf16x2(__uint_as_float(v[6]), __uint_as_float(v[7]));
+            *reinterpret_cast<Vec16*>(row + ((c ^ (r & 7)) << 4)) = o;
+          }
+          fence_proxy_async();                             // generic writes to smem, async-proxy read
+          epilogue_sync();
+          if (etid == 0) {
+            char* dst = static_cast<char*>(p.buffers[dest]) + p.inbox_offset +
+                        strip_offset(p.rank, mb, ni, sidx, p.blocks_per_rank, p.n_tiles_n);
+            bulk_store(dst, buf, kStripBytesOne);
+            bulk_commit_group();
+          }
+          ++strip_ctr;
+          ++strips;
+        }
+      }
+      // the accumulator has been read (or holds nothing to ship): hand it back to the leader's MMA thread
+      tcgen05_fence_before_thread_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc]), 0));
+      if (etid == 0) {
+        if (prev_counter != nullptr) {
+          // everything older than this tile's groups has completed
+          if (strips == 4) bulk_wait_group<4>();
+          else bulk_wait_group<0>();
+          fence_proxy_async();
+          red_add_release_sys(prev_counter, 1u);
+        }
+        prev_counter = valid ? p.pads[dest] + kFlagSlotsBase + 2 + mb * p.n_tiles_n + ni : nullptr;
+      }
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+    if (etid == 0) {
+      bulk_wait_group<0>();
+      if (prev_counter != nullptr && !failed) {
+        fence_proxy_async();
+        red_add_release_sys(prev_counter, 1u);
+      }
+    }
+  }
+
+  // ---------------- GEMM teardown ----------------
+  if (__any_sync(0xffffffffu, failed)) {
+    for (int i = 0; i < 100; ++i) __nanosleep(1000);
+  }
+  tcgen05_fence_before_thread_sync();
+  failed = __syncthreads_or(failed) != 0;
+  cluster_sync_all();   // the peer may still read this CTA's smem / signal its barriers until here
+  tcgen05_fence_after_thread_sync();
+  if (warp == 1) tmem_dealloc_pair(tmem_base, kTmemCols);
+  if (p.trace != nullptr && threadIdx.x == 0) p.trace[blockIdx.x * 4 + 2] = globaltimer_ns();
+
+  // ---------------- reduce the tiles of this rank (every CTA on its own) ----------------
+  if (!failed) {
+    const int my_tiles = p.blocks_per_rank * p.n_tiles_n;
+    const char* inbox = static_cast<const char*>(p.buffers[p.rank]) + p.inbox_offset;
+    for (int t = blockIdx.x; t < my_tiles; t += gridDim.x) {
+      const int mb = t / p.n_tiles_n, ni = t - mb * p.n_tiles_n;
+      bool ok = true;
+      if (threadIdx.x == 0 && !wait_ge_acquire_sys(&my_counters[t], target, p.timeout_ns)) {
+        report_status(p.status, kTimeoutFlag, p.rank, blockIdx.x, t, kWhereRsArrive, target);
+        ok = false;
+      }
+      if (!__syncthreads_and(ok)) break;
+      switch (p.world_size) {
+        case 2: reduce_tile<2>(p, inbox, mb, ni); break;
+        case 4: reduce_tile<4>(p, inbox, mb, ni); break;
+        case 8: reduce_tile<8>(p, inbox, mb, ni); break;
+        default: reduce_tile<0>(p, inbox, mb, ni); break;
+      }
+    }
+  }
+
+  // ---------------- the last CTA to finish publishes this call's number ----------------
+  __syncthreads();
+  if (p.trace != nullptr && threadIdx.x == 0) p.trace[blockIdx.x * 4 + 3] = globaltimer_ns();
+  if (threadIdx.x == 0) {
+    uint32_t done = atomicAdd(&header[1], 1u);
+    if (done == gridDim.x - 1) {
+      header[1] = 0u;
+      __threadfence();
+      st_release_gpu(&header[0], epoch);
+    }
+  }
+}
+
+}  // namespace
+
+int launch_matmul_reduce_scatter_2cta(const MatmulRsArgs& a, cudaStream_t stream) {
+  const int ws = a.pv.world_size;
+  if (a.M <= 0 || a.N % 8 != 0 || a.K % 8 != 0 || a.M % (ws * kBM) != 0) return cudaErrorInvalidValue;
+  RsParams p{};
+  p.M = a.M; p.N = a.N; p.K = a.K;
+  p.rank = a.pv.rank; p.world_size = ws;
+  p.blocks_per_rank = a.M / ws / kBM;
+  p.n_tiles_n = (a.N + kBN - 1) / kBN;
+  if ((uint32_t)(p.blocks_per_rank * p.n_tiles_n) + 2u > kFusedFlagSlots) return cudaErrorInvalidValue;
+  p.buffers = a.pv.buffers;
+  p.inbox_offset = a.inbox_offset;
+  p.pads = a.pv.pads;
+  p.local_pad = a.local_pad;
+  p.out = static_cast<__nv_bfloat16*>(a.out);
+  p.timeout_ns = a.timeout_ns;
+  p.status = a.status;
+  p.trace = a.trace;
+  CUtensorMap ta, tb;
+  if (make_tmap(&ta, a.a, (uint64_t)a.M, (uint64_t)a.K, kBM)) return cudaErrorInvalidValue;
+  if (make_tmap(&tb, a.b, (uint64_t)a.N, (uint64_t)a.K, kBN / 2)) return cudaErrorInvalidValue;
+  const int n_rb = ws * p.blocks_per_rank;
+  const int total_tiles = ((n_rb + 1) / 2) * p.n_tiles_n;
+  int pairs = a.num_sms / 2;
+  if (pairs > total_tiles) pairs = total_tiles;
+  if (pairs < 1) return cudaErrorInvalidValue;
+  const int grid = 2 * pairs;
+  if ((uint32_t)(1024 + grid) * (uint32_t)ws > kBlockSlots) return cudaErrorInvalidValue;
+  using L = PairRsSmem<5, 4>;
+  auto kern = matmul_rs_2cta_kernel<5, 4>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::kTotal);
+  if (e != cudaSuccess) return (int)e;
+  kern<<<grid, kThreads, L::kTotal, stream>>>(ta, tb, p);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace smr

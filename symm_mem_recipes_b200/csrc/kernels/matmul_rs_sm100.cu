@@ -26,54 +26,16 @@
 //  * An entry barrier over the signal pad proves that every rank has finished
 //    reducing the previous call before its inbox is overwritten.  Counters
 //    count calls (epoch word in the pad), so nothing is reset between calls.
-#include <cuda.h>
-#include <cuda_runtime.h>
-
-#include "../device/barrier.cuh"
-#include "../device/mbarrier.cuh"
-#include "../device/tcgen05.cuh"
-#include "../device/tma.cuh"
-#include "../device/vec.cuh"
-#include "../symm/driver_api.h"
-#include "launch.h"
+#include "matmul_rs_common.cuh"
 
 namespace smr {
 
+using namespace rs;
+
 namespace {
 
-constexpr int kBM = 128;
-constexpr int kBN = 256;
-constexpr int kBK = 64;
-constexpr int kUmmaK = 16;
-constexpr int kThreads = 192;
-constexpr uint32_t kTmemCols = 512;
-constexpr int kStripCols = 64;                         // columns staged at a time (128 bytes: one swizzle row)
-constexpr uint32_t kStripBytesOne = kBM * kStripCols * 2;   // 16 KB
-constexpr int kStripsPerTile = kBN / kStripCols;       // 4
-
-// Byte offset of a strip inside an inbox: [src][row block][N tile][strip] x 16 KB
-__host__ __device__ __forceinline__ size_t strip_offset(int src, int mb, int ni, int sidx, int blocks_per_rank,
-                                                        int n_tiles_n) {
-  return ((((size_t)src * blocks_per_rank + mb) * n_tiles_n + ni) * kStripsPerTile + sidx) * kStripBytesOne;
-}
-
-struct RsParams {
-  int M, N, K;
-  int rank, world_size;
-  int blocks_per_rank;       // 128-row blocks per destination
-  int n_tiles_n;
-  void* const* buffers;      // workspace payload base of every rank
-  size_t inbox_offset;       // inbox [WS src][M/WS][N] bf16 inside the payload
-  uint32_t* const* pads;
-  uint32_t* local_pad;
-  __nv_bfloat16* out;        // [M/WS, N]
-  uint64_t timeout_ns;
-  Status* status;
-  uint64_t* trace;           // optional [grid][4] %globaltimer stamps: start, entered, GEMM done, reduced
-};
-
 template <int kStages, int kNStrips>
-struct Smem {
+struct RsSmem {
   static constexpr uint32_t kABytes = kBM * kBK * 2;
   static constexpr uint32_t kBBytes = kBN * kBK * 2;
   static constexpr uint32_t kStageBytes = kABytes + kBBytes;
@@ -85,9 +47,7 @@ struct Smem {
   static constexpr uint32_t kMiscOffset = kBarOffset + 8 * kNumBars;
   static constexpr uint32_t kTotal = kMiscOffset + 16 + 1024;
 };
-static_assert(Smem<4, 2>::kTotal <= 232448 && Smem<3, 5>::kTotal <= 232448, "shared memory limit exceeded");
-
-__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+static_assert(RsSmem<4, 2>::kTotal <= 232448 && RsSmem<3, 5>::kTotal <= 232448, "shared memory limit exceeded");
 
 // tile index -> destination rank, 128-row block inside the destination, N tile
 __device__ __forceinline__ void tile_coords(const RsParams& p, int t, int& dest, int& mb, int& ni) {
@@ -99,77 +59,6 @@ __device__ __forceinline__ void tile_coords(const RsParams& p, int t, int& dest,
   ni = rem - mb * p.n_tiles_n;
 }
 
-// Ordered fp32 sum of the WS partials of one [128 x 256] output tile, read from the
-// strip-major inbox (un-doing the row XOR of the 16-byte chunks) and written row-major.
-// 16 independent 16-byte loads are in flight per thread (the phase is bound by memory
-// latency otherwise): 16 / WS output vectors at a time.  WS = 0: generic loop.
-template <int WS>
-__device__ __forceinline__ void reduce_tile(const RsParams& p, const char* inbox, int mb, int ni) {
-  const int n0 = ni * kBN;
-  const int strips = min(kStripsPerTile, (p.N - n0 + kStripCols - 1) / kStripCols);
-  const int total = strips * kBM * 8;                       // 16-byte vectors of the tile
-  const size_t src_stride = (size_t)p.blocks_per_rank * p.n_tiles_n * kStripsPerTile * kStripBytesOne;
-  const char* tile_base = inbox + strip_offset(0, mb, ni, 0, p.blocks_per_rank, p.n_tiles_n);
-  // vector idx -> (strip, row, chunk): consecutive idx walk a strip's bytes in order (coalesced)
-  auto locate = [&](int idx, size_t& in_off, size_t& out_off, bool& in_range) {
-    const int sidx = idx / (kBM * 8), rem = idx - sidx * (kBM * 8);
-    const int row = rem >> 3, pos = rem & 7;                // pos: position inside the swizzled row
-    const int c = pos ^ (row & 7);                          // logical 16-byte chunk
-    in_off = (size_t)sidx * kStripBytesOne + (size_t)rem * 16;
-    const int col = n0 + sidx * kStripCols + c * 8;
-    in_range = col < p.N;
-    out_off = (size_t)(mb * kBM + row) * p.N + col;
-  };
-  constexpr int U = WS == 0 ? 1 : 16 / WS;
-  for (int idx0 = threadIdx.x; idx0 < total; idx0 += kThreads * U) {
-    Vec16 v[U][WS == 0 ? 1 : WS];
-    size_t out_off[U];
-    bool live[U];
-    float s[U][8];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int idx = idx0 + u * kThreads;
-      size_t in_off = 0;
-      live[u] = false;
-      if (idx < total) locate(idx, in_off, out_off[u], live[u]);
-#pragma unroll
-      for (int q = 0; q < 8; ++q) s[u][q] = 0.f;
-      if (live[u]) {
-        if constexpr (WS == 0) {
-          for (int src = 0; src < p.world_size; ++src) {
-            const Vec16 w = ld_16_stream(tile_base + (size_t)src * src_stride + in_off);
-            s[u][0] += bf16lo_to_f32(w.x); s[u][1] += bf16hi_to_f32(w.x);
-            s[u][2] += bf16lo_to_f32(w.y); s[u][3] += bf16hi_to_f32(w.y);
-            s[u][4] += bf16lo_to_f32(w.z); s[u][5] += bf16hi_to_f32(w.z);
-            s[u][6] += bf16lo_to_f32(w.w); s[u][7] += bf16hi_to_f32(w.w);
-          }
-        } else {
-#pragma unroll
-          for (int src = 0; src < WS; ++src) v[u][src] = ld_16_stream(tile_base + (size_t)src * src_stride + in_off);
-        }
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      if (!live[u]) continue;
-      if constexpr (WS != 0) {
-#pragma unroll
-        for (int src = 0; src < WS; ++src) {
-          const Vec16& w = v[u][src];
-          s[u][0] += bf16lo_to_f32(w.x); s[u][1] += bf16hi_to_f32(w.x);
-          s[u][2] += bf16lo_to_f32(w.y); s[u][3] += bf16hi_to_f32(w.y);
-          s[u][4] += bf16lo_to_f32(w.z); s[u][5] += bf16hi_to_f32(w.z);
-          s[u][6] += bf16lo_to_f32(w.w); s[u][7] += bf16hi_to_f32(w.w);
-        }
-      }
-      Vec16 o;
-      o.x = pack_bf16x2(s[u][0], s[u][1]); o.y = pack_bf16x2(s[u][2], s[u][3]);
-      o.z = pack_bf16x2(s[u][4], s[u][5]); o.w = pack_bf16x2(s[u][6], s[u][7]);
-      st_16(p.out + out_off[u], o);
-    }
-  }
-}
-
 // kStages: depth of the operand ring; kNStrips: epilogue strips that may be on the wire at once.
 // <4, 2> is the default; <3, 5> trades a stage for three more strips in flight (short-K shapes,
 // where the wire, not the main loop, is the limit).
@@ -177,7 +66,7 @@ template <int kStages, int kNStrips>
 __global__ void __launch_bounds__(kThreads, 1)
 matmul_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const RsParams p) {
-  using Smem = smr::Smem<kStages, kNStrips>;
+  using Smem = RsSmem<kStages, kNStrips>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* strip = smem + Smem::kStripOffset;
@@ -405,19 +294,6 @@ matmul_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   }
 }
 
-int make_tmap(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
-  const DriverApi& d = DriverApi::get();
-  cuuint64_t dims[2] = {cols, rows};
-  cuuint64_t strides[1] = {cols * 2};
-  cuuint32_t box[2] = {(cuuint32_t)kBK, box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = d.cuTensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base),
-                                        dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
-}
-
 }  // namespace
 
 size_t matmul_rs_workspace_bytes(int M, int N) {
@@ -426,6 +302,7 @@ size_t matmul_rs_workspace_bytes(int M, int N) {
 }
 
 int launch_matmul_reduce_scatter(const MatmulRsArgs& a, cudaStream_t stream) {
+  if (a.cta_pair) return launch_matmul_reduce_scatter_2cta(a, stream);
   const int ws = a.pv.world_size;
   if (a.M <= 0 || a.N % 8 != 0 || a.K % 8 != 0 || a.M % (ws * kBM) != 0) return cudaErrorInvalidValue;
   RsParams p{};
@@ -450,13 +327,13 @@ int launch_matmul_reduce_scatter(const MatmulRsArgs& a, cudaStream_t stream) {
   if (grid < 1 || (uint32_t)(1024 + grid) * (uint32_t)ws > kBlockSlots) return cudaErrorInvalidValue;
   if (a.deep_strips) {
     auto kern = matmul_rs_kernel<3, 5>;
-    constexpr int smem = (int)Smem<3, 5>::kTotal;
+    constexpr int smem = (int)RsSmem<3, 5>::kTotal;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     kern<<<grid, kThreads, smem, stream>>>(ta, tb, p);
   } else {
     auto kern = matmul_rs_kernel<4, 2>;
-    constexpr int smem = (int)Smem<4, 2>::kTotal;
+    constexpr int smem = (int)RsSmem<4, 2>::kTotal;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     kern<<<grid, kThreads, smem, stream>>>(ta, tb, p);

@@ -5,7 +5,7 @@ import torch
 from symm_mem_recipes_b200.utils.testing import spawn_ranks
 
 
-def _rs_worker(rank, world_size, M, N, K):
+def _rs_worker(rank, world_size, M, N, K, variant=None):
     import symm_mem_recipes_b200 as smr
     from symm_mem_recipes_b200.parallel import symm_mem
 
@@ -21,8 +21,17 @@ def _rs_worker(rank, world_size, M, N, K):
             b_r = (torch.randn(N, K, generator=gens[r]) * 0.05).to(torch.bfloat16)
             parts.append((a_r, b_r))
         a, b = parts[rank][0].to(dev), parts[rank][1].to(dev)
-        out = smr.matmul_reduce_scatter(a, b)
+        out = smr.matmul_reduce_scatter(a, b, **{variant: True} if variant else {})
         symm_mem.check_status(dev)
+        if variant:
+            # every variant ships bf16 partials and sums them in the same order; with the same MMA
+            # shape (deep_strips) the partials, hence the sums, have the same bits
+            plain = smr.matmul_reduce_scatter(a, b)
+            symm_mem.check_status(dev)
+            if variant == "deep_strips" and not torch.equal(plain.view(torch.int16), out.view(torch.int16)):
+                failures.append(f"call {it}: {variant} differs bitwise from the default kernel")
+            if not torch.allclose(plain.float(), out.float(), rtol=2.0 ** -6, atol=1e-3):
+                failures.append(f"call {it}: {variant} differs from the default kernel")
         ref = torch.zeros(rows, N, dtype=torch.float32)
         for a_r, b_r in parts:
             # every partial is rounded to bf16 on the wire, then summed in fp32
@@ -44,6 +53,18 @@ def _rs_worker(rank, world_size, M, N, K):
 @pytest.mark.parametrize("M,N,K", [(256, 256, 128), (512, 328, 192), (4096, 8192, 1024)])
 def test_matmul_reduce_scatter_2gpu(M, N, K):
     spawn_ranks(_rs_worker, 2, "nccl", (M, N, K))
+
+
+# Variants compiled for sm_100a whose first run on hardware is pending (SMR_TEST_FIRST_RUN=1 opts in).
+# (768, 328, 192) at 2 ranks: 3 row blocks per rank, so a CTA pair straddles two destinations and the
+# N edge is ragged; (384, 256, 128) at WS 3 would give an odd block count, which needs 3 GPUs.
+@pytest.mark.gpu
+@pytest.mark.first_run
+@pytest.mark.multigpu(2)
+@pytest.mark.parametrize("variant", ["cta_pair", "deep_strips"])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 128), (768, 328, 192), (4096, 8192, 1024)])
+def test_matmul_reduce_scatter_variants_2gpu(M, N, K, variant):
+    spawn_ranks(_rs_worker, 2, "nccl", (M, N, K, variant))
 
 
 @pytest.mark.gpu
