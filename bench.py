@@ -121,7 +121,7 @@ def main() -> int:
         ref = torch.matmul(a_shard, b.t())
     ok = bool(torch.allclose(c_out.float(), ref.float(), rtol=2e-2, atol=2e-3))
     del ref
-    # every rank learns the verdict (a rank that left alone would strand the others in a collective)
+    # every rank learns the outcome (a rank that left alone would strand the others in a collective)
     if max_over_ranks(0.0 if ok else 1.0, dev) != 0.0:
         raise SystemExit(f"rank {rank}: fused result differs from all-gather + matmul (this rank ok: {ok})")
 
