@@ -122,3 +122,67 @@ def test_rejects_foreign_tensor():
 
     with pytest.raises(SymmMemError):
         smr.one_shot_all_reduce(torch.zeros(64, dtype=torch.bfloat16))
+
+
+# ---- host-side liveness: a rank that leaves between steps is noticed before the next launch ----
+def _heartbeat_worker(rank, world_size):
+    import time
+
+    import symm_mem_recipes_b200 as smr
+    from symm_mem_recipes_b200.parallel import symm_mem
+    from symm_mem_recipes_b200.parallel.health import Heartbeat, PeerLost
+
+    hb = Heartbeat(interval_s=0.05)
+    hb.wait_for_all(timeout_s=30)
+    t = symm_mem.empty(4096, dtype=torch.bfloat16, device="cpu")
+    t.copy_(seeded_normal_bf16(4096, rank))
+    hdl = symm_mem.rendezvous(t)
+    for step in range(2):                       # everybody is there: the check passes, the op runs
+        hb.check(max_age_s=5.0)
+        hdl.barrier()
+        smr.one_shot_all_reduce(t)
+        hdl.barrier()
+    if rank == world_size - 1:
+        hb.stop()                               # leaves between steps, nothing of it in flight
+        return
+    lost = None
+    deadline = time.time() + 20
+    while lost is None and time.time() < deadline:
+        try:
+            hb.check(max_age_s=5.0)
+            time.sleep(0.02)
+        except PeerLost as e:
+            lost = e
+    assert lost is not None and lost.rank == world_size - 1 and "left" in lost.reason
+    hb.stop(leaving=False)
+
+
+@pytest.mark.parametrize("world_size", [2, 3])
+def test_heartbeat_names_the_rank_that_left(world_size):
+    spawn_ranks(_heartbeat_worker, world_size, "gloo")
+
+
+def test_heartbeat_goes_stale_without_a_goodbye():
+    """A rank whose process stops beating (no orderly leave) is reported by age."""
+    import time
+
+    from torch.distributed import HashStore
+
+    from symm_mem_recipes_b200.parallel.health import Heartbeat, PeerLost
+
+    store = HashStore()
+    a = Heartbeat(store=store, rank=0, world_size=2, interval_s=0.02)
+    b = Heartbeat(store=store, rank=1, world_size=2, interval_s=0.02)
+    a.wait_for_all(5)
+    a.check(max_age_s=1.0)
+    b.stop(leaving=False)                       # as if its process had died
+    time.sleep(0.3)
+    with pytest.raises(PeerLost) as e:
+        a.check(max_age_s=0.2)
+    assert e.value.rank == 1 and "ago" in e.value.reason
+    a.stop()
+    # a rank that never came up
+    c = Heartbeat(store=HashStore(), rank=0, world_size=2, interval_s=0.02)
+    with pytest.raises(PeerLost):
+        c.wait_for_all(timeout_s=0.2)
+    c.stop()
