@@ -7,7 +7,9 @@ cuBLAS mm only, this package's mm only, cuBLAS + NCCL, fused.
 
 M is the gathered row count; N and K are the per-rank weight dims.  Median of
 `--iters` timed calls after `--warmup`, L2 flushed before each, CUDA events,
-maximum over ranks.
+maximum over ranks.  `--upstream-table` runs the nine shapes of the upstream
+README (three models x M in 4096, 8192, 16384, README.md:17-36) and attaches the
+numbers published there (8 x H100) to every record.
 """
 from __future__ import annotations
 
@@ -18,6 +20,15 @@ import sys
 
 import torch
 import torch.distributed as dist
+
+
+# upstream README.md:20-36, µs on 8 x H100: (N, K) -> M -> (cuBLAS, Triton mm, cuBLAS + NCCL, fused)
+UPSTREAM_TABLE = {
+    (1792, 4096): {4096: (105, 125, 230, 213), 8192: (194, 236, 416, 318), 16384: (391, 434, 819, 514)},
+    (3584, 8192): {4096: (403, 483, 652, 543), 8192: (828, 849, 1291, 948), 16384: (1672, 1655, 2541, 1846)},
+    (6656, 16384): {4096: (1558, 1595, 2077, 1776), 8192: (2879, 2953, 3847, 3243),
+                    16384: (5842, 5948, 7801, 6538)},
+}
 
 
 def main(argv=None, standalone: bool = True) -> int:
@@ -37,6 +48,8 @@ def main(argv=None, standalone: bool = True) -> int:
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--iters", type=int, default=25)
     ap.add_argument("--out", default=None)
+    ap.add_argument("--upstream-table", action="store_true",
+                    help="run the nine (model, M) shapes of the upstream README instead of --M/--N/--K")
     ap.add_argument("--print-ptxas", "--print_ptx", dest="print_ptxas", action="store_true",
                     help="print what the compiler made of the kernels (registers, spills, shared memory from "
                          "`ptxas -v`); upstream's --print_ptx dumps Triton's PTX at this point")
@@ -46,12 +59,30 @@ def main(argv=None, standalone: bool = True) -> int:
 
     rank, local_rank, world, dev = init_distributed()
 
+    lines = []
+    if args.upstream_table:
+        shapes = [(M, N, K) for (N, K), by_m in UPSTREAM_TABLE.items() for M in by_m]
+    else:
+        shapes = [(args.M, args.N, args.K)]
+    for M, N, K in shapes:
+        _one_shape(args, M, N, K, rank, world, dev, lines)
+    if args.print_ptxas and rank == 0:
+        from symm_mem_recipes_b200 import _build
+        print(_build.ptxas_report())
+    if args.out and rank == 0:
+        with open(args.out, "a") as f:
+            f.write("\n".join(lines) + "\n")
+    if standalone:
+        finish()
+    return 0
+
+
+def _one_shape(args, M, N, K, rank, world, dev, lines) -> None:
     import symm_mem_recipes_b200 as smr
     from symm_mem_recipes_b200.ops.ag_matmul import AgMatmulConfig
     from symm_mem_recipes_b200.parallel import symm_mem
     from symm_mem_recipes_b200.utils.benchmark import benchmark_with_event
 
-    M, N, K = args.M, args.N, args.K
     assert M % world == 0
     torch.manual_seed(42 + rank)
     a_shard = symm_mem.empty(M // world, K, dtype=torch.bfloat16, device=dev)
@@ -65,11 +96,17 @@ def main(argv=None, standalone: bool = True) -> int:
     symm_mem.rendezvous(a_shard)
     symm_mem.rendezvous(a_out)
     flops = 2.0 * M * N * K
-    lines = []
+    published = UPSTREAM_TABLE.get((N, K), {}).get(M)
+    published_by_impl = {} if published is None or world != 8 else {
+        "cublas_mm_only": published[0], "smr_mm_only": published[1], "cublas_plus_nccl": published[2],
+        "smr_fused": published[3]}
 
     def emit(name, us, **extra):
         rec = {"op": "all_gather_matmul", "impl": name, "world_size": world, "M": M, "N": N, "K": K,
                "us": round(us, 1), "tflops": round(flops / us / 1e6, 1), **extra}
+        if name in published_by_impl:
+            # the same row of the upstream table (for smr_mm_only: upstream's Triton mm only)
+            rec["upstream_8xh100_us"] = published_by_impl[name]
         if rank == 0:
             s = json.dumps(rec)
             print(s, flush=True)
@@ -96,15 +133,6 @@ def main(argv=None, standalone: bool = True) -> int:
         us = benchmark_with_event(lambda: smr.all_gather_matmul(a_shard, b, a_out_plain, c, cfg), **bench)
         emit("smr_fused", us, copy_ctas=n_copy, gather="pull")
         symm_mem.check_status(dev)
-    if args.print_ptxas and rank == 0:
-        from symm_mem_recipes_b200 import _build
-        print(_build.ptxas_report())
-    if args.out and rank == 0:
-        with open(args.out, "a") as f:
-            f.write("\n".join(lines) + "\n")
-    if standalone:
-        finish()
-    return 0
 
 
 if __name__ == "__main__":

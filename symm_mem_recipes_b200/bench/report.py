@@ -113,6 +113,7 @@ def ag_matmul_table(recs: list[dict], peaks: Optional[dict]) -> Optional[str]:
     for (ws, M, N, K), impls in sorted(groups.items()):
         flops = 2.0 * M * N * K
         base = impls.get("cublas_plus_nccl", {}).get("us")
+        with_upstream = any("upstream_8xh100_us" in r for r in impls.values())
         rows = []
         for name, r in impls.items():
             us = float(r["us"])
@@ -121,9 +122,13 @@ def ag_matmul_table(recs: list[dict], peaks: Optional[dict]) -> Optional[str]:
             if peaks:
                 row.append(_fmt(100.0 * tf / peaks["bf16_tflops"], 1) + " %" if name != "nccl_all_gather_only" else "-")
             row.append(_fmt(base / us, 2) + "x" if base else "-")
+            if with_upstream:
+                up = r.get("upstream_8xh100_us")
+                row.append(f"{up} ({up / us:.2f}x)" if up else "-")
             rows.append(row)
         header = ["impl", "µs", "TFLOPS / GPU"] + (["of measured cuBLAS burst peak"] if peaks else []) + \
-                 ["vs NCCL all-gather + cuBLAS"]
+                 ["vs NCCL all-gather + cuBLAS"] + \
+                 (["same row of the upstream table, 8 x H100 µs (ratio)"] if with_upstream else [])
         text = f"### all_gather_matmul, WS {ws}, M {M}, N {N}, K {K}\n\n" + _table(header, rows)
         if peaks:
             t_math = flops / peaks["bf16_tflops"] / 1e6

@@ -132,6 +132,20 @@ def matmul(a: torch.Tensor, b: torch.Tensor, c_out: Optional[torch.Tensor] = Non
 _gather_buffers: dict[tuple, torch.Tensor] = {}
 
 
+def _check_gather_geometry(notes: dict, geometry: tuple) -> None:
+    """The arrival counters of the push gather live in the signal pad of the
+    a_out allocation and count CALLS: block i has arrived when its counter
+    reaches (calls so far) x (pieces per block).  That only holds while every
+    call on one allocation gathers the same [M, K] at the same offset, so a
+    second geometry on the same allocation is refused here instead of timing
+    out on the device.  One symmetric buffer per gathered shape (what
+    `gather_buffer` hands out) is the intended use."""
+    seen = notes.setdefault("gather_geometry", geometry)
+    if seen != geometry:
+        raise SymmMemError(f"this symmetric allocation already serves a gather of (offset, M, K, dtype) = {seen}; "
+                           f"got {geometry}.  Use one symmetric a_out per gathered shape.")
+
+
 def gather_buffer(M: int, K: int, device: torch.device, group=None,
                   dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
     """The symmetric [M, K] buffer that `all_gather_matmul` gathers into when
@@ -193,10 +207,11 @@ def all_gather_matmul(a_shard: torch.Tensor, b: torch.Tensor, a_out: Optional[to
         # push: every CTA is a GEMM CTA, the epilogue warps broadcast the shard
         bn = config.block_n or choose_block_n(M, N, sms, config.cta_pair)
         n_copy = 0
-        _, aout_offset = symm_mem._find_record(a_out)
+        rec, aout_offset = symm_mem._find_record(a_out)
         hdl = symm_mem.rendezvous(a_out, group)
         if aout_offset % 16:
             raise SymmMemError("a_out must start on a 16-byte boundary of its allocation")
+        _check_gather_geometry(rec.notes, (aout_offset, M, K, a_shard.dtype))
         C.ag_matmul(a_shard, b, c_out, 2, None, 0, hdl.native, aout_offset, a_out, None,
                     bn, sms, n_copy, t_ns, config.cta_pair, _tail_buffer(a_shard.device, config))
         return c_out

@@ -54,6 +54,7 @@ class _Record:
     nbytes: int
     handle: Optional["SymmetricMemory"] = None
     views: list = field(default_factory=list)
+    notes: dict = field(default_factory=dict)   # per-allocation state of the ops (dies with the allocation)
 
 
 _records: dict[int, _Record] = {}

@@ -63,3 +63,17 @@ def test_status_decoding():
         raise_for_status((2, 3, 7, 5, 10, 0))
     assert (e.value.rank, e.value.block, e.value.peer) == (3, 7, 5)
     assert "never arrived" in str(e.value)
+
+
+def test_one_gather_geometry_per_symmetric_allocation():
+    import torch
+
+    from symm_mem_recipes_b200.errors import SymmMemError
+    from symm_mem_recipes_b200.ops.ag_matmul import _check_gather_geometry
+
+    notes = {}
+    _check_gather_geometry(notes, (0, 4096, 8192, torch.bfloat16))
+    _check_gather_geometry(notes, (0, 4096, 8192, torch.bfloat16))        # same again: fine
+    with pytest.raises(SymmMemError):
+        _check_gather_geometry(notes, (0, 8192, 8192, torch.bfloat16))    # another M on the same counters
+    _check_gather_geometry({}, (0, 8192, 8192, torch.bfloat16))           # a new allocation starts clean
