@@ -18,6 +18,9 @@ def main() -> int:
     ap.add_argument("--only", default="barrier,all_reduce,all_gather_matmul,gemv,layer")
     ap.add_argument("--with-reference-triton", action="store_true")
     ap.add_argument("--ar-max-bytes", type=int, default=256 * 1024 * 1024)
+    ap.add_argument("--layer-detail", action="store_true",
+                    help="layer benchmark: time it with PyTorch glue and with the single-pass glue kernels, and print "
+                         "the device time of every phase")
     args = ap.parse_args()
     from symm_mem_recipes_b200.bench import (all_gather_matmul, all_reduce, barrier, gemv_all_reduce,
                                              llama_layer)
@@ -40,10 +43,13 @@ def main() -> int:
     if "all_gather_matmul" in only:
         all_gather_matmul.main(["--M", "16384", "--N", "3584", "--K", "8192", "--out", out("agmm")],
                                standalone=False)
+    if "upstream_table" in only:         # not in the default list: nine shapes, a few minutes
+        all_gather_matmul.main(["--upstream-table", "--out", out("agmm_table")], standalone=False)
     if "gemv" in only:
         gemv_all_reduce.main(["--out", out("gemv")], standalone=False)
     if "layer" in only:
-        llama_layer.main(["--out", out("layer")], standalone=False)
+        llama_layer.main(["--out", out("layer")] + (["--fused-glue", "both", "--breakdown"] if args.layer_detail
+                                                    else []), standalone=False)
     finish()
     return 0
 
