@@ -370,11 +370,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
 
   // ---- device ops ----
   m.def("barrier_test", [](const std::shared_ptr<CudaSymmAllocation>& a, int blocks, int threads,
-                           uint64_t timeout_ns) {
+                           uint64_t timeout_ns, int kind) {
     c10::cuda::CUDAGuard guard(a->device());
     rt_check(launch_barrier_test(view_of(*a), blocks, threads, timeout_ns, status_for(a->device()),
-                                 current_stream(a->device())), "barrier_test");
-  });
+                                 current_stream(a->device()), kind), "barrier_test");
+  }, py::arg("alloc"), py::arg("blocks"), py::arg("threads"), py::arg("timeout_ns"), py::arg("kind") = 0);
   m.def("channel_barrier", [](const std::shared_ptr<CudaSymmAllocation>& a, int channel,
                               uint64_t timeout_ns) {
     c10::cuda::CUDAGuard guard(a->device());
@@ -425,12 +425,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                                         current_stream(a->device())), "two_shot_all_reduce");
   });
   m.def("multimem_all_reduce", [](const std::shared_ptr<CudaSymmAllocation>& a, int64_t offset_bytes,
-                                  int64_t numel, int max_blocks, uint64_t timeout_ns) {
+                                  int64_t numel, int max_blocks, uint64_t timeout_ns, bool nvls_barrier) {
     c10::cuda::CUDAGuard guard(a->device());
     rt_check(launch_multimem_all_reduce(view_of(*a), (size_t)offset_bytes, (size_t)numel, max_blocks,
                                         timeout_ns, status_for(a->device()),
-                                        current_stream(a->device())), "multimem_all_reduce");
-  });
+                                        current_stream(a->device()), nvls_barrier), "multimem_all_reduce");
+  }, py::arg("alloc"), py::arg("offset_bytes"), py::arg("numel"), py::arg("max_blocks"), py::arg("timeout_ns"),
+     py::arg("nvls_barrier") = false);
 
   // a: own shard (or all of A when mode == 0), b: [N, K], c: [M, N]
   // mode 1 (pull): `shard_alloc` holds a; a_out is an ordinary tensor.

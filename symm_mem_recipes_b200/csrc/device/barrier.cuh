@@ -131,4 +131,58 @@ struct EpochBarrier {
   }
 };
 
+// ---------------------------------------------------------------------------
+// NVLS barrier: arrival is ONE `multimem.red.add` on a counter in the multicast
+// mapping of the signal pad, which the NVSwitch applies to the copy of that
+// counter on every rank; each rank then polls its own copy until it reads
+// (barriers so far) x world_size.  One instruction on the wire per rank and
+// barrier instead of world_size stores.  Needs a multicast mapping that covers
+// the pad (the allocator binds the whole block).  Slots of the block's group:
+// [1] = arrivals (sum over ranks and barriers), [2] = this rank's barrier count;
+// they do not overlap the epoch barrier's slots, and like them they only grow.
+// ---------------------------------------------------------------------------
+struct MulticastBarrier {
+  uint32_t* mine;        // this rank's group of kArFlagStride slots for this block id
+  uint32_t* mc_arrivals; // multicast address of slot [1] of that group
+  uint32_t slot_base;
+  uint32_t count;
+  int rank, world_size;
+
+  // `buffers[rank]` / `pads[rank]`: local payload and pad base; `multicast`: multicast payload base.
+  __device__ __forceinline__ MulticastBarrier(uint32_t* const* pads, void* const* buffers, void* multicast,
+                                              uint32_t block_id, int rank_, int ws)
+      : rank(rank_), world_size(ws) {
+    slot_base = kArFlagBase + block_id * kArFlagStride;
+    mine = pads[rank] + slot_base;
+    const size_t pad_offset = reinterpret_cast<const char*>(pads[rank]) - static_cast<const char*>(buffers[rank]);
+    mc_arrivals = reinterpret_cast<uint32_t*>(static_cast<char*>(multicast) + pad_offset) + slot_base + 1u;
+    count = ld_relaxed_gpu(mine + 2);
+  }
+
+  // All threads of the CTA call it.  false on timeout (Status recorded).
+  __device__ __forceinline__ bool sync(uint64_t timeout_ns, Status* st, uint32_t where) {
+    ++count;
+    __syncthreads();   // the CTA's earlier writes precede the release
+    bool ok = true;
+    if (flat_tid() == 0) {
+      asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;" ::"l"(mc_arrivals), "r"(1u) : "memory");
+      const uint32_t target = count * (uint32_t)world_size;
+      Deadline d(timeout_ns);
+      while ((int32_t)(ld_acquire_sys(mine + 1) - target) < 0) {
+        if (!d.alive()) {
+          report_status(st, kTimeoutBarrierWait, rank, slot_base, 0, where, count);
+          ok = false;
+          break;
+        }
+      }
+    }
+    return __syncthreads_and(ok) != 0;
+  }
+
+  // Once, by every thread, after the kernel's last sync.
+  __device__ __forceinline__ void finish() {
+    if (flat_tid() == 0) mine[2] = count;
+  }
+};
+
 }  // namespace smr

@@ -31,6 +31,25 @@ __global__ void barrier_test_kernel(PeerView pv, uint64_t timeout_ns, Status* st
   blockwise_barrier(pv.pads, flat_block_id(), pv.rank, pv.world_size, timeout_ns, st, kWhereTest);
 }
 
+// The two counting barriers behind one constructor signature.
+struct EpochBar : EpochBarrier {
+  __device__ __forceinline__ EpochBar(const PeerView& pv, uint32_t block_id)
+      : EpochBarrier(pv.pads, block_id, pv.rank, pv.world_size) {}
+};
+struct NvlsBar : MulticastBarrier {
+  __device__ __forceinline__ NvlsBar(const PeerView& pv, uint32_t block_id)
+      : MulticastBarrier(pv.pads, pv.buffers, pv.multicast, block_id, pv.rank, pv.world_size) {}
+};
+
+// Same smoke test for the counting barriers (two rounds, so that the count written back is used).
+template <class Bar>
+__global__ void counting_barrier_test_kernel(PeerView pv, uint64_t timeout_ns, Status* st) {
+  Bar bar(pv, flat_block_id());
+  if (!bar.sync(timeout_ns, st, kWhereTest)) return;
+  bar.sync(timeout_ns, st, kWhereTest);
+  bar.finish();
+}
+
 // One CTA; slot = kBlockSlots + channel * WS + sender.
 __global__ void channel_barrier_kernel(PeerView pv, int channel, uint64_t timeout_ns, Status* st) {
   int t = threadIdx.x;
@@ -146,11 +165,12 @@ two_shot_all_reduce_kernel(PeerView pv, size_t offset_bytes, size_t n_vec, uint6
   bar.finish();
 }
 
+template <class Bar>
 __global__ void __launch_bounds__(kArThreads)
 multimem_all_reduce_kernel(PeerView pv, size_t offset_bytes, size_t n_vec, uint64_t timeout_ns,
                            Status* st) {
   const int rank = pv.rank, ws = pv.world_size;
-  EpochBarrier bar(pv.pads, blockIdx.x, rank, ws);
+  Bar bar(pv, blockIdx.x);
   if (!bar.sync(timeout_ns, st, kWhereMultimemEntry)) return;
   Vec16* mc = reinterpret_cast<Vec16*>(static_cast<char*>(pv.multicast) + offset_bytes);
   size_t begin, end;
@@ -260,10 +280,19 @@ int last_error() { return (int)cudaGetLastError(); }
 }  // namespace
 
 int launch_barrier_test(const PeerView& pv, int num_blocks, int threads, uint64_t timeout_ns,
-                        Status* status, cudaStream_t stream) {
+                        Status* status, cudaStream_t stream, int kind) {
   if (num_blocks < 1 || (uint32_t)num_blocks * pv.world_size > kBlockSlots) return cudaErrorInvalidValue;
   if (threads < pv.world_size) return cudaErrorInvalidValue;
-  barrier_test_kernel<<<num_blocks, threads, 0, stream>>>(pv, timeout_ns, status);
+  if (kind != 0 && (uint32_t)num_blocks > kArMaxBlocks) return cudaErrorInvalidValue;
+  switch (kind) {
+    case 0: barrier_test_kernel<<<num_blocks, threads, 0, stream>>>(pv, timeout_ns, status); break;
+    case 1: counting_barrier_test_kernel<EpochBar><<<num_blocks, threads, 0, stream>>>(pv, timeout_ns, status); break;
+    case 2:
+      if (pv.multicast == nullptr) return cudaErrorNotSupported;
+      counting_barrier_test_kernel<NvlsBar><<<num_blocks, threads, 0, stream>>>(pv, timeout_ns, status);
+      break;
+    default: return cudaErrorInvalidValue;
+  }
   return last_error();
 }
 
@@ -349,14 +378,18 @@ int launch_two_shot_all_reduce(const PeerView& pv, size_t offset_bytes, size_t n
 
 int launch_multimem_all_reduce(const PeerView& pv, size_t offset_bytes, size_t numel,
                                int max_blocks, uint64_t timeout_ns, Status* status,
-                               cudaStream_t stream) {
+                               cudaStream_t stream, bool nvls_barrier) {
   if (numel % 8 != 0 || offset_bytes % 16 != 0) return cudaErrorInvalidValue;
   if (pv.multicast == nullptr) return cudaErrorNotSupported;
   size_t n_vec = numel / 8;
   if ((uint32_t)max_blocks > kArMaxBlocks) max_blocks = (int)kArMaxBlocks;
   int blocks = blocks_for((n_vec + pv.world_size - 1) / pv.world_size, max_blocks);
-  multimem_all_reduce_kernel<<<blocks, kArThreads, 0, stream>>>(pv, offset_bytes, n_vec,
-                                                                 timeout_ns, status);
+  if (nvls_barrier)
+    multimem_all_reduce_kernel<NvlsBar><<<blocks, kArThreads, 0, stream>>>(pv, offset_bytes, n_vec,
+                                                                          timeout_ns, status);
+  else
+    multimem_all_reduce_kernel<EpochBar><<<blocks, kArThreads, 0, stream>>>(pv, offset_bytes, n_vec,
+                                                                           timeout_ns, status);
   return last_error();
 }
 

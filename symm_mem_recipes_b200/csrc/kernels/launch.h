@@ -19,8 +19,10 @@ struct PeerView {
 };
 
 // ---- barrier ---------------------------------------------------------------
+// `kind`: 0 = blockwise_barrier (CAS protocol, pad returns to zero), 1 = epoch barrier (one store per
+// peer, counters only grow), 2 = NVLS barrier (one multimem.red per rank; needs a multicast mapping).
 int launch_barrier_test(const PeerView& pv, int num_blocks, int threads, uint64_t timeout_ns,
-                        Status* status, cudaStream_t stream);
+                        Status* status, cudaStream_t stream, int kind = 0);
 int launch_channel_barrier(const PeerView& pv, int channel, uint64_t timeout_ns, Status* status,
                            cudaStream_t stream);
 // Waits on a flag nothing sets unless `*flag >= target`; used to prove that a
@@ -45,9 +47,10 @@ int launch_ll_all_reduce(const PeerView& pv, const void* in, void* out, size_t n
 int launch_two_shot_all_reduce(const PeerView& pv, size_t offset_bytes, size_t numel,
                                int max_blocks, uint64_t timeout_ns, Status* status,
                                cudaStream_t stream);
+// `nvls_barrier`: entry / exit barriers by multimem.red instead of per-peer stores.
 int launch_multimem_all_reduce(const PeerView& pv, size_t offset_bytes, size_t numel,
                                int max_blocks, uint64_t timeout_ns, Status* status,
-                               cudaStream_t stream);
+                               cudaStream_t stream, bool nvls_barrier = false);
 
 // ---- all_gather_matmul (tcgen05 GEMM + in-kernel all-gather) ---------------
 struct AgMatmulArgs {

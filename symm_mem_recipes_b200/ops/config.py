@@ -27,6 +27,8 @@ class AllReduceConfig:
     one_shot_max_blocks: int = _env_int("SMR_AR_ONE_SHOT_MAX_BLOCKS", 32)
     two_shot_max_blocks: int = _env_int("SMR_AR_TWO_SHOT_MAX_BLOCKS", 128)
     multimem_max_blocks: int = _env_int("SMR_AR_MULTIMEM_MAX_BLOCKS", 16)
+    # multimem kernel: entry / exit barriers by one multimem.red per rank (NVLS) instead of per-peer stores
+    multimem_nvls_barrier: int = _env_int("SMR_AR_NVLS_BARRIER", 0)
     # one-shot: rank r starts its peer loads at rank r+1 (0 = every rank starts at rank 0, as upstream)
     one_shot_stagger: int = _env_int("SMR_AR_ONE_SHOT_STAGGER", 1)
     timeout_ms: int = _env_int("SMR_TIMEOUT_MS", 10000)

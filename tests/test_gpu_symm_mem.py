@@ -160,3 +160,49 @@ def test_all_reduce_4gpu():
 @pytest.mark.multigpu(8)
 def test_all_reduce_8gpu():
     spawn_ranks(_ar_worker, 8, "nccl", (1 << 18,))
+
+
+def _counting_barriers_worker(rank, world_size, numel):
+    """The epoch barrier and the NVLS (multimem.red) barrier as kernels of their
+    own, then the multimem all-reduce with NVLS barriers against the default."""
+    import symm_mem_recipes_b200 as smr
+    from symm_mem_recipes_b200.ops.config import AllReduceConfig
+    from symm_mem_recipes_b200.parallel import symm_mem
+
+    dev = torch.device("cuda", rank)
+    failures = []
+    t = symm_mem.empty(numel, dtype=torch.bfloat16, device=dev)
+    hdl = symm_mem.rendezvous(t)
+    kinds = ["epoch"] + (["nvls"] if hdl.has_multicast else [])
+    for kind in kinds:
+        for blocks in (1, 7, 32, 148):
+            for _ in range(20):
+                smr.barrier_test(hdl, num_blocks=blocks, kind=kind, timeout_ms=2000)
+        hdl.barrier()
+        hdl.check()
+    if hdl.has_multicast:
+        srcs = [seeded_normal_bf16(numel, r) for r in range(world_size)]
+        results = []
+        for nvls in (0, 1, 1, 0):            # alternating kinds share the pad without disturbing each other
+            hdl.barrier()
+            t.copy_(srcs[rank].to(dev))
+            hdl.barrier()
+            smr.multimem_all_reduce_(t, config=AllReduceConfig(multimem_nvls_barrier=nvls, timeout_ms=2000))
+            hdl.check()
+            results.append(t.clone())
+        ref = results[0].float()
+        for r in results[1:]:
+            # the switch's summation order is its own: within one bf16 ulp
+            if not bool(((r.float() - ref).abs() <= ref.abs() * 2.0 ** -7 + 1e-6).all()):
+                failures.append("multimem all-reduce with NVLS barriers differs from the default")
+    elif world_size > 1:
+        failures.append("no multicast mapping on an NVSwitch machine")
+    torch.cuda.synchronize()
+    assert not failures, failures
+
+
+@pytest.mark.gpu
+@pytest.mark.first_run
+@pytest.mark.multigpu(2)
+def test_counting_barriers_2gpu():
+    spawn_ranks(_counting_barriers_worker, 2, "nccl", (1 << 20,))
