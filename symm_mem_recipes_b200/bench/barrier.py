@@ -19,6 +19,9 @@ import torch.distributed as dist
 def main(argv=None, standalone: bool = True) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--blocks", default="1,32,148")
+    ap.add_argument("--kinds", default="cas",
+                    help="comma-separated: cas (blockwise_barrier), epoch, nvls; the counting kinds run the barrier "
+                         "twice per launch and are timed on a second allocation")
     args = ap.parse_args(argv)
     from symm_mem_recipes_b200.bench._common import finish, init_distributed
 
@@ -39,7 +42,22 @@ def main(argv=None, standalone: bool = True) -> int:
                               "us": round(us, 2), "timing": "graph"}), flush=True)
     us = benchmark_with_graph(lambda: hdl.barrier(0), calls_per_graph=50)
     hdl.check()
-    pad_sum = int(hdl.get_signal_pad().abs().sum())
+    pad_sum = int(hdl.get_signal_pad().abs().sum())     # before the counting kinds: they leave counters behind
+    counting = [k for k in args.kinds.split(",") if k in ("epoch", "nvls")]
+    if counting:
+        t2 = symm_mem.empty(4096, dtype=torch.int32, device=dev)
+        hdl2 = symm_mem.rendezvous(t2)
+        for kind in counting:
+            if kind == "nvls" and not hdl2.has_multicast:
+                continue
+            for blocks in [int(b) for b in args.blocks.split(",")]:
+                smr.barrier_test(hdl2, num_blocks=blocks, kind=kind)
+                hdl2.check()
+                us_k = benchmark_with_graph(lambda: smr.barrier_test(hdl2, num_blocks=blocks, kind=kind),
+                                            calls_per_graph=50)
+                if rank == 0:
+                    print(json.dumps({"op": f"{kind}_barrier_x2", "world_size": world, "blocks": blocks,
+                                      "us": round(us_k, 2), "timing": "graph"}), flush=True)
     if rank == 0:
         print(json.dumps({"op": "channel_barrier", "world_size": world, "us": round(us, 2), "timing": "graph"}))
         print(json.dumps({"op": "barrier_test", "signal_pad_abs_sum": pad_sum, "ok": pad_sum == 0}))
