@@ -441,7 +441,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                         std::shared_ptr<CudaSymmAllocation> aout_alloc, int64_t aout_offset,
                         c10::optional<torch::Tensor> a_out, c10::optional<torch::Tensor> flags,
                         int block_n, int num_sms, int n_copy, uint64_t timeout_ns, bool cta_pair,
-                        c10::optional<torch::Tensor> tail_scratch) {
+                        c10::optional<torch::Tensor> tail_scratch, int epilogue) {
     const auto dtype = a.scalar_type();
     const bool fp8 = dtype == at::kFloat8_e4m3fn;
     TORCH_CHECK(fp8 || dtype == torch::kBFloat16, "a must be bfloat16 or float8_e4m3fn");
@@ -462,6 +462,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     args.N = (int)b.size(0);
     args.K = (int)a.size(1);
     args.elem_bytes = fp8 ? 1 : 2;
+    args.epilogue = epilogue;
+    TORCH_CHECK(epilogue == 0 || (epilogue == 1 && cta_pair && mode != 1 && !fp8),
+                "the SwiGLU epilogue runs on the bf16 CTA-pair kernel (a_out symmetric or absent)");
     args.block_n = block_n;
     args.num_sms = num_sms;
     args.timeout_ns = timeout_ns;
@@ -501,7 +504,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       args.n_copy = 0;
       args.M = (int)a.size(0);
     }
-    TORCH_CHECK(c.size(0) == args.M && c.size(1) == args.N, "c must be [M, N]");
+    TORCH_CHECK(c.size(0) == args.M && c.size(1) == (epilogue == 1 ? args.N / 2 : args.N),
+                "c must be [M, N] ([M, N / 2] with the SwiGLU epilogue)");
     if (tail_scratch.has_value() && cta_pair) {
       // first 4 KiB: arrival counters; the rest: fp32 partial accumulators
       TORCH_CHECK(tail_scratch->is_cuda() && tail_scratch->is_contiguous() && tail_scratch->nbytes() > 8192,
@@ -517,7 +521,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   }, py::arg("a"), py::arg("b"), py::arg("c"), py::arg("mode"), py::arg("shard_alloc"),
      py::arg("shard_offset"), py::arg("aout_alloc"), py::arg("aout_offset"), py::arg("a_out"),
      py::arg("flags"), py::arg("block_n"), py::arg("num_sms"), py::arg("n_copy"), py::arg("timeout_ns"),
-     py::arg("cta_pair") = false, py::arg("tail_scratch") = py::none());
+     py::arg("cta_pair") = false, py::arg("tail_scratch") = py::none(), py::arg("epilogue") = 0);
 
   m.def("check_push_schedule", &check_push_schedule);
   m.def("check_pair_work", &check_pair_work);

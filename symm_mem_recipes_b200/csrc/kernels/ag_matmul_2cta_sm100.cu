@@ -51,7 +51,12 @@ struct PairSmem {
 // kFp8: A, B, C (and the gathered A) hold e4m3 bytes.  All byte geometry stays
 // (128-byte rows, 16 KB A stage, 32 bytes of K per MMA); a K block is then 128
 // elements instead of 64 and the epilogue packs four outputs per 32-bit word.
-template <int BN, int STAGES, bool kFp8>
+// kSwiGlu (bf16, BN = 256): the rows of B are interleaved in groups of 128 so that every
+// 256-column tile holds 128 gate columns followed by the 128 matching up columns;
+// the epilogue writes SiLU(gate) * up, i.e. C is [M, N / 2] and tile ni covers its
+// columns [128 ni, 128 ni + 128).  The activation never makes a round trip through
+// memory and C is half as wide.  The split-K tail is not used with it.
+template <int BN, int STAGES, bool kFp8, bool kSwiGlu = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
                       const __grid_constant__ CUtensorMap tmap_a_out,
@@ -70,6 +75,7 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t cta_rank = cluster_ctarank();
   const bool leader = cta_rank == 0;
+  static_assert(!kSwiGlu || (BN == 256 && !kFp8), "the SwiGLU epilogue is built for bf16 tiles of 256 columns");
 
   uint32_t epoch = 0, flag_target = p.flag_target;
   if (p.mode == 2) {
@@ -295,6 +301,35 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
         if (acc == 0) acc_phase ^= 1;
         continue;
       }
+      if constexpr (kSwiGlu) {
+        const int F = p.N >> 1;                            // output columns
+        __nv_bfloat16* orow = p.c + (size_t)row * F + (size_t)ni * (BN / 2);
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          uint32_t g[32], u[32];
+          tmem_ld_32x32b_x32(taddr + (uint32_t)(c * 32), g);                 // gate columns
+          tmem_ld_32x32b_x32(taddr + (uint32_t)(BN / 2 + c * 32), u);        // the matching up columns
+          tmem_ld_wait();
+          const int col0 = ni * (BN / 2) + c * 32;
+          if (valid && row < p.M) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              if (col0 + v * 8 < F) {
+                float y[8];
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                  const float gv = __uint_as_float(g[v * 8 + q]);
+                  y[q] = gv / (1.0f + __expf(-gv)) * __uint_as_float(u[v * 8 + q]);
+                }
+                Vec16 o;
+                o.x = pack_bf16x2(y[0], y[1]); o.y = pack_bf16x2(y[2], y[3]);
+                o.z = pack_bf16x2(y[4], y[5]); o.w = pack_bf16x2(y[6], y[7]);
+                st_16(orow + c * 32 + v * 8, o);
+              }
+            }
+          }
+        }
+      } else {
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -334,6 +369,7 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
           }
         }
       }
+      }   // plain epilogue
       tcgen05_fence_before_thread_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc]), 0));
@@ -362,12 +398,12 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
   }
 }
 
-template <int BN, int STAGES, bool kFp8>
+template <int BN, int STAGES, bool kFp8, bool kSwiGlu = false>
 int launch_pair_variant(const CUtensorMap& ta_shard, const CUtensorMap& ta_out, const CUtensorMap& tb,
                         const AgMatmulParams& p, int grid, cudaStream_t stream) {
   using L = PairSmem<BN, STAGES>;
   static_assert(L::kTotal <= 232448, "shared memory limit exceeded");
-  auto kern = ag_matmul_2cta_kernel<BN, STAGES, kFp8>;
+  auto kern = ag_matmul_2cta_kernel<BN, STAGES, kFp8, kSwiGlu>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::kTotal);
   if (e != cudaSuccess) return (int)e;
   kern<<<grid, kGemmThreads, L::kTotal, stream>>>(ta_shard, ta_out, tb, p);
@@ -392,6 +428,10 @@ int launch_ag_matmul_2cta(const AgMatmulArgs& a, cudaStream_t stream) {
   }
   const int bn = a.block_n;
   if (bn != 128 && bn != 192 && bn != 224 && bn != 256) return cudaErrorInvalidValue;
+  const bool swiglu = a.epilogue == 1;
+  if (a.epilogue != 0 && a.epilogue != 1) return cudaErrorInvalidValue;
+  // gate / up interleaved in groups of 128 rows of B: whole groups only, bf16, 256-column tiles
+  if (swiglu && (fp8 || bn != 256 || a.N % 256 != 0)) return cudaErrorInvalidValue;
 
   AgMatmulParams p{};
   p.c = static_cast<__nv_bfloat16*>(a.c);
@@ -443,7 +483,7 @@ int launch_ag_matmul_2cta(const AgMatmulArgs& a, cudaStream_t stream) {
   p.tail_splits = 1;
   const int rem = total_tiles % pairs;
   const int k_blocks = (a.K * es + 127) / 128;                    // one K block = 128 bytes of a row
-  if (a.tail_scratch != nullptr && rem > 0 && rem * 2 <= pairs) {
+  if (a.tail_scratch != nullptr && !swiglu && rem > 0 && rem * 2 <= pairs) {
     int splits = pairs / rem;
     splits = splits >= 8 ? 8 : (splits >= 4 ? 4 : 2);
     // every part reduces BN / splits columns in vectors of 8
@@ -458,6 +498,7 @@ int launch_ag_matmul_2cta(const AgMatmulArgs& a, cudaStream_t stream) {
       if (me != cudaSuccess) return (int)me;
     }
   }
+  if (swiglu) return launch_pair_variant<256, 6, false, true>(ta_shard, ta_out, tb, p, grid, stream);
   if (fp8) {
     switch (bn) {
       case 128: return launch_pair_variant<128, 8, true>(ta_shard, ta_out, tb, p, grid, stream);

@@ -61,6 +61,9 @@ struct AgMatmulArgs {
   // 0 or 2: bf16.  1: A, B, C and a_out hold fp8 e4m3 (fp32 accumulation, no scale factors,
   // as upstream's FP8_OUTPUT path); 2-CTA kernel, modes 0 and 2; N and K multiples of 16.
   int elem_bytes;
+  // 0: C[M, N] = A B^T.  1 (2-CTA kernel, bf16, block_n 256, N % 256 == 0): B's rows are interleaved
+  // in groups of 128 (gate rows, then the matching up rows) and C[M, N / 2] = SiLU(gate) * up.
+  int epilogue;
   int block_n;           // 128, 192, 224 or 256
   int num_sms;           // CTAs to launch at most (copiers included)
   // communication: mode 0 = none (GEMM over a_local only),

@@ -23,7 +23,9 @@ PyTorch compositions by default; `fused_glue=True` (or SMR_FUSED_GLUE=1) swaps
 in the single-pass kernels of `ops.layer_glue`: RMSNorm writes straight into
 the symmetric buffer the next all_gather_matmul reads (and folds in the
 residual add before it), RoPE rotates Q and K in place inside the QKV buffer,
-SiLU(gate) * up is one pass.
+SiLU(gate) * up is one pass.  `fused_swiglu=True` (SMR_FUSED_SWIGLU=1) goes one
+step further for prefill: the gate and up weights are interleaved so that the
+activation is applied to the accumulators inside the all_gather_matmul epilogue.
 """
 from __future__ import annotations
 
@@ -80,9 +82,13 @@ class LlamaTPDecoderLayer:
     reference forward passes.  Plain object, inference only."""
 
     def __init__(self, cfg: LlamaTPConfig, device: torch.device, group=None, seed: int = 0,
-                 dtype: torch.dtype = torch.bfloat16, fused_glue: Optional[bool] = None):
+                 dtype: torch.dtype = torch.bfloat16, fused_glue: Optional[bool] = None,
+                 fused_swiglu: Optional[bool] = None):
         self.cfg, self.device, self.group = cfg, device, group
         self.fused_glue = (os.environ.get("SMR_FUSED_GLUE", "0") == "1") if fused_glue is None else bool(fused_glue)
+        # SiLU(gate) * up inside the epilogue of the gate/up all_gather_matmul (prefill only)
+        self.fused_swiglu = ((os.environ.get("SMR_FUSED_SWIGLU", "0") == "1") if fused_swiglu is None
+                             else bool(fused_swiglu))
         self.ws = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         ws = self.ws
@@ -103,6 +109,12 @@ class LlamaTPDecoderLayer:
         # decode path wants [K_local, N] (weights streamed row by row)
         self.w_o_t = self.w_o.t().contiguous()
         self.w_down_t = self.w_down.t().contiguous()
+        self.w_gate_up_interleaved = None
+        if self.fused_swiglu:
+            if self.ffn_local % 128:
+                raise ValueError("fused_swiglu needs the FFN width per rank to be a multiple of 128")
+            self.w_gate_up_interleaved = ops.interleave_gate_up(self.w_gate_up[: self.ffn_local],
+                                                                self.w_gate_up[self.ffn_local:])
         gn = torch.Generator(device="cpu").manual_seed(seed + 7919)   # norms are replicated
         self.norm1 = (1.0 + 0.1 * torch.randn(H, generator=gn)).to(dtype).to(device)
         self.norm2 = (1.0 + 0.1 * torch.randn(H, generator=gn)).to(dtype).to(device)
@@ -193,9 +205,13 @@ class LlamaTPDecoderLayer:
             x1 = x_shard + o
             h2.copy_(_rms_norm(x1, self.norm2, cfg.eps))
         self._mark("residual_norm2")
-        gu = ops.all_gather_matmul(h2, self.w_gate_up, group=self.group)
-        self._mark("gate_up_all_gather_matmul")
-        act = self._mlp_act(gu)
+        if self.fused_swiglu:
+            act = ops.all_gather_matmul(h2, self.w_gate_up_interleaved, group=self.group, epilogue="swiglu")
+            self._mark("gate_up_all_gather_matmul")
+        else:
+            gu = ops.all_gather_matmul(h2, self.w_gate_up, group=self.group)
+            self._mark("gate_up_all_gather_matmul")
+            act = self._mlp_act(gu)
         self._mark("silu_mul")
         if barrier_between_phases:
             symm_mem.rendezvous(h2, self.group).barrier(channel=2)

@@ -110,22 +110,50 @@ def _check_fp8_config(dtype: torch.dtype, config: "AgMatmulConfig") -> None:
         raise SymmMemError("float8_e4m3fn needs the CTA-pair kernel (config.cta_pair)")
 
 
+_EPILOGUES = {None: 0, "none": 0, "swiglu": 1}
+
+
+def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor, group: int = 128) -> torch.Tensor:
+    """Weight layout for `epilogue="swiglu"`: rows `[g*group, (g+1)*group)` of
+    `w_gate` [F, K], then the same rows of `w_up`, for g = 0, 1, ...  With it
+    every 256-column output tile holds 128 gate columns and their up columns.
+    Done once when the weights are loaded.  F must be a multiple of `group`."""
+    F, K = w_gate.shape
+    if w_up.shape != w_gate.shape or F % group:
+        raise SymmMemError(f"need w_gate and w_up of one shape [F, K] with F a multiple of {group}")
+    return torch.stack([w_gate.view(F // group, group, K), w_up.view(F // group, group, K)], dim=1) \
+        .reshape(2 * F, K).contiguous()
+
+
+def _epilogue_code(epilogue, dtype: torch.dtype, N: int, config: "AgMatmulConfig") -> int:
+    if epilogue not in _EPILOGUES:
+        raise SymmMemError('epilogue must be None or "swiglu"')
+    code = _EPILOGUES[epilogue]
+    if code == 1:
+        if dtype != torch.bfloat16 or not config.cta_pair or N % 256 or config.block_n not in (0, 256):
+            raise SymmMemError('epilogue="swiglu" needs bfloat16, the CTA-pair kernel, block_n 256 and N % 256 == 0 '
+                               "(B = interleave_gate_up(w_gate, w_up))")
+    return code
+
+
 @traced("smr.matmul")
 def matmul(a: torch.Tensor, b: torch.Tensor, c_out: Optional[torch.Tensor] = None,
-           config: AgMatmulConfig = DEFAULT_CONFIG) -> torch.Tensor:
-    """C[M, N] = A[M, K] @ B[N, K]^T on the tcgen05 kernel, no communication."""
+           config: AgMatmulConfig = DEFAULT_CONFIG, epilogue: Optional[str] = None) -> torch.Tensor:
+    """C[M, N] = A[M, K] @ B[N, K]^T on the tcgen05 kernel, no communication.
+    `epilogue="swiglu"`: see `all_gather_matmul`."""
     _check_2d("a", a)
     _check_2d("b", b, a.dtype)
     _check_fp8_config(a.dtype, config)
     M, K = a.shape
     N = b.shape[0]
     _check_nk(N, K, b, a.dtype)
+    epi = _epilogue_code(epilogue, a.dtype, N, config)
     if c_out is None:
-        c_out = torch.empty(M, N, dtype=a.dtype, device=a.device)
+        c_out = torch.empty(M, N // 2 if epi else N, dtype=a.dtype, device=a.device)
     sms = config.num_sms or _num_sms(a.device)
-    bn = config.block_n or choose_block_n(M, N, sms, config.cta_pair)
+    bn = 256 if epi else (config.block_n or choose_block_n(M, N, sms, config.cta_pair))
     C.ag_matmul(a, b, c_out, 0, None, 0, None, 0, None, None, bn, sms, 0, config.timeout_ms * 1_000_000,
-                config.cta_pair, _tail_buffer(a.device, config))
+                config.cta_pair, _tail_buffer(a.device, config), epi)
     return c_out
 
 
@@ -163,7 +191,7 @@ def gather_buffer(M: int, K: int, device: torch.device, group=None,
 @traced("smr.all_gather_matmul")
 def all_gather_matmul(a_shard: torch.Tensor, b: torch.Tensor, a_out: Optional[torch.Tensor] = None,
                       c_out: Optional[torch.Tensor] = None, config: AgMatmulConfig = DEFAULT_CONFIG,
-                      mm_only: bool = False, group=None) -> torch.Tensor:
+                      mm_only: bool = False, group=None, epilogue: Optional[str] = None) -> torch.Tensor:
     """`a_shard` is this rank's [M/WS, K] rows of A; `b` is [N, K]; returns
     `c_out` [M, N] = all_gather(A) @ B^T and leaves the gathered A in `a_out`.
 
@@ -176,22 +204,28 @@ def all_gather_matmul(a_shard: torch.Tensor, b: torch.Tensor, a_out: Optional[to
 
     `mm_only=True` skips the gather and multiplies `a_out` (or `a_shard` when
     no `a_out` is given) as it is, to time the GEMM alone.
+
+    `epilogue="swiglu"`: `b` is `interleave_gate_up(w_gate, w_up)` ([2F, K]) and
+    the result is `SiLU(A @ w_gate^T) * (A @ w_up^T)`, [M, F], computed on the
+    accumulators before they leave the SM (bf16, push gather or no gather).
     """
     _check_2d("a_shard", a_shard)
     _check_2d("b", b, a_shard.dtype)
     _check_fp8_config(a_shard.dtype, config)
     if mm_only:
-        return matmul(a_out if a_out is not None else a_shard, b, c_out, config)
+        return matmul(a_out if a_out is not None else a_shard, b, c_out, config, epilogue)
     rows, K = a_shard.shape
     N = b.shape[0]
     _check_nk(N, K, b, a_shard.dtype)
+    epi = _epilogue_code(epilogue, a_shard.dtype, N, config)
+    n_out = N // 2 if epi else N
     ws = dist.get_world_size(group) if dist.is_initialized() else 1
     M = rows * ws
     if c_out is None:
-        c_out = torch.empty(M, N, dtype=a_shard.dtype, device=a_shard.device)
+        c_out = torch.empty(M, n_out, dtype=a_shard.dtype, device=a_shard.device)
     if ws == 1:
         # nothing to gather: the shard is the gathered A; copy only on request
-        matmul(a_shard, b, c_out, config)
+        matmul(a_shard, b, c_out, config, epilogue)
         if a_out is not None:
             a_out.copy_(a_shard)
         return c_out
@@ -199,13 +233,14 @@ def all_gather_matmul(a_shard: torch.Tensor, b: torch.Tensor, a_out: Optional[to
         raise SymmMemError("rows per rank must be a multiple of 128 (the M tile and flag granularity)")
     if a_out is None:
         a_out = gather_buffer(M, K, a_shard.device, group, a_shard.dtype)
-    if tuple(a_out.shape) != (M, K) or tuple(c_out.shape) != (M, N):
-        raise SymmMemError("a_out must be [M, K] and c_out [M, N] with M = rows * world_size")
+    if tuple(a_out.shape) != (M, K) or tuple(c_out.shape) != (M, n_out):
+        raise SymmMemError("a_out must be [M, K] and c_out [M, N] ([M, N / 2] with the SwiGLU epilogue), "
+                           "M = rows * world_size")
     sms = config.num_sms or _num_sms(a_shard.device)
     t_ns = config.timeout_ms * 1_000_000
     if symm_mem.is_symm_mem_tensor(a_out):
         # push: every CTA is a GEMM CTA, the epilogue warps broadcast the shard
-        bn = config.block_n or choose_block_n(M, N, sms, config.cta_pair)
+        bn = 256 if epi else (config.block_n or choose_block_n(M, N, sms, config.cta_pair))
         n_copy = 0
         rec, aout_offset = symm_mem._find_record(a_out)
         hdl = symm_mem.rendezvous(a_out, group)
@@ -213,8 +248,10 @@ def all_gather_matmul(a_shard: torch.Tensor, b: torch.Tensor, a_out: Optional[to
             raise SymmMemError("a_out must start on a 16-byte boundary of its allocation")
         _check_gather_geometry(rec.notes, (aout_offset, M, K, a_shard.dtype))
         C.ag_matmul(a_shard, b, c_out, 2, None, 0, hdl.native, aout_offset, a_out, None,
-                    bn, sms, n_copy, t_ns, config.cta_pair, _tail_buffer(a_shard.device, config))
+                    bn, sms, n_copy, t_ns, config.cta_pair, _tail_buffer(a_shard.device, config), epi)
         return c_out
+    if epi:
+        raise SymmMemError('epilogue="swiglu" is not available in the pull mode; allocate a_out with symm_mem.empty')
     if a_shard.dtype != torch.bfloat16:
         raise SymmMemError("the pull mode (a_out in ordinary memory) is bfloat16 only; allocate a_out with "
                            "symm_mem.empty, or pass None")

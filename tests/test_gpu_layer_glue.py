@@ -85,3 +85,43 @@ def test_layer_with_fused_glue_matches_fp32():
     ref = full_precision_reference(weights, cfg, x.cpu(), batch, seq)
     assert (y.float().cpu() - ref).abs().max().item() < 0.1
     assert (y.float() - y_plain.float()).abs().max().item() < 0.1
+
+
+@pytest.mark.parametrize("M,F,K", [(128, 128, 64), (200, 384, 96), (640, 1024, 1024), (4096, 3584, 2048)])
+def test_matmul_with_swiglu_epilogue(M, F, K):
+    from symm_mem_recipes_b200 import ops
+    from symm_mem_recipes_b200.ops.ag_matmul import AgMatmulConfig
+    from symm_mem_recipes_b200.parallel import symm_mem
+    from symm_mem_recipes_b200.utils.testing import guarded_empty
+
+    torch.manual_seed(M + F + K)
+    a = (torch.randn(M, K, device="cuda") * 0.5).to(torch.bfloat16)
+    wg = (torch.randn(F, K, device="cuda") * 0.2).to(torch.bfloat16)
+    wu = (torch.randn(F, K, device="cuda") * 0.2).to(torch.bfloat16)
+    out, intact = guarded_empty((M, F), torch.bfloat16, "cuda")
+    out.fill_(float("nan"))
+    ops.matmul(a, ops.interleave_gate_up(wg, wu), out, AgMatmulConfig(timeout_ms=2000), epilogue="swiglu")
+    symm_mem.check_status("cuda")
+    g, u = a.float() @ wg.float().t(), a.float() @ wu.float().t()
+    ref = torch.nn.functional.silu(g) * u
+    err = (out.float() - ref).abs()
+    tol = ref.abs() * 2.0 ** -6 + 2e-3 * (K ** 0.5) * 0.1
+    assert bool((err <= tol).all()), float(err.max())
+    assert intact()
+
+
+def test_layer_with_fused_swiglu_matches_fp32():
+    from symm_mem_recipes_b200.models.llama_tp_layer import (LlamaTPConfig, LlamaTPDecoderLayer,
+                                                             full_precision_reference)
+
+    dev = torch.device("cuda", 0)
+    cfg = LlamaTPConfig.tiny(1)
+    layer = LlamaTPDecoderLayer(cfg, dev, seed=1, fused_glue=True, fused_swiglu=True)
+    batch, seq = 2, 128
+    torch.manual_seed(3)
+    x = (torch.randn(batch * seq, cfg.hidden, device=dev) * 0.5).to(torch.bfloat16)
+    y = layer.forward(x, batch, seq)
+    weights = [(layer.w_qkv.cpu(), layer.w_o.cpu(), layer.w_gate_up.cpu(), layer.w_down.cpu(),
+                layer.norm1.cpu(), layer.norm2.cpu())]
+    ref = full_precision_reference(weights, cfg, x.cpu(), batch, seq)
+    assert (y.float().cpu() - ref).abs().max().item() < 0.1

@@ -77,3 +77,27 @@ def test_one_gather_geometry_per_symmetric_allocation():
     with pytest.raises(SymmMemError):
         _check_gather_geometry(notes, (0, 8192, 8192, torch.bfloat16))    # another M on the same counters
     _check_gather_geometry({}, (0, 8192, 8192, torch.bfloat16))           # a new allocation starts clean
+
+
+def test_interleaved_gate_up_puts_matching_columns_in_one_tile():
+    """Layout contract of the SwiGLU epilogue: tile ni of A @ B^T (256 columns)
+    holds gate columns [128 ni, 128 ni + 128) followed by the same up columns."""
+    import torch
+
+    from symm_mem_recipes_b200.errors import SymmMemError
+    from symm_mem_recipes_b200.ops.ag_matmul import interleave_gate_up
+
+    F, K, M = 384, 32, 8
+    g = torch.Generator().manual_seed(0)
+    wg, wu, a = torch.randn(F, K, generator=g), torch.randn(F, K, generator=g), torch.randn(M, K, generator=g)
+    b = interleave_gate_up(wg, wu)
+    assert b.shape == (2 * F, K) and b.is_contiguous()
+    full = a @ b.t()
+    want = torch.nn.functional.silu(a @ wg.t()) * (a @ wu.t())
+    got = torch.empty(M, F)
+    for ni in range(2 * F // 256):
+        tile = full[:, ni * 256:(ni + 1) * 256]
+        got[:, ni * 128:(ni + 1) * 128] = torch.nn.functional.silu(tile[:, :128]) * tile[:, 128:]
+    assert torch.allclose(got, want, atol=1e-5)
+    with pytest.raises(SymmMemError):
+        interleave_gate_up(wg[:100], wu[:100])
