@@ -28,9 +28,10 @@ def main(argv=None, standalone: bool = True) -> int:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--skip-layer", action="store_true")
-    ap.add_argument("--fused-glue", default="env", choices=["env", "0", "1", "both"],
+    ap.add_argument("--fused-glue", default="env", choices=["env", "0", "1", "both", "all"],
                     help="norms / RoPE / SiLU-mul as single-pass kernels (1) or PyTorch compositions (0); "
-                         "env: SMR_FUSED_GLUE")
+                         "both: time the two; all: also with SiLU-mul inside the gate/up epilogue; "
+                         "env: SMR_FUSED_GLUE / SMR_FUSED_SWIGLU")
     ap.add_argument("--breakdown", action="store_true", help="also print the device time of every phase of the layer")
     ap.add_argument("--out", default=None)
     args = ap.parse_args(argv)
@@ -88,11 +89,14 @@ def main(argv=None, standalone: bool = True) -> int:
         del a, b, out, ref
     # ---- whole layer ----
     if not args.skip_layer:
-        glue_variants = {"env": [None], "0": [False], "1": [True], "both": [False, True]}[args.fused_glue]
+        # (fused_glue, fused_swiglu)
+        glue_variants = {"env": [(None, None)], "0": [(False, False)], "1": [(True, False)],
+                         "both": [(False, False), (True, False)],
+                         "all": [(False, False), (True, False), (True, True)]}[args.fused_glue]
         x = (torch.randn(T // world, cfg.hidden, device=dev) * 0.5).to(torch.bfloat16)
         us_r = None
-        for glue in glue_variants:
-            layer = LlamaTPDecoderLayer(cfg, dev, seed=1, fused_glue=glue)
+        for glue, swiglu in glue_variants:
+            layer = LlamaTPDecoderLayer(cfg, dev, seed=1, fused_glue=glue, fused_swiglu=swiglu)
             y = layer.forward(x, args.batch, args.seq)
             symm_mem.check_status(dev)
             y_ref = layer.forward_reference(x, args.batch, args.seq)
@@ -105,13 +109,14 @@ def main(argv=None, standalone: bool = True) -> int:
                 us_r = benchmark_with_event(lambda: layer.forward_reference(x, args.batch, args.seq), **bench)
             symm_mem.check_status(dev)
             emit({"op": "llama70b_layer_prefill", "world_size": world, "batch": args.batch, "seq": args.seq,
-                  "fused_glue": layer.fused_glue, "matches_library": ok, "max_rel_diff": round(rel, 5),
+                  "fused_glue": layer.fused_glue, "fused_swiglu": layer.fused_swiglu, "matches_library": ok, "max_rel_diff": round(rel, 5),
                   "smr_fused_us": round(us_f, 1), "nccl_cublas_us": round(us_r, 1),
                   "tokens_per_s_fused": round(T / us_f * 1e6), "speedup": round(us_r / us_f, 3)})
             if args.breakdown:
                 phases = layer.phase_times_us(x, args.batch, args.seq)
                 symm_mem.check_status(dev)
                 emit({"op": "llama70b_layer_prefill_phases", "world_size": world, "fused_glue": layer.fused_glue,
+                      "fused_swiglu": layer.fused_swiglu,
                       "rank": 0, "us": {k: round(v, 1) for k, v in phases.items()}})
         for B in (1, 4, 16):
             xd = (torch.randn(B, cfg.hidden, device=dev) * 0.5).to(torch.bfloat16)

@@ -183,8 +183,10 @@ def layer_tables(recs: list[dict]) -> Optional[str]:
              "outbound GB/s", "speed-up"], rows))
     if pre or dec:
         rows = []
-        for r in {(r["world_size"], r["batch"], r["seq"], r.get("fused_glue", False)): r for r in pre}.values():
+        for r in {(r["world_size"], r["batch"], r["seq"], r.get("fused_glue", False), r.get("fused_swiglu", False)): r
+                  for r in pre}.values():
             glue = ", single-pass norm / RoPE / SiLU kernels" if r.get("fused_glue") else ""
+            glue += ", SwiGLU in the GEMM epilogue" if r.get("fused_swiglu") else ""
             rows.append([str(r["world_size"]), f"prefill {r['batch']} x {r['seq']}{glue}", _fmt(r["smr_fused_us"]),
                          _fmt(r["nccl_cublas_us"]), f"{r['speedup']:.2f}x"])
         for r in {(r["world_size"], r["batch"]): r for r in dec}.values():
@@ -197,6 +199,7 @@ def layer_tables(recs: list[dict]) -> Optional[str]:
             total = sum(r["us"].values())
             rows = [[k, _fmt(v), _fmt(100.0 * v / total) + " %"] for k, v in r["us"].items()]
             glue = "single-pass glue kernels" if r.get("fused_glue") else "PyTorch glue"
+            glue += " + SwiGLU epilogue" if r.get("fused_swiglu") else ""
             parts.append(f"### prefill phases, WS {r['world_size']}, {glue} (rank 0)\n\n" +
                          _table(["phase", "µs", "share"], rows))
     return "\n\n".join(parts) if parts else None

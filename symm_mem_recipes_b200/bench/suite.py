@@ -48,7 +48,7 @@ def main() -> int:
     if "gemv" in only:
         gemv_all_reduce.main(["--out", out("gemv")], standalone=False)
     if "layer" in only:
-        llama_layer.main(["--out", out("layer")] + (["--fused-glue", "both", "--breakdown"] if args.layer_detail
+        llama_layer.main(["--out", out("layer")] + (["--fused-glue", "all", "--breakdown"] if args.layer_detail
                                                     else []), standalone=False)
     finish()
     return 0
