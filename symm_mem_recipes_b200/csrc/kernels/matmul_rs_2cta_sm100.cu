@@ -45,14 +45,6 @@ struct PairRsSmem {
 };
 static_assert(PairRsSmem<5, 4>::kTotal <= 232448, "shared memory limit exceeded");
 
-// Entry `rb` of the visiting order -> destination rank and row block inside it.
-__device__ __forceinline__ void row_block_coords(const RsParams& p, int rb, int& dest, int& mb) {
-  const int step = rb / p.blocks_per_rank;
-  mb = rb - step * p.blocks_per_rank;
-  dest = p.rank + 1 + step;
-  if (dest >= p.world_size) dest -= p.world_size;
-}
-
 template <int kStages, int kNStrips>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 matmul_rs_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,

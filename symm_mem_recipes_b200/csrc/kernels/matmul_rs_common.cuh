@@ -50,6 +50,16 @@ struct RsParams {
 
 __device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
+// CTA-pair kernel: entry `rb` of the list of 128-row blocks in visiting order (destination rank+1
+// first, own rows last) -> destination rank and row block inside it.  CTA c of the pair working on
+// tile t handles entry 2 * (t / n_tiles_n) + c.
+__host__ __device__ __forceinline__ void row_block_coords(const RsParams& p, int rb, int& dest, int& mb) {
+  const int step = rb / p.blocks_per_rank;
+  mb = rb - step * p.blocks_per_rank;
+  dest = p.rank + 1 + step;
+  if (dest >= p.world_size) dest -= p.world_size;
+}
+
 // Ordered fp32 sum of the WS partials of one [128 x 256] output tile, read from the
 // strip-major inbox (un-doing the row XOR of the 16-byte chunks) and written row-major.
 // 16 independent 16-byte loads are in flight per thread (the phase is bound by memory

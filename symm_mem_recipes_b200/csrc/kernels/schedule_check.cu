@@ -6,6 +6,7 @@
 #include <vector>
 
 #include "ag_matmul_common.cuh"
+#include "matmul_rs_common.cuh"
 
 namespace smr {
 
@@ -77,6 +78,38 @@ int check_pair_work(int total_tiles, int n_pairs, int k_blocks, int tail_tiles, 
   }
   for (int v : cover)
     if (v != 1) return 4;
+  return 0;
+}
+
+// CTA-pair reduce-scatter kernel: over all pairs, both CTAs and all tiles, every (destination, row
+// block, N tile) is produced exactly once, own rows last; entries past the end are skipped.
+// 0 = holds; 1 = a tile is missing or doubled; 2 = a destination other than the own one follows it.
+int check_rs_pair_schedule(int world_size, int rank, int blocks_per_rank, int n_tiles_n, int n_pairs) {
+  rs::RsParams p{};
+  p.world_size = world_size;
+  p.rank = rank;
+  p.blocks_per_rank = blocks_per_rank;
+  p.n_tiles_n = n_tiles_n;
+  const int n_rb = world_size * blocks_per_rank;
+  const int total_tiles = ((n_rb + 1) / 2) * n_tiles_n;
+  std::vector<int> cover((size_t)n_rb * n_tiles_n, 0);
+  for (int pair = 0; pair < n_pairs; ++pair)
+    for (int cta = 0; cta < 2; ++cta) {
+      bool own_seen = false;
+      for (int t = pair; t < total_tiles; t += n_pairs) {
+        const int pr = t / n_tiles_n, ni = t - pr * n_tiles_n;
+        const int rb = 2 * pr + cta;
+        if (rb >= n_rb) continue;
+        int dest, mb;
+        rs::row_block_coords(p, rb, dest, mb);
+        if (dest < 0 || dest >= world_size || mb < 0 || mb >= blocks_per_rank) return 1;
+        if (own_seen && dest != rank) return 2;
+        own_seen = own_seen || dest == rank;
+        cover[((size_t)dest * blocks_per_rank + mb) * n_tiles_n + ni]++;
+      }
+    }
+  for (int v : cover)
+    if (v != 1) return 1;
   return 0;
 }
 

@@ -66,3 +66,16 @@ def test_split_k_tail_covers_every_tile_once():
             if rc != 0:
                 bad.append((total, pairs, kb, tail, splits, rc))
     assert not bad, bad[:10]
+
+
+def test_reduce_scatter_pair_schedule_covers_every_tile_once():
+    # decoder-layer shapes at TP8: 32 row blocks per rank, N = 8192 (32 tiles), 74 pairs
+    for rank in range(8):
+        assert C.check_rs_pair_schedule(8, rank, 32, 32, 74) == 0
+    bad = []
+    for ws, bpr, n_tiles_n, pairs in itertools.product((2, 3, 4, 8), (1, 2, 3, 5, 32), (1, 2, 5, 32), (1, 3, 74)):
+        for rank in {0, ws - 1, ws // 2}:
+            rc = C.check_rs_pair_schedule(ws, rank, bpr, n_tiles_n, pairs)
+            if rc != 0:
+                bad.append((ws, rank, bpr, n_tiles_n, pairs, rc))
+    assert not bad, bad[:10]
