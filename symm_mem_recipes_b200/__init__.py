@@ -14,5 +14,6 @@ from .ops import (all_reduce, barrier_test, low_latency_all_reduce, multimem_all
 from .ops import all_gather_matmul, matmul, reference_all_gather_matmul  # noqa: F401,E402
 from .ops import gemv_all_reduce, reference_gemv_all_reduce  # noqa: F401,E402
 from .ops import matmul_reduce_scatter, reference_matmul_reduce_scatter  # noqa: F401,E402
+from .ops import matmul_all_reduce, reference_matmul_all_reduce  # noqa: F401,E402
 
 __version__ = "0.1.0"

@@ -609,6 +609,47 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
      py::arg("timeout_ns"), py::arg("trace") = py::none(), py::arg("deep_strips") = false,
      py::arg("cta_pair") = false);
 
+  // all-reduce form: `out` [M, N] lives in the symmetric allocation `out_alloc` at `out_offset`
+  m.def("matmul_all_reduce", [](torch::Tensor a, torch::Tensor b, torch::Tensor out,
+                                const std::shared_ptr<CudaSymmAllocation>& out_alloc, int64_t out_offset,
+                                const std::shared_ptr<CudaSymmAllocation>& workspace, int num_sms,
+                                uint64_t timeout_ns, bool cta_pair) {
+    auto ok2d = [](const torch::Tensor& t) {
+      return t.is_cuda() && t.dim() == 2 && t.is_contiguous() && t.scalar_type() == torch::kBFloat16;
+    };
+    TORCH_CHECK(ok2d(a) && ok2d(b) && ok2d(out), "a, b, out must be contiguous 2-D bf16 CUDA tensors");
+    TORCH_CHECK(a.size(1) == b.size(1), "A[M, K] and B[N, K] disagree on K");
+    TORCH_CHECK(out.size(0) == a.size(0) && out.size(1) == b.size(0), "out must be [M, N]");
+    TORCH_CHECK((char*)out.data_ptr() == (char*)out_alloc->local_ptr() + out_offset,
+                "out does not sit at out_offset of its allocation");
+    int dev = a.get_device();
+    c10::cuda::CUDAGuard guard(dev);
+    MatmulRsArgs args{};
+    args.a = a.data_ptr();
+    args.b = b.data_ptr();
+    args.out = nullptr;
+    args.M = (int)a.size(0);
+    args.N = (int)b.size(0);
+    args.K = (int)a.size(1);
+    args.pv = view_of(*workspace);
+    PeerView ov = view_of(*out_alloc);
+    TORCH_CHECK(ov.world_size == args.pv.world_size && ov.rank == args.pv.rank, "out and workspace: different groups");
+    TORCH_CHECK(matmul_rs_workspace_bytes(args.M, args.N) <= workspace->payload_bytes(), "workspace too small");
+    args.inbox_offset = 0;
+    for (int r = 0; r < args.pv.world_size; ++r) args.peer_base[r] = workspace->peer_ptr(r);
+    args.local_pad = workspace->peer_pad(args.pv.rank);
+    args.num_sms = num_sms;
+    args.timeout_ns = timeout_ns;
+    args.status = status_for(dev);
+    args.cta_pair = cta_pair;
+    args.all_reduce = true;
+    args.ar_peers = ov.buffers;
+    args.ar_mc = ov.multicast;
+    args.ar_offset = (size_t)out_offset;
+    rt_check(launch_matmul_reduce_scatter(args, current_stream(dev)), "matmul_all_reduce");
+  }, py::arg("a"), py::arg("b"), py::arg("out"), py::arg("out_alloc"), py::arg("out_offset"), py::arg("workspace"),
+     py::arg("num_sms"), py::arg("timeout_ns"), py::arg("cta_pair") = false);
+
   // ---- rank-local layer glue ----
   m.def("rms_norm", [](torch::Tensor x, c10::optional<torch::Tensor> residual, torch::Tensor w,
                        c10::optional<torch::Tensor> sum_out, torch::Tensor out, double eps) {

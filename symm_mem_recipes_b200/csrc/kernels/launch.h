@@ -141,6 +141,12 @@ struct MatmulRsArgs {
   uint64_t* trace;     // optional [num_sms][4] %globaltimer stamps per CTA (start, entered, GEMM done, reduced)
   bool deep_strips;    // 3-stage ring and five epilogue strips on the wire instead of 4 stages and two
   bool cta_pair;       // tcgen05 cta_group::2 main loop (256 x 256 tiles on CTA pairs), 5 stages, four strips
+  // all-reduce form: every rank ends up with the whole [M, N] sum in a SYMMETRIC output (`out` is unused);
+  // each rank reduces its rows and broadcasts them (multimem.st when `ar_mc`, else stores to every peer)
+  bool all_reduce;
+  void* const* ar_peers;   // device table: payload base of the output allocation on every rank
+  void* ar_mc;             // its multicast base or nullptr
+  size_t ar_offset;        // offset of the output tensor inside that payload
 };
 size_t matmul_rs_workspace_bytes(int M, int N);
 // Dispatches on `cta_pair` / `deep_strips`; same workspace layout and result bits for every variant.

@@ -45,7 +45,7 @@ struct PairRsSmem {
 };
 static_assert(PairRsSmem<5, 4>::kTotal <= 232448, "shared memory limit exceeded");
 
-template <int kStages, int kNStrips>
+template <int kStages, int kNStrips, bool kAllReduce = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 matmul_rs_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                       const RsParams p) {
@@ -277,12 +277,18 @@ matmul_rs_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       }
       if (!__syncthreads_and(ok)) break;
       switch (p.world_size) {
-        case 2: reduce_tile<2>(p, inbox, mb, ni); break;
-        case 4: reduce_tile<4>(p, inbox, mb, ni); break;
-        case 8: reduce_tile<8>(p, inbox, mb, ni); break;
-        default: reduce_tile<0>(p, inbox, mb, ni); break;
+        case 2: reduce_tile<2, kAllReduce>(p, inbox, mb, ni); break;
+        case 4: reduce_tile<4, kAllReduce>(p, inbox, mb, ni); break;
+        case 8: reduce_tile<8, kAllReduce>(p, inbox, mb, ni); break;
+        default: reduce_tile<0, kAllReduce>(p, inbox, mb, ni); break;
       }
     }
+  }
+
+  if constexpr (kAllReduce) {
+    // CTA i of every rank has finished broadcasting its rows: when all CTAs of this rank have passed
+    // here, the whole [M, N] output of this rank is complete
+    blockwise_barrier(p.pads, 1024u + blockIdx.x, p.rank, p.world_size, p.timeout_ns, p.status, kWhereRsArrive);
   }
 
   // ---------------- the last CTA to finish publishes this call's number ----------------
@@ -317,6 +323,14 @@ int launch_matmul_reduce_scatter_2cta(const MatmulRsArgs& a, cudaStream_t stream
   p.timeout_ns = a.timeout_ns;
   p.status = a.status;
   p.trace = a.trace;
+  if (a.all_reduce) {
+    if (a.ar_peers == nullptr || a.ar_offset % 16 != 0) return cudaErrorInvalidValue;
+    p.ar_peers = a.ar_peers;
+    p.ar_mc = a.ar_mc;
+    p.ar_offset = a.ar_offset;
+  } else if (a.out == nullptr) {
+    return cudaErrorInvalidValue;
+  }
   CUtensorMap ta, tb;
   if (make_tmap(&ta, a.a, (uint64_t)a.M, (uint64_t)a.K, kBM)) return cudaErrorInvalidValue;
   if (make_tmap(&tb, a.b, (uint64_t)a.N, (uint64_t)a.K, kBN / 2)) return cudaErrorInvalidValue;
@@ -328,6 +342,13 @@ int launch_matmul_reduce_scatter_2cta(const MatmulRsArgs& a, cudaStream_t stream
   const int grid = 2 * pairs;
   if ((uint32_t)(1024 + grid) * (uint32_t)ws > kBlockSlots) return cudaErrorInvalidValue;
   using L = PairRsSmem<5, 4>;
+  if (a.all_reduce) {
+    auto kern = matmul_rs_2cta_kernel<5, 4, true>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::kTotal);
+    if (e != cudaSuccess) return (int)e;
+    kern<<<grid, kThreads, L::kTotal, stream>>>(ta, tb, p);
+    return (int)cudaGetLastError();
+  }
   auto kern = matmul_rs_2cta_kernel<5, 4>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::kTotal);
   if (e != cudaSuccess) return (int)e;

@@ -8,6 +8,7 @@
 
 #include "../device/barrier.cuh"
 #include "../device/mbarrier.cuh"
+#include "../device/multimem.cuh"
 #include "../device/tcgen05.cuh"
 #include "../device/tma.cuh"
 #include "../device/vec.cuh"
@@ -46,6 +47,10 @@ struct RsParams {
   uint64_t timeout_ns;
   Status* status;
   uint64_t* trace;           // optional [grid][4] %globaltimer stamps: start, entered, GEMM done, reduced
+  // all-reduce form only: the reduced rows are broadcast into a symmetric [M, N] output on every rank
+  void* const* ar_peers;     // payload base of the output allocation on every rank
+  void* ar_mc;               // its multicast base, or nullptr (then plain stores to every peer)
+  size_t ar_offset;          // offset of the output tensor inside that payload
 };
 
 __device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
@@ -64,7 +69,9 @@ __host__ __device__ __forceinline__ void row_block_coords(const RsParams& p, int
 // strip-major inbox (un-doing the row XOR of the 16-byte chunks) and written row-major.
 // 16 independent 16-byte loads are in flight per thread (the phase is bound by memory
 // latency otherwise): 16 / WS output vectors at a time.  WS = 0: generic loop.
-template <int WS>
+// kAllReduce: instead of the local [M/WS, N] output, the tile goes to rows
+// [rank * M/WS + ...] of the symmetric [M, N] output of EVERY rank (one multimem.st, or WS stores).
+template <int WS, bool kAllReduce = false>
 __device__ __forceinline__ void reduce_tile(const RsParams& p, const char* inbox, int mb, int ni) {
   const int n0 = ni * kBN;
   const int strips = min(kStripsPerTile, (p.N - n0 + kStripCols - 1) / kStripCols);
@@ -126,7 +133,21 @@ __device__ __forceinline__ void reduce_tile(const RsParams& p, const char* inbox
       Vec16 o;
       o.x = pack_bf16x2(s[u][0], s[u][1]); o.y = pack_bf16x2(s[u][2], s[u][3]);
       o.z = pack_bf16x2(s[u][4], s[u][5]); o.w = pack_bf16x2(s[u][6], s[u][7]);
-      st_16(p.out + out_off[u], o);
+      if constexpr (kAllReduce) {
+        const size_t off = p.ar_offset +
+                           ((size_t)p.rank * p.blocks_per_rank * kBM * p.N + out_off[u]) * sizeof(__nv_bfloat16);
+        if (p.ar_mc != nullptr) {
+          multimem_st_16(static_cast<char*>(p.ar_mc) + off, o);
+        } else {
+          for (int s2 = 1; s2 <= p.world_size; ++s2) {            // own copy last
+            int peer = p.rank + s2;
+            if (peer >= p.world_size) peer -= p.world_size;
+            st_16(static_cast<char*>(p.ar_peers[peer]) + off, o);
+          }
+        }
+      } else {
+        st_16(p.out + out_off[u], o);
+      }
     }
   }
 }

@@ -62,7 +62,7 @@ __device__ __forceinline__ void tile_coords(const RsParams& p, int t, int& dest,
 // kStages: depth of the operand ring; kNStrips: epilogue strips that may be on the wire at once.
 // <4, 2> is the default; <3, 5> trades a stage for three more strips in flight (short-K shapes,
 // where the wire, not the main loop, is the limit).
-template <int kStages, int kNStrips>
+template <int kStages, int kNStrips, bool kAllReduce = false>
 __global__ void __launch_bounds__(kThreads, 1)
 matmul_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const RsParams p) {
@@ -273,12 +273,18 @@ matmul_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
       if (!__syncthreads_and(ok)) break;
       switch (p.world_size) {
-        case 2: reduce_tile<2>(p, inbox, mb, ni); break;
-        case 4: reduce_tile<4>(p, inbox, mb, ni); break;
-        case 8: reduce_tile<8>(p, inbox, mb, ni); break;
-        default: reduce_tile<0>(p, inbox, mb, ni); break;
+        case 2: reduce_tile<2, kAllReduce>(p, inbox, mb, ni); break;
+        case 4: reduce_tile<4, kAllReduce>(p, inbox, mb, ni); break;
+        case 8: reduce_tile<8, kAllReduce>(p, inbox, mb, ni); break;
+        default: reduce_tile<0, kAllReduce>(p, inbox, mb, ni); break;
       }
     }
+  }
+
+  if constexpr (kAllReduce) {
+    // CTA i of every rank has finished broadcasting its rows: when all CTAs of this rank have passed
+    // here, the whole [M, N] output of this rank is complete
+    blockwise_barrier(p.pads, 1024u + blockIdx.x, p.rank, p.world_size, p.timeout_ns, p.status, kWhereRsArrive);
   }
 
   // ---------------- the last CTA to finish publishes this call's number ----------------
@@ -319,6 +325,14 @@ int launch_matmul_reduce_scatter(const MatmulRsArgs& a, cudaStream_t stream) {
   p.timeout_ns = a.timeout_ns;
   p.status = a.status;
   p.trace = a.trace;
+  if (a.all_reduce) {
+    if (a.ar_peers == nullptr || a.deep_strips || a.ar_offset % 16 != 0) return cudaErrorInvalidValue;
+    p.ar_peers = a.ar_peers;
+    p.ar_mc = a.ar_mc;
+    p.ar_offset = a.ar_offset;
+  } else if (a.out == nullptr) {
+    return cudaErrorInvalidValue;
+  }
   CUtensorMap ta, tb;
   if (make_tmap(&ta, a.a, (uint64_t)a.M, (uint64_t)a.K, kBM)) return cudaErrorInvalidValue;
   if (make_tmap(&tb, a.b, (uint64_t)a.N, (uint64_t)a.K, kBN)) return cudaErrorInvalidValue;
@@ -328,6 +342,12 @@ int launch_matmul_reduce_scatter(const MatmulRsArgs& a, cudaStream_t stream) {
   if (a.deep_strips) {
     auto kern = matmul_rs_kernel<3, 5>;
     constexpr int smem = (int)RsSmem<3, 5>::kTotal;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    kern<<<grid, kThreads, smem, stream>>>(ta, tb, p);
+  } else if (a.all_reduce) {
+    auto kern = matmul_rs_kernel<4, 2, true>;
+    constexpr int smem = (int)RsSmem<4, 2>::kTotal;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     kern<<<grid, kThreads, smem, stream>>>(ta, tb, p);

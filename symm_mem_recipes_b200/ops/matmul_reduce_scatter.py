@@ -85,6 +85,60 @@ def matmul_reduce_scatter(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.
     return out
 
 
+_ar_outputs: dict[tuple, torch.Tensor] = {}
+
+
+@traced("smr.matmul_all_reduce")
+def matmul_all_reduce(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, group=None,
+                      num_sms: int = 0, timeout_ms: int = _TIMEOUT_MS, cta_pair: Optional[bool] = None) -> torch.Tensor:
+    """The same kernel with an all-reduce ending, for tensor parallelism without
+    sequence parallelism: every rank gets the whole [M, N] sum.  Rank r reduces
+    its M/WS rows as in `matmul_reduce_scatter` and then broadcasts them into
+    the output of every rank (one `multimem.st` through the NVSwitch, or plain
+    stores to every peer); an exit barrier inside the kernel proves that all
+    rows have landed.  Same bits on every rank.
+
+    `out` must live in symmetric memory (peers write into it).  With
+    `out=None` an internal symmetric [M, N] buffer per shape is used and
+    returned: it is overwritten by the next call of that shape.
+    Built, not yet run on a GPU."""
+    if a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[1]:
+        raise SymmMemError("need a[M, K] and b[N, K]")
+    ws = dist.get_world_size(group) if dist.is_initialized() else 1
+    M, K = a.shape
+    N = b.shape[0]
+    if ws == 1:
+        return matmul(a, b, out)
+    if M % (ws * 128) or N % 8 or K % 8:
+        raise SymmMemError("need M a multiple of 128 * world_size, N and K multiples of 8")
+    if out is None:
+        key = (M, N, a.device.index, symm_mem._group_key(group))
+        out = _ar_outputs.get(key)
+        if out is None:
+            out = symm_mem.empty(M, N, dtype=torch.bfloat16, device=a.device)
+            symm_mem.rendezvous(out, group)
+            _ar_outputs[key] = out
+    if not symm_mem.is_symm_mem_tensor(out) or tuple(out.shape) != (M, N):
+        raise SymmMemError("out must be a symmetric [M, N] tensor (symm_mem.empty): every rank writes into it")
+    _, out_offset = symm_mem._find_record(out)
+    out_hdl = symm_mem.rendezvous(out, group)
+    wsp = _workspace(M, N, a.device, group)
+    hdl = symm_mem.rendezvous(wsp, group)
+    if cta_pair is None:
+        cta_pair = os.environ.get("SMR_RS_CTA_PAIR", "0") == "1"
+    C.matmul_all_reduce(a, b, out, out_hdl.native, out_offset, hdl.native, num_sms or _num_sms(a.device),
+                        int(timeout_ms) * 1_000_000, bool(cta_pair))
+    return out
+
+
+def reference_matmul_all_reduce(a: torch.Tensor, b: torch.Tensor, group=None) -> torch.Tensor:
+    """Library baseline: cuBLAS GEMM, then NCCL all-reduce (bf16)."""
+    full = torch.matmul(a, b.t())
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(full, group=group)
+    return full
+
+
 def reference_matmul_reduce_scatter(a: torch.Tensor, b: torch.Tensor, group=None) -> torch.Tensor:
     """Library baseline: cuBLAS GEMM, then NCCL reduce-scatter (bf16)."""
     full = torch.matmul(a, b.t())

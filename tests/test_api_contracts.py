@@ -70,3 +70,8 @@ def test_barrier_test_kinds_are_checked():
         smr.barrier_test(FakeHandle(), kind="ring")
     with pytest.raises(SymmMemError, match="multicast"):
         smr.barrier_test(FakeHandle(), kind="nvls")
+
+
+def test_matmul_all_reduce_shape_checks():
+    with pytest.raises(SymmMemError, match="a\\[M, K\\]"):
+        smr.matmul_all_reduce(_bf16(256, 64), _bf16(128, 32))

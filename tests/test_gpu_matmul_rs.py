@@ -82,3 +82,44 @@ def test_matmul_reduce_scatter_world_of_one():
     b = (torch.randn(64, 128, device="cuda") * 0.1).to(torch.bfloat16)
     out = smr.matmul_reduce_scatter(a, b)
     assert torch.allclose(out.float(), a.float() @ b.float().t(), rtol=2e-2, atol=2e-2)
+
+
+def _ar_worker(rank, world_size, M, N, K, cta_pair):
+    import symm_mem_recipes_b200 as smr
+    from symm_mem_recipes_b200.parallel import symm_mem
+
+    dev = torch.device("cuda", rank)
+    failures = []
+    for it in range(3):
+        gens = [torch.Generator().manual_seed(2000 * it + r) for r in range(world_size)]
+        parts = [((torch.randn(M, K, generator=g) * 0.05).to(torch.bfloat16),
+                  (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16)) for g in gens]
+        a, b = parts[rank][0].to(dev), parts[rank][1].to(dev)
+        out = smr.matmul_all_reduce(a, b, cta_pair=cta_pair)
+        symm_mem.check_status(dev)
+        ref = torch.zeros(M, N, dtype=torch.float32)
+        for a_r, b_r in parts:
+            ref += (a_r.float() @ b_r.float().t()).to(torch.bfloat16).float()    # bf16 partials, fp32 sum
+        err = (out.float().cpu() - ref).abs()
+        if not bool((err <= ref.abs() * 2.0 ** -6 + 3e-2).all()):
+            failures.append(f"call {it}: max err {float(err.max())}")
+        gathered = [torch.empty_like(out) for _ in range(world_size)]
+        torch.distributed.all_gather(gathered, out.clone())
+        if not all(torch.equal(g.view(torch.int16), out.view(torch.int16)) for g in gathered):
+            failures.append(f"call {it}: ranks disagree bitwise")
+        rs = smr.matmul_reduce_scatter(a, b)
+        rows = M // world_size
+        if not torch.equal(rs.view(torch.int16), out[rank * rows:(rank + 1) * rows].view(torch.int16)):
+            failures.append(f"call {it}: own rows differ from matmul_reduce_scatter")
+        torch.cuda.synchronize()
+        torch.distributed.barrier()
+    assert not failures, failures
+
+
+@pytest.mark.gpu
+@pytest.mark.first_run
+@pytest.mark.multigpu(2)
+@pytest.mark.parametrize("cta_pair", [False, True])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 128), (768, 328, 192), (4096, 8192, 1024)])
+def test_matmul_all_reduce_2gpu(M, N, K, cta_pair):
+    spawn_ranks(_ar_worker, 2, "nccl", (M, N, K, cta_pair))
