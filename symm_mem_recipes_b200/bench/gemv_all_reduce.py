@@ -25,6 +25,8 @@ def main(argv=None, standalone: bool = True) -> int:
     ap.add_argument("--K", type=int, default=3584)
     ap.add_argument("--N", type=int, default=8192)
     ap.add_argument("--batches", default="1,4,16")
+    ap.add_argument("--extra-algos", default="",
+                    help="comma-separated kernels to time besides the default one: tc_tagged, simt")
     ap.add_argument("--out", default=None)
     args = ap.parse_args(argv)
     from symm_mem_recipes_b200.bench._common import finish, init_distributed
@@ -59,7 +61,17 @@ def main(argv=None, standalone: bool = True) -> int:
             state["i"] = (state["i"] + 1) % n_w
             torch.matmul(x, ws_[state["i"]])
 
-        for name, fn in (("smr_fused", fused), ("cublas_plus_nccl", lib), ("cublas_gemv_only", gemv_only)):
+        variants = [("smr_fused", fused), ("cublas_plus_nccl", lib), ("cublas_gemv_only", gemv_only)]
+        for algo in [a for a in args.extra_algos.split(",") if a]:
+            smr.gemv_all_reduce(x, ws_[0], out, algo=algo)
+            symm_mem.check_status(dev)
+
+            def fused_algo(algo=algo):
+                state["i"] = (state["i"] + 1) % n_w
+                smr.gemv_all_reduce(x, ws_[state["i"]], out, algo=algo)
+
+            variants.append((f"smr_fused:{algo}", fused_algo))
+        for name, fn in variants:
             us = benchmark_with_graph(fn, calls_per_graph=20, replays=10)
             rec = {"op": "gemv_all_reduce", "impl": name, "world_size": world, "batch": b, "K": args.K,
                    "N": args.N, "us": round(us, 2), "timing": "graph",

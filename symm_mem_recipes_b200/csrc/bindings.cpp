@@ -530,12 +530,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemv_workspace_bytes", [](int batch_tile, int N, int world_size) {
     return gemv_workspace_bytes(batch_tile, N, world_size, nullptr, nullptr, nullptr);
   });
-  m.def("gemv_tc_workspace_bytes", [](int N, int K, int world_size, int num_sms) {
-    return gemv_tc_workspace_bytes(N, K, world_size, num_sms, nullptr, nullptr, nullptr, nullptr);
-  });
+  m.def("gemv_tc_workspace_bytes", [](int N, int K, int world_size, int num_sms, bool tagged) {
+    return gemv_tc_workspace_bytes(N, K, world_size, num_sms, nullptr, nullptr, nullptr, nullptr, tagged);
+  }, py::arg("N"), py::arg("K"), py::arg("world_size"), py::arg("num_sms"), py::arg("tagged") = false);
   m.def("gemv_all_reduce", [](torch::Tensor x, torch::Tensor w, torch::Tensor out,
                               const std::shared_ptr<CudaSymmAllocation>& workspace, int64_t ws_offset,
-                              uint64_t timeout_ns, bool tensor_core, int num_sms) {
+                              uint64_t timeout_ns, bool tensor_core, int num_sms, bool tagged) {
     auto ok2d = [](const torch::Tensor& t) {
       return t.is_cuda() && t.dim() == 2 && t.is_contiguous() && t.scalar_type() == torch::kBFloat16;
     };
@@ -557,17 +557,18 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     args.status = status_for(dev);
     int bt = gemv_batch_tile(args.batch);
     TORCH_CHECK(bt > 0, "batch must be between 1 and 16");
+    TORCH_CHECK(!tagged || tensor_core, "the tagged exchange belongs to the tcgen05 kernel");
     if (tensor_core) {
       TORCH_CHECK(gemv_tc_workspace_bytes(args.N, args.K, args.pv.world_size, num_sms, nullptr, nullptr, nullptr,
-                                          nullptr) <= workspace->payload_bytes(), "workspace too small");
-      rt_check(launch_gemv_all_reduce_tc(args, num_sms, current_stream(dev)), "gemv_all_reduce (tcgen05)");
+                                          nullptr, tagged) <= workspace->payload_bytes(), "workspace too small");
+      rt_check(launch_gemv_all_reduce_tc(args, num_sms, current_stream(dev), tagged), "gemv_all_reduce (tcgen05)");
       return;
     }
     TORCH_CHECK(gemv_workspace_bytes(bt, args.N, args.pv.world_size, nullptr, nullptr, nullptr) + (size_t)ws_offset
                     <= workspace->payload_bytes(), "workspace too small");
     rt_check(launch_gemv_all_reduce(args, current_stream(dev)), "gemv_all_reduce");
   }, py::arg("x"), py::arg("w"), py::arg("out"), py::arg("workspace"), py::arg("ws_offset"),
-     py::arg("timeout_ns"), py::arg("tensor_core") = false, py::arg("num_sms") = 148);
+     py::arg("timeout_ns"), py::arg("tensor_core") = false, py::arg("num_sms") = 148, py::arg("tagged") = false);
 
   m.def("matmul_rs_workspace_bytes", &matmul_rs_workspace_bytes);
   m.def("matmul_reduce_scatter", [](torch::Tensor a, torch::Tensor b, torch::Tensor out,

@@ -19,6 +19,14 @@
 // tile's columns in slot order, so every rank produces the same bits.
 // Epoch / parity handling as in gemv_allreduce.cu: nothing is reset between
 // calls and the kernel can be replayed from a CUDA graph.
+//
+// Tagged variant (kTagged, meant for batch <= 4): the partials travel as 8-byte
+// words {fp32 value, call number}, the protocol of the low-latency all-reduce
+// in all_reduce.cu.  No flag and no release fence (which has to wait for the
+// acknowledgements of all pushes): the reducer polls the words themselves
+// until they carry this call's number.  Twice the bytes on the wire, one
+// NVLink crossing on the critical path instead of a crossing, a fence and a
+// flag.
 #include <cuda.h>
 #include <cuda_runtime.h>
 
@@ -58,7 +66,7 @@ struct GemvTcParams {
   int ksplit;
   void* const* buffers;   // workspace payload base of every rank
   size_t flags_offset;    // [2 parity][tiles][kFlagStride] u32
-  size_t inbox_offset;    // [2 parity][WS * ksplit][16][N] fp32
+  size_t inbox_offset;    // [2 parity][WS * ksplit][16][N] fp32 (tagged: 8-byte words {fp32, call number})
   int tiles;
   uint64_t timeout_ns;
   Status* status;
@@ -88,6 +96,7 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)
 
 __device__ __forceinline__ void group_sync_128() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
+template <bool kTagged>
 __global__ void __launch_bounds__(kThreads, 1)
 gemv_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                const GemvTcParams p) {
@@ -210,6 +219,59 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
 #pragma unroll
     for (int b = 0; b < 16; ++b) part[b * kTileN + col] = __uint_as_float(acc[b]);
     group_sync_128();
+    if constexpr (kTagged) {
+      // ---- push {value, call number} words; then poll the own inbox for every slot's words ----
+      if (!failed) {
+        const size_t off = parity_off + (size_t)my_slot * slot_stride + n0;          // in words
+        for (int item = etid; item < p.batch * (kTileN / 4); item += 128) {
+          const int b = item / (kTileN / 4), c4 = (item % (kTileN / 4)) * 4;
+          if (n0 + c4 >= p.N) continue;
+          const Vec16 v = *reinterpret_cast<const Vec16*>(&part[b * kTileN + c4]);
+          const Vec16 w0{v.x, epoch, v.y, epoch}, w1{v.z, epoch, v.w, epoch};
+          for (int j = 1; j <= ws; ++j) {                                 // own inbox last
+            int peer = rank + j;
+            if (peer >= ws) peer -= ws;
+            char* dst = static_cast<char*>(p.buffers[peer]) + p.inbox_offset + (off + (size_t)b * p.N + c4) * 8;
+            st_16(dst, w0);
+            st_16(dst + 16, w1);
+          }
+        }
+        const int share = kTileN / p.ksplit;
+        const int c0 = n0 + kh * share;
+        const char* inbox = my_ws + p.inbox_offset;
+        for (int item = etid; item < p.batch * (share / 4) && flags_ok; item += 128) {
+          const int b = item / (share / 4), c = c0 + (item % (share / 4)) * 4;
+          if (c >= p.N) continue;
+          float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
+          Deadline d(p.timeout_ns);
+          for (int sl = 0; sl < slots; ++sl) {                            // slot order: same bits on every rank
+            const char* src = inbox + (parity_off + (size_t)sl * slot_stride + (size_t)b * p.N + c) * 8;
+            Vec16 a, g;
+            bool got = false;
+            while (!got) {
+              asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                           : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(src) : "memory");
+              asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                           : "=r"(g.x), "=r"(g.y), "=r"(g.z), "=r"(g.w) : "l"(src + 16) : "memory");
+              got = a.y == epoch && a.w == epoch && g.y == epoch && g.w == epoch;
+              if (!got && !d.alive()) {
+                report_status(p.status, kTimeoutFlag, rank, tile, sl, kWhereGemvArrive, epoch);
+                flags_ok = 0;
+                break;
+              }
+            }
+            if (!got) break;
+            s4.x += __uint_as_float(a.x); s4.y += __uint_as_float(a.z);
+            s4.z += __uint_as_float(g.x); s4.w += __uint_as_float(g.z);
+          }
+          if (!flags_ok) break;
+          uint2 o;
+          o.x = pack_bf16x2(s4.x, s4.y);
+          o.y = pack_bf16x2(s4.z, s4.w);
+          *reinterpret_cast<uint2*>(p.out + (size_t)b * p.N + c) = o;
+        }
+      }
+    } else {
     if (!failed) {
       const size_t off = parity_off + (size_t)my_slot * slot_stride + n0;
       for (int item = etid; item < p.batch * (kTileN / 4); item += 128) {
@@ -270,6 +332,7 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         *reinterpret_cast<uint2*>(p.out + (size_t)b * p.N + c) = o;
       }
     }
+    }   // flagged exchange
   }
 
   if (__any_sync(0xffffffffu, failed)) {
@@ -316,13 +379,13 @@ int pick_ksplit(int N, int K, int num_sms) {
 }  // namespace
 
 size_t gemv_tc_workspace_bytes(int N, int K, int world_size, int num_sms, size_t* flags_offset,
-                               size_t* inbox_offset, int* tiles, int* ksplit) {
+                               size_t* inbox_offset, int* tiles, int* ksplit, bool tagged) {
   int t = (N + kTileN - 1) / kTileN;
   int ks = pick_ksplit(N, K, num_sms);
   size_t flags_off = 256;
   size_t flags_bytes = (size_t)2 * t * kFlagStride * 4;
   size_t inbox_off = (flags_off + flags_bytes + 255) & ~(size_t)255;
-  size_t inbox_bytes = (size_t)2 * world_size * ks * kBatchN * N * 4;
+  size_t inbox_bytes = (size_t)2 * world_size * ks * kBatchN * N * (tagged ? 8 : 4);
   if (flags_offset) *flags_offset = flags_off;
   if (inbox_offset) *inbox_offset = inbox_off;
   if (tiles) *tiles = t;
@@ -330,7 +393,7 @@ size_t gemv_tc_workspace_bytes(int N, int K, int world_size, int num_sms, size_t
   return inbox_off + inbox_bytes;
 }
 
-int launch_gemv_all_reduce_tc(const GemvArgs& a, int num_sms, cudaStream_t stream) {
+int launch_gemv_all_reduce_tc(const GemvArgs& a, int num_sms, cudaStream_t stream, bool tagged) {
   if (a.batch < 1 || a.batch > kBatchN || a.N % 8 != 0 || a.K % 8 != 0 || a.ws_offset != 0)
     return cudaErrorInvalidValue;
   GemvTcParams p{};
@@ -341,15 +404,22 @@ int launch_gemv_all_reduce_tc(const GemvArgs& a, int num_sms, cudaStream_t strea
   p.timeout_ns = a.timeout_ns;
   p.status = a.status;
   gemv_tc_workspace_bytes(a.N, a.K, a.pv.world_size, num_sms, &p.flags_offset, &p.inbox_offset, &p.tiles,
-                          &p.ksplit);
+                          &p.ksplit, tagged);
   if (p.world_size * p.ksplit > kFlagStride) return cudaErrorInvalidValue;
   CUtensorMap tw, tx;
   if (encode(&tw, a.w, (uint64_t)a.N, (uint64_t)a.K, 64, kBK)) return cudaErrorInvalidValue;
   if (encode(&tx, a.x, (uint64_t)a.K, (uint64_t)a.batch, kBK, kBatchN)) return cudaErrorInvalidValue;
-  cudaError_t e = cudaFuncSetAttribute(gemv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  if (tagged) {
+    cudaError_t e = cudaFuncSetAttribute(gemv_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)kSmemTotal);
+    if (e != cudaSuccess) return (int)e;
+    gemv_tc_kernel<true><<<p.tiles * p.ksplit, kThreads, kSmemTotal, stream>>>(tw, tx, p);
+    return (int)cudaGetLastError();
+  }
+  cudaError_t e = cudaFuncSetAttribute(gemv_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)kSmemTotal);
   if (e != cudaSuccess) return (int)e;
-  gemv_tc_kernel<<<p.tiles * p.ksplit, kThreads, kSmemTotal, stream>>>(tw, tx, p);
+  gemv_tc_kernel<false><<<p.tiles * p.ksplit, kThreads, kSmemTotal, stream>>>(tw, tx, p);
   return (int)cudaGetLastError();
 }
 
@@ -428,7 +498,7 @@ extern "C" int smr_gemv_bf16_noalloc(const void* x, const void* w, void* out, in
   p.buffers = reinterpret_cast<void* const*>(base);
   p.timeout_ns = 2000000000ull;
   p.status = nullptr;
-  size_t need = gemv_tc_workspace_bytes(N, K, 1, sms, &p.flags_offset, &p.inbox_offset, &p.tiles, &p.ksplit);
+  size_t need = gemv_tc_workspace_bytes(N, K, 1, sms, &p.flags_offset, &p.inbox_offset, &p.tiles, &p.ksplit, false);
   if (need + 256 > (size_t)SMR_GEMV_NOALLOC_SCRATCH_BYTES)
     return noalloc_fail(1, err, err_len, "this shape needs more scratch than the static array holds");
   CUtensorMap tw, tx;
@@ -441,9 +511,9 @@ extern "C" int smr_gemv_bf16_noalloc(const void* x, const void* w, void* out, in
   // "CTAs done" must read zero when the kernel starts; an aborted earlier call may have left it set
   e = cudaMemsetAsync(base + 256 + 4, 0, 4, stream);
   if (e != cudaSuccess) return noalloc_fail(3, err, err_len, "cudaMemsetAsync: ", cudaGetErrorString(e));
-  e = cudaFuncSetAttribute(gemv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTotal);
+  e = cudaFuncSetAttribute(gemv_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTotal);
   if (e != cudaSuccess) return noalloc_fail(3, err, err_len, "cudaFuncSetAttribute: ", cudaGetErrorString(e));
-  gemv_tc_kernel<<<p.tiles * p.ksplit, kThreads, kSmemTotal, stream>>>(tw, tx, p);
+  gemv_tc_kernel<false><<<p.tiles * p.ksplit, kThreads, kSmemTotal, stream>>>(tw, tx, p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return noalloc_fail(3, err, err_len, "kernel launch: ", cudaGetErrorString(e));
   return 0;

@@ -121,9 +121,11 @@ size_t gemv_workspace_bytes(int batch_tile, int N, int world_size, size_t* flags
 int gemv_batch_tile(int batch);   // smallest supported tile >= batch, -1 if none
 int launch_gemv_all_reduce(const GemvArgs& args, cudaStream_t stream);
 // Tensor-core (tcgen05, swap A/B) variant; its workspace layout differs.
+// `tagged`: partials travel as {fp32, call number} words and are polled directly (no flags, no
+// release fence); twice the inbox.  Meant for batch <= 4.
 size_t gemv_tc_workspace_bytes(int N, int K, int world_size, int num_sms, size_t* flags_offset,
-                               size_t* inbox_offset, int* tiles, int* ksplit);
-int launch_gemv_all_reduce_tc(const GemvArgs& args, int num_sms, cudaStream_t stream);
+                               size_t* inbox_offset, int* tiles, int* ksplit, bool tagged = false);
+int launch_gemv_all_reduce_tc(const GemvArgs& args, int num_sms, cudaStream_t stream, bool tagged = false);
 
 // ---- fused GEMM + reduce-scatter (prefill, row-parallel linear) --------------
 struct MatmulRsArgs {

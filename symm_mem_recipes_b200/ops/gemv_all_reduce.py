@@ -27,16 +27,16 @@ _TIMEOUT_MS = int(os.environ.get("SMR_TIMEOUT_MS", "10000"))
 
 
 def _workspace(batch_tile: int, N: int, K: int, device: torch.device, group, tensor_core: bool,
-               sms: int) -> torch.Tensor:
+               sms: int, tagged: bool = False) -> torch.Tensor:
     """Symmetric scratch (inboxes, flags, epoch) for one (kernel, batch tile,
     N, K): allocated and rendezvoused at the first call, which is therefore
     collective; all ranks must make the same sequence of first calls."""
     ws = dist.get_world_size(group) if dist.is_initialized() else 1
-    key = (tensor_core, batch_tile, N, K, device.index, symm_mem._group_key(group))
+    key = (tensor_core, tagged, batch_tile, N, K, device.index, symm_mem._group_key(group))
     t = _workspaces.get(key)
     if t is None:
         if tensor_core:
-            nbytes = C.gemv_tc_workspace_bytes(N, K, ws, sms)
+            nbytes = C.gemv_tc_workspace_bytes(N, K, ws, sms, tagged)
         else:
             nbytes = C.gemv_workspace_bytes(batch_tile, N, ws)
         t = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
@@ -52,7 +52,10 @@ def gemv_all_reduce(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor
     all-reduced [B, N] in bf16, bitwise identical on every rank.
 
     `algo`: "tc" = tcgen05 kernel (weights streamed by TMA, swap-A/B MMA);
-    "simt" = CUDA-core kernel.  Default from SMR_GEMV_ALGO, else "tc"."""
+    "simt" = CUDA-core kernel; "tc_tagged" = the tcgen05 kernel exchanging its
+    partials as {value, call number} words that the reducer polls directly
+    (no flags, no release fence; meant for batch <= 4; built, not yet run on a
+    GPU).  Default from SMR_GEMV_ALGO, else "tc"."""
     if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[0]:
         raise SymmMemError("need x[B, K] and w[K, N]")
     B, N = x.shape[0], w.shape[1]
@@ -63,14 +66,17 @@ def gemv_all_reduce(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor
     if out is None:
         out = torch.empty(B, N, dtype=torch.bfloat16, device=x.device)
     algo = algo or os.environ.get("SMR_GEMV_ALGO", "tc")
-    if algo not in ("tc", "simt"):
-        raise SymmMemError('algo must be "tc" or "simt"')
-    tensor_core = algo == "tc" and x.shape[1] % 8 == 0
+    if algo not in ("tc", "simt", "tc_tagged"):
+        raise SymmMemError('algo must be "tc", "tc_tagged" or "simt"')
+    if algo == "tc_tagged" and x.shape[1] % 8:
+        raise SymmMemError("the tcgen05 kernels need K to be a multiple of 8")
+    tagged = algo == "tc_tagged"
+    tensor_core = algo != "simt" and x.shape[1] % 8 == 0
     sms = _num_sms(x.device)
     bt = 16 if tensor_core else C.gemv_batch_tile(B)
-    wsp = _workspace(bt, N, x.shape[1], x.device, group, tensor_core, sms)
+    wsp = _workspace(bt, N, x.shape[1], x.device, group, tensor_core, sms, tagged)
     hdl = symm_mem.rendezvous(wsp, group)
-    C.gemv_all_reduce(x.contiguous(), w, out, hdl.native, 0, int(timeout_ms) * 1_000_000, tensor_core, sms)
+    C.gemv_all_reduce(x.contiguous(), w, out, hdl.native, 0, int(timeout_ms) * 1_000_000, tensor_core, sms, tagged)
     return out
 
 

@@ -67,3 +67,20 @@ def test_gemv_all_reduce_2gpu(B, algo):
 @pytest.mark.multigpu(8)
 def test_gemv_all_reduce_8gpu():
     spawn_ranks(_gemv_worker, 8, "nccl", (16, 3584, 8192))
+
+
+# The tagged-word exchange of the tcgen05 kernel: compiled, first run on hardware pending.
+@pytest.mark.gpu
+@pytest.mark.first_run
+@pytest.mark.parametrize("B,K,N", [(1, 512, 256), (4, 3584, 8192), (16, 3584, 8192), (3, 1000, 328)])
+def test_gemv_tagged_world_of_one(B, K, N):
+    torch.cuda.set_device(0)
+    _gemv_worker(0, 1, B, K, N, "tc_tagged")
+
+
+@pytest.mark.gpu
+@pytest.mark.first_run
+@pytest.mark.multigpu(2)
+@pytest.mark.parametrize("B", [1, 4, 16])
+def test_gemv_tagged_2gpu(B):
+    spawn_ranks(_gemv_worker, 2, "nccl", (B, 3584, 8192, "tc_tagged"))
