@@ -206,3 +206,60 @@ def _counting_barriers_worker(rank, world_size, numel):
 @pytest.mark.multigpu(2)
 def test_counting_barriers_2gpu():
     spawn_ranks(_counting_barriers_worker, 2, "nccl", (1 << 20,))
+
+
+def _leaving_rank_worker(rank, world_size):
+    """A rank stops taking part between steps (nothing of it in flight); the
+    others learn of it on the host and do not launch.  The leaver stays alive
+    until the survivors are done, so no mapping of a dead process is involved."""
+    import time
+
+    import symm_mem_recipes_b200 as smr
+    from symm_mem_recipes_b200.parallel import symm_mem
+    from symm_mem_recipes_b200.parallel.health import Heartbeat, PeerLost
+    from symm_mem_recipes_b200.parallel.store import _store_of
+
+    dev = torch.device("cuda", rank)
+    store = _store_of(None)
+    hb = Heartbeat(interval_s=0.05)
+    hb.wait_for_all(timeout_s=60)
+    t = symm_mem.empty(1 << 16, dtype=torch.bfloat16, device=dev)
+    t.copy_(seeded_normal_bf16(1 << 16, rank).to(dev))
+    hdl = symm_mem.rendezvous(t)
+    assert not hdl.has_multicast                 # plain peer loads only in this test
+    for _ in range(3):                           # all present: check passes, kernels run
+        hb.check(max_age_s=10.0)
+        smr.one_shot_all_reduce(t, exit_barrier=True)
+        hdl.check()
+    torch.cuda.synchronize()
+    torch.distributed.barrier()
+    leaver = world_size - 1
+    if rank == leaver:
+        hb.stop()                                # announces the leave; launches nothing from here on
+        store.wait([f"leaving_test/done/{r}" for r in range(world_size - 1)])
+        return
+    lost = None
+    deadline = time.time() + 30
+    while lost is None and time.time() < deadline:
+        try:
+            hb.check(max_age_s=10.0)             # what a serving loop calls before every launch
+            time.sleep(0.02)
+        except PeerLost as e:
+            lost = e
+    ok = lost is not None and lost.rank == leaver
+    # the device is untouched and healthy: a local kernel still runs, the status record is clean
+    x = torch.ones(1024, device=dev)
+    ok = ok and float(x.sum()) == 1024.0
+    hdl.check()
+    hb.stop(leaving=False)
+    store.set(f"leaving_test/done/{rank}", "1")
+    assert ok, f"expected PeerLost for rank {leaver}, got {lost!r}"
+
+
+@pytest.mark.gpu
+@pytest.mark.first_run
+@pytest.mark.multigpu(2)
+def test_rank_leaving_between_steps_is_noticed_before_the_next_launch(monkeypatch):
+    monkeypatch.setenv("NCCL_NVLS_ENABLE", "0")
+    monkeypatch.setenv("SMR_DISABLE_MULTICAST", "1")
+    spawn_ranks(_leaving_rank_worker, 2, "nccl", ())
