@@ -4,6 +4,9 @@ down-projection decode shape: x [b, 3584], W [3584, 8192] per rank, b in {1, 4, 
     torchrun --nnodes 1 --nproc-per-node 8 --master-addr 127.0.0.1 \
         -m symm_mem_recipes_b200.bench.gemv_all_reduce
 
+No upstream counterpart; timing follows the upstream drivers' conventions
+(median, kernel time, rank 0 prints: symm_mem_recipes/triton_one_shot_all_reduce.py:156-162).
+
 Device time per call from CUDA-graph replay (the ops take ~10-30 µs, less than
 an eager launch), maximum over ranks.  The weight (56 MiB) is larger than what a
 single call can keep in L2 together with the previous call's, and both

@@ -9,7 +9,10 @@ Times (device, CUDA events, max over ranks, L2 flushed before every timed call):
     down-proj [T, 3584] x [8192, 3584]^T per rank at TP8;
   * the whole prefill layer, fused and reference;
   * one decode step (batch 1/4/16), fused GEMV + all-reduce against cuBLAS + NCCL.
-Random-init weights (seeded per rank), synthetic activations.
+Random-init weights (seeded per rank), synthetic activations.  No upstream
+counterpart: the upstream recipes time single ops (the fused all-gather
+matmul, symm_mem_recipes/triton_all_gather_matmul.py:394-418); this is the
+workload those ops were written for, with the shapes of its README.md:24-29 rows.
 """
 from __future__ import annotations
 

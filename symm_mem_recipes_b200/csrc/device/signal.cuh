@@ -1,6 +1,10 @@
 // Cross-GPU signalling primitives: scoped loads / stores / atomics in inline
 // PTX and bounded spin loops built on them.
 //
+// Upstream writes these qualifiers inline where it needs them and spins
+// without a bound (symm_mem_recipes/triton_barrier.py:112-139,
+// triton_all_gather_matmul.py:72-95).
+//
 // Every wait takes a deadline in nanoseconds of %globaltimer plus a hard
 // iteration cap.  When either runs out the wait records a Status and returns
 // false; the caller unwinds (frees TMEM, drains copies) and returns.

@@ -1,6 +1,9 @@
 // 5th-generation tensor core (tcgen05) and tensor memory (TMEM) in inline PTX:
 // allocation, shared-memory matrix descriptors, the instruction descriptor,
 // MMA issue, commit to an mbarrier and accumulator read-back.  sm_100a only.
+// Upstream's contraction is `tl.dot(a, b.T, accumulator)`
+// (symm_mem_recipes/triton_all_gather_matmul.py:185), which Triton lowers to
+// Hopper's warpgroup MMA; this header is its Blackwell counterpart written out.
 #pragma once
 #include <stdint.h>
 

@@ -2,6 +2,9 @@
 // (cp.async.bulk) in inline PTX.  No load here carries a cluster-multicast
 // qualifier: a remote tile is fetched by the CTA that needs it.
 //
+// Upstream reaches TMA through Triton's descriptor loads and stores
+// (symm_mem_recipes/triton_all_gather_matmul.py:166-193, descriptors built at :255-286).
+//
 // Alignment rule for every tiled copy: the innermost coordinate times the
 // element size must be a multiple of 16 bytes (8 elements for bf16).
 #pragma once

@@ -1,4 +1,6 @@
-// all_gather_matmul with tcgen05 `cta_group::2`: two CTAs on neighbouring SMs
+// The consumer GEMM of all_gather_matmul (upstream: `matmul_kernel_tma_persistent`,
+// symm_mem_recipes/triton_all_gather_matmul.py:98-193, launched from :295-315)
+// with tcgen05 `cta_group::2`: two CTAs on neighbouring SMs
 // (a cluster of 2) share one 256 x BN tile.  Each CTA stages ITS OWN 128 rows
 // of A and ITS OWN half of the B tile (BN/2 rows) with ordinary TMA loads — no
 // cluster-multicast qualifier anywhere — and the leader CTA's single MMA thread

@@ -1,6 +1,13 @@
 // Pieces shared by the 1-CTA and the 2-CTA (cta_group::2) all_gather_matmul
 // kernels: parameters, the M schedule, the epilogue-warp push of the own shard
 // and the tensor-map builder.
+//
+// Upstream counterparts (symm_mem_recipes/triton_all_gather_matmul.py):
+//   push_pieces + arrival counters   <->  all_gather_with_progress, :20-56 (copy
+//                                         engine + cuStreamWriteValue32 per shard)
+//   flag wait in the producer warp   <->  wait_signal, :72-95
+//   scheduled_block                  <->  the rank pivot of pid_m, :157-163
+//   make_tmap                        <->  create_2d_tma_descriptor + cache, :196-213, 255-286
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>

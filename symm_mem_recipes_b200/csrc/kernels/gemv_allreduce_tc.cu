@@ -1,5 +1,7 @@
 // Fused GEMV + all-reduce on the tensor cores (tcgen05), for decode batches
-// 1..16.  Same contract as gemv_allreduce.cu:
+// 1..16.  No upstream counterpart (upstream's only reduction is the one-shot
+// all-reduce, symm_mem_recipes/triton_one_shot_all_reduce.py:59-93, whose
+// rank-ordered sum this kernel keeps).  Same contract as gemv_allreduce.cu:
 //     out[b, n] = sum over ranks r of  x_r[b, :] . W_r[:, n]
 //
 // The product is computed transposed ("swap A/B") so that the skinny batch

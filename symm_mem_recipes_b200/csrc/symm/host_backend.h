@@ -2,7 +2,9 @@
 // pad) mapped by every rank of the host, and the same barrier / all-reduce
 // protocols executed with host atomics.  It exists so that the allocator API,
 // the rendezvous, the dispatcher and the barrier state machine can be tested
-// with `gloo` ranks on a machine without a GPU.
+// with `gloo` ranks on a machine without a GPU.  No upstream counterpart: the
+// upstream recipes are only exercised by GPU drivers
+// (symm_mem_recipes/triton_barrier.py:173-200, triton_one_shot_all_reduce.py:128-164).
 #pragma once
 #include <stdint.h>
 

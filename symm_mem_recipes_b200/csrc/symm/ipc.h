@@ -4,6 +4,11 @@
 // as SCM_RIGHTS ancillary data with a small header saying who sent it and what
 // it is.  The socket names themselves are exchanged through the
 // torch.distributed Store by the Python layer.
+//
+// Upstream has no code for this: its `rendezvous` calls
+// (symm_mem_recipes/triton_all_gather_matmul.py:28, 226;
+// triton_one_shot_all_reduce.py:111; triton_barrier.py:198) rely on torch's
+// own handle exchange.
 #pragma once
 #include <stdint.h>
 
