@@ -48,6 +48,8 @@ def main(argv=None, standalone: bool = True) -> int:
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--iters", type=int, default=25)
     ap.add_argument("--out", default=None)
+    ap.add_argument("--with-push-copy", action="store_true",
+                    help="also time an ordinary a_out served by the push kernel plus one local copy")
     ap.add_argument("--upstream-table", action="store_true",
                     help="run the nine (model, M) shapes of the upstream README instead of --M/--N/--K")
     ap.add_argument("--print-ptxas", "--print_ptx", dest="print_ptxas", action="store_true",
@@ -132,6 +134,11 @@ def _one_shape(args, M, N, K, rank, world, dev, lines) -> None:
         cfg = AgMatmulConfig(block_n=args.block_n, n_copy=n_copy)
         us = benchmark_with_event(lambda: smr.all_gather_matmul(a_shard, b, a_out_plain, c, cfg), **bench)
         emit("smr_fused", us, copy_ctas=n_copy, gather="pull")
+        symm_mem.check_status(dev)
+    if args.with_push_copy:
+        cfgp = AgMatmulConfig(block_n=args.block_n, plain_a_out="push_copy")
+        us = benchmark_with_event(lambda: smr.all_gather_matmul(a_shard, b, a_out_plain, c, cfgp), **bench)
+        emit("smr_fused", us, gather="push_copy")
         symm_mem.check_status(dev)
 
 

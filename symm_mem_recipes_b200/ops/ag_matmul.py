@@ -48,6 +48,10 @@ class AgMatmulConfig:
     cta_pair: bool = bool(_env_int("SMR_AGMM_CTA_PAIR", 1))
     # cut the tiles of a thinly filled last wave along K (2-CTA kernel only)
     split_k_tail: bool = bool(_env_int("SMR_AGMM_SPLIT_K_TAIL", 1))
+    # a_out in ordinary memory (the upstream calling convention): "pull" = the 1-CTA kernel fetches the peers'
+    # shards with copier CTAs; "push_copy" = gather by push into the internal symmetric buffer on the CTA-pair
+    # kernel, then one device-to-device copy into a_out
+    plain_a_out: str = os.environ.get("SMR_AGMM_PLAIN_A_OUT", "pull")
     timeout_ms: int = _env_int("SMR_TIMEOUT_MS", 10000)
 
 
@@ -250,6 +254,13 @@ def all_gather_matmul(a_shard: torch.Tensor, b: torch.Tensor, a_out: Optional[to
         C.ag_matmul(a_shard, b, c_out, 2, None, 0, hdl.native, aout_offset, a_out, None,
                     bn, sms, n_copy, t_ns, config.cta_pair, _tail_buffer(a_shard.device, config), epi)
         return c_out
+    if config.plain_a_out == "push_copy":
+        staged = gather_buffer(M, K, a_shard.device, group, a_shard.dtype)
+        all_gather_matmul(a_shard, b, staged, c_out, config, group=group, epilogue=epilogue)
+        a_out.copy_(staged)
+        return c_out
+    if config.plain_a_out != "pull":
+        raise SymmMemError('AgMatmulConfig.plain_a_out must be "pull" or "push_copy"')
     if epi:
         raise SymmMemError('epilogue="swiglu" is not available in the pull mode; allocate a_out with symm_mem.empty')
     if a_shard.dtype != torch.bfloat16:

@@ -94,13 +94,15 @@ def _agmm_worker(rank, world_size, rows, N, K, n_copy, mode, cta_pair=False):
     M = rows * world_size
     if mode == "push":          # gathered A lands in symmetric memory: shards are broadcast
         a_out = symm_mem.empty(M, K, dtype=torch.bfloat16, device=dev)
-    elif mode == "pull":        # ordinary a_out, as in the upstream API: shards are fetched
+    elif mode in ("pull", "push_copy"):   # ordinary a_out, as in the upstream API
         a_out = torch.zeros(M, K, dtype=torch.bfloat16, device=dev)
     else:                       # internal symmetric buffer
         from symm_mem_recipes_b200.ops.ag_matmul import gather_buffer
         a_out = None
     c_out = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
     cfg = AgMatmulConfig(n_copy=n_copy, timeout_ms=5000, cta_pair=cta_pair)
+    if mode == "push_copy":     # ordinary a_out served by the push kernel plus one local copy
+        cfg = AgMatmulConfig(timeout_ms=5000, plain_a_out="push_copy")
     failures = []
     for it in range(3):
         smr.all_gather_matmul(a_shard, b, a_out, c_out, cfg)
@@ -156,3 +158,11 @@ def test_all_gather_matmul_push_without_multicast(monkeypatch):
 @pytest.mark.multigpu(8)
 def test_all_gather_matmul_8gpu():
     spawn_ranks(_agmm_worker, 8, "nccl", (2048, 3584, 8192, 4, "push"))
+
+
+@pytest.mark.gpu
+@pytest.mark.first_run
+@pytest.mark.multigpu(2)
+@pytest.mark.parametrize("rows,N,K", [(256, 512, 1024), (2048, 3584, 8192)])
+def test_all_gather_matmul_plain_a_out_by_push_and_copy_2gpu(rows, N, K):
+    spawn_ranks(_agmm_worker, 2, "nccl", (rows, N, K, 0, "push_copy"))
