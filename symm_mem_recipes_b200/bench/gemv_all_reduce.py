@@ -16,11 +16,9 @@ from __future__ import annotations
 
 import argparse
 import json
-import os
 import sys
 
 import torch
-import torch.distributed as dist
 
 
 def main(argv=None, standalone: bool = True) -> int:
