@@ -1,0 +1,114 @@
+"""The decoder layer's control flow on the CPU: every combination of its
+options runs end to end against the fp32 reference, with the GPU kernels
+replaced by host stand-ins that follow the kernels' contracts (the GEMM by a
+plain fp32 product, the glue ops by the C++ oracles, the SwiGLU epilogue by the
+tile layout it is defined on).  What this pins down is the plumbing between
+the ops: shapes, buffers, weight interleaving, in-place semantics, residuals.
+"""
+import pytest
+import torch
+
+from symm_mem_recipes_b200._ext import C as REAL_C
+
+
+class _FakeC:
+    """Host stand-ins with the signatures of the native entry points the layer reaches."""
+
+    def __getattr__(self, name):
+        return getattr(REAL_C, name)
+
+    @staticmethod
+    def ag_matmul(a, b, c, mode, shard_alloc, shard_offset, aout_alloc, aout_offset, a_out, flags, block_n,
+                  num_sms, n_copy, timeout_ns, cta_pair=False, tail_scratch=None, epilogue=0):
+        assert mode == 0, "world of one: no gather"
+        full = a.float() @ b.float().t()
+        if epilogue == 1:
+            assert block_n == 256 and full.shape[1] % 256 == 0
+            tiles = full.view(full.shape[0], -1, 2, 128)                 # [M, tile, gate|up, 128]
+            full = (torch.nn.functional.silu(tiles[:, :, 0]) * tiles[:, :, 1]).reshape(full.shape[0], -1)
+        assert tuple(c.shape) == tuple(full.shape)
+        c.copy_(full.to(c.dtype))
+
+    @staticmethod
+    def rms_norm(x, residual, w, sum_out, out, eps):
+        o, s = REAL_C.oracle_rms_norm_bf16(x, residual, w, eps)
+        out.copy_(o)
+        if sum_out is not None:
+            sum_out.copy_(s)
+
+    @staticmethod
+    def rope_inplace(qkv, n_heads, head_dim, seq, pos0, theta, num_sms):
+        qkv.copy_(REAL_C.oracle_rope_bf16(qkv, n_heads, head_dim, seq, pos0, theta))
+
+    @staticmethod
+    def silu_mul(gate_up, out, num_sms):
+        out.copy_(REAL_C.oracle_silu_mul_bf16(gate_up))
+
+
+@pytest.fixture
+def host_kernels(monkeypatch):
+    from symm_mem_recipes_b200.ops import ag_matmul, layer_glue
+
+    fake = _FakeC()
+    for mod in (ag_matmul, layer_glue):
+        monkeypatch.setattr(mod, "C", fake)
+    monkeypatch.setattr(ag_matmul, "_num_sms", lambda device: 148)
+    monkeypatch.setattr(layer_glue, "_num_sms", lambda device: 148)
+    monkeypatch.setattr(ag_matmul, "_tail_buffer", lambda device, config: None)
+
+    def relaxed_2d(name, t, dtype=None):
+        assert t.dim() == 2 and t.is_contiguous(), name
+        assert dtype is None or t.dtype == dtype, name
+
+    def relaxed(name, t, dim):
+        assert t.dim() == dim and t.is_contiguous() and t.dtype == torch.bfloat16, name
+
+    monkeypatch.setattr(ag_matmul, "_check_2d", relaxed_2d)
+    monkeypatch.setattr(layer_glue, "_check", relaxed)
+
+
+def _layer_and_reference(fused_glue, fused_swiglu):
+    from symm_mem_recipes_b200.models.llama_tp_layer import (LlamaTPConfig, LlamaTPDecoderLayer,
+                                                             full_precision_reference)
+
+    cfg = LlamaTPConfig.tiny(1)
+    layer = LlamaTPDecoderLayer(cfg, torch.device("cpu"), seed=1, fused_glue=fused_glue, fused_swiglu=fused_swiglu)
+    batch, seq = 2, 16
+    torch.manual_seed(3)
+    x = (torch.randn(batch * seq, cfg.hidden) * 0.5).to(torch.bfloat16)
+    weights = [(layer.w_qkv, layer.w_o, layer.w_gate_up, layer.w_down, layer.norm1, layer.norm2)]
+    ref = full_precision_reference(weights, cfg, x, batch, seq)
+    return cfg, layer, x, batch, seq, ref
+
+
+@pytest.mark.parametrize("fused_glue,fused_swiglu", [(False, False), (True, False), (True, True), (False, True)])
+def test_prefill_flow_matches_fp32(host_kernels, fused_glue, fused_swiglu):
+    cfg, layer, x, batch, seq, ref = _layer_and_reference(fused_glue, fused_swiglu)
+    x_before = x.clone()
+    y = layer.forward(x, batch, seq)
+    assert y.shape == x.shape and torch.equal(x, x_before)          # the input is not modified
+    assert (y.float() - ref).abs().max().item() < 0.1
+    y2 = layer.forward(x, batch, seq)                                # buffers are reused: same result again
+    assert torch.equal(y, y2)
+    y_lib = layer.forward_reference(x, batch, seq)
+    assert (y.float() - y_lib.float()).abs().max().item() < 0.1
+
+
+@pytest.mark.parametrize("fused_glue", [False, True])
+def test_decode_flow_matches_prefill(host_kernels, fused_glue):
+    """Decoding the tokens one by one through the KV cache gives what the
+    prefill of the same sequence gives at every position."""
+    cfg, layer, x, batch, seq, _ = _layer_and_reference(fused_glue, False)
+    want = layer.forward(x, batch, seq).view(batch, seq, cfg.hidden)
+    k_cache = torch.zeros(batch, seq, layer.hkv, cfg.head_dim, dtype=torch.bfloat16)
+    v_cache = torch.zeros_like(k_cache)
+    xs = x.view(batch, seq, cfg.hidden)
+    for pos in range(seq):
+        got = layer.decode(xs[:, pos].contiguous(), k_cache, v_cache, pos, fused=True)
+        assert (got.float() - want[:, pos].float()).abs().max().item() < 0.1, pos
+
+
+def test_phase_marks_are_off_by_default(host_kernels):
+    _, layer, x, batch, seq, _ = _layer_and_reference(False, False)
+    layer.forward(x, batch, seq)
+    assert layer.phase_marks is None
