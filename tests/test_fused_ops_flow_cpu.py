@@ -1,0 +1,209 @@
+"""Host-side plumbing of the fused multi-rank ops with gloo ranks: which
+branch a call takes, which allocation and offset it hands to the kernel, the
+geometry rule of the gather buffer, the ordinary-a_out path by push and copy,
+the weight interleaving of the SwiGLU epilogue.  The kernels are replaced by
+host stand-ins that move the same bytes through the POSIX-shm symmetric memory
+(each rank writes its shard into every rank's a_out, as the push gather does).
+"""
+import pytest
+import torch
+
+from symm_mem_recipes_b200.utils.testing import spawn_ranks
+
+
+def _install_host_kernels():
+    import torch.distributed as dist
+
+    from symm_mem_recipes_b200._ext import C as real
+    from symm_mem_recipes_b200.ops import ag_matmul
+
+    calls = []
+
+    class Fake:
+        def __getattr__(self, name):
+            return getattr(real, name)
+
+        @staticmethod
+        def ag_matmul(a, b, c, mode, shard_alloc, shard_offset, aout_alloc, aout_offset, a_out, flags, block_n,
+                      num_sms, n_copy, timeout_ns, cta_pair=False, tail_scratch=None, epilogue=0):
+            calls.append(mode)
+            if mode == 2:
+                ws, rank = dist.get_world_size(), dist.get_rank()
+                rows, K = a.shape
+                assert a_out.data_ptr() == real.host_view(aout_alloc, -1, [1], torch.uint8, aout_offset).data_ptr()
+                dist.barrier()                                   # the kernel's entry barrier
+                for r in range(ws):                              # push: own shard into every rank's a_out
+                    peer = real.host_view(aout_alloc, r, [rows * ws, K], a.dtype, aout_offset)
+                    peer[rank * rows:(rank + 1) * rows].copy_(a)
+                dist.barrier()                                   # arrival of every shard
+                full_a = a_out
+            else:
+                assert mode == 0
+                full_a = a
+            full = full_a.float() @ b.float().t()
+            if epilogue == 1:
+                tiles = full.view(full.shape[0], -1, 2, 128)
+                full = (torch.nn.functional.silu(tiles[:, :, 0]) * tiles[:, :, 1]).reshape(full.shape[0], -1)
+            c.copy_(full.to(c.dtype))
+
+    ag_matmul.C = Fake()
+    ag_matmul._num_sms = lambda device: 148
+    ag_matmul._tail_buffer = lambda device, config: None
+
+    def relaxed_2d(name, t, dtype=None):
+        assert t.dim() == 2 and t.is_contiguous(), name
+        assert dtype is None or t.dtype == dtype, name
+
+    ag_matmul._check_2d = relaxed_2d
+    return calls
+
+
+def _agmm_flow_worker(rank, world_size):
+    import torch.distributed as dist
+
+    import symm_mem_recipes_b200 as smr
+    from symm_mem_recipes_b200.errors import SymmMemError
+    from symm_mem_recipes_b200.ops.ag_matmul import AgMatmulConfig, interleave_gate_up
+    from symm_mem_recipes_b200.parallel import symm_mem
+
+    calls = _install_host_kernels()
+    rows, K, F = 128, 64, 256
+    M = rows * world_size
+    g = torch.Generator().manual_seed(5)
+    wg = (torch.randn(F, K, generator=g) * 0.3).to(torch.bfloat16)
+    wu = (torch.randn(F, K, generator=g) * 0.3).to(torch.bfloat16)
+    shards = [(torch.randn(rows, K, generator=torch.Generator().manual_seed(10 + r)) * 0.5).to(torch.bfloat16)
+              for r in range(world_size)]
+    full_a = torch.cat(shards)
+    a_shard = symm_mem.empty(rows, K, dtype=torch.bfloat16, device="cpu")
+    a_shard.copy_(shards[rank])
+
+    # 1. a_out = None: the internal symmetric buffer, gathered by push
+    c = smr.all_gather_matmul(a_shard, wg)
+    assert calls[-1] == 2 and c.shape == (M, F)
+    assert torch.allclose(c.float(), full_a.float() @ wg.float().t(), atol=0.05)
+
+    # 2. a symmetric a_out placed at an offset inside a larger allocation
+    big = symm_mem.empty(2 * M * K, dtype=torch.bfloat16, device="cpu")
+    a_out = big[M * K:].view(M, K)
+    c2 = smr.all_gather_matmul(a_shard, wg, a_out)
+    assert torch.equal(a_out, full_a) and torch.equal(c2, c)
+    # the same allocation may not serve a gather of another geometry
+    with pytest.raises(SymmMemError, match="already serves"):
+        smr.all_gather_matmul(a_shard, wg, big[: M * K].view(M, K))
+    dist.barrier()
+
+    # 3. an ordinary a_out served by push into the internal buffer plus one copy
+    plain = torch.zeros(M, K, dtype=torch.bfloat16)
+    c3 = smr.all_gather_matmul(a_shard, wg, plain, config=AgMatmulConfig(plain_a_out="push_copy"))
+    assert calls[-1] == 2 and torch.equal(plain, full_a) and torch.equal(c3, c)
+
+    # 4. SwiGLU epilogue over the gather
+    act = smr.all_gather_matmul(a_shard, interleave_gate_up(wg, wu), epilogue="swiglu")
+    want = torch.nn.functional.silu(full_a.float() @ wg.float().t()) * (full_a.float() @ wu.float().t())
+    assert act.shape == (M, F) and torch.allclose(act.float(), want, atol=0.05)
+
+    # 5. mm_only: no communication, multiplies what it is given
+    c5 = smr.all_gather_matmul(a_shard, wg, a_out=a_out, mm_only=True)
+    assert calls[-1] == 0 and torch.equal(c5, c)
+
+    # 6. shape errors are raised on the host
+    with pytest.raises(SymmMemError, match="rows per rank"):
+        smr.all_gather_matmul(a_shard[:100].contiguous(), wg)
+    with pytest.raises(SymmMemError, match="a_out must be"):
+        smr.all_gather_matmul(a_shard, wg, symm_mem.empty(M + 128, K, dtype=torch.bfloat16, device="cpu"))
+    dist.barrier()
+
+
+@pytest.mark.parametrize("world_size", [2, 4])
+def test_all_gather_matmul_host_flow(world_size):
+    spawn_ranks(_agmm_flow_worker, world_size, "gloo")
+
+
+def _row_parallel_flow_worker(rank, world_size):
+    import torch.distributed as dist
+
+    import symm_mem_recipes_b200 as smr
+    from symm_mem_recipes_b200._ext import C as real
+    from symm_mem_recipes_b200.errors import SymmMemError
+    from symm_mem_recipes_b200.parallel import symm_mem
+
+    # the package re-exports functions under the names of these modules: import the modules themselves
+    import importlib
+    gemv_mod = importlib.import_module("symm_mem_recipes_b200.ops.gemv_all_reduce")
+    rs_mod = importlib.import_module("symm_mem_recipes_b200.ops.matmul_reduce_scatter")
+    seen = {}
+
+    def summed(a, b):
+        part = (a.float() @ b.float().t()).to(torch.bfloat16).float()     # bf16 partials, fp32 sum
+        dist.all_reduce(part)
+        return part
+
+    class Fake:
+        def __getattr__(self, name):
+            return getattr(real, name)
+
+        @staticmethod
+        def matmul_reduce_scatter(a, b, out, workspace, num_sms, timeout_ns, trace=None, deep_strips=False,
+                                  cta_pair=False):
+            seen["rs"] = (deep_strips, cta_pair, workspace.payload_bytes)
+            rows = out.shape[0]
+            out.copy_(summed(a, b)[rank * rows:(rank + 1) * rows].to(out.dtype))
+
+        @staticmethod
+        def matmul_all_reduce(a, b, out, out_alloc, out_offset, workspace, num_sms, timeout_ns, cta_pair=False):
+            assert out.data_ptr() == real.host_view(out_alloc, -1, [1], torch.uint8, out_offset).data_ptr()
+            seen["ar"] = cta_pair
+            out.copy_(summed(a, b).to(out.dtype))
+
+        @staticmethod
+        def gemv_all_reduce(x, w, out, workspace, ws_offset, timeout_ns, tensor_core=False, num_sms=148,
+                            tagged=False):
+            seen["gemv"] = (tensor_core, tagged)
+            part = x.float() @ w.float()
+            dist.all_reduce(part)
+            out.copy_(part.to(out.dtype))
+
+    rs_mod.C = Fake()
+    gemv_mod.C = Fake()
+    rs_mod._num_sms = gemv_mod._num_sms = lambda device: 148
+
+    M, N, K = 128 * world_size, 64, 32
+    g = torch.Generator().manual_seed(100 + rank)
+    a = (torch.randn(M, K, generator=g) * 0.3).to(torch.bfloat16)
+    b = (torch.randn(N, K, generator=g) * 0.3).to(torch.bfloat16)
+    want = summed(a, b)
+    rows = M // world_size
+
+    out = smr.matmul_reduce_scatter(a, b)
+    assert out.shape == (rows, N) and torch.allclose(out.float(), want[rank * rows:(rank + 1) * rows], atol=0.02)
+    assert seen["rs"][:2] == (False, False) and seen["rs"][2] >= real.matmul_rs_workspace_bytes(M, N)
+    smr.matmul_reduce_scatter(a, b, cta_pair=True)
+    assert seen["rs"][:2] == (False, True)
+    smr.matmul_reduce_scatter(a, b, deep_strips=True)
+    assert seen["rs"][:2] == (True, False)
+
+    full = smr.matmul_all_reduce(a, b)                       # internal symmetric output, cached per shape
+    assert symm_mem.is_symm_mem_tensor(full) and torch.allclose(full.float(), want, atol=0.02)
+    assert smr.matmul_all_reduce(a, b, cta_pair=True).data_ptr() == full.data_ptr() and seen["ar"] is True
+    with pytest.raises(SymmMemError, match="symmetric"):
+        smr.matmul_all_reduce(a, b, out=torch.empty(M, N, dtype=torch.bfloat16))
+    with pytest.raises(SymmMemError, match="multiple of 128"):
+        smr.matmul_reduce_scatter(a[:100].contiguous(), b)
+
+    x = (torch.randn(4, K, generator=g) * 0.3).to(torch.bfloat16)
+    w = (torch.randn(K, N, generator=g) * 0.3).to(torch.bfloat16)
+    y = smr.gemv_all_reduce(x, w)
+    assert seen["gemv"] == (True, False) and y.shape == (4, N)
+    smr.gemv_all_reduce(x, w, algo="tc_tagged")
+    assert seen["gemv"] == (True, True)
+    smr.gemv_all_reduce(x, w, algo="simt")
+    assert seen["gemv"] == (False, False)
+    ref = x.float() @ w.float()
+    dist.all_reduce(ref)
+    assert torch.allclose(y.float(), ref, atol=0.02)
+    dist.barrier()
+
+
+def test_row_parallel_ops_host_flow():
+    spawn_ranks(_row_parallel_flow_worker, 2, "gloo")
