@@ -4,6 +4,7 @@ dict of tile sizes: symm_mem_recipes/triton_one_shot_all_reduce.py:97-100,
 symm_mem_recipes/triton_all_gather_matmul.py:380-388)."""
 from __future__ import annotations
 
+import json
 import os
 from dataclasses import dataclass
 
@@ -34,4 +35,27 @@ class AllReduceConfig:
     timeout_ms: int = _env_int("SMR_TIMEOUT_MS", 10000)
 
 
-DEFAULT_ALL_REDUCE = AllReduceConfig()
+    @staticmethod
+    def from_tuning(path: str, world_size: int = 0) -> "AllReduceConfig":
+        """Thresholds measured on the machine at hand: `path` is the JSON written by
+        `python -m symm_mem_recipes_b200.bench.tune_all_reduce` ({"by_world_size": {"8": {...}}}).
+        Fields the file does not name keep their defaults; `world_size` 0 takes the
+        largest world size in the file."""
+        with open(path) as f:
+            table = json.load(f)["by_world_size"]
+        key = str(world_size) if world_size else max(table, key=int)
+        if key not in table:
+            raise KeyError(f"{path} has no entry for world size {key}; it has {sorted(table, key=int)}")
+        cfg = AllReduceConfig()
+        for name, value in table[key].items():
+            if name in cfg.__dataclass_fields__:
+                setattr(cfg, name, int(value))
+        return cfg
+
+
+def _default_all_reduce() -> AllReduceConfig:
+    path = os.environ.get("SMR_AR_TUNING_FILE")
+    return AllReduceConfig.from_tuning(path) if path else AllReduceConfig()
+
+
+DEFAULT_ALL_REDUCE = _default_all_reduce()

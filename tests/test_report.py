@@ -53,3 +53,34 @@ def test_report_cli_without_peaks(tmp_path, capsys):
     empty.write_text(json.dumps({"no": "op"}) + "\n")
     assert report.main([str(empty)]) == 0
     assert "no benchmark records" in capsys.readouterr().out
+
+
+def test_all_reduce_thresholds_from_a_sweep(tmp_path, monkeypatch):
+    from symm_mem_recipes_b200.bench import tune_all_reduce
+    from symm_mem_recipes_b200.ops.config import AllReduceConfig
+
+    def rec(impl, nbytes, us, ws=8):
+        return json.dumps({"op": "all_reduce", "impl": impl, "world_size": ws, "bytes": nbytes, "us": us})
+
+    lines = [
+        # 4 KiB, 8 KiB: low_latency wins; 16 KiB: one_shot wins; 32 KiB on: multimem wins
+        rec("nccl", 4096, 1.0), rec("low_latency", 4096, 5), rec("one_shot", 4096, 12), rec("multimem", 4096, 10),
+        rec("low_latency", 8192, 6), rec("one_shot", 8192, 12), rec("multimem", 8192, 10),
+        rec("low_latency", 16384, 14), rec("one_shot", 16384, 9), rec("two_shot", 16384, 13), rec("multimem", 16384, 10),
+        rec("one_shot", 32768, 20), rec("multimem", 32768, 11),
+        rec("low_latency", 65536, 1), rec("multimem", 65536, 12),     # past the break: must not reopen the range
+        rec("low_latency", 4096, 5, ws=2), rec("two_shot", 4096, 9, ws=2),
+    ]
+    f = tmp_path / "sweep.jsonl"
+    f.write_text("\n".join(lines) + "\n")
+    out = tmp_path / "tuning.json"
+    assert tune_all_reduce.main([str(f), "--out", str(out)]) == 0
+    table = json.loads(out.read_text())["by_world_size"]
+    assert table["8"] == {"ll_max_bytes": 8192, "one_shot_max_bytes": 16384}
+    assert table["2"] == {"ll_max_bytes": 4096, "one_shot_max_bytes": 0}
+    cfg = AllReduceConfig.from_tuning(str(out), world_size=8)
+    assert (cfg.ll_max_bytes, cfg.one_shot_max_bytes) == (8192, 16384)
+    assert AllReduceConfig.from_tuning(str(out)).ll_max_bytes == 8192           # largest world size in the file
+    from symm_mem_recipes_b200.ops.all_reduce import choose_algo
+    assert [choose_algo(n, 8, True, cfg) for n in (4096, 16384, 32768)] == ["low_latency", "one_shot", "multimem"]
+    assert choose_algo(32768, 8, False, cfg) == "two_shot"
