@@ -186,3 +186,33 @@ def test_heartbeat_goes_stale_without_a_goodbye():
     with pytest.raises(PeerLost):
         c.wait_for_all(timeout_s=0.2)
     c.stop()
+
+
+# ---- upstream entry points under their own names ----
+def _compat_worker(rank, world_size):
+    from symm_mem_recipes_b200 import compat
+    from symm_mem_recipes_b200.parallel import symm_mem
+
+    rows, cols, splits = 8, 16, 2
+    big = symm_mem.empty(2, rows, cols, dtype=torch.bfloat16, device="cpu")
+    inp = big[1]                                                   # a view at an offset inside the allocation
+    inp.copy_(torch.full((rows, cols), float(rank + 1)).to(torch.bfloat16))
+    symm_mem.rendezvous(big).barrier()
+    out = torch.zeros(rows * world_size, cols, dtype=torch.bfloat16)
+    progress = torch.zeros(world_size * splits, dtype=torch.int32)
+    compat.all_gather_with_progress(out, inp, progress, splits)
+    assert bool((progress == 1).all())
+    for r in range(world_size):
+        assert bool((out[r * rows:(r + 1) * rows] == r + 1).all())
+    ones = symm_mem.empty(64, dtype=torch.bfloat16, device="cpu")
+    ones.fill_(1)
+    symm_mem.rendezvous(ones).barrier()
+    assert bool(compat.one_shot_all_reduce(ones).eq(world_size).all())   # upstream's own check
+    cfg = compat._config_from_dict({"BLOCK_SIZE_M": 128, "BLOCK_SIZE_N": 256, "BLOCK_SIZE_K": 64, "num_stages": 3})
+    assert cfg.block_n == 256 and compat._config_from_dict({"BLOCK_SIZE_N": 64}).block_n == 0
+    assert compat.all_gather_matmul_baseline is not None and compat.benchmark_with_event is not None
+
+
+@pytest.mark.parametrize("world_size", [2, 3])
+def test_upstream_names(world_size):
+    spawn_ranks(_compat_worker, world_size, "gloo")
