@@ -263,3 +263,30 @@ def test_rank_leaving_between_steps_is_noticed_before_the_next_launch(monkeypatc
     monkeypatch.setenv("NCCL_NVLS_ENABLE", "0")
     monkeypatch.setenv("SMR_DISABLE_MULTICAST", "1")
     spawn_ranks(_leaving_rank_worker, 2, "nccl", ())
+
+
+def _compat_gpu_worker(rank, world_size):
+    from symm_mem_recipes_b200 import compat
+    from symm_mem_recipes_b200.parallel import symm_mem
+
+    dev = torch.device("cuda", rank)
+    rows, cols, splits = 256, 1024, 2
+    inp = symm_mem.empty(rows, cols, dtype=torch.bfloat16, device=dev)
+    inp.copy_(seeded_normal_bf16(rows * cols, rank).view(rows, cols).to(dev))
+    symm_mem.rendezvous(inp).barrier()
+    out = torch.zeros(rows * world_size, cols, dtype=torch.bfloat16, device=dev)
+    progress = torch.zeros(world_size * splits, dtype=torch.int32, device=dev)
+    compat.all_gather_with_progress(out, inp, progress, splits)    # contiguous peer copies: copy engine
+    torch.cuda.synchronize()
+    assert bool((progress == 1).all())
+    for r in range(world_size):
+        want = seeded_normal_bf16(rows * cols, r).view(rows, cols)
+        assert torch.equal(out[r * rows:(r + 1) * rows].cpu(), want)
+    symm_mem.check_status(dev)
+
+
+@pytest.mark.gpu
+@pytest.mark.first_run
+@pytest.mark.multigpu(2)
+def test_upstream_all_gather_with_progress_2gpu():
+    spawn_ranks(_compat_gpu_worker, 2, "nccl", ())
