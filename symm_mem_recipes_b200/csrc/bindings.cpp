@@ -225,8 +225,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("offset_bytes"), py::arg("multicast") = false);
   m.def("cuda_pad_view", &cuda_pad_view);
 
-  py::class_<HostSymmAllocation, std::shared_ptr<HostSymmAllocation>>(m, "HostSymmAllocation")
-      .def(py::init<const std::string&, size_t>())
+  py::class_<HostSymmAllocation, std::shared_ptr<HostSymmAllocation>> host_cls(m, "HostSymmAllocation");
+  host_cls.def(py::init<const std::string&, size_t>())
       .def_property_readonly("shm_name", &HostSymmAllocation::shm_name)
       .def_property_readonly("payload_bytes", &HostSymmAllocation::payload_bytes)
       .def_property_readonly("block_bytes", &HostSymmAllocation::block_bytes)
@@ -247,6 +247,16 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
              }
              return py::make_tuple(code, peer);
            });
+  host_cls
+      .def("put_signal",
+           [](HostSymmAllocation& a, int dst, uint32_t slot_base, uint64_t timeout_ns) {
+             py::gil_scoped_release nogil;
+             return a.put_signal(dst, slot_base, timeout_ns);
+           })
+      .def("wait_signal", [](HostSymmAllocation& a, int src, uint32_t slot_base, uint64_t timeout_ns) {
+        py::gil_scoped_release nogil;
+        return a.wait_signal(src, slot_base, timeout_ns);
+      });
   m.def("host_view", &host_view);
   m.def("host_pad_view", &host_pad_view);
   m.def("host_all_reduce", &host_all_reduce);
@@ -380,6 +390,16 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     c10::cuda::CUDAGuard guard(a->device());
     rt_check(launch_channel_barrier(view_of(*a), channel, timeout_ns, status_for(a->device()),
                                     current_stream(a->device())), "channel_barrier");
+  });
+  m.def("put_signal", [](const std::shared_ptr<CudaSymmAllocation>& a, int dst, int channel, uint64_t timeout_ns) {
+    c10::cuda::CUDAGuard guard(a->device());
+    rt_check(launch_put_signal(view_of(*a), dst, channel, timeout_ns, status_for(a->device()),
+                               current_stream(a->device())), "put_signal");
+  });
+  m.def("wait_signal", [](const std::shared_ptr<CudaSymmAllocation>& a, int src, int channel, uint64_t timeout_ns) {
+    c10::cuda::CUDAGuard guard(a->device());
+    rt_check(launch_wait_signal(view_of(*a), src, channel, timeout_ns, status_for(a->device()),
+                                current_stream(a->device())), "wait_signal");
   });
   m.def("wait_flag", [](torch::Tensor flag, uint32_t target, uint64_t timeout_ns) {
     TORCH_CHECK(flag.is_cuda() && flag.element_size() == 4, "flag must be a 32-bit CUDA tensor");

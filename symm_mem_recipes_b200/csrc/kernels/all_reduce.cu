@@ -60,6 +60,30 @@ __global__ void channel_barrier_kernel(PeerView pv, int channel, uint64_t timeou
   }
 }
 
+// One thread, one peer: the two halves of the channel barrier on their own.
+__global__ void put_signal_kernel(PeerView pv, int dst, int channel, uint64_t timeout_ns, Status* st) {
+  if (threadIdx.x != 0) return;
+  uint32_t* slot = pv.pads[dst] + kBlockSlots + (uint32_t)channel * (uint32_t)pv.world_size + pv.rank;
+  Deadline d(timeout_ns);
+  while (cas_release_sys(slot, 0u, 1u) != 0u) {
+    if (!d.alive()) {
+      report_status(st, kTimeoutBarrierSend, pv.rank, (uint32_t)channel, dst, kWhereBarrierKernel);
+      return;
+    }
+  }
+}
+__global__ void wait_signal_kernel(PeerView pv, int src, int channel, uint64_t timeout_ns, Status* st) {
+  if (threadIdx.x != 0) return;
+  uint32_t* slot = pv.pads[pv.rank] + kBlockSlots + (uint32_t)channel * (uint32_t)pv.world_size + src;
+  Deadline d(timeout_ns);
+  while (cas_acquire_sys(slot, 1u, 0u) != 1u) {
+    if (!d.alive()) {
+      report_status(st, kTimeoutBarrierWait, pv.rank, (uint32_t)channel, src, kWhereBarrierKernel);
+      return;
+    }
+  }
+}
+
 __global__ void wait_flag_kernel(const uint32_t* flag, uint32_t target, uint64_t timeout_ns,
                                  int rank, Status* st) {
   if (threadIdx.x == 0) {
@@ -300,6 +324,22 @@ int launch_channel_barrier(const PeerView& pv, int channel, uint64_t timeout_ns,
                            cudaStream_t stream) {
   if (channel < 0 || (uint32_t)(channel + 1) * pv.world_size > kChannelSlots) return cudaErrorInvalidValue;
   channel_barrier_kernel<<<1, 32, 0, stream>>>(pv, channel, timeout_ns, status);
+  return last_error();
+}
+
+int launch_put_signal(const PeerView& pv, int dst, int channel, uint64_t timeout_ns, Status* status,
+                      cudaStream_t stream) {
+  if (dst < 0 || dst >= pv.world_size || channel < 0 || (uint32_t)(channel + 1) * pv.world_size > kChannelSlots)
+    return cudaErrorInvalidValue;
+  put_signal_kernel<<<1, 32, 0, stream>>>(pv, dst, channel, timeout_ns, status);
+  return last_error();
+}
+
+int launch_wait_signal(const PeerView& pv, int src, int channel, uint64_t timeout_ns, Status* status,
+                       cudaStream_t stream) {
+  if (src < 0 || src >= pv.world_size || channel < 0 || (uint32_t)(channel + 1) * pv.world_size > kChannelSlots)
+    return cudaErrorInvalidValue;
+  wait_signal_kernel<<<1, 32, 0, stream>>>(pv, src, channel, timeout_ns, status);
   return last_error();
 }
 

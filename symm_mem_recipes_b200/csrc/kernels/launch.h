@@ -25,6 +25,13 @@ int launch_barrier_test(const PeerView& pv, int num_blocks, int threads, uint64_
                         Status* status, cudaStream_t stream, int kind = 0);
 int launch_channel_barrier(const PeerView& pv, int channel, uint64_t timeout_ns, Status* status,
                            cudaStream_t stream);
+// One-to-one signalling on a channel (the two halves of the channel barrier): `put_signal` raises
+// this rank's slot on `dst` (release; waits while an earlier signal is unconsumed), `wait_signal`
+// consumes `src`'s signal on this rank (acquire).  Stream-ordered, bounded, status on expiry.
+int launch_put_signal(const PeerView& pv, int dst, int channel, uint64_t timeout_ns, Status* status,
+                      cudaStream_t stream);
+int launch_wait_signal(const PeerView& pv, int src, int channel, uint64_t timeout_ns, Status* status,
+                       cudaStream_t stream);
 // Waits on a flag nothing sets unless `*flag >= target`; used to prove that a
 // timed-out wait returns an error status and leaves the device usable.
 int launch_wait_flag(const uint32_t* flag, uint32_t target, uint64_t timeout_ns, int rank,

@@ -200,6 +200,31 @@ uint32_t host_ll_all_reduce(void* const* workspaces, int rank, int world_size, c
   return kOk;
 }
 
+namespace {
+// 0 -> 1 (release) or 1 -> 0 (acquire) on one slot, bounded
+uint32_t flip_slot(uint32_t* slot, uint32_t from, uint32_t to, int order, uint64_t timeout_ns, uint32_t on_timeout) {
+  const uint64_t deadline = now_ns() + timeout_ns;
+  for (uint32_t spins = 0;; ++spins) {
+    uint32_t expected = from;
+    if (__atomic_compare_exchange_n(slot, &expected, to, false, order, __ATOMIC_RELAXED)) return kOk;
+    if ((spins & 255u) == 255u) {
+      if (now_ns() > deadline) return on_timeout;
+      sched_yield();
+    }
+  }
+}
+}  // namespace
+
+uint32_t HostSymmAllocation::put_signal(int dst, uint32_t slot_base, uint64_t timeout_ns) {
+  if (!rendezvoused_) throw std::runtime_error("put_signal on an allocation that is not rendezvoused");
+  return flip_slot(peer_pad(dst) + slot_base + rank_, 0u, 1u, __ATOMIC_RELEASE, timeout_ns, kTimeoutBarrierSend);
+}
+
+uint32_t HostSymmAllocation::wait_signal(int src, uint32_t slot_base, uint64_t timeout_ns) {
+  if (!rendezvoused_) throw std::runtime_error("wait_signal on an allocation that is not rendezvoused");
+  return flip_slot(peer_pad(rank_) + slot_base + src, 1u, 0u, __ATOMIC_ACQUIRE, timeout_ns, kTimeoutBarrierWait);
+}
+
 uint32_t HostSymmAllocation::barrier(uint32_t slot_base, uint64_t timeout_ns, int* failed_peer) {
   if (!rendezvoused_) throw std::runtime_error("barrier on an allocation that is not rendezvoused");
   std::vector<uint32_t*> pads(world_size_);

@@ -44,6 +44,11 @@ class HostSymmAllocation {
   // Same slot protocol as the device barrier; `slot_base` selects block or
   // channel slots.  Returns a StatusCode (kOk on success) and fills `peer`.
   uint32_t barrier(uint32_t slot_base, uint64_t timeout_ns, int* failed_peer);
+  // The two halves of that protocol on their own, towards ONE peer: `put_signal` flips slot
+  // [slot_base + this rank] of `dst`'s pad from 0 to 1 (release; waits while an earlier signal is
+  // unconsumed), `wait_signal` flips slot [slot_base + src] of the own pad from 1 to 0 (acquire).
+  uint32_t put_signal(int dst, uint32_t slot_base, uint64_t timeout_ns);
+  uint32_t wait_signal(int src, uint32_t slot_base, uint64_t timeout_ns);
 
  private:
   std::string name_;

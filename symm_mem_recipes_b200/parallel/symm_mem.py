@@ -247,6 +247,47 @@ class SymmetricMemory:
             code, peer = self._alloc.barrier(C.BLOCK_SLOTS + int(channel) * self.world_size, t_ns)
             raise_for_status((code, self.rank, channel, peer, 1, 0))
 
+    def put_signal(self, dst_rank: int, channel: int = 0, timeout_ms: int = DEFAULT_TIMEOUT_MS) -> None:
+        """One-to-one signal on a channel: everything this rank wrote before (in
+        stream order on CUDA) is visible to `dst_rank` once its `wait_signal`
+        returns.  Waits, bounded, while an earlier signal to that rank on that
+        channel is still unconsumed.  Signals and `barrier()` share the
+        channels: give them different ones."""
+        t_ns = int(timeout_ms) * 1_000_000
+        if self.kind == "cuda":
+            C.put_signal(self._alloc, int(dst_rank), int(channel), t_ns)
+        else:
+            code = self._alloc.put_signal(int(dst_rank), C.BLOCK_SLOTS + int(channel) * self.world_size, t_ns)
+            raise_for_status((code, self.rank, channel, dst_rank, 1, 0))
+
+    def wait_signal(self, src_rank: int, channel: int = 0, timeout_ms: int = DEFAULT_TIMEOUT_MS) -> None:
+        """Consumes `src_rank`'s signal on `channel` (see `put_signal`).  On
+        CUDA the wait runs on the current stream and a timeout is reported by
+        the next `check()`; on CPU it raises SymmMemTimeout itself."""
+        t_ns = int(timeout_ms) * 1_000_000
+        if self.kind == "cuda":
+            C.wait_signal(self._alloc, int(src_rank), int(channel), t_ns)
+        else:
+            code = self._alloc.wait_signal(int(src_rank), C.BLOCK_SLOTS + int(channel) * self.world_size, t_ns)
+            raise_for_status((code, self.rank, channel, src_rank, 1, 0))
+
+    @staticmethod
+    def stream_write_value32(flags: torch.Tensor, offset: int, value: int) -> None:
+        """`flags[offset] = value`, ordered after everything already queued on
+        the current stream (the role cuStreamWriteValue32 plays upstream,
+        symm_mem_recipes/triton_all_gather_matmul.py:51-55)."""
+        flags.view(-1)[int(offset):int(offset) + 1].fill_(int(value))
+
+    @property
+    def buffer_ptrs(self) -> list:
+        """Address of every rank's payload as mapped in this process."""
+        return [self.get_buffer(r, (1,), torch.uint8).data_ptr() for r in range(self.world_size)]
+
+    @property
+    def signal_pad_ptrs(self) -> list:
+        """Address of every rank's signal pad as mapped in this process."""
+        return [self.get_signal_pad(r).data_ptr() for r in range(self.world_size)]
+
     def check(self) -> None:
         """Synchronise the device and raise if any kernel reported a failure."""
         if self.kind == "cuda":

@@ -290,3 +290,29 @@ def _compat_gpu_worker(rank, world_size):
 @pytest.mark.multigpu(2)
 def test_upstream_all_gather_with_progress_2gpu():
     spawn_ranks(_compat_gpu_worker, 2, "nccl", ())
+
+
+def _signals_gpu_worker(rank, world_size):
+    from symm_mem_recipes_b200.parallel import symm_mem
+
+    dev = torch.device("cuda", rank)
+    t = symm_mem.empty(1 << 16, dtype=torch.float32, device=dev)
+    hdl = symm_mem.rendezvous(t)
+    nxt, prv = (rank + 1) % world_size, (rank - 1) % world_size
+    for it in range(20):                       # ring: write, signal the next rank, wait for the previous, read it
+        t.fill_(float(100 * it + rank))
+        hdl.put_signal(nxt, channel=3, timeout_ms=2000)
+        hdl.wait_signal(prv, channel=3, timeout_ms=2000)
+        got = hdl.get_buffer(prv, (1 << 16,), torch.float32).clone()
+        hdl.barrier(channel=1)
+        assert float(got[0]) == float(100 * it + prv) and float(got[-1]) == float(100 * it + prv)
+    hdl.check()
+    assert int(hdl.get_signal_pad().abs().sum()) == 0
+    assert len(hdl.buffer_ptrs) == world_size and hdl.buffer_ptrs[rank] == t.data_ptr()
+
+
+@pytest.mark.gpu
+@pytest.mark.first_run
+@pytest.mark.multigpu(2)
+def test_one_to_one_signals_2gpu():
+    spawn_ranks(_signals_gpu_worker, 2, "nccl", ())

@@ -216,3 +216,35 @@ def _compat_worker(rank, world_size):
 @pytest.mark.parametrize("world_size", [2, 3])
 def test_upstream_names(world_size):
     spawn_ranks(_compat_worker, world_size, "gloo")
+
+
+def _signal_worker(rank, world_size):
+    from symm_mem_recipes_b200.errors import SymmMemTimeout
+    from symm_mem_recipes_b200.parallel import symm_mem
+
+    t = symm_mem.empty(1024, dtype=torch.float32, device="cpu")
+    hdl = symm_mem.rendezvous(t)
+    assert len(hdl.buffer_ptrs) == world_size and hdl.buffer_ptrs[rank] == t.data_ptr()
+    assert len(set(hdl.signal_pad_ptrs)) == world_size
+    nxt, prv = (rank + 1) % world_size, (rank - 1) % world_size
+    for it in range(50):                       # a ring of one-to-one signals: write, signal, wait, read
+        t.fill_(float(100 * it + rank))
+        hdl.put_signal(nxt, channel=3)
+        hdl.wait_signal(prv, channel=3)
+        got = hdl.get_buffer(prv, (1024,), torch.float32)
+        assert float(got[0]) == float(100 * it + prv) and float(got[-1]) == float(100 * it + prv)
+        hdl.barrier(channel=1)                 # nobody overwrites before everybody has read
+    assert int(hdl.get_signal_pad().abs().sum()) == 0          # every signal was consumed
+    flags = torch.zeros(4, dtype=torch.int32)
+    hdl.stream_write_value32(flags, 2, 7)
+    assert flags.tolist() == [0, 0, 7, 0]
+    if rank == 0:
+        with pytest.raises(SymmMemTimeout) as e:              # nobody signals on channel 9
+            hdl.wait_signal(nxt, channel=9, timeout_ms=50)
+        assert e.value.peer == nxt
+    hdl.barrier(channel=1)
+
+
+@pytest.mark.parametrize("world_size", [2, 4])
+def test_one_to_one_signals(world_size):
+    spawn_ranks(_signal_worker, world_size, "gloo")
