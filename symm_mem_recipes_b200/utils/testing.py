@@ -6,6 +6,7 @@ rendezvous address is always 127.0.0.1.
 from __future__ import annotations
 
 import os
+import signal
 import socket
 import traceback
 
@@ -36,6 +37,16 @@ def _entry(rank: int, world_size: int, backend: str, port: int, fn, args, errq):
     os.environ["RANK"] = str(rank)
     os.environ["LOCAL_RANK"] = str(rank)
     os.environ["WORLD_SIZE"] = str(world_size)
+
+    # A rank that the parent gives up on is asked to stop with SIGTERM: leave through the `finally`
+    # below (orderly unbinding of multicast memory) instead of dying with its mappings in place.
+    # The teardown itself may wait for peers that are gone (a process-group shutdown can retry for
+    # minutes), so an alarm ends the process if it has not left within 20 s.
+    def _on_sigterm(signum, frame):
+        signal.alarm(20)
+        raise SystemExit(143)
+
+    signal.signal(signal.SIGTERM, _on_sigterm)
     ok = False
     try:
         if backend == "nccl":
@@ -84,7 +95,11 @@ def spawn_ranks(fn, world_size: int, backend: str = "gloo", args=(), timeout_s: 
     hung = [p for p in procs if p.is_alive()]
     for p in hung:
         p.terminate()
-        p.join(10)
+    for p in hung:
+        p.join(30)        # bounded device waits end within their timeout, then the rank tears down in order
+        if p.is_alive():
+            p.kill()
+            p.join(10)
     errors = []
     while not errq.empty():
         errors.append(errq.get())

@@ -110,3 +110,26 @@ def test_guarded_empty_detects_stores_outside():
     before = torch.as_strided(t2, (1,), (1,), storage_offset=t2.storage_offset() - 1)
     before.fill_(3.0)
     assert not intact2()
+
+
+def _one_rank_hangs(rank, world_size):
+    import time
+
+    if rank == 1:
+        time.sleep(1000)
+
+
+def test_spawn_ranks_gives_up_on_a_hung_rank_and_lets_it_tear_down():
+    import time
+
+    import pytest
+
+    from symm_mem_recipes_b200.utils.testing import spawn_ranks
+
+    t0 = time.monotonic()
+    with pytest.raises(RuntimeError, match="did not finish") as e:
+        spawn_ranks(_one_rank_hangs, 2, "gloo", timeout_s=25.0)     # long enough for the ranks to come up
+    # the hung rank was asked to stop and left (through its teardown, naming where it had been, when it
+    # was up far enough to have installed the handler); the parent did not wait for the full join
+    assert "1 rank(s) did not finish" in str(e.value)
+    assert time.monotonic() - t0 < 25.0 + 45.0
