@@ -90,6 +90,8 @@ def test_prefill_flow_matches_fp32(host_kernels, fused_glue, fused_swiglu):
     assert (y.float() - ref).abs().max().item() < 0.1
     y2 = layer.forward(x, batch, seq)                                # buffers are reused: same result again
     assert torch.equal(y, y2)
+    y3 = layer.forward(x, batch, seq, barrier_between_phases=True)   # the optional phase barriers change nothing
+    assert torch.equal(y, y3)
     y_lib = layer.forward_reference(x, batch, seq)
     assert (y.float() - y_lib.float()).abs().max().item() < 0.1
 
