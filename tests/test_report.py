@@ -84,3 +84,19 @@ def test_all_reduce_thresholds_from_a_sweep(tmp_path, monkeypatch):
     from symm_mem_recipes_b200.ops.all_reduce import choose_algo
     assert [choose_algo(n, 8, True, cfg) for n in (4096, 16384, 32768)] == ["low_latency", "one_shot", "multimem"]
     assert choose_algo(32768, 8, False, cfg) == "two_shot"
+
+
+def test_roofline_expectations():
+    from symm_mem_recipes_b200.bench.expect import DEFAULT_PEAKS, expect
+
+    e = expect("all_gather_matmul", 8, DEFAULT_PEAKS, M=16384, N=3584, K=8192)
+    assert e["bound_by"] == "tensor" and e["target_us"] == 584.0 and e["nvlink_in_us"] == 305.0
+    e = expect("matmul_reduce_scatter", 8, DEFAULT_PEAKS, M=32768, N=8192, K=1024)
+    assert e["bound_by"] == "nvlink_out" and abs(e["target_us"] - 610.1) < 0.2       # the o-projection is wire-bound
+    e = expect("matmul_reduce_scatter", 8, DEFAULT_PEAKS, M=32768, N=8192, K=3584)
+    assert e["bound_by"] == "tensor"
+    e = expect("gemv_all_reduce", 8, DEFAULT_PEAKS, K=3584, N=8192, batch=1)
+    assert e["bound_by"] == "hbm" and e["target_us"] == 9.0
+    nvls = expect("all_reduce", 8, DEFAULT_PEAKS, nbytes=64 << 20)
+    p2p = expect("all_reduce", 8, DEFAULT_PEAKS, nbytes=64 << 20, nvls=False)
+    assert nvls["target_us"] < p2p["target_us"] and nvls["bound_by"] == "nvlink"
