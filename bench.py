@@ -17,7 +17,8 @@ launching stream with an L2 flush (256 MB write) before it; barrier +
 synchronize on both sides of the timed region; maximum over ranks.
 `e2e` repeats the measurement through the public API including, every step,
 the host-to-device copy of the step's A shard from pinned memory and a
-device-to-host read of a checksum of C.
+device-to-host read of a checksum of C.  `same_box_baseline` is the library
+composition (NCCL all-gather + cuBLAS) timed the same way in the same run.
 """
 from __future__ import annotations
 
@@ -155,6 +156,18 @@ def main() -> int:
             timed(step, args.steps)
     symm_mem.check_status(dev)
 
+    # ---- the library composition on the same box, same shape, same timing: NCCL all-gather + cuBLAS
+    #      (upstream's own baseline, triton_all_gather_matmul.py:322-326); cuBLAS alone when N = 1 ----
+    def baseline_step():
+        if distributed:
+            smr.reference_all_gather_matmul(a_shard, b)
+        else:
+            torch.matmul(a_shard, b.t(), out=c_out)
+
+    for _ in range(3):
+        baseline_step()
+    baseline_ms, _ = timed(baseline_step, args.steps)
+
     # ---- end to end: H2D of the step's input, public API, D2H of a checksum ----
     def e2e_step():
         a_shard.copy_(a_host, non_blocking=True)
@@ -194,6 +207,10 @@ def main() -> int:
         "e2e": {"value": round(e2e_tflops, 2), "unit": "TFLOPS (aggregate over GPUs)",
                 "ms_per_step": round(e2e_ms, 5),
                 "h2d_bytes_per_step": a_host.numel() * 2, "d2h_bytes_per_step": 4},
+        "same_box_baseline": {
+            "what": "NCCL all_gather_into_tensor + cuBLAS torch.matmul" if distributed else
+                    "cuBLAS torch.matmul alone (nothing to gather at one GPU)",
+            "ms_per_step": round(baseline_ms, 5), "speedup": round(baseline_ms / ms_per_step, 4)},
         "gpu_launches": args.steps,   # one fused kernel per step
         "clocks": clocks.summary(),
         "wall_s_timed_region": round(wall, 4),
