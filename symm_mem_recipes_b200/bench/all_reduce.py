@@ -35,6 +35,9 @@ def main(argv=None, standalone: bool = True) -> int:
                     help="graph: CUDA-graph replay (device time per call) up to --graph-limit bytes")
     ap.add_argument("--graph-limit", type=int, default=4 * 1024 * 1024)
     ap.add_argument("--out", default=None, help="also append the JSON lines to this file")
+    ap.add_argument("--multimem-blocks", type=int, default=0, help="CTAs of the multimem kernel (0: configured default)")
+    ap.add_argument("--multimem-unroll", type=int, default=0, help="4, 8 or 16 reductions in flight per thread")
+    ap.add_argument("--nvls-barrier", action="store_true", help="multimem kernel: barriers by multimem.red")
     args = ap.parse_args(argv)
 
     from symm_mem_recipes_b200.bench._common import finish, init_distributed
@@ -53,6 +56,12 @@ def main(argv=None, standalone: bool = True) -> int:
     hdl = symm_mem.rendezvous(buf)
     plain = torch.randn(max_numel, device=dev).to(torch.bfloat16)
     cfg = AllReduceConfig()
+    if args.multimem_blocks:
+        cfg.multimem_max_blocks = args.multimem_blocks
+    if args.multimem_unroll:
+        cfg.multimem_unroll = args.multimem_unroll
+    if args.nvls_barrier:
+        cfg.multimem_nvls_barrier = 1
     ref_fn = ref_buf = None
     if args.with_reference_triton:
         try:
@@ -147,7 +156,11 @@ def main(argv=None, standalone: bool = True) -> int:
                 us = benchmark_with_event(fn, warm, iters, flush_l2=False)
                 how = "event"
             buf.normal_()   # in-place algorithms grow the values; refresh
-            emit({"op": "all_reduce", "impl": name, "world_size": world, "bytes": nbytes, "timing": how,
+            extra = {}
+            if name == "multimem":
+                extra = {"multimem_blocks": cfg.multimem_max_blocks, "multimem_unroll": cfg.multimem_unroll,
+                         "nvls_barrier": bool(cfg.multimem_nvls_barrier)}
+            emit({"op": "all_reduce", "impl": name, "world_size": world, "bytes": nbytes, "timing": how, **extra,
                   "us": round(us, 2), "alg_gbs": round(nbytes / us / 1e3, 2),
                   "bus_gbs": round(2 * (world - 1) / world * nbytes / us / 1e3, 2)})
         hdl.check()
