@@ -38,6 +38,9 @@ def main(argv=None, standalone: bool = True) -> int:
     ap.add_argument("--multimem-blocks", type=int, default=0, help="CTAs of the multimem kernel (0: configured default)")
     ap.add_argument("--multimem-unroll", type=int, default=0, help="4, 8 or 16 reductions in flight per thread")
     ap.add_argument("--nvls-barrier", action="store_true", help="multimem kernel: barriers by multimem.red")
+    ap.add_argument("--multimem-sweep", action="store_true",
+                    help="instead of the size sweep: the multimem kernel over CTA counts, unroll factors and both "
+                         "barrier kinds at 16, 64 and 256 MiB (clamped to --max-bytes), one start-up")
     args = ap.parse_args(argv)
 
     from symm_mem_recipes_b200.bench._common import finish, init_distributed
@@ -119,6 +122,31 @@ def main(argv=None, standalone: bool = True) -> int:
             s = json.dumps(rec)
             print(s, flush=True)
             lines.append(s)
+
+    if args.multimem_sweep:
+        if world > 1 and hdl.has_multicast:
+            for nbytes in (16 << 20, 64 << 20, 256 << 20):
+                if nbytes > args.max_bytes:
+                    continue
+                t = buf[:nbytes // 2]
+                for nvls in (0, 1):
+                    for blocks in (8, 12, 16, 24, 32):
+                        for unroll in (4, 8, 16):
+                            c = AllReduceConfig(multimem_max_blocks=blocks, multimem_unroll=unroll,
+                                                multimem_nvls_barrier=nvls)
+                            us = benchmark_with_event(lambda: smr.multimem_all_reduce_(t, config=c), 5, 15,
+                                                      flush_l2=False)
+                            hdl.check()
+                            buf.normal_()
+                            emit({"op": "all_reduce_multimem_sweep", "world_size": world, "bytes": nbytes,
+                                  "blocks": blocks, "unroll": unroll, "nvls_barrier": bool(nvls), "us": round(us, 2),
+                                  "bus_gbs": round(2 * (world - 1) / world * nbytes / us / 1e3, 1)})
+        if args.out and rank == 0:
+            with open(args.out, "a") as f:
+                f.write("\n".join(lines) + "\n")
+        if standalone:
+            finish()
+        return 0
 
     algos = [a for a in args.algos.split(",") if a]
     nbytes = args.min_bytes
