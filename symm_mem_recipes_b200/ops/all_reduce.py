@@ -139,11 +139,21 @@ def multimem_all_reduce_(t: torch.Tensor, *, config: AllReduceConfig = DEFAULT_A
     return t
 
 
+_UNROLLED_WORLD_SIZES = frozenset({1, 2, 4, 8})
+
+
 def choose_algo(nbytes: int, world_size: int, has_multicast: bool,
                 config: AllReduceConfig = DEFAULT_ALL_REDUCE) -> str:
     """The dispatcher's decision, exposed for tests and benchmarks."""
     if world_size == 1:
         return "one_shot"
+    if world_size not in _UNROLLED_WORLD_SIZES:
+        # the peer-to-peer kernels are compiled with the world size unrolled; any other world (say 7
+        # ranks left after one was lost) goes through the switch, whose kernel takes it at run time
+        if not has_multicast:
+            raise SymmMemError(f"all-reduce over {world_size} ranks needs a multicast mapping: the peer-to-peer "
+                               f"kernels are built for {sorted(_UNROLLED_WORLD_SIZES)} ranks")
+        return "multimem"
     if nbytes <= min(config.ll_max_bytes, _LL_CAPACITY_NUMEL * 2):
         return "low_latency"
     if nbytes <= config.one_shot_max_bytes:

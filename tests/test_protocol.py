@@ -101,3 +101,14 @@ def test_interleaved_gate_up_puts_matching_columns_in_one_tile():
     assert torch.allclose(got, want, atol=1e-5)
     with pytest.raises(SymmMemError):
         interleave_gate_up(wg[:100], wu[:100])
+
+
+def test_dispatcher_sends_odd_world_sizes_through_the_switch():
+    from symm_mem_recipes_b200.errors import SymmMemError
+    from symm_mem_recipes_b200.ops.all_reduce import choose_algo
+
+    for ws in (3, 5, 6, 7):
+        assert choose_algo(4096, ws, True) == "multimem" and choose_algo(1 << 26, ws, True) == "multimem"
+        with pytest.raises(SymmMemError, match="multicast"):
+            choose_algo(4096, ws, False)
+    assert choose_algo(4096, 8, True) == "low_latency" and choose_algo(4096, 1, False) == "one_shot"
