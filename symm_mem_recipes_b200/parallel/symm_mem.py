@@ -404,10 +404,24 @@ def shutdown() -> None:
     _groups.clear()
 
 
-def _reset_for_tests() -> None:
+def reset() -> None:
+    """`shutdown()`, after which the module accepts new allocations again.  For a
+    job that re-forms its process group (for example the survivors after
+    `PeerLost`): every symmetric tensor and every cached workspace of the ops
+    is gone afterwards and is re-created, collectively, by the new group."""
     global _shutdown_done
     shutdown()
     _shutdown_done = False
+    # workspaces the ops keep per (shape, group): they point into released allocations
+    import importlib
+    for mod, names in (("ag_matmul", ("_gather_buffers",)), ("all_reduce", ("_ll_workspaces",)),
+                       ("gemv_all_reduce", ("_workspaces",)), ("matmul_reduce_scatter", ("_workspaces", "_ar_outputs"))):
+        m = importlib.import_module(f"symm_mem_recipes_b200.ops.{mod}")
+        for name in names:
+            getattr(m, name).clear()
+
+
+_reset_for_tests = reset
 
 
 atexit.register(shutdown)

@@ -248,3 +248,57 @@ def _signal_worker(rank, world_size):
 @pytest.mark.parametrize("world_size", [2, 4])
 def test_one_to_one_signals(world_size):
     spawn_ranks(_signal_worker, world_size, "gloo")
+
+
+# ---- elastic: the survivors of a lost rank re-form a smaller group and carry on ----
+def _reform_worker(rank, world_size, rdzv_file):
+    import time
+
+    import torch.distributed as dist
+
+    import symm_mem_recipes_b200 as smr
+    from symm_mem_recipes_b200._ext import C
+    from symm_mem_recipes_b200.parallel import symm_mem
+    from symm_mem_recipes_b200.parallel.health import Heartbeat, PeerLost
+
+    hb = Heartbeat(interval_s=0.05)
+    hb.wait_for_all(timeout_s=30)
+    numel = 4096
+    t = symm_mem.empty(numel, dtype=torch.bfloat16, device="cpu")
+    t.copy_(seeded_normal_bf16(numel, rank))
+    hdl = symm_mem.rendezvous(t)
+    hdl.barrier()
+    out3 = smr.one_shot_all_reduce(t)
+    hdl.barrier()
+    assert torch.equal(out3, C.oracle_ordered_sum_bf16([seeded_normal_bf16(numel, r) for r in range(world_size)]))
+    small = smr.low_latency_all_reduce(t[:512].clone())          # leaves a cached workspace behind
+    assert small.shape == (512,)
+    if rank == world_size - 1:
+        hb.stop()                                                # the rank that goes away, between steps
+        return
+    while True:                                                  # survivors notice on the host ...
+        try:
+            hb.check(max_age_s=10.0)
+            time.sleep(0.02)
+        except PeerLost as e:
+            assert e.rank == world_size - 1
+            break
+    hb.stop(leaving=False)
+    symm_mem.reset()                                             # ... drop everything tied to the old group,
+    dist.destroy_process_group()
+    survivors = world_size - 1
+    dist.init_process_group("gloo", init_method=f"file://{rdzv_file}", rank=rank, world_size=survivors)
+    t2 = symm_mem.empty(numel, dtype=torch.bfloat16, device="cpu")   # ... and carry on as a smaller world
+    t2.copy_(seeded_normal_bf16(numel, rank))
+    hdl2 = symm_mem.rendezvous(t2)
+    assert hdl2.world_size == survivors
+    hdl2.barrier()
+    out2 = smr.one_shot_all_reduce(t2)
+    hdl2.barrier()
+    assert torch.equal(out2, C.oracle_ordered_sum_bf16([seeded_normal_bf16(numel, r) for r in range(survivors)]))
+    again = smr.low_latency_all_reduce(t2[:512].clone())         # the cached workspace was re-created
+    assert torch.equal(again, out2[:512])
+
+
+def test_survivors_reform_a_smaller_group(tmp_path):
+    spawn_ranks(_reform_worker, 3, "gloo", (str(tmp_path / "rdzv2"),))
