@@ -75,3 +75,12 @@ def test_barrier_test_kinds_are_checked():
 def test_matmul_all_reduce_shape_checks():
     with pytest.raises(SymmMemError, match="a\\[M, K\\]"):
         smr.matmul_all_reduce(_bf16(256, 64), _bf16(128, 32))
+
+
+def test_info_runs_without_a_gpu():
+    from symm_mem_recipes_b200 import info
+
+    d = info.collect()
+    assert "torch" in d and "gpus" in d and d["limits"]["max_world_size"] >= 8
+    if not torch.cuda.is_available():
+        assert d["gpus"] == [] and "CPU backend" in d["note"]
