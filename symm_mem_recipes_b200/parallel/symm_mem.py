@@ -371,9 +371,16 @@ def _setup_multicast(alloc, st: _GroupState) -> None:
 
 
 def free(t: torch.Tensor) -> None:
-    """Unmap the allocation behind `t` on this rank.  All ranks should call it
-    at the same point, with no kernel in flight; `t` must not be used again."""
+    """Release the allocation behind `t`; `t` and every view of it must not be
+    used again.  For a rendezvoused allocation this is collective over its
+    group: the ranks synchronise their devices and meet (through the Store)
+    before anyone unmaps, so that no kernel of a peer still reaches the memory
+    and nobody unbinds multicast memory that a peer still uses."""
     rec, _ = _find_record(t)
+    if rec.kind == "cuda" and torch.cuda.is_available():
+        torch.cuda.synchronize()
+    if rec.handle is not None and rec.handle.world_size > 1 and dist.is_initialized():
+        _group_state(rec.handle.group).exchange.barrier()
     _records.pop(rec.base_ptr, None)
     rec.alloc.release()
 

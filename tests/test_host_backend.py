@@ -302,3 +302,28 @@ def _reform_worker(rank, world_size, rdzv_file):
 
 def test_survivors_reform_a_smaller_group(tmp_path):
     spawn_ranks(_reform_worker, 3, "gloo", (str(tmp_path / "rdzv2"),))
+
+
+def _free_worker(rank, world_size):
+    import time
+
+    from symm_mem_recipes_b200.parallel import symm_mem
+
+    a = symm_mem.empty(1024, dtype=torch.float32, device="cpu")
+    b = symm_mem.empty(1024, dtype=torch.float32, device="cpu")
+    ha, hb = symm_mem.rendezvous(a), symm_mem.rendezvous(b)
+    a.fill_(float(rank + 1))
+    ha.barrier()
+    if rank == 0:
+        time.sleep(0.5)                          # a slow reader: rank 1 must not unmap under it
+        assert float(ha.get_buffer(1, (1024,), torch.float32)[-1]) == 2.0
+    symm_mem.free(a)                             # collective: nobody releases before everybody is here
+    assert not symm_mem.is_symm_mem_tensor(a)
+    b.fill_(float(rank))
+    hb.barrier()
+    assert float(hb.get_buffer((rank + 1) % world_size, (1024,), torch.float32)[0]) == float((rank + 1) % world_size)
+    hb.barrier()
+
+
+def test_free_is_collective():
+    spawn_ranks(_free_worker, 2, "gloo")
