@@ -5,6 +5,8 @@ and of the world-of-one GEMV and all-reduce kernels.  Also the program that
 
     python -m symm_mem_recipes_b200.bench.matmul --M 16384 --N 3584 --K 8192
     python -m symm_mem_recipes_b200.bench.matmul --op gemv --batch 16
+    python -m symm_mem_recipes_b200.bench.matmul --op glue --M 32768          # RMSNorm, RoPE, SiLU-mul kernels
+    python -m symm_mem_recipes_b200.bench.matmul --op matmul --variant fp8    # or swiglu
 """
 from __future__ import annotations
 
@@ -17,7 +19,10 @@ import torch
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="matmul", choices=["matmul", "gemv", "all_reduce"])
+    ap.add_argument("--op", default="matmul", choices=["matmul", "gemv", "all_reduce", "glue"])
+    ap.add_argument("--variant", default="bf16", choices=["bf16", "fp8", "swiglu"],
+                    help="matmul: float8_e4m3fn operands and output, or the SwiGLU epilogue (N = 2 x FFN width)")
+    ap.add_argument("--gemv-algo", default=None, help="gemv: tc, tc_tagged or simt")
     ap.add_argument("--M", type=int, default=16384)
     ap.add_argument("--N", type=int, default=3584)
     ap.add_argument("--K", type=int, default=8192)
@@ -45,15 +50,17 @@ def main() -> int:
     with ClockSampler(0, period_ms=100) as clocks:
         if args.op == "matmul":
             M, N, K = args.M, args.N, args.K
-            a = (torch.randn(M, K, device=dev) * 0.02).to(torch.bfloat16)
-            b = (torch.randn(N, K, device=dev) * 0.02).to(torch.bfloat16)
-            c = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+            dt = torch.float8_e4m3fn if args.variant == "fp8" else torch.bfloat16
+            a = (torch.randn(M, K, device=dev) * 0.02).to(dt)
+            b = (torch.randn(N, K, device=dev) * 0.02).to(dt)
+            epilogue = "swiglu" if args.variant == "swiglu" else None
+            c = torch.empty(M, N // 2 if epilogue else N, dtype=dt, device=dev)
             cfg = AgMatmulConfig(block_n=args.block_n)
             flops = 2.0 * M * N * K
-            us = benchmark_with_event(lambda: smr.matmul(a, b, c, cfg), **bench)
-            out.update(M=M, N=N, K=K, block_n=args.block_n or choose_block_n(M, N, 148),
+            us = benchmark_with_event(lambda: smr.matmul(a, b, c, cfg, epilogue), **bench)
+            out.update(M=M, N=N, K=K, variant=args.variant, block_n=args.block_n or choose_block_n(M, N, 148),
                        smr_us=round(us, 1), smr_tflops=round(flops / us / 1e6, 1))
-            if not args.no_cublas:
+            if not args.no_cublas and args.variant == "bf16":
                 bt = b.t()
                 us2 = benchmark_with_event(lambda: torch.matmul(a, bt, out=c), **bench)
                 out.update(cublas_us=round(us2, 1), cublas_tflops=round(flops / us2 / 1e6, 1))
@@ -69,7 +76,7 @@ def main() -> int:
 
             def fused():
                 state["i"] = (state["i"] + 1) % 4
-                smr.gemv_all_reduce(x, ws_[state["i"]], y)
+                smr.gemv_all_reduce(x, ws_[state["i"]], y, algo=args.gemv_algo)
 
             def lib():
                 state["i"] = (state["i"] + 1) % 4
@@ -85,6 +92,28 @@ def main() -> int:
             if not args.no_cublas and not args.eager:
                 us2 = benchmark_with_graph(lib, calls_per_graph=20, replays=10, all_ranks_max=False)
                 out.update(cublas_us=round(us2, 2))
+        elif args.op == "glue":
+            # the layer-glue kernels at the decoder layer's per-rank sizes: T tokens, hidden 8192,
+            # 8 + 1 + 1 heads of 128 in the QKV buffer, FFN 3584 per rank; all bound by HBM
+            from symm_mem_recipes_b200 import ops
+            T = args.M
+            x = (torch.randn(T // 8, 8192, device=dev) * 0.5).to(torch.bfloat16)
+            r = (torch.randn(T // 8, 8192, device=dev) * 0.5).to(torch.bfloat16)
+            w = torch.ones(8192, dtype=torch.bfloat16, device=dev)
+            o1, s1 = torch.empty_like(x), torch.empty_like(x)
+            qkv = (torch.randn(T, 1280, device=dev) * 0.5).to(torch.bfloat16)
+            gu = (torch.randn(T, 7168, device=dev) * 0.5).to(torch.bfloat16)
+            act = torch.empty(T, 3584, dtype=torch.bfloat16, device=dev)
+            cases = {
+                "rms_norm": (lambda: ops.rms_norm(x, w, 1e-5, out=o1), 2 * x.numel() * 2),
+                "add_rms_norm": (lambda: ops.rms_norm(x, w, 1e-5, out=o1, residual=r, sum_out=s1), 4 * x.numel() * 2),
+                "rope": (lambda: ops.rope_(qkv, 9, 128, 2048, 500000.0), 2 * T * 9 * 128 * 2),
+                "silu_mul": (lambda: ops.silu_mul(gu, act), (gu.numel() + act.numel()) * 2),
+            }
+            for name, (fn, nbytes) in cases.items():
+                us = benchmark_with_event(fn, **bench)
+                out[name] = {"us": round(us, 1), "gbs": round(nbytes / us / 1e3, 1)}
+            out["tokens"] = T
         else:
             numel = args.bytes // 2
             t = symm_mem.empty(numel, dtype=torch.bfloat16, device=dev)
