@@ -13,6 +13,10 @@ Prefill (`forward`), activations sharded on tokens between the blocks:
 Decode (`decode`), activations replicated, batch <= 16: the two row-parallel
 projections use the fused GEMV + all-reduce.
 
+Prefill without sequence parallelism (`forward_tp`), activations replicated:
+local GEMMs for the column-parallel projections, `matmul_all_reduce` for the
+row-parallel ones.
+
 `forward_reference` / `decode_reference` build the same layer from NCCL
 collectives and cuBLAS and are the baseline the fused layer is timed against.
 The upstream recipes stop at the single fused op; this module is how the ops
@@ -220,6 +224,46 @@ class LlamaTPDecoderLayer:
         y = x1 + d
         self._mark("residual")
         return y
+
+    # ------------------------------------------------------------------
+    def forward_tp(self, x: torch.Tensor, batch: int, seq: int) -> torch.Tensor:
+        """Prefill under plain tensor parallelism (no sequence parallelism):
+        `x` [batch*seq, H] is replicated on every rank, the column-parallel
+        projections are local tcgen05 GEMMs, and the two row-parallel ones end
+        in an all-reduce inside the kernel (`matmul_all_reduce`).  Returns the
+        full [batch*seq, H] output, identical on every rank."""
+        cfg = self.cfg
+        assert x.shape[0] == batch * seq
+        h = ops.rms_norm(x, self.norm1, cfg.eps) if self.fused_glue else _rms_norm(x, self.norm1, cfg.eps)
+        qkv = ops.matmul(h, self.w_qkv)
+        attn = self._attention(qkv, batch, seq, glue=self.fused_glue)
+        o = ops.matmul_all_reduce(attn, self.w_o, group=self.group)      # internal symmetric buffer: consume it
+        if self.fused_glue:                                              # before the next call of this shape
+            h2, x1 = ops.rms_norm(x, self.norm2, cfg.eps, residual=o)
+        else:
+            x1 = x + o
+            h2 = _rms_norm(x1, self.norm2, cfg.eps)
+        if self.fused_swiglu:
+            act = ops.matmul(h2, self.w_gate_up_interleaved, epilogue="swiglu")
+        else:
+            act = self._mlp_act(ops.matmul(h2, self.w_gate_up))
+        return x1 + ops.matmul_all_reduce(act, self.w_down, group=self.group)
+
+    def forward_tp_reference(self, x: torch.Tensor, batch: int, seq: int) -> torch.Tensor:
+        """`forward_tp` from cuBLAS and NCCL all-reduce."""
+        cfg = self.cfg
+
+        def reduced(t):
+            if self.ws > 1:
+                dist.all_reduce(t, group=self.group)
+            return t
+
+        h = _rms_norm(x, self.norm1, cfg.eps)
+        attn = self._attention(h @ self.w_qkv.t(), batch, seq)
+        x1 = x + reduced(attn @ self.w_o.t())
+        h2 = _rms_norm(x1, self.norm2, cfg.eps)
+        act = self._mlp_act_torch(h2 @ self.w_gate_up.t(), self.ffn_local)
+        return x1 + reduced(act @ self.w_down.t())
 
     def forward_reference(self, x_shard: torch.Tensor, batch: int, seq: int) -> torch.Tensor:
         """The same layer from NCCL all-gather / reduce-scatter and cuBLAS."""

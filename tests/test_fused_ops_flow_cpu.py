@@ -207,3 +207,91 @@ def _row_parallel_flow_worker(rank, world_size):
 
 def test_row_parallel_ops_host_flow():
     spawn_ranks(_row_parallel_flow_worker, 2, "gloo")
+
+
+def _install_row_parallel_and_glue_stand_ins():
+    """matmul_reduce_scatter / matmul_all_reduce by a gloo all-reduce of bf16 partials, glue ops by the oracles."""
+    import importlib
+
+    import torch.distributed as dist
+
+    from symm_mem_recipes_b200._ext import C as real
+
+    rs_mod = importlib.import_module("symm_mem_recipes_b200.ops.matmul_reduce_scatter")
+    glue_mod = importlib.import_module("symm_mem_recipes_b200.ops.layer_glue")
+
+    def summed(a, b):
+        part = (a.float() @ b.float().t()).to(torch.bfloat16).float()
+        dist.all_reduce(part)
+        return part
+
+    class Fake:
+        def __getattr__(self, name):
+            return getattr(real, name)
+
+        @staticmethod
+        def matmul_reduce_scatter(a, b, out, workspace, num_sms, timeout_ns, trace=None, deep_strips=False,
+                                  cta_pair=False):
+            rank, rows = dist.get_rank(), out.shape[0]
+            out.copy_(summed(a, b)[rank * rows:(rank + 1) * rows].to(out.dtype))
+
+        @staticmethod
+        def matmul_all_reduce(a, b, out, out_alloc, out_offset, workspace, num_sms, timeout_ns, cta_pair=False):
+            out.copy_(summed(a, b).to(out.dtype))
+
+        @staticmethod
+        def rms_norm(x, residual, w, sum_out, out, eps):
+            o, s = real.oracle_rms_norm_bf16(x, residual, w, eps)
+            out.copy_(o)
+            if sum_out is not None:
+                sum_out.copy_(s)
+
+        @staticmethod
+        def rope_inplace(qkv, n_heads, head_dim, seq, pos0, theta, num_sms):
+            qkv.copy_(real.oracle_rope_bf16(qkv, n_heads, head_dim, seq, pos0, theta))
+
+        @staticmethod
+        def silu_mul(gate_up, out, num_sms):
+            out.copy_(real.oracle_silu_mul_bf16(gate_up))
+
+    rs_mod.C = glue_mod.C = Fake()
+    rs_mod._num_sms = glue_mod._num_sms = lambda device: 148
+    glue_mod._check = lambda name, t, dim: None
+
+
+def _layer_flow_worker(rank, world_size, fused_glue, fused_swiglu):
+    import torch.distributed as dist
+
+    from symm_mem_recipes_b200.models.llama_tp_layer import (LlamaTPConfig, LlamaTPDecoderLayer,
+                                                             full_precision_reference)
+
+    _install_host_kernels()
+    _install_row_parallel_and_glue_stand_ins()
+    cfg = LlamaTPConfig.tiny(world_size)
+    layer = LlamaTPDecoderLayer(cfg, torch.device("cpu"), seed=1, fused_glue=fused_glue, fused_swiglu=fused_swiglu)
+    mine = (layer.w_qkv, layer.w_o, layer.w_gate_up, layer.w_down, layer.norm1, layer.norm2)
+    weights = [None] * world_size
+    dist.all_gather_object(weights, mine)
+    batch, seq = 2, 64 * world_size                       # 128 token rows per rank
+    g = torch.Generator().manual_seed(3)
+    x = (torch.randn(batch * seq, cfg.hidden, generator=g) * 0.5).to(torch.bfloat16)     # same on every rank
+    ref = full_precision_reference(weights, cfg, x, batch, seq)
+    rows = batch * seq // world_size
+
+    # sequence-parallel prefill: token-sharded in, token-sharded out
+    y = layer.forward(x[rank * rows:(rank + 1) * rows].contiguous(), batch, seq)
+    assert (y.float() - ref[rank * rows:(rank + 1) * rows]).abs().max().item() < 0.15
+    y_again = layer.forward(x[rank * rows:(rank + 1) * rows].contiguous(), batch, seq, barrier_between_phases=True)
+    assert torch.equal(y, y_again)                        # the symmetric buffers are reused cleanly
+    # plain tensor parallelism: replicated in, replicated out
+    y_tp = layer.forward_tp(x, batch, seq)
+    assert (y_tp.float() - ref).abs().max().item() < 0.15
+    assert (y_tp[rank * rows:(rank + 1) * rows].float() - y.float()).abs().max().item() < 0.15
+    # the library compositions agree too
+    assert (layer.forward_tp_reference(x, batch, seq).float() - ref).abs().max().item() < 0.15
+    dist.barrier()
+
+
+@pytest.mark.parametrize("fused_glue,fused_swiglu", [(False, False), (True, True)])
+def test_decoder_layer_host_flow_two_ranks(fused_glue, fused_swiglu):
+    spawn_ranks(_layer_flow_worker, 2, "gloo", (fused_glue, fused_swiglu))

@@ -79,3 +79,39 @@ def test_layer_2gpu():
 @pytest.mark.multigpu(4)
 def test_layer_4gpu():
     spawn_ranks(_layer_worker, 4, "nccl")
+
+
+def _layer_tp_worker(rank, world_size, fused_glue, fused_swiglu):
+    """Prefill without sequence parallelism (matmul_all_reduce endings) and the sequence-parallel
+    prefill with the single-pass glue kernels, against the library compositions."""
+    from symm_mem_recipes_b200.models.llama_tp_layer import LlamaTPConfig, LlamaTPDecoderLayer
+    from symm_mem_recipes_b200.parallel import symm_mem
+
+    dev = torch.device("cuda", rank)
+    cfg = LlamaTPConfig.tiny(world_size)
+    layer = LlamaTPDecoderLayer(cfg, dev, seed=11, fused_glue=fused_glue, fused_swiglu=fused_swiglu)
+    batch, seq = 2, 128 * world_size
+    rows = batch * seq // world_size
+    g = torch.Generator().manual_seed(5)
+    x = (torch.randn(batch * seq, cfg.hidden, generator=g) * 0.5).to(torch.bfloat16).to(dev)
+    failures = []
+    for it in range(2):
+        y_tp = layer.forward_tp(x, batch, seq)
+        symm_mem.check_status(dev)
+        y_tp_lib = layer.forward_tp_reference(x, batch, seq)
+        if not torch.allclose(y_tp.float(), y_tp_lib.float(), rtol=5e-2, atol=5e-2):
+            failures.append(f"call {it}: TP prefill vs cuBLAS + NCCL: {(y_tp.float() - y_tp_lib.float()).abs().max().item()}")
+        y_sp = layer.forward(x[rank * rows:(rank + 1) * rows].contiguous(), batch, seq)
+        symm_mem.check_status(dev)
+        if not torch.allclose(y_sp.float(), y_tp_lib[rank * rows:(rank + 1) * rows].float(), rtol=5e-2, atol=5e-2):
+            failures.append(f"call {it}: SP prefill differs from the TP result")
+    torch.cuda.synchronize()
+    assert not failures, failures
+
+
+@pytest.mark.gpu
+@pytest.mark.first_run
+@pytest.mark.multigpu(2)
+@pytest.mark.parametrize("fused_glue,fused_swiglu", [(False, False), (True, True)])
+def test_layer_tensor_parallel_prefill_2gpu(fused_glue, fused_swiglu):
+    spawn_ranks(_layer_tp_worker, 2, "nccl", (fused_glue, fused_swiglu))

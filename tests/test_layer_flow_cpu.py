@@ -114,3 +114,14 @@ def test_phase_marks_are_off_by_default(host_kernels):
     _, layer, x, batch, seq, _ = _layer_and_reference(False, False)
     layer.forward(x, batch, seq)
     assert layer.phase_marks is None
+
+
+@pytest.mark.parametrize("fused_glue,fused_swiglu", [(False, False), (True, False), (True, True)])
+def test_tensor_parallel_prefill_flow_matches_fp32(host_kernels, fused_glue, fused_swiglu):
+    """Without sequence parallelism (replicated activations, all-reduce endings): same layer, same answer."""
+    cfg, layer, x, batch, seq, ref = _layer_and_reference(fused_glue, fused_swiglu)
+    y = layer.forward_tp(x, batch, seq)
+    assert y.shape == x.shape and (y.float() - ref).abs().max().item() < 0.1
+    y_lib = layer.forward_tp_reference(x, batch, seq)
+    assert (y.float() - y_lib.float()).abs().max().item() < 0.1
+    assert (y.float() - layer.forward(x, batch, seq).float()).abs().max().item() < 0.1
