@@ -36,6 +36,9 @@ def main(argv=None, standalone: bool = True) -> int:
                          "both: time the two; all: also with SiLU-mul inside the gate/up epilogue; "
                          "env: SMR_FUSED_GLUE / SMR_FUSED_SWIGLU")
     ap.add_argument("--breakdown", action="store_true", help="also print the device time of every phase of the layer")
+    ap.add_argument("--tp", action="store_true",
+                    help="also time the prefill without sequence parallelism (replicated activations, "
+                         "matmul_all_reduce endings) against cuBLAS + NCCL all-reduce")
     ap.add_argument("--out", default=None)
     args = ap.parse_args(argv)
     from symm_mem_recipes_b200.bench._common import finish, init_distributed
@@ -121,6 +124,21 @@ def main(argv=None, standalone: bool = True) -> int:
                 emit({"op": "llama70b_layer_prefill_phases", "world_size": world, "fused_glue": layer.fused_glue,
                       "fused_swiglu": layer.fused_swiglu,
                       "rank": 0, "us": {k: round(v, 1) for k, v in phases.items()}})
+        if args.tp:
+            x_full = (torch.randn(T, cfg.hidden, device=dev) * 0.5).to(torch.bfloat16)
+            if world > 1:
+                dist.broadcast(x_full, 0)
+            y = layer.forward_tp(x_full, args.batch, args.seq)
+            symm_mem.check_status(dev)
+            y_ref = layer.forward_tp_reference(x_full, args.batch, args.seq)
+            rel = float((y.float() - y_ref.float()).abs().max() / y_ref.float().abs().max())
+            us_f = benchmark_with_event(lambda: layer.forward_tp(x_full, args.batch, args.seq), **bench)
+            us_r = benchmark_with_event(lambda: layer.forward_tp_reference(x_full, args.batch, args.seq), **bench)
+            symm_mem.check_status(dev)
+            emit({"op": "llama70b_layer_prefill_tp", "world_size": world, "batch": args.batch, "seq": args.seq,
+                  "fused_glue": layer.fused_glue, "fused_swiglu": layer.fused_swiglu, "matches_library": rel < 3e-2,
+                  "max_rel_diff": round(rel, 5), "smr_fused_us": round(us_f, 1), "nccl_cublas_us": round(us_r, 1),
+                  "speedup": round(us_r / us_f, 3)})
         for B in (1, 4, 16):
             xd = (torch.randn(B, cfg.hidden, device=dev) * 0.5).to(torch.bfloat16)
             if world > 1:
