@@ -170,7 +170,7 @@ def gemv_table(recs: list[dict], peaks: Optional[dict]) -> Optional[str]:
 
 def layer_tables(recs: list[dict]) -> Optional[str]:
     rs = [r for r in recs if r.get("op") == "matmul_reduce_scatter"]
-    pre = [r for r in recs if r.get("op") == "llama70b_layer_prefill"]
+    pre = [r for r in recs if r.get("op") in ("llama70b_layer_prefill", "llama70b_layer_prefill_tp")]
     dec = [r for r in recs if r.get("op") == "llama70b_layer_decode"]
     parts = []
     if rs:
@@ -183,9 +183,10 @@ def layer_tables(recs: list[dict]) -> Optional[str]:
              "outbound GB/s", "speed-up"], rows))
     if pre or dec:
         rows = []
-        for r in {(r["world_size"], r["batch"], r["seq"], r.get("fused_glue", False), r.get("fused_swiglu", False)): r
-                  for r in pre}.values():
-            glue = ", single-pass norm / RoPE / SiLU kernels" if r.get("fused_glue") else ""
+        for r in {(r["op"], r["world_size"], r["batch"], r["seq"], r.get("fused_glue", False),
+                   r.get("fused_swiglu", False)): r for r in pre}.values():
+            glue = ", no sequence parallelism" if r["op"].endswith("_tp") else ""
+            glue += ", single-pass norm / RoPE / SiLU kernels" if r.get("fused_glue") else ""
             glue += ", SwiGLU in the GEMM epilogue" if r.get("fused_swiglu") else ""
             rows.append([str(r["world_size"]), f"prefill {r['batch']} x {r['seq']}{glue}", _fmt(r["smr_fused_us"]),
                          _fmt(r["nccl_cublas_us"]), f"{r['speedup']:.2f}x"])
