@@ -370,6 +370,25 @@ def _setup_multicast(alloc, st: _GroupState) -> None:
         xchg.barrier()
 
 
+def memory_summary() -> dict:
+    """Symmetric memory held by this process: one entry per allocation (payload
+    bytes, bytes of the mapped block including the signal pad and granularity
+    rounding, whether it is rendezvoused and bound to a multicast object) and
+    the totals.  A CUDA allocation also occupies (world_size - 1) x block bytes
+    of address space for the peers' mappings, but no more physical memory."""
+    allocations = []
+    for rec in _records.values():
+        h = rec.handle
+        allocations.append({
+            "kind": rec.kind, "payload_bytes": int(rec.nbytes), "block_bytes": int(rec.alloc.block_bytes),
+            "rendezvoused": h is not None, "world_size": h.world_size if h is not None else None,
+            "multicast": bool(h.has_multicast) if h is not None else False,
+        })
+    return {"allocations": allocations, "count": len(allocations),
+            "payload_bytes": sum(a["payload_bytes"] for a in allocations),
+            "block_bytes": sum(a["block_bytes"] for a in allocations)}
+
+
 def free(t: torch.Tensor) -> None:
     """Release the allocation behind `t`; `t` and every view of it must not be
     used again.  For a rendezvoused allocation this is collective over its

@@ -327,3 +327,20 @@ def _free_worker(rank, world_size):
 
 def test_free_is_collective():
     spawn_ranks(_free_worker, 2, "gloo")
+
+
+def test_memory_summary_counts_allocations():
+    from symm_mem_recipes_b200.parallel import symm_mem
+
+    before = symm_mem.memory_summary()
+    t = symm_mem.empty(1000, dtype=torch.float32, device="cpu")
+    u = symm_mem.empty(16, 16, dtype=torch.bfloat16, device="cpu")
+    symm_mem.rendezvous(u)
+    s = symm_mem.memory_summary()
+    assert s["count"] == before["count"] + 2
+    assert s["payload_bytes"] == before["payload_bytes"] + 4000 + 512
+    assert s["block_bytes"] >= s["payload_bytes"] + 2 * 128 * 1024          # each block carries its signal pad
+    assert sum(a["rendezvoused"] for a in s["allocations"]) == sum(a["rendezvoused"] for a in before["allocations"]) + 1
+    symm_mem.free(t)
+    symm_mem.free(u)
+    assert symm_mem.memory_summary()["count"] == before["count"]
