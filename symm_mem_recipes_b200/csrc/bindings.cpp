@@ -595,7 +595,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("matmul_reduce_scatter", [](torch::Tensor a, torch::Tensor b, torch::Tensor out,
                                     const std::shared_ptr<CudaSymmAllocation>& workspace, int num_sms,
                                     uint64_t timeout_ns, c10::optional<torch::Tensor> trace, bool deep_strips,
-                                    bool cta_pair) {
+                                    bool cta_pair, bool thread_stores) {
     auto ok2d = [](const torch::Tensor& t) {
       return t.is_cuda() && t.dim() == 2 && t.is_contiguous() && t.scalar_type() == torch::kBFloat16;
     };
@@ -626,10 +626,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     }
     args.deep_strips = deep_strips;
     args.cta_pair = cta_pair;
+    args.thread_stores = thread_stores;
     rt_check(launch_matmul_reduce_scatter(args, current_stream(dev)), "matmul_reduce_scatter");
   }, py::arg("a"), py::arg("b"), py::arg("out"), py::arg("workspace"), py::arg("num_sms"),
      py::arg("timeout_ns"), py::arg("trace") = py::none(), py::arg("deep_strips") = false,
-     py::arg("cta_pair") = false);
+     py::arg("cta_pair") = false, py::arg("thread_stores") = false);
 
   // all-reduce form: `out` [M, N] lives in the symmetric allocation `out_alloc` at `out_offset`
   m.def("matmul_all_reduce", [](torch::Tensor a, torch::Tensor b, torch::Tensor out,

@@ -151,6 +151,7 @@ struct MatmulRsArgs {
   uint64_t* trace;     // optional [num_sms][4] %globaltimer stamps per CTA (start, entered, GEMM done, reduced)
   bool deep_strips;    // 3-stage ring and five epilogue strips on the wire instead of 4 stages and two
   bool cta_pair;       // tcgen05 cta_group::2 main loop (256 x 256 tiles on CTA pairs), 5 stages, four strips
+  bool thread_stores;  // 1-CTA kernel: strips leave shared memory by coalesced stores of the epilogue threads
   // all-reduce form: every rank ends up with the whole [M, N] sum in a SYMMETRIC output (`out` is unused);
   // each rank reduces its rows and broadcasts them (multimem.st when `ar_mc`, else stores to every peer)
   bool all_reduce;

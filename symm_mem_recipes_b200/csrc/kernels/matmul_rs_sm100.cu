@@ -62,7 +62,11 @@ __device__ __forceinline__ void tile_coords(const RsParams& p, int t, int& dest,
 // kStages: depth of the operand ring; kNStrips: epilogue strips that may be on the wire at once.
 // <4, 2> is the default; <3, 5> trades a stage for three more strips in flight (short-K shapes,
 // where the wire, not the main loop, is the limit).
-template <int kStages, int kNStrips, bool kAllReduce = false>
+// kThreadStores: a strip leaves shared memory by coalesced 16-byte loads and stores of the 128
+// epilogue threads (512 contiguous bytes per warp instruction) instead of one bulk store by one
+// thread.  Stores issued by threads are not capped at kNStrips per SM on the wire, the buffer is
+// free as soon as it has been read, and the tile's counter is bumped right after its last strip.
+template <int kStages, int kNStrips, bool kAllReduce = false, bool kThreadStores = false>
 __global__ void __launch_bounds__(kThreads, 1)
 matmul_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const RsParams p) {
@@ -199,7 +203,9 @@ matmul_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         tmem_ld_32x32b_x32(taddr + (uint32_t)(sidx * kStripCols + 32), v1);
         tmem_ld_wait();
         // the store issued two strips ago has finished reading the buffer we are about to fill
-        if (etid == 0) bulk_wait_group_read<kNStrips - 1>();
+        if constexpr (!kThreadStores) {
+          if (etid == 0) bulk_wait_group_read<kNStrips - 1>();
+        }
         epilogue_sync();
         uint8_t* buf = strip + (size_t)(strip_ctr % (uint32_t)kNStrips) * kStripBytesOne;
         uint8_t* row = buf + (size_t)r * 128;
@@ -213,6 +219,16 @@ matmul_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           o.w = pack_bf16x2(__uint_as_float(v[6]), __uint_as_float(v[7]));
           *reinterpret_cast<Vec16*>(row + ((c ^ (r & 7)) << 4)) = o;
         }
+        if constexpr (kThreadStores) {
+          epilogue_sync();                               // the strip is complete in shared memory
+          char* dst = static_cast<char*>(p.buffers[dest]) + p.inbox_offset +
+                      strip_offset(p.rank, mb, ni, sidx, p.blocks_per_rank, p.n_tiles_n);
+#pragma unroll
+          for (int j = 0; j < (int)(kStripBytesOne / 16 / 128); ++j) {
+            const int idx = etid + j * 128;              // 16-byte vector of the strip
+            st_16(dst + (size_t)idx * 16, *reinterpret_cast<const Vec16*>(buf + (size_t)idx * 16));
+          }
+        } else {
         fence_proxy_async();                             // generic writes to smem, async-proxy read
         epilogue_sync();
         if (etid == 0) {
@@ -221,6 +237,7 @@ matmul_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           bulk_store(dst, buf, kStripBytesOne);
           bulk_commit_group();
         }
+        }
         ++strip_ctr;
         ++strips;
       }
@@ -228,7 +245,11 @@ matmul_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       tcgen05_fence_before_thread_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
-      if (etid == 0) {
+      if constexpr (kThreadStores) {
+        epilogue_sync();                                 // every thread has issued its stores of this tile
+        if (etid == 0 && strips > 0)
+          red_add_release_sys(p.pads[dest] + kFlagSlotsBase + 2 + mb * p.n_tiles_n + ni, 1u);
+      } else if (etid == 0) {
         if (prev_counter != nullptr) {
           // everything older than this tile's groups has completed
           if (strips == 4) bulk_wait_group<4>();
@@ -342,6 +363,12 @@ int launch_matmul_reduce_scatter(const MatmulRsArgs& a, cudaStream_t stream) {
   if (a.deep_strips) {
     auto kern = matmul_rs_kernel<3, 5>;
     constexpr int smem = (int)RsSmem<3, 5>::kTotal;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    kern<<<grid, kThreads, smem, stream>>>(ta, tb, p);
+  } else if (a.thread_stores && !a.all_reduce) {
+    auto kern = matmul_rs_kernel<4, 2, false, true>;
+    constexpr int smem = (int)RsSmem<4, 2>::kTotal;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     kern<<<grid, kThreads, smem, stream>>>(ta, tb, p);

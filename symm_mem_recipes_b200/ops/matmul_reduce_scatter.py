@@ -44,7 +44,7 @@ def _workspace(M: int, N: int, device: torch.device, group) -> torch.Tensor:
 def matmul_reduce_scatter(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None,
                           group=None, num_sms: int = 0, timeout_ms: int = _TIMEOUT_MS,
                           trace: Optional[torch.Tensor] = None, deep_strips: Optional[bool] = None,
-                          cta_pair: Optional[bool] = None) -> torch.Tensor:
+                          cta_pair: Optional[bool] = None, thread_stores: Optional[bool] = None) -> torch.Tensor:
     """`a` [M, K_local] (all tokens, this rank's slice of the reduction
     dimension), `b` [N, K_local]; returns this rank's [M/WS, N] rows of the sum
     over ranks, bitwise identical to what any other summation site would get
@@ -62,7 +62,12 @@ def matmul_reduce_scatter(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.
     `cta_pair` (default from SMR_RS_CTA_PAIR, off): the main loop on CTA pairs
     (tcgen05 cta_group::2, 256 x 256 tiles, 5 stages, four strips in flight;
     csrc/kernels/matmul_rs_2cta_sm100.cu).  Same inbox layout and the same
-    result bits.  Built, not yet run on a GPU."""
+    result bits.  Built, not yet run on a GPU.
+
+    `thread_stores` (default from SMR_RS_THREAD_STORES, off): the 1-CTA kernel
+    with the epilogue strips copied out of shared memory by coalesced stores of
+    the 128 epilogue threads instead of one bulk store each: no cap on the
+    strips an SM has on the wire.  Same inbox, same bits.  Built, not yet run."""
     if a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[1]:
         raise SymmMemError("need a[M, K] and b[N, K]")
     ws = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -80,8 +85,11 @@ def matmul_reduce_scatter(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.
         deep_strips = os.environ.get("SMR_RS_DEEP_STRIPS", "0") == "1"
     if cta_pair is None:
         cta_pair = os.environ.get("SMR_RS_CTA_PAIR", "0") == "1"
+    if thread_stores is None:
+        thread_stores = os.environ.get("SMR_RS_THREAD_STORES", "0") == "1"
     C.matmul_reduce_scatter(a, b, out, hdl.native, num_sms or _num_sms(a.device),
-                            int(timeout_ms) * 1_000_000, trace, bool(deep_strips), bool(cta_pair))
+                            int(timeout_ms) * 1_000_000, trace, bool(deep_strips), bool(cta_pair),
+                            bool(thread_stores))
     return out
 
 

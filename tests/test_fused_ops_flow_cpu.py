@@ -145,8 +145,8 @@ def _row_parallel_flow_worker(rank, world_size):
 
         @staticmethod
         def matmul_reduce_scatter(a, b, out, workspace, num_sms, timeout_ns, trace=None, deep_strips=False,
-                                  cta_pair=False):
-            seen["rs"] = (deep_strips, cta_pair, workspace.payload_bytes)
+                                  cta_pair=False, thread_stores=False):
+            seen["rs"] = (deep_strips, cta_pair, workspace.payload_bytes, thread_stores)
             rows = out.shape[0]
             out.copy_(summed(a, b)[rank * rows:(rank + 1) * rows].to(out.dtype))
 
@@ -182,6 +182,8 @@ def _row_parallel_flow_worker(rank, world_size):
     assert seen["rs"][:2] == (False, True)
     smr.matmul_reduce_scatter(a, b, deep_strips=True)
     assert seen["rs"][:2] == (True, False)
+    smr.matmul_reduce_scatter(a, b, thread_stores=True)
+    assert seen["rs"][:2] == (False, False) and seen["rs"][3] is True
 
     full = smr.matmul_all_reduce(a, b)                       # internal symmetric output, cached per shape
     assert symm_mem.is_symm_mem_tensor(full) and torch.allclose(full.float(), want, atol=0.02)
@@ -231,7 +233,7 @@ def _install_row_parallel_and_glue_stand_ins():
 
         @staticmethod
         def matmul_reduce_scatter(a, b, out, workspace, num_sms, timeout_ns, trace=None, deep_strips=False,
-                                  cta_pair=False):
+                                  cta_pair=False, thread_stores=False):
             rank, rows = dist.get_rank(), out.shape[0]
             out.copy_(summed(a, b)[rank * rows:(rank + 1) * rows].to(out.dtype))
 

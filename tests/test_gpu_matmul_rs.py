@@ -28,7 +28,7 @@ def _rs_worker(rank, world_size, M, N, K, variant=None):
             # shape (deep_strips) the partials, hence the sums, have the same bits
             plain = smr.matmul_reduce_scatter(a, b)
             symm_mem.check_status(dev)
-            if variant == "deep_strips" and not torch.equal(plain.view(torch.int16), out.view(torch.int16)):
+            if variant in ("deep_strips", "thread_stores") and not torch.equal(plain.view(torch.int16), out.view(torch.int16)):
                 failures.append(f"call {it}: {variant} differs bitwise from the default kernel")
             if not torch.allclose(plain.float(), out.float(), rtol=2.0 ** -6, atol=1e-3):
                 failures.append(f"call {it}: {variant} differs from the default kernel")
@@ -61,7 +61,7 @@ def test_matmul_reduce_scatter_2gpu(M, N, K):
 @pytest.mark.gpu
 @pytest.mark.first_run
 @pytest.mark.multigpu(2)
-@pytest.mark.parametrize("variant", ["cta_pair", "deep_strips"])
+@pytest.mark.parametrize("variant", ["cta_pair", "deep_strips", "thread_stores"])
 @pytest.mark.parametrize("M,N,K", [(256, 256, 128), (768, 328, 192), (4096, 8192, 1024)])
 def test_matmul_reduce_scatter_variants_2gpu(M, N, K, variant):
     spawn_ranks(_rs_worker, 2, "nccl", (M, N, K, variant))
