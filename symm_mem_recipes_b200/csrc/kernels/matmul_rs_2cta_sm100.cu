@@ -43,9 +43,12 @@ struct PairRsSmem {
   static constexpr uint32_t kTotal = kMiscOffset + 16 + 1024;
   static_assert(kStageBytes % 1024 == 0, "stage bases must stay 1024-byte aligned");
 };
-static_assert(PairRsSmem<5, 4>::kTotal <= 232448, "shared memory limit exceeded");
+static_assert(PairRsSmem<5, 4>::kTotal <= 232448 && PairRsSmem<6, 2>::kTotal <= 232448,
+              "shared memory limit exceeded");
 
-template <int kStages, int kNStrips, bool kAllReduce = false>
+// kThreadStores: see matmul_rs_sm100.cu (strips copied out by coalesced stores of the epilogue
+// threads; two strip buffers suffice, which leaves room for a sixth stage).
+template <int kStages, int kNStrips, bool kAllReduce = false, bool kThreadStores = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 matmul_rs_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                       const RsParams p) {
@@ -201,7 +204,9 @@ matmul_rs_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           tmem_ld_32x32b_x32(taddr + (uint32_t)(sidx * kStripCols + 32), v1);
           tmem_ld_wait();
           // the store issued kNStrips strips ago has finished reading the buffer we are about to fill
-          if (etid == 0) bulk_wait_group_read<kNStrips - 1>();
+          if constexpr (!kThreadStores) {
+            if (etid == 0) bulk_wait_group_read<kNStrips - 1>();
+          }
           epilogue_sync();
           uint8_t* buf = strip + (size_t)(strip_ctr % (uint32_t)kNStrips) * kStripBytesOne;
           uint8_t* row = buf + (size_t)r * 128;
@@ -215,6 +220,16 @@ matmul_rs_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             o.w = pack_bf16x2(__uint_as_float(v[6]), __uint_as_float(v[7]));
             *reinterpret_cast<Vec16*>(row + ((c ^ (r & 7)) << 4)) = o;
           }
+          if constexpr (kThreadStores) {
+            epilogue_sync();                               // the strip is complete in shared memory
+            char* dst = static_cast<char*>(p.buffers[dest]) + p.inbox_offset +
+                        strip_offset(p.rank, mb, ni, sidx, p.blocks_per_rank, p.n_tiles_n);
+#pragma unroll
+            for (int j = 0; j < (int)(kStripBytesOne / 16 / 128); ++j) {
+              const int idx = etid + j * 128;              // 16-byte vector of the strip
+              st_16(dst + (size_t)idx * 16, *reinterpret_cast<const Vec16*>(buf + (size_t)idx * 16));
+            }
+          } else {
           fence_proxy_async();                             // generic writes to smem, async-proxy read
           epilogue_sync();
           if (etid == 0) {
@@ -222,6 +237,7 @@ matmul_rs_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                         strip_offset(p.rank, mb, ni, sidx, p.blocks_per_rank, p.n_tiles_n);
             bulk_store(dst, buf, kStripBytesOne);
             bulk_commit_group();
+          }
           }
           ++strip_ctr;
           ++strips;
@@ -231,7 +247,11 @@ matmul_rs_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       tcgen05_fence_before_thread_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc]), 0));
-      if (etid == 0) {
+      if constexpr (kThreadStores) {
+        epilogue_sync();                                 // every thread has issued its stores of this tile
+        if (etid == 0 && strips > 0)
+          red_add_release_sys(p.pads[dest] + kFlagSlotsBase + 2 + mb * p.n_tiles_n + ni, 1u);
+      } else if (etid == 0) {
         if (prev_counter != nullptr) {
           // everything older than this tile's groups has completed
           if (strips == 4) bulk_wait_group<4>();
@@ -341,6 +361,14 @@ int launch_matmul_reduce_scatter_2cta(const MatmulRsArgs& a, cudaStream_t stream
   if (pairs < 1) return cudaErrorInvalidValue;
   const int grid = 2 * pairs;
   if ((uint32_t)(1024 + grid) * (uint32_t)ws > kBlockSlots) return cudaErrorInvalidValue;
+  if (a.thread_stores && !a.all_reduce) {
+    using L6 = PairRsSmem<6, 2>;
+    auto kern = matmul_rs_2cta_kernel<6, 2, false, true>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L6::kTotal);
+    if (e != cudaSuccess) return (int)e;
+    kern<<<grid, kThreads, L6::kTotal, stream>>>(ta, tb, p);
+    return (int)cudaGetLastError();
+  }
   using L = PairRsSmem<5, 4>;
   if (a.all_reduce) {
     auto kern = matmul_rs_2cta_kernel<5, 4, true>;

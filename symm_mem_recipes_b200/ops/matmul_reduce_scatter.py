@@ -64,10 +64,11 @@ def matmul_reduce_scatter(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.
     csrc/kernels/matmul_rs_2cta_sm100.cu).  Same inbox layout and the same
     result bits.  Built, not yet run on a GPU.
 
-    `thread_stores` (default from SMR_RS_THREAD_STORES, off): the 1-CTA kernel
-    with the epilogue strips copied out of shared memory by coalesced stores of
-    the 128 epilogue threads instead of one bulk store each: no cap on the
-    strips an SM has on the wire.  Same inbox, same bits.  Built, not yet run."""
+    `thread_stores` (default from SMR_RS_THREAD_STORES, off): the epilogue
+    strips are copied out of shared memory by coalesced stores of the 128
+    epilogue threads instead of one bulk store each: no cap on the strips an SM
+    has on the wire.  Combines with `cta_pair` (then six operand stages).  Same
+    inbox, same bits.  Built, not yet run."""
     if a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[1]:
         raise SymmMemError("need a[M, K] and b[N, K]")
     ws = dist.get_world_size(group) if dist.is_initialized() else 1

@@ -21,7 +21,7 @@ def _rs_worker(rank, world_size, M, N, K, variant=None):
             b_r = (torch.randn(N, K, generator=gens[r]) * 0.05).to(torch.bfloat16)
             parts.append((a_r, b_r))
         a, b = parts[rank][0].to(dev), parts[rank][1].to(dev)
-        out = smr.matmul_reduce_scatter(a, b, **{variant: True} if variant else {})
+        out = smr.matmul_reduce_scatter(a, b, **({v: True for v in variant.split(",")} if variant else {}))
         symm_mem.check_status(dev)
         if variant:
             # every variant ships bf16 partials and sums them in the same order; with the same MMA
@@ -61,7 +61,7 @@ def test_matmul_reduce_scatter_2gpu(M, N, K):
 @pytest.mark.gpu
 @pytest.mark.first_run
 @pytest.mark.multigpu(2)
-@pytest.mark.parametrize("variant", ["cta_pair", "deep_strips", "thread_stores"])
+@pytest.mark.parametrize("variant", ["cta_pair", "deep_strips", "thread_stores", "cta_pair,thread_stores"])
 @pytest.mark.parametrize("M,N,K", [(256, 256, 128), (768, 328, 192), (4096, 8192, 1024)])
 def test_matmul_reduce_scatter_variants_2gpu(M, N, K, variant):
     spawn_ranks(_rs_worker, 2, "nccl", (M, N, K, variant))
