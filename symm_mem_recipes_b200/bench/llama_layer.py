@@ -36,6 +36,9 @@ def main(argv=None, standalone: bool = True) -> int:
                          "both: time the two; all: also with SiLU-mul inside the gate/up epilogue; "
                          "env: SMR_FUSED_GLUE / SMR_FUSED_SWIGLU")
     ap.add_argument("--breakdown", action="store_true", help="also print the device time of every phase of the layer")
+    ap.add_argument("--rs-variants", default="",
+                    help="comma-separated kernel variants of matmul_reduce_scatter to time besides the default: "
+                         "cta_pair, deep_strips, thread_stores, cta_pair+thread_stores")
     ap.add_argument("--tp", action="store_true",
                     help="also time the prefill without sequence parallelism (replicated activations, "
                          "matmul_all_reduce endings) against cuBLAS + NCCL all-reduce")
@@ -92,6 +95,17 @@ def main(argv=None, standalone: bool = True) -> int:
               "cublas_plus_nccl_us": round(us_r, 1), "cublas_mm_only_us": round(us_mm, 1),
               "fused_tflops": round(flops / us_f / 1e6, 1), "wire_gbs": round(wire / us_f / 1e3, 1),
               "speedup": round(us_r / us_f, 3), "phases": {k: round(v, 1) for k, v in phases.items()}})
+        for variant in [v for v in args.rs_variants.split(",") if v]:
+            kw = {k: True for k in variant.split("+")}
+            got = smr.matmul_reduce_scatter(a, b, **kw)
+            symm_mem.check_status(dev)
+            same = bool(torch.allclose(got.float(), out.float(), rtol=2 ** -6, atol=1e-3))
+            us_v = benchmark_with_event(lambda: smr.matmul_reduce_scatter(a, b, out, **kw), **bench)
+            symm_mem.check_status(dev)
+            emit({"op": "matmul_reduce_scatter_variant", "shape": name, "variant": variant, "world_size": world,
+                  "M": T, "N": cfg.hidden, "K_local": k_local, "matches_default": same, "smr_fused_us": round(us_v, 1),
+                  "cublas_plus_nccl_us": round(us_r, 1), "wire_gbs": round(wire / us_v / 1e3, 1),
+                  "speedup": round(us_r / us_v, 3)})
         del a, b, out, ref
     # ---- whole layer ----
     if not args.skip_layer:

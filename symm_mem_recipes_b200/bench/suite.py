@@ -48,7 +48,9 @@ def main() -> int:
     if "gemv" in only:
         gemv_all_reduce.main(["--out", out("gemv")], standalone=False)
     if "layer" in only:
-        llama_layer.main(["--out", out("layer")] + (["--fused-glue", "all", "--breakdown"] if args.layer_detail
+        llama_layer.main(["--out", out("layer")] + (["--fused-glue", "all", "--breakdown", "--tp", "--rs-variants",
+                                                     "cta_pair,deep_strips,thread_stores,cta_pair+thread_stores"]
+                                                    if args.layer_detail
                                                     else []), standalone=False)
     finish()
     return 0
