@@ -19,8 +19,9 @@ def main() -> int:
     ap.add_argument("--with-reference-triton", action="store_true")
     ap.add_argument("--ar-max-bytes", type=int, default=256 * 1024 * 1024)
     ap.add_argument("--layer-detail", action="store_true",
-                    help="layer benchmark: time it with PyTorch glue and with the single-pass glue kernels, and print "
-                         "the device time of every phase")
+                    help="also time the opt-in kernel variants: the layer with the single-pass glue kernels and the "
+                         "SwiGLU epilogue, its phases, the prefill without sequence parallelism, the reduce-scatter "
+                         "variants, the tagged GEMV exchange")
     args = ap.parse_args()
     from symm_mem_recipes_b200.bench import (all_gather_matmul, all_reduce, barrier, gemv_all_reduce,
                                              llama_layer)
@@ -46,7 +47,8 @@ def main() -> int:
     if "upstream_table" in only:         # not in the default list: nine shapes, a few minutes
         all_gather_matmul.main(["--upstream-table", "--out", out("agmm_table")], standalone=False)
     if "gemv" in only:
-        gemv_all_reduce.main(["--out", out("gemv")], standalone=False)
+        gemv_all_reduce.main(["--out", out("gemv")] + (["--extra-algos", "tc_tagged"] if args.layer_detail else []),
+                             standalone=False)
     if "layer" in only:
         llama_layer.main(["--out", out("layer")] + (["--fused-glue", "all", "--breakdown", "--tp", "--rs-variants",
                                                      "cta_pair,deep_strips,thread_stores,cta_pair+thread_stores"]
