@@ -35,7 +35,8 @@ def main(argv=None, standalone: bool = True) -> int:
                     help="graph: CUDA-graph replay (device time per call) up to --graph-limit bytes")
     ap.add_argument("--graph-limit", type=int, default=4 * 1024 * 1024)
     ap.add_argument("--out", default=None, help="also append the JSON lines to this file")
-    ap.add_argument("--multimem-blocks", type=int, default=0, help="CTAs of the multimem kernel (0: configured default)")
+    ap.add_argument("--multimem-blocks", type=int, default=0,
+                    help="CTAs of the multimem kernel (0: configured default)")
     ap.add_argument("--multimem-unroll", type=int, default=0, help="4, 8 or 16 reductions in flight per thread")
     ap.add_argument("--nvls-barrier", action="store_true", help="multimem kernel: barriers by multimem.red")
     ap.add_argument("--multimem-sweep", action="store_true",

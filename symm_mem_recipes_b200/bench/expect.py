@@ -38,7 +38,8 @@ def expect(op: str, ws: int, peaks: dict, M: int = 0, N: int = 0, K: int = 0, ba
         parts["nvlink_in_us"] = _us((ws - 1) / ws * M * K * 2.0, link)      # the remote shards arrive once
     elif op == "matmul_reduce_scatter":      # K = this rank's slice of the reduction dimension
         parts["tensor_us"] = _us(2.0 * M * N * K, tflops)
-        parts["hbm_us"] = _us((M * K + N * K) * 2.0 + 2.0 * (M * N * 2.0), hbm)   # operands; partials land and are re-read
+        # operands once; the bf16 partials land in the inboxes and are read back by the reduction
+        parts["hbm_us"] = _us((M * K + N * K) * 2.0 + 2.0 * (M * N * 2.0), hbm)
         parts["nvlink_out_us"] = _us((ws - 1) / ws * M * N * 2.0, link)     # bf16 partials to their owners
     elif op == "gemv_all_reduce":            # W [K, N] per rank is streamed once
         parts["hbm_us"] = _us(K * N * 2.0, hbm)

@@ -129,7 +129,8 @@ def main(argv=None, standalone: bool = True) -> int:
                 us_r = benchmark_with_event(lambda: layer.forward_reference(x, args.batch, args.seq), **bench)
             symm_mem.check_status(dev)
             emit({"op": "llama70b_layer_prefill", "world_size": world, "batch": args.batch, "seq": args.seq,
-                  "fused_glue": layer.fused_glue, "fused_swiglu": layer.fused_swiglu, "matches_library": ok, "max_rel_diff": round(rel, 5),
+                  "fused_glue": layer.fused_glue, "fused_swiglu": layer.fused_swiglu, "matches_library": ok,
+                  "max_rel_diff": round(rel, 5),
                   "smr_fused_us": round(us_f, 1), "nccl_cublas_us": round(us_r, 1),
                   "tokens_per_s_fused": round(T / us_f * 1e6), "speedup": round(us_r / us_f, 3)})
             if args.breakdown:

@@ -105,7 +105,8 @@ def ag_matmul_table(recs: list[dict], peaks: Optional[dict]) -> Optional[str]:
             continue
         name = r["impl"]
         if name == "smr_fused":
-            name = f"smr_fused ({r.get('gather', 'push')}" + (f", {r['copy_ctas']} copy CTAs)" if "copy_ctas" in r else ")")
+            copiers = f", {r['copy_ctas']} copy CTAs" if "copy_ctas" in r else ""
+            name = f"smr_fused ({r.get('gather', 'push')}{copiers})"
         groups.setdefault((r["world_size"], r["M"], r["N"], r["K"]), {})[name] = r
     if not groups:
         return None

@@ -441,7 +441,8 @@ def reset() -> None:
     # workspaces the ops keep per (shape, group): they point into released allocations
     import importlib
     for mod, names in (("ag_matmul", ("_gather_buffers",)), ("all_reduce", ("_ll_workspaces",)),
-                       ("gemv_all_reduce", ("_workspaces",)), ("matmul_reduce_scatter", ("_workspaces", "_ar_outputs"))):
+                       ("gemv_all_reduce", ("_workspaces",)),
+                       ("matmul_reduce_scatter", ("_workspaces", "_ar_outputs"))):
         m = importlib.import_module(f"symm_mem_recipes_b200.ops.{mod}")
         for name in names:
             getattr(m, name).clear()

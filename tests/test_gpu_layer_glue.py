@@ -38,7 +38,8 @@ def test_rms_norm(rows, H):
     assert ok, err
 
 
-@pytest.mark.parametrize("batch,seq,hq,hkv,D,pos0", [(2, 24, 4, 1, 64, 0), (1, 2048, 8, 1, 128, 0), (4, 1, 8, 1, 128, 1777)])
+@pytest.mark.parametrize("batch,seq,hq,hkv,D,pos0",
+                         [(2, 24, 4, 1, 64, 0), (1, 2048, 8, 1, 128, 0), (4, 1, 8, 1, 128, 1777)])
 def test_rope(batch, seq, hq, hkv, D, pos0):
     from symm_mem_recipes_b200 import ops
     from symm_mem_recipes_b200._ext import C

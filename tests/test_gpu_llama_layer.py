@@ -100,7 +100,8 @@ def _layer_tp_worker(rank, world_size, fused_glue, fused_swiglu):
         symm_mem.check_status(dev)
         y_tp_lib = layer.forward_tp_reference(x, batch, seq)
         if not torch.allclose(y_tp.float(), y_tp_lib.float(), rtol=5e-2, atol=5e-2):
-            failures.append(f"call {it}: TP prefill vs cuBLAS + NCCL: {(y_tp.float() - y_tp_lib.float()).abs().max().item()}")
+            worst = (y_tp.float() - y_tp_lib.float()).abs().max().item()
+            failures.append(f"call {it}: TP prefill vs cuBLAS + NCCL: {worst}")
         y_sp = layer.forward(x[rank * rows:(rank + 1) * rows].contiguous(), batch, seq)
         symm_mem.check_status(dev)
         if not torch.allclose(y_sp.float(), y_tp_lib[rank * rows:(rank + 1) * rows].float(), rtol=5e-2, atol=5e-2):

@@ -28,7 +28,8 @@ def _rs_worker(rank, world_size, M, N, K, variant=None):
             # shape (deep_strips) the partials, hence the sums, have the same bits
             plain = smr.matmul_reduce_scatter(a, b)
             symm_mem.check_status(dev)
-            if variant in ("deep_strips", "thread_stores") and not torch.equal(plain.view(torch.int16), out.view(torch.int16)):
+            same_bits = torch.equal(plain.view(torch.int16), out.view(torch.int16))
+            if variant in ("deep_strips", "thread_stores") and not same_bits:
                 failures.append(f"call {it}: {variant} differs bitwise from the default kernel")
             if not torch.allclose(plain.float(), out.float(), rtol=2.0 ** -6, atol=1e-3):
                 failures.append(f"call {it}: {variant} differs from the default kernel")

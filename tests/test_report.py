@@ -11,11 +11,15 @@ LINES = [
     '{"op": "all_reduce", "impl": "auto:low_latency", "world_size": 8, "bytes": 4096, "timing": "graph", "us": 5.5}',
     '{"op": "all_reduce", "impl": "nccl", "world_size": 8, "bytes": 67108864, "timing": "event", "us": 279.04}',
     '{"op": "all_reduce", "impl": "multimem", "world_size": 8, "bytes": 67108864, "timing": "event", "us": 166.38}',
-    '{"op": "all_gather_matmul", "impl": "cublas_plus_nccl", "world_size": 8, "M": 16384, "N": 3584, "K": 8192, "us": 1341.5}',
-    '{"op": "all_gather_matmul", "impl": "smr_fused", "world_size": 8, "M": 16384, "N": 3584, "K": 8192, "us": 772.1, "gather": "push"}',
+    '{"op": "all_gather_matmul", "impl": "cublas_plus_nccl", "world_size": 8, "M": 16384,'
+    ' "N": 3584, "K": 8192, "us": 1341.5}',
+    '{"op": "all_gather_matmul", "impl": "smr_fused", "world_size": 8, "M": 16384, "N": 3584,'
+    ' "K": 8192, "us": 772.1, "gather": "push"}',
     '{"op": "gemv_all_reduce", "impl": "smr_fused", "world_size": 8, "batch": 1, "K": 3584, "N": 8192, "us": 22.6}',
-    '{"op": "gemv_all_reduce", "impl": "cublas_plus_nccl", "world_size": 8, "batch": 1, "K": 3584, "N": 8192, "us": 39.52}',
-    '{"op": "llama70b_layer_decode", "world_size": 8, "batch": 1, "smr_fused_us": 197.2, "nccl_cublas_us": 237.6, "speedup": 1.205}',
+    '{"op": "gemv_all_reduce", "impl": "cublas_plus_nccl", "world_size": 8, "batch": 1, "K": 3584,'
+    ' "N": 8192, "us": 39.52}',
+    '{"op": "llama70b_layer_decode", "world_size": 8, "batch": 1, "smr_fused_us": 197.2,'
+    ' "nccl_cublas_us": 237.6, "speedup": 1.205}',
     '{"truncated": ',
 ]
 PEAKS = {"bf16_tflops": 1647.3, "bf16_tflops_sustained": 1411.0, "hbm_gbs": 6541.5}
@@ -66,7 +70,8 @@ def test_all_reduce_thresholds_from_a_sweep(tmp_path, monkeypatch):
         # 4 KiB, 8 KiB: low_latency wins; 16 KiB: one_shot wins; 32 KiB on: multimem wins
         rec("nccl", 4096, 1.0), rec("low_latency", 4096, 5), rec("one_shot", 4096, 12), rec("multimem", 4096, 10),
         rec("low_latency", 8192, 6), rec("one_shot", 8192, 12), rec("multimem", 8192, 10),
-        rec("low_latency", 16384, 14), rec("one_shot", 16384, 9), rec("two_shot", 16384, 13), rec("multimem", 16384, 10),
+        rec("low_latency", 16384, 14), rec("one_shot", 16384, 9), rec("two_shot", 16384, 13),
+        rec("multimem", 16384, 10),
         rec("one_shot", 32768, 20), rec("multimem", 32768, 11),
         rec("low_latency", 65536, 1), rec("multimem", 65536, 12),     # past the break: must not reopen the range
         rec("low_latency", 4096, 5, ws=2), rec("two_shot", 4096, 9, ws=2),
