@@ -204,7 +204,9 @@ def all_gather_matmul(a_shard: torch.Tensor, b: torch.Tensor, a_out: Optional[to
         symmetric buffer, see `gather_buffer`): every rank broadcasts its own
         shard through the NVSwitch (push).  This is the fast path.
       * `a_out` an ordinary tensor, as in the upstream API: `a_shard` must be
-        in symmetric memory and the kernel pulls the peers' shards.
+        in symmetric memory and the kernel pulls the peers' shards
+        (`config.plain_a_out = "push_copy"` instead gathers by push into the
+        internal buffer and copies it into `a_out`).
 
     `mm_only=True` skips the gather and multiplies `a_out` (or `a_shard` when
     no `a_out` is given) as it is, to time the GEMM alone.
