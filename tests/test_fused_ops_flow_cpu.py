@@ -297,3 +297,77 @@ def _layer_flow_worker(rank, world_size, fused_glue, fused_swiglu):
 @pytest.mark.parametrize("fused_glue,fused_swiglu", [(False, False), (True, True)])
 def test_decoder_layer_host_flow_two_ranks(fused_glue, fused_swiglu):
     spawn_ranks(_layer_flow_worker, 2, "gloo", (fused_glue, fused_swiglu))
+
+
+def _selfcheck_worker(rank, world_size):
+    """The self-check program's own logic (shapes, references, outcome agreement) with host
+    stand-ins for the kernels: a wrong reference there would cost GPU time to find."""
+    import importlib
+
+    import torch.distributed as dist
+
+    from symm_mem_recipes_b200 import selfcheck
+    from symm_mem_recipes_b200._ext import C as real
+    from symm_mem_recipes_b200.parallel import symm_mem
+
+    _install_host_kernels()
+    _install_row_parallel_and_glue_stand_ins()
+    ag_mod = importlib.import_module("symm_mem_recipes_b200.ops.ag_matmul")
+    gemv_mod = importlib.import_module("symm_mem_recipes_b200.ops.gemv_all_reduce")
+    push_fake = ag_mod.C
+
+    class AgFake:                                     # adds the pull mode to the push / plain stand-in
+        def __getattr__(self, name):
+            return getattr(push_fake, name)
+
+        @staticmethod
+        def ag_matmul(a, b, c, mode, shard_alloc, shard_offset, *rest, **kw):
+            if mode != 1:
+                return push_fake.ag_matmul(a, b, c, mode, shard_alloc, shard_offset, *rest, **kw)
+            a_out = rest[2]
+            rows, K = a.shape
+            dist.barrier()
+            for r in range(dist.get_world_size()):
+                a_out[r * rows:(r + 1) * rows].copy_(real.host_view(shard_alloc, r, [rows, K], a.dtype, shard_offset))
+            dist.barrier()
+            c.copy_((a_out.float() @ b.float().t()).to(c.dtype))
+
+    ag_mod.C = AgFake()
+
+    class GemvFake:
+        def __getattr__(self, name):
+            return getattr(real, name)
+
+        @staticmethod
+        def gemv_all_reduce(x, w, out, workspace, ws_offset, timeout_ns, tensor_core=False, num_sms=148, tagged=False):
+            part = x.float() @ w.float()
+            dist.all_reduce(part)
+            out.copy_(part.to(out.dtype))
+
+    gemv_mod.C = GemvFake()
+    gemv_mod._num_sms = lambda device: 148
+    symm_mem.check_status = lambda device=None: None
+
+    def reduce_scatter_by_all_reduce(out, inp, group=None):       # gloo has no reduce_scatter_tensor
+        full = inp.float()
+        dist.all_reduce(full, group=group)
+        rows = out.shape[0]
+        out.copy_(full[dist.get_rank() * rows:(dist.get_rank() + 1) * rows].to(out.dtype))
+
+    dist.reduce_scatter_tensor = reduce_scatter_by_all_reduce
+
+    failures, ran = [], 0
+    for group, name, pending, fn in selfcheck.build_checks(True, world_size, rank, torch.device("cpu")):
+        if (group == "barrier" and "barrier" in name.lower()) or "NVLS" in name:
+            continue                                   # barrier_test kernels exist on the GPU only
+        ok, detail = fn()
+        ran += 1
+        if not ok:
+            failures.append(f"{group}: {name}: {detail}")
+        dist.barrier()
+    assert not failures, failures
+    assert ran >= 30, ran
+
+
+def test_selfcheck_logic_two_ranks():
+    spawn_ranks(_selfcheck_worker, 2, "gloo")
