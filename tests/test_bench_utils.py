@@ -133,3 +133,20 @@ def test_spawn_ranks_gives_up_on_a_hung_rank_and_lets_it_tear_down():
     # was up far enough to have installed the handler); the parent did not wait for the full join
     assert "did not finish" in str(e.value)
     assert time.monotonic() - t0 < 25.0 + 60.0
+
+
+def test_build_targets_sm_100a_only_and_covers_every_source():
+    from symm_mem_recipes_b200 import _build
+
+    flags = " ".join(_build.NVCC_FLAGS)
+    assert "arch=compute_100a,code=sm_100a" in flags and "-lineinfo" in flags
+    assert flags.count("-gencode") == 1                      # one architecture, no fallback targets
+    cu, cpp = _build.sources()
+    names = {p.name for p in cu}
+    for must in ("all_reduce.cu", "ag_matmul_2cta_sm100.cu", "ag_matmul_sm100.cu", "gemv_allreduce_tc.cu",
+                 "matmul_rs_sm100.cu", "matmul_rs_2cta_sm100.cu", "layer_glue.cu"):
+        assert must in names, must
+    ninja = _build.write_ninja().read_text()
+    for src in cu + cpp:
+        assert str(src) in ninja
+    assert str(_build.so_path()) in ninja
