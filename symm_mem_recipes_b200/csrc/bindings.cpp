@@ -556,13 +556,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   }, py::arg("N"), py::arg("K"), py::arg("world_size"), py::arg("num_sms"), py::arg("tagged") = false);
   m.def("gemv_all_reduce", [](torch::Tensor x, torch::Tensor w, torch::Tensor out,
                               const std::shared_ptr<CudaSymmAllocation>& workspace, int64_t ws_offset,
-                              uint64_t timeout_ns, bool tensor_core, int num_sms, bool tagged) {
+                              uint64_t timeout_ns, bool tensor_core, int num_sms, bool tagged, bool weights_nk) {
     auto ok2d = [](const torch::Tensor& t) {
       return t.is_cuda() && t.dim() == 2 && t.is_contiguous() && t.scalar_type() == torch::kBFloat16;
     };
     TORCH_CHECK(ok2d(x) && ok2d(w) && ok2d(out), "x, w, out must be contiguous 2-D bf16 CUDA tensors");
-    TORCH_CHECK(x.size(1) == w.size(0) && out.size(0) == x.size(0) && out.size(1) == w.size(1),
-                "need x[B, K], w[K, N], out[B, N]");
+    TORCH_CHECK(!weights_nk || tensor_core, "weights stored [N, K] are read by the tcgen05 kernel only");
+    const int64_t w_k = weights_nk ? w.size(1) : w.size(0), w_n = weights_nk ? w.size(0) : w.size(1);
+    TORCH_CHECK(x.size(1) == w_k && out.size(0) == x.size(0) && out.size(1) == w_n,
+                "need x[B, K], w[K, N] (or [N, K] with weights_nk), out[B, N]");
     int dev = x.get_device();
     c10::cuda::CUDAGuard guard(dev);
     GemvArgs args{};
@@ -571,7 +573,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     args.out = out.data_ptr();
     args.batch = (int)x.size(0);
     args.K = (int)x.size(1);
-    args.N = (int)w.size(1);
+    args.N = (int)w_n;
     args.pv = view_of(*workspace);
     args.ws_offset = (size_t)ws_offset;
     args.timeout_ns = timeout_ns;
@@ -582,14 +584,16 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     if (tensor_core) {
       TORCH_CHECK(gemv_tc_workspace_bytes(args.N, args.K, args.pv.world_size, num_sms, nullptr, nullptr, nullptr,
                                           nullptr, tagged) <= workspace->payload_bytes(), "workspace too small");
-      rt_check(launch_gemv_all_reduce_tc(args, num_sms, current_stream(dev), tagged), "gemv_all_reduce (tcgen05)");
+      rt_check(launch_gemv_all_reduce_tc(args, num_sms, current_stream(dev), tagged, weights_nk),
+               "gemv_all_reduce (tcgen05)");
       return;
     }
     TORCH_CHECK(gemv_workspace_bytes(bt, args.N, args.pv.world_size, nullptr, nullptr, nullptr) + (size_t)ws_offset
                     <= workspace->payload_bytes(), "workspace too small");
     rt_check(launch_gemv_all_reduce(args, current_stream(dev)), "gemv_all_reduce");
   }, py::arg("x"), py::arg("w"), py::arg("out"), py::arg("workspace"), py::arg("ws_offset"),
-     py::arg("timeout_ns"), py::arg("tensor_core") = false, py::arg("num_sms") = 148, py::arg("tagged") = false);
+     py::arg("timeout_ns"), py::arg("tensor_core") = false, py::arg("num_sms") = 148, py::arg("tagged") = false,
+     py::arg("weights_nk") = false);
 
   m.def("matmul_rs_workspace_bytes", &matmul_rs_workspace_bytes);
   m.def("matmul_reduce_scatter", [](torch::Tensor a, torch::Tensor b, torch::Tensor out,

@@ -98,7 +98,10 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)
 
 __device__ __forceinline__ void group_sync_128() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
-template <bool kTagged>
+// kWeightsNK: W is stored [N, K] (K contiguous), the layout the prefill GEMMs use, so that one
+// copy of a row-parallel weight serves prefill and decode.  The A operand is then K-major: one
+// [128 n x 64 k] TMA box per stage and the K-major descriptor of the GEMM kernels.
+template <bool kTagged, bool kWeightsNK = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemv_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                const GemvTcParams p) {
@@ -162,8 +165,12 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         }
         uint8_t* sw = smem + (size_t)stage * kStageBytes;
         mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
-        tma_load_2d(sw, &tmap_w, &full_bar[stage], n0, kb * kBK);               // n 0..63
-        tma_load_2d(sw + 8192, &tmap_w, &full_bar[stage], n0 + 64, kb * kBK);   // n 64..127
+        if constexpr (kWeightsNK) {
+          tma_load_2d(sw, &tmap_w, &full_bar[stage], kb * kBK, n0);             // [128 n x 64 k], 16 KB
+        } else {
+          tma_load_2d(sw, &tmap_w, &full_bar[stage], n0, kb * kBK);               // n 0..63
+          tma_load_2d(sw + 8192, &tmap_w, &full_bar[stage], n0 + 64, kb * kBK);   // n 64..127
+        }
         tma_load_2d(sw + kWBytes, &tmap_x, &full_bar[stage], kb * kBK, 0);
         if (++stage == kStages) { stage = 0; phase ^= 1; }
       }
@@ -171,7 +178,7 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   } else if (warp == 1) {
     if (lane == 0) {
       // kind::f16, bf16 x bf16 -> fp32, A MN-major (bit 15), B K-major, M = 128, N = 16
-      constexpr uint32_t idesc = umma_idesc_bf16_f32(kTileN, kBatchN) | (1u << 15);
+      constexpr uint32_t idesc = umma_idesc_bf16_f32(kTileN, kBatchN) | (kWeightsNK ? 0u : (1u << 15));
       uint32_t stage = 0, phase = 0;
       for (int i = 0; i < n_kb; ++i) {
         if (!mbar_wait(&full_bar[stage], phase, p.timeout_ns)) {
@@ -181,13 +188,13 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         }
         tcgen05_fence_after_thread_sync();
         const uint32_t sw = smem_u32(smem + (size_t)stage * kStageBytes);
-        const uint64_t da = umma_smem_desc_mn_sw128(sw);
+        const uint64_t da = kWeightsNK ? umma_smem_desc_sw128(sw) : umma_smem_desc_mn_sw128(sw);
         const uint64_t db = umma_smem_desc_sw128(sw + kWBytes);
 #pragma unroll
         for (int k = 0; k < kBK / kUmmaK; ++k) {
-          // A: +16 k rows = +2048 B; B: +16 k elements inside the 128-byte row = +32 B
-          umma_bf16_ss(tmem_base, da + (uint64_t)(k * (2048 >> 4)), db + (uint64_t)(2 * k), idesc,
-                       (i | k) != 0 ? 1u : 0u);
+          // A, MN-major: +16 k rows = +2048 B; A, K-major and B: +16 k elements inside the 128-byte row = +32 B
+          const uint64_t a_step = kWeightsNK ? (uint64_t)(2 * k) : (uint64_t)(k * (2048 >> 4));
+          umma_bf16_ss(tmem_base, da + a_step, db + (uint64_t)(2 * k), idesc, (i | k) != 0 ? 1u : 0u);
         }
         umma_commit(&empty_bar[stage]);
         if (++stage == kStages) { stage = 0; phase ^= 1; }
@@ -395,7 +402,7 @@ size_t gemv_tc_workspace_bytes(int N, int K, int world_size, int num_sms, size_t
   return inbox_off + inbox_bytes;
 }
 
-int launch_gemv_all_reduce_tc(const GemvArgs& a, int num_sms, cudaStream_t stream, bool tagged) {
+int launch_gemv_all_reduce_tc(const GemvArgs& a, int num_sms, cudaStream_t stream, bool tagged, bool weights_nk) {
   if (a.batch < 1 || a.batch > kBatchN || a.N % 8 != 0 || a.K % 8 != 0 || a.ws_offset != 0)
     return cudaErrorInvalidValue;
   GemvTcParams p{};
@@ -409,8 +416,26 @@ int launch_gemv_all_reduce_tc(const GemvArgs& a, int num_sms, cudaStream_t strea
                           &p.ksplit, tagged);
   if (p.world_size * p.ksplit > kFlagStride) return cudaErrorInvalidValue;
   CUtensorMap tw, tx;
-  if (encode(&tw, a.w, (uint64_t)a.N, (uint64_t)a.K, 64, kBK)) return cudaErrorInvalidValue;
+  if (weights_nk) {
+    if (encode(&tw, a.w, (uint64_t)a.K, (uint64_t)a.N, kBK, kTileN)) return cudaErrorInvalidValue;   // [N, K]
+  } else {
+    if (encode(&tw, a.w, (uint64_t)a.N, (uint64_t)a.K, 64, kBK)) return cudaErrorInvalidValue;       // [K, N]
+  }
   if (encode(&tx, a.x, (uint64_t)a.K, (uint64_t)a.batch, kBK, kBatchN)) return cudaErrorInvalidValue;
+  if (weights_nk) {
+    if (tagged) {
+      cudaError_t e = cudaFuncSetAttribute(gemv_tc_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)kSmemTotal);
+      if (e != cudaSuccess) return (int)e;
+      gemv_tc_kernel<true, true><<<p.tiles * p.ksplit, kThreads, kSmemTotal, stream>>>(tw, tx, p);
+    } else {
+      cudaError_t e = cudaFuncSetAttribute(gemv_tc_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)kSmemTotal);
+      if (e != cudaSuccess) return (int)e;
+      gemv_tc_kernel<false, true><<<p.tiles * p.ksplit, kThreads, kSmemTotal, stream>>>(tw, tx, p);
+    }
+    return (int)cudaGetLastError();
+  }
   if (tagged) {
     cudaError_t e = cudaFuncSetAttribute(gemv_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)kSmemTotal);

@@ -115,7 +115,7 @@ int check_rs_pair_schedule(int world_size, int rank, int blocks_per_rank, int n_
 // ---- fused GEMV + all-reduce (decode) -------------------------------------
 struct GemvArgs {
   const void* x;      // [batch, K] bf16, batch <= 16
-  const void* w;      // [K, N] bf16
+  const void* w;      // [K, N] bf16 ([N, K] for the tcgen05 kernel with weights_nk)
   void* out;          // [batch, N] bf16
   int batch, K, N;
   PeerView pv;        // of the symmetric workspace
@@ -133,7 +133,9 @@ int launch_gemv_all_reduce(const GemvArgs& args, cudaStream_t stream);
 // release fence); twice the inbox.  Meant for batch <= 4.
 size_t gemv_tc_workspace_bytes(int N, int K, int world_size, int num_sms, size_t* flags_offset,
                                size_t* inbox_offset, int* tiles, int* ksplit, bool tagged = false);
-int launch_gemv_all_reduce_tc(const GemvArgs& args, int num_sms, cudaStream_t stream, bool tagged = false);
+// `weights_nk`: `args.w` is [N, K] (K contiguous), the layout of the prefill GEMMs' B operand.
+int launch_gemv_all_reduce_tc(const GemvArgs& args, int num_sms, cudaStream_t stream, bool tagged = false,
+                              bool weights_nk = false);
 
 // ---- fused GEMM + reduce-scatter (prefill, row-parallel linear) --------------
 struct MatmulRsArgs {

@@ -87,7 +87,7 @@ class LlamaTPDecoderLayer:
 
     def __init__(self, cfg: LlamaTPConfig, device: torch.device, group=None, seed: int = 0,
                  dtype: torch.dtype = torch.bfloat16, fused_glue: Optional[bool] = None,
-                 fused_swiglu: Optional[bool] = None):
+                 fused_swiglu: Optional[bool] = None, shared_row_weights: Optional[bool] = None):
         self.cfg, self.device, self.group = cfg, device, group
         self.fused_glue = (os.environ.get("SMR_FUSED_GLUE", "0") == "1") if fused_glue is None else bool(fused_glue)
         # SiLU(gate) * up inside the epilogue of the gate/up all_gather_matmul (prefill only)
@@ -110,9 +110,13 @@ class LlamaTPDecoderLayer:
         self.w_o = w(H, self.hq * D)
         self.w_gate_up = w(2 * self.ffn_local, H)
         self.w_down = w(H, self.ffn_local)
-        # decode path wants [K_local, N] (weights streamed row by row)
-        self.w_o_t = self.w_o.t().contiguous()
-        self.w_down_t = self.w_down.t().contiguous()
+        # The decode GEMV streams [K_local, N] weights by default, which costs a transposed copy of the
+        # two row-parallel weights; `shared_row_weights` (SMR_GEMV_WEIGHTS_NK=1) lets it read the [N, K_local]
+        # layout of the prefill GEMMs instead: one copy serves both.
+        self.shared_row_weights = ((os.environ.get("SMR_GEMV_WEIGHTS_NK", "0") == "1") if shared_row_weights is None
+                                   else bool(shared_row_weights))
+        self.w_o_t = None if self.shared_row_weights else self.w_o.t().contiguous()
+        self.w_down_t = None if self.shared_row_weights else self.w_down.t().contiguous()
         self.w_gate_up_interleaved = None
         if self.fused_swiglu:
             if self.ffn_local % 128:
@@ -298,10 +302,12 @@ class LlamaTPDecoderLayer:
         cfg = self.cfg
         B, D, hq, hkv = x.shape[0], cfg.head_dim, self.hq, self.hkv
 
-        def row_parallel(act, w_t):
+        nk = self.shared_row_weights
+
+        def row_parallel(act, w):               # w: [K_local, N], or [N, K_local] with shared_row_weights
             if fused and self.ws > 1:
-                return ops.gemv_all_reduce(act, w_t, group=self.group)
-            return ops.reference_gemv_all_reduce(act, w_t, group=self.group)
+                return ops.gemv_all_reduce(act, w, group=self.group, weights_nk=nk)
+            return ops.reference_gemv_all_reduce(act, w, group=self.group, weights_nk=nk)
 
         glue = fused and self.fused_glue
         norm = (lambda t, w: ops.rms_norm(t, w, cfg.eps)) if glue else (lambda t, w: _rms_norm(t, w, cfg.eps))
@@ -317,10 +323,10 @@ class LlamaTPDecoderLayer:
         v_cache[:, pos] = v.view(B, hkv, D)
         o = F.scaled_dot_product_attention(q.transpose(1, 2), k_cache[:, : pos + 1].transpose(1, 2),
                                            v_cache[:, : pos + 1].transpose(1, 2), enable_gqa=True)
-        x1 = x + row_parallel(o.transpose(1, 2).reshape(B, hq * D).contiguous(), self.w_o_t)
+        x1 = x + row_parallel(o.transpose(1, 2).reshape(B, hq * D).contiguous(), self.w_o if nk else self.w_o_t)
         gu = norm(x1, self.norm2) @ self.w_gate_up.t()
         act = ops.silu_mul(gu) if glue else LlamaTPDecoderLayer._mlp_act_torch(gu, self.ffn_local)
-        return x1 + row_parallel(act, self.w_down_t)
+        return x1 + row_parallel(act, self.w_down if nk else self.w_down_t)
 
 
 def full_precision_reference(layers_weights: list, cfg: LlamaTPConfig, x: torch.Tensor, batch: int,

@@ -47,7 +47,8 @@ def _workspace(batch_tile: int, N: int, K: int, device: torch.device, group, ten
 
 @traced("smr.gemv_all_reduce")
 def gemv_all_reduce(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
-                    group=None, timeout_ms: int = _TIMEOUT_MS, algo: Optional[str] = None) -> torch.Tensor:
+                    group=None, timeout_ms: int = _TIMEOUT_MS, algo: Optional[str] = None,
+                    weights_nk: bool = False) -> torch.Tensor:
     """`x` [B, K] and `w` [K, N] are this rank's (ordinary) tensors; returns the
     all-reduced [B, N] in bf16, bitwise identical on every rank.
 
@@ -55,10 +56,15 @@ def gemv_all_reduce(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor
     "simt" = CUDA-core kernel; "tc_tagged" = the tcgen05 kernel exchanging its
     partials as {value, call number} words that the reducer polls directly
     (no flags, no release fence; meant for batch <= 4; built, not yet run on a
-    GPU).  Default from SMR_GEMV_ALGO, else "tc"."""
-    if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[0]:
-        raise SymmMemError("need x[B, K] and w[K, N]")
-    B, N = x.shape[0], w.shape[1]
+    GPU).  Default from SMR_GEMV_ALGO, else "tc".
+
+    `weights_nk=True`: `w` is [N, K] (K contiguous), the layout
+    `matmul_reduce_scatter` takes, so that one copy of a row-parallel weight
+    serves prefill and decode (tcgen05 kernels only; built, not yet run)."""
+    k_dim, n_dim = (1, 0) if weights_nk else (0, 1)
+    if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[k_dim]:
+        raise SymmMemError("need x[B, K] and w[K, N]" + (" given as [N, K]" if weights_nk else ""))
+    B, N = x.shape[0], w.shape[n_dim]
     if not 1 <= B <= 16:
         raise SymmMemError("batch must be between 1 and 16 (decode); use matmul_reduce_scatter for prefill")
     if N % 8:
@@ -72,17 +78,21 @@ def gemv_all_reduce(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor
         raise SymmMemError("the tcgen05 kernels need K to be a multiple of 8")
     tagged = algo == "tc_tagged"
     tensor_core = algo != "simt" and x.shape[1] % 8 == 0
+    if weights_nk and not tensor_core:
+        raise SymmMemError("weights_nk needs one of the tcgen05 kernels (K a multiple of 8)")
     sms = _num_sms(x.device)
     bt = 16 if tensor_core else C.gemv_batch_tile(B)
     wsp = _workspace(bt, N, x.shape[1], x.device, group, tensor_core, sms, tagged)
     hdl = symm_mem.rendezvous(wsp, group)
-    C.gemv_all_reduce(x.contiguous(), w, out, hdl.native, 0, int(timeout_ms) * 1_000_000, tensor_core, sms, tagged)
+    C.gemv_all_reduce(x.contiguous(), w, out, hdl.native, 0, int(timeout_ms) * 1_000_000, tensor_core, sms, tagged,
+                      bool(weights_nk))
     return out
 
 
-def reference_gemv_all_reduce(x: torch.Tensor, w: torch.Tensor, group=None) -> torch.Tensor:
+def reference_gemv_all_reduce(x: torch.Tensor, w: torch.Tensor, group=None,
+                              weights_nk: bool = False) -> torch.Tensor:
     """Library baseline: cuBLAS GEMM, then NCCL all-reduce (bf16)."""
-    y = torch.matmul(x, w)
+    y = torch.matmul(x, w.t() if weights_nk else w)
     if dist.is_initialized() and dist.get_world_size(group) > 1:
         dist.all_reduce(y, group=group)
     return y

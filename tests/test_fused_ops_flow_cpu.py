@@ -158,9 +158,10 @@ def _row_parallel_flow_worker(rank, world_size):
 
         @staticmethod
         def gemv_all_reduce(x, w, out, workspace, ws_offset, timeout_ns, tensor_core=False, num_sms=148,
-                            tagged=False):
+                            tagged=False, weights_nk=False):
             seen["gemv"] = (tensor_core, tagged)
-            part = x.float() @ w.float()
+            seen["gemv_nk"] = weights_nk
+            part = x.float() @ (w.float().t() if weights_nk else w.float())
             dist.all_reduce(part)
             out.copy_(part.to(out.dtype))
 
@@ -201,6 +202,10 @@ def _row_parallel_flow_worker(rank, world_size):
     assert seen["gemv"] == (True, True)
     smr.gemv_all_reduce(x, w, algo="simt")
     assert seen["gemv"] == (False, False)
+    y_nk = smr.gemv_all_reduce(x, w.t().contiguous(), weights_nk=True)       # [N, K] weights: same product
+    assert seen["gemv_nk"] is True and torch.equal(y_nk, y)
+    with pytest.raises(SymmMemError, match="tcgen05"):
+        smr.gemv_all_reduce(x, w.t().contiguous(), algo="simt", weights_nk=True)
     ref = x.float() @ w.float()
     dist.all_reduce(ref)
     assert torch.allclose(y.float(), ref, atol=0.02)
@@ -339,8 +344,9 @@ def _selfcheck_worker(rank, world_size):
             return getattr(real, name)
 
         @staticmethod
-        def gemv_all_reduce(x, w, out, workspace, ws_offset, timeout_ns, tensor_core=False, num_sms=148, tagged=False):
-            part = x.float() @ w.float()
+        def gemv_all_reduce(x, w, out, workspace, ws_offset, timeout_ns, tensor_core=False, num_sms=148, tagged=False,
+                            weights_nk=False):
+            part = x.float() @ (w.float().t() if weights_nk else w.float())
             dist.all_reduce(part)
             out.copy_(part.to(out.dtype))
 

@@ -84,3 +84,37 @@ def test_gemv_tagged_world_of_one(B, K, N):
 @pytest.mark.parametrize("B", [1, 4, 16])
 def test_gemv_tagged_2gpu(B):
     spawn_ranks(_gemv_worker, 2, "nccl", (B, 3584, 8192, "tc_tagged"))
+
+
+def _gemv_nk_worker(rank, world_size, B, K, N, algo):
+    """Weights stored [N, K] (the prefill layout): same result as the [K, N] form."""
+    import symm_mem_recipes_b200 as smr
+    from symm_mem_recipes_b200.parallel import symm_mem
+
+    dev = torch.device("cuda", rank)
+    x, w = _inputs(rank, B, K, N)
+    x, w = x.to(dev), w.to(dev)
+    want = smr.gemv_all_reduce(x, w, algo="tc")
+    symm_mem.check_status(dev)
+    w_nk = w.t().contiguous()
+    for _ in range(3):
+        got = smr.gemv_all_reduce(x, w_nk, algo=algo, weights_nk=True)
+    symm_mem.check_status(dev)
+    assert torch.allclose(got.float(), want.float(), rtol=2.0 ** -6, atol=2e-2), (got.float() - want.float()).abs().max()
+    torch.cuda.synchronize()
+
+
+@pytest.mark.gpu
+@pytest.mark.first_run
+@pytest.mark.parametrize("algo", ["tc", "tc_tagged"])
+@pytest.mark.parametrize("B,K,N", [(1, 512, 256), (4, 3584, 8192), (3, 1000, 328)])
+def test_gemv_weights_nk_world_of_one(B, K, N, algo):
+    torch.cuda.set_device(0)
+    _gemv_nk_worker(0, 1, B, K, N, algo)
+
+
+@pytest.mark.gpu
+@pytest.mark.first_run
+@pytest.mark.multigpu(2)
+def test_gemv_weights_nk_2gpu():
+    spawn_ranks(_gemv_nk_worker, 2, "nccl", (4, 3584, 8192, "tc"))

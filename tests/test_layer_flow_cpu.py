@@ -67,12 +67,13 @@ def host_kernels(monkeypatch):
     monkeypatch.setattr(layer_glue, "_check", relaxed)
 
 
-def _layer_and_reference(fused_glue, fused_swiglu):
+def _layer_and_reference(fused_glue, fused_swiglu, **kw):
     from symm_mem_recipes_b200.models.llama_tp_layer import (LlamaTPConfig, LlamaTPDecoderLayer,
                                                              full_precision_reference)
 
     cfg = LlamaTPConfig.tiny(1)
-    layer = LlamaTPDecoderLayer(cfg, torch.device("cpu"), seed=1, fused_glue=fused_glue, fused_swiglu=fused_swiglu)
+    layer = LlamaTPDecoderLayer(cfg, torch.device("cpu"), seed=1, fused_glue=fused_glue, fused_swiglu=fused_swiglu,
+                                **kw)
     batch, seq = 2, 16
     torch.manual_seed(3)
     x = (torch.randn(batch * seq, cfg.hidden) * 0.5).to(torch.bfloat16)
@@ -96,11 +97,12 @@ def test_prefill_flow_matches_fp32(host_kernels, fused_glue, fused_swiglu):
     assert (y.float() - y_lib.float()).abs().max().item() < 0.1
 
 
-@pytest.mark.parametrize("fused_glue", [False, True])
-def test_decode_flow_matches_prefill(host_kernels, fused_glue):
+@pytest.mark.parametrize("fused_glue,shared", [(False, False), (True, False), (True, True)])
+def test_decode_flow_matches_prefill(host_kernels, fused_glue, shared):
     """Decoding the tokens one by one through the KV cache gives what the
     prefill of the same sequence gives at every position."""
-    cfg, layer, x, batch, seq, _ = _layer_and_reference(fused_glue, False)
+    cfg, layer, x, batch, seq, _ = _layer_and_reference(fused_glue, False, shared_row_weights=shared)
+    assert (layer.w_o_t is None) == shared                        # one copy of the row-parallel weights
     want = layer.forward(x, batch, seq).view(batch, seq, cfg.hidden)
     k_cache = torch.zeros(batch, seq, layer.hkv, cfg.head_dim, dtype=torch.bfloat16)
     v_cache = torch.zeros_like(k_cache)
