@@ -200,15 +200,16 @@ def build_checks(first_run: bool, world: int, rank: int, dev: torch.device) -> l
     add("matmul_all_reduce", "cta_pair", row_parallel("ar", cta_pair=True), True)
 
     # ------------------------------------------------------------------ GEMV + all-reduce
-    def gemv(algo, B):
+    def gemv(algo, B, nk=False):
         def fn():
             x = randn(B, 1024, std=0.5, seed=60 + rank)
             w = randn(1024, 512, seed=80 + rank)
             ref = x.float() @ w.float()
             if multi:
                 dist.all_reduce(ref)
+            w_arg = w.t().contiguous() if nk else w
             for _ in range(3):
-                got = smr.gemv_all_reduce(x, w, algo=algo)
+                got = smr.gemv_all_reduce(x, w_arg, algo=algo, weights_nk=nk)
             symm_mem.check_status(dev)
             ok, err = _close(got, ref, 2.0 ** -6, 3e-2)
             return ok, f"max err {err:.4f}"
@@ -218,6 +219,7 @@ def build_checks(first_run: bool, world: int, rank: int, dev: torch.device) -> l
         add("gemv", f"tcgen05, batch {B}", gemv("tc", B))
         add("gemv", f"CUDA cores, batch {B}", gemv("simt", B))
         add("gemv", f"tcgen05 tagged words, batch {B}", gemv("tc_tagged", B), True)
+        add("gemv", f"tcgen05, weights stored [N, K], batch {B}", gemv("tc", B, nk=True), True)
 
     # ------------------------------------------------------------------ layer glue and the layer
     def glue():
