@@ -3,7 +3,8 @@
 // plain reads of every peer), the epoch barrier and the low-latency all-reduce (tagged words, two
 // parities).  The host builds use the same slot layout and the same release / acquire placement as
 // the device code, so a missing ordering shows up here as a reported race or a wrong value.
-// Built and run by tests/test_tsan_protocols.py with -fsanitize=thread; exit code 0 = clean.
+// Built and run by tests/test_tsan_protocols.py with -fsanitize=thread and with
+// -fsanitize=address,undefined; exit code 0 = clean.
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -41,6 +42,8 @@ int main(int argc, char** argv) {
       }
     });
   for (auto& t : th) t.join();
+  for (auto p : pads) free(p);
+  for (auto w : wsp) free(w);
   int total = 0; for (int b : bad) total += b;
   printf("ws=%d iters=%d failures=%d\n", ws, iters, total);
   return total != 0;
