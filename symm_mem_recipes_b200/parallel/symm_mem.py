@@ -17,6 +17,12 @@ Typical use, one process per GPU::
     hdl = symm_mem.rendezvous(t)          # collective, cached
     peer0 = hdl.get_buffer(0, t.shape, t.dtype)
     hdl.barrier()
+
+Beyond that: `hdl.put_signal / wait_signal` (one-to-one signals on a channel),
+`check_status()` (turns a kernel's recorded timeout into `SymmMemTimeout`),
+`free(t)` (collective), `memory_summary()`, `shutdown()` (orderly teardown
+before `destroy_process_group`) and `reset()` (teardown that allows a new
+process group to start over).
 """
 from __future__ import annotations
 
