@@ -55,6 +55,34 @@ struct RsParams {
 
 __device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
+// Epilogue, one thread per row of the tile: the row's 64 accumulator columns of a strip (v0: columns
+// 0..31, v1: 32..63) become bf16 and go to row `r` of the strip buffer, whose 16-byte chunks are
+// XOR-swizzled by row so that the 32 lanes of a warp do not collide on shared-memory banks.
+__device__ __forceinline__ void strip_row_to_smem(uint8_t* buf, int r, const uint32_t (&v0)[32],
+                                                  const uint32_t (&v1)[32]) {
+  uint8_t* row = buf + (size_t)r * 128;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {                    // 16-byte chunk c of the row
+    const uint32_t* v = c < 4 ? &v0[c * 8] : &v1[(c - 4) * 8];
+    Vec16 o;
+    o.x = pack_bf16x2(__uint_as_float(v[0]), __uint_as_float(v[1]));
+    o.y = pack_bf16x2(__uint_as_float(v[2]), __uint_as_float(v[3]));
+    o.z = pack_bf16x2(__uint_as_float(v[4]), __uint_as_float(v[5]));
+    o.w = pack_bf16x2(__uint_as_float(v[6]), __uint_as_float(v[7]));
+    *reinterpret_cast<Vec16*>(row + ((c ^ (r & 7)) << 4)) = o;
+  }
+}
+
+// Thread-store epilogue: the 128 epilogue threads copy a finished 16 KB strip from shared memory to
+// `dst` (a peer's inbox) with 16-byte loads and stores, 512 contiguous bytes per warp instruction.
+__device__ __forceinline__ void strip_copy_out(char* dst, const uint8_t* buf, int etid) {
+#pragma unroll
+  for (int j = 0; j < (int)(kStripBytesOne / 16 / 128); ++j) {
+    const int idx = etid + j * 128;                // 16-byte vector of the strip
+    st_16(dst + (size_t)idx * 16, *reinterpret_cast<const Vec16*>(buf + (size_t)idx * 16));
+  }
+}
+
 // CTA-pair kernel: entry `rb` of the list of 128-row blocks in visiting order (destination rank+1
 // first, own rows last) -> destination rank and row block inside it.  CTA c of the pair working on
 // tile t handles entry 2 * (t / n_tiles_n) + c.

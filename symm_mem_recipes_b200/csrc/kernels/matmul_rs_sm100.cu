@@ -208,26 +208,12 @@ matmul_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
         epilogue_sync();
         uint8_t* buf = strip + (size_t)(strip_ctr % (uint32_t)kNStrips) * kStripBytesOne;
-        uint8_t* row = buf + (size_t)r * 128;
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {                    // 16-byte chunk c of the row, 128-byte swizzle
-          const uint32_t* v = c < 4 ? &v0[c * 8] : &v1[(c - 4) * 8];
-          Vec16 o;
-          o.x = pack_bf16x2(__uint_as_float(v[0]), __uint_as_float(v[1]));
-          o.y = pack_bf16x2(__uint_as_float(v[2]), __uint_as_float(v[3]));
-          o.z = pack_bf16x2(__uint_as_float(v[4]), __uint_as_float(v[5]));
-          o.w = pack_bf16x2(__uint_as_float(v[6]), __uint_as_float(v[7]));
-          *reinterpret_cast<Vec16*>(row + ((c ^ (r & 7)) << 4)) = o;
-        }
+        strip_row_to_smem(buf, r, v0, v1);
         if constexpr (kThreadStores) {
           epilogue_sync();                               // the strip is complete in shared memory
           char* dst = static_cast<char*>(p.buffers[dest]) + p.inbox_offset +
                       strip_offset(p.rank, mb, ni, sidx, p.blocks_per_rank, p.n_tiles_n);
-#pragma unroll
-          for (int j = 0; j < (int)(kStripBytesOne / 16 / 128); ++j) {
-            const int idx = etid + j * 128;              // 16-byte vector of the strip
-            st_16(dst + (size_t)idx * 16, *reinterpret_cast<const Vec16*>(buf + (size_t)idx * 16));
-          }
+          strip_copy_out(dst, buf, etid);
         } else {
         fence_proxy_async();                             // generic writes to smem, async-proxy read
         epilogue_sync();
