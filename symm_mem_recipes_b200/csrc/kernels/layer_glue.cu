@@ -44,10 +44,12 @@ __device__ __forceinline__ float round_bf16(float f) {
 
 // One CTA per row.  Pass 1: s = x (+ r), sum of squares (s stored when asked
 // for).  Pass 2 re-reads s (from L1 / L2) and writes the normalised row.
+// `sum_out` may be the buffer of `x` or of `residual` (running residual stream
+// updated in place) and `out` may be the buffer of `x`; `out` must not be the
+// buffer of `sum_out` or of `residual`.
 __global__ void __launch_bounds__(kNormThreads)
-rms_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ residual,
-                const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ sum_out,
-                __nv_bfloat16* __restrict__ out, int H, float eps) {
+rms_norm_kernel(const __nv_bfloat16* x, const __nv_bfloat16* residual, const __nv_bfloat16* __restrict__ w,
+                __nv_bfloat16* sum_out, __nv_bfloat16* out, int H, float eps) {
   const size_t row = blockIdx.x;
   const Vec16* xr = reinterpret_cast<const Vec16*>(x + row * H);
   const Vec16* rr = residual ? reinterpret_cast<const Vec16*>(residual + row * H) : nullptr;
@@ -86,12 +88,18 @@ rms_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
   Vec16* orow = reinterpret_cast<Vec16*>(out + row * H);
   for (int i = threadIdx.x; i < n_vec; i += kNormThreads) {
     float a[8], g[8];
-    unpack8(ld_16(xr + i), a);
-    if (rr != nullptr) {
-      float b[8];
-      unpack8(ld_16(rr + i), b);
+    if (sr != nullptr) {
+      // this thread stored s[i] itself in pass 1; reading it back (instead of x and r again) also
+      // keeps the kernel correct when sum_out is the same buffer as x or as the residual
+      unpack8(ld_16(sr + i), a);
+    } else {
+      unpack8(ld_16(xr + i), a);
+      if (rr != nullptr) {
+        float b[8];
+        unpack8(ld_16(rr + i), b);
 #pragma unroll
-      for (int q = 0; q < 8; ++q) a[q] = round_bf16(a[q] + b[q]);
+        for (int q = 0; q < 8; ++q) a[q] = round_bf16(a[q] + b[q]);
+      }
     }
     unpack8(ld_16(wr + i), g);
 #pragma unroll

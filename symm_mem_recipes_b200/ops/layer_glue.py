@@ -29,8 +29,9 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: Optional[to
              residual: Optional[torch.Tensor] = None, sum_out: Optional[torch.Tensor] = None):
     """`out = bf16(bf16(s * rsqrt(mean(s^2) + eps)) * weight)` per row of `s`,
     where `s = x`, or `bf16(x + residual)` when a residual is given (then `s`
-    itself is written to `sum_out` if provided).  `out` may be a symmetric
-    buffer, so the result lands where `all_gather_matmul` reads it.  Returns
+    itself is written to `sum_out`, which may be `x` or `residual` for a residual
+    stream kept in place).  `out` may be a symmetric buffer, so the result lands
+    where `all_gather_matmul` reads it, or `x` itself without a residual.  Returns
     `out`, or `(out, sum_out)` with a residual."""
     _check("x", x, 2)
     _check("weight", weight, 1)
@@ -42,6 +43,17 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: Optional[to
         sum_out = torch.empty_like(x)
     if residual is None and sum_out is not None:
         raise SymmMemError("sum_out is only written when a residual is given")
+    if residual is not None:
+        _check("residual", residual, 2)
+        _check("sum_out", sum_out, 2)
+        if residual.shape != x.shape or sum_out.shape != x.shape:
+            raise SymmMemError("residual and sum_out must have the shape of x")
+        if out.data_ptr() in (sum_out.data_ptr(), residual.data_ptr()):
+            raise SymmMemError("out must not be the buffer of sum_out or of the residual "
+                               "(sum_out may be the buffer of x or of the residual)")
+    _check("out", out, 2)
+    if out.shape != x.shape:
+        raise SymmMemError("out must have the shape of x")
     C.rms_norm(x, residual, weight, sum_out, out, float(eps))
     return out if residual is None else (out, sum_out)
 

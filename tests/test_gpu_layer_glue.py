@@ -36,6 +36,14 @@ def test_rms_norm(rows, H):
     assert torch.equal(s2.cpu(), sum2)
     ok, err = _ulp_close(out2, ref2)
     assert ok, err
+    # residual stream kept in place: sum_out is the residual's own buffer
+    stream = r.cuda()
+    out3, s3 = ops.rms_norm(x.cuda(), w.cuda(), 1e-5, residual=stream, sum_out=stream)
+    assert s3 is stream and torch.equal(stream.cpu(), sum2)
+    ok, err = _ulp_close(out3, ref2)
+    assert ok, err
+    with pytest.raises(Exception, match="out must not be"):
+        ops.rms_norm(x.cuda(), w.cuda(), 1e-5, out=stream, residual=stream)
 
 
 @pytest.mark.parametrize("batch,seq,hq,hkv,D,pos0",
