@@ -42,6 +42,11 @@ def main(argv=None, standalone: bool = True) -> int:
     ap.add_argument("--tp", action="store_true",
                     help="also time the prefill without sequence parallelism (replicated activations, "
                          "matmul_all_reduce endings) against cuBLAS + NCCL all-reduce")
+    ap.add_argument("--decode-graph", type=int, default=0, metavar="LAYERS",
+                    help="also time serving-style decode: LAYERS layers captured in one CUDA graph (DecodeGraph, "
+                         "cache of --decode-cache entries, position in a device tensor), replayed per token, "
+                         "against the same steps launched eagerly")
+    ap.add_argument("--decode-cache", type=int, default=4096)
     ap.add_argument("--out", default=None)
     args = ap.parse_args(argv)
     from symm_mem_recipes_b200.bench._common import finish, init_distributed
@@ -168,6 +173,47 @@ def main(argv=None, standalone: bool = True) -> int:
             emit({"op": "llama70b_layer_decode", "world_size": world, "batch": B, "timing": "graph",
                   "smr_fused_us": round(us_f, 1), "nccl_cublas_us": round(us_r, 1),
                   "speedup": round(us_r / us_f, 3)})
+    if args.decode_graph > 0:
+        from symm_mem_recipes_b200.models.llama_tp_layer import DecodeGraph
+        from symm_mem_recipes_b200.utils.benchmark import max_over_ranks
+
+        stack = [LlamaTPDecoderLayer(cfg, dev, seed=100 + i) for i in range(args.decode_graph)]
+        for B in (1, 4, 16):
+            xd = (torch.randn(B, cfg.hidden, device=dev) * 0.5).to(torch.bfloat16)
+            if world > 1:
+                dist.broadcast(xd, 0)
+            graph = DecodeGraph(stack, B, args.decode_cache)
+            first = args.decode_cache // 2
+            steps = 32
+
+            def replayed():
+                for i in range(steps):
+                    graph.step(xd, first + i)
+
+            def eager():
+                for i in range(steps):
+                    h = xd
+                    for lyr, (kc, vc) in zip(stack, graph.caches):
+                        h = lyr.decode(h, kc, vc, first + i, fused=True)
+
+            times = {}
+            for name, fn in (("graph", replayed), ("eager", eager)):
+                fn()
+                beg, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                if world > 1:
+                    dist.barrier()
+                beg.record()
+                fn()
+                end.record()
+                torch.cuda.synchronize()
+                times[name] = max_over_ranks(beg.elapsed_time(end) * 1e3 / steps, dev)
+            symm_mem.check_status(dev)
+            emit({"op": "llama70b_decode_graph", "world_size": world, "batch": B, "layers": args.decode_graph,
+                  "cache_entries": args.decode_cache, "first_position": first, "steps": steps,
+                  "graph_us_per_step": round(times["graph"], 1), "eager_us_per_step": round(times["eager"], 1),
+                  "speedup": round(times["eager"] / times["graph"], 3)})
+            del graph
     if args.out and rank == 0:
         with open(args.out, "a") as f:
             f.write("\n".join(lines) + "\n")

@@ -694,15 +694,21 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                              sum_out ? sum_out->data_ptr() : nullptr, out.data_ptr(), (int)x.size(0),
                              (int)x.size(1), (float)eps, current_stream(dev)), "rms_norm");
   }, py::arg("x"), py::arg("residual"), py::arg("w"), py::arg("sum_out"), py::arg("out"), py::arg("eps"));
+  // `pos` (optional): int32 CUDA tensor of one element that holds the first position; read on the device
   m.def("rope_inplace", [](torch::Tensor qkv, int n_heads, int head_dim, int seq, int pos0, double theta,
-                           int num_sms) {
+                           int num_sms, c10::optional<torch::Tensor> pos) {
     TORCH_CHECK(qkv.is_cuda() && qkv.is_contiguous() && qkv.dim() == 2 && qkv.scalar_type() == torch::kBFloat16,
                 "rope_inplace: qkv[tokens, row] contiguous bf16 on the GPU");
     int dev = qkv.get_device();
+    TORCH_CHECK(!pos.has_value() || (pos->is_cuda() && pos->get_device() == dev && pos->numel() == 1 &&
+                                     pos->scalar_type() == torch::kInt32),
+                "rope_inplace: pos must be an int32 tensor of one element on qkv's GPU");
     c10::cuda::CUDAGuard guard(dev);
     rt_check(launch_rope_inplace(qkv.data_ptr(), qkv.size(0), (int)qkv.size(1), n_heads, head_dim, seq, pos0,
-                                 (float)theta, num_sms, current_stream(dev)), "rope_inplace");
-  });
+                                 pos ? static_cast<const int*>(pos->data_ptr()) : nullptr, (float)theta, num_sms,
+                                 current_stream(dev)), "rope_inplace");
+  }, py::arg("qkv"), py::arg("n_heads"), py::arg("head_dim"), py::arg("seq"), py::arg("pos0"), py::arg("theta"),
+     py::arg("num_sms"), py::arg("pos") = py::none());
   m.def("silu_mul", [](torch::Tensor gate_up, torch::Tensor out, int num_sms) {
     auto ok = [](const torch::Tensor& t) {
       return t.is_cuda() && t.is_contiguous() && t.dim() == 2 && t.scalar_type() == torch::kBFloat16;

@@ -168,13 +168,15 @@ int launch_matmul_reduce_scatter_2cta(const MatmulRsArgs& args, cudaStream_t str
 
 // ---- rank-local layer glue (layer_glue.cu): bf16 data, fp32 math, one pass each ----
 // out[rows, H] = RMSNorm(x (+ residual)) * w.  With `residual`, `sum_out` (optional) receives
-// bf16(x + residual).  Outputs must not alias inputs.  H % 8 == 0, 16-byte aligned pointers.
+// bf16(x + residual).  `sum_out` may be the buffer of `x` or of `residual`, `out` the buffer of `x`;
+// `out` must not be the buffer of `sum_out` or `residual`.  H % 8 == 0, 16-byte aligned pointers.
 int launch_rms_norm(const void* x, const void* residual, const void* w, void* sum_out, void* out, int rows, int H,
                     float eps, cudaStream_t stream);
 // Rotary embedding in place on heads [0, n_heads) of every row (`row_stride` elements per row);
-// token t is at position pos0 + t % seq.  head_dim % 16 == 0.
+// token t is at position pos0 + t % seq, with pos0 read from `pos_dev` on the device when that is
+// not null (graph-captured decode).  head_dim % 16 == 0.
 int launch_rope_inplace(void* qkv, long long tokens, int row_stride, int n_heads, int head_dim, int seq, int pos0,
-                        float theta, int num_sms, cudaStream_t stream);
+                        const int* pos_dev, float theta, int num_sms, cudaStream_t stream);
 // out[rows, F] = SiLU(gate_up[:, :F]) * gate_up[:, F:].  F % 8 == 0.
 int launch_silu_mul(const void* gate_up, void* out, long long rows, int F, int num_sms, cudaStream_t stream);
 

@@ -109,10 +109,13 @@ rms_norm_kernel(const __nv_bfloat16* x, const __nv_bfloat16* residual, const __n
 }
 
 // In place on rows of `row_stride` elements: heads [0, n_heads) of D elements
-// each are rotated.  Token t sits at position pos0 + (t % seq).  One thread
-// per (token, head, 8 consecutive pair indices).
+// each are rotated.  Token t sits at position pos0 + (t % seq); with `pos_dev`
+// the first position is read from device memory instead (a decode step
+// captured in a CUDA graph takes its position from a tensor).  One thread per
+// (token, head, 8 consecutive pair indices).
 __global__ void rope_kernel(__nv_bfloat16* __restrict__ qkv, long long n_items, int row_stride, int n_heads, int D,
-                            int seq, int pos0, float log2_theta) {
+                            int seq, int pos0, const int* __restrict__ pos_dev, float log2_theta) {
+  if (pos_dev != nullptr) pos0 = *pos_dev;
   const int vec_per_head = D / 16;                      // vectors of 8 pairs
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x; item < n_items; item += stride) {
@@ -187,14 +190,14 @@ int launch_rms_norm(const void* x, const void* residual, const void* w, void* su
 }
 
 int launch_rope_inplace(void* qkv, long long tokens, int row_stride, int n_heads, int head_dim, int seq, int pos0,
-                        float theta, int num_sms, cudaStream_t stream) {
+                        const int* pos_dev, float theta, int num_sms, cudaStream_t stream) {
   if (tokens < 0 || n_heads < 1 || head_dim < 16 || head_dim % 16 != 0 || seq < 1 || row_stride % 8 != 0 ||
       (long long)n_heads * head_dim > row_stride || theta <= 1.0f || !aligned16(qkv))
     return cudaErrorInvalidValue;
   if (tokens == 0) return cudaSuccess;
   const long long items = tokens * n_heads * (head_dim / 16);
   rope_kernel<<<grid_for(items, 256, num_sms), 256, 0, stream>>>(static_cast<__nv_bfloat16*>(qkv), items, row_stride,
-                                                                n_heads, head_dim, seq, pos0, log2f(theta));
+                                                                n_heads, head_dim, seq, pos0, pos_dev, log2f(theta));
   return (int)cudaGetLastError();
 }
 

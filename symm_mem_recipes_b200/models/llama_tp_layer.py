@@ -11,7 +11,10 @@ Prefill (`forward`), activations sharded on tokens between the blocks:
       -> SiLU(gate) * up -> matmul_reduce_scatter with W_down -> + residual
 
 Decode (`decode`), activations replicated, batch <= 16: the two row-parallel
-projections use the fused GEMV + all-reduce.
+projections use the fused GEMV + all-reduce.  `decode_static` is the same step
+with shapes and launches independent of the position, and `DecodeGraph`
+captures it (through any number of layers) in one CUDA graph that is replayed
+per token.
 
 Prefill without sequence parallelism (`forward_tp`), activations replicated:
 local GEMMs for the column-parallel projections, `matmul_all_reduce` for the
@@ -295,23 +298,30 @@ class LlamaTPDecoderLayer:
         return x1 + scatter(act @ self.w_down.t())
 
     # ------------------------------------------------------------------
+    def _row_parallel_decode(self, act: torch.Tensor, which: str, fused: bool) -> torch.Tensor:
+        """act [B, K_local] times this rank's rows of the o- or down-projection, summed over the ranks."""
+        nk = self.shared_row_weights
+        w = {"o": self.w_o if nk else self.w_o_t, "down": self.w_down if nk else self.w_down_t}[which]
+        if fused and self.ws > 1:
+            return ops.gemv_all_reduce(act, w, group=self.group, weights_nk=nk)
+        return ops.reference_gemv_all_reduce(act, w, group=self.group, weights_nk=nk)
+
+    def _decode_norm(self, t: torch.Tensor, w: torch.Tensor, glue: bool) -> torch.Tensor:
+        return ops.rms_norm(t, w, self.cfg.eps) if glue else _rms_norm(t, w, self.cfg.eps)
+
+    def _decode_mlp(self, x1: torch.Tensor, fused: bool, glue: bool) -> torch.Tensor:
+        gu = self._decode_norm(x1, self.norm2, glue) @ self.w_gate_up.t()
+        act = ops.silu_mul(gu) if glue else LlamaTPDecoderLayer._mlp_act_torch(gu, self.ffn_local)
+        return x1 + self._row_parallel_decode(act, "down", fused)
+
     def decode(self, x: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, pos: int,
                fused: bool = True) -> torch.Tensor:
         """One decode step.  x [B, H] replicated on all ranks; caches
         [B, S_max, hkv, D] hold this rank's KV heads and are updated at `pos`."""
         cfg = self.cfg
         B, D, hq, hkv = x.shape[0], cfg.head_dim, self.hq, self.hkv
-
-        nk = self.shared_row_weights
-
-        def row_parallel(act, w):               # w: [K_local, N], or [N, K_local] with shared_row_weights
-            if fused and self.ws > 1:
-                return ops.gemv_all_reduce(act, w, group=self.group, weights_nk=nk)
-            return ops.reference_gemv_all_reduce(act, w, group=self.group, weights_nk=nk)
-
         glue = fused and self.fused_glue
-        norm = (lambda t, w: ops.rms_norm(t, w, cfg.eps)) if glue else (lambda t, w: _rms_norm(t, w, cfg.eps))
-        qkv = norm(x, self.norm1) @ self.w_qkv.t()
+        qkv = self._decode_norm(x, self.norm1, glue) @ self.w_qkv.t()
         if glue:
             ops.rope_(qkv, hq + hkv, D, 1, cfg.rope_theta, pos0=pos)
         q, k, v = qkv.split([hq * D, hkv * D, hkv * D], dim=-1)
@@ -323,10 +333,95 @@ class LlamaTPDecoderLayer:
         v_cache[:, pos] = v.view(B, hkv, D)
         o = F.scaled_dot_product_attention(q.transpose(1, 2), k_cache[:, : pos + 1].transpose(1, 2),
                                            v_cache[:, : pos + 1].transpose(1, 2), enable_gqa=True)
-        x1 = x + row_parallel(o.transpose(1, 2).reshape(B, hq * D).contiguous(), self.w_o if nk else self.w_o_t)
-        gu = norm(x1, self.norm2) @ self.w_gate_up.t()
-        act = ops.silu_mul(gu) if glue else LlamaTPDecoderLayer._mlp_act_torch(gu, self.ffn_local)
-        return x1 + row_parallel(act, self.w_down if nk else self.w_down_t)
+        x1 = x + self._row_parallel_decode(o.transpose(1, 2).reshape(B, hq * D).contiguous(), "o", fused)
+        return self._decode_mlp(x1, fused, glue)
+
+    def decode_static(self, x: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, pos: torch.Tensor,
+                      fused: bool = True) -> torch.Tensor:
+        """`decode` with every shape and every launch independent of the
+        position, so that ONE captured CUDA graph serves all positions: `pos`
+        is an int32 tensor of one element on the device, the caches are written
+        with `index_copy_`, and attention runs over the whole cache under a
+        mask that hides the entries beyond `pos`.  Same result as `decode`."""
+        cfg = self.cfg
+        B, D, hq, hkv = x.shape[0], cfg.head_dim, self.hq, self.hkv
+        s_max = k_cache.shape[1]
+        glue = fused and self.fused_glue
+        qkv = self._decode_norm(x, self.norm1, glue) @ self.w_qkv.t()
+        if glue:
+            ops.rope_(qkv, hq + hkv, D, 1, cfg.rope_theta, pos0=pos)
+        q, k, v = qkv.split([hq * D, hkv * D, hkv * D], dim=-1)
+        q, k = q.view(B, 1, hq, D), k.view(B, 1, hkv, D)
+        if not glue:
+            p = pos.view(1, 1).expand(B, 1)
+            q, k = _rope(q, p, cfg.rope_theta), _rope(k, p, cfg.rope_theta)
+        idx = pos.view(1).long()
+        k_cache.index_copy_(1, idx, k)
+        v_cache.index_copy_(1, idx, v.reshape(B, 1, hkv, D))
+        visible = (torch.arange(s_max, device=x.device, dtype=torch.int32) <= pos.view(1)).view(1, 1, 1, s_max)
+        o = F.scaled_dot_product_attention(q.transpose(1, 2), k_cache.transpose(1, 2), v_cache.transpose(1, 2),
+                                           attn_mask=visible, enable_gqa=True)
+        x1 = x + self._row_parallel_decode(o.transpose(1, 2).reshape(B, hq * D).contiguous(), "o", fused)
+        return self._decode_mlp(x1, fused, glue)
+
+
+class DecodeGraph:
+    """A decode step through a stack of layers captured once in a CUDA graph
+    and replayed for every token: the launch-bound part of serving (a dozen
+    kernels of a few microseconds per layer) costs one graph launch per step.
+
+        g = DecodeGraph(layers, batch=4, max_seq=4096)
+        for pos, x in enumerate(tokens):           # x [B, H], replicated on all ranks
+            y = g.step(x, pos)                     # y is overwritten by the next step
+
+    Every rank builds and replays the same graph (the fused GEMV + all-reduce
+    kernels inside meet their peers as in eager mode).  The KV caches live in
+    the object; `reset()` starts a new sequence.  No upstream counterpart: the
+    upstream recipes time single kernels.
+    """
+
+    def __init__(self, layers, batch: int, max_seq: int, fused: bool = True, warmup: int = 2):
+        self.layers = list(layers)
+        first = self.layers[0]
+        dev, cfg = first.device, first.cfg
+        self.max_seq = int(max_seq)
+        self.fused = fused
+        self.x = torch.zeros(batch, cfg.hidden, dtype=torch.bfloat16, device=dev)
+        self.pos = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.caches = [(torch.zeros(batch, max_seq, lyr.hkv, cfg.head_dim, dtype=torch.bfloat16, device=dev),
+                        torch.zeros(batch, max_seq, lyr.hkv, cfg.head_dim, dtype=torch.bfloat16, device=dev))
+                       for lyr in self.layers]
+        # first calls allocate workspaces and rendezvous: outside the capture, on a side stream
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(max(1, warmup)):
+                self._run()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.y = self._run()
+        self.reset()
+
+    def _run(self) -> torch.Tensor:
+        h = self.x
+        for lyr, (kc, vc) in zip(self.layers, self.caches):
+            h = lyr.decode_static(h, kc, vc, self.pos, fused=self.fused)
+        return h
+
+    def reset(self) -> None:
+        for kc, vc in self.caches:
+            kc.zero_()
+            vc.zero_()
+
+    def step(self, x: torch.Tensor, pos: int) -> torch.Tensor:
+        if not 0 <= pos < self.max_seq:
+            raise ValueError(f"position {pos} outside the cache of {self.max_seq} entries")
+        self.x.copy_(x)
+        self.pos.fill_(pos)
+        self.graph.replay()
+        return self.y
 
 
 def full_precision_reference(layers_weights: list, cfg: LlamaTPConfig, x: torch.Tensor, batch: int,

@@ -9,7 +9,7 @@ which at Llama-70B prefill sizes costs more than the o-projection GEMM.
 """
 from __future__ import annotations
 
-from typing import Optional
+from typing import Optional, Union
 
 import torch
 
@@ -59,15 +59,24 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: Optional[to
 
 
 @traced("smr.rope_")
-def rope_(qkv: torch.Tensor, n_heads: int, head_dim: int, seq: int, theta: float, pos0: int = 0) -> torch.Tensor:
+def rope_(qkv: torch.Tensor, n_heads: int, head_dim: int, seq: int, theta: float,
+          pos0: Union[int, torch.Tensor] = 0) -> torch.Tensor:
     """Rotate heads `[0, n_heads)` of every row of `qkv` [tokens, row] in place
     (Llama pairing `(i, i + head_dim/2)`); token `t` is at position
     `pos0 + t % seq`.  With the Q heads followed by the K heads at the start of
-    the row, `n_heads = q_heads + kv_heads` rotates both and leaves V alone."""
+    the row, `n_heads = q_heads + kv_heads` rotates both and leaves V alone.
+    `pos0` may be an int32 tensor of one element on the same device: the kernel
+    then reads the position when it runs, so a decode step captured in a CUDA
+    graph serves every position."""
     _check("qkv", qkv, 2)
     if head_dim % 16 or n_heads * head_dim > qkv.shape[1] or qkv.shape[1] % 8:
         raise SymmMemError("need head_dim % 16 == 0, n_heads * head_dim <= row length, row length % 8 == 0")
-    C.rope_inplace(qkv, int(n_heads), int(head_dim), int(seq), int(pos0), float(theta), _num_sms(qkv.device))
+    if isinstance(pos0, torch.Tensor):
+        if pos0.dtype != torch.int32 or pos0.numel() != 1 or pos0.device != qkv.device:
+            raise SymmMemError("a position tensor must be int32, of one element, on qkv's device")
+        C.rope_inplace(qkv, int(n_heads), int(head_dim), int(seq), 0, float(theta), _num_sms(qkv.device), pos0)
+    else:
+        C.rope_inplace(qkv, int(n_heads), int(head_dim), int(seq), int(pos0), float(theta), _num_sms(qkv.device))
     return qkv
 
 

@@ -267,6 +267,26 @@ def build_checks(first_run: bool, world: int, rank: int, dev: torch.device) -> l
     add("layer", "prefill, glue kernels + SwiGLU epilogue", layer("sp", True, True), True)
     add("layer", "prefill, no sequence parallelism", layer("tp"), True)
     add("layer", "decode, single-pass glue kernels", layer("decode", True), True)
+
+    def decode_graph():
+        from symm_mem_recipes_b200.models.llama_tp_layer import DecodeGraph
+        cfg = LlamaTPConfig.tiny(world)
+        lay = LlamaTPDecoderLayer(cfg, dev, seed=11)
+        graph = DecodeGraph([lay], batch=4, max_seq=8)
+        kc = torch.zeros(4, 8, lay.hkv, cfg.head_dim, dtype=torch.bfloat16, device=dev)
+        vc = torch.zeros_like(kc)
+        all_ok, worst = True, 0.0
+        for pos in range(3):
+            xd = randn(4, cfg.hidden, std=0.5, seed=20 + pos)
+            got = graph.step(xd, pos).clone()
+            ref = lay.decode(xd, kc, vc, pos, fused=True)
+            ok, err = _close(got, ref, 5e-2, 5e-2)
+            all_ok, worst = all_ok and ok, max(worst, err)
+        symm_mem.check_status(dev)
+        return all_ok, f"three replayed positions, max diff from the eager step {worst:.4f}"
+
+    if dev.type == "cuda":                          # CUDA graphs: nothing to capture on the CPU backend
+        add("layer", "decode through one captured CUDA graph", decode_graph, True)
     return [c for c in checks if first_run or not c[2]]
 
 

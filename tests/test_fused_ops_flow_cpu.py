@@ -254,7 +254,8 @@ def _install_row_parallel_and_glue_stand_ins():
                 sum_out.copy_(s)
 
         @staticmethod
-        def rope_inplace(qkv, n_heads, head_dim, seq, pos0, theta, num_sms):
+        def rope_inplace(qkv, n_heads, head_dim, seq, pos0, theta, num_sms, pos=None):
+            pos0 = pos0 if pos is None else int(pos)
             qkv.copy_(real.oracle_rope_bf16(qkv, n_heads, head_dim, seq, pos0, theta))
 
         @staticmethod

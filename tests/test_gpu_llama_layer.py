@@ -116,3 +116,53 @@ def _layer_tp_worker(rank, world_size, fused_glue, fused_swiglu):
 @pytest.mark.parametrize("fused_glue,fused_swiglu", [(False, False), (True, True)])
 def test_layer_tensor_parallel_prefill_2gpu(fused_glue, fused_swiglu):
     spawn_ranks(_layer_tp_worker, 2, "nccl", (fused_glue, fused_swiglu))
+
+
+def _decode_graph_worker(rank, world_size, fused_glue):
+    """Two layers, one captured graph, replayed for six positions: every step
+    equals the eager decode step run beside it with its own caches."""
+    from symm_mem_recipes_b200.models.llama_tp_layer import DecodeGraph, LlamaTPConfig, LlamaTPDecoderLayer
+    from symm_mem_recipes_b200.parallel import symm_mem
+
+    dev = torch.device("cuda", rank)
+    cfg = LlamaTPConfig.tiny(world_size)
+    layers = [LlamaTPDecoderLayer(cfg, dev, seed=21 + 100 * i, fused_glue=fused_glue) for i in range(2)]
+    batch, max_seq, steps = 4, 32, 6
+    graph = DecodeGraph(layers, batch, max_seq)
+    symm_mem.check_status(dev)
+    eager_caches = [(torch.zeros(batch, max_seq, lyr.hkv, cfg.head_dim, dtype=torch.bfloat16, device=dev),
+                     torch.zeros(batch, max_seq, lyr.hkv, cfg.head_dim, dtype=torch.bfloat16, device=dev))
+                    for lyr in layers]
+    g = torch.Generator().manual_seed(9)              # same tokens on every rank: activations are replicated
+    failures = []
+    for pos in range(steps):
+        x = (torch.randn(batch, cfg.hidden, generator=g) * 0.5).to(torch.bfloat16).to(dev)
+        got = graph.step(x, pos).clone()
+        want = x
+        for lyr, (kc, vc) in zip(layers, eager_caches):
+            want = lyr.decode(want, kc, vc, pos, fused=True)
+        symm_mem.check_status(dev)
+        err = (got.float() - want.float()).abs().max().item()
+        if err > 5e-2:
+            failures.append(f"position {pos}: graph replay differs from the eager step by {err}")
+    for (kc, vc), (kg, vg) in zip(eager_caches, graph.caches):
+        if not (torch.allclose(kc.float(), kg.float(), atol=2e-2) and torch.allclose(vc.float(), vg.float(), atol=2e-2)):
+            failures.append("KV caches of the graph differ from the eager ones")
+    torch.cuda.synchronize()
+    assert not failures, failures
+
+
+@pytest.mark.gpu
+@pytest.mark.first_run
+@pytest.mark.parametrize("fused_glue", [False, True])
+def test_decode_graph_world_of_one(fused_glue):
+    torch.cuda.set_device(0)
+    _decode_graph_worker(0, 1, fused_glue)
+
+
+@pytest.mark.gpu
+@pytest.mark.first_run
+@pytest.mark.multigpu(2)
+@pytest.mark.parametrize("fused_glue", [False, True])
+def test_decode_graph_2gpu(fused_glue):
+    spawn_ranks(_decode_graph_worker, 2, "nccl", (fused_glue,))

@@ -37,7 +37,8 @@ class _FakeC:
             sum_out.copy_(s)
 
     @staticmethod
-    def rope_inplace(qkv, n_heads, head_dim, seq, pos0, theta, num_sms):
+    def rope_inplace(qkv, n_heads, head_dim, seq, pos0, theta, num_sms, pos=None):
+        pos0 = pos0 if pos is None else int(pos)
         qkv.copy_(REAL_C.oracle_rope_bf16(qkv, n_heads, head_dim, seq, pos0, theta))
 
     @staticmethod
@@ -110,6 +111,29 @@ def test_decode_flow_matches_prefill(host_kernels, fused_glue, shared):
     for pos in range(seq):
         got = layer.decode(xs[:, pos].contiguous(), k_cache, v_cache, pos, fused=True)
         assert (got.float() - want[:, pos].float()).abs().max().item() < 0.1, pos
+
+
+@pytest.mark.parametrize("fused_glue", [False, True])
+def test_static_decode_matches_decode(host_kernels, fused_glue):
+    """The graph-capturable form (position in a tensor, whole-cache attention
+    under a mask, index_copy_ into the caches) against the plain decode step,
+    token by token, with a cache longer than the sequence."""
+    cfg, layer, x, batch, seq, _ = _layer_and_reference(fused_glue, False)
+    xs = x.view(batch, seq, cfg.hidden)
+    caches = [torch.zeros(batch, s_max, layer.hkv, cfg.head_dim, dtype=torch.bfloat16) for s_max in (seq, seq,
+                                                                                                       seq + 5, seq + 5)]
+    (k_a, v_a, k_b, v_b) = caches
+    k_b.fill_(7.0)                                     # stale entries beyond the position must stay hidden
+    v_b.fill_(-3.0)
+    pos_t = torch.zeros(1, dtype=torch.int32)
+    for pos in range(seq):
+        step_in = xs[:, pos].contiguous()
+        want = layer.decode(step_in, k_a, v_a, pos, fused=True)
+        pos_t.fill_(pos)
+        got = layer.decode_static(step_in, k_b, v_b, pos_t, fused=True)
+        assert (got.float() - want.float()).abs().max().item() < 2e-2, pos
+    assert torch.equal(k_b[:, :seq], k_a) and torch.equal(v_b[:, :seq], v_a)
+    assert bool((k_b[:, seq:] == 7.0).all()) and bool((v_b[:, seq:] == -3.0).all())
 
 
 def test_phase_marks_are_off_by_default(host_kernels):

@@ -20,6 +20,8 @@ LINES = [
     ' "N": 8192, "us": 39.52}',
     '{"op": "llama70b_layer_decode", "world_size": 8, "batch": 1, "smr_fused_us": 197.2,'
     ' "nccl_cublas_us": 237.6, "speedup": 1.205}',
+    '{"op": "llama70b_decode_graph", "world_size": 8, "batch": 4, "layers": 2, "cache_entries": 4096,'
+    ' "first_position": 2048, "steps": 32, "graph_us_per_step": 410.0, "eager_us_per_step": 615.0, "speedup": 1.5}',
     '{"truncated": ',
 ]
 PEAKS = {"bf16_tflops": 1647.3, "bf16_tflops_sustained": 1411.0, "hbm_gbs": 6541.5}
@@ -29,7 +31,7 @@ def test_report_tables(tmp_path):
     f = tmp_path / "r.jsonl"
     f.write_text("\n".join(LINES) + "\n")
     recs = report.read_records([str(f)])
-    assert len(recs) == 11                       # the log line and the truncated object are skipped
+    assert len(recs) == 12                       # the log line and the truncated object are skipped
     text = report.render(recs, PEAKS)
     # all-reduce: best of this package and both speed-ups
     row = [ln for ln in text.splitlines() if ln.startswith("| 8 | 4 KiB")][0]
@@ -44,6 +46,8 @@ def test_report_tables(tmp_path):
     row = [ln for ln in text.splitlines() if ln.startswith("| 8 | 3584 x 8192 | 1 |")][0]
     assert "1.75x" in row and "9.0" in row
     assert "decode batch 1" in text and "1.21x" in text
+    row = [ln for ln in text.splitlines() if ln.startswith("| 8 | 2 | 4 | 4096")][0]
+    assert "410.0" in row and "1.50x" in row
 
 
 def test_report_cli_without_peaks(tmp_path, capsys):
