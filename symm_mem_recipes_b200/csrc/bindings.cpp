@@ -462,7 +462,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                         std::shared_ptr<CudaSymmAllocation> aout_alloc, int64_t aout_offset,
                         c10::optional<torch::Tensor> a_out, c10::optional<torch::Tensor> flags,
                         int block_n, int num_sms, int n_copy, uint64_t timeout_ns, bool cta_pair,
-                        c10::optional<torch::Tensor> tail_scratch, int epilogue) {
+                        c10::optional<torch::Tensor> tail_scratch, int epilogue, int l2_hints) {
     const auto dtype = a.scalar_type();
     const bool fp8 = dtype == at::kFloat8_e4m3fn;
     TORCH_CHECK(fp8 || dtype == torch::kBFloat16, "a must be bfloat16 or float8_e4m3fn");
@@ -484,6 +484,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     args.K = (int)a.size(1);
     args.elem_bytes = fp8 ? 1 : 2;
     args.epilogue = epilogue;
+    args.l2_hints = l2_hints;
+    TORCH_CHECK(l2_hints == 0 || (l2_hints >= 1 && l2_hints <= 3 && cta_pair && mode != 1 && !fp8 && epilogue == 0),
+                "L2 eviction hints (1..3) exist on the bf16 CTA-pair kernel with the plain epilogue");
     TORCH_CHECK(epilogue == 0 || (epilogue == 1 && cta_pair && mode != 1 && !fp8),
                 "the SwiGLU epilogue runs on the bf16 CTA-pair kernel (a_out symmetric or absent)");
     args.block_n = block_n;
@@ -542,7 +545,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   }, py::arg("a"), py::arg("b"), py::arg("c"), py::arg("mode"), py::arg("shard_alloc"),
      py::arg("shard_offset"), py::arg("aout_alloc"), py::arg("aout_offset"), py::arg("a_out"),
      py::arg("flags"), py::arg("block_n"), py::arg("num_sms"), py::arg("n_copy"), py::arg("timeout_ns"),
-     py::arg("cta_pair") = false, py::arg("tail_scratch") = py::none(), py::arg("epilogue") = 0);
+     py::arg("cta_pair") = false, py::arg("tail_scratch") = py::none(), py::arg("epilogue") = 0,
+     py::arg("l2_hints") = 0);
 
   m.def("check_push_schedule", &check_push_schedule);
   m.def("check_pair_work", &check_pair_work);

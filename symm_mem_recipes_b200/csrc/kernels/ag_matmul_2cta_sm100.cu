@@ -58,7 +58,7 @@ struct PairSmem {
 // the epilogue writes SiLU(gate) * up, i.e. C is [M, N / 2] and tile ni covers its
 // columns [128 ni, 128 ni + 128).  The activation never makes a round trip through
 // memory and C is half as wide.  The split-K tail is not used with it.
-template <int BN, int STAGES, bool kFp8, bool kSwiGlu = false>
+template <int BN, int STAGES, bool kFp8, bool kSwiGlu = false, bool kL2Hints = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
                       const __grid_constant__ CUtensorMap tmap_a_out,
@@ -123,6 +123,12 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       PairWork w;
+      // B is re-read by every wave of tiles: keep it; A passes through once
+      [[maybe_unused]] uint64_t pol_a = 0, pol_b = 0;
+      if constexpr (kL2Hints) {
+        pol_b = l2_policy_evict_last();
+        pol_a = p.l2_hints >= 2 ? l2_policy_evict_first() : l2_policy_evict_normal();
+      }
       for (int wi = 0; !failed && pair_work(p, pair, n_pairs, total_tiles, k_blocks, wi, w); ++wi) {
         const int t = w.tile;
         const int mi = (t / p.n_tiles_n) * 2 + (int)cta_rank, ni = t % p.n_tiles_n;
@@ -157,8 +163,13 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
           uint8_t* sb = sa + L::kABytes;
           if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2u * L::kStageBytes);
           const uint32_t full_leader = map_to_cta(smem_u32(&full_bar[stage]), 0);
-          tma_load_2d_pair(sa, amap, full_leader, kb * kBKE, row0);
-          tma_load_2d_pair(sb, &tmap_b, full_leader, kb * kBKE, ni * BN + (int)cta_rank * (BN / 2));
+          if constexpr (kL2Hints) {
+            tma_load_2d_pair_hint(sa, amap, full_leader, kb * kBKE, row0, pol_a);
+            tma_load_2d_pair_hint(sb, &tmap_b, full_leader, kb * kBKE, ni * BN + (int)cta_rank * (BN / 2), pol_b);
+          } else {
+            tma_load_2d_pair(sa, amap, full_leader, kb * kBKE, row0);
+            tma_load_2d_pair(sb, &tmap_b, full_leader, kb * kBKE, ni * BN + (int)cta_rank * (BN / 2));
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -212,6 +223,8 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
     const int etid = (int)threadIdx.x - 64;
     int next_piece = (int)blockIdx.x, round = 0;
     const int all_pieces = p.blocks_per_rank * p.pieces;
+    [[maybe_unused]] uint64_t pol_c = 0;               // C is written once and not read again by this kernel
+    if constexpr (kL2Hints) pol_c = l2_policy_evict_first();
     if (p.mode == 2 && !push_entry_barrier(p, (int)blockIdx.x, etid)) failed = true;
     __shared__ int tail_ok;
     PairWork w;
@@ -366,7 +379,12 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
               o.y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
               o.z = pack_bf16x2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
               o.w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
-              st_16(crow + c * 32 + v * 8, o);
+              if constexpr (kL2Hints) {
+                if (p.l2_hints >= 3) st_16_hint(crow + c * 32 + v * 8, o, pol_c);
+                else st_16(crow + c * 32 + v * 8, o);
+              } else {
+                st_16(crow + c * 32 + v * 8, o);
+              }
             }
           }
         }
@@ -400,12 +418,12 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
   }
 }
 
-template <int BN, int STAGES, bool kFp8, bool kSwiGlu = false>
+template <int BN, int STAGES, bool kFp8, bool kSwiGlu = false, bool kL2Hints = false>
 int launch_pair_variant(const CUtensorMap& ta_shard, const CUtensorMap& ta_out, const CUtensorMap& tb,
                         const AgMatmulParams& p, int grid, cudaStream_t stream) {
   using L = PairSmem<BN, STAGES>;
   static_assert(L::kTotal <= 232448, "shared memory limit exceeded");
-  auto kern = ag_matmul_2cta_kernel<BN, STAGES, kFp8, kSwiGlu>;
+  auto kern = ag_matmul_2cta_kernel<BN, STAGES, kFp8, kSwiGlu, kL2Hints>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::kTotal);
   if (e != cudaSuccess) return (int)e;
   kern<<<grid, kGemmThreads, L::kTotal, stream>>>(ta_shard, ta_out, tb, p);
@@ -498,6 +516,16 @@ int launch_ag_matmul_2cta(const AgMatmulArgs& a, cudaStream_t stream) {
       p.tail_counters = a.tail_counters;
       cudaError_t me = cudaMemsetAsync(a.tail_counters, 0, sizeof(uint32_t) * rem * 2, stream);
       if (me != cudaSuccess) return (int)me;
+    }
+  }
+  if (a.l2_hints < 0 || a.l2_hints > 3 || (a.l2_hints != 0 && (fp8 || swiglu))) return cudaErrorInvalidValue;
+  p.l2_hints = a.l2_hints;
+  if (a.l2_hints != 0) {
+    switch (bn) {
+      case 128: return launch_pair_variant<128, 8, false, false, true>(ta_shard, ta_out, tb, p, grid, stream);
+      case 192: return launch_pair_variant<192, 7, false, false, true>(ta_shard, ta_out, tb, p, grid, stream);
+      case 224: return launch_pair_variant<224, 7, false, false, true>(ta_shard, ta_out, tb, p, grid, stream);
+      default:  return launch_pair_variant<256, 6, false, false, true>(ta_shard, ta_out, tb, p, grid, stream);
     }
   }
   if (swiglu) return launch_pair_variant<256, 6, false, true>(ta_shard, ta_out, tb, p, grid, stream);

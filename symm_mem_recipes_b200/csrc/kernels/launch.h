@@ -101,6 +101,9 @@ struct AgMatmulArgs {
   size_t tail_scratch_bytes;
   uint32_t* tail_counters;
   size_t tail_counter_slots;
+  // 2-CTA kernel, bf16, plain epilogue: L2 eviction hints on the operand loads (0 = none;
+  // 1 = B evict_last; 2 = also A evict_first; 3 = also the stores of C evict_first)
+  int l2_hints;
 };
 int launch_ag_matmul(const AgMatmulArgs& args, cudaStream_t stream);
 // Same contract on CTA pairs (tcgen05 cta_group::2, 256 x BN tiles); modes 0 and 2 only.
