@@ -79,12 +79,18 @@ CudaSymmAllocation::CudaSymmAllocation(int device, size_t payload_bytes)
   granularity_ = gran;
   pad_offset_ = round_up(payload_bytes_ == 0 ? 16 : payload_bytes_, 256);
   block_bytes_ = round_up(pad_offset_ + kSignalPadBytes, gran);
-  SMR_CU_CHECK(d.cuMemCreate(&handle_, block_bytes_, &prop, 0));
-  SMR_CU_CHECK(d.cuMemAddressReserve(&va_, block_bytes_, gran, 0, 0));
-  SMR_CU_CHECK(d.cuMemMap(va_, block_bytes_, 0, handle_, 0));
-  set_rw_access(va_, block_bytes_, device_);
-  rt_check(cudaMemset(reinterpret_cast<void*>(va_), 0, block_bytes_), "cudaMemset(block)");
-  rt_check(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+  try {
+    SMR_CU_CHECK(d.cuMemCreate(&handle_, block_bytes_, &prop, 0));
+    SMR_CU_CHECK(d.cuMemAddressReserve(&va_, block_bytes_, gran, 0, 0));
+    SMR_CU_CHECK(d.cuMemMap(va_, block_bytes_, 0, handle_, 0));
+    set_rw_access(va_, block_bytes_, device_);
+    rt_check(cudaMemset(reinterpret_cast<void*>(va_), 0, block_bytes_), "cudaMemset(block)");
+    rt_check(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+  } catch (...) {
+    // a constructor that throws runs no destructor: give back what was obtained so far
+    release();
+    throw;
+  }
 }
 
 CudaSymmAllocation::~CudaSymmAllocation() {
@@ -139,9 +145,9 @@ void CudaSymmAllocation::exchange_and_map(const FdChannel& chan,
     CUdeviceptr va = 0;
     // aligned to the allocation granularity so that the mapping can use large pages
     SMR_CU_CHECK(d.cuMemAddressReserve(&va, block_bytes_, granularity_, 0, 0));
+    peer_va_[m.src_rank] = va;          // recorded at once: release() returns it if a later step throws
     SMR_CU_CHECK(d.cuMemMap(va, block_bytes_, 0, h, 0));
     set_rw_access(va, block_bytes_, device_);
-    peer_va_[m.src_rank] = va;
   }
 }
 
