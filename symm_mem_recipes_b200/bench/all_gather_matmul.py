@@ -30,7 +30,7 @@ UPSTREAM_TABLE = {
 }
 
 
-def main(argv=None, standalone: bool = True) -> int:
+def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser()
     ap.add_argument("--M", type=int, default=4096)
     ap.add_argument("--N", type=int, default=6656)
@@ -54,7 +54,11 @@ def main(argv=None, standalone: bool = True) -> int:
     ap.add_argument("--print-ptxas", "--print_ptx", dest="print_ptxas", action="store_true",
                     help="print what the compiler made of the kernels (registers, spills, shared memory from "
                          "`ptxas -v`); upstream's --print_ptx dumps Triton's PTX at this point")
-    args = ap.parse_args(argv)
+    return ap
+
+
+def main(argv=None, standalone: bool = True) -> int:
+    args = build_parser().parse_args(argv)
 
     from symm_mem_recipes_b200.bench._common import finish, init_distributed
 

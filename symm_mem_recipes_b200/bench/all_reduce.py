@@ -21,7 +21,7 @@ import torch
 import torch.distributed as dist
 
 
-def main(argv=None, standalone: bool = True) -> int:
+def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser()
     ap.add_argument("--min-bytes", type=int, default=4096)
     ap.add_argument("--max-bytes", type=int, default=256 * 1024 * 1024)
@@ -42,7 +42,11 @@ def main(argv=None, standalone: bool = True) -> int:
     ap.add_argument("--multimem-sweep", action="store_true",
                     help="instead of the size sweep: the multimem kernel over CTA counts, unroll factors and both "
                          "barrier kinds at 16, 64 and 256 MiB (clamped to --max-bytes), one start-up")
-    args = ap.parse_args(argv)
+    return ap
+
+
+def main(argv=None, standalone: bool = True) -> int:
+    args = build_parser().parse_args(argv)
 
     from symm_mem_recipes_b200.bench._common import finish, init_distributed
 

@@ -14,13 +14,17 @@ import sys
 import torch
 
 
-def main(argv=None, standalone: bool = True) -> int:
+def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser()
     ap.add_argument("--blocks", default="1,32,148")
     ap.add_argument("--kinds", default="cas",
                     help="comma-separated: cas (blockwise_barrier), epoch, nvls; the counting kinds run the barrier "
                          "twice per launch and are timed on a second allocation")
-    args = ap.parse_args(argv)
+    return ap
+
+
+def main(argv=None, standalone: bool = True) -> int:
+    args = build_parser().parse_args(argv)
     from symm_mem_recipes_b200.bench._common import finish, init_distributed
 
     rank, local_rank, world, dev = init_distributed()

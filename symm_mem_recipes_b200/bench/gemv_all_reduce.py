@@ -21,7 +21,7 @@ import sys
 import torch
 
 
-def main(argv=None, standalone: bool = True) -> int:
+def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser()
     ap.add_argument("--K", type=int, default=3584)
     ap.add_argument("--N", type=int, default=8192)
@@ -29,7 +29,11 @@ def main(argv=None, standalone: bool = True) -> int:
     ap.add_argument("--extra-algos", default="",
                     help="comma-separated kernels to time besides the default one: tc_tagged, simt")
     ap.add_argument("--out", default=None)
-    args = ap.parse_args(argv)
+    return ap
+
+
+def main(argv=None, standalone: bool = True) -> int:
+    args = build_parser().parse_args(argv)
     from symm_mem_recipes_b200.bench._common import finish, init_distributed
 
     rank, local_rank, world, dev = init_distributed()

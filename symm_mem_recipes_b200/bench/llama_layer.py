@@ -24,7 +24,7 @@ import torch
 import torch.distributed as dist
 
 
-def main(argv=None, standalone: bool = True) -> int:
+def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser()
     ap.add_argument("--batch", type=int, default=16)
     ap.add_argument("--seq", type=int, default=2048)
@@ -48,7 +48,11 @@ def main(argv=None, standalone: bool = True) -> int:
                          "against the same steps launched eagerly")
     ap.add_argument("--decode-cache", type=int, default=4096)
     ap.add_argument("--out", default=None)
-    args = ap.parse_args(argv)
+    return ap
+
+
+def main(argv=None, standalone: bool = True) -> int:
+    args = build_parser().parse_args(argv)
     from symm_mem_recipes_b200.bench._common import finish, init_distributed
 
     rank, local_rank, world, dev = init_distributed()

@@ -21,7 +21,7 @@ def main() -> int:
     ap.add_argument("--layer-detail", action="store_true",
                     help="also time the opt-in kernel variants: the layer with the single-pass glue kernels and the "
                          "SwiGLU epilogue, its phases, the prefill without sequence parallelism, the reduce-scatter "
-                         "variants, the tagged GEMV exchange")
+                         "variants, the tagged GEMV exchange, decode from one CUDA graph")
     args = ap.parse_args()
     from symm_mem_recipes_b200.bench import (all_gather_matmul, all_reduce, barrier, gemv_all_reduce,
                                              llama_layer)
@@ -51,7 +51,8 @@ def main() -> int:
                              standalone=False)
     if "layer" in only:
         llama_layer.main(["--out", out("layer")] + (["--fused-glue", "all", "--breakdown", "--tp", "--rs-variants",
-                                                     "cta_pair,deep_strips,thread_stores,cta_pair+thread_stores"]
+                                                     "cta_pair,deep_strips,thread_stores,cta_pair+thread_stores",
+                                                     "--decode-graph", "2"]
                                                     if args.layer_detail
                                                     else []), standalone=False)
     finish()

@@ -109,3 +109,34 @@ def test_roofline_expectations():
     nvls = expect("all_reduce", 8, DEFAULT_PEAKS, nbytes=64 << 20)
     p2p = expect("all_reduce", 8, DEFAULT_PEAKS, nbytes=64 << 20, nvls=False)
     assert nvls["target_us"] < p2p["target_us"] and nvls["bound_by"] == "nvlink"
+
+
+def test_suite_hands_each_benchmark_arguments_its_parser_accepts(monkeypatch, tmp_path):
+    """The suite runner builds argument lists for the other drivers; each list must parse with the
+    driver's own parser (a misspelt flag would otherwise end an 8-GPU run at that benchmark)."""
+    import sys
+
+    import torch
+
+    from symm_mem_recipes_b200.bench import (_common, all_gather_matmul, all_reduce, barrier, gemv_all_reduce,
+                                             llama_layer, suite)
+
+    seen = {}
+    for mod in (all_gather_matmul, all_reduce, barrier, gemv_all_reduce, llama_layer):
+        def fake_main(argv=None, standalone=True, _mod=mod):
+            ns = _mod.build_parser().parse_args(argv)          # argparse exits on an unknown flag
+            seen.setdefault(_mod.__name__.rsplit(".", 1)[1], []).append(ns)
+            return 0
+        monkeypatch.setattr(mod, "main", fake_main)
+    monkeypatch.setattr(_common, "init_distributed", lambda: (0, 0, 8, torch.device("cpu")))
+    monkeypatch.setattr(_common, "finish", lambda: None)
+    monkeypatch.setattr(sys, "argv", ["suite", "--out-dir", str(tmp_path), "--layer-detail", "--with-reference-triton",
+                                      "--only", "barrier,all_reduce,all_gather_matmul,upstream_table,gemv,layer"])
+    assert suite.main() == 0
+    assert set(seen) == {"all_gather_matmul", "all_reduce", "barrier", "gemv_all_reduce", "llama_layer"}
+    assert len(seen["all_gather_matmul"]) == 2 and seen["all_gather_matmul"][1].upstream_table
+    layer = seen["llama_layer"][0]
+    assert layer.fused_glue == "all" and layer.breakdown and layer.tp and layer.decode_graph == 2
+    assert layer.rs_variants.split(",") == ["cta_pair", "deep_strips", "thread_stores", "cta_pair+thread_stores"]
+    assert seen["gemv_all_reduce"][0].extra_algos == "tc_tagged"
+    assert seen["all_reduce"][0].with_reference_triton and seen["all_reduce"][0].out.endswith("all_reduce_ws8.jsonl")
