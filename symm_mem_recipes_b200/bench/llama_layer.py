@@ -187,8 +187,8 @@ def main(argv=None, standalone: bool = True) -> int:
             if world > 1:
                 dist.broadcast(xd, 0)
             graph = DecodeGraph(stack, B, args.decode_cache)
-            first = args.decode_cache // 2
-            steps = 32
+            steps = min(32, args.decode_cache)
+            first = min(args.decode_cache // 2, args.decode_cache - steps)
 
             def replayed():
                 for i in range(steps):

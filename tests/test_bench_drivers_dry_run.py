@@ -1,0 +1,171 @@
+"""The multi-GPU benchmark drivers on two gloo ranks without a GPU: kernels by
+host stand-ins, timers by a single call, the 70B configuration by the tiny
+one.  What is checked is the drivers' own code (argument handling, shapes,
+reference comparisons, the records they emit), so that a GPU run is not spent
+on a typo."""
+import contextlib
+import io
+import json
+import pathlib
+
+import pytest
+import torch
+
+from symm_mem_recipes_b200.utils.testing import spawn_ranks
+
+
+def _prepare(rank, world_size):
+    import torch.distributed as dist
+
+    import test_fused_ops_flow_cpu as flow
+    from symm_mem_recipes_b200.bench import _common
+    from symm_mem_recipes_b200.models import llama_tp_layer
+    from symm_mem_recipes_b200.utils import benchmark
+
+    flow._install_all_stand_ins()
+    dev = torch.device("cpu")
+    _common.init_distributed = lambda default_port=0: (rank, rank, world_size, dev)
+    _common.finish = lambda: None
+
+    def once(fn, *a, **k):
+        fn()
+        return 100.0                                   # "microseconds"
+
+    benchmark.benchmark_with_event = once
+    benchmark.benchmark_with_graph = once
+    torch.cuda.synchronize = lambda device=None: None
+    tiny = llama_tp_layer.LlamaTPConfig.tiny(world_size)
+    llama_tp_layer.LlamaTPConfig.llama3_70b = staticmethod(lambda: tiny)
+    # CUDA events of the per-phase timing: one made-up figure per phase
+    llama_tp_layer.LlamaTPDecoderLayer.phase_times_us = (
+        lambda self, x, batch, seq, iters=5: {"norm": 1.0, "qkv": 2.0, "rest": 3.0})
+
+    class EagerDecodeGraph:                            # replays by running the static step eagerly
+        def __init__(self, layers, batch, max_seq, fused=True, warmup=2):
+            self.layers, self.fused = list(layers), fused
+            cfg = self.layers[0].cfg
+            self.pos = torch.zeros(1, dtype=torch.int32)
+            self.caches = [(torch.zeros(batch, max_seq, lyr.hkv, cfg.head_dim, dtype=torch.bfloat16),
+                            torch.zeros(batch, max_seq, lyr.hkv, cfg.head_dim, dtype=torch.bfloat16))
+                           for lyr in self.layers]
+
+        def step(self, x, pos):
+            self.pos.fill_(pos)
+            for lyr, (kc, vc) in zip(self.layers, self.caches):
+                x = lyr.decode_static(x, kc, vc, self.pos, fused=self.fused)
+            return x
+
+    llama_tp_layer.DecodeGraph = EagerDecodeGraph
+
+    class _Event:
+        def __init__(self, enable_timing=False):
+            pass
+
+        def record(self):
+            pass
+
+        def elapsed_time(self, other):
+            return 3.2
+
+    torch.cuda.Event = _Event
+    return dist
+
+
+def _run(main, argv, rank, out_path):
+    buf = io.StringIO()
+    with contextlib.redirect_stdout(buf):
+        assert main(argv, standalone=False) == 0
+    if rank == 0:
+        pathlib.Path(out_path).write_text(buf.getvalue())
+
+
+def _layer_worker(rank, world_size, out_path):
+    _prepare(rank, world_size)
+    from symm_mem_recipes_b200.bench import llama_layer
+
+    _run(llama_layer.main, ["--batch", "2", "--seq", "128", "--warmup", "1", "--iters", "1", "--fused-glue", "all",
+                            "--breakdown", "--tp", "--rs-variants", "cta_pair,thread_stores,cta_pair+thread_stores",
+                            "--decode-graph", "2", "--decode-cache", "48"], rank, out_path)
+
+
+def _agmm_worker(rank, world_size, out_path):
+    _prepare(rank, world_size)
+    from symm_mem_recipes_b200.bench import all_gather_matmul
+
+    _run(all_gather_matmul.main, ["--M", "512", "--N", "256", "--K", "128", "--warmup", "1", "--iters", "1",
+                                  "--copy-ctas", "4", "--with-push-copy"], rank, out_path)
+
+
+def _gemv_worker(rank, world_size, out_path):
+    _prepare(rank, world_size)
+    from symm_mem_recipes_b200.bench import gemv_all_reduce
+
+    _run(gemv_all_reduce.main, ["--K", "256", "--N", "512", "--batches", "1,4", "--extra-algos", "tc_tagged,simt"],
+         rank, out_path)
+
+
+def _records(path):
+    return [json.loads(ln) for ln in pathlib.Path(path).read_text().splitlines() if ln.startswith("{")]
+
+
+def test_layer_driver(tmp_path):
+    out = tmp_path / "layer.txt"
+    spawn_ranks(_layer_worker, 2, "gloo", (str(out),), timeout_s=240.0)
+    recs = _records(out)
+    ops = [r["op"] for r in recs]
+    assert ops.count("matmul_reduce_scatter") == 2 and ops.count("matmul_reduce_scatter_variant") == 6
+    assert ops.count("llama70b_layer_prefill") == 3 and ops.count("llama70b_layer_prefill_phases") == 3
+    assert ops.count("llama70b_layer_prefill_tp") == 1 and ops.count("llama70b_layer_decode") == 3
+    assert ops.count("llama70b_decode_graph") == 3
+    assert all(r["matches_library"] for r in recs if "matches_library" in r)
+    assert all(r["matches_default"] for r in recs if "matches_default" in r)
+    rs = [r for r in recs if r["op"] == "matmul_reduce_scatter"][0]
+    assert rs["phases"] == {"entered_us": 1.1, "gemm_done_first_us": 8.0, "gemm_done_last_us": 8.5,
+                            "reduced_last_us": 11.5}
+    # and the report renders what the driver wrote
+    from symm_mem_recipes_b200.bench import report
+    text = report.render(recs, None)
+    assert "decode steps replayed from one CUDA graph" in text and "GEMM + reduce-scatter" in text
+
+
+def test_all_gather_matmul_driver(tmp_path):
+    out = tmp_path / "agmm.txt"
+    spawn_ranks(_agmm_worker, 2, "gloo", (str(out),), timeout_s=120.0)
+    recs = _records(out)
+    impls = [(r["impl"], r.get("gather")) for r in recs]
+    assert impls == [("cublas_mm_only", None), ("smr_mm_only", None), ("cublas_plus_nccl", None),
+                     ("nccl_all_gather_only", None), ("smr_fused", "push"), ("smr_fused", "pull"),
+                     ("smr_fused", "push_copy")]
+
+
+def test_gemv_driver(tmp_path):
+    out = tmp_path / "gemv.txt"
+    spawn_ranks(_gemv_worker, 2, "gloo", (str(out),), timeout_s=120.0)
+    recs = _records(out)
+    assert len(recs) >= 4 and all(r["op"] == "gemv_all_reduce" for r in recs)
+
+
+def _all_reduce_worker(rank, world_size, out_path):
+    _prepare(rank, world_size)
+    from symm_mem_recipes_b200.bench import all_reduce
+
+    _run(all_reduce.main, ["--min-bytes", "4096", "--max-bytes", "65536", "--warmup", "1", "--iters", "1"],
+         rank, out_path)
+
+
+def test_all_reduce_driver(tmp_path):
+    """Host backend: the ordered-sum kernels run as their host builds, the multimem kernel is skipped
+    (no multicast mapping), NCCL is gloo."""
+    out = tmp_path / "ar.txt"
+    spawn_ranks(_all_reduce_worker, 2, "gloo", (str(out),), timeout_s=120.0)
+    recs = _records(out)
+    checks = [r for r in recs if r["op"] == "all_reduce_check"]
+    assert checks[0]["output_equals_world_size"] is True
+    assert {r["impl"] for r in checks[1:]} == {"one_shot", "two_shot", "low_latency"} and all(r["ok"] for r in checks[1:])
+    timed = [r for r in recs if r["op"] == "all_reduce"]
+    assert {r["bytes"] for r in timed} == {4096, 8192, 16384, 32768, 65536}
+    assert {"nccl", "low_latency", "one_shot", "two_shot"} <= {r["impl"] for r in timed}
+    # the tuning tool reads what the driver writes
+    from symm_mem_recipes_b200.bench import tune_all_reduce
+    table = tune_all_reduce.thresholds(timed)
+    assert set(table["by_world_size"]) == {"2"}

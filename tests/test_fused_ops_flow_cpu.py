@@ -241,6 +241,8 @@ def _install_row_parallel_and_glue_stand_ins():
                                   cta_pair=False, thread_stores=False):
             rank, rows = dist.get_rank(), out.shape[0]
             out.copy_(summed(a, b)[rank * rows:(rank + 1) * rows].to(out.dtype))
+            if trace is not None:                                # [CTA][start, entered, GEMM done, reduced] in ns
+                trace.view(-1, 4)[:2] = torch.tensor([[1000, 2000, 9000, 12000], [1100, 2100, 9500, 12500]])
 
         @staticmethod
         def matmul_all_reduce(a, b, out, out_alloc, out_offset, workspace, num_sms, timeout_ns, cta_pair=False):
@@ -305,14 +307,13 @@ def test_decoder_layer_host_flow_two_ranks(fused_glue, fused_swiglu):
     spawn_ranks(_layer_flow_worker, 2, "gloo", (fused_glue, fused_swiglu))
 
 
-def _selfcheck_worker(rank, world_size):
-    """The self-check program's own logic (shapes, references, outcome agreement) with host
-    stand-ins for the kernels: a wrong reference there would cost GPU time to find."""
+def _install_all_stand_ins():
+    """Every kernel entry point the ops reach, as host code over gloo and the POSIX-shm symmetric
+    memory; NCCL-only collectives of the library compositions re-expressed with what gloo has."""
     import importlib
 
     import torch.distributed as dist
 
-    from symm_mem_recipes_b200 import selfcheck
     from symm_mem_recipes_b200._ext import C as real
     from symm_mem_recipes_b200.parallel import symm_mem
 
@@ -362,6 +363,16 @@ def _selfcheck_worker(rank, world_size):
         out.copy_(full[dist.get_rank() * rows:(dist.get_rank() + 1) * rows].to(out.dtype))
 
     dist.reduce_scatter_tensor = reduce_scatter_by_all_reduce
+
+
+def _selfcheck_worker(rank, world_size):
+    """The self-check program's own logic (shapes, references, outcome agreement) with host
+    stand-ins for the kernels: a wrong reference there would cost GPU time to find."""
+    import torch.distributed as dist
+
+    from symm_mem_recipes_b200 import selfcheck
+
+    _install_all_stand_ins()
 
     failures, ran = [], 0
     for group, name, pending, fn in selfcheck.build_checks(True, world_size, rank, torch.device("cpu")):
