@@ -169,3 +169,94 @@ def test_all_reduce_driver(tmp_path):
     from symm_mem_recipes_b200.bench import tune_all_reduce
     table = tune_all_reduce.thresholds(timed)
     assert set(table["by_world_size"]) == {"2"}
+
+
+class _FakeTorchOneGpu:
+    """`torch` as the single-GPU driver sees it: the only device is the CPU."""
+
+    def __init__(self):
+        import types
+        self.cuda = types.SimpleNamespace(set_device=lambda d: None, synchronize=lambda d=None: None)
+
+    def __getattr__(self, name):
+        return getattr(torch, name)
+
+    @staticmethod
+    def device(*args):
+        return torch.device("cpu")
+
+
+@pytest.mark.parametrize("argv", [
+    ["--M", "256", "--N", "512", "--K", "128", "--l2-hints", "sweep"],
+    ["--M", "256", "--N", "512", "--K", "128", "--variant", "fp8"],
+    ["--M", "256", "--N", "512", "--K", "128", "--variant", "swiglu"],
+    ["--op", "gemv", "--batch", "4", "--K", "256", "--N", "512", "--gemv-algo", "tc_tagged"],
+    ["--op", "gemv", "--batch", "4", "--eager"],
+    ["--op", "glue", "--M", "64"],
+    ["--op", "all_reduce", "--bytes", "65536"],
+])
+def test_single_gpu_driver(monkeypatch, capsys, argv):
+    import importlib
+    import sys
+
+    import test_fused_ops_flow_cpu as flow
+    from symm_mem_recipes_b200._ext import C as real
+    from symm_mem_recipes_b200.bench import matmul as driver
+    from symm_mem_recipes_b200.parallel import symm_mem
+    from symm_mem_recipes_b200.utils import benchmark
+
+    ag_mod = importlib.import_module("symm_mem_recipes_b200.ops.ag_matmul")
+    gemv_mod = importlib.import_module("symm_mem_recipes_b200.ops.gemv_all_reduce")
+    rs_mod = importlib.import_module("symm_mem_recipes_b200.ops.matmul_reduce_scatter")
+    glue_mod = importlib.import_module("symm_mem_recipes_b200.ops.layer_glue")
+    saved = [(m, k, getattr(m, k)) for m in (ag_mod, gemv_mod, rs_mod, glue_mod)
+             for k in ("C", "_num_sms", "_check", "_check_2d", "_tail_buffer") if hasattr(m, k)]
+    try:
+        flow._install_host_kernels()
+        flow._install_row_parallel_and_glue_stand_ins()
+
+        class GemvFake:
+            def __getattr__(self, name):
+                return getattr(real, name)
+
+            @staticmethod
+            def gemv_all_reduce(x, w, out, workspace, ws_offset, timeout_ns, tensor_core=False, num_sms=148,
+                                tagged=False, weights_nk=False):
+                out.copy_((x.float() @ (w.float().t() if weights_nk else w.float())).to(out.dtype))
+
+        gemv_mod.C = GemvFake()
+        gemv_mod._num_sms = lambda device: 148
+        monkeypatch.setattr(driver, "torch", _FakeTorchOneGpu())
+        monkeypatch.setattr(symm_mem, "check_status", lambda device=None: None)
+        monkeypatch.setattr(benchmark, "benchmark_with_event", lambda fn, *a, **k: (fn(), 50.0)[1])
+        monkeypatch.setattr(benchmark, "benchmark_with_graph", lambda fn, *a, **k: (fn(), 50.0)[1])
+
+        class Clocks:
+            def __init__(self, *a, **k):
+                pass
+
+            def __enter__(self):
+                return self
+
+            def __exit__(self, *exc):
+                return False
+
+            def summary(self):
+                return {"sm_mhz": 1500.0}
+
+        monkeypatch.setattr(benchmark, "ClockSampler", Clocks)
+        monkeypatch.setattr(sys, "argv", ["matmul"] + argv)
+        real_randn = torch.randn
+        monkeypatch.setattr(torch, "randn", lambda *shape, device=None, **kw: real_randn(*shape, **kw))
+        real_empty, real_ones = torch.empty, torch.ones
+        monkeypatch.setattr(torch, "empty", lambda *shape, device=None, **kw: real_empty(*shape, **kw))
+        monkeypatch.setattr(torch, "ones", lambda *shape, device=None, **kw: real_ones(*shape, **kw))
+        assert driver.main() == 0
+    finally:
+        for m, k, v in saved:
+            setattr(m, k, v)
+        symm_mem.reset()
+    rec = json.loads([ln for ln in capsys.readouterr().out.splitlines() if ln.startswith("{")][-1])
+    assert rec["op"] == (argv[1] if argv[0] == "--op" else "matmul") and "clocks" in rec
+    if "--l2-hints" in argv:
+        assert {"smr_us", "smr_l2_hints_1_us", "smr_l2_hints_2_us", "smr_l2_hints_3_us"} <= set(rec)
