@@ -49,6 +49,9 @@ def _map_cuda_to_cpu():
         return real_empty(*size, dtype=dtype, device="cpu")
 
     symm_mem.empty = empty
+    ag_mod = importlib.import_module("symm_mem_recipes_b200.ops.ag_matmul")
+    real_gather_buffer = ag_mod.gather_buffer
+    ag_mod.gather_buffer = lambda M, K, device, *a, **k: real_gather_buffer(M, K, torch.device("cpu"), *a, **k)
     import symm_mem_recipes_b200.utils.testing as testing
     real_guarded = testing.guarded_empty
     testing.guarded_empty = lambda shape, dtype, device, *a, **k: real_guarded(shape, dtype, "cpu", *a, **k)
@@ -81,6 +84,8 @@ def _dry(rank, world_size, module, fn_name, args, by_name):
     _map_cuda_to_cpu()
     flow._install_all_stand_ins()
     _eager_decode_graph()
+    import symm_mem_recipes_b200 as smr
+    smr.barrier_test = lambda hdl, num_blocks=32, **k: hdl.barrier()     # the kernel form exists on the GPU only
     mod = importlib.import_module(module)
     for dep in ("guarded_empty",):                     # names the test modules imported before the mapping
         if hasattr(mod, dep):
@@ -105,10 +110,14 @@ WORKERS = [
     ("test_gpu_llama_layer", "_layer_tp_worker", (2,), (True, True)),
     ("test_gpu_llama_layer", "_decode_graph_worker", (1, 2), (True,)),
     ("test_gpu_symm_mem", "_signals_gpu_worker", (2,), ()),
+    ("test_gpu_symm_mem", "_compat_gpu_worker", (2,), ()),
+    ("test_gpu_matmul", "_agmm_worker", (2,), (128, 256, 256, 1, "push_copy")),
+    ("test_gpu_matmul", "_agmm_worker", (2,), (128, 256, 256, 2, "pull")),
+    ("test_gpu_matmul", "_agmm_worker", (2,), (128, 256, 256, 0, "internal", True)),
 ]
 
 
-@pytest.mark.parametrize("module,worker,worlds,args", WORKERS, ids=[f"{m}.{w}" for m, w, _, _ in WORKERS])
+@pytest.mark.parametrize("module,worker,worlds,args", WORKERS, ids=[f"{m}.{w}{i}" for i, (m, w, _, _) in enumerate(WORKERS)])
 def test_gpu_test_worker_runs_on_the_cpu(module, worker, worlds, args):
     mod = importlib.import_module(module)
     assert hasattr(mod, worker), f"{module} has no {worker}"
