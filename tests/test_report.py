@@ -140,3 +140,26 @@ def test_suite_hands_each_benchmark_arguments_its_parser_accepts(monkeypatch, tm
     assert layer.rs_variants.split(",") == ["cta_pair", "deep_strips", "thread_stores", "cta_pair+thread_stores"]
     assert seen["gemv_all_reduce"][0].extra_algos == "tc_tagged"
     assert seen["all_reduce"][0].with_reference_triton and seen["all_reduce"][0].out.endswith("all_reduce_ws8.jsonl")
+
+
+def test_ncu_summary_from_raw_csv():
+    """The raw-page CSV of Nsight Compute (header row, unit row, one row per launch) into the
+    Markdown summary kept under profiles/, with the derived roofline figures."""
+    from symm_mem_recipes_b200.bench import ncu_summary
+
+    header = ["ID", "Kernel Name", "gpu__time_duration.sum", "dram__bytes_read.sum", "dram__bytes_write.sum",
+              "sm__pipe_tensor_cycles_active.avg.pct_of_peak_sustained_active", "launch__registers_per_thread",
+              "launch__shared_mem_per_block_dynamic", "launch__grid_size"]
+    units = ["", "", "us", "Mbyte", "Mbyte", "%", "register/thread", "Kbyte/block", ""]
+    row = ["0", "void smr::kernel<256, 6>(Params)", "182.912", "249.496064", "22.527232", "92.063681", "151",
+           "197.8", "148"]
+    text = "==PROF== some banner\n" + "\n".join(",".join(f'"{c}"' for c in r) for r in (header, units, row)) + "\n"
+    launches = ncu_summary.parse_raw_csv(text)
+    assert len(launches) == 1 and launches[0]["launch__grid_size"] == ("148", "")
+    md = ncu_summary.render(launches, title="GEMM", command="ncu ... python -m x", flops=2.405e11, nbytes=1.55e8,
+                            peaks={"hbm_gbs": 6541.5, "bf16_tflops": 1647.3})
+    assert "# GEMM" in md and "182.9 µs" in md and "92.1 %" in md and "249.5 MB" in md and "197.8 KB" in md
+    # 272.0 MB in 182.9 µs = 1487 GB/s = 0.23 of the copy rate; 1.75x the algorithmic bytes; 1315 TFLOPS = 0.80
+    assert "272.0 MB at 1487 GB/s" in md and "1.75x" in md and "0.23 of the measured copy rate" in md
+    assert "1315 TFLOPS" in md and "0.80 of the measured burst" in md
+    assert ncu_summary.render([], "x") == "no captured launch in the report\n"
