@@ -29,6 +29,9 @@ def _us(amount: float, rate_per_s: float) -> float:
 
 def expect(op: str, ws: int, peaks: dict, M: int = 0, N: int = 0, K: int = 0, batch: int = 0,
            nbytes: int = 0, nvls: bool = True) -> dict:
+    """Time each resource needs for one call of `op` at world size `ws` (tensor
+    cores, HBM, NVLink in and out, at the given peaks), the largest of them as
+    `target_us`, and which one it is (`bound_by`)."""
     tflops, hbm = peaks["bf16_tflops"] * 1e12, peaks["hbm_gbs"] * 1e9
     link = NVLINK_GBS * 1e9
     parts: dict[str, float] = {}

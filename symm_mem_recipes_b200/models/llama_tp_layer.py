@@ -50,6 +50,8 @@ from ..parallel import symm_mem
 
 @dataclass
 class LlamaTPConfig:
+    """Shape of the un-sharded layer; the defaults are Llama-3-70B.  Heads, KV
+    heads and the FFN width must divide by the world size."""
     hidden: int = 8192
     n_heads: int = 64
     n_kv_heads: int = 8
@@ -411,11 +413,15 @@ class DecodeGraph:
         return h
 
     def reset(self) -> None:
+        """Start a new sequence: the KV caches are zeroed (the graph is kept)."""
         for kc, vc in self.caches:
             kc.zero_()
             vc.zero_()
 
     def step(self, x: torch.Tensor, pos: int) -> torch.Tensor:
+        """One token at position `pos` for every sequence of the batch: copies
+        `x` [B, H] into the graph's input, replays, and returns the graph's
+        output tensor (overwritten by the next step)."""
         if not 0 <= pos < self.max_seq:
             raise ValueError(f"position {pos} outside the cache of {self.max_seq} entries")
         self.x.copy_(x)

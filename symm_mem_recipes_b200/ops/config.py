@@ -16,6 +16,11 @@ def _env_int(name: str, default: int) -> int:
 
 @dataclass
 class AllReduceConfig:
+    """Thresholds and launch sizes of the all-reduce kernels (the upstream
+    wrapper hard-codes its own: 512 threads, at most 24 CTAs,
+    symm_mem_recipes/triton_one_shot_all_reduce.py:97-109).  Every field has an
+    SMR_AR_* environment override; `from_tuning` loads thresholds derived from
+    a measured sweep."""
     # Message sizes (bytes) up to which each algorithm is picked by `algo="auto"`.
     # low-latency push kernel (tagged words, no barrier) up to this size ...
     ll_max_bytes: int = _env_int("SMR_AR_LL_MAX_BYTES", 256 * 1024)

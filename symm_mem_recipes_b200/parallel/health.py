@@ -41,6 +41,11 @@ class PeerLost(SymmMemError):
 
 
 class Heartbeat:
+    """Host-side liveness over the group's Store: a background thread of every
+    rank publishes a time stamp every `interval_s`; `check()` raises `PeerLost`
+    naming a rank that announced its leave (`stop()`) or whose stamp is stale.
+    Call `check()` between steps, before launching kernels that wait on peers."""
+
     def __init__(self, group=None, interval_s: float = 0.5, store=None, rank: Optional[int] = None,
                  world_size: Optional[int] = None, namespace: str = "smr_health"):
         """`store`, `rank`, `world_size` default to those of `group` (the default

@@ -33,6 +33,7 @@ class StoreExchange:
         self._seq = 0
 
     def all_gather(self, obj) -> list:
+        """Every rank's picklable `obj`, in rank order (collective; raises when a rank stays away past the timeout)."""
         seq = self._seq
         self._seq += 1
         self.store.set(f"{seq}/{self.rank}", pickle.dumps(obj))

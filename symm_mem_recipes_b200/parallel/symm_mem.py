@@ -90,6 +90,7 @@ def enable_symm_mem_for_group(group_name: Optional[str] = None) -> None:
 
 
 def multicast_supported(device: Optional[torch.device] = None) -> bool:
+    """Whether the GPU reports NVLink multicast (NVLS) support; False without a GPU."""
     if not torch.cuda.is_available():
         return False
     dev = torch.device(device or "cuda")
@@ -157,6 +158,7 @@ def _find_record(t: torch.Tensor) -> tuple[_Record, int]:
 
 
 def is_symm_mem_tensor(t: torch.Tensor) -> bool:
+    """Whether `t` (or the storage it views) lives in an allocation made by `empty()`."""
     try:
         _find_record(t)
         return True
@@ -197,11 +199,13 @@ class SymmetricMemory:
     # ---- raw pointers (device tables of WS pointers, as integers) ----
     @property
     def buffer_ptrs_dev(self) -> int:
+        """Device address of the table of WS payload pointers (what upstream's kernels take as `buffer_ptrs_dev`)."""
         self._need_cuda("buffer_ptrs_dev")
         return self._alloc.buffer_ptrs_dev
 
     @property
     def signal_pad_ptrs_dev(self) -> int:
+        """Device address of the table of WS signal-pad pointers (symm_mem_recipes/triton_barrier.py:167-169)."""
         self._need_cuda("signal_pad_ptrs_dev")
         return self._alloc.signal_pad_ptrs_dev
 
@@ -230,6 +234,8 @@ class SymmetricMemory:
         return C.host_view(self._alloc, int(rank), sizes, dtype, off)
 
     def get_multicast_buffer(self, sizes, dtype: torch.dtype, storage_offset: int = 0) -> torch.Tensor:
+        """View of the payload through its NVLink multicast mapping: a store lands in every
+        rank's copy; only `multimem.*` instructions and plain stores may touch it."""
         self._need_cuda("multicast views")
         off = int(storage_offset) * torch.empty((), dtype=dtype).element_size()
         return C.cuda_view(self._alloc, -1, [int(s) for s in sizes], dtype, off, True)
