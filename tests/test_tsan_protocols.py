@@ -16,14 +16,14 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CSRC = os.path.join(ROOT, "symm_mem_recipes_b200", "csrc")
 
 
-def _build(tmp_path_factory, sanitizers: str) -> str:
+def _build(tmp_path_factory, sanitizers: str, program: str = "protocol_stress") -> str:
     if shutil.which("g++") is None:
         pytest.skip("no g++")
     cuda_inc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "include")
-    out = str(tmp_path_factory.mktemp("san") / "protocol_stress")
+    out = str(tmp_path_factory.mktemp("san") / program)
     cmd = ["g++", "-std=c++17", "-O1", "-g", f"-fsanitize={sanitizers}", "-fno-sanitize-recover=all", "-I", CSRC,
            "-I", cuda_inc,
-           os.path.join(ROOT, "tests", "native", "protocol_stress.cpp"),
+           os.path.join(ROOT, "tests", "native", program + ".cpp"),
            os.path.join(CSRC, "symm", "host_backend.cpp"), os.path.join(CSRC, "oracle", "cpu_reference.cpp"),
            "-o", out, "-lpthread", "-lrt"]
     built = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
@@ -57,3 +57,27 @@ def test_protocols_are_clean_under_asan_and_ubsan(stress_binary_asan):
     assert run.returncode == 0, (run.returncode, run.stdout[-500:], run.stderr[-2000:])
     assert "failures=0" in run.stdout and "ERROR: AddressSanitizer" not in run.stderr
     assert "runtime error" not in run.stderr
+
+
+@pytest.fixture(scope="module")
+def fused_stress_binary(tmp_path_factory):
+    return _build(tmp_path_factory, "thread", "fused_protocol_stress")
+
+
+@pytest.mark.parametrize("world_size,ctas,calls", [(2, 3, 200), (4, 3, 100), (8, 2, 40)])
+def test_fused_kernel_protocol_is_race_free_under_tsan(fused_stress_binary, world_size, ctas, calls):
+    """Arrival counters that count calls, the call number published by the last CTA, the entry
+    barrier per CTA index: the protocol of matmul_reduce_scatter and of the push gather, one
+    thread per CTA."""
+    run = subprocess.run([fused_stress_binary, str(world_size), str(ctas), str(calls)], capture_output=True,
+                         text=True, timeout=600, env={**os.environ, "TSAN_OPTIONS": "halt_on_error=0 exitcode=66"})
+    assert "WARNING: ThreadSanitizer" not in run.stderr, run.stderr[-2000:]
+    assert run.returncode == 0 and "failures=0" in run.stdout, (run.returncode, run.stdout[-500:])
+
+
+def test_fused_kernel_protocol_needs_its_entry_barrier(fused_stress_binary):
+    """Without the entry barrier a rank's stores of call n + 1 race with a slower rank's reads of
+    call n: the model must show it (so a clean run above means something)."""
+    run = subprocess.run([fused_stress_binary, "4", "3", "150", "no-entry-barrier"], capture_output=True, text=True,
+                         timeout=600, env={**os.environ, "TSAN_OPTIONS": "halt_on_error=0 exitcode=66"})
+    assert "WARNING: ThreadSanitizer: data race" in run.stderr or "failures=0" not in run.stdout
