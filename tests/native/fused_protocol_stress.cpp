@@ -34,10 +34,67 @@ constexpr int kWords = 32;           // payload words per (source, tile)
 uint32_t value_of(int call, int src, int tile, int w) { return (uint32_t)(call * 1000003 + src * 8191 + tile * 131 + w); }
 }  // namespace
 
+// The exchange of the fused GEMV + all-reduce (gemv_allreduce*.cu): no barrier at all.  CTA (tile) of
+// every rank stores its partial into slot [rank] of the tile's inbox on EVERY rank, in the half
+// selected by the parity of the call number, then release-stores the call number into its flag there;
+// it acquire-waits until all world-size flags of the tile (its own rank's copy) carry the call
+// number and reads the partials in slot order.  Two halves suffice because a rank can be at most
+// one call ahead of any other: it cannot finish call n + 1 without the partial that the slowest
+// rank pushes only after its own call n has ended.  `one_parity` uses a single half, which must fail.
+int gemv_model(int ws, int tiles, int calls, bool one_parity) {
+  const int halves = one_parity ? 1 : 2;
+  std::vector<std::vector<uint32_t>> inbox(ws, std::vector<uint32_t>((size_t)halves * tiles * ws * kWords, 0));
+  std::vector<std::vector<uint32_t>> flags(ws, std::vector<uint32_t>((size_t)halves * tiles * ws, 0));
+  std::vector<uint32_t> header(ws * 2, 0);                  // per rank: [0] call number, [1] CTAs done
+  std::vector<pthread_barrier_t> stream(ws);
+  for (auto& b : stream) pthread_barrier_init(&b, nullptr, tiles);
+  std::vector<int> bad((size_t)ws * tiles, 0);
+  std::vector<std::thread> th;
+  for (int r = 0; r < ws; ++r)
+    for (int t = 0; t < tiles; ++t)
+      th.emplace_back([&, r, t] {
+        int& failures = bad[(size_t)r * tiles + t];
+        for (int call = 1; call <= calls; ++call) {
+          const uint32_t epoch = __atomic_load_n(&header[r * 2], __ATOMIC_RELAXED) + 1u;
+          if (epoch != (uint32_t)call) failures++;
+          const size_t half = one_parity ? 0 : (epoch & 1u);
+          for (int j = 1; j <= ws; ++j) {                       // own inbox last
+            const int peer = (r + j) % ws;
+            uint32_t* dst = inbox[peer].data() + ((half * tiles + t) * ws + r) * kWords;
+            for (int w = 0; w < kWords; ++w) dst[w] = value_of(call, r, t, w);
+          }
+          for (int peer = 0; peer < ws; ++peer)
+            __atomic_store_n(&flags[peer][(half * tiles + t) * ws + r], epoch, __ATOMIC_RELEASE);
+          for (int s = 0; s < ws; ++s) {
+            long spins = 0;
+            while (__atomic_load_n(&flags[r][(half * tiles + t) * ws + s], __ATOMIC_ACQUIRE) != epoch) {
+              if (++spins > 400000000L) { failures++; break; }
+              std::this_thread::yield();
+            }
+            const uint32_t* src = inbox[r].data() + ((half * tiles + t) * ws + s) * kWords;
+            for (int w = 0; w < kWords; ++w)
+              if (src[w] != value_of(call, s, t, w)) failures++;
+          }
+          const uint32_t done = __atomic_fetch_add(&header[r * 2 + 1], 1u, __ATOMIC_ACQ_REL);
+          if (done == (uint32_t)tiles - 1u) {
+            __atomic_store_n(&header[r * 2 + 1], 0u, __ATOMIC_RELAXED);
+            __atomic_store_n(&header[r * 2], epoch, __ATOMIC_RELEASE);
+          }
+          pthread_barrier_wait(&stream[r]);
+        }
+      });
+  for (auto& t : th) t.join();
+  int total = 0;
+  for (int b : bad) total += b;
+  printf("gemv ws=%d tiles=%d calls=%d halves=%d failures=%d\n", ws, tiles, calls, halves, total);
+  return total != 0;
+}
+
 int main(int argc, char** argv) {
   const int ws = argc > 1 ? atoi(argv[1]) : 4;
   const int ctas = argc > 2 ? atoi(argv[2]) : 3;
   const int calls = argc > 3 ? atoi(argv[3]) : 100;
+  if (argc > 4 && strncmp(argv[4], "gemv", 4) == 0) return gemv_model(ws, ctas, calls, strcmp(argv[4], "gemv-one-parity") == 0);
   const bool entry_barrier = !(argc > 4 && strcmp(argv[4], "no-entry-barrier") == 0);
   const uint64_t timeout_ns = 20000000000ull;
 

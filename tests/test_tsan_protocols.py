@@ -81,3 +81,20 @@ def test_fused_kernel_protocol_needs_its_entry_barrier(fused_stress_binary):
     run = subprocess.run([fused_stress_binary, "4", "3", "150", "no-entry-barrier"], capture_output=True, text=True,
                          timeout=600, env={**os.environ, "TSAN_OPTIONS": "halt_on_error=0 exitcode=66"})
     assert "WARNING: ThreadSanitizer: data race" in run.stderr or "failures=0" not in run.stdout
+
+
+@pytest.mark.parametrize("world_size,tiles,calls", [(2, 3, 300), (4, 2, 150), (8, 2, 40)])
+def test_gemv_exchange_is_race_free_under_tsan(fused_stress_binary, world_size, tiles, calls):
+    """The barrier-free exchange of the fused GEMV + all-reduce: partials into the half of the inbox
+    chosen by the parity of the call number, the call number as the flag."""
+    run = subprocess.run([fused_stress_binary, str(world_size), str(tiles), str(calls), "gemv"], capture_output=True,
+                         text=True, timeout=600, env={**os.environ, "TSAN_OPTIONS": "halt_on_error=0 exitcode=66"})
+    assert "WARNING: ThreadSanitizer" not in run.stderr, run.stderr[-2000:]
+    assert run.returncode == 0 and "failures=0" in run.stdout, (run.returncode, run.stdout[-500:])
+
+
+def test_gemv_exchange_needs_both_halves(fused_stress_binary):
+    """With one half a rank that is a call ahead overwrites partials a slower rank still reads."""
+    run = subprocess.run([fused_stress_binary, "4", "2", "300", "gemv-one-parity"], capture_output=True, text=True,
+                         timeout=600, env={**os.environ, "TSAN_OPTIONS": "halt_on_error=0 exitcode=66"})
+    assert "WARNING: ThreadSanitizer: data race" in run.stderr or "failures=0" not in run.stdout
