@@ -68,7 +68,8 @@ int gemv_model(int ws, int tiles, int calls, bool one_parity) {
           for (int s = 0; s < ws; ++s) {
             long spins = 0;
             while (__atomic_load_n(&flags[r][(half * tiles + t) * ws + s], __ATOMIC_ACQUIRE) != epoch) {
-              if (++spins > 400000000L) { failures++; break; }
+              // with one half a flag can be overwritten by the next call before it is seen: give up soon there
+              if (++spins > (one_parity ? 200000L : 400000000L)) { failures++; break; }
               std::this_thread::yield();
             }
             const uint32_t* src = inbox[r].data() + ((half * tiles + t) * ws + s) * kWords;

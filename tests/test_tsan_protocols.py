@@ -95,6 +95,6 @@ def test_gemv_exchange_is_race_free_under_tsan(fused_stress_binary, world_size, 
 
 def test_gemv_exchange_needs_both_halves(fused_stress_binary):
     """With one half a rank that is a call ahead overwrites partials a slower rank still reads."""
-    run = subprocess.run([fused_stress_binary, "4", "2", "300", "gemv-one-parity"], capture_output=True, text=True,
+    run = subprocess.run([fused_stress_binary, "4", "2", "100", "gemv-one-parity"], capture_output=True, text=True,
                          timeout=600, env={**os.environ, "TSAN_OPTIONS": "halt_on_error=0 exitcode=66"})
     assert "WARNING: ThreadSanitizer: data race" in run.stderr or "failures=0" not in run.stdout
