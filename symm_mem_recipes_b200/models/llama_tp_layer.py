@@ -311,8 +311,14 @@ class LlamaTPDecoderLayer:
     def _decode_norm(self, t: torch.Tensor, w: torch.Tensor, glue: bool) -> torch.Tensor:
         return ops.rms_norm(t, w, self.cfg.eps) if glue else _rms_norm(t, w, self.cfg.eps)
 
-    def _decode_mlp(self, x1: torch.Tensor, fused: bool, glue: bool) -> torch.Tensor:
-        gu = self._decode_norm(x1, self.norm2, glue) @ self.w_gate_up.t()
+    def _decode_mlp(self, x: torch.Tensor, o_proj: torch.Tensor, fused: bool, glue: bool) -> torch.Tensor:
+        """Second half of a decode step: residual add of the attention output, norm, MLP, residual add."""
+        if glue:
+            h2, x1 = ops.rms_norm(o_proj, self.norm2, self.cfg.eps, residual=x)    # x1 = x + o_proj, one kernel
+        else:
+            x1 = x + o_proj
+            h2 = _rms_norm(x1, self.norm2, self.cfg.eps)
+        gu = h2 @ self.w_gate_up.t()
         act = ops.silu_mul(gu) if glue else LlamaTPDecoderLayer._mlp_act_torch(gu, self.ffn_local)
         return x1 + self._row_parallel_decode(act, "down", fused)
 
@@ -335,8 +341,8 @@ class LlamaTPDecoderLayer:
         v_cache[:, pos] = v.view(B, hkv, D)
         o = F.scaled_dot_product_attention(q.transpose(1, 2), k_cache[:, : pos + 1].transpose(1, 2),
                                            v_cache[:, : pos + 1].transpose(1, 2), enable_gqa=True)
-        x1 = x + self._row_parallel_decode(o.transpose(1, 2).reshape(B, hq * D).contiguous(), "o", fused)
-        return self._decode_mlp(x1, fused, glue)
+        o_proj = self._row_parallel_decode(o.transpose(1, 2).reshape(B, hq * D).contiguous(), "o", fused)
+        return self._decode_mlp(x, o_proj, fused, glue)
 
     def decode_static(self, x: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, pos: torch.Tensor,
                       fused: bool = True) -> torch.Tensor:
@@ -363,8 +369,8 @@ class LlamaTPDecoderLayer:
         visible = (torch.arange(s_max, device=x.device, dtype=torch.int32) <= pos.view(1)).view(1, 1, 1, s_max)
         o = F.scaled_dot_product_attention(q.transpose(1, 2), k_cache.transpose(1, 2), v_cache.transpose(1, 2),
                                            attn_mask=visible, enable_gqa=True)
-        x1 = x + self._row_parallel_decode(o.transpose(1, 2).reshape(B, hq * D).contiguous(), "o", fused)
-        return self._decode_mlp(x1, fused, glue)
+        o_proj = self._row_parallel_decode(o.transpose(1, 2).reshape(B, hq * D).contiguous(), "o", fused)
+        return self._decode_mlp(x, o_proj, fused, glue)
 
 
 class DecodeGraph:
