@@ -124,8 +124,10 @@ def main(argv=None, standalone: bool = True) -> int:
                          "all": [(False, False), (True, False), (True, True)]}[args.fused_glue]
         x = (torch.randn(T // world, cfg.hidden, device=dev) * 0.5).to(torch.bfloat16)
         us_r = None
+        decode_layers = {}                     # fused_glue -> a layer built that way (decode ignores fused_swiglu)
         for glue, swiglu in glue_variants:
             layer = LlamaTPDecoderLayer(cfg, dev, seed=1, fused_glue=glue, fused_swiglu=swiglu)
+            decode_layers.setdefault(layer.fused_glue, layer)
             y = layer.forward(x, args.batch, args.seq)
             symm_mem.check_status(dev)
             y_ref = layer.forward_reference(x, args.batch, args.seq)
@@ -167,16 +169,22 @@ def main(argv=None, standalone: bool = True) -> int:
             xd = (torch.randn(B, cfg.hidden, device=dev) * 0.5).to(torch.bfloat16)
             if world > 1:
                 dist.broadcast(xd, 0)
-            kc = torch.zeros(B, 64, layer.hkv, cfg.head_dim, dtype=torch.bfloat16, device=dev)
-            vc = torch.zeros_like(kc)
-            layer.decode(xd, kc, vc, 0, fused=True)
-            symm_mem.check_status(dev)
-            us_f = benchmark_with_graph(lambda: layer.decode(xd, kc, vc, 8, fused=True), calls_per_graph=5)
-            us_r = benchmark_with_graph(lambda: layer.decode(xd, kc, vc, 8, fused=False), calls_per_graph=5)
-            symm_mem.check_status(dev)
-            emit({"op": "llama70b_layer_decode", "world_size": world, "batch": B, "timing": "graph",
-                  "smr_fused_us": round(us_f, 1), "nccl_cublas_us": round(us_r, 1),
-                  "speedup": round(us_r / us_f, 3)})
+            us_r = None
+            for glue_on, dlayer in sorted(decode_layers.items()):
+                kc = torch.zeros(B, 64, dlayer.hkv, cfg.head_dim, dtype=torch.bfloat16, device=dev)
+                vc = torch.zeros_like(kc)
+                y_f = dlayer.decode(xd, kc, vc, 0, fused=True)
+                symm_mem.check_status(dev)
+                y_r = dlayer.decode(xd, kc, vc, 0, fused=False)
+                rel = float((y_f.float() - y_r.float()).abs().max() / y_r.float().abs().max())
+                us_f = benchmark_with_graph(lambda: dlayer.decode(xd, kc, vc, 8, fused=True), calls_per_graph=5)
+                if us_r is None:               # the library composition does not depend on the glue switch
+                    us_r = benchmark_with_graph(lambda: dlayer.decode(xd, kc, vc, 8, fused=False), calls_per_graph=5)
+                symm_mem.check_status(dev)
+                emit({"op": "llama70b_layer_decode", "world_size": world, "batch": B, "timing": "graph",
+                      "fused_glue": bool(glue_on), "matches_library": rel < 3e-2, "max_rel_diff": round(rel, 5),
+                      "smr_fused_us": round(us_f, 1), "nccl_cublas_us": round(us_r, 1),
+                      "speedup": round(us_r / us_f, 3)})
     if args.decode_graph > 0:
         from symm_mem_recipes_b200.models.llama_tp_layer import DecodeGraph
         from symm_mem_recipes_b200.utils.benchmark import max_over_ranks

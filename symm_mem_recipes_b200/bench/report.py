@@ -191,8 +191,9 @@ def layer_tables(recs: list[dict]) -> Optional[str]:
             glue += ", SwiGLU in the GEMM epilogue" if r.get("fused_swiglu") else ""
             rows.append([str(r["world_size"]), f"prefill {r['batch']} x {r['seq']}{glue}", _fmt(r["smr_fused_us"]),
                          _fmt(r["nccl_cublas_us"]), f"{r['speedup']:.2f}x"])
-        for r in {(r["world_size"], r["batch"]): r for r in dec}.values():
-            rows.append([str(r["world_size"]), f"decode batch {r['batch']}", _fmt(r["smr_fused_us"]),
+        for r in {(r["world_size"], r["batch"], r.get("fused_glue", False)): r for r in dec}.values():
+            glue = ", single-pass norm / RoPE / SiLU kernels" if r.get("fused_glue") else ""
+            rows.append([str(r["world_size"]), f"decode batch {r['batch']}{glue}", _fmt(r["smr_fused_us"]),
                          _fmt(r["nccl_cublas_us"]), f"{r['speedup']:.2f}x"])
         parts.append("### Llama-3-70B TP decoder layer\n\n" + _table(
             ["WS", "step", "this package µs", "NCCL + cuBLAS µs", "speed-up"], rows))

@@ -115,7 +115,10 @@ def test_layer_driver(tmp_path):
     ops = [r["op"] for r in recs]
     assert ops.count("matmul_reduce_scatter") == 2 and ops.count("matmul_reduce_scatter_variant") == 6
     assert ops.count("llama70b_layer_prefill") == 3 and ops.count("llama70b_layer_prefill_phases") == 3
-    assert ops.count("llama70b_layer_prefill_tp") == 1 and ops.count("llama70b_layer_decode") == 3
+    assert ops.count("llama70b_layer_prefill_tp") == 1
+    decodes = [r for r in recs if r["op"] == "llama70b_layer_decode"]
+    assert sorted((r["batch"], r["fused_glue"]) for r in decodes) == [(1, False), (1, True), (4, False), (4, True),
+                                                                      (16, False), (16, True)]
     assert ops.count("llama70b_decode_graph") == 3
     assert all(r["matches_library"] for r in recs if "matches_library" in r)
     assert all(r["matches_default"] for r in recs if "matches_default" in r)
