@@ -10,8 +10,9 @@ An installation check for users, and the cheapest way to try many kernel
 variants on hardware: the pytest suite starts a fresh set of processes per
 case, this program starts once.  Rank 0 prints one line per check and a JSON
 summary; the exit code is the number of failed checks.  After every check the
-ranks agree on its outcome; a check that ends in a device-side timeout stops
-the run (the symmetric allocations it used are in an unknown state).
+ranks agree on its outcome; after a check that ends in a device-side timeout
+(the allocations it used are then in an unknown state) the ranks drop all
+symmetric memory together and carry on with fresh allocations.
 No upstream counterpart (the upstream drivers check one op each:
 symm_mem_recipes/triton_one_shot_all_reduce.py:145-154,
 triton_all_gather_matmul.py:390-392).
@@ -33,6 +34,10 @@ def _close(got: torch.Tensor, ref: torch.Tensor, rtol: float = 3e-2, atol: float
     err = (got.float() - ref.float()).abs()
     ok = bool((err <= ref.float().abs() * rtol + atol).all())
     return ok, float(err.max())
+
+
+_SHARED_STATE: list = []
+_MAX_RECOVERIES = 8
 
 
 def build_checks(first_run: bool, world: int, rank: int, dev: torch.device) -> list:
@@ -57,6 +62,7 @@ def build_checks(first_run: bool, world: int, rank: int, dev: torch.device) -> l
     # ------------------------------------------------------------------ all-reduce and barriers
     numel = 1 << 16
     state: dict = {}
+    _SHARED_STATE.append(state)      # symmetric tensors kept between checks; dropped when main() resets the module
 
     def ar_setup():
         if "t" not in state:
@@ -292,6 +298,57 @@ def build_checks(first_run: bool, world: int, rank: int, dev: torch.device) -> l
     return [c for c in checks if first_run or not c[2]]
 
 
+def run_checks(checks: list, rank: int, dev: torch.device, only=()) -> tuple:
+    """Runs the checks in order; returns (results, recoveries, stopped_early).  Collective: every
+    rank runs the same list and learns every rank's outcome after each check."""
+    from symm_mem_recipes_b200.errors import SymmMemTimeout
+    from symm_mem_recipes_b200.parallel import symm_mem
+    from symm_mem_recipes_b200.utils.benchmark import max_over_ranks
+
+    results, stop, recoveries = [], False, 0
+    for group, name, pending, fn in checks:
+        if only and group not in only:
+            continue
+        t0 = time.monotonic()
+        timed_out = False
+        try:
+            ok, detail = fn()
+        except SymmMemTimeout as e:
+            ok, detail, timed_out = False, f"device-side timeout: {e}", True
+        except Exception as e:  # noqa: BLE001 - reported, the run goes on
+            ok, detail = False, f"{type(e).__name__}: {e}"
+            if rank == 0:
+                traceback.print_exc()
+        # every rank learns the outcome of every rank
+        bad = max_over_ranks(0.0 if ok else 1.0, dev) != 0.0
+        stop = max_over_ranks(1.0 if timed_out else 0.0, dev) != 0.0
+        results.append({"group": group, "check": name, "first_run": pending, "ok": not bad,
+                        "detail": detail if not ok or detail else "", "seconds": round(time.monotonic() - t0, 2)})
+        if rank == 0:
+            print(f"[{'ok' if not bad else 'FAILED'}] {group}: {name}  {results[-1]['detail']}", flush=True)
+        if stop:
+            # A bounded wait ran out somewhere: counters and barrier slots of the allocations in use are no longer
+            # trustworthy.  The kernels have returned, so the ranks drop ALL symmetric memory together and the
+            # next check starts from fresh allocations.
+            recoveries += 1
+            if recoveries > _MAX_RECOVERIES:
+                if rank == 0:
+                    print("stopping: too many device-side timeouts", flush=True)
+                break
+            for shared in _SHARED_STATE:
+                shared.clear()
+            if dev.type == "cuda":
+                try:                                   # a timeout recorded on this rank but not yet read
+                    symm_mem.check_status(dev)
+                except SymmMemTimeout:
+                    pass
+            symm_mem.reset()
+            stop = False
+            if rank == 0:
+                print("a bounded wait ran out: symmetric memory dropped and re-created for the next check", flush=True)
+    return results, recoveries, recoveries > _MAX_RECOVERIES
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("--first-run", action="store_true", help="include the variants whose first run on hardware is pending")
@@ -314,39 +371,13 @@ def main(argv=None) -> int:
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
-    from symm_mem_recipes_b200.errors import SymmMemTimeout
     from symm_mem_recipes_b200.parallel import symm_mem
-    from symm_mem_recipes_b200.utils.benchmark import max_over_ranks
 
-    results, stop = [], False
-    for group, name, pending, fn in build_checks(args.first_run, world, rank, dev):
-        if only and group not in only:
-            continue
-        t0 = time.monotonic()
-        timed_out = False
-        try:
-            ok, detail = fn()
-        except SymmMemTimeout as e:
-            ok, detail, timed_out = False, f"device-side timeout: {e}", True
-        except Exception as e:  # noqa: BLE001 - reported, the run goes on
-            ok, detail = False, f"{type(e).__name__}: {e}"
-            if rank == 0:
-                traceback.print_exc()
-        # every rank learns the outcome of every rank
-        bad = max_over_ranks(0.0 if ok else 1.0, dev) != 0.0
-        stop = max_over_ranks(1.0 if timed_out else 0.0, dev) != 0.0
-        results.append({"group": group, "check": name, "first_run": pending, "ok": not bad,
-                        "detail": detail if not ok or detail else "", "seconds": round(time.monotonic() - t0, 2)})
-        if rank == 0:
-            print(f"[{'ok' if not bad else 'FAILED'}] {group}: {name}  {results[-1]['detail']}", flush=True)
-        if stop:
-            if rank == 0:
-                print("stopping: a bounded wait ran out, symmetric state is no longer trustworthy", flush=True)
-            break
+    results, recoveries, stopped = run_checks(build_checks(args.first_run, world, rank, dev), rank, dev, only)
     failed = [r for r in results if not r["ok"]]
     if rank == 0:
         print(json.dumps({"op": "selfcheck", "world_size": world, "checks": len(results), "failed": len(failed),
-                          "stopped_early": stop, "failures": [f"{r['group']}: {r['check']}" for r in failed]}))
+                          "stopped_early": stopped, "recoveries": recoveries, "failures": [f"{r['group']}: {r['check']}" for r in failed]}))
     symm_mem.shutdown()
     if world > 1:
         dist.destroy_process_group()

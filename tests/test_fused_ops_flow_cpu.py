@@ -374,18 +374,53 @@ def _selfcheck_worker(rank, world_size):
 
     _install_all_stand_ins()
 
-    failures, ran = [], 0
-    for group, name, pending, fn in selfcheck.build_checks(True, world_size, rank, torch.device("cpu")):
-        if (group == "barrier" and "barrier" in name.lower()) or "NVLS" in name:
-            continue                                   # barrier_test kernels exist on the GPU only
-        ok, detail = fn()
-        ran += 1
-        if not ok:
-            failures.append(f"{group}: {name}: {detail}")
-        dist.barrier()
+    checks = [c for c in selfcheck.build_checks(True, world_size, rank, torch.device("cpu"))
+              if not ((c[0] == "barrier" and "barrier" in c[1].lower()) or "NVLS" in c[1])]   # GPU-only kernels
+    results, recoveries, stopped = selfcheck.run_checks(checks, rank, torch.device("cpu"))
+    failures = [f"{r['group']}: {r['check']}: {r['detail']}" for r in results if not r["ok"]]
     assert not failures, failures
-    assert ran >= 30, ran
+    assert len(results) >= 30 and recoveries == 0 and not stopped, (len(results), recoveries)
+    dist.barrier()
 
 
 def test_selfcheck_logic_two_ranks():
     spawn_ranks(_selfcheck_worker, 2, "gloo")
+
+
+def _selfcheck_recovery_worker(rank, world_size):
+    """A check that ends in a device-side timeout on ONE rank: every rank drops its symmetric memory,
+    and the checks after it run on fresh allocations."""
+    import torch.distributed as dist
+
+    from symm_mem_recipes_b200 import selfcheck
+    from symm_mem_recipes_b200.errors import SymmMemTimeout
+    from symm_mem_recipes_b200.parallel import symm_mem
+
+    seen = []
+
+    def healthy():
+        t = symm_mem.empty(64, dtype=torch.float32, device="cpu")
+        hdl = symm_mem.rendezvous(t)
+        t.fill_(float(rank + 1))
+        hdl.barrier()
+        total = sum(float(hdl.get_buffer(r, (64,), torch.float32)[0]) for r in range(world_size))
+        hdl.barrier()
+        seen.append(symm_mem.memory_summary()["count"])
+        return total == sum(range(1, world_size + 1)), ""
+
+    def times_out_on_rank_1():
+        if rank == 1:
+            raise SymmMemTimeout(3, rank, 0, 0, 1, 0)
+        return True, ""
+
+    checks = [("a", "healthy", False, healthy), ("a", "timeout on one rank", True, times_out_on_rank_1),
+              ("a", "healthy again", False, healthy), ("a", "and again", False, healthy)]
+    results, recoveries, stopped = selfcheck.run_checks(checks, rank, torch.device("cpu"))
+    assert [r["ok"] for r in results] == [True, False, True, True], results
+    assert recoveries == 1 and not stopped
+    assert seen == [1, 1, 2]            # the allocation of the first check was dropped by the recovery
+    dist.barrier()
+
+
+def test_selfcheck_recovers_from_a_timeout_on_one_rank():
+    spawn_ranks(_selfcheck_recovery_worker, 2, "gloo")
