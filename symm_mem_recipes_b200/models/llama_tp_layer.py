@@ -132,6 +132,7 @@ class LlamaTPDecoderLayer:
         self.norm1 = (1.0 + 0.1 * torch.randn(H, generator=gn)).to(dtype).to(device)
         self.norm2 = (1.0 + 0.1 * torch.randn(H, generator=gn)).to(dtype).to(device)
         self._sym: dict[tuple, torch.Tensor] = {}
+        self._sym_generation = symm_mem.generation()
         # set to a list to get (phase name, CUDA event) pairs appended by `forward` (see `phase_times_us`)
         self.phase_marks: Optional[list] = None
 
@@ -157,6 +158,9 @@ class LlamaTPDecoderLayer:
 
     # ---- symmetric staging for the gather inputs ----
     def _symmetric(self, tag: str, rows: int) -> torch.Tensor:
+        if self._sym_generation != symm_mem.generation():       # symm_mem.reset() ran: the cached buffers are gone
+            self._sym.clear()
+            self._sym_generation = symm_mem.generation()
         key = (tag, rows)
         t = self._sym.get(key)
         if t is None:

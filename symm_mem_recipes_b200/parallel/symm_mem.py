@@ -67,6 +67,14 @@ _records: dict[int, _Record] = {}
 _groups: dict[int, _GroupState] = {}
 _enabled_groups: set[str] = set()
 _shutdown_done = False
+_generation = 0          # bumped by reset(): caches of symmetric tensors kept elsewhere compare it
+
+
+def generation() -> int:
+    """How many times `reset()` has run in this process.  Code that caches symmetric tensors
+    (a model's gather buffers, for instance) keeps the value it saw and drops its cache when
+    the number has moved on: those tensors point into released allocations."""
+    return _generation
 
 
 def _group_key(group) -> int:
@@ -77,7 +85,9 @@ def _group_state(group) -> _GroupState:
     key = _group_key(group)
     st = _groups.get(key)
     if st is None:
-        st = _GroupState(group=group, exchange=StoreExchange(group))
+        # a namespace per reset() generation: a new exchange on the same process group must not
+        # find the keys its predecessor left in the Store
+        st = _GroupState(group=group, exchange=StoreExchange(group, namespace=f"smr/g{_generation}"))
         _groups[key] = st
     return st
 
@@ -447,9 +457,10 @@ def reset() -> None:
     job that re-forms its process group (for example the survivors after
     `PeerLost`): every symmetric tensor and every cached workspace of the ops
     is gone afterwards and is re-created, collectively, by the new group."""
-    global _shutdown_done
+    global _shutdown_done, _generation
     shutdown()
     _shutdown_done = False
+    _generation += 1
     # workspaces the ops keep per (shape, group): they point into released allocations
     import importlib
     for mod, names in (("ag_matmul", ("_gather_buffers",)), ("all_reduce", ("_ll_workspaces",)),

@@ -344,3 +344,31 @@ def test_memory_summary_counts_allocations():
     symm_mem.free(t)
     symm_mem.free(u)
     assert symm_mem.memory_summary()["count"] == before["count"]
+
+
+def _reset_same_group_worker(rank, world_size):
+    """reset() and carry on with the SAME process group (what a driver does after a device-side
+    timeout): the new allocations rendezvous through a Store that still holds the old exchange's
+    keys, and must not read them."""
+    import symm_mem_recipes_b200 as smr
+    from symm_mem_recipes_b200._ext import C
+    from symm_mem_recipes_b200.parallel import symm_mem
+
+    for generation, numel in enumerate((4096, 1024, 8192)):
+        assert symm_mem.generation() == generation
+        t = symm_mem.empty(numel, dtype=torch.bfloat16, device="cpu")
+        t.copy_(seeded_normal_bf16(numel, rank + 10 * generation))
+        hdl = symm_mem.rendezvous(t)
+        hdl.barrier()
+        peer = hdl.get_buffer((rank + 1) % world_size, (numel,), torch.bfloat16)
+        assert torch.equal(peer, seeded_normal_bf16(numel, (rank + 1) % world_size + 10 * generation))
+        out = smr.one_shot_all_reduce(t, exit_barrier=True)
+        want = C.oracle_ordered_sum_bf16([seeded_normal_bf16(numel, r + 10 * generation) for r in range(world_size)])
+        assert torch.equal(out, want)
+        assert smr.low_latency_all_reduce(t[:512].clone()).shape == (512,)      # a cached workspace to drop
+        symm_mem.reset()
+        assert symm_mem.memory_summary()["count"] == 0
+
+
+def test_reset_and_carry_on_with_the_same_group():
+    spawn_ranks(_reset_same_group_worker, 3, "gloo")
