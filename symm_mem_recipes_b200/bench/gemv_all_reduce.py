@@ -34,7 +34,7 @@ def build_parser() -> argparse.ArgumentParser:
 
 def main(argv=None, standalone: bool = True) -> int:
     args = build_parser().parse_args(argv)
-    from symm_mem_recipes_b200.bench._common import finish, init_distributed
+    from symm_mem_recipes_b200.bench._common import attempt, finish, init_distributed
 
     rank, local_rank, world, dev = init_distributed()
 
@@ -66,26 +66,39 @@ def main(argv=None, standalone: bool = True) -> int:
             state["i"] = (state["i"] + 1) % n_w
             torch.matmul(x, ws_[state["i"]])
 
-        variants = [("smr_fused", fused), ("cublas_plus_nccl", lib), ("cublas_gemv_only", gemv_only)]
-        for algo in [a for a in args.extra_algos.split(",") if a]:
-            smr.gemv_all_reduce(x, ws_[0], out, algo=algo)
-            symm_mem.check_status(dev)
-
-            def fused_algo(algo=algo):
-                state["i"] = (state["i"] + 1) % n_w
-                smr.gemv_all_reduce(x, ws_[state["i"]], out, algo=algo)
-
-            variants.append((f"smr_fused:{algo}", fused_algo))
-        for name, fn in variants:
-            us = benchmark_with_graph(fn, calls_per_graph=20, replays=10)
-            rec = {"op": "gemv_all_reduce", "impl": name, "world_size": world, "batch": b, "K": args.K,
-                   "N": args.N, "us": round(us, 2), "timing": "graph",
-                   "weight_gbs": round(args.K * args.N * 2 / us / 1e3, 1)}
+        def emit(rec):
             if rank == 0:
                 s = json.dumps(rec)
                 print(s, flush=True)
                 lines.append(s)
+
+        def timed(name, fn):
+            us = benchmark_with_graph(fn, calls_per_graph=20, replays=10)
+            emit({"op": "gemv_all_reduce", "impl": name, "world_size": world, "batch": b, "K": args.K,
+                  "N": args.N, "us": round(us, 2), "timing": "graph",
+                  "weight_gbs": round(args.K * args.N * 2 / us / 1e3, 1)})
+
+        for name, fn in (("smr_fused", fused), ("cublas_plus_nccl", lib), ("cublas_gemv_only", gemv_only)):
+            timed(name, fn)
         symm_mem.check_status(dev)
+        # the other kernels, each on its own: one that fails (or times out) does not end the run
+        for algo in [a for a in args.extra_algos.split(",") if a]:
+            def extra(algo=algo):
+                want = smr.gemv_all_reduce(x, ws_[0]).clone()
+                smr.gemv_all_reduce(x, ws_[0], out, algo=algo)
+                symm_mem.check_status(dev)
+                same = bool(torch.allclose(out.float(), want.float(), rtol=2.0 ** -6, atol=2e-2))
+
+                def fused_algo():
+                    state["i"] = (state["i"] + 1) % n_w
+                    smr.gemv_all_reduce(x, ws_[state["i"]], out, algo=algo)
+
+                timed(f"smr_fused:{algo}", fused_algo)
+                symm_mem.check_status(dev)
+                if not same:
+                    raise RuntimeError(f"{algo} differs from the default kernel")
+
+            attempt(f"gemv_all_reduce {algo}, batch {b}", extra, dev, emit)
     if args.out and rank == 0:
         with open(args.out, "a") as f:
             f.write("\n".join(lines) + "\n")
