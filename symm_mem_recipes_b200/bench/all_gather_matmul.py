@@ -139,10 +139,17 @@ def _one_shape(args, M, N, K, rank, world, dev, lines) -> None:
         emit("smr_fused", us, copy_ctas=n_copy, gather="pull")
         symm_mem.check_status(dev)
     if args.with_push_copy:
-        cfgp = AgMatmulConfig(block_n=args.block_n, plain_a_out="push_copy")
-        us = benchmark_with_event(lambda: smr.all_gather_matmul(a_shard, b, a_out_plain, c, cfgp), **bench)
-        emit("smr_fused", us, gather="push_copy")
-        symm_mem.check_status(dev)
+        def push_copy():
+            cfgp = AgMatmulConfig(block_n=args.block_n, plain_a_out="push_copy")
+            us = benchmark_with_event(lambda: smr.all_gather_matmul(a_shard, b, a_out_plain, c, cfgp), **bench)
+            symm_mem.check_status(dev)
+            if not torch.allclose(c0.float(), c.float(), rtol=2e-2, atol=2e-3):
+                raise RuntimeError("push_copy result differs from NCCL + cuBLAS")
+            emit("smr_fused", us, gather="push_copy")
+
+        from symm_mem_recipes_b200.bench._common import attempt
+        attempt("all_gather_matmul with an ordinary a_out by push and copy", push_copy, dev,
+                lambda rec: (print(json.dumps(rec), flush=True), lines.append(json.dumps(rec))) if rank == 0 else None)
 
 
 if __name__ == "__main__":

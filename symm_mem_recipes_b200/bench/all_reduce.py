@@ -48,7 +48,7 @@ def build_parser() -> argparse.ArgumentParser:
 def main(argv=None, standalone: bool = True) -> int:
     args = build_parser().parse_args(argv)
 
-    from symm_mem_recipes_b200.bench._common import finish, init_distributed
+    from symm_mem_recipes_b200.bench._common import attempt, finish, init_distributed
 
     rank, local_rank, world, dev = init_distributed()
 
@@ -137,15 +137,28 @@ def main(argv=None, standalone: bool = True) -> int:
                 for nvls in (0, 1):
                     for blocks in (8, 12, 16, 24, 32):
                         for unroll in (4, 8, 16):
-                            c = AllReduceConfig(multimem_max_blocks=blocks, multimem_unroll=unroll,
-                                                multimem_nvls_barrier=nvls)
-                            us = benchmark_with_event(lambda: smr.multimem_all_reduce_(t, config=c), 5, 15,
-                                                      flush_l2=False)
-                            hdl.check()
-                            buf.normal_()
-                            emit({"op": "all_reduce_multimem_sweep", "world_size": world, "bytes": nbytes,
-                                  "blocks": blocks, "unroll": unroll, "nvls_barrier": bool(nvls), "us": round(us, 2),
-                                  "bus_gbs": round(2 * (world - 1) / world * nbytes / us / 1e3, 1)})
+                            def one(blocks=blocks, unroll=unroll, nvls=nvls, t=t, nbytes=nbytes):
+                                c = AllReduceConfig(multimem_max_blocks=blocks, multimem_unroll=unroll,
+                                                    multimem_nvls_barrier=nvls)
+                                us = benchmark_with_event(lambda: smr.multimem_all_reduce_(t, config=c), 5, 15,
+                                                          flush_l2=False)
+                                hdl.check()
+                                buf.normal_()
+                                emit({"op": "all_reduce_multimem_sweep", "world_size": world, "bytes": nbytes,
+                                      "blocks": blocks, "unroll": unroll, "nvls_barrier": bool(nvls),
+                                      "us": round(us, 2),
+                                      "bus_gbs": round(2 * (world - 1) / world * nbytes / us / 1e3, 1)})
+
+                            if not attempt(f"multimem sweep: {nbytes} bytes, {blocks} CTAs, unroll {unroll}, "
+                                           f"nvls_barrier {nvls}", one, dev, emit):
+                                # after a device-side timeout the buffer itself is gone (reset): stop the sweep
+                                if not symm_mem.is_symm_mem_tensor(buf):
+                                    if args.out and rank == 0:
+                                        with open(args.out, "a") as f:
+                                            f.write("\n".join(lines) + "\n")
+                                    if standalone:
+                                        finish()
+                                    return 1
         if args.out and rank == 0:
             with open(args.out, "a") as f:
                 f.write("\n".join(lines) + "\n")

@@ -388,8 +388,9 @@ class DecodeGraph:
 
     Every rank builds and replays the same graph (the fused GEMV + all-reduce
     kernels inside meet their peers as in eager mode).  The KV caches live in
-    the object; `reset()` starts a new sequence.  No upstream counterpart: the
-    upstream recipes time single kernels.
+    the object; `reset()` starts a new sequence.  The graph holds the addresses
+    of the ops' symmetric workspaces: after `symm_mem.reset()` build a new one.
+    No upstream counterpart: the upstream recipes time single kernels.
     """
 
     def __init__(self, layers, batch: int, max_seq: int, fused: bool = True, warmup: int = 2):
