@@ -163,3 +163,17 @@ def test_ncu_summary_from_raw_csv():
     assert "272.0 MB at 1487 GB/s" in md and "1.75x" in md and "0.23 of the measured copy rate" in md
     assert "1315 TFLOPS" in md and "0.80 of the measured burst" in md
     assert ncu_summary.render([], "x") == "no captured launch in the report\n"
+
+
+def test_layer_roofline_expectations():
+    from symm_mem_recipes_b200.bench.expect import DEFAULT_PEAKS, expect_layer
+
+    pre = expect_layer(8, DEFAULT_PEAKS, batch=16, seq=2048)
+    assert pre["phases"]["qkv"]["bound_by"] == "nvlink_in" and pre["phases"]["o_proj"]["bound_by"] == "nvlink_out"
+    assert pre["phases"]["gate_up"]["bound_by"] == "tensor" and pre["phases"]["down_proj"]["bound_by"] == "tensor"
+    assert abs(pre["target_us"] - sum(p["target_us"] for p in pre["phases"].values())) < 0.2
+    assert 4900 < pre["target_us"] < 5100                      # about 5.0 ms for the 70B layer at TP8
+    dec = expect_layer(8, DEFAULT_PEAKS, batch=1, decode=True)
+    # every weight of the rank once: (1280 + 7168 + 1024 + 3584) x 8192 x 2 B = 214 MB at 6541 GB/s
+    assert abs(dec["target_us"] - 214.0e6 / 6541.5e3) < 0.3 and set(dec["phases"]) == {"qkv", "gate_up", "o_proj",
+                                                                                         "down_proj"}
