@@ -88,6 +88,9 @@ def matmul_reduce_scatter(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.
         cta_pair = os.environ.get("SMR_RS_CTA_PAIR", "0") == "1"
     if thread_stores is None:
         thread_stores = os.environ.get("SMR_RS_THREAD_STORES", "0") == "1"
+    if deep_strips and (cta_pair or thread_stores):
+        raise SymmMemError("deep_strips is a variant of the 1-CTA bulk-store kernel: it does not combine with "
+                           "cta_pair or thread_stores")
     C.matmul_reduce_scatter(a, b, out, hdl.native, num_sms or _num_sms(a.device),
                             int(timeout_ms) * 1_000_000, trace, bool(deep_strips), bool(cta_pair),
                             bool(thread_stores))

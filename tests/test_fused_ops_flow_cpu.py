@@ -185,6 +185,8 @@ def _row_parallel_flow_worker(rank, world_size):
     assert seen["rs"][:2] == (True, False)
     smr.matmul_reduce_scatter(a, b, thread_stores=True)
     assert seen["rs"][:2] == (False, False) and seen["rs"][3] is True
+    with pytest.raises(SymmMemError, match="does not combine"):
+        smr.matmul_reduce_scatter(a, b, deep_strips=True, thread_stores=True)
 
     full = smr.matmul_all_reduce(a, b)                       # internal symmetric output, cached per shape
     assert symm_mem.is_symm_mem_tensor(full) and torch.allclose(full.float(), want, atol=0.02)
