@@ -11,7 +11,8 @@ Prefill (`forward`), activations sharded on tokens between the blocks:
       -> SiLU(gate) * up -> matmul_reduce_scatter with W_down -> + residual
 
 Decode (`decode`), activations replicated, batch <= 16: the two row-parallel
-projections use the fused GEMV + all-reduce.  `decode_static` is the same step
+projections use the fused GEMV + all-reduce.  It continues from KV caches that
+the prefill fills when given `kv_cache=(k_cache, v_cache)`.  `decode_static` is the same step
 with shapes and launches independent of the position, and `DecodeGraph`
 captures it (through any number of layers) in one CUDA graph that is replayed
 per token.
@@ -170,7 +171,10 @@ class LlamaTPDecoderLayer:
         return t
 
     # ---- rank-local attention on [T, (hq + 2 hkv) * D] ----
-    def _attention(self, qkv: torch.Tensor, batch: int, seq: int, glue: bool = False) -> torch.Tensor:
+    def _attention(self, qkv: torch.Tensor, batch: int, seq: int, glue: bool = False, kv_cache=None) -> torch.Tensor:
+        """Causal attention of this rank's heads over `batch` sequences of `seq` tokens.  With
+        `kv_cache = (k_cache, v_cache)` ([batch, S_max, hkv, D] each) the keys (rotated) and values of
+        positions [0, seq) are also written there, which is what `decode` continues from."""
         D, hq, hkv = self.cfg.head_dim, self.hq, self.hkv
         if glue:
             ops.rope_(qkv, hq + hkv, D, seq, self.cfg.rope_theta)      # Q and K heads, in place
@@ -181,6 +185,12 @@ class LlamaTPDecoderLayer:
         if not glue:
             pos = torch.arange(seq, device=qkv.device)[None, :].expand(batch, seq)
             q, k = _rope(q, pos, self.cfg.rope_theta), _rope(k, pos, self.cfg.rope_theta)
+        if kv_cache is not None:
+            k_cache, v_cache = kv_cache
+            if k_cache.shape[0] != batch or k_cache.shape[1] < seq or v_cache.shape != k_cache.shape:
+                raise ValueError("kv_cache: two [batch, S_max >= seq, kv heads per rank, head_dim] tensors")
+            k_cache[:, :seq].copy_(k)
+            v_cache[:, :seq].copy_(v)
         o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
                                            is_causal=True, enable_gqa=True)
         return o.transpose(1, 2).reshape(batch * seq, hq * D).contiguous()
@@ -194,9 +204,10 @@ class LlamaTPDecoderLayer:
         return ops.silu_mul(gu) if self.fused_glue else self._mlp_act_torch(gu, self.ffn_local)
 
     # ------------------------------------------------------------------
-    def forward(self, x_shard: torch.Tensor, batch: int, seq: int, barrier_between_phases: bool = False
-                ) -> torch.Tensor:
-        """x_shard [batch*seq/WS, H] (this rank's tokens) -> same shape."""
+    def forward(self, x_shard: torch.Tensor, batch: int, seq: int, barrier_between_phases: bool = False,
+                kv_cache=None) -> torch.Tensor:
+        """x_shard [batch*seq/WS, H] (this rank's tokens) -> same shape.  `kv_cache = (k_cache,
+        v_cache)` receives this rank's keys and values of the prompt, for `decode` to continue from."""
         cfg = self.cfg
         rows = x_shard.shape[0]
         assert rows * self.ws == batch * seq
@@ -209,7 +220,7 @@ class LlamaTPDecoderLayer:
         self._mark("norm1")
         qkv = ops.all_gather_matmul(h, self.w_qkv, group=self.group)
         self._mark("qkv_all_gather_matmul")
-        attn = self._attention(qkv, batch, seq, glue=self.fused_glue)
+        attn = self._attention(qkv, batch, seq, glue=self.fused_glue, kv_cache=kv_cache)
         self._mark("rope_attention")
         if barrier_between_phases:
             symm_mem.rendezvous(h, self.group).barrier(channel=1)
@@ -239,7 +250,7 @@ class LlamaTPDecoderLayer:
         return y
 
     # ------------------------------------------------------------------
-    def forward_tp(self, x: torch.Tensor, batch: int, seq: int) -> torch.Tensor:
+    def forward_tp(self, x: torch.Tensor, batch: int, seq: int, kv_cache=None) -> torch.Tensor:
         """Prefill under plain tensor parallelism (no sequence parallelism):
         `x` [batch*seq, H] is replicated on every rank, the column-parallel
         projections are local tcgen05 GEMMs, and the two row-parallel ones end
@@ -249,7 +260,7 @@ class LlamaTPDecoderLayer:
         assert x.shape[0] == batch * seq
         h = ops.rms_norm(x, self.norm1, cfg.eps) if self.fused_glue else _rms_norm(x, self.norm1, cfg.eps)
         qkv = ops.matmul(h, self.w_qkv)
-        attn = self._attention(qkv, batch, seq, glue=self.fused_glue)
+        attn = self._attention(qkv, batch, seq, glue=self.fused_glue, kv_cache=kv_cache)
         o = ops.matmul_all_reduce(attn, self.w_o, group=self.group)      # internal symmetric buffer: consume it
         if self.fused_glue:                                              # before the next call of this shape
             h2, x1 = ops.rms_norm(x, self.norm2, cfg.eps, residual=o)
@@ -383,7 +394,9 @@ class DecodeGraph:
     kernels of a few microseconds per layer) costs one graph launch per step.
 
         g = DecodeGraph(layers, batch=4, max_seq=4096)
-        for pos, x in enumerate(tokens):           # x [B, H], replicated on all ranks
+        for lyr, cache in zip(layers, g.caches):   # prompt: prefill straight into the graph's caches
+            h = lyr.forward(h, batch, prompt_len, kv_cache=cache)
+        for pos, x in enumerate(tokens, start=prompt_len):     # x [B, H], replicated on all ranks
             y = g.step(x, pos)                     # y is overwritten by the next step
 
     Every rank builds and replays the same graph (the fused GEMV + all-reduce

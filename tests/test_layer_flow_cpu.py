@@ -136,6 +136,33 @@ def test_static_decode_matches_decode(host_kernels, fused_glue):
     assert bool((k_b[:, seq:] == 7.0).all()) and bool((v_b[:, seq:] == -3.0).all())
 
 
+@pytest.mark.parametrize("fused_glue,tp", [(False, False), (True, False), (True, True)])
+def test_prefill_hands_its_kv_cache_to_decode(host_kernels, fused_glue, tp):
+    """Prefill of a prompt that also fills the KV cache, then decode of the following tokens:
+    same outputs as the prefill of the whole sequence, and the same cache as decoding all the way."""
+    cfg, layer, x, batch, seq, _ = _layer_and_reference(fused_glue, False)
+    prompt = seq // 2
+    xs = x.view(batch, seq, cfg.hidden)
+    want = layer.forward(x, batch, seq).view(batch, seq, cfg.hidden)
+    k_cache = torch.zeros(batch, seq + 3, layer.hkv, cfg.head_dim, dtype=torch.bfloat16)
+    v_cache = torch.zeros_like(k_cache)
+    x_prompt = xs[:, :prompt].reshape(batch * prompt, cfg.hidden).contiguous()
+    fwd = layer.forward_tp if tp else layer.forward
+    y_prompt = fwd(x_prompt, batch, prompt, kv_cache=(k_cache, v_cache)).view(batch, prompt, cfg.hidden)
+    assert (y_prompt.float() - want[:, :prompt].float()).abs().max().item() < 0.1
+    for pos in range(prompt, seq):
+        got = layer.decode(xs[:, pos].contiguous(), k_cache, v_cache, pos, fused=True)
+        assert (got.float() - want[:, pos].float()).abs().max().item() < 0.1, pos
+    # the cache a token-by-token decode builds is the same
+    k2, v2 = torch.zeros_like(k_cache), torch.zeros_like(v_cache)
+    for pos in range(seq):
+        layer.decode(xs[:, pos].contiguous(), k2, v2, pos, fused=True)
+    assert (k_cache.float() - k2.float()).abs().max().item() < 0.05
+    assert (v_cache.float() - v2.float()).abs().max().item() < 0.05
+    with pytest.raises(ValueError, match="kv_cache"):
+        layer.forward(x, batch, seq, kv_cache=(k_cache[:, :4], v_cache[:, :4]))
+
+
 def test_phase_marks_are_off_by_default(host_kernels):
     _, layer, x, batch, seq, _ = _layer_and_reference(False, False)
     layer.forward(x, batch, seq)
