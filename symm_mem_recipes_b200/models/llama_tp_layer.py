@@ -21,7 +21,7 @@ Prefill without sequence parallelism (`forward_tp`), activations replicated:
 local GEMMs for the column-parallel projections, `matmul_all_reduce` for the
 row-parallel ones.
 
-`forward_reference` / `decode_reference` build the same layer from NCCL
+`forward_reference` / `forward_tp_reference` / `decode(fused=False)` build the same layer from NCCL
 collectives and cuBLAS and are the baseline the fused layer is timed against.
 The upstream recipes stop at the single fused op; this module is how the ops
 compose in the workload they were written for (Llama-3-70B at TP8: hidden
