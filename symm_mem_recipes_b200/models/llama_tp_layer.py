@@ -388,6 +388,13 @@ class LlamaTPDecoderLayer:
         return self._decode_mlp(x, o_proj, fused, glue)
 
 
+def new_kv_caches(layers, batch: int, max_seq: int) -> list:
+    """One zeroed (k_cache, v_cache) pair per layer, [batch, max_seq, kv heads per rank, head_dim] each."""
+    return [(torch.zeros(batch, max_seq, lyr.hkv, lyr.cfg.head_dim, dtype=torch.bfloat16, device=lyr.device),
+             torch.zeros(batch, max_seq, lyr.hkv, lyr.cfg.head_dim, dtype=torch.bfloat16, device=lyr.device))
+            for lyr in layers]
+
+
 class DecodeGraph:
     """A decode step through a stack of layers captured once in a CUDA graph
     and replayed for every token: the launch-bound part of serving (a dozen
@@ -406,7 +413,7 @@ class DecodeGraph:
     No upstream counterpart: the upstream recipes time single kernels.
     """
 
-    def __init__(self, layers, batch: int, max_seq: int, fused: bool = True, warmup: int = 2):
+    def __init__(self, layers, batch: int, max_seq: int, fused: bool = True, warmup: int = 2, caches=None):
         self.layers = list(layers)
         first = self.layers[0]
         dev, cfg = first.device, first.cfg
@@ -414,9 +421,10 @@ class DecodeGraph:
         self.fused = fused
         self.x = torch.zeros(batch, cfg.hidden, dtype=torch.bfloat16, device=dev)
         self.pos = torch.zeros(1, dtype=torch.int32, device=dev)
-        self.caches = [(torch.zeros(batch, max_seq, lyr.hkv, cfg.head_dim, dtype=torch.bfloat16, device=dev),
-                        torch.zeros(batch, max_seq, lyr.hkv, cfg.head_dim, dtype=torch.bfloat16, device=dev))
-                       for lyr in self.layers]
+        # `caches`: one (k_cache, v_cache) pair per layer owned by the caller; zeroed here like the own ones
+        self.caches = caches if caches is not None else new_kv_caches(self.layers, batch, max_seq)
+        if len(self.caches) != len(self.layers) or any(kc.shape[:2] != (batch, max_seq) for kc, _ in self.caches):
+            raise ValueError("caches: one ([batch, max_seq, kv heads per rank, head_dim] x 2) pair per layer")
         # first calls allocate workspaces and rendezvous: outside the capture, on a side stream
         side = torch.cuda.Stream(dev)
         side.wait_stream(torch.cuda.current_stream(dev))
@@ -452,6 +460,60 @@ class DecodeGraph:
         self.pos.fill_(pos)
         self.graph.replay()
         return self.y
+
+
+class LlamaTPStack:
+    """A stack of decoder layers with their KV caches, the way a serving loop
+    drives them: `prefill` a prompt (sequence parallel; fills the caches), then
+    `decode_step` token by token, replayed from ONE CUDA graph on a GPU
+    (`use_graph`, default on CUDA devices) or run eagerly.  Embedding, final norm
+    and the LM head are outside (they involve none of this package's ops).
+
+        stack = LlamaTPStack(cfg, n_layers=4, device=dev, batch=4, max_seq=4096)
+        y_shard = stack.prefill(x_shard, seq=prompt_len)      # [batch * prompt_len / WS, H] in and out
+        for pos in range(prompt_len, prompt_len + new_tokens):
+            y = stack.decode_step(x, pos)                      # [batch, H] in and out, replicated on all ranks
+    """
+
+    def __init__(self, cfg: LlamaTPConfig, n_layers: int, device: torch.device, batch: int, max_seq: int,
+                 group=None, seed: int = 0, use_graph: Optional[bool] = None, **layer_kwargs):
+        self.cfg, self.batch, self.max_seq = cfg, int(batch), int(max_seq)
+        self.layers = [LlamaTPDecoderLayer(cfg, device, group=group, seed=seed + 1000 * i, **layer_kwargs)
+                       for i in range(n_layers)]
+        self.caches = new_kv_caches(self.layers, batch, max_seq)
+        self.use_graph = (device.type == "cuda") if use_graph is None else bool(use_graph)
+        self._pos = torch.zeros(1, dtype=torch.int32, device=device)
+        # built before any prefill: capturing runs warm-up steps that write into the caches
+        self.graph = DecodeGraph(self.layers, batch, max_seq, caches=self.caches) if self.use_graph else None
+
+    def reset(self) -> None:
+        """Start new sequences: zero the caches."""
+        for kc, vc in self.caches:
+            kc.zero_()
+            vc.zero_()
+
+    def prefill(self, x_shard: torch.Tensor, seq: int) -> torch.Tensor:
+        """The prompt's hidden states, this rank's [batch * seq / WS, H] rows, through every layer;
+        each layer leaves its keys and values of positions [0, seq) in its cache."""
+        if seq > self.max_seq:
+            raise ValueError(f"a prompt of {seq} tokens does not fit the cache of {self.max_seq}")
+        h = x_shard
+        for lyr, cache in zip(self.layers, self.caches):
+            h = lyr.forward(h, self.batch, seq, kv_cache=cache)
+        return h
+
+    def decode_step(self, x: torch.Tensor, pos: int) -> torch.Tensor:
+        """One token per sequence at position `pos`: [batch, H] in (replicated), [batch, H] out.  With
+        the graph the result tensor is overwritten by the next step."""
+        if self.graph is not None:
+            return self.graph.step(x, pos)
+        if not 0 <= pos < self.max_seq:
+            raise ValueError(f"position {pos} outside the cache of {self.max_seq} entries")
+        self._pos.fill_(pos)
+        h = x
+        for lyr, (kc, vc) in zip(self.layers, self.caches):
+            h = lyr.decode_static(h, kc, vc, self._pos)
+        return h
 
 
 def full_precision_reference(layers_weights: list, cfg: LlamaTPConfig, x: torch.Tensor, batch: int,

@@ -41,13 +41,13 @@ def _prepare(rank, world_size):
         lambda self, x, batch, seq, iters=5: {"norm": 1.0, "qkv": 2.0, "rest": 3.0})
 
     class EagerDecodeGraph:                            # replays by running the static step eagerly
-        def __init__(self, layers, batch, max_seq, fused=True, warmup=2):
+        def __init__(self, layers, batch, max_seq, fused=True, warmup=2, caches=None):
             self.layers, self.fused = list(layers), fused
             cfg = self.layers[0].cfg
             self.pos = torch.zeros(1, dtype=torch.int32)
-            self.caches = [(torch.zeros(batch, max_seq, lyr.hkv, cfg.head_dim, dtype=torch.bfloat16),
-                            torch.zeros(batch, max_seq, lyr.hkv, cfg.head_dim, dtype=torch.bfloat16))
-                           for lyr in self.layers]
+            self.caches = caches if caches is not None else [
+                (torch.zeros(batch, max_seq, lyr.hkv, cfg.head_dim, dtype=torch.bfloat16),
+                 torch.zeros(batch, max_seq, lyr.hkv, cfg.head_dim, dtype=torch.bfloat16)) for lyr in self.layers]
 
         def step(self, x, pos):
             self.pos.fill_(pos)

@@ -166,3 +166,57 @@ def test_decode_graph_world_of_one(fused_glue):
 @pytest.mark.parametrize("fused_glue", [False, True])
 def test_decode_graph_2gpu(fused_glue):
     spawn_ranks(_decode_graph_worker, 2, "nccl", (fused_glue,))
+
+
+def _stack_worker(rank, world_size):
+    """LlamaTPStack as a serving loop drives it: sequence-parallel prefill of the prompt into the
+    caches, then decode from the captured graph; against the prefill of the whole sequence."""
+    from symm_mem_recipes_b200.models.llama_tp_layer import LlamaTPConfig, LlamaTPStack
+    from symm_mem_recipes_b200.parallel import symm_mem
+
+    dev = torch.device("cuda", rank)
+    cfg = LlamaTPConfig.tiny(world_size)
+    batch, prompt, new_tokens = 2, 64 * world_size, 4
+    seq = prompt + new_tokens
+    stack = LlamaTPStack(cfg, 2, dev, batch, max_seq=seq + 8, seed=5)
+    assert stack.graph is not None
+    g = torch.Generator().manual_seed(2)              # same activations on every rank
+    x = (torch.randn(batch, seq, cfg.hidden, generator=g) * 0.5).to(torch.bfloat16).to(dev)
+    rows = batch * prompt // world_size
+    x_prompt = x[:, :prompt].reshape(batch * prompt, cfg.hidden)
+    y_prompt = stack.prefill(x_prompt[rank * rows:(rank + 1) * rows].contiguous(), prompt)
+    symm_mem.check_status(dev)
+    # reference: the library composition of the same layers, token by token through caches of its own
+    ref_caches = [(torch.zeros_like(kc), torch.zeros_like(vc)) for kc, vc in stack.caches]
+    failures = []
+    ref_prompt = x_prompt[rank * rows:(rank + 1) * rows].contiguous()
+    for lyr in stack.layers:
+        ref_prompt = lyr.forward_reference(ref_prompt, batch, prompt)
+    if not torch.allclose(y_prompt.float(), ref_prompt.float(), rtol=5e-2, atol=5e-2):
+        failures.append("prefill differs from the library composition")
+    for pos in range(seq):                            # fills the reference caches from position 0
+        h = x[:, pos].contiguous()
+        for lyr, (kc, vc) in zip(stack.layers, ref_caches):
+            h = lyr.decode(h, kc, vc, pos, fused=False)
+        if pos >= prompt:
+            y = stack.decode_step(x[:, pos].contiguous(), pos).clone()
+            symm_mem.check_status(dev)
+            err = (y.float() - h.float()).abs().max().item()
+            if err > 0.1:
+                failures.append(f"position {pos}: decode after prefill differs from the library composition by {err}")
+    torch.cuda.synchronize()
+    assert not failures, failures
+
+
+@pytest.mark.gpu
+@pytest.mark.first_run
+def test_stack_prefill_then_graph_decode_world_of_one():
+    torch.cuda.set_device(0)
+    _stack_worker(0, 1)
+
+
+@pytest.mark.gpu
+@pytest.mark.first_run
+@pytest.mark.multigpu(2)
+def test_stack_prefill_then_graph_decode_2gpu():
+    spawn_ranks(_stack_worker, 2, "nccl")

@@ -61,13 +61,13 @@ def _eager_decode_graph():
     from symm_mem_recipes_b200.models import llama_tp_layer
 
     class EagerDecodeGraph:                            # same interface; replays by running the static step
-        def __init__(self, layers, batch, max_seq, fused=True, warmup=2):
+        def __init__(self, layers, batch, max_seq, fused=True, warmup=2, caches=None):
             self.layers, self.fused, self.max_seq = list(layers), fused, max_seq
             cfg = self.layers[0].cfg
             self.pos = torch.zeros(1, dtype=torch.int32)
-            self.caches = [(torch.zeros(batch, max_seq, lyr.hkv, cfg.head_dim, dtype=torch.bfloat16),
-                            torch.zeros(batch, max_seq, lyr.hkv, cfg.head_dim, dtype=torch.bfloat16))
-                           for lyr in self.layers]
+            self.caches = caches if caches is not None else [
+                (torch.zeros(batch, max_seq, lyr.hkv, cfg.head_dim, dtype=torch.bfloat16),
+                 torch.zeros(batch, max_seq, lyr.hkv, cfg.head_dim, dtype=torch.bfloat16)) for lyr in self.layers]
 
         def step(self, x, pos):
             self.pos.fill_(pos)
@@ -109,6 +109,7 @@ WORKERS = [
     ("test_gpu_llama_layer", "_layer_worker", (1, 2), ()),
     ("test_gpu_llama_layer", "_layer_tp_worker", (2,), (True, True)),
     ("test_gpu_llama_layer", "_decode_graph_worker", (1, 2), (True,)),
+    ("test_gpu_llama_layer", "_stack_worker", (1, 2), ()),
     ("test_gpu_symm_mem", "_signals_gpu_worker", (2,), ()),
     ("test_gpu_symm_mem", "_compat_gpu_worker", (2,), ()),
     ("test_gpu_matmul", "_agmm_worker", (2,), (128, 256, 256, 1, "push_copy")),

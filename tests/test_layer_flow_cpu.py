@@ -163,6 +163,32 @@ def test_prefill_hands_its_kv_cache_to_decode(host_kernels, fused_glue, tp):
         layer.forward(x, batch, seq, kv_cache=(k_cache[:, :4], v_cache[:, :4]))
 
 
+def test_stack_prefill_then_decode(host_kernels):
+    """Two layers as a serving loop drives them: prefill of the prompt, then token-by-token decode;
+    against the prefill of the whole sequence through the same two layers."""
+    from symm_mem_recipes_b200.models.llama_tp_layer import LlamaTPConfig, LlamaTPStack
+
+    cfg = LlamaTPConfig.tiny(1)
+    batch, seq, prompt = 2, 24, 16
+    stack = LlamaTPStack(cfg, 2, torch.device("cpu"), batch, max_seq=seq + 4, seed=5, fused_glue=True)
+    assert stack.graph is None and len(stack.caches) == 2                  # no CUDA graphs on the CPU
+    g = torch.Generator().manual_seed(2)
+    x = (torch.randn(batch, seq, cfg.hidden, generator=g) * 0.5).to(torch.bfloat16)
+    whole = x.reshape(batch * seq, cfg.hidden)
+    for lyr in stack.layers:
+        whole = lyr.forward(whole, batch, seq)
+    whole = whole.view(batch, seq, cfg.hidden)
+    y_prompt = stack.prefill(x[:, :prompt].reshape(batch * prompt, cfg.hidden).contiguous(), prompt)
+    assert (y_prompt.view(batch, prompt, -1).float() - whole[:, :prompt].float()).abs().max().item() < 0.1
+    for pos in range(prompt, seq):
+        y = stack.decode_step(x[:, pos].contiguous(), pos)
+        assert (y.float() - whole[:, pos].float()).abs().max().item() < 0.15, pos
+    with pytest.raises(ValueError, match="outside the cache"):
+        stack.decode_step(x[:, 0].contiguous(), seq + 4)
+    stack.reset()
+    assert float(stack.caches[0][0].abs().sum()) == 0.0
+
+
 def test_phase_marks_are_off_by_default(host_kernels):
     _, layer, x, batch, seq, _ = _layer_and_reference(False, False)
     layer.forward(x, batch, seq)
