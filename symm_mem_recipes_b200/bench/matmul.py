@@ -117,6 +117,14 @@ def main() -> int:
                 "rope": (lambda: ops.rope_(qkv, 9, 128, 2048, 500000.0), 2 * T * 9 * 128 * 2),
                 "silu_mul": (lambda: ops.silu_mul(gu, act), (gu.numel() + act.numel()) * 2),
             }
+            # one decode step's attention over a full cache of 4096 entries (8 query heads on one KV head of 128)
+            for batch in (1, 16):
+                kc = (torch.randn(batch, 4096, 1, 128, device=dev) * 0.5).to(torch.bfloat16)
+                vc = torch.randn_like(kc)
+                step = (torch.randn(batch, 10 * 128, device=dev) * 0.5).to(torch.bfloat16)
+                cases[f"decode_attention_b{batch}_s4096"] = (
+                    lambda step=step, kc=kc, vc=vc: ops.decode_attention_(step, kc, vc, 8, 4095),
+                    2 * kc.numel() * 2)
             for name, (fn, nbytes) in cases.items():
                 us = benchmark_with_event(fn, **bench)
                 out[name] = {"us": round(us, 1), "gbs": round(nbytes / us / 1e3, 1)}

@@ -725,6 +725,35 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                              current_stream(dev)), "silu_mul");
   });
 
+  m.def("decode_attention_scratch_bytes", [](int batch, int hkv, int head_dim, int s_max) {
+    return decode_attention_scratch_bytes(batch, hkv, head_dim, s_max, nullptr);
+  });
+  // `pos` (optional): int32 CUDA tensor of one element holding the position; read on the device
+  m.def("decode_attention", [](torch::Tensor qkv, torch::Tensor k_cache, torch::Tensor v_cache, torch::Tensor out,
+                               torch::Tensor scratch, int hq, int hkv, int pos0, c10::optional<torch::Tensor> pos) {
+    auto ok = [](const torch::Tensor& t) {
+      return t.is_cuda() && t.is_contiguous() && t.scalar_type() == torch::kBFloat16;
+    };
+    TORCH_CHECK(ok(qkv) && ok(k_cache) && ok(v_cache) && ok(out) && qkv.dim() == 2 && k_cache.dim() == 4 &&
+                v_cache.sizes() == k_cache.sizes(), "decode_attention: contiguous bf16 CUDA tensors, caches [B, S, hkv, D]");
+    const int B = (int)qkv.size(0), s_max = (int)k_cache.size(1), D = (int)k_cache.size(3);
+    TORCH_CHECK(k_cache.size(0) == B && k_cache.size(2) == hkv && qkv.size(1) == (int64_t)(hq + 2 * hkv) * D &&
+                out.dim() == 2 && out.size(0) == B && out.size(1) == (int64_t)hq * D,
+                "decode_attention: qkv [B, (hq + 2 hkv) D], out [B, hq D]");
+    TORCH_CHECK(scratch.is_cuda() && scratch.is_contiguous() && scratch.scalar_type() == torch::kUInt8,
+                "scratch must be a uint8 CUDA tensor");
+    int dev = qkv.get_device();
+    TORCH_CHECK(!pos.has_value() || (pos->is_cuda() && pos->get_device() == dev && pos->numel() == 1 &&
+                                     pos->scalar_type() == torch::kInt32),
+                "decode_attention: pos must be an int32 tensor of one element on the same GPU");
+    c10::cuda::CUDAGuard guard(dev);
+    rt_check(launch_decode_attention(qkv.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+                                     scratch.data_ptr(), (size_t)scratch.nbytes(), B, hq, hkv, D, s_max, pos0,
+                                     pos ? static_cast<const int*>(pos->data_ptr()) : nullptr, current_stream(dev)),
+             "decode_attention");
+  }, py::arg("qkv"), py::arg("k_cache"), py::arg("v_cache"), py::arg("out"), py::arg("scratch"), py::arg("hq"),
+     py::arg("hkv"), py::arg("pos0"), py::arg("pos") = py::none());
+
   // ---- oracles (CPU tensors) ----
   m.def("oracle_rms_norm_bf16", [](torch::Tensor x, c10::optional<torch::Tensor> residual, torch::Tensor w,
                                    double eps) {
@@ -747,6 +776,22 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     TORCH_CHECK(gu.dim() == 2 && gu.size(1) % 2 == 0, "gate_up[rows, 2F]");
     torch::Tensor out = torch::empty({gu.size(0), gu.size(1) / 2}, gu.options());
     silu_mul_bf16(bf16_ptr(gu), reinterpret_cast<uint16_t*>(out.data_ptr()), gu.size(0), (int)gu.size(1) / 2);
+    return out;
+  });
+  // the caches are updated in place (CPU tensors), as the kernel does
+  m.def("oracle_decode_attention_bf16", [](torch::Tensor qkv, torch::Tensor k_cache, torch::Tensor v_cache, int hq,
+                                           int hkv, int pos) {
+    TORCH_CHECK(qkv.dim() == 2 && k_cache.dim() == 4 && v_cache.sizes() == k_cache.sizes() && hkv > 0 &&
+                k_cache.size(2) == hkv && k_cache.size(0) == qkv.size(0) && hq % hkv == 0, "bad shapes");
+    const int D = (int)k_cache.size(3), s_max = (int)k_cache.size(1), B = (int)qkv.size(0);
+    TORCH_CHECK(qkv.size(1) == (int64_t)(hq + 2 * hkv) * D && pos >= 0 && pos < s_max, "bad qkv row or position");
+    TORCH_CHECK(k_cache.is_contiguous() && v_cache.is_contiguous() && qkv.is_contiguous(), "contiguous tensors");
+    bf16_ptr(k_cache);
+    bf16_ptr(v_cache);
+    torch::Tensor out = torch::empty({B, (int64_t)hq * D}, qkv.options());
+    decode_attention_bf16(bf16_ptr(qkv), reinterpret_cast<uint16_t*>(k_cache.data_ptr()),
+                          reinterpret_cast<uint16_t*>(v_cache.data_ptr()),
+                          reinterpret_cast<uint16_t*>(out.data_ptr()), B, hq, hkv, D, s_max, pos);
     return out;
   });
   m.def("oracle_ordered_sum_bf16", [](std::vector<torch::Tensor> srcs) {

@@ -182,5 +182,14 @@ int launch_rope_inplace(void* qkv, long long tokens, int row_stride, int n_heads
                         const int* pos_dev, float theta, int num_sms, cudaStream_t stream);
 // out[rows, F] = SiLU(gate_up[:, :F]) * gate_up[:, F:].  F % 8 == 0.
 int launch_silu_mul(const void* gate_up, void* out, long long rows, int F, int num_sms, cudaStream_t stream);
+// Attention of one decode step: qkv [batch, (hq + 2 hkv) * head_dim] (new token, keys already rotated),
+// caches [batch, s_max, hkv, head_dim]; writes the new key / value into the caches at the position
+// and out [batch, hq * head_dim].  The position is `pos0`, or read from `pos_dev` on the device.
+// `scratch`: decode_attention_scratch_bytes(...) bytes, zero-filled once; head_dim 64 or 128,
+// hq / hkv <= 8.
+size_t decode_attention_scratch_bytes(int batch, int hkv, int head_dim, int s_max, int* n_split_out);
+int launch_decode_attention(const void* qkv, void* k_cache, void* v_cache, void* out, void* scratch,
+                            size_t scratch_bytes, int batch, int hq, int hkv, int head_dim, int s_max, int pos0,
+                            const int* pos_dev, cudaStream_t stream);
 
 }  // namespace smr

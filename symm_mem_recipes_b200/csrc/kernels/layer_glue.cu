@@ -1,7 +1,7 @@
 // Rank-local pieces of a Llama-style decoder layer that sit between the fused
 // GEMM + collective kernels: RMSNorm (optionally fused with the residual add
 // that precedes it), rotary embedding in place on the QKV buffer, and
-// SiLU(gate) * up.  Each is one pass over its operand in bf16 with fp32 math;
+// SiLU(gate) * up, and the attention of one decode step.  Each is one pass over its operand in bf16 with fp32 math;
 // the PyTorch compositions they replace take five to ten passes with fp32
 // temporaries.  No upstream counterpart (the upstream recipes stop at the
 // single fused op).
@@ -14,6 +14,7 @@
 //   rope:      pairs (i, i + D/2) of every rotated head, Llama convention:
 //              angle = pos * theta^(-2i/D), fp32; results rounded to bf16.
 //   silu_mul:  out = bf16( g / (1 + exp(-g)) * u ) for gate g, up u.
+//   decode_attention: softmax(q . K / sqrt(D)) V over the cached positions 0..pos, fp32; bf16 out.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
@@ -163,6 +164,137 @@ __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloa
   }
 }
 
+// One decode step of attention (one new token per sequence) for this rank's heads, split along the
+// cached sequence ("flash decoding"): CTA (b x kv head, split) has four warps, each a unit that walks
+// positions unit, unit + n_units, ... <= pos with an online softmax for the G = hq / hkv query heads
+// that share the KV head (a lane owns VEC of the D = 32 * VEC dimensions; one K row is one coalesced
+// warp load).  Units park (max, sum, weighted V) in scratch; the last CTA of a (b, kv head) to
+// arrive combines them and writes bf16.  The new token's key and value come from the QKV row (and
+// are written into the caches by split 0), so no CTA depends on another's cache write.  The
+// position may come from device memory, and the grid does not depend on it: a captured graph
+// serves every position.
+constexpr int kAttnWarps = 4;
+constexpr int kAttnMaxG = 8;
+
+// VEC (2 or 4) consecutive bf16 as one 4- or 8-byte access
+template <int VEC>
+__device__ __forceinline__ void load_bf16_vec(const __nv_bfloat16* p, float (&f)[VEC]) {
+  static_assert(VEC == 2 || VEC == 4, "a lane owns 2 or 4 of the head's dimensions");
+  if constexpr (VEC == 4) {
+    const uint2 w = *reinterpret_cast<const uint2*>(p);
+    f[0] = bf16lo_to_f32(w.x); f[1] = bf16hi_to_f32(w.x);
+    f[2] = bf16lo_to_f32(w.y); f[3] = bf16hi_to_f32(w.y);
+  } else {
+    const uint32_t w = *reinterpret_cast<const uint32_t*>(p);
+    f[0] = bf16lo_to_f32(w); f[1] = bf16hi_to_f32(w);
+  }
+}
+template <int VEC>
+__device__ __forceinline__ void copy_bf16_vec(__nv_bfloat16* dst, const __nv_bfloat16* src) {
+  if constexpr (VEC == 4) *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(src);
+  else *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(src);
+}
+
+template <int VEC>
+__global__ void __launch_bounds__(kAttnWarps * 32)
+decode_attention_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* k_cache, __nv_bfloat16* v_cache,
+                        __nv_bfloat16* __restrict__ out, float* scratch, unsigned int* counters, int hq, int hkv,
+                        int s_max, int pos0, const int* __restrict__ pos_dev, float scale) {
+  constexpr int D = 32 * VEC;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bh = blockIdx.x, b = bh / hkv, kvh = bh - b * hkv;
+  const int n_split = gridDim.y, split = blockIdx.y;
+  const int n_units = n_split * kAttnWarps, unit = split * kAttnWarps + warp;
+  const int G = hq / hkv;
+  int pos = pos_dev != nullptr ? *pos_dev : pos0;
+  pos = pos < 0 ? 0 : (pos >= s_max ? s_max - 1 : pos);
+  const __nv_bfloat16* row = qkv + (size_t)b * (hq + 2 * hkv) * D;
+  const __nv_bfloat16* k_new = row + (size_t)hq * D + (size_t)kvh * D + lane * VEC;
+  const __nv_bfloat16* v_new = row + (size_t)(hq + hkv) * D + (size_t)kvh * D + lane * VEC;
+
+  float q[kAttnMaxG][VEC], acc[kAttnMaxG][VEC], m[kAttnMaxG], l[kAttnMaxG];
+#pragma unroll
+  for (int g = 0; g < kAttnMaxG; ++g) {
+    m[g] = -INFINITY;
+    l[g] = 0.f;
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) acc[g][j] = q[g][j] = 0.f;
+    if (g < G) {
+      load_bf16_vec<VEC>(row + (size_t)(kvh * G + g) * D + lane * VEC, q[g]);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) q[g][j] *= scale;
+    }
+  }
+  for (int p = unit; p <= pos; p += n_units) {
+    const size_t off = (((size_t)b * s_max + p) * hkv + kvh) * D + lane * VEC;
+    const __nv_bfloat16* kp = p == pos ? k_new : k_cache + off;
+    const __nv_bfloat16* vp = p == pos ? v_new : v_cache + off;
+    float k[VEC], v[VEC];
+    load_bf16_vec<VEC>(kp, k);
+    load_bf16_vec<VEC>(vp, v);
+#pragma unroll
+    for (int g = 0; g < kAttnMaxG; ++g) {
+      if (g < G) {
+        float s = 0.f;
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) s += q[g][j] * k[j];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        const float m_new = fmaxf(m[g], s);
+        const float corr = __expf(m[g] - m_new), w = __expf(s - m_new);
+        l[g] = l[g] * corr + w;
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) acc[g][j] = acc[g][j] * corr + w * v[j];
+        m[g] = m_new;
+      }
+    }
+  }
+  if (split == 0 && warp == 0) {                      // the new token's key and value enter the caches
+    const size_t off = (((size_t)b * s_max + pos) * hkv + kvh) * D + lane * VEC;
+    copy_bf16_vec<VEC>(k_cache + off, k_new);
+    copy_bf16_vec<VEC>(v_cache + off, v_new);
+  }
+  // park this unit's partial: per query head D weighted-V sums, then max and sum
+  float* mine = scratch + ((size_t)bh * n_units + unit) * kAttnMaxG * (D + 2);
+#pragma unroll
+  for (int g = 0; g < kAttnMaxG; ++g) {
+    if (g < G) {
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) mine[g * (D + 2) + lane * VEC + j] = acc[g][j];
+      if (lane == 0) {
+        mine[g * (D + 2) + D] = m[g];
+        mine[g * (D + 2) + D + 1] = l[g];
+      }
+    }
+  }
+  __threadfence();
+  __syncthreads();
+  __shared__ int is_last;
+  if (threadIdx.x == 0) is_last = atomicAdd(&counters[bh], 1u) == (unsigned int)(n_split - 1);
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  const float* all = scratch + (size_t)bh * n_units * kAttnMaxG * (D + 2);
+  for (int g = warp; g < G; g += kAttnWarps) {        // a warp per query head
+    float big = -INFINITY;
+    for (int u = 0; u < n_units; ++u) big = fmaxf(big, __ldcg(all + ((size_t)u * kAttnMaxG + g) * (D + 2) + D));
+    float sum = 0.f, o[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) o[j] = 0.f;
+    for (int u = 0; u < n_units; ++u) {
+      const float* part = all + ((size_t)u * kAttnMaxG + g) * (D + 2);
+      const float w = __expf(__ldcg(part + D) - big);  // 0 for a unit that saw no position (max = -inf)
+      sum += w * __ldcg(part + D + 1);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) o[j] += w * __ldcg(part + lane * VEC + j);
+    }
+    __nv_bfloat16* dst = out + ((size_t)b * hq + kvh * G + g) * D + lane * VEC;
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) dst[j] = __float2bfloat16_rn(o[j] / sum);
+  }
+  if (threadIdx.x == 0) counters[bh] = 0u;            // ready for the next launch
+}
+
 int grid_for(long long items, int threads, int num_sms) {
   long long blocks = (items + threads - 1) / threads;
   const long long cap = (long long)num_sms * 8;
@@ -207,6 +339,45 @@ int launch_silu_mul(const void* gate_up, void* out, long long rows, int F, int n
   const long long n_vec = rows * (F / 8);
   silu_mul_kernel<<<grid_for(n_vec, 256, num_sms), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(gate_up),
                                                                     static_cast<__nv_bfloat16*>(out), n_vec, F);
+  return (int)cudaGetLastError();
+}
+
+size_t decode_attention_scratch_bytes(int batch, int hkv, int head_dim, int s_max, int* n_split_out) {
+  // enough units to spread a long cache over the SMs, few enough for one CTA to combine them
+  int n_split = (s_max + 255) / 256;
+  n_split = n_split < 1 ? 1 : (n_split > 16 ? 16 : n_split);
+  if (n_split_out) *n_split_out = n_split;
+  const size_t partials = (size_t)batch * hkv * n_split * kAttnWarps * kAttnMaxG * (head_dim + 2) * sizeof(float);
+  return 256 + ((size_t)batch * hkv * sizeof(unsigned int) + 255) / 256 * 256 + partials;
+}
+
+int launch_decode_attention(const void* qkv, void* k_cache, void* v_cache, void* out, void* scratch,
+                            size_t scratch_bytes, int batch, int hq, int hkv, int head_dim, int s_max, int pos0,
+                            const int* pos_dev, cudaStream_t stream) {
+  if (batch < 1 || hq < 1 || hkv < 1 || hq % hkv != 0 || hq / hkv > kAttnMaxG || (head_dim != 64 && head_dim != 128) ||
+      s_max < 1 || (pos_dev == nullptr && (pos0 < 0 || pos0 >= s_max)))
+    return cudaErrorInvalidValue;
+  if (!aligned16(qkv) || !aligned16(k_cache) || !aligned16(v_cache) || !aligned16(out) || !aligned16(scratch))
+    return cudaErrorInvalidValue;
+  int n_split = 1;
+  if (decode_attention_scratch_bytes(batch, hkv, head_dim, s_max, &n_split) > scratch_bytes) return cudaErrorInvalidValue;
+  // layout of the scratch: [0, 256) unused, then one arrival counter per (b, kv head) (zero between
+  // launches: the combining CTA resets it), then the partials
+  unsigned int* counters = reinterpret_cast<unsigned int*>(static_cast<char*>(scratch) + 256);
+  const size_t counter_bytes = ((size_t)batch * hkv * sizeof(unsigned int) + 255) / 256 * 256;
+  float* partials = reinterpret_cast<float*>(static_cast<char*>(scratch) + 256 + counter_bytes);
+  const dim3 grid((unsigned)(batch * hkv), (unsigned)n_split);
+  const float scale = 1.0f / sqrtf((float)head_dim);
+  auto q = static_cast<const __nv_bfloat16*>(qkv);
+  auto kc = static_cast<__nv_bfloat16*>(k_cache);
+  auto vc = static_cast<__nv_bfloat16*>(v_cache);
+  auto o = static_cast<__nv_bfloat16*>(out);
+  if (head_dim == 128)
+    decode_attention_kernel<4><<<grid, kAttnWarps * 32, 0, stream>>>(q, kc, vc, o, partials, counters, hq, hkv, s_max,
+                                                                      pos0, pos_dev, scale);
+  else
+    decode_attention_kernel<2><<<grid, kAttnWarps * 32, 0, stream>>>(q, kc, vc, o, partials, counters, hq, hkv, s_max,
+                                                                      pos0, pos_dev, scale);
   return (int)cudaGetLastError();
 }
 

@@ -96,4 +96,43 @@ void silu_mul_bf16(const uint16_t* gu, uint16_t* out, long long rows, int F) {
     }
 }
 
+void decode_attention_bf16(const uint16_t* qkv, uint16_t* k_cache, uint16_t* v_cache, uint16_t* out, int B, int hq,
+                           int hkv, int D, int s_max, int pos) {
+  const int row = (hq + 2 * hkv) * D, G = hq / hkv;
+  const float scale = 1.0f / std::sqrt((float)D);
+  std::vector<float> score((size_t)pos + 1), acc((size_t)D);
+  for (int b = 0; b < B; ++b) {
+    const uint16_t* r = qkv + (size_t)b * row;
+    for (int kvh = 0; kvh < hkv; ++kvh) {
+      uint16_t* kc = k_cache + (((size_t)b * s_max + pos) * hkv + kvh) * D;
+      uint16_t* vc = v_cache + (((size_t)b * s_max + pos) * hkv + kvh) * D;
+      for (int d = 0; d < D; ++d) {
+        kc[d] = r[(size_t)hq * D + (size_t)kvh * D + d];
+        vc[d] = r[(size_t)(hq + hkv) * D + (size_t)kvh * D + d];
+      }
+    }
+    for (int h = 0; h < hq; ++h) {
+      const int kvh = h / G;
+      const uint16_t* q = r + (size_t)h * D;
+      float m = -INFINITY;
+      for (int p = 0; p <= pos; ++p) {
+        const uint16_t* k = k_cache + (((size_t)b * s_max + p) * hkv + kvh) * D;
+        float s = 0.f;
+        for (int d = 0; d < D; ++d) s += bf16_to_f32(q[d]) * bf16_to_f32(k[d]);
+        score[p] = s * scale;
+        m = std::max(m, score[p]);
+      }
+      float l = 0.f;
+      std::fill(acc.begin(), acc.end(), 0.f);
+      for (int p = 0; p <= pos; ++p) {
+        const float w = std::exp(score[p] - m);
+        const uint16_t* v = v_cache + (((size_t)b * s_max + p) * hkv + kvh) * D;
+        l += w;
+        for (int d = 0; d < D; ++d) acc[d] += w * bf16_to_f32(v[d]);
+      }
+      for (int d = 0; d < D; ++d) out[((size_t)b * hq + h) * D + d] = f32_to_bf16(acc[d] / l);
+    }
+  }
+}
+
 }  // namespace smr

@@ -50,5 +50,11 @@ void rms_norm_bf16(const uint16_t* x, const uint16_t* residual, const uint16_t* 
 void rope_bf16(uint16_t* qkv, long long tokens, int row_stride, int n_heads, int D, int seq, int pos0, float theta);
 // out[T, F] = bf16( silu(gu[:, :F]) * gu[:, F:] )
 void silu_mul_bf16(const uint16_t* gu, uint16_t* out, long long rows, int F);
+// One decode step of attention for this rank's heads.  qkv [B, (hq + 2 hkv) * D] holds the new
+// token's (already rotated) queries and keys and its values; caches are [B, s_max, hkv, D].  Writes
+// the new key / value rows into the caches at `pos`, then out[b, h] = softmax(q_h . K[0..pos] /
+// sqrt(D)) V[0..pos] for every query head h (head h reads KV head h / (hq / hkv)); fp32 math, bf16 out.
+void decode_attention_bf16(const uint16_t* qkv, uint16_t* k_cache, uint16_t* v_cache, uint16_t* out, int B, int hq,
+                           int hkv, int D, int s_max, int pos);
 
 }  // namespace smr

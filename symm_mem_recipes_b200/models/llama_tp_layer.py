@@ -346,7 +346,10 @@ class LlamaTPDecoderLayer:
         glue = fused and self.fused_glue
         qkv = self._decode_norm(x, self.norm1, glue) @ self.w_qkv.t()
         if glue:
+            # rotate Q and K in place, then ONE kernel writes the caches and attends over positions 0..pos
             ops.rope_(qkv, hq + hkv, D, 1, cfg.rope_theta, pos0=pos)
+            o_proj = self._row_parallel_decode(ops.decode_attention_(qkv, k_cache, v_cache, hq, pos), "o", fused)
+            return self._decode_mlp(x, o_proj, fused, glue)
         q, k, v = qkv.split([hq * D, hkv * D, hkv * D], dim=-1)
         q, k = q.view(B, 1, hq, D), k.view(B, 1, hkv, D)
         if not glue:
@@ -373,6 +376,8 @@ class LlamaTPDecoderLayer:
         qkv = self._decode_norm(x, self.norm1, glue) @ self.w_qkv.t()
         if glue:
             ops.rope_(qkv, hq + hkv, D, 1, cfg.rope_theta, pos0=pos)
+            o_proj = self._row_parallel_decode(ops.decode_attention_(qkv, k_cache, v_cache, hq, pos), "o", fused)
+            return self._decode_mlp(x, o_proj, fused, glue)
         q, k, v = qkv.split([hq * D, hkv * D, hkv * D], dim=-1)
         q, k = q.view(B, 1, hq, D), k.view(B, 1, hkv, D)
         if not glue:

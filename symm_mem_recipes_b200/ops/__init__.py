@@ -6,4 +6,4 @@ from .ag_matmul import (AgMatmulConfig, all_gather_matmul, interleave_gate_up, m
 from .gemv_all_reduce import gemv_all_reduce, reference_gemv_all_reduce  # noqa: F401
 from .matmul_reduce_scatter import (matmul_all_reduce, matmul_reduce_scatter,  # noqa: F401
                                     reference_matmul_all_reduce, reference_matmul_reduce_scatter)
-from .layer_glue import rms_norm, rope_, silu_mul  # noqa: F401
+from .layer_glue import decode_attention_, rms_norm, rope_, silu_mul  # noqa: F401

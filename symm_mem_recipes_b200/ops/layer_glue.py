@@ -90,3 +90,46 @@ def silu_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch
         out = torch.empty(gate_up.shape[0], gate_up.shape[1] // 2, dtype=torch.bfloat16, device=gate_up.device)
     C.silu_mul(gate_up, out, _num_sms(gate_up.device))
     return out
+
+
+_attn_scratch: dict[tuple, torch.Tensor] = {}
+
+
+@traced("smr.decode_attention_")
+def decode_attention_(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, n_q_heads: int,
+                      pos: Union[int, torch.Tensor], out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Attention of one decode step in one kernel.  `qkv` [B, (hq + 2 hkv) * D]
+    holds the new token's queries and keys (already rotated, see `rope_`) and its
+    values; the caches are [B, S_max, hkv, D].  Writes the new key and value into
+    the caches at `pos` (hence the trailing underscore) and returns
+    `out[B, hq * D] = softmax(q . K[0..pos] / sqrt(D)) V[0..pos]` per query head
+    (grouped-query: head h reads KV head h // (hq / hkv)).  The cached sequence
+    is split over CTAs whatever the position, and `pos` may be an int32 tensor
+    of one element on the device, so a captured CUDA graph serves every
+    position.  Replaces, in a decode step, two cache writes and PyTorch's
+    attention under a mask (about ten small kernels).  D is 64 or 128 and
+    hq / hkv at most 8."""
+    _check("qkv", qkv, 2)
+    _check("k_cache", k_cache, 4)
+    _check("v_cache", v_cache, 4)
+    B, s_max, hkv, D = k_cache.shape
+    if v_cache.shape != k_cache.shape or qkv.shape != (B, (n_q_heads + 2 * hkv) * D):
+        raise SymmMemError("need caches [B, S_max, hkv, D] and qkv [B, (hq + 2 hkv) * D]")
+    if n_q_heads % hkv or n_q_heads // hkv > 8 or D not in (64, 128):
+        raise SymmMemError("need hq a multiple of hkv with hq / hkv <= 8, and head_dim 64 or 128")
+    if out is None:
+        out = torch.empty(B, n_q_heads * D, dtype=torch.bfloat16, device=qkv.device)
+    key = (qkv.device.type, qkv.device.index, B, hkv, D, s_max)
+    scratch = _attn_scratch.get(key)
+    if scratch is None:
+        scratch = torch.zeros(C.decode_attention_scratch_bytes(B, hkv, D, s_max), dtype=torch.uint8, device=qkv.device)
+        _attn_scratch[key] = scratch
+    if isinstance(pos, torch.Tensor):
+        if pos.dtype != torch.int32 or pos.numel() != 1 or pos.device != qkv.device:
+            raise SymmMemError("a position tensor must be int32, of one element, on qkv's device")
+        C.decode_attention(qkv, k_cache, v_cache, out, scratch, int(n_q_heads), int(hkv), 0, pos)
+    else:
+        if not 0 <= int(pos) < s_max:
+            raise SymmMemError(f"position {pos} outside the cache of {s_max} entries")
+        C.decode_attention(qkv, k_cache, v_cache, out, scratch, int(n_q_heads), int(hkv), int(pos))
+    return out

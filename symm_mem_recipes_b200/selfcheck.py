@@ -242,10 +242,16 @@ def build_checks(first_run: bool, world: int, rank: int, dev: torch.device) -> l
         ok2 = _close(ops.rope_(qkv.clone(), 5, 64, 24, 500000.0).cpu(), ref_q, 2.0 ** -7, 4e-3)[0]
         gu = randn(50, 2 * 48, std=3.0, seed=5)
         ok3 = _close(ops.silu_mul(gu).cpu(), C.oracle_silu_mul_bf16(gu.cpu()), 2.0 ** -7, 1e-6)[0]
+        kc, vc = randn(2, 300, 1, 128, std=0.7, seed=6), randn(2, 300, 1, 128, std=0.7, seed=7)
+        step = randn(2, (8 + 2) * 128, std=0.7, seed=8)
+        kc_cpu, vc_cpu = kc.cpu(), vc.cpu()
+        ref_a = C.oracle_decode_attention_bf16(step.cpu(), kc_cpu, vc_cpu, 8, 1, 257)
+        got_a = ops.decode_attention_(step, kc, vc, 8, 257)
+        ok4 = _close(got_a.cpu(), ref_a, 2.0 ** -6, 4e-3)[0] and torch.equal(kc.cpu(), kc_cpu)
         symm_mem.check_status(dev)
-        return ok1 and ok2 and ok3, f"rms_norm {ok1}, rope {ok2}, silu_mul {ok3}"
+        return ok1 and ok2 and ok3 and ok4, f"rms_norm {ok1}, rope {ok2}, silu_mul {ok3}, decode_attention {ok4}"
 
-    add("glue", "rms_norm / rope / silu_mul", glue, True)
+    add("glue", "rms_norm / rope / silu_mul / decode_attention", glue, True)
 
     def layer(kind, fused_glue=False, fused_swiglu=False):
         def fn():

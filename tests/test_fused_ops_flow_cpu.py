@@ -263,6 +263,11 @@ def _install_row_parallel_and_glue_stand_ins():
             qkv.copy_(real.oracle_rope_bf16(qkv, n_heads, head_dim, seq, pos0, theta))
 
         @staticmethod
+        def decode_attention(qkv, k_cache, v_cache, out, scratch, hq, hkv, pos0, pos=None):
+            where = pos0 if pos is None else int(pos)
+            out.copy_(real.oracle_decode_attention_bf16(qkv, k_cache, v_cache, hq, hkv, where))
+
+        @staticmethod
         def silu_mul(gate_up, out, num_sms):
             out.copy_(real.oracle_silu_mul_bf16(gate_up))
 

@@ -134,3 +134,36 @@ def test_layer_with_fused_swiglu_matches_fp32():
                 layer.norm1.cpu(), layer.norm2.cpu())]
     ref = full_precision_reference(weights, cfg, x.cpu(), batch, seq)
     assert (y.float().cpu() - ref).abs().max().item() < 0.1
+
+
+@pytest.mark.parametrize("B,hq,hkv,D,s_max,positions", [
+    (1, 8, 1, 128, 4096, (0, 1, 255, 256, 2047, 4095)),      # the 70B shape per rank at TP8, long cache
+    (16, 8, 1, 128, 512, (0, 300, 511)),
+    (3, 4, 2, 64, 40, (0, 7, 39)),                            # two KV heads, 64-wide heads, one split
+    (2, 4, 4, 64, 700, (5, 699)),                             # no grouping (one query head per KV head)
+])
+def test_decode_attention(B, hq, hkv, D, s_max, positions):
+    """One kernel for a decode step's attention (cache write + softmax(QK^T)V over 0..pos) against the
+    CPU oracle; the position both as a launch argument and from a device tensor; repeated calls reuse
+    the scratch and its arrival counters."""
+    from symm_mem_recipes_b200 import ops
+    from symm_mem_recipes_b200._ext import C
+
+    g = torch.Generator().manual_seed(B * 1000 + s_max)
+    k_cache = (torch.randn(B, s_max, hkv, D, generator=g) * 0.7).to(torch.bfloat16)
+    v_cache = (torch.randn(B, s_max, hkv, D, generator=g) * 0.7).to(torch.bfloat16)
+    k_dev, v_dev = k_cache.cuda(), v_cache.cuda()
+    pos_dev = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for i, pos in enumerate(positions):
+        qkv = (torch.randn(B, (hq + 2 * hkv) * D, generator=g) * 0.7).to(torch.bfloat16)
+        want = C.oracle_decode_attention_bf16(qkv, k_cache, v_cache, hq, hkv, pos)       # updates the CPU caches
+        if i % 2 == 0:
+            got = ops.decode_attention_(qkv.cuda(), k_dev, v_dev, hq, pos)
+        else:
+            pos_dev.fill_(pos)
+            got = ops.decode_attention_(qkv.cuda(), k_dev, v_dev, hq, pos_dev)
+        err = (got.float().cpu() - want.float()).abs()
+        # fp32 sums in another order and fast exp: a bf16 ulp of the output, which is an average of values ~0.7
+        assert bool((err <= want.float().abs() * 2.0 ** -6 + 4e-3).all()), (pos, float(err.max()))
+        assert torch.equal(k_dev.cpu(), k_cache) and torch.equal(v_dev.cpu(), v_cache), pos     # caches written
+    torch.cuda.synchronize()

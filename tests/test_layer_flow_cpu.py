@@ -42,6 +42,11 @@ class _FakeC:
         qkv.copy_(REAL_C.oracle_rope_bf16(qkv, n_heads, head_dim, seq, pos0, theta))
 
     @staticmethod
+    def decode_attention(qkv, k_cache, v_cache, out, scratch, hq, hkv, pos0, pos=None):
+        where = pos0 if pos is None else int(pos)
+        out.copy_(REAL_C.oracle_decode_attention_bf16(qkv, k_cache, v_cache, hq, hkv, where))
+
+    @staticmethod
     def silu_mul(gate_up, out, num_sms):
         out.copy_(REAL_C.oracle_silu_mul_bf16(gate_up))
 
