@@ -165,16 +165,18 @@ __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloa
 }
 
 // One decode step of attention (one new token per sequence) for this rank's heads, split along the
-// cached sequence ("flash decoding"): CTA (b x kv head, split) has four warps, each a unit that walks
-// positions unit, unit + n_units, ... <= pos with an online softmax for the G = hq / hkv query heads
-// that share the KV head (a lane owns VEC of the D = 32 * VEC dimensions; one K row is one coalesced
-// warp load).  Units park (max, sum, weighted V) in scratch; the last CTA of a (b, kv head) to
-// arrive combines them and writes bf16.  The new token's key and value come from the QKV row (and
-// are written into the caches by split 0), so no CTA depends on another's cache write.  The
-// position may come from device memory, and the grid does not depend on it: a captured graph
-// serves every position.
-constexpr int kAttnWarps = 4;
+// cached sequence ("flash decoding").  CTA (b x kv head, split) has eight warps; warp `unit` walks
+// positions unit, unit + n_units, ... <= pos, four at a time (eight independent row loads in flight),
+// with an online softmax for the G = hq / hkv query heads that share the KV head: a lane owns VEC of
+// the D = 32 * VEC dimensions, so one K or V row is one coalesced warp load.  The warps of a CTA
+// merge their (max, sum, weighted V) through shared memory into one partial per CTA in scratch; the
+// last CTA of a (b, kv head) to arrive merges those and writes bf16.  The new token's key and value
+// come from the QKV row (split 0 also writes them into the caches), so no CTA depends on another's
+// cache write.  The position may come from device memory and the grid does not depend on it: a
+// captured graph serves every position.
+constexpr int kAttnWarps = 8;
 constexpr int kAttnMaxG = 8;
+constexpr int kAttnBatch = 4;            // positions whose rows are loaded before any is used
 
 // VEC (2 or 4) consecutive bf16 as one 4- or 8-byte access
 template <int VEC>
@@ -195,12 +197,35 @@ __device__ __forceinline__ void copy_bf16_vec(__nv_bfloat16* dst, const __nv_bfl
   else *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(src);
 }
 
+// Merges `n` partials of query head g, dimension d: partial i has its max at m[i * m_stride], its sum
+// at l[i * m_stride] and its weighted V at a[i * a_stride].  Returns the merged weighted V, max, sum.
+// kGlobal: the partials were written by other CTAs (read past L1).
+template <bool kGlobal>
+__device__ __forceinline__ void merge_partials(const float* m, const float* l, const float* a, int n, int m_stride,
+                                               int a_stride, float& out_a, float& out_m, float& out_l) {
+  auto ld = [](const float* p) { return kGlobal ? __ldcg(p) : *p; };
+  float big = -INFINITY;
+#pragma unroll 8
+  for (int i = 0; i < n; ++i) big = fmaxf(big, ld(m + (size_t)i * m_stride));
+  float sum = 0.f, acc = 0.f;
+#pragma unroll 8
+  for (int i = 0; i < n; ++i) {
+    const float w = __expf(ld(m + (size_t)i * m_stride) - big);   // 0 for a partial that saw no position
+    sum += w * ld(l + (size_t)i * m_stride);
+    acc += w * ld(a + (size_t)i * a_stride);
+  }
+  out_a = acc; out_m = big; out_l = sum;
+}
+
 template <int VEC>
 __global__ void __launch_bounds__(kAttnWarps * 32)
 decode_attention_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* k_cache, __nv_bfloat16* v_cache,
                         __nv_bfloat16* __restrict__ out, float* scratch, unsigned int* counters, int hq, int hkv,
                         int s_max, int pos0, const int* __restrict__ pos_dev, float scale) {
   constexpr int D = 32 * VEC;
+  constexpr int kRow = D + 2;                                  // D weighted-V sums, then max and sum
+  __shared__ float sm[kAttnWarps][kAttnMaxG][kRow];
+  __shared__ int is_last;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bh = blockIdx.x, b = bh / hkv, kvh = bh - b * hkv;
   const int n_split = gridDim.y, split = blockIdx.y;
@@ -225,27 +250,36 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* k_
       for (int j = 0; j < VEC; ++j) q[g][j] *= scale;
     }
   }
-  for (int p = unit; p <= pos; p += n_units) {
-    const size_t off = (((size_t)b * s_max + p) * hkv + kvh) * D + lane * VEC;
-    const __nv_bfloat16* kp = p == pos ? k_new : k_cache + off;
-    const __nv_bfloat16* vp = p == pos ? v_new : v_cache + off;
-    float k[VEC], v[VEC];
-    load_bf16_vec<VEC>(kp, k);
-    load_bf16_vec<VEC>(vp, v);
+  for (int p0 = unit; p0 <= pos; p0 += kAttnBatch * n_units) {
+    float k[kAttnBatch][VEC], v[kAttnBatch][VEC];
 #pragma unroll
-    for (int g = 0; g < kAttnMaxG; ++g) {
-      if (g < G) {
-        float s = 0.f;
+    for (int i = 0; i < kAttnBatch; ++i) {                      // all loads of the batch before any use
+      const int p = p0 + i * n_units;
+      if (p <= pos) {
+        const size_t off = (((size_t)b * s_max + p) * hkv + kvh) * D + lane * VEC;
+        load_bf16_vec<VEC>(p == pos ? k_new : k_cache + off, k[i]);
+        load_bf16_vec<VEC>(p == pos ? v_new : v_cache + off, v[i]);
+      }
+    }
 #pragma unroll
-        for (int j = 0; j < VEC; ++j) s += q[g][j] * k[j];
+    for (int i = 0; i < kAttnBatch; ++i) {
+      if (p0 + i * n_units <= pos) {                            // uniform over the warp
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-        const float m_new = fmaxf(m[g], s);
-        const float corr = __expf(m[g] - m_new), w = __expf(s - m_new);
-        l[g] = l[g] * corr + w;
+        for (int g = 0; g < kAttnMaxG; ++g) {
+          if (g < G) {
+            float s = 0.f;
 #pragma unroll
-        for (int j = 0; j < VEC; ++j) acc[g][j] = acc[g][j] * corr + w * v[j];
-        m[g] = m_new;
+            for (int j = 0; j < VEC; ++j) s += q[g][j] * k[i][j];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            const float m_new = fmaxf(m[g], s);
+            const float corr = __expf(m[g] - m_new), w = __expf(s - m_new);
+            l[g] = l[g] * corr + w;
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) acc[g][j] = acc[g][j] * corr + w * v[i][j];
+            m[g] = m_new;
+          }
+        }
       }
     }
   }
@@ -254,43 +288,45 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* k_
     copy_bf16_vec<VEC>(k_cache + off, k_new);
     copy_bf16_vec<VEC>(v_cache + off, v_new);
   }
-  // park this unit's partial: per query head D weighted-V sums, then max and sum
-  float* mine = scratch + ((size_t)bh * n_units + unit) * kAttnMaxG * (D + 2);
+  // ---- the CTA's warps merge through shared memory into one partial per CTA ----
 #pragma unroll
   for (int g = 0; g < kAttnMaxG; ++g) {
     if (g < G) {
 #pragma unroll
-      for (int j = 0; j < VEC; ++j) mine[g * (D + 2) + lane * VEC + j] = acc[g][j];
+      for (int j = 0; j < VEC; ++j) sm[warp][g][lane * VEC + j] = acc[g][j];
       if (lane == 0) {
-        mine[g * (D + 2) + D] = m[g];
-        mine[g * (D + 2) + D + 1] = l[g];
+        sm[warp][g][D] = m[g];
+        sm[warp][g][D + 1] = l[g];
       }
+    }
+  }
+  __syncthreads();
+  float* mine = scratch + ((size_t)bh * n_split + split) * kAttnMaxG * kRow;
+  for (int item = threadIdx.x; item < G * D; item += kAttnWarps * 32) {
+    const int g = item / D, d = item - g * D;
+    float a, mm, ll;
+    merge_partials<false>(&sm[0][g][D], &sm[0][g][D + 1], &sm[0][g][d], kAttnWarps, kAttnMaxG * kRow,
+                          kAttnMaxG * kRow, a, mm, ll);
+    mine[g * kRow + d] = a;
+    if (d == 0) {
+      mine[g * kRow + D] = mm;
+      mine[g * kRow + D + 1] = ll;
     }
   }
   __threadfence();
   __syncthreads();
-  __shared__ int is_last;
   if (threadIdx.x == 0) is_last = atomicAdd(&counters[bh], 1u) == (unsigned int)(n_split - 1);
   __syncthreads();
   if (!is_last) return;
+  // ---- the last CTA of this (b, kv head) merges the CTAs' partials ----
   __threadfence();
-  const float* all = scratch + (size_t)bh * n_units * kAttnMaxG * (D + 2);
-  for (int g = warp; g < G; g += kAttnWarps) {        // a warp per query head
-    float big = -INFINITY;
-    for (int u = 0; u < n_units; ++u) big = fmaxf(big, __ldcg(all + ((size_t)u * kAttnMaxG + g) * (D + 2) + D));
-    float sum = 0.f, o[VEC];
-#pragma unroll
-    for (int j = 0; j < VEC; ++j) o[j] = 0.f;
-    for (int u = 0; u < n_units; ++u) {
-      const float* part = all + ((size_t)u * kAttnMaxG + g) * (D + 2);
-      const float w = __expf(__ldcg(part + D) - big);  // 0 for a unit that saw no position (max = -inf)
-      sum += w * __ldcg(part + D + 1);
-#pragma unroll
-      for (int j = 0; j < VEC; ++j) o[j] += w * __ldcg(part + lane * VEC + j);
-    }
-    __nv_bfloat16* dst = out + ((size_t)b * hq + kvh * G + g) * D + lane * VEC;
-#pragma unroll
-    for (int j = 0; j < VEC; ++j) dst[j] = __float2bfloat16_rn(o[j] / sum);
+  const float* all = scratch + (size_t)bh * n_split * kAttnMaxG * kRow;
+  for (int item = threadIdx.x; item < G * D; item += kAttnWarps * 32) {
+    const int g = item / D, d = item - g * D;
+    float a, mm, ll;
+    merge_partials<true>(all + g * kRow + D, all + g * kRow + D + 1, all + g * kRow + d, n_split, kAttnMaxG * kRow,
+                         kAttnMaxG * kRow, a, mm, ll);
+    out[((size_t)b * hq + kvh * G + g) * D + d] = __float2bfloat16_rn(a / ll);
   }
   if (threadIdx.x == 0) counters[bh] = 0u;            // ready for the next launch
 }
@@ -345,9 +381,9 @@ int launch_silu_mul(const void* gate_up, void* out, long long rows, int F, int n
 size_t decode_attention_scratch_bytes(int batch, int hkv, int head_dim, int s_max, int* n_split_out) {
   // enough units to spread a long cache over the SMs, few enough for one CTA to combine them
   int n_split = (s_max + 255) / 256;
-  n_split = n_split < 1 ? 1 : (n_split > 16 ? 16 : n_split);
+  n_split = n_split < 1 ? 1 : (n_split > 32 ? 32 : n_split);
   if (n_split_out) *n_split_out = n_split;
-  const size_t partials = (size_t)batch * hkv * n_split * kAttnWarps * kAttnMaxG * (head_dim + 2) * sizeof(float);
+  const size_t partials = (size_t)batch * hkv * n_split * kAttnMaxG * (head_dim + 2) * sizeof(float);
   return 256 + ((size_t)batch * hkv * sizeof(unsigned int) + 255) / 256 * 256 + partials;
 }
 
