@@ -177,6 +177,10 @@ __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloa
 constexpr int kAttnWarps = 8;
 constexpr int kAttnMaxG = 8;
 constexpr int kAttnBatch = 4;            // positions whose rows are loaded before any is used
+// "No position seen yet" as a running maximum.  A finite stand-in for minus infinity: a warp or a CTA
+// may see no position at all (pos + 1 < units), and exp(-inf - (-inf)) would be NaN in the merges,
+// while exp(kNoScore - kNoScore) = 1 weights a sum and a vector that are both zero.
+constexpr float kNoScore = -1.0e30f;
 
 // VEC (2 or 4) consecutive bf16 as one 4- or 8-byte access
 template <int VEC>
@@ -204,13 +208,13 @@ template <bool kGlobal>
 __device__ __forceinline__ void merge_partials(const float* m, const float* l, const float* a, int n, int m_stride,
                                                int a_stride, float& out_a, float& out_m, float& out_l) {
   auto ld = [](const float* p) { return kGlobal ? __ldcg(p) : *p; };
-  float big = -INFINITY;
+  float big = kNoScore;
 #pragma unroll 8
   for (int i = 0; i < n; ++i) big = fmaxf(big, ld(m + (size_t)i * m_stride));
   float sum = 0.f, acc = 0.f;
 #pragma unroll 8
   for (int i = 0; i < n; ++i) {
-    const float w = __expf(ld(m + (size_t)i * m_stride) - big);   // 0 for a partial that saw no position
+    const float w = __expf(ld(m + (size_t)i * m_stride) - big);   // 0 for a partial that saw no position while another did
     sum += w * ld(l + (size_t)i * m_stride);
     acc += w * ld(a + (size_t)i * a_stride);
   }
@@ -240,7 +244,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* k_
   float q[kAttnMaxG][VEC], acc[kAttnMaxG][VEC], m[kAttnMaxG], l[kAttnMaxG];
 #pragma unroll
   for (int g = 0; g < kAttnMaxG; ++g) {
-    m[g] = -INFINITY;
+    m[g] = kNoScore;
     l[g] = 0.f;
 #pragma unroll
     for (int j = 0; j < VEC; ++j) acc[g][j] = q[g][j] = 0.f;

@@ -108,3 +108,81 @@ def test_silu_mul_oracle_matches_the_layer_math():
     ref = (torch.nn.functional.silu(gate.float()) * up.float()).to(torch.bfloat16)
     diff = (out.float() - ref.float()).abs()
     assert bool((diff <= ref.float().abs() * 2.0 ** -7 + 1e-6).all())
+
+
+def _emulate_decode_attention(qkv, k_cache, v_cache, hq, hkv, pos, n_split, warps=8, no_score=-1.0e30):
+    """The decode-attention kernel's algorithm step by step in fp32 (units of strided positions with an
+    online softmax, merge of a CTA's warps, merge of the CTAs), with its finite stand-in for "no
+    position seen": what the kernel computes if its code follows its design."""
+    import math
+
+    B, s_max, _, D = k_cache.shape
+    G = hq // hkv
+    n_units = n_split * warps
+    scale = 1.0 / math.sqrt(D)
+    out = torch.zeros(B, hq * D)
+
+    def merge(parts):                                   # [(m, l, acc[D])] -> (m, l, acc)
+        big = max([no_score] + [m for m, _, _ in parts])
+        lsum, acc = 0.0, torch.zeros(D)
+        for m, l, a in parts:
+            w = math.exp(max(m - big, -745.0))          # exp underflows to 0 like __expf
+            lsum += w * l
+            acc = acc + w * a
+        return big, lsum, acc
+
+    for b in range(B):
+        row = qkv[b].float()
+        for kvh in range(hkv):
+            k_new = row[(hq + kvh) * D:(hq + kvh + 1) * D]
+            v_new = row[(hq + hkv + kvh) * D:(hq + hkv + kvh + 1) * D]
+            for g in range(G):
+                q = row[(kvh * G + g) * D:(kvh * G + g + 1) * D] * scale
+                cta_parts = []
+                for split in range(n_split):
+                    warp_parts = []
+                    for warp in range(warps):
+                        unit = split * warps + warp
+                        m, l, acc = no_score, 0.0, torch.zeros(D)
+                        for p in range(unit, pos + 1, n_units):
+                            k = k_new if p == pos else k_cache[b, p, kvh].float()
+                            v = v_new if p == pos else v_cache[b, p, kvh].float()
+                            s = float(q @ k)
+                            m_new = max(m, s)
+                            corr, w = math.exp(max(m - m_new, -745.0)), math.exp(s - m_new)
+                            l = l * corr + w
+                            acc = acc * corr + w * v
+                            m = m_new
+                        warp_parts.append((m, l, acc))
+                    cta_parts.append(merge(warp_parts))
+                _, l, acc = merge(cta_parts)
+                out[b, (kvh * G + g) * D:(kvh * G + g + 1) * D] = acc / l
+    return out
+
+
+def test_decode_attention_algorithm_and_oracle():
+    """The split / merge scheme of the decode-attention kernel (emulated in fp32) against the C++
+    oracle and against PyTorch's attention, including positions where most units see nothing."""
+    import torch.nn.functional as F
+
+    from symm_mem_recipes_b200._ext import C
+
+    g = torch.Generator().manual_seed(4)
+    B, hq, hkv, D, s_max = 2, 4, 2, 64, 300
+    for pos, n_split in ((0, 2), (1, 2), (15, 2), (16, 1), (150, 2), (299, 2)):
+        qkv = (torch.randn(B, (hq + 2 * hkv) * D, generator=g) * 0.7).to(torch.bfloat16)
+        kc = (torch.randn(B, s_max, hkv, D, generator=g) * 0.7).to(torch.bfloat16)
+        vc = (torch.randn(B, s_max, hkv, D, generator=g) * 0.7).to(torch.bfloat16)
+        emulated = _emulate_decode_attention(qkv, kc, vc, hq, hkv, pos, n_split)
+        kc2, vc2 = kc.clone(), vc.clone()
+        oracle = C.oracle_decode_attention_bf16(qkv, kc2, vc2, hq, hkv, pos)
+        assert torch.isfinite(emulated).all()
+        assert (emulated - oracle.float()).abs().max().item() < 1e-2, pos
+        # the oracle wrote the new key / value rows, and agrees with PyTorch on the updated caches
+        q, k, v = qkv.split([hq * D, hkv * D, hkv * D], dim=-1)
+        assert torch.equal(kc2[:, pos], k.view(B, hkv, D)) and torch.equal(vc2[:, pos], v.view(B, hkv, D))
+        assert torch.equal(kc2[:, :pos], kc[:, :pos]) and torch.equal(kc2[:, pos + 1:], kc[:, pos + 1:])
+        ref = F.scaled_dot_product_attention(q.view(B, 1, hq, D).transpose(1, 2).float(),
+                                             kc2[:, :pos + 1].transpose(1, 2).float(),
+                                             vc2[:, :pos + 1].transpose(1, 2).float(), enable_gqa=True)
+        assert (oracle.float() - ref.transpose(1, 2).reshape(B, hq * D)).abs().max().item() < 1e-2, pos
