@@ -108,7 +108,8 @@ def decode_attention_(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.T
     of one element on the device, so a captured CUDA graph serves every
     position.  Replaces, in a decode step, two cache writes and PyTorch's
     attention under a mask (about ten small kernels).  D is 64 or 128 and
-    hq / hkv at most 8."""
+    hq / hkv at most 8.  Calls of one shape share a scratch buffer: issue them
+    on one stream (or in one captured graph), not concurrently."""
     _check("qkv", qkv, 2)
     _check("k_cache", k_cache, 4)
     _check("v_cache", v_cache, 4)
