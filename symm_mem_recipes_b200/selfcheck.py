@@ -301,7 +301,13 @@ def build_checks(first_run: bool, world: int, rank: int, dev: torch.device) -> l
 
     if dev.type == "cuda":                          # CUDA graphs: nothing to capture on the CPU backend
         add("layer", "decode through one captured CUDA graph", decode_graph, True)
-    return [c for c in checks if first_run or not c[2]]
+    # What has run on hardware before goes first; the pending variants follow, the rank-local kernels
+    # before the ones that talk to peers (a fault in one of them would end the process and take the
+    # checks after it along).
+    order = {"glue": 0, "all_gather_matmul": 1, "gemv": 2, "barrier": 3, "all_reduce": 4,
+             "matmul_reduce_scatter": 5, "matmul_all_reduce": 6, "layer": 7}
+    chosen = [c for c in checks if first_run or not c[2]]
+    return sorted(chosen, key=lambda c: (c[2], order.get(c[0], 8) if c[2] else 0))
 
 
 def run_checks(checks: list, rank: int, dev: torch.device, only=()) -> tuple:
