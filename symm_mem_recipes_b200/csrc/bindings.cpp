@@ -474,6 +474,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     TORCH_CHECK(!fp8 || (cta_pair && mode != 1),
                 "float8_e4m3fn runs on the CTA-pair kernel: a_out must be symmetric memory (push) or absent");
     int dev = a.get_device();
+    TORCH_CHECK(b.get_device() == dev && c.get_device() == dev, "a, b and c must live on one GPU");
     c10::cuda::CUDAGuard guard(dev);
     cudaStream_t stream = current_stream(dev);
     AgMatmulArgs args{};
@@ -570,6 +571,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     TORCH_CHECK(x.size(1) == w_k && out.size(0) == x.size(0) && out.size(1) == w_n,
                 "need x[B, K], w[K, N] (or [N, K] with weights_nk), out[B, N]");
     int dev = x.get_device();
+    TORCH_CHECK(w.get_device() == dev && out.get_device() == dev && workspace->device() == dev,
+                "x, w, out and the workspace must live on one GPU");
     c10::cuda::CUDAGuard guard(dev);
     GemvArgs args{};
     args.x = x.data_ptr();
@@ -610,6 +613,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     TORCH_CHECK(ok2d(a) && ok2d(b) && ok2d(out), "a, b, out must be contiguous 2-D bf16 CUDA tensors");
     TORCH_CHECK(a.size(1) == b.size(1), "A[M, K] and B[N, K] disagree on K");
     int dev = a.get_device();
+    TORCH_CHECK(b.get_device() == dev && out.get_device() == dev && workspace->device() == dev,
+                "a, b, out and the workspace must live on one GPU");
     c10::cuda::CUDAGuard guard(dev);
     MatmulRsArgs args{};
     args.a = a.data_ptr();
@@ -654,6 +659,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     TORCH_CHECK((char*)out.data_ptr() == (char*)out_alloc->local_ptr() + out_offset,
                 "out does not sit at out_offset of its allocation");
     int dev = a.get_device();
+    TORCH_CHECK(b.get_device() == dev && out.get_device() == dev && workspace->device() == dev &&
+                out_alloc->device() == dev, "a, b, out and the workspace must live on one GPU");
     c10::cuda::CUDAGuard guard(dev);
     MatmulRsArgs args{};
     args.a = a.data_ptr();
