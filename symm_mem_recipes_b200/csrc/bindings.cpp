@@ -737,7 +737,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   });
   // `pos` (optional): int32 CUDA tensor of one element holding the position; read on the device
   m.def("decode_attention", [](torch::Tensor qkv, torch::Tensor k_cache, torch::Tensor v_cache, torch::Tensor out,
-                               torch::Tensor scratch, int hq, int hkv, int pos0, c10::optional<torch::Tensor> pos) {
+                               torch::Tensor scratch, int hq, int hkv, int pos0, c10::optional<torch::Tensor> pos,
+                               double rope_theta) {
     auto ok = [](const torch::Tensor& t) {
       return t.is_cuda() && t.is_contiguous() && t.scalar_type() == torch::kBFloat16;
     };
@@ -756,10 +757,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     c10::cuda::CUDAGuard guard(dev);
     rt_check(launch_decode_attention(qkv.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
                                      scratch.data_ptr(), (size_t)scratch.nbytes(), B, hq, hkv, D, s_max, pos0,
-                                     pos ? static_cast<const int*>(pos->data_ptr()) : nullptr, current_stream(dev)),
+                                     pos ? static_cast<const int*>(pos->data_ptr()) : nullptr, (float)rope_theta,
+                                     current_stream(dev)),
              "decode_attention");
   }, py::arg("qkv"), py::arg("k_cache"), py::arg("v_cache"), py::arg("out"), py::arg("scratch"), py::arg("hq"),
-     py::arg("hkv"), py::arg("pos0"), py::arg("pos") = py::none());
+     py::arg("hkv"), py::arg("pos0"), py::arg("pos") = py::none(), py::arg("rope_theta") = 0.0);
 
   // ---- oracles (CPU tensors) ----
   m.def("oracle_rms_norm_bf16", [](torch::Tensor x, c10::optional<torch::Tensor> residual, torch::Tensor w,

@@ -188,8 +188,9 @@ int launch_silu_mul(const void* gate_up, void* out, long long rows, int F, int n
 // `scratch`: decode_attention_scratch_bytes(...) bytes, zero-filled once; head_dim 64 or 128,
 // hq / hkv <= 8.
 size_t decode_attention_scratch_bytes(int batch, int hkv, int head_dim, int s_max, int* n_split_out);
+// `rope_theta` != 0: the new token's queries and key are taken unrotated and rotated in the kernel.
 int launch_decode_attention(const void* qkv, void* k_cache, void* v_cache, void* out, void* scratch,
                             size_t scratch_bytes, int batch, int hq, int hkv, int head_dim, int s_max, int pos0,
-                            const int* pos_dev, cudaStream_t stream);
+                            const int* pos_dev, float rope_theta, cudaStream_t stream);
 
 }  // namespace smr

@@ -196,6 +196,17 @@ __device__ __forceinline__ void load_bf16_vec(const __nv_bfloat16* p, float (&f)
   }
 }
 template <int VEC>
+__device__ __forceinline__ void store_bf16_vec(__nv_bfloat16* dst, const float (&f)[VEC]) {
+  if constexpr (VEC == 4) {
+    uint2 w;
+    w.x = pack_bf16x2(f[0], f[1]);
+    w.y = pack_bf16x2(f[2], f[3]);
+    *reinterpret_cast<uint2*>(dst) = w;
+  } else {
+    *reinterpret_cast<uint32_t*>(dst) = pack_bf16x2(f[0], f[1]);
+  }
+}
+template <int VEC>
 __device__ __forceinline__ void copy_bf16_vec(__nv_bfloat16* dst, const __nv_bfloat16* src) {
   if constexpr (VEC == 4) *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(src);
   else *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(src);
@@ -225,7 +236,7 @@ template <int VEC>
 __global__ void __launch_bounds__(kAttnWarps * 32)
 decode_attention_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* k_cache, __nv_bfloat16* v_cache,
                         __nv_bfloat16* __restrict__ out, float* scratch, unsigned int* counters, int hq, int hkv,
-                        int s_max, int pos0, const int* __restrict__ pos_dev, float scale) {
+                        int s_max, int pos0, const int* __restrict__ pos_dev, float scale, float log2_theta) {
   constexpr int D = 32 * VEC;
   constexpr int kRow = D + 2;                                  // D weighted-V sums, then max and sum
   __shared__ float sm[kAttnWarps][kAttnMaxG][kRow];
@@ -241,6 +252,32 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* k_
   const __nv_bfloat16* k_new = row + (size_t)hq * D + (size_t)kvh * D + lane * VEC;
   const __nv_bfloat16* v_new = row + (size_t)(hq + hkv) * D + (size_t)kvh * D + lane * VEC;
 
+  // Rotary embedding of the new token's queries and key inside this kernel (log2_theta != 0): the
+  // pair (i, i + D/2) sits in lanes t and t ^ 16 at the same j; results are rounded to bf16 as the
+  // stand-alone RoPE kernel rounds them, so both routes give the same bits.
+  float cs[VEC], sn[VEC];
+  const bool rotate = log2_theta != 0.f;
+  if (rotate) {
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+      const int i = (lane * VEC + j) & (D / 2 - 1);
+      float ang = (float)pos * exp2f(-(2.0f * (float)i / (float)D) * log2_theta);
+      ang -= 6.283185307179586f * rintf(ang * 0.15915494309189535f);
+      __sincosf(ang, &sn[j], &cs[j]);
+    }
+  }
+  auto rope = [&](float (&x)[VEC]) {
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+      const float other = __shfl_xor_sync(0xffffffffu, x[j], 16);
+      x[j] = round_bf16(lane < 16 ? x[j] * cs[j] - other * sn[j] : x[j] * cs[j] + other * sn[j]);
+    }
+  };
+  float k_tok[VEC], v_tok[VEC];                          // the new token's key (rotated) and value
+  load_bf16_vec<VEC>(k_new, k_tok);
+  load_bf16_vec<VEC>(v_new, v_tok);
+  if (rotate) rope(k_tok);
+
   float q[kAttnMaxG][VEC], acc[kAttnMaxG][VEC], m[kAttnMaxG], l[kAttnMaxG];
 #pragma unroll
   for (int g = 0; g < kAttnMaxG; ++g) {
@@ -250,6 +287,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* k_
     for (int j = 0; j < VEC; ++j) acc[g][j] = q[g][j] = 0.f;
     if (g < G) {
       load_bf16_vec<VEC>(row + (size_t)(kvh * G + g) * D + lane * VEC, q[g]);
+      if (rotate) rope(q[g]);
 #pragma unroll
       for (int j = 0; j < VEC; ++j) q[g][j] *= scale;
     }
@@ -259,10 +297,16 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* k_
 #pragma unroll
     for (int i = 0; i < kAttnBatch; ++i) {                      // all loads of the batch before any use
       const int p = p0 + i * n_units;
-      if (p <= pos) {
+      if (p < pos) {
         const size_t off = (((size_t)b * s_max + p) * hkv + kvh) * D + lane * VEC;
-        load_bf16_vec<VEC>(p == pos ? k_new : k_cache + off, k[i]);
-        load_bf16_vec<VEC>(p == pos ? v_new : v_cache + off, v[i]);
+        load_bf16_vec<VEC>(k_cache + off, k[i]);
+        load_bf16_vec<VEC>(v_cache + off, v[i]);
+      } else if (p == pos) {
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) {
+          k[i][j] = k_tok[j];
+          v[i][j] = v_tok[j];
+        }
       }
     }
 #pragma unroll
@@ -289,7 +333,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* k_
   }
   if (split == 0 && warp == 0) {                      // the new token's key and value enter the caches
     const size_t off = (((size_t)b * s_max + pos) * hkv + kvh) * D + lane * VEC;
-    copy_bf16_vec<VEC>(k_cache + off, k_new);
+    store_bf16_vec<VEC>(k_cache + off, k_tok);
     copy_bf16_vec<VEC>(v_cache + off, v_new);
   }
   // ---- the CTA's warps merge through shared memory into one partial per CTA ----
@@ -393,7 +437,9 @@ size_t decode_attention_scratch_bytes(int batch, int hkv, int head_dim, int s_ma
 
 int launch_decode_attention(const void* qkv, void* k_cache, void* v_cache, void* out, void* scratch,
                             size_t scratch_bytes, int batch, int hq, int hkv, int head_dim, int s_max, int pos0,
-                            const int* pos_dev, cudaStream_t stream) {
+                            const int* pos_dev, float rope_theta, cudaStream_t stream) {
+  if (rope_theta != 0.f && rope_theta <= 1.0f) return cudaErrorInvalidValue;
+  const float log2_theta = rope_theta != 0.f ? log2f(rope_theta) : 0.f;
   if (batch < 1 || hq < 1 || hkv < 1 || hq % hkv != 0 || hq / hkv > kAttnMaxG || (head_dim != 64 && head_dim != 128) ||
       s_max < 1 || (pos_dev == nullptr && (pos0 < 0 || pos0 >= s_max)))
     return cudaErrorInvalidValue;
@@ -414,10 +460,10 @@ int launch_decode_attention(const void* qkv, void* k_cache, void* v_cache, void*
   auto o = static_cast<__nv_bfloat16*>(out);
   if (head_dim == 128)
     decode_attention_kernel<4><<<grid, kAttnWarps * 32, 0, stream>>>(q, kc, vc, o, partials, counters, hq, hkv, s_max,
-                                                                      pos0, pos_dev, scale);
+                                                                      pos0, pos_dev, scale, log2_theta);
   else
     decode_attention_kernel<2><<<grid, kAttnWarps * 32, 0, stream>>>(q, kc, vc, o, partials, counters, hq, hkv, s_max,
-                                                                      pos0, pos_dev, scale);
+                                                                      pos0, pos_dev, scale, log2_theta);
   return (int)cudaGetLastError();
 }
 

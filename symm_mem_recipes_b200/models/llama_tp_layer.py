@@ -346,10 +346,9 @@ class LlamaTPDecoderLayer:
         glue = fused and self.fused_glue
         qkv = self._decode_norm(x, self.norm1, glue) @ self.w_qkv.t()
         if glue:
-            # rotate Q and K in place, then ONE kernel writes the caches and attends over positions 0..pos
-            ops.rope_(qkv, hq + hkv, D, 1, cfg.rope_theta, pos0=pos)
-            o_proj = self._row_parallel_decode(ops.decode_attention_(qkv, k_cache, v_cache, hq, pos), "o", fused)
-            return self._decode_mlp(x, o_proj, fused, glue)
+            # ONE kernel rotates the new Q and K, writes the caches and attends over positions 0..pos
+            attn = ops.decode_attention_(qkv, k_cache, v_cache, hq, pos, rope_theta=cfg.rope_theta)
+            return self._decode_mlp(x, self._row_parallel_decode(attn, "o", fused), fused, glue)
         q, k, v = qkv.split([hq * D, hkv * D, hkv * D], dim=-1)
         q, k = q.view(B, 1, hq, D), k.view(B, 1, hkv, D)
         if not glue:
@@ -375,9 +374,8 @@ class LlamaTPDecoderLayer:
         glue = fused and self.fused_glue
         qkv = self._decode_norm(x, self.norm1, glue) @ self.w_qkv.t()
         if glue:
-            ops.rope_(qkv, hq + hkv, D, 1, cfg.rope_theta, pos0=pos)
-            o_proj = self._row_parallel_decode(ops.decode_attention_(qkv, k_cache, v_cache, hq, pos), "o", fused)
-            return self._decode_mlp(x, o_proj, fused, glue)
+            attn = ops.decode_attention_(qkv, k_cache, v_cache, hq, pos, rope_theta=cfg.rope_theta)
+            return self._decode_mlp(x, self._row_parallel_decode(attn, "o", fused), fused, glue)
         q, k, v = qkv.split([hq * D, hkv * D, hkv * D], dim=-1)
         q, k = q.view(B, 1, hq, D), k.view(B, 1, hkv, D)
         if not glue:

@@ -97,10 +97,14 @@ _attn_scratch: dict[tuple, torch.Tensor] = {}
 
 @traced("smr.decode_attention_")
 def decode_attention_(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, n_q_heads: int,
-                      pos: Union[int, torch.Tensor], out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      pos: Union[int, torch.Tensor], out: Optional[torch.Tensor] = None,
+                      rope_theta: float = 0.0) -> torch.Tensor:
     """Attention of one decode step in one kernel.  `qkv` [B, (hq + 2 hkv) * D]
-    holds the new token's queries and keys (already rotated, see `rope_`) and its
-    values; the caches are [B, S_max, hkv, D].  Writes the new key and value into
+    holds the new token's queries and keys and its values; with `rope_theta`
+    (say 500000.0) queries and key are given unrotated and the kernel applies
+    the rotary embedding for position `pos` itself (same bits as `rope_` first),
+    otherwise they must be rotated already.  `qkv` is not modified.  The caches
+    are [B, S_max, hkv, D].  Writes the new (rotated) key and the value into
     the caches at `pos` (hence the trailing underscore) and returns
     `out[B, hq * D] = softmax(q . K[0..pos] / sqrt(D)) V[0..pos]` per query head
     (grouped-query: head h reads KV head h // (hq / hkv)).  The cached sequence
@@ -118,6 +122,8 @@ def decode_attention_(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.T
         raise SymmMemError("need caches [B, S_max, hkv, D] and qkv [B, (hq + 2 hkv) * D]")
     if n_q_heads % hkv or n_q_heads // hkv > 8 or D not in (64, 128):
         raise SymmMemError("need hq a multiple of hkv with hq / hkv <= 8, and head_dim 64 or 128")
+    if rope_theta != 0.0 and rope_theta <= 1.0:
+        raise SymmMemError("rope_theta must be 0 (no rotation) or larger than 1")
     if out is None:
         out = torch.empty(B, n_q_heads * D, dtype=torch.bfloat16, device=qkv.device)
     key = (qkv.device.type, qkv.device.index, B, hkv, D, s_max)
@@ -128,9 +134,10 @@ def decode_attention_(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.T
     if isinstance(pos, torch.Tensor):
         if pos.dtype != torch.int32 or pos.numel() != 1 or pos.device != qkv.device:
             raise SymmMemError("a position tensor must be int32, of one element, on qkv's device")
-        C.decode_attention(qkv, k_cache, v_cache, out, scratch, int(n_q_heads), int(hkv), 0, pos)
+        C.decode_attention(qkv, k_cache, v_cache, out, scratch, int(n_q_heads), int(hkv), 0, pos, float(rope_theta))
     else:
         if not 0 <= int(pos) < s_max:
             raise SymmMemError(f"position {pos} outside the cache of {s_max} entries")
-        C.decode_attention(qkv, k_cache, v_cache, out, scratch, int(n_q_heads), int(hkv), int(pos))
+        C.decode_attention(qkv, k_cache, v_cache, out, scratch, int(n_q_heads), int(hkv), int(pos), None,
+                           float(rope_theta))
     return out

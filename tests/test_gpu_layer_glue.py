@@ -156,14 +156,23 @@ def test_decode_attention(B, hq, hkv, D, s_max, positions):
     pos_dev = torch.zeros(1, dtype=torch.int32, device="cuda")
     for i, pos in enumerate(positions):
         qkv = (torch.randn(B, (hq + 2 * hkv) * D, generator=g) * 0.7).to(torch.bfloat16)
-        want = C.oracle_decode_attention_bf16(qkv, k_cache, v_cache, hq, hkv, pos)       # updates the CPU caches
+        # odd steps: the kernel rotates the new queries and key itself (oracle: RoPE first, then attention)
+        theta = 500000.0 if i % 2 else 0.0
+        rotated = C.oracle_rope_bf16(qkv, hq + hkv, D, 1, pos, theta) if theta else qkv
+        want = C.oracle_decode_attention_bf16(rotated, k_cache, v_cache, hq, hkv, pos)   # updates the CPU caches
+        qkv_dev = qkv.cuda()
         if i % 2 == 0:
-            got = ops.decode_attention_(qkv.cuda(), k_dev, v_dev, hq, pos)
+            got = ops.decode_attention_(qkv_dev, k_dev, v_dev, hq, pos, rope_theta=theta)
         else:
             pos_dev.fill_(pos)
-            got = ops.decode_attention_(qkv.cuda(), k_dev, v_dev, hq, pos_dev)
+            got = ops.decode_attention_(qkv_dev, k_dev, v_dev, hq, pos_dev, rope_theta=theta)
+        assert torch.equal(qkv_dev.cpu(), qkv)                                           # the input row is left alone
         err = (got.float().cpu() - want.float()).abs()
         # fp32 sums in another order and fast exp: a bf16 ulp of the output, which is an average of values ~0.7
         assert bool((err <= want.float().abs() * 2.0 ** -6 + 4e-3).all()), (pos, float(err.max()))
-        assert torch.equal(k_dev.cpu(), k_cache) and torch.equal(v_dev.cpu(), v_cache), pos     # caches written
+        # caches written: bit-exact for the value, within the fast sine / cosine (a bf16 ulp) for a rotated key
+        assert torch.equal(v_dev.cpu(), v_cache), pos
+        k_err = (k_dev.cpu().float() - k_cache.float()).abs()
+        assert bool((k_err <= k_cache.float().abs() * 2.0 ** -7 + (4e-3 if theta else 0.0)).all()), pos
+        k_dev.copy_(k_cache)                                                             # keep both histories equal
     torch.cuda.synchronize()

@@ -42,8 +42,10 @@ class _FakeC:
         qkv.copy_(REAL_C.oracle_rope_bf16(qkv, n_heads, head_dim, seq, pos0, theta))
 
     @staticmethod
-    def decode_attention(qkv, k_cache, v_cache, out, scratch, hq, hkv, pos0, pos=None):
+    def decode_attention(qkv, k_cache, v_cache, out, scratch, hq, hkv, pos0, pos=None, rope_theta=0.0):
         where = pos0 if pos is None else int(pos)
+        if rope_theta:
+            qkv = REAL_C.oracle_rope_bf16(qkv, hq + hkv, k_cache.shape[3], 1, where, rope_theta)
         out.copy_(REAL_C.oracle_decode_attention_bf16(qkv, k_cache, v_cache, hq, hkv, where))
 
     @staticmethod
