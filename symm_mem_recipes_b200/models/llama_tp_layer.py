@@ -326,8 +326,10 @@ class LlamaTPDecoderLayer:
     def _decode_norm(self, t: torch.Tensor, w: torch.Tensor, glue: bool) -> torch.Tensor:
         return ops.rms_norm(t, w, self.cfg.eps) if glue else _rms_norm(t, w, self.cfg.eps)
 
-    def _decode_mlp(self, x: torch.Tensor, o_proj: torch.Tensor, fused: bool, glue: bool) -> torch.Tensor:
-        """Second half of a decode step: residual add of the attention output, norm, MLP, residual add."""
+    def _decode_mlp(self, x: torch.Tensor, o_proj: torch.Tensor, fused: bool, glue: bool,
+                    defer_residual: bool = False):
+        """Second half of a decode step: residual add of the attention output, norm, MLP, residual add.
+        `defer_residual`: return `(down, x1)` and leave `x1 + down` to the next layer's first kernel."""
         if glue:
             h2, x1 = ops.rms_norm(o_proj, self.norm2, self.cfg.eps, residual=x)    # x1 = x + o_proj, one kernel
         else:
@@ -335,7 +337,8 @@ class LlamaTPDecoderLayer:
             h2 = _rms_norm(x1, self.norm2, self.cfg.eps)
         gu = h2 @ self.w_gate_up.t()
         act = ops.silu_mul(gu) if glue else LlamaTPDecoderLayer._mlp_act_torch(gu, self.ffn_local)
-        return x1 + self._row_parallel_decode(act, "down", fused)
+        down = self._row_parallel_decode(act, "down", fused)
+        return (down, x1) if defer_residual else x1 + down
 
     def decode(self, x: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, pos: int,
                fused: bool = True) -> torch.Tensor:
@@ -361,21 +364,37 @@ class LlamaTPDecoderLayer:
         o_proj = self._row_parallel_decode(o.transpose(1, 2).reshape(B, hq * D).contiguous(), "o", fused)
         return self._decode_mlp(x, o_proj, fused, glue)
 
+    def chains_residual(self, fused: bool = True) -> bool:
+        """Whether `decode_static` can take and hand on an unfinished residual add (glue kernels only)."""
+        return bool(fused and self.fused_glue)
+
     def decode_static(self, x: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, pos: torch.Tensor,
-                      fused: bool = True) -> torch.Tensor:
+                      fused: bool = True, pending_residual: Optional[torch.Tensor] = None,
+                      defer_residual: bool = False):
         """`decode` with every shape and every launch independent of the
         position, so that ONE captured CUDA graph serves all positions: `pos`
         is an int32 tensor of one element on the device, the caches are written
         with `index_copy_`, and attention runs over the whole cache under a
-        mask that hides the entries beyond `pos`.  Same result as `decode`."""
+        mask that hides the entries beyond `pos`.  Same result as `decode`.
+
+        Between stacked layers the closing residual add of one layer can ride
+        in the first RMSNorm kernel of the next (`chains_residual`): with
+        `defer_residual` the layer returns `(down, x1)` instead of `x1 + down`,
+        and the next layer takes them as `x=down, pending_residual=x1`."""
         cfg = self.cfg
         B, D, hq, hkv = x.shape[0], cfg.head_dim, self.hq, self.hkv
         s_max = k_cache.shape[1]
         glue = fused and self.fused_glue
-        qkv = self._decode_norm(x, self.norm1, glue) @ self.w_qkv.t()
+        if (pending_residual is not None or defer_residual) and not glue:
+            raise ValueError("chaining the residual add needs the glue kernels (see chains_residual)")
+        if pending_residual is not None:
+            h1, x = ops.rms_norm(x, self.norm1, cfg.eps, residual=pending_residual)    # x = previous x1 + down
+        else:
+            h1 = self._decode_norm(x, self.norm1, glue)
+        qkv = h1 @ self.w_qkv.t()
         if glue:
             attn = ops.decode_attention_(qkv, k_cache, v_cache, hq, pos, rope_theta=cfg.rope_theta)
-            return self._decode_mlp(x, self._row_parallel_decode(attn, "o", fused), fused, glue)
+            return self._decode_mlp(x, self._row_parallel_decode(attn, "o", fused), fused, glue, defer_residual)
         q, k, v = qkv.split([hq * D, hkv * D, hkv * D], dim=-1)
         q, k = q.view(B, 1, hq, D), k.view(B, 1, hkv, D)
         if not glue:
@@ -389,6 +408,18 @@ class LlamaTPDecoderLayer:
                                            attn_mask=visible, enable_gqa=True)
         o_proj = self._row_parallel_decode(o.transpose(1, 2).reshape(B, hq * D).contiguous(), "o", fused)
         return self._decode_mlp(x, o_proj, fused, glue)
+
+
+def decode_static_through(layers, caches, x: torch.Tensor, pos: torch.Tensor, fused: bool = True) -> torch.Tensor:
+    """One decode step through stacked layers; where two neighbours both run the glue kernels the
+    residual add that closes the first rides in the RMSNorm kernel that opens the second."""
+    layers = list(layers)
+    h, pending = x, None
+    for i, (lyr, (kc, vc)) in enumerate(zip(layers, caches)):
+        defer = (i + 1 < len(layers) and lyr.chains_residual(fused) and layers[i + 1].chains_residual(fused))
+        out = lyr.decode_static(h, kc, vc, pos, fused=fused, pending_residual=pending, defer_residual=defer)
+        h, pending = out if defer else (out, None)
+    return h
 
 
 def new_kv_caches(layers, batch: int, max_seq: int) -> list:
@@ -442,10 +473,7 @@ class DecodeGraph:
         self.reset()
 
     def _run(self) -> torch.Tensor:
-        h = self.x
-        for lyr, (kc, vc) in zip(self.layers, self.caches):
-            h = lyr.decode_static(h, kc, vc, self.pos, fused=self.fused)
-        return h
+        return decode_static_through(self.layers, self.caches, self.x, self.pos, fused=self.fused)
 
     def reset(self) -> None:
         """Start a new sequence: the KV caches are zeroed (the graph is kept)."""
@@ -513,10 +541,7 @@ class LlamaTPStack:
         if not 0 <= pos < self.max_seq:
             raise ValueError(f"position {pos} outside the cache of {self.max_seq} entries")
         self._pos.fill_(pos)
-        h = x
-        for lyr, (kc, vc) in zip(self.layers, self.caches):
-            h = lyr.decode_static(h, kc, vc, self._pos)
-        return h
+        return decode_static_through(self.layers, self.caches, x, self._pos)
 
 
 def full_precision_reference(layers_weights: list, cfg: LlamaTPConfig, x: torch.Tensor, batch: int,

@@ -50,10 +50,9 @@ def _prepare(rank, world_size):
                  torch.zeros(batch, max_seq, lyr.hkv, cfg.head_dim, dtype=torch.bfloat16)) for lyr in self.layers]
 
         def step(self, x, pos):
+            from symm_mem_recipes_b200.models.llama_tp_layer import decode_static_through
             self.pos.fill_(pos)
-            for lyr, (kc, vc) in zip(self.layers, self.caches):
-                x = lyr.decode_static(x, kc, vc, self.pos, fused=self.fused)
-            return x
+            return decode_static_through(self.layers, self.caches, x, self.pos, fused=self.fused)
 
     llama_tp_layer.DecodeGraph = EagerDecodeGraph
 

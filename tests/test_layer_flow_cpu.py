@@ -196,6 +196,32 @@ def test_stack_prefill_then_decode(host_kernels):
     assert float(stack.caches[0][0].abs().sum()) == 0.0
 
 
+def test_residual_chaining_between_layers_changes_no_bit(host_kernels):
+    """x1 + down of one layer computed by the next layer's first RMSNorm kernel: same bits as the
+    separate add, and layers without the glue kernels are left out of the chain."""
+    from symm_mem_recipes_b200.models.llama_tp_layer import (LlamaTPConfig, LlamaTPDecoderLayer,
+                                                              decode_static_through, new_kv_caches)
+
+    cfg = LlamaTPConfig.tiny(1)
+    dev = torch.device("cpu")
+    glue = [True, True, False, True]
+    layers = [LlamaTPDecoderLayer(cfg, dev, seed=7 + i, fused_glue=g) for i, g in enumerate(glue)]
+    assert [lyr.chains_residual() for lyr in layers] == glue
+    a, b = new_kv_caches(layers, 2, 8), new_kv_caches(layers, 2, 8)
+    pos = torch.zeros(1, dtype=torch.int32)
+    g = torch.Generator().manual_seed(1)
+    for step in range(3):
+        x = (torch.randn(2, cfg.hidden, generator=g) * 0.5).to(torch.bfloat16)
+        pos.fill_(step)
+        chained = decode_static_through(layers, a, x, pos)
+        plain = x
+        for lyr, (kc, vc) in zip(layers, b):
+            plain = lyr.decode_static(plain, kc, vc, pos)
+        assert torch.equal(chained, plain), step
+    with pytest.raises(ValueError, match="glue kernels"):
+        layers[2].decode_static(x, *b[2], pos, defer_residual=True)
+
+
 def test_phase_marks_are_off_by_default(host_kernels):
     _, layer, x, batch, seq, _ = _layer_and_reference(False, False)
     layer.forward(x, batch, seq)
