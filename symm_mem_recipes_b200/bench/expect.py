@@ -117,7 +117,8 @@ def main(argv=None) -> int:
         with open(args.peaks) as f:
             peaks.update({k: v for k, v in json.load(f).items() if k in DEFAULT_PEAKS})
     if args.op.startswith("layer_"):
-        print(json.dumps(expect_layer(args.ws, peaks, batch=args.batch, seq=args.seq, decode=args.op == "layer_decode")))
+        print(json.dumps(expect_layer(args.ws, peaks, batch=args.batch, seq=args.seq,
+                                      decode=args.op == "layer_decode")))
         return 0
     print(json.dumps(expect(args.op, args.ws, peaks, args.M, args.N, args.K, args.batch, args.nbytes,
                             not args.no_nvls)))

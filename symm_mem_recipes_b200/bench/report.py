@@ -208,7 +208,8 @@ def layer_tables(recs: list[dict]) -> Optional[str]:
     graphs = {(r["world_size"], r["layers"], r["batch"]): r for r in recs if r.get("op") == "llama70b_decode_graph"}
     if graphs:
         rows = [[str(ws), str(layers), str(batch), str(r["cache_entries"]), _fmt(r["graph_us_per_step"]),
-                 _fmt(r["eager_us_per_step"]), f"{r['speedup']:.2f}x"] for (ws, layers, batch), r in sorted(graphs.items())]
+                 _fmt(r["eager_us_per_step"]), f"{r['speedup']:.2f}x"]
+                for (ws, layers, batch), r in sorted(graphs.items())]
         parts.append("### decode steps replayed from one CUDA graph\n\n" + _table(
             ["WS", "layers", "batch", "KV cache entries", "graph µs / step", "eager µs / step", "speed-up"], rows))
     return "\n\n".join(parts) if parts else None

@@ -100,7 +100,8 @@ def build_checks(first_run: bool, world: int, rank: int, dev: torch.device) -> l
     if multi:
         add("all_reduce", "multimem", ar("multimem"))
         add("all_reduce", "multimem, NVLS barriers", ar("multimem", AllReduceConfig(multimem_nvls_barrier=1)), True)
-        add("all_reduce", "multimem, 16 reductions in flight", ar("multimem", AllReduceConfig(multimem_unroll=16)), True)
+        add("all_reduce", "multimem, 16 reductions in flight", ar("multimem", AllReduceConfig(multimem_unroll=16)),
+            True)
 
     def barriers(kind):
         def fn():
@@ -363,7 +364,8 @@ def run_checks(checks: list, rank: int, dev: torch.device, only=()) -> tuple:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("--first-run", action="store_true", help="include the variants whose first run on hardware is pending")
+    ap.add_argument("--first-run", action="store_true",
+                    help="include the variants whose first run on hardware is pending")
     ap.add_argument("--only", default="", help="comma-separated groups (all_reduce, barrier, all_gather_matmul, "
                                                "matmul_reduce_scatter, matmul_all_reduce, gemv, glue, layer)")
     ap.add_argument("--list", action="store_true", help="print the checks and exit (no GPU needed)")
@@ -389,7 +391,8 @@ def main(argv=None) -> int:
     failed = [r for r in results if not r["ok"]]
     if rank == 0:
         print(json.dumps({"op": "selfcheck", "world_size": world, "checks": len(results), "failed": len(failed),
-                          "stopped_early": stopped, "recoveries": recoveries, "failures": [f"{r['group']}: {r['check']}" for r in failed]}))
+                          "stopped_early": stopped, "recoveries": recoveries,
+                          "failures": [f"{r['group']}: {r['check']}" for r in failed]}))
     symm_mem.shutdown()
     if world > 1:
         dist.destroy_process_group()

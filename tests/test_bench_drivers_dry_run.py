@@ -199,7 +199,8 @@ def test_all_reduce_driver(tmp_path):
     recs = _records(out)
     checks = [r for r in recs if r["op"] == "all_reduce_check"]
     assert checks[0]["output_equals_world_size"] is True
-    assert {r["impl"] for r in checks[1:]} == {"one_shot", "two_shot", "low_latency"} and all(r["ok"] for r in checks[1:])
+    assert {r["impl"] for r in checks[1:]} == {"one_shot", "two_shot", "low_latency"}
+    assert all(r["ok"] for r in checks[1:])
     timed = [r for r in recs if r["op"] == "all_reduce"]
     assert {r["bytes"] for r in timed} == {4096, 8192, 16384, 32768, 65536}
     assert {"nccl", "low_latency", "one_shot", "two_shot"} <= {r["impl"] for r in timed}

@@ -100,7 +100,8 @@ def _gemv_nk_worker(rank, world_size, B, K, N, algo):
     for _ in range(3):
         got = smr.gemv_all_reduce(x, w_nk, algo=algo, weights_nk=True)
     symm_mem.check_status(dev)
-    assert torch.allclose(got.float(), want.float(), rtol=2.0 ** -6, atol=2e-2), (got.float() - want.float()).abs().max()
+    worst = (got.float() - want.float()).abs().max()
+    assert torch.allclose(got.float(), want.float(), rtol=2.0 ** -6, atol=2e-2), worst
     torch.cuda.synchronize()
 
 

@@ -146,7 +146,8 @@ def _decode_graph_worker(rank, world_size, fused_glue):
         if err > 5e-2:
             failures.append(f"position {pos}: graph replay differs from the eager step by {err}")
     for (kc, vc), (kg, vg) in zip(eager_caches, graph.caches):
-        if not (torch.allclose(kc.float(), kg.float(), atol=2e-2) and torch.allclose(vc.float(), vg.float(), atol=2e-2)):
+        same_k = torch.allclose(kc.float(), kg.float(), atol=2e-2)
+        if not (same_k and torch.allclose(vc.float(), vg.float(), atol=2e-2)):
             failures.append("KV caches of the graph differ from the eager ones")
     torch.cuda.synchronize()
     assert not failures, failures

@@ -117,7 +117,8 @@ WORKERS = [
 ]
 
 
-@pytest.mark.parametrize("module,worker,worlds,args", WORKERS, ids=[f"{m}.{w}{i}" for i, (m, w, _, _) in enumerate(WORKERS)])
+@pytest.mark.parametrize("module,worker,worlds,args", WORKERS,
+                         ids=[f"{m}.{w}{i}" for i, (m, w, _, _) in enumerate(WORKERS)])
 def test_gpu_test_worker_runs_on_the_cpu(module, worker, worlds, args):
     mod = importlib.import_module(module)
     assert hasattr(mod, worker), f"{module} has no {worker}"

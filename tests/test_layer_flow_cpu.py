@@ -127,8 +127,8 @@ def test_static_decode_matches_decode(host_kernels, fused_glue):
     token by token, with a cache longer than the sequence."""
     cfg, layer, x, batch, seq, _ = _layer_and_reference(fused_glue, False)
     xs = x.view(batch, seq, cfg.hidden)
-    caches = [torch.zeros(batch, s_max, layer.hkv, cfg.head_dim, dtype=torch.bfloat16) for s_max in (seq, seq,
-                                                                                                       seq + 5, seq + 5)]
+    caches = [torch.zeros(batch, s_max, layer.hkv, cfg.head_dim, dtype=torch.bfloat16)
+              for s_max in (seq, seq, seq + 5, seq + 5)]
     (k_a, v_a, k_b, v_b) = caches
     k_b.fill_(7.0)                                     # stale entries beyond the position must stay hidden
     v_b.fill_(-3.0)
