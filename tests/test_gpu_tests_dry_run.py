@@ -135,6 +135,7 @@ FUNCTIONS = [
     ("test_gpu_matmul", "test_matmul_l2_hints_change_nothing_but_the_cache_policy",
      {"level": 3, "block_n": 256, "shape": (256, 512, 128)}),
     ("test_gpu_matmul", "test_matmul_small", {"block_n": 224, "shape": (200, 328, 96), "cta_pair": True}),
+    ("__graft_entry__", "smoke", {}),                  # the smoke check that runs on a GPU before the benchmark
 ]
 
 
