@@ -136,9 +136,17 @@ FUNCTIONS = [
      {"level": 3, "block_n": 256, "shape": (256, 512, 128)}),
     ("test_gpu_matmul", "test_matmul_small", {"block_n": 224, "shape": (200, 328, 96), "cta_pair": True}),
     ("__graft_entry__", "smoke", {}),                  # the smoke check that runs on a GPU before the benchmark
+    # the single-GPU tests that run at every GPU test pass
+    ("test_gpu_symm_mem", "test_world_of_one_all_paths", {}),
+    ("test_gpu_gemv", "test_gemv_world_of_one", {"B": 3, "K": 1000, "N": 328, "algo": "tc"}),
+    ("test_gpu_gemv", "test_gemv_world_of_one", {"B": 8, "K": 256, "N": 64, "algo": "simt"}),
+    ("test_gpu_matmul_rs", "test_matmul_reduce_scatter_world_of_one", {}),
+    ("test_gpu_llama_layer", "test_layer_world_of_one", {}),
+    ("test_gpu_matmul", "test_matmul_split_k_tail", {"shape": (768, 768, 1024), "num_sms": 8}),
 ]
 
 
-@pytest.mark.parametrize("module,name,kwargs", FUNCTIONS, ids=[f"{m}.{n}" for m, n, _ in FUNCTIONS])
+@pytest.mark.parametrize("module,name,kwargs", FUNCTIONS,
+                         ids=[f"{m}.{n}{i}" for i, (m, n, _) in enumerate(FUNCTIONS)])
 def test_gpu_test_function_runs_on_the_cpu(module, name, kwargs):
     spawn_ranks(_dry, 1, "gloo", (module, name, kwargs, True), timeout_s=240.0)
