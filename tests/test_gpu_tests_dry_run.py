@@ -114,6 +114,10 @@ WORKERS = [
     ("test_gpu_matmul", "_agmm_worker", (2,), (128, 256, 256, 1, "push_copy")),
     ("test_gpu_matmul", "_agmm_worker", (2,), (128, 256, 256, 2, "pull")),
     ("test_gpu_matmul", "_agmm_worker", (2,), (128, 256, 256, 0, "internal", True)),
+    # the default forms of the multi-GPU tests
+    ("test_gpu_matmul", "_agmm_worker", (2,), (128, 256, 256, 1, "push")),
+    ("test_gpu_gemv", "_gemv_worker", (2,), (4, 256, 512, "tc")),
+    ("test_gpu_matmul_rs", "_rs_worker", (2,), (256, 256, 128)),
 ]
 
 
