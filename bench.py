@@ -19,6 +19,9 @@ synchronize on both sides of the timed region; maximum over ranks.
 the host-to-device copy of the step's A shard from pinned memory and a
 device-to-host read of a checksum of C.  `same_box_baseline` is the library
 composition (NCCL all-gather + cuBLAS) timed the same way in the same run.
+`--e2e-pipelined` adds `e2e_pipelined`: the same end-to-end step fed the way a
+serving loop feeds it, the next step's host-to-device copy running on a copy
+stream under the current step's kernel (two shard buffers).
 """
 from __future__ import annotations
 
