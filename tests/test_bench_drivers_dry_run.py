@@ -123,6 +123,15 @@ def _gemv_worker(rank, world_size, out_path):
          rank, out_path)
 
 
+def _barrier_worker(rank, world_size, out_path):
+    _prepare(rank, world_size)
+    import symm_mem_recipes_b200 as smr
+    from symm_mem_recipes_b200.bench import barrier
+
+    smr.barrier_test = lambda hdl, num_blocks=32, **k: hdl.barrier()      # the kernel form exists on the GPU only
+    _run(barrier.main, ["--blocks", "1,32", "--kinds", "cas,epoch,nvls"], rank, out_path)
+
+
 def _records(path):
     return [json.loads(ln) for ln in pathlib.Path(path).read_text().splitlines() if ln.startswith("{")]
 
@@ -299,3 +308,12 @@ def test_single_gpu_driver(monkeypatch, capsys, argv):
     assert rec["op"] == (argv[1] if argv[0] == "--op" else "matmul") and "clocks" in rec
     if "--l2-hints" in argv:
         assert {"smr_us", "smr_l2_hints_1_us", "smr_l2_hints_2_us", "smr_l2_hints_3_us"} <= set(rec)
+
+
+def test_barrier_driver(tmp_path):
+    out = tmp_path / "barrier.txt"
+    spawn_ranks(_barrier_worker, 2, "gloo", (str(out),), timeout_s=120.0)
+    recs = _records(out)
+    assert [r["op"] for r in recs] == ["blockwise_barrier", "blockwise_barrier", "epoch_barrier_x2", "epoch_barrier_x2",
+                                       "channel_barrier", "barrier_test"]      # no multicast on the CPU: nvls skipped
+    assert recs[-1]["ok"] is True
