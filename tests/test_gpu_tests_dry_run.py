@@ -92,7 +92,8 @@ def _dry(rank, world_size, module, fn_name, args, by_name):
             setattr(mod, dep, getattr(testing, dep))
     fn = getattr(mod, fn_name)
     if by_name:                                        # a test function: keyword arguments, no rank
-        fn(**args)
+        result = fn(**args)
+        assert not isinstance(result, int) or result == 0, f"{fn_name} returned {result}"   # a program's exit code
     else:
         fn(rank, world_size, *args)
 
@@ -140,6 +141,7 @@ FUNCTIONS = [
      {"level": 3, "block_n": 256, "shape": (256, 512, 128)}),
     ("test_gpu_matmul", "test_matmul_small", {"block_n": 224, "shape": (200, 328, 96), "cta_pair": True}),
     ("__graft_entry__", "smoke", {}),                  # the smoke check that runs on a GPU before the benchmark
+    ("symm_mem_recipes_b200.selfcheck", "main", {"argv": ["--first-run"]}),     # the one-GPU form of the self-check
     # the single-GPU tests that run at every GPU test pass
     ("test_gpu_symm_mem", "test_world_of_one_all_paths", {}),
     ("test_gpu_gemv", "test_gemv_world_of_one", {"B": 3, "K": 1000, "N": 328, "algo": "tc"}),
