@@ -150,3 +150,20 @@ def test_build_targets_sm_100a_only_and_covers_every_source():
     for src in cu + cpp:
         assert str(src) in ninja
     assert str(_build.so_path()) in ninja
+
+
+def test_in_tree_extension_is_current():
+    """The built extension travels with the tree to the GPU machines: it must not be older than
+    any of its sources (a kernel edited without a rebuild would be tested here but not run there)."""
+    import shutil
+
+    import pytest
+
+    from symm_mem_recipes_b200 import _build
+
+    if shutil.which("ninja") is None or not _build.so_path().exists():
+        pytest.skip("no ninja or no built extension in this tree")
+    ninja_file = _build.write_ninja()
+    dry = subprocess.run(["ninja", "-C", str(ninja_file.parent), "-n"], capture_output=True, text=True, timeout=120)
+    assert dry.returncode == 0 and "no work to do" in dry.stdout, (
+        "the extension is stale: run python -m symm_mem_recipes_b200._build\n" + dry.stdout[-600:])
