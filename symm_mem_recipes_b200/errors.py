@@ -11,6 +11,21 @@ _CODES = {
 }
 
 
+# where in which kernel the wait ran out (csrc/device/status.h, enum Where)
+_WHERE = {
+    1: "barrier kernel / signal", 10: "one-shot all-reduce, entry barrier", 11: "one-shot all-reduce, exit barrier",
+    12: "two-shot all-reduce, entry barrier", 13: "two-shot all-reduce, exit barrier",
+    14: "multimem all-reduce, entry barrier", 15: "multimem all-reduce, exit barrier",
+    20: "GEMM: operands never arrived in shared memory (full barrier)",
+    21: "GEMM: shared-memory stage never freed (empty barrier)",
+    22: "GEMM: accumulator never completed (TMEM full)", 23: "GEMM: accumulator never drained (TMEM empty)",
+    24: "all_gather_matmul: a gathered block never arrived", 25: "all_gather_matmul: entry barrier",
+    26: "all_gather_matmul: exit barrier", 30: "gemv_all_reduce: a partial never arrived",
+    31: "gemv_all_reduce: call number", 40: "matmul_reduce_scatter: a tile's partials never arrived / exit barrier",
+    41: "matmul_reduce_scatter: entry barrier", 42: "matmul_reduce_scatter: exit barrier", 99: "test kernel",
+}
+
+
 class SymmMemError(RuntimeError):
     """A kernel or host protocol of this library reported a failure."""
 
@@ -23,7 +38,8 @@ class SymmMemTimeout(SymmMemError):
             int(code), int(rank), int(block), int(peer), int(where), int(aux))
         super().__init__(
             f"{_CODES.get(self.code, 'status %d' % self.code)}: rank={self.rank} "
-            f"block={self.block} peer={self.peer} where={self.where} aux={self.aux}")
+            f"block={self.block} peer={self.peer} where={self.where} ({_WHERE.get(self.where, 'unknown')}) "
+            f"aux={self.aux}")
 
 
 def raise_for_status(record) -> None:

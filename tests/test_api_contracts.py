@@ -84,3 +84,19 @@ def test_info_runs_without_a_gpu():
     assert "torch" in d and "gpus" in d and d["limits"]["max_world_size"] >= 8
     if not torch.cuda.is_available():
         assert d["gpus"] == [] and "CPU backend" in d["note"]
+
+
+def test_timeout_messages_name_the_place():
+    """Every `Where` code of the native status record has a description on the Python side."""
+    import pathlib
+    import re
+
+    from symm_mem_recipes_b200 import errors
+
+    header = (pathlib.Path(errors.__file__).parent / "csrc" / "device" / "status.h").read_text()
+    body = header[header.index("enum Where"):]
+    body = body[:body.index("};")]
+    codes = {int(v) for v in re.findall(r"kWhere\w+\s*=\s*(\d+)", body)}
+    assert codes and codes == set(errors._WHERE), (sorted(codes), sorted(errors._WHERE))
+    e = errors.SymmMemTimeout(3, 1, 5, 0, 24, 7)
+    assert "a gathered block never arrived" in str(e) and "rank=1" in str(e) and e.where == 24
