@@ -37,6 +37,7 @@ activation is applied to the accumulators inside the all_gather_matmul epilogue.
 """
 from __future__ import annotations
 
+import contextlib
 import os
 from dataclasses import dataclass
 from typing import Optional
@@ -70,6 +71,17 @@ class LlamaTPConfig:
         """Same structure at a size a unit test can check against fp32."""
         return LlamaTPConfig(hidden=512, n_heads=4 * world_size, n_kv_heads=world_size, head_dim=64,
                              ffn=512 * world_size)
+
+
+def _sdpa_backends():
+    """Context for the prefill attention call.  Attention is rank-local library code
+    (`scaled_dot_product_attention`); with SMR_SDPA_CUDNN=1 PyTorch is asked to try its cuDNN
+    backend first and fall back to its usual order.  Off by default."""
+    if os.environ.get("SMR_SDPA_CUDNN", "0") != "1":
+        return contextlib.nullcontext()
+    from torch.nn.attention import SDPBackend, sdpa_kernel
+    return sdpa_kernel([SDPBackend.CUDNN_ATTENTION, SDPBackend.FLASH_ATTENTION, SDPBackend.EFFICIENT_ATTENTION,
+                        SDPBackend.MATH], set_priority=True)
 
 
 def _rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
@@ -191,8 +203,9 @@ class LlamaTPDecoderLayer:
                 raise ValueError("kv_cache: two [batch, S_max >= seq, kv heads per rank, head_dim] tensors")
             k_cache[:, :seq].copy_(k)
             v_cache[:, :seq].copy_(v)
-        o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
-                                           is_causal=True, enable_gqa=True)
+        with _sdpa_backends():
+            o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
+                                               is_causal=True, enable_gqa=True)
         return o.transpose(1, 2).reshape(batch * seq, hq * D).contiguous()
 
     @staticmethod
