@@ -3,7 +3,7 @@ PY ?= python
 NPROC ?= 8
 TORCHRUN = $(PY) -m torch.distributed.run --nnodes 1 --nproc-per-node $(NPROC) --master-addr 127.0.0.1
 
-.PHONY: build test test-gpu test-first-run selfcheck bench bench-suite bench-detail report expect clean
+.PHONY: build test test-gpu selfcheck bench bench-suite bench-detail report expect clean
 
 build:            ## nvcc -gencode arch=compute_100a,code=sm_100a for every kernel, link the extension
 	$(PY) -m symm_mem_recipes_b200._build
@@ -14,10 +14,7 @@ test: build       ## oracles, host backend, gloo ranks, schedules, flow tests
 test-gpu: build   ## on a B200 box; multi-GPU cases skip when GPUs are missing
 	$(PY) -m pytest tests -q -m gpu
 
-test-first-run: build   ## also the variants whose first run on hardware is pending
-	SMR_TEST_FIRST_RUN=1 $(PY) -m pytest tests -q -m gpu
-
-selfcheck: build  ## every op once on small shapes in one start-up, NPROC GPUs (add ARGS=--first-run)
+selfcheck: build  ## every op once on small shapes in one start-up, NPROC GPUs (ARGS="--only gemv,glue" narrows it)
 	if [ "$(NPROC)" = "1" ]; then $(PY) -m symm_mem_recipes_b200.selfcheck $(ARGS); \
 	else $(TORCHRUN) -m symm_mem_recipes_b200.selfcheck $(ARGS); fi
 

@@ -49,6 +49,11 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--out", default=None)
     ap.add_argument("--with-push-copy", action="store_true",
                     help="also time an ordinary a_out served by the push kernel plus one local copy")
+    ap.add_argument("--leads", default="", help="push mode: comma-separated counts of own 128-row blocks multiplied "
+                                                "before the first remote one, each timed")
+    ap.add_argument("--trace", action="store_true",
+                    help="print the per-CTA timing record of one fused call and one GEMM-only call, per rank")
+    ap.add_argument("--per-rank", action="store_true", help="also print every rank's own median beside the maximum")
     ap.add_argument("--upstream-table", action="store_true",
                     help="run the nine (model, M) shapes of the upstream README instead of --M/--N/--K")
     ap.add_argument("--print-ptxas", "--print_ptx", dest="print_ptxas", action="store_true",
@@ -123,16 +128,63 @@ def _one_shape(args, M, N, K, rank, world, dev, lines) -> None:
     assert torch.allclose(c0.float(), c1.float(), rtol=2e-2, atol=2e-3), "fused != NCCL + cuBLAS"
 
     bench = dict(warmup_iters=args.warmup, benchmark_iters=args.iters, flush_l2=True)
-    emit("cublas_mm_only", benchmark_with_event(lambda: torch.matmul(a, bt, out=c), **bench))
+
+    def timed(fn):
+        """Maximum over ranks of the per-rank medians; with --per-rank also the list of them."""
+        own = benchmark_with_event(fn, all_ranks_max=False, **bench)
+        per_rank = [None] * world
+        if world > 1:
+            dist.all_gather_object(per_rank, round(own, 1))
+        else:
+            per_rank = [round(own, 1)]
+        return max(per_rank), ({"per_rank_us": per_rank} if args.per_rank else {})
+
+    us, extra = timed(lambda: torch.matmul(a, bt, out=c))
+    emit("cublas_mm_only", us, **extra)
     cfg0 = AgMatmulConfig(block_n=args.block_n)
-    emit("smr_mm_only", benchmark_with_event(lambda: smr.matmul(a, b, c, cfg0), **bench))
-    emit("cublas_plus_nccl", benchmark_with_event(lambda: smr.reference_all_gather_matmul(a_shard, b), **bench))
+    us, extra = timed(lambda: smr.matmul(a, b, c, cfg0))
+    emit("smr_mm_only", us, **extra)
+    us, extra = timed(lambda: smr.reference_all_gather_matmul(a_shard, b))
+    emit("cublas_plus_nccl", us, **extra)
     gathered = torch.empty(M, K, dtype=torch.bfloat16, device=dev)
-    emit("nccl_all_gather_only",
-         benchmark_with_event(lambda: dist.all_gather_into_tensor(gathered, a_shard), **bench))
-    us = benchmark_with_event(lambda: smr.all_gather_matmul(a_shard, b, a_out, c, cfg0), **bench)
-    emit("smr_fused", us, gather="push")
+    us, extra = timed(lambda: dist.all_gather_into_tensor(gathered, a_shard))
+    emit("nccl_all_gather_only", us, **extra)
+    us, extra = timed(lambda: smr.all_gather_matmul(a_shard, b, a_out, c, cfg0))
+    emit("smr_fused", us, gather="push", **extra)
     symm_mem.check_status(dev)
+    for lead in [int(x) for x in args.leads.split(",") if x]:
+        cfgl = AgMatmulConfig(block_n=args.block_n, lead=lead)
+        us, extra = timed(lambda: smr.all_gather_matmul(a_shard, b, a_out, c, cfgl))
+        emit("smr_fused", us, gather="push", lead=lead, **extra)
+        symm_mem.check_status(dev)
+    if args.trace:
+        from symm_mem_recipes_b200.ops.ag_matmul import summarize_trace
+        from symm_mem_recipes_b200.utils.benchmark import flush_l2
+
+        for what, fn in (("smr_fused", lambda tr: smr.all_gather_matmul(a_shard, b, a_out, c, cfg0, trace=tr)),
+                         ("smr_mm_only", lambda tr: smr.matmul(a, b, c, cfg0, trace=tr))):
+            tr = torch.zeros(160, 12, dtype=torch.int64, device=dev)
+            for _ in range(3):
+                fn(tr)
+            torch.cuda.synchronize()
+            dist.barrier() if world > 1 else None
+            tr.zero_()
+            flush_l2(dev)
+            fn(tr)
+            torch.cuda.synchronize()
+            summ = summarize_trace(tr)
+            all_s = [None] * world
+            if world > 1:
+                dist.all_gather_object(all_s, summ)
+            else:
+                all_s = [summ]
+            if rank == 0:
+                for r, s_ in enumerate(all_s):
+                    line = json.dumps({"op": "all_gather_matmul_trace", "impl": what, "world_size": world,
+                                       "rank": r, "M": M, "N": N, "K": K, "us": s_})
+                    print(line, flush=True)
+                    lines.append(line)
+        symm_mem.check_status(dev)
     for n_copy in [int(x) for x in args.copy_ctas.split(",") if x]:
         cfg = AgMatmulConfig(block_n=args.block_n, n_copy=n_copy)
         us = benchmark_with_event(lambda: smr.all_gather_matmul(a_shard, b, a_out_plain, c, cfg), **bench)

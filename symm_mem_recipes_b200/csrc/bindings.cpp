@@ -462,7 +462,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                         std::shared_ptr<CudaSymmAllocation> aout_alloc, int64_t aout_offset,
                         c10::optional<torch::Tensor> a_out, c10::optional<torch::Tensor> flags,
                         int block_n, int num_sms, int n_copy, uint64_t timeout_ns, bool cta_pair,
-                        c10::optional<torch::Tensor> tail_scratch, int epilogue, int l2_hints) {
+                        c10::optional<torch::Tensor> tail_scratch, int epilogue, int l2_hints,
+                        c10::optional<torch::Tensor> trace, int lead) {
     const auto dtype = a.scalar_type();
     const bool fp8 = dtype == at::kFloat8_e4m3fn;
     TORCH_CHECK(fp8 || dtype == torch::kBFloat16, "a must be bfloat16 or float8_e4m3fn");
@@ -541,13 +542,21 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       args.tail_scratch = base + 4096;
       args.tail_scratch_bytes = tail_scratch->nbytes() - 4096;
     }
+    args.lead = lead;
+    if (trace.has_value()) {
+      TORCH_CHECK(cta_pair && mode != 1, "the timing record belongs to the CTA-pair kernel");
+      TORCH_CHECK(trace->is_cuda() && trace->get_device() == dev && trace->is_contiguous() &&
+                  trace->scalar_type() == torch::kInt64 && trace->numel() >= (int64_t)num_sms * 12,
+                  "trace must be a contiguous int64 CUDA tensor of num_sms x 12 words");
+      args.trace = reinterpret_cast<uint64_t*>(trace->data_ptr());
+    }
     rt_check(cta_pair && mode != 1 ? launch_ag_matmul_2cta(args, stream) : launch_ag_matmul(args, stream),
              "ag_matmul");
   }, py::arg("a"), py::arg("b"), py::arg("c"), py::arg("mode"), py::arg("shard_alloc"),
      py::arg("shard_offset"), py::arg("aout_alloc"), py::arg("aout_offset"), py::arg("a_out"),
      py::arg("flags"), py::arg("block_n"), py::arg("num_sms"), py::arg("n_copy"), py::arg("timeout_ns"),
      py::arg("cta_pair") = false, py::arg("tail_scratch") = py::none(), py::arg("epilogue") = 0,
-     py::arg("l2_hints") = 0);
+     py::arg("l2_hints") = 0, py::arg("trace") = py::none(), py::arg("lead") = -1);
 
   m.def("check_push_schedule", &check_push_schedule);
   m.def("check_pair_work", &check_pair_work);

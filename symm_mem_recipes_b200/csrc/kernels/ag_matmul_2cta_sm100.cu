@@ -37,13 +37,24 @@ using namespace agmm;
 
 namespace {
 
-template <int BN, int STAGES>
+// Whether an instantiation's epilogue leaves through shared memory and TMA stores: plain bf16
+// output in whole boxes of 64 columns (a 224-wide tile would spill into its neighbour's columns).
+template <int BN, bool kFp8, bool kSwiGlu>
+constexpr bool pair_tma_store() { return !kFp8 && !kSwiGlu && BN % 64 == 0; }
+
+// kOut: the plain bf16 epilogue leaves through shared memory: each epilogue warp owns two
+// 4 KB boxes (32 rows x 64 columns, 128-byte swizzle) that it fills from its accumulator rows
+// and hands to a TMA store while it converts the next 64 columns into the other box.
+template <int BN, int STAGES, bool kOut = false>
 struct PairSmem {
   static constexpr uint32_t kABytes = kBM * kBK * 2;
   static constexpr uint32_t kBBytes = (BN / 2) * kBK * 2;     // this CTA's half of the B tile
   static constexpr uint32_t kStageBytes = kABytes + kBBytes;
   static constexpr uint32_t kRingBytes = kStageBytes * STAGES;
-  static constexpr uint32_t kBarOffset = kRingBytes;
+  static constexpr uint32_t kOutBoxBytes = 32 * 128;          // 32 rows x 64 bf16
+  static constexpr uint32_t kOutOffset = kRingBytes;
+  static constexpr uint32_t kOutBytes = kOut ? 4 * 2 * kOutBoxBytes : 0;
+  static constexpr uint32_t kBarOffset = kRingBytes + kOutBytes;
   static constexpr uint32_t kNumBars = 2 * STAGES + 4;
   static constexpr uint32_t kMiscOffset = kBarOffset + 8 * kNumBars;
   static constexpr uint32_t kTotal = kMiscOffset + 16 + 1024;
@@ -62,8 +73,10 @@ template <int BN, int STAGES, bool kFp8, bool kSwiGlu = false, bool kL2Hints = f
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
                       const __grid_constant__ CUtensorMap tmap_a_out,
-                      const __grid_constant__ CUtensorMap tmap_b, const AgMatmulParams p) {
-  using L = PairSmem<BN, STAGES>;
+                      const __grid_constant__ CUtensorMap tmap_b,
+                      const __grid_constant__ CUtensorMap tmap_c, const AgMatmulParams p) {
+  constexpr bool kTmaStore = pair_tma_store<BN, kFp8, kSwiGlu>();
+  using L = PairSmem<BN, STAGES, kTmaStore>;
   extern __shared__ uint8_t smem_raw[];
   // same offset in both CTAs: the dynamic window starts at the same shared address
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -98,6 +111,7 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
     tma_prefetch_desc(&tmap_a_shard);
     tma_prefetch_desc(&tmap_a_out);
     tma_prefetch_desc(&tmap_b);
+    if constexpr (kTmaStore) tma_prefetch_desc(&tmap_c);
   }
   if (warp == 1) {
     tmem_alloc_pair(tmem_slot, kTmemCols);
@@ -108,6 +122,9 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
   cluster_sync_all();                 // barriers of both CTAs initialised, TMEM allocated
   tcgen05_fence_after_thread_sync();
   const uint32_t tmem_base = *tmem_slot;
+  const bool tr = p.trace != nullptr;
+  uint64_t* trc = tr ? p.trace + (size_t)blockIdx.x * ag_trace::kTraceSlots : nullptr;
+  if (tr && threadIdx.x == 0) trc[ag_trace::kStart] = globaltimer_ns();
 
   const int pair = (int)blockIdx.x >> 1;
   const int n_pairs = (int)gridDim.x >> 1;
@@ -123,6 +140,8 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       PairWork w;
+      uint64_t t_flag = 0, t_stage = 0, t_first = 0;
+      bool first_remote = true;
       // B is re-read by every wave of tiles: keep it; A passes through once
       [[maybe_unused]] uint64_t pol_a = 0, pol_b = 0;
       if constexpr (kL2Hints) {
@@ -143,21 +162,31 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
             row0 -= p.rank * rows_per_rank;
           }
           if (!local) {
+            const uint64_t t0 = tr ? globaltimer_ns() : 0;
             if (!wait_ge_acquire_sys(&p.flags[mblk], flag_target, p.timeout_ns)) {
               report_status(p.status, kTimeoutFlag, p.rank, blockIdx.x, mblk, kWhereGemmProgress);
               failed = true;
               break;
             }
             fence_proxy_async();
+            if (tr) {
+              const uint64_t dt = globaltimer_ns() - t0;
+              t_flag += dt;
+              if (first_remote) { t_first = dt; first_remote = false; }
+            }
           }
         } else {
           row0 = p.n_blocks_m * kBM;   // odd tail: rows past M read as zero
         }
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.timeout_ns)) {
-            report_status(p.status, kTimeoutMbarrier, p.rank, blockIdx.x, stage, kWhereGemmEmpty);
-            failed = true;
-            break;
+          if (!mbar_try_wait(&empty_bar[stage], phase ^ 1)) {
+            const uint64_t t0 = tr ? globaltimer_ns() : 0;
+            if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.timeout_ns)) {
+              report_status(p.status, kTimeoutMbarrier, p.rank, blockIdx.x, stage, kWhereGemmEmpty);
+              failed = true;
+              break;
+            }
+            if (tr) t_stage += globaltimer_ns() - t0;
           }
           uint8_t* sa = smem + (size_t)stage * L::kStageBytes;
           uint8_t* sb = sa + L::kABytes;
@@ -173,6 +202,11 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
+      if (tr) {
+        trc[ag_trace::kFlagWait] = t_flag;
+        trc[ag_trace::kStageWait] = t_stage;
+        trc[ag_trace::kFirstFlagWait] = t_first;
+      }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer (leader CTA only) ----------------
@@ -180,19 +214,28 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
       constexpr uint32_t idesc = kFp8 ? umma_idesc_e4m3_f32(2 * kBM, BN) : umma_idesc_bf16_f32(2 * kBM, BN);
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       PairWork w;
+      uint64_t t_tmem = 0, t_opnd = 0;
       for (int wi = 0; !failed && pair_work(p, pair, n_pairs, total_tiles, k_blocks, wi, w); ++wi) {
-        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, p.timeout_ns)) {
-          report_status(p.status, kTimeoutMbarrier, p.rank, blockIdx.x, acc, kWhereGemmTmemEmpty);
-          failed = true;
-          break;
+        if (!mbar_try_wait(&tmem_empty[acc], acc_phase ^ 1)) {
+          const uint64_t t0 = tr ? globaltimer_ns() : 0;
+          if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, p.timeout_ns)) {
+            report_status(p.status, kTimeoutMbarrier, p.rank, blockIdx.x, acc, kWhereGemmTmemEmpty);
+            failed = true;
+            break;
+          }
+          if (tr) t_tmem += globaltimer_ns() - t0;
         }
         tcgen05_fence_after_thread_sync();
         const uint32_t d_tmem = tmem_base + acc * 256u;
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
-          if (!mbar_wait(&full_bar[stage], phase, p.timeout_ns)) {
-            report_status(p.status, kTimeoutMbarrier, p.rank, blockIdx.x, stage, kWhereGemmFull);
-            failed = true;
-            break;
+          if (!mbar_try_wait(&full_bar[stage], phase)) {
+            const uint64_t t0 = tr ? globaltimer_ns() : 0;
+            if (!mbar_wait(&full_bar[stage], phase, p.timeout_ns)) {
+              report_status(p.status, kTimeoutMbarrier, p.rank, blockIdx.x, stage, kWhereGemmFull);
+              failed = true;
+              break;
+            }
+            if (tr) t_opnd += globaltimer_ns() - t0;
           }
           tcgen05_fence_after_thread_sync();
           const uint32_t sa = smem_u32(smem + (size_t)stage * L::kStageBytes);
@@ -215,6 +258,10 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1;
       }
+      if (tr) {
+        trc[ag_trace::kTmemWait] = t_tmem;
+        trc[ag_trace::kOperandWait] = t_opnd;
+      }
     }
   } else {
     // ---------------- epilogue (warps 2..5 of both CTAs) ----------------
@@ -225,7 +272,11 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
     const int all_pieces = p.blocks_per_rank * p.pieces;
     [[maybe_unused]] uint64_t pol_c = 0;               // C is written once and not read again by this kernel
     if constexpr (kL2Hints) pol_c = l2_policy_evict_first();
+    [[maybe_unused]] int out_box = 0;                  // which of this warp's two output boxes is filled next
     if (p.mode == 2 && !push_entry_barrier(p, (int)blockIdx.x, etid)) failed = true;
+    const bool trt = tr && etid == 0;
+    uint64_t t_push = 0, t_acc = 0, n_units = 0;
+    if (trt) trc[ag_trace::kEntered] = globaltimer_ns();
     __shared__ int tail_ok;
     PairWork w;
     for (int wi = 0; !failed && pair_work(p, pair, n_pairs, total_tiles, k_blocks, wi, w); ++wi) {
@@ -235,15 +286,21 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
       const bool valid = mi < p.n_blocks_m;
       const int mblk = valid ? scheduled_block(p, mi, local_unused) : 0;
       if (p.mode == 2) {
+        const uint64_t t0 = trt ? globaltimer_ns() : 0;
         next_piece = push_pieces(p, next_piece, (int)gridDim.x,
                                  pieces_needed_through_round(p, round + 1, n_pairs, 2), etid);
         ++round;
+        if (trt) t_push += globaltimer_ns() - t0;
       }
-      if (!mbar_wait(&tmem_full[acc], acc_phase, p.timeout_ns)) {
-        if (lane == 0)
-          report_status(p.status, kTimeoutMbarrier, p.rank, blockIdx.x, acc, kWhereGemmTmemFull);
-        failed = true;
-        break;
+      {
+        const uint64_t t0 = trt ? globaltimer_ns() : 0;
+        if (!mbar_wait(&tmem_full[acc], acc_phase, p.timeout_ns)) {
+          if (lane == 0)
+            report_status(p.status, kTimeoutMbarrier, p.rank, blockIdx.x, acc, kWhereGemmTmemFull);
+          failed = true;
+          break;
+        }
+        if (trt) { t_acc += globaltimer_ns() - t0; ++n_units; }
       }
       tcgen05_fence_after_thread_sync();
       const int row = mblk * kBM + quarter * 32 + lane;
@@ -344,6 +401,61 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
             }
           }
         }
+      } else if constexpr (kTmaStore) {
+        // 64 columns at a time: two TMEM loads in flight, bf16 into this warp's free box
+        // (16-byte chunk j of row r sits at chunk j ^ (r & 7): the 128-byte swizzle of the
+        // tensor map, and conflict-free for the warp's stores), then one TMA store.
+        const uint32_t box0 = smem_u32(smem + L::kOutOffset) + (uint32_t)quarter * 2u * L::kOutBoxBytes;
+        const bool store_ok = valid && mblk * kBM + quarter * 32 < p.M;
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32b_x32(taddr + (uint32_t)(c * 64), r0);
+          tmem_ld_32x32b_x32(taddr + (uint32_t)(c * 64 + 32), r1);
+          if (lane == 0) bulk_wait_group_read<1>();      // the store that last read this box is done with it
+          __syncwarp();
+          tmem_ld_wait();
+          if (c == BN / 64 - 1) {
+            // the accumulator is in registers: hand it back before the stores
+            tcgen05_fence_before_thread_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc]), 0));
+          }
+          const uint32_t box = box0 + (uint32_t)out_box * L::kOutBoxBytes;
+          const uint32_t rowaddr = box + (uint32_t)lane * 128u;
+          const uint32_t sw = (uint32_t)(lane & 7);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            st_shared_16(rowaddr + ((((uint32_t)j) ^ sw) << 4),
+                         pack_bf16x2(__uint_as_float(r0[j * 8 + 0]), __uint_as_float(r0[j * 8 + 1])),
+                         pack_bf16x2(__uint_as_float(r0[j * 8 + 2]), __uint_as_float(r0[j * 8 + 3])),
+                         pack_bf16x2(__uint_as_float(r0[j * 8 + 4]), __uint_as_float(r0[j * 8 + 5])),
+                         pack_bf16x2(__uint_as_float(r0[j * 8 + 6]), __uint_as_float(r0[j * 8 + 7])));
+            st_shared_16(rowaddr + ((((uint32_t)(j + 4)) ^ sw) << 4),
+                         pack_bf16x2(__uint_as_float(r1[j * 8 + 0]), __uint_as_float(r1[j * 8 + 1])),
+                         pack_bf16x2(__uint_as_float(r1[j * 8 + 2]), __uint_as_float(r1[j * 8 + 3])),
+                         pack_bf16x2(__uint_as_float(r1[j * 8 + 4]), __uint_as_float(r1[j * 8 + 5])),
+                         pack_bf16x2(__uint_as_float(r1[j * 8 + 6]), __uint_as_float(r1[j * 8 + 7])));
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (store_ok && ni * BN + c * 64 < p.N) {
+              uint8_t* src = smem + L::kOutOffset + ((size_t)quarter * 2 + out_box) * L::kOutBoxBytes;
+              if constexpr (kL2Hints) {
+                if (p.l2_hints >= 3) tma_store_2d_hint(&tmap_c, src, ni * BN + c * 64, mblk * kBM + quarter * 32, pol_c);
+                else tma_store_2d(&tmap_c, src, ni * BN + c * 64, mblk * kBM + quarter * 32);
+              } else {
+                tma_store_2d(&tmap_c, src, ni * BN + c * 64, mblk * kBM + quarter * 32);
+              }
+            }
+            bulk_commit_group();
+          }
+          out_box ^= 1;
+        }
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+        continue;
       } else {
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -379,12 +491,7 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
               o.y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
               o.z = pack_bf16x2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
               o.w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
-              if constexpr (kL2Hints) {
-                if (p.l2_hints >= 3) st_16_hint(crow + c * 32 + v * 8, o, pol_c);
-                else st_16(crow + c * 32 + v * 8, o);
-              } else {
-                st_16(crow + c * 32 + v * 8, o);
-              }
+              st_16(crow + c * 32 + v * 8, o);
             }
           }
         }
@@ -396,7 +503,21 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
-    if (p.mode == 2 && !failed) push_pieces(p, next_piece, (int)gridDim.x, all_pieces, etid);
+    if constexpr (kTmaStore) {
+      if (lane == 0) bulk_wait_group<0>();             // C is written before the kernel ends
+    }
+    if (trt) trc[ag_trace::kTilesDone] = globaltimer_ns();
+    if (p.mode == 2 && !failed) {
+      const uint64_t t0 = trt ? globaltimer_ns() : 0;
+      push_pieces(p, next_piece, (int)gridDim.x, all_pieces, etid);
+      if (trt) t_push += globaltimer_ns() - t0;
+    }
+    if (trt) {
+      trc[ag_trace::kPush] = t_push;
+      trc[ag_trace::kAccWait] = t_acc;
+      trc[ag_trace::kTiles] = n_units;
+      trc[ag_trace::kEnd] = globaltimer_ns();
+    }
   }
 
   // ---------------- teardown ----------------
@@ -420,13 +541,13 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
 
 template <int BN, int STAGES, bool kFp8, bool kSwiGlu = false, bool kL2Hints = false>
 int launch_pair_variant(const CUtensorMap& ta_shard, const CUtensorMap& ta_out, const CUtensorMap& tb,
-                        const AgMatmulParams& p, int grid, cudaStream_t stream) {
-  using L = PairSmem<BN, STAGES>;
+                        const CUtensorMap& tc, const AgMatmulParams& p, int grid, cudaStream_t stream) {
+  using L = PairSmem<BN, STAGES, pair_tma_store<BN, kFp8, kSwiGlu>()>;
   static_assert(L::kTotal <= 232448, "shared memory limit exceeded");
   auto kern = ag_matmul_2cta_kernel<BN, STAGES, kFp8, kSwiGlu, kL2Hints>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::kTotal);
   if (e != cudaSuccess) return (int)e;
-  kern<<<grid, kGemmThreads, L::kTotal, stream>>>(ta_shard, ta_out, tb, p);
+  kern<<<grid, kGemmThreads, L::kTotal, stream>>>(ta_shard, ta_out, tb, tc, p);
   return (int)cudaGetLastError();
 }
 
@@ -468,6 +589,7 @@ int launch_ag_matmul_2cta(const AgMatmulArgs& a, cudaStream_t stream) {
   p.pieces = 1;
   if (comm) {
     p.lead = p.blocks_per_rank < 4 ? p.blocks_per_rank : 4;
+    if (a.lead >= 0) p.lead = a.lead < p.blocks_per_rank ? a.lead : p.blocks_per_rank;
     size_t block_vecs = (size_t)kBM * a.K * es / 16;
     p.pieces = block_vecs >= 8192 ? 16 : (block_vecs >= 1024 ? 4 : 1);
   }
@@ -483,13 +605,17 @@ int launch_ag_matmul_2cta(const AgMatmulArgs& a, cudaStream_t stream) {
   p.barrier_block_base = a.barrier_block_base;
   p.timeout_ns = a.timeout_ns;
   p.status = a.status;
+  p.trace = a.trace;
 
-  CUtensorMap ta_shard, ta_out, tb;
+  CUtensorMap ta_shard, ta_out, tb, tc;
   int rows_local = comm ? a.rows_per_rank : a.M;
   if (make_tmap(&ta_shard, a.a_local, (uint64_t)rows_local, (uint64_t)a.K, kBM, es)) return cudaErrorInvalidValue;
   if (make_tmap(&ta_out, comm ? a.a_out : a.a_local, (uint64_t)a.M, (uint64_t)a.K, kBM, es))
     return cudaErrorInvalidValue;
   if (make_tmap(&tb, a.b, (uint64_t)a.N, (uint64_t)a.K, (uint32_t)(bn / 2), es)) return cudaErrorInvalidValue;
+  // C as the TMA stores of the plain bf16 epilogue see it: boxes of 32 rows x 64 columns
+  const int c_cols = swiglu ? a.N / 2 : a.N;
+  if (make_tmap(&tc, a.c, (uint64_t)a.M, (uint64_t)c_cols, 32, es)) return cudaErrorInvalidValue;
 
   const int total_tiles = ((p.n_blocks_m + 1) / 2) * p.n_tiles_n;
   int pairs = a.num_sms / 2;
@@ -522,26 +648,26 @@ int launch_ag_matmul_2cta(const AgMatmulArgs& a, cudaStream_t stream) {
   p.l2_hints = a.l2_hints;
   if (a.l2_hints != 0) {
     switch (bn) {
-      case 128: return launch_pair_variant<128, 8, false, false, true>(ta_shard, ta_out, tb, p, grid, stream);
-      case 192: return launch_pair_variant<192, 7, false, false, true>(ta_shard, ta_out, tb, p, grid, stream);
-      case 224: return launch_pair_variant<224, 7, false, false, true>(ta_shard, ta_out, tb, p, grid, stream);
-      default:  return launch_pair_variant<256, 6, false, false, true>(ta_shard, ta_out, tb, p, grid, stream);
+      case 128: return launch_pair_variant<128, 8, false, false, true>(ta_shard, ta_out, tb, tc, p, grid, stream);
+      case 192: return launch_pair_variant<192, 6, false, false, true>(ta_shard, ta_out, tb, tc, p, grid, stream);
+      case 224: return launch_pair_variant<224, 7, false, false, true>(ta_shard, ta_out, tb, tc, p, grid, stream);
+      default:  return launch_pair_variant<256, 6, false, false, true>(ta_shard, ta_out, tb, tc, p, grid, stream);
     }
   }
-  if (swiglu) return launch_pair_variant<256, 6, false, true>(ta_shard, ta_out, tb, p, grid, stream);
+  if (swiglu) return launch_pair_variant<256, 6, false, true>(ta_shard, ta_out, tb, tc, p, grid, stream);
   if (fp8) {
     switch (bn) {
-      case 128: return launch_pair_variant<128, 8, true>(ta_shard, ta_out, tb, p, grid, stream);
-      case 192: return launch_pair_variant<192, 7, true>(ta_shard, ta_out, tb, p, grid, stream);
-      case 224: return launch_pair_variant<224, 7, true>(ta_shard, ta_out, tb, p, grid, stream);
-      default:  return launch_pair_variant<256, 6, true>(ta_shard, ta_out, tb, p, grid, stream);
+      case 128: return launch_pair_variant<128, 8, true>(ta_shard, ta_out, tb, tc, p, grid, stream);
+      case 192: return launch_pair_variant<192, 7, true>(ta_shard, ta_out, tb, tc, p, grid, stream);
+      case 224: return launch_pair_variant<224, 7, true>(ta_shard, ta_out, tb, tc, p, grid, stream);
+      default:  return launch_pair_variant<256, 6, true>(ta_shard, ta_out, tb, tc, p, grid, stream);
     }
   }
   switch (bn) {
-    case 128: return launch_pair_variant<128, 8, false>(ta_shard, ta_out, tb, p, grid, stream);
-    case 192: return launch_pair_variant<192, 7, false>(ta_shard, ta_out, tb, p, grid, stream);
-    case 224: return launch_pair_variant<224, 7, false>(ta_shard, ta_out, tb, p, grid, stream);
-    default:  return launch_pair_variant<256, 6, false>(ta_shard, ta_out, tb, p, grid, stream);
+    case 128: return launch_pair_variant<128, 8, false>(ta_shard, ta_out, tb, tc, p, grid, stream);
+    case 192: return launch_pair_variant<192, 6, false>(ta_shard, ta_out, tb, tc, p, grid, stream);
+    case 224: return launch_pair_variant<224, 7, false>(ta_shard, ta_out, tb, tc, p, grid, stream);
+    default:  return launch_pair_variant<256, 6, false>(ta_shard, ta_out, tb, tc, p, grid, stream);
   }
 }
 

@@ -69,7 +69,29 @@ struct AgMatmulParams {
   // L2 eviction hints (2-CTA kernel, bf16, hinted instantiation only): 1 = B tiles evict_last,
   // 2 = also A tiles evict_first, 3 = also the stores of C evict_first
   int l2_hints;
+  // optional per-CTA %globaltimer record (2-CTA kernel), kTraceSlots words per CTA; see ag_trace::
+  uint64_t* trace;
 };
+
+// Per-CTA timing record of the CTA-pair kernel (nanoseconds of %globaltimer).  Absolute stamps
+// and accumulated waiting times of each warp role, enough to tell where a fused call loses time
+// against the GEMM alone.  Upstream has no counterpart (it reads kernel times from the profiler,
+// symm_mem_recipes/utils.py:74-82).
+namespace ag_trace {
+constexpr int kStart = 0;          // stamp: kernel entry
+constexpr int kEntered = 1;        // stamp: entry barrier of the push mode passed
+constexpr int kFlagWait = 2;       // producer: total wait for arrival flags of remote blocks
+constexpr int kPush = 3;           // epilogue warps: total time inside push_pieces
+constexpr int kAccWait = 4;        // epilogue warps: total wait for a complete accumulator
+constexpr int kTilesDone = 5;      // stamp: last tile stored
+constexpr int kTmemWait = 6;       // MMA thread: total wait for a free accumulator
+constexpr int kOperandWait = 7;    // MMA thread: total wait for operand stages
+constexpr int kStageWait = 8;      // producer: total wait for free stages
+constexpr int kEnd = 9;            // stamp: epilogue warps done (trailing pushes included)
+constexpr int kFirstFlagWait = 10; // producer: wait for the first remote block
+constexpr int kTiles = 11;         // units of work of this CTA
+constexpr int kTraceSlots = 12;
+}  // namespace ag_trace
 
 // ---------------------------------------------------------------------------
 // Push, run by the 128 epilogue threads of every GEMM CTA before their first

@@ -104,6 +104,10 @@ struct AgMatmulArgs {
   // 2-CTA kernel, bf16, plain epilogue: L2 eviction hints on the operand loads (0 = none;
   // 1 = B evict_last; 2 = also A evict_first; 3 = also the stores of C evict_first)
   int l2_hints;
+  // 2-CTA kernel: optional [num_sms][12] words of per-CTA timing (ag_trace:: in ag_matmul_common.cuh)
+  uint64_t* trace;
+  // push mode: own 128-row blocks multiplied before the first remote one (-1 = chosen by the launcher)
+  int lead;
 };
 int launch_ag_matmul(const AgMatmulArgs& args, cudaStream_t stream);
 // Same contract on CTA pairs (tcgen05 cta_group::2, 256 x BN tiles); modes 0 and 2 only.

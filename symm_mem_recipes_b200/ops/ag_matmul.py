@@ -56,6 +56,8 @@ class AgMatmulConfig:
     # wave of tiles re-reads B); 2 = also A tiles evict_first (A passes through once); 3 = also the stores
     # of C evict_first
     l2_hints: int = _env_int("SMR_AGMM_L2_HINTS", 0)
+    # push gather: own 128-row blocks multiplied before the first remote one (-1 = the launcher's choice)
+    lead: int = _env_int("SMR_AGMM_LEAD", -1)
     timeout_ms: int = _env_int("SMR_TIMEOUT_MS", 10000)
 
 
@@ -130,6 +132,33 @@ def _check_fp8_config(dtype: torch.dtype, config: "AgMatmulConfig") -> None:
 
 _EPILOGUES = {None: 0, "none": 0, "swiglu": 1}
 
+# the words of one CTA's timing record (csrc/kernels/ag_matmul_common.cuh, namespace ag_trace): stamps are
+# nanoseconds of %globaltimer, the others accumulated nanoseconds
+TRACE_FIELDS = ("start", "entered", "flag_wait", "push", "acc_wait", "tiles_done", "tmem_wait", "operand_wait",
+                "stage_wait", "end", "first_flag_wait", "tiles")
+
+
+def summarize_trace(trace: torch.Tensor) -> dict:
+    """Per-field summary (µs) of a timing record filled by `all_gather_matmul(..., trace=...)`:
+    stamps relative to the earliest kernel entry, waits as mean and maximum over the CTAs that ran."""
+    t = trace.view(-1, len(TRACE_FIELDS)).cpu()
+    t = t[t[:, 0] > 0]
+    if t.numel() == 0:
+        return {}
+    t0 = int(t[:, 0].min())
+    out = {"ctas": int(t.shape[0])}
+    for i, name in enumerate(TRACE_FIELDS):
+        col = t[:, i]
+        if name in ("start", "entered", "tiles_done", "end"):
+            col = col[col > 0] - t0
+            if col.numel():
+                out[name] = {"min": round(float(col.min()) / 1e3, 1), "max": round(float(col.max()) / 1e3, 1)}
+        elif name == "tiles":
+            out[name] = {"min": int(col[col > 0].min()) if (col > 0).any() else 0, "max": int(col.max())}
+        else:
+            out[name] = {"mean": round(float(col.float().mean()) / 1e3, 1), "max": round(float(col.max()) / 1e3, 1)}
+    return out
+
 
 def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor, group: int = 128) -> torch.Tensor:
     """Weight layout for `epilogue="swiglu"`: rows `[g*group, (g+1)*group)` of
@@ -156,7 +185,8 @@ def _epilogue_code(epilogue, dtype: torch.dtype, N: int, config: "AgMatmulConfig
 
 @traced("smr.matmul")
 def matmul(a: torch.Tensor, b: torch.Tensor, c_out: Optional[torch.Tensor] = None,
-           config: AgMatmulConfig = DEFAULT_CONFIG, epilogue: Optional[str] = None) -> torch.Tensor:
+           config: AgMatmulConfig = DEFAULT_CONFIG, epilogue: Optional[str] = None,
+           trace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """C[M, N] = A[M, K] @ B[N, K]^T on the tcgen05 kernel, no communication.
     `epilogue="swiglu"`: see `all_gather_matmul`."""
     _check_2d("a", a)
@@ -171,7 +201,7 @@ def matmul(a: torch.Tensor, b: torch.Tensor, c_out: Optional[torch.Tensor] = Non
     sms = config.num_sms or _num_sms(a.device)
     bn = 256 if epi else (config.block_n or choose_block_n(M, N, sms, config.cta_pair))
     C.ag_matmul(a, b, c_out, 0, None, 0, None, 0, None, None, bn, sms, 0, config.timeout_ms * 1_000_000,
-                config.cta_pair, _tail_buffer(a.device, config), epi, _l2_hints(config, a.dtype, epi))
+                config.cta_pair, _tail_buffer(a.device, config), epi, _l2_hints(config, a.dtype, epi), trace)
     return c_out
 
 
@@ -209,7 +239,8 @@ def gather_buffer(M: int, K: int, device: torch.device, group=None,
 @traced("smr.all_gather_matmul")
 def all_gather_matmul(a_shard: torch.Tensor, b: torch.Tensor, a_out: Optional[torch.Tensor] = None,
                       c_out: Optional[torch.Tensor] = None, config: AgMatmulConfig = DEFAULT_CONFIG,
-                      mm_only: bool = False, group=None, epilogue: Optional[str] = None) -> torch.Tensor:
+                      mm_only: bool = False, group=None, epilogue: Optional[str] = None,
+                      trace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """`a_shard` is this rank's [M/WS, K] rows of A; `b` is [N, K]; returns
     `c_out` [M, N] = all_gather(A) @ B^T and leaves the gathered A in `a_out`.
 
@@ -228,12 +259,15 @@ def all_gather_matmul(a_shard: torch.Tensor, b: torch.Tensor, a_out: Optional[to
     `epilogue="swiglu"`: `b` is `interleave_gate_up(w_gate, w_up)` ([2F, K]) and
     the result is `SiLU(A @ w_gate^T) * (A @ w_up^T)`, [M, F], computed on the
     accumulators before they leave the SM (bf16, push gather or no gather).
+
+    `trace`: an int64 CUDA tensor [num_sms, 12] that receives the per-CTA timing
+    record of the CTA-pair kernel (`TRACE_FIELDS`; push gather or no gather).
     """
     _check_2d("a_shard", a_shard)
     _check_2d("b", b, a_shard.dtype)
     _check_fp8_config(a_shard.dtype, config)
     if mm_only:
-        return matmul(a_out if a_out is not None else a_shard, b, c_out, config, epilogue)
+        return matmul(a_out if a_out is not None else a_shard, b, c_out, config, epilogue, trace)
     rows, K = a_shard.shape
     N = b.shape[0]
     _check_nk(N, K, b, a_shard.dtype)
@@ -245,7 +279,7 @@ def all_gather_matmul(a_shard: torch.Tensor, b: torch.Tensor, a_out: Optional[to
         c_out = torch.empty(M, n_out, dtype=a_shard.dtype, device=a_shard.device)
     if ws == 1:
         # nothing to gather: the shard is the gathered A; copy only on request
-        matmul(a_shard, b, c_out, config, epilogue)
+        matmul(a_shard, b, c_out, config, epilogue, trace)
         if a_out is not None:
             a_out.copy_(a_shard)
         return c_out
@@ -269,7 +303,7 @@ def all_gather_matmul(a_shard: torch.Tensor, b: torch.Tensor, a_out: Optional[to
         _check_gather_geometry(rec.notes, (aout_offset, M, K, a_shard.dtype))
         C.ag_matmul(a_shard, b, c_out, 2, None, 0, hdl.native, aout_offset, a_out, None,
                     bn, sms, n_copy, t_ns, config.cta_pair, _tail_buffer(a_shard.device, config), epi,
-                    _l2_hints(config, a_shard.dtype, epi))
+                    _l2_hints(config, a_shard.dtype, epi), trace, config.lead)
         return c_out
     if config.plain_a_out == "push_copy":
         staged = gather_buffer(M, K, a_shard.device, group, a_shard.dtype)

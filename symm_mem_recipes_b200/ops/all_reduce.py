@@ -165,14 +165,18 @@ def all_reduce(t: torch.Tensor, algo: str = "auto", *,
                config: AllReduceConfig = DEFAULT_ALL_REDUCE) -> torch.Tensor:
     """All-reduce of a symmetric bf16 tensor; the result is returned in `t`
     itself for the in-place algorithms and copied into `t` for one-shot, so the
-    caller always reads the sum from the returned tensor (`t`)."""
+    caller always reads the sum from the returned tensor (`t`).  The ranks that
+    take part are those of the group `t` was rendezvoused on (the default group
+    when this call is its rendezvous)."""
     if algo not in _ALGOS:
         raise SymmMemError(f"algo must be one of {_ALGOS}")
+    hdl = symm_mem.rendezvous(t)
     if algo == "auto":
-        hdl = symm_mem.rendezvous(t)
         algo = choose_algo(t.numel() * t.element_size(), hdl.world_size, hdl.has_multicast, config)
     if algo == "low_latency":
-        return low_latency_all_reduce(t, out=t, config=config)
+        # the inbox workspace belongs to the same group as the tensor: a sub-group's small messages
+        # must not land in the inboxes of the whole world
+        return low_latency_all_reduce(t, out=t, group=hdl.group, config=config)
     if algo == "one_shot":
         one_shot_all_reduce(t, write_back=True, config=config)
         return t

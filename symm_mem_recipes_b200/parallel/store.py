@@ -27,7 +27,8 @@ class StoreExchange:
         self.group = group
         self.rank = dist.get_rank(group)
         self.world_size = dist.get_world_size(group)
-        name = "world" if group is None else getattr(group, "group_name", str(id(group)))
+        name = "world" if group is None or group is dist.group.WORLD else \
+            (getattr(group, "group_name", None) or str(id(group)))
         self.store = dist.PrefixStore(f"{namespace}/{name}", _store_of(group))
         self.timeout = timedelta(seconds=timeout_s)
         self._seq = 0
@@ -39,7 +40,16 @@ class StoreExchange:
         self.store.set(f"{seq}/{self.rank}", pickle.dumps(obj))
         keys = [f"{seq}/{r}" for r in range(self.world_size)]
         self.store.wait(keys, self.timeout)
-        return [pickle.loads(self.store.get(k)) for k in keys]
+        out = [pickle.loads(self.store.get(k)) for k in keys]
+        # Every rank has now read round seq - 2: a rank can only publish round seq after it has
+        # finished reading round seq - 1, and this rank has just seen every rank's round seq.
+        # So this rank's own key of round seq - 2 can go; the Store stays at two rounds per group.
+        if seq >= 2:
+            try:
+                self.store.delete_key(f"{seq - 2}/{self.rank}")
+            except Exception:  # noqa: BLE001 - a Store without delete support just keeps the key
+                pass
+        return out
 
     def barrier(self) -> None:
         self.all_gather(None)

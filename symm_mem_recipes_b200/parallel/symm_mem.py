@@ -77,8 +77,12 @@ def generation() -> int:
     return _generation
 
 
-def _group_key(group) -> int:
-    return 0 if group is None or group is dist.group.WORLD else id(group)
+def _group_key(group):
+    """Cache key of a process group: its name, which torch never hands out twice in one job (the
+    address of a collected group object can be reused by a later one)."""
+    if group is None or group is dist.group.WORLD:
+        return 0
+    return getattr(group, "group_name", None) or id(group)
 
 
 def _group_state(group) -> _GroupState:
@@ -423,7 +427,29 @@ def free(t: torch.Tensor) -> None:
     if rec.handle is not None and rec.handle.world_size > 1 and dist.is_initialized():
         _group_state(rec.handle.group).exchange.barrier()
     _records.pop(rec.base_ptr, None)
+    _drop_cached_views(rec)
     rec.alloc.release()
+
+
+def _op_caches():
+    """The dictionaries in which the ops keep symmetric workspaces between calls."""
+    import importlib
+    for mod, names in (("ag_matmul", ("_gather_buffers",)), ("all_reduce", ("_ll_workspaces",)),
+                       ("gemv_all_reduce", ("_workspaces",)),
+                       ("matmul_reduce_scatter", ("_workspaces", "_ar_outputs"))):
+        m = importlib.import_module(f"symm_mem_recipes_b200.ops.{mod}")
+        for name in names:
+            yield getattr(m, name)
+
+
+def _drop_cached_views(rec: _Record) -> None:
+    """Forget every cached workspace that lives in `rec`: it is about to be unmapped."""
+    lo, hi = rec.base_ptr, rec.base_ptr + max(rec.nbytes, 1)
+    for cache in _op_caches():
+        for key in [k for k, v in cache.items()
+                    if any(isinstance(x, torch.Tensor) and lo <= x.data_ptr() < hi
+                           for x in (v if isinstance(v, (tuple, list)) else (v,)))]:
+            del cache[key]
 
 
 def shutdown() -> None:
@@ -462,13 +488,8 @@ def reset() -> None:
     _shutdown_done = False
     _generation += 1
     # workspaces the ops keep per (shape, group): they point into released allocations
-    import importlib
-    for mod, names in (("ag_matmul", ("_gather_buffers",)), ("all_reduce", ("_ll_workspaces",)),
-                       ("gemv_all_reduce", ("_workspaces",)),
-                       ("matmul_reduce_scatter", ("_workspaces", "_ar_outputs"))):
-        m = importlib.import_module(f"symm_mem_recipes_b200.ops.{mod}")
-        for name in names:
-            getattr(m, name).clear()
+    for cache in _op_caches():
+        cache.clear()
 
 
 _reset_for_tests = reset

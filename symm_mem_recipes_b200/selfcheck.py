@@ -3,7 +3,6 @@ composition or a PyTorch reference, in ONE start-up.
 
     python -m symm_mem_recipes_b200.selfcheck                       # one GPU: world-of-one forms
     torchrun --nnodes 1 --nproc-per-node 2 --master-addr 127.0.0.1 -m symm_mem_recipes_b200.selfcheck
-    ... -m symm_mem_recipes_b200.selfcheck --first-run              # also the variants whose first run is pending
     ... -m symm_mem_recipes_b200.selfcheck --only gemv,glue --list
 
 An installation check for users, and the cheapest way to try many kernel
@@ -40,8 +39,9 @@ _SHARED_STATE: list = []
 _MAX_RECOVERIES = 8
 
 
-def build_checks(first_run: bool, world: int, rank: int, dev: torch.device) -> list:
-    """[(group, name, needs_first_run, fn)]; fn() -> (ok, detail)."""
+def build_checks(world: int, rank: int, dev: torch.device) -> list:
+    """[(group, name, is_variant, fn)]; fn() -> (ok, detail).  `is_variant`: an opt-in variant of an op
+    (run after the default forms)."""
     import symm_mem_recipes_b200 as smr
     from symm_mem_recipes_b200 import ops
     from symm_mem_recipes_b200.models.llama_tp_layer import LlamaTPConfig, LlamaTPDecoderLayer
@@ -52,8 +52,8 @@ def build_checks(first_run: bool, world: int, rank: int, dev: torch.device) -> l
     multi = world > 1
     checks: list = []
 
-    def add(group, name, fn, pending=False):
-        checks.append((group, name, pending, fn))
+    def add(group, name, fn, variant=False):
+        checks.append((group, name, variant, fn))
 
     def randn(*shape, std=0.05, seed=0):
         g = torch.Generator(device="cpu").manual_seed(seed)
@@ -302,13 +302,11 @@ def build_checks(first_run: bool, world: int, rank: int, dev: torch.device) -> l
 
     if dev.type == "cuda":                          # CUDA graphs: nothing to capture on the CPU backend
         add("layer", "decode through one captured CUDA graph", decode_graph, True)
-    # What has run on hardware before goes first; the pending variants follow, the rank-local kernels
-    # before the ones that talk to peers (a fault in one of them would end the process and take the
-    # checks after it along).
+    # The default forms go first; the variants follow, the rank-local kernels before the ones that
+    # talk to peers (a fault in one of them would end the process and take the checks after it along).
     order = {"glue": 0, "all_gather_matmul": 1, "gemv": 2, "barrier": 3, "all_reduce": 4,
              "matmul_reduce_scatter": 5, "matmul_all_reduce": 6, "layer": 7}
-    chosen = [c for c in checks if first_run or not c[2]]
-    return sorted(chosen, key=lambda c: (c[2], order.get(c[0], 8) if c[2] else 0))
+    return sorted(checks, key=lambda c: (c[2], order.get(c[0], 8) if c[2] else 0))
 
 
 def run_checks(checks: list, rank: int, dev: torch.device, only=()) -> tuple:
@@ -319,7 +317,7 @@ def run_checks(checks: list, rank: int, dev: torch.device, only=()) -> tuple:
     from symm_mem_recipes_b200.utils.benchmark import max_over_ranks
 
     results, stop, recoveries = [], False, 0
-    for group, name, pending, fn in checks:
+    for group, name, variant, fn in checks:
         if only and group not in only:
             continue
         t0 = time.monotonic()
@@ -335,7 +333,7 @@ def run_checks(checks: list, rank: int, dev: torch.device, only=()) -> tuple:
         # every rank learns the outcome of every rank
         bad = max_over_ranks(0.0 if ok else 1.0, dev) != 0.0
         stop = max_over_ranks(1.0 if timed_out else 0.0, dev) != 0.0
-        results.append({"group": group, "check": name, "first_run": pending, "ok": not bad,
+        results.append({"group": group, "check": name, "variant": variant, "ok": not bad,
                         "detail": detail if not ok or detail else "", "seconds": round(time.monotonic() - t0, 2)})
         if rank == 0:
             print(f"[{'ok' if not bad else 'FAILED'}] {group}: {name}  {results[-1]['detail']}", flush=True)
@@ -364,8 +362,6 @@ def run_checks(checks: list, rank: int, dev: torch.device, only=()) -> tuple:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("--first-run", action="store_true",
-                    help="include the variants whose first run on hardware is pending")
     ap.add_argument("--only", default="", help="comma-separated groups (all_reduce, barrier, all_gather_matmul, "
                                                "matmul_reduce_scatter, matmul_all_reduce, gemv, glue, layer)")
     ap.add_argument("--list", action="store_true", help="print the checks and exit (no GPU needed)")
@@ -375,9 +371,9 @@ def main(argv=None) -> int:
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     only = {g for g in args.only.split(",") if g}
     if args.list:
-        for group, name, pending, _ in build_checks(True, max(world, 2), 0, torch.device("cpu")):
+        for group, name, variant, _ in build_checks(max(world, 2), 0, torch.device("cpu")):
             if not only or group in only:
-                print(f"{group:24s} {name}{'   [first run pending]' if pending else ''}")
+                print(f"{group:24s} {name}{'   [variant]' if variant else ''}")
         return 0
 
     torch.cuda.set_device(local_rank)
@@ -387,7 +383,7 @@ def main(argv=None) -> int:
         dist.init_process_group("nccl", device_id=dev)
     from symm_mem_recipes_b200.parallel import symm_mem
 
-    results, recoveries, stopped = run_checks(build_checks(args.first_run, world, rank, dev), rank, dev, only)
+    results, recoveries, stopped = run_checks(build_checks(world, rank, dev), rank, dev, only)
     failed = [r for r in results if not r["ok"]]
     if rank == 0:
         print(json.dumps({"op": "selfcheck", "world_size": world, "checks": len(results), "failed": len(failed),

@@ -9,19 +9,13 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs at least one CUDA device (B200)")
     config.addinivalue_line("markers", "multigpu(n): needs at least n CUDA devices")
-    config.addinivalue_line("markers", "first_run: GPU code that compiles for sm_100a but has not yet had its first "
-                                       "run on hardware; skipped unless SMR_TEST_FIRST_RUN=1")
 
 
 def pytest_collection_modifyitems(config, items):
     import torch
 
     n = torch.cuda.device_count() if torch.cuda.is_available() else 0
-    first_run = os.environ.get("SMR_TEST_FIRST_RUN") == "1"
     for item in items:
-        if item.get_closest_marker("first_run") is not None and not first_run:
-            item.add_marker(pytest.mark.skip(reason="awaits its first run on hardware; opt in with "
-                                                    "SMR_TEST_FIRST_RUN=1"))
         m = item.get_closest_marker("multigpu")
         if m is not None:
             need = int(m.args[0]) if m.args else 2

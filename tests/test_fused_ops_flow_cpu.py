@@ -25,7 +25,7 @@ def _install_host_kernels():
 
         @staticmethod
         def ag_matmul(a, b, c, mode, shard_alloc, shard_offset, aout_alloc, aout_offset, a_out, flags, block_n,
-                      num_sms, n_copy, timeout_ns, cta_pair=False, tail_scratch=None, epilogue=0, l2_hints=0):
+                      num_sms, n_copy, timeout_ns, cta_pair=False, tail_scratch=None, epilogue=0, l2_hints=0, trace=None, lead=-1):
             calls.append(mode)
             if mode == 2:
                 ws, rank = dist.get_world_size(), dist.get_rank()
@@ -383,7 +383,7 @@ def _selfcheck_worker(rank, world_size):
 
     _install_all_stand_ins()
 
-    checks = [c for c in selfcheck.build_checks(True, world_size, rank, torch.device("cpu"))
+    checks = [c for c in selfcheck.build_checks(world_size, rank, torch.device("cpu"))
               if not ((c[0] == "barrier" and "barrier" in c[1].lower()) or "NVLS" in c[1])]   # GPU-only kernels
     results, recoveries, stopped = selfcheck.run_checks(checks, rank, torch.device("cpu"))
     failures = [f"{r['group']}: {r['check']}: {r['detail']}" for r in results if not r["ok"]]

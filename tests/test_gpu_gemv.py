@@ -69,9 +69,8 @@ def test_gemv_all_reduce_8gpu():
     spawn_ranks(_gemv_worker, 8, "nccl", (16, 3584, 8192))
 
 
-# The tagged-word exchange of the tcgen05 kernel: compiled, first run on hardware pending.
+# The tagged-word exchange of the tcgen05 kernel.
 @pytest.mark.gpu
-@pytest.mark.first_run
 @pytest.mark.parametrize("B,K,N", [(1, 512, 256), (4, 3584, 8192), (16, 3584, 8192), (3, 1000, 328)])
 def test_gemv_tagged_world_of_one(B, K, N):
     torch.cuda.set_device(0)
@@ -79,7 +78,6 @@ def test_gemv_tagged_world_of_one(B, K, N):
 
 
 @pytest.mark.gpu
-@pytest.mark.first_run
 @pytest.mark.multigpu(2)
 @pytest.mark.parametrize("B", [1, 4, 16])
 def test_gemv_tagged_2gpu(B):
@@ -106,7 +104,6 @@ def _gemv_nk_worker(rank, world_size, B, K, N, algo):
 
 
 @pytest.mark.gpu
-@pytest.mark.first_run
 @pytest.mark.parametrize("algo", ["tc", "tc_tagged"])
 @pytest.mark.parametrize("B,K,N", [(1, 512, 256), (4, 3584, 8192), (3, 1000, 328)])
 def test_gemv_weights_nk_world_of_one(B, K, N, algo):
@@ -115,7 +112,6 @@ def test_gemv_weights_nk_world_of_one(B, K, N, algo):
 
 
 @pytest.mark.gpu
-@pytest.mark.first_run
 @pytest.mark.multigpu(2)
 def test_gemv_weights_nk_2gpu():
     spawn_ranks(_gemv_nk_worker, 2, "nccl", (4, 3584, 8192, "tc"))

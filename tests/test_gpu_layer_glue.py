@@ -1,13 +1,10 @@
 """RMSNorm, rotary embedding and SiLU-mul kernels against their CPU oracles
 (same rounding points) and, through the decoder layer, against fp32.
-
-Marked `first_run`: compiled for sm_100a, CPU oracles tested, first run on
-hardware pending (opt in with SMR_TEST_FIRST_RUN=1).
 """
 import pytest
 import torch
 
-pytestmark = [pytest.mark.gpu, pytest.mark.first_run]
+pytestmark = [pytest.mark.gpu]
 
 
 def _ulp_close(got, ref, extra_abs=1e-6):

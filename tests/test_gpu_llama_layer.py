@@ -111,7 +111,6 @@ def _layer_tp_worker(rank, world_size, fused_glue, fused_swiglu):
 
 
 @pytest.mark.gpu
-@pytest.mark.first_run
 @pytest.mark.multigpu(2)
 @pytest.mark.parametrize("fused_glue,fused_swiglu", [(False, False), (True, True)])
 def test_layer_tensor_parallel_prefill_2gpu(fused_glue, fused_swiglu):
@@ -154,7 +153,6 @@ def _decode_graph_worker(rank, world_size, fused_glue):
 
 
 @pytest.mark.gpu
-@pytest.mark.first_run
 @pytest.mark.parametrize("fused_glue", [False, True])
 def test_decode_graph_world_of_one(fused_glue):
     torch.cuda.set_device(0)
@@ -162,7 +160,6 @@ def test_decode_graph_world_of_one(fused_glue):
 
 
 @pytest.mark.gpu
-@pytest.mark.first_run
 @pytest.mark.multigpu(2)
 @pytest.mark.parametrize("fused_glue", [False, True])
 def test_decode_graph_2gpu(fused_glue):
@@ -210,14 +207,12 @@ def _stack_worker(rank, world_size):
 
 
 @pytest.mark.gpu
-@pytest.mark.first_run
 def test_stack_prefill_then_graph_decode_world_of_one():
     torch.cuda.set_device(0)
     _stack_worker(0, 1)
 
 
 @pytest.mark.gpu
-@pytest.mark.first_run
 @pytest.mark.multigpu(2)
 def test_stack_prefill_then_graph_decode_2gpu():
     spawn_ranks(_stack_worker, 2, "nccl")

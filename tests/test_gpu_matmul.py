@@ -38,7 +38,6 @@ def test_matmul_small(block_n, shape, cta_pair):
 
 
 @pytest.mark.gpu
-@pytest.mark.first_run
 @pytest.mark.parametrize("level", [1, 2, 3])
 @pytest.mark.parametrize("block_n,shape", [(256, (640, 1000, 1024)), (224, (200, 328, 96)), (128, (2048, 3584, 512))])
 def test_matmul_l2_hints_change_nothing_but_the_cache_policy(level, block_n, shape):
@@ -183,7 +182,6 @@ def test_all_gather_matmul_8gpu():
 
 
 @pytest.mark.gpu
-@pytest.mark.first_run
 @pytest.mark.multigpu(2)
 @pytest.mark.parametrize("rows,N,K", [(256, 512, 1024), (2048, 3584, 8192)])
 def test_all_gather_matmul_plain_a_out_by_push_and_copy_2gpu(rows, N, K):

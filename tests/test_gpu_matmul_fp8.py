@@ -2,17 +2,14 @@
 follows `a_shard`, as upstream's FP8_OUTPUT switch does,
 symm_mem_recipes/triton_all_gather_matmul.py:123, 311).
 
-The fp8 instantiations of the CTA-pair kernel have been compiled for sm_100a
-but have not yet had a first run on hardware, so these tests carry the
-`first_run` marker (opt in with SMR_TEST_FIRST_RUN=1).  Every case runs in a
-child process.
+Every case runs in a child process.
 """
 import pytest
 import torch
 
 from symm_mem_recipes_b200.utils.testing import spawn_ranks
 
-pytestmark = [pytest.mark.gpu, pytest.mark.first_run]
+pytestmark = [pytest.mark.gpu]
 
 FP8 = torch.float8_e4m3fn
 

@@ -56,11 +56,10 @@ def test_matmul_reduce_scatter_2gpu(M, N, K):
     spawn_ranks(_rs_worker, 2, "nccl", (M, N, K))
 
 
-# Variants compiled for sm_100a whose first run on hardware is pending (SMR_TEST_FIRST_RUN=1 opts in).
+# The kernel variants.
 # (768, 328, 192) at 2 ranks: 3 row blocks per rank, so a CTA pair straddles two destinations and the
 # N edge is ragged; (384, 256, 128) at WS 3 would give an odd block count, which needs 3 GPUs.
 @pytest.mark.gpu
-@pytest.mark.first_run
 @pytest.mark.multigpu(2)
 @pytest.mark.parametrize("variant", ["cta_pair", "deep_strips", "thread_stores", "cta_pair,thread_stores"])
 @pytest.mark.parametrize("M,N,K", [(256, 256, 128), (768, 328, 192), (4096, 8192, 1024)])
@@ -118,7 +117,6 @@ def _ar_worker(rank, world_size, M, N, K, cta_pair):
 
 
 @pytest.mark.gpu
-@pytest.mark.first_run
 @pytest.mark.multigpu(2)
 @pytest.mark.parametrize("cta_pair", [False, True])
 @pytest.mark.parametrize("M,N,K", [(256, 256, 128), (768, 328, 192), (4096, 8192, 1024)])

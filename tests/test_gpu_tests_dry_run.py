@@ -144,7 +144,7 @@ FUNCTIONS = [
     ("test_gpu_layer_glue", "test_layer_with_fused_swiglu_matches_fp32", {}),
     ("test_gpu_layer_glue", "test_matmul_with_swiglu_epilogue", {"M": 200, "F": 384, "K": 96}),
     ("__graft_entry__", "smoke", {}),                  # the smoke check that runs on a GPU before the benchmark
-    ("symm_mem_recipes_b200.selfcheck", "main", {"argv": ["--first-run"]}),     # the one-GPU form of the self-check
+    ("symm_mem_recipes_b200.selfcheck", "main", {"argv": []}),     # the one-GPU form of the self-check
     # the single-GPU tests that run at every GPU test pass
     ("test_gpu_symm_mem", "test_world_of_one_all_paths", {}),
     ("test_gpu_gemv", "test_gemv_world_of_one", {"B": 3, "K": 1000, "N": 328, "algo": "tc"}),
@@ -159,39 +159,3 @@ FUNCTIONS = [
                          ids=[f"{m}.{n}{i}" for i, (m, n, _) in enumerate(FUNCTIONS)])
 def test_gpu_test_function_runs_on_the_cpu(module, name, kwargs):
     spawn_ranks(_dry, 1, "gloo", (module, name, kwargs, True), timeout_s=240.0)
-
-
-# first-run tests whose code cannot run on the CPU harness, each with the reason
-NOT_DRY_RUN = {
-    "test_counting_barriers_2gpu": "needs an NVLink multicast mapping",
-    "test_rank_leaving_between_steps_is_noticed_before_the_next_launch": "NCCL process-group timeouts",
-    "test_matmul_fp8_small": "same worker as test_matmul_fp8_split_k_tail (covered through _mm_worker)",
-}
-
-
-def test_every_first_run_test_is_exercised_here():
-    """A GPU test that has never run on hardware should at least have run on the CPU harness: every
-    test marked `first_run` either appears in the tables above (itself or the worker it spawns) or
-    is listed in NOT_DRY_RUN with the reason."""
-    import ast
-    import pathlib
-
-    covered = {w for _, w, _, _ in WORKERS} | {n for _, n, _ in FUNCTIONS}
-    missing = []
-    for path in sorted(pathlib.Path(__file__).parent.glob("test_gpu_*.py")):
-        if path.name == pathlib.Path(__file__).name:
-            continue
-        tree = ast.parse(path.read_text())
-        module_first_run = "first_run" in ast.unparse(next(
-            (n for n in tree.body if isinstance(n, ast.Assign) and any(
-                isinstance(t, ast.Name) and t.id == "pytestmark" for t in n.targets)), ast.Pass()))
-        for node in tree.body:
-            if not (isinstance(node, ast.FunctionDef) and node.name.startswith("test_")):
-                continue
-            marked = module_first_run or any("first_run" in ast.unparse(d) for d in node.decorator_list)
-            if not marked or node.name in NOT_DRY_RUN:
-                continue
-            used = {n.id for n in ast.walk(node) if isinstance(n, ast.Name)} | {node.name}
-            if not used & covered:
-                missing.append(f"{path.name}::{node.name}")
-    assert not missing, missing

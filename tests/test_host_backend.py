@@ -235,6 +235,10 @@ def _signal_worker(rank, world_size):
         assert float(got[0]) == float(100 * it + prv) and float(got[-1]) == float(100 * it + prv)
         hdl.barrier(channel=1)                 # nobody overwrites before everybody has read
     assert int(hdl.get_signal_pad().abs().sum()) == 0          # every signal was consumed
+    # a rendezvous that does not touch the pad: a fast rank's next pad barrier would otherwise raise
+    # a slot on a rank that is still summing its pad above
+    import torch.distributed as dist
+    dist.barrier()
     flags = torch.zeros(4, dtype=torch.int32)
     hdl.stream_write_value32(flags, 2, 7)
     assert flags.tolist() == [0, 0, 7, 0]
