@@ -42,6 +42,10 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--multimem-sweep", action="store_true",
                     help="instead of the size sweep: the multimem kernel over CTA counts, unroll factors and both "
                          "barrier kinds at 16, 64 and 256 MiB (clamped to --max-bytes), one start-up")
+    ap.add_argument("--one-shot-sweep", action="store_true",
+                    help="instead of the size sweep: the one-shot kernel over its launch knobs (CTAs, threads, "
+                         "vectors per thread, barrier kind, rotated walk) at 4 KiB, 64 KiB, 1 MiB and 8 MiB, each "
+                         "variant first compared bit for bit with the default one")
     return ap
 
 
@@ -127,6 +131,63 @@ def main(argv=None, standalone: bool = True) -> int:
             s = json.dumps(rec)
             print(s, flush=True)
             lines.append(s)
+
+    if args.one_shot_sweep:
+        import itertools
+
+        def variants(nbytes):
+            if nbytes <= 64 * 1024:          # latency: the barrier and the CTA shape
+                for barrier, threads in itertools.product((0, 1, 2), (256, 512)):
+                    yield dict(one_shot_barrier=barrier, one_shot_threads=threads, one_shot_max_blocks=32)
+            else:                            # bandwidth: loads in flight
+                for barrier, blocks, unroll, rotate in itertools.product((0, 2), (24, 32, 64, 128), (1, 2), (0, 1)):
+                    yield dict(one_shot_barrier=barrier, one_shot_max_blocks=blocks, one_shot_unroll=unroll,
+                               one_shot_rotate=rotate, one_shot_threads=512)
+                for blocks, unroll in itertools.product((64, 128, 192), (1, 2)):
+                    yield dict(one_shot_barrier=0, one_shot_max_blocks=blocks, one_shot_unroll=unroll,
+                               one_shot_rotate=1, one_shot_threads=256)
+
+        for nbytes in (4096, 65536, 1 << 20, 8 << 20):
+            if nbytes > args.max_bytes:
+                continue
+            t = buf[:nbytes // 2]
+            out = torch.empty_like(t)
+            hdl.barrier()
+            want = smr.one_shot_all_reduce(t, exit_barrier=True).clone()
+            if ref_fn is not None and nbytes // 2 <= ref_buf.numel():
+                rt = ref_buf[:nbytes // 2]
+                us = benchmark_with_graph(lambda: ref_fn(rt), calls_per_graph=20, warmup_iters=5, replays=10)
+                emit({"op": "all_reduce_one_shot_sweep", "impl": "reference_triton", "world_size": world,
+                      "bytes": nbytes, "us": round(us, 2)})
+            us = benchmark_with_graph(lambda: dist.all_reduce(plain[:nbytes // 2]), calls_per_graph=20,
+                                      warmup_iters=5, replays=10)
+            emit({"op": "all_reduce_one_shot_sweep", "impl": "nccl", "world_size": world, "bytes": nbytes,
+                  "us": round(us, 2)})
+            for knobs in variants(nbytes):
+                def one(knobs=knobs, t=t, out=out, nbytes=nbytes, want=want):
+                    c = AllReduceConfig(**knobs)
+                    smr.one_shot_all_reduce(t, out=out, exit_barrier=True, config=c)
+                    hdl.check()
+                    same = bool(torch.equal(out, want))
+                    us = benchmark_with_graph(lambda: smr.one_shot_all_reduce(t, out=out, config=c),
+                                              calls_per_graph=20, warmup_iters=5, replays=10)
+                    hdl.check()
+                    emit({"op": "all_reduce_one_shot_sweep", "impl": "one_shot", "world_size": world,
+                          "bytes": nbytes, **{k.replace("one_shot_", ""): v for k, v in knobs.items()},
+                          "same_bits_as_default": same, "us": round(us, 2),
+                          "bus_gbs": round(2 * (world - 1) / world * nbytes / us / 1e3, 1)})
+
+                if not attempt(f"one-shot sweep: {nbytes} bytes, {knobs}", one, dev, emit):
+                    if not symm_mem.is_symm_mem_tensor(buf):
+                        break
+            if not symm_mem.is_symm_mem_tensor(buf):
+                break
+        if args.out and rank == 0:
+            with open(args.out, "a") as f:
+                f.write("\n".join(lines) + "\n")
+        if standalone:
+            finish()
+        return 0
 
     if args.multimem_sweep:
         if world > 1 and hdl.has_multicast:

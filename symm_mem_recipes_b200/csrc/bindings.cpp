@@ -410,17 +410,23 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   });
   m.def("one_shot_all_reduce", [](const std::shared_ptr<CudaSymmAllocation>& a, int64_t offset_bytes,
                                   torch::Tensor out, int64_t numel, int max_blocks, bool exit_barrier,
-                                  uint64_t timeout_ns, bool write_back, bool stagger) {
+                                  uint64_t timeout_ns, bool write_back, int threads, int unroll, int barrier,
+                                  bool rotate) {
     TORCH_CHECK(out.is_cuda() && out.is_contiguous() && out.scalar_type() == torch::kBFloat16 &&
                 out.numel() == numel, "bad output tensor");
     c10::cuda::CUDAGuard guard(a->device());
+    OneShotTuning tune;
+    tune.threads = threads;
+    tune.unroll = unroll;
+    tune.barrier = barrier;
+    tune.rotate = rotate;
     rt_check(launch_one_shot_all_reduce(view_of(*a), (size_t)offset_bytes, out.data_ptr(), (size_t)numel,
-                                        max_blocks, exit_barrier, write_back, stagger, timeout_ns,
+                                        max_blocks, exit_barrier, write_back, tune, timeout_ns,
                                         status_for(a->device()), current_stream(a->device())),
              "one_shot_all_reduce");
   }, py::arg("alloc"), py::arg("offset_bytes"), py::arg("out"), py::arg("numel"), py::arg("max_blocks"),
      py::arg("exit_barrier"), py::arg("timeout_ns"), py::arg("write_back") = false,
-     py::arg("stagger") = true);
+     py::arg("threads") = 512, py::arg("unroll") = 1, py::arg("barrier") = 0, py::arg("rotate") = false);
   m.def("ll_all_reduce_workspace_bytes", &ll_all_reduce_workspace_bytes);
   m.def("ll_all_reduce", [](const std::shared_ptr<CudaSymmAllocation>& workspace, torch::Tensor in,
                             torch::Tensor out, int64_t capacity_numel, int max_blocks, uint64_t timeout_ns) {
@@ -463,7 +469,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                         c10::optional<torch::Tensor> a_out, c10::optional<torch::Tensor> flags,
                         int block_n, int num_sms, int n_copy, uint64_t timeout_ns, bool cta_pair,
                         c10::optional<torch::Tensor> tail_scratch, int epilogue, int l2_hints,
-                        c10::optional<torch::Tensor> trace, int lead) {
+                        c10::optional<torch::Tensor> trace, int lead, int push_ahead, int push_spread) {
     const auto dtype = a.scalar_type();
     const bool fp8 = dtype == at::kFloat8_e4m3fn;
     TORCH_CHECK(fp8 || dtype == torch::kBFloat16, "a must be bfloat16 or float8_e4m3fn");
@@ -543,6 +549,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       args.tail_scratch_bytes = tail_scratch->nbytes() - 4096;
     }
     args.lead = lead;
+    args.push_ahead = push_ahead;
+    args.push_spread = push_spread;
     if (trace.has_value()) {
       TORCH_CHECK(cta_pair && mode != 1, "the timing record belongs to the CTA-pair kernel");
       TORCH_CHECK(trace->is_cuda() && trace->get_device() == dev && trace->is_contiguous() &&
@@ -556,7 +564,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
      py::arg("shard_offset"), py::arg("aout_alloc"), py::arg("aout_offset"), py::arg("a_out"),
      py::arg("flags"), py::arg("block_n"), py::arg("num_sms"), py::arg("n_copy"), py::arg("timeout_ns"),
      py::arg("cta_pair") = false, py::arg("tail_scratch") = py::none(), py::arg("epilogue") = 0,
-     py::arg("l2_hints") = 0, py::arg("trace") = py::none(), py::arg("lead") = -1);
+     py::arg("l2_hints") = 0, py::arg("trace") = py::none(), py::arg("lead") = -1,
+     py::arg("push_ahead") = 0, py::arg("push_spread") = 0);
 
   m.def("check_push_schedule", &check_push_schedule);
   m.def("check_pair_work", &check_pair_work);

@@ -67,6 +67,12 @@ __device__ __forceinline__ uint32_t cas_acquire_sys(uint32_t* p, uint32_t cmp, u
                : "=r"(old) : "l"(p), "r"(cmp), "r"(val) : "memory");
   return old;
 }
+__device__ __forceinline__ uint32_t cas_relaxed_sys(uint32_t* p, uint32_t cmp, uint32_t val) {
+  uint32_t old;
+  asm volatile("atom.global.relaxed.sys.cas.b32 %0, [%1], %2, %3;"
+               : "=r"(old) : "l"(p), "r"(cmp), "r"(val) : "memory");
+  return old;
+}
 __device__ __forceinline__ void fence_acq_rel_sys() {
   asm volatile("fence.acq_rel.sys;" ::: "memory");
 }

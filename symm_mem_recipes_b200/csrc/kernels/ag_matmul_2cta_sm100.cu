@@ -288,7 +288,7 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
       if (p.mode == 2) {
         const uint64_t t0 = trt ? globaltimer_ns() : 0;
         next_piece = push_pieces(p, next_piece, (int)gridDim.x,
-                                 pieces_needed_through_round(p, round + 1, n_pairs, 2), etid);
+                                 pieces_due(p, round, n_pairs, 2, all_pieces), etid);
         ++round;
         if (trt) t_push += globaltimer_ns() - t0;
       }
@@ -590,6 +590,7 @@ int launch_ag_matmul_2cta(const AgMatmulArgs& a, cudaStream_t stream) {
   if (comm) {
     p.lead = p.blocks_per_rank < 4 ? p.blocks_per_rank : 4;
     if (a.lead >= 0) p.lead = a.lead < p.blocks_per_rank ? a.lead : p.blocks_per_rank;
+    p.push_ahead = a.push_ahead > 0 ? a.push_ahead : 2;
     size_t block_vecs = (size_t)kBM * a.K * es / 16;
     p.pieces = block_vecs >= 8192 ? 16 : (block_vecs >= 1024 ? 4 : 1);
   }
@@ -622,6 +623,11 @@ int launch_ag_matmul_2cta(const AgMatmulArgs& a, cudaStream_t stream) {
   if (pairs > total_tiles) pairs = total_tiles;
   if (pairs < 1) return cudaErrorInvalidValue;
   const int grid = 2 * pairs;
+  if (comm) {
+    const int n_rounds = (total_tiles + pairs - 1) / pairs;
+    // by default the whole shard is on the wire by the middle of the kernel
+    p.push_spread = a.push_spread > 0 ? a.push_spread : (n_rounds / 2 > 1 ? n_rounds / 2 : 1);
+  }
   // the entry barrier of CTA i uses block slot (barrier_block_base + i): it must stay inside the block-slot region
   if (comm && ((size_t)a.barrier_block_base + grid) * a.world_size > kBlockSlots) return cudaErrorInvalidValue;
   // split-K tail: only when the last wave fills less than half of the pairs

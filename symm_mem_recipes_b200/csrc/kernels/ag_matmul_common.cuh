@@ -47,6 +47,8 @@ struct AgMatmulParams {
   int mode;              // 0 none, 1 pull, 2 push
   int lead;              // own blocks scheduled before the first remote one
   int pieces;            // push: pieces per 128-row block (arrivals per block and call)
+  int push_ahead;        // push: rounds of tiles by which the broadcast runs ahead of the first need (>= 1)
+  int push_spread;       // push: rounds over which the whole shard is broadcast at the latest
   uint32_t* flags;       // [n_blocks_m] arrival flags read by the GEMM CTAs (local memory)
   uint32_t flag_target;  // pull: 1 (flags zeroed before launch); push: filled from the epoch
   uint32_t* header;      // push: [0] epoch, [1] CTAs done (local, in the a_out signal pad)
@@ -215,6 +217,22 @@ __host__ __device__ __forceinline__ int pieces_needed_through_round(const AgMatm
   int k_max = q < full * ws ? q / ws : full + (q - full * ws) / (ws - 1);
   if (k_max >= bpr) k_max = bpr - 1;
   return (k_max + 1) * p.pieces;
+}
+
+// Pieces of the own shard that should be on the wire once round `round` begins.  Never less
+// than the schedule needs (`pieces_needed_through_round(round + 1)`: nobody can then block on a
+// piece that a blocked CTA still holds), and beyond that ahead of the need: `push_ahead` rounds
+// of lookahead absorb a rank that entered the kernel late, and an even spread over
+// `push_spread` rounds keeps the epilogue warps' share of every round short when the shard is
+// large (few ranks).
+__host__ __device__ __forceinline__ int pieces_due(const AgMatmulParams& p, int round, int n_units,
+                                                   int pos_per_tile, int all_pieces) {
+  int due = pieces_needed_through_round(p, round + (p.push_ahead > 1 ? p.push_ahead : 1), n_units, pos_per_tile);
+  if (p.push_spread > 0) {
+    long long even = ((long long)(round + 1) * all_pieces + p.push_spread - 1) / p.push_spread;
+    if (even > due) due = (int)even;
+  }
+  return due < all_pieces ? due : all_pieces;
 }
 
 // The i-th piece of work of a CTA pair in the 2-CTA kernel: a whole tile, or

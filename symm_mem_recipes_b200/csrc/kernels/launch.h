@@ -39,11 +39,16 @@ int launch_wait_flag(const uint32_t* flag, uint32_t target, uint64_t timeout_ns,
 
 // ---- all-reduce (bf16) -----------------------------------------------------
 // `offset_bytes` is the offset of the tensor inside the symmetric payload.
-// `stagger`: rank r issues its peer loads starting at rank r+1 (else at rank 0, as upstream).
 // `write_back` (needs exit_barrier): after the exit barrier the sum also replaces this
 // rank's symmetric input, i.e. the in-place form used by the dispatcher.
+struct OneShotTuning {
+  int threads = 512;    // per CTA: 128, 256 or 512
+  int unroll = 1;       // 16-byte vectors per thread and iteration (1, 2, 4; unroll x WS <= 16)
+  int barrier = 0;      // 0 CAS (upstream's protocol), 1 CAS with split sender / waiter threads, 2 epoch barrier
+  bool rotate = false;  // rank r starts its walk at r / WS of the buffer
+};
 int launch_one_shot_all_reduce(const PeerView& pv, size_t offset_bytes, void* out, size_t numel,
-                               int max_blocks, bool exit_barrier, bool write_back, bool stagger,
+                               int max_blocks, bool exit_barrier, bool write_back, const OneShotTuning& tune,
                                uint64_t timeout_ns, Status* status, cudaStream_t stream);
 // Low-latency (push, tagged words) all-reduce for small messages.  `pv` is the view of a
 // symmetric workspace of ll_all_reduce_workspace_bytes(capacity_numel, WS); `in` / `out` are
@@ -108,6 +113,10 @@ struct AgMatmulArgs {
   uint64_t* trace;
   // push mode: own 128-row blocks multiplied before the first remote one (-1 = chosen by the launcher)
   int lead;
+  // push mode pacing (0 = the launcher's choice): rounds of lookahead of the broadcast over the
+  // first need, and the number of rounds over which the whole shard is broadcast at the latest
+  int push_ahead;
+  int push_spread;
 };
 int launch_ag_matmul(const AgMatmulArgs& args, cudaStream_t stream);
 // Same contract on CTA pairs (tcgen05 cta_group::2, 256 x BN tiles); modes 0 and 2 only.

@@ -58,6 +58,10 @@ class AgMatmulConfig:
     l2_hints: int = _env_int("SMR_AGMM_L2_HINTS", 0)
     # push gather: own 128-row blocks multiplied before the first remote one (-1 = the launcher's choice)
     lead: int = _env_int("SMR_AGMM_LEAD", -1)
+    # push gather pacing (0 = the launcher's choice): rounds of tiles by which the broadcast runs ahead of the
+    # first need, and rounds over which the whole shard is on the wire at the latest
+    push_ahead: int = _env_int("SMR_AGMM_PUSH_AHEAD", 0)
+    push_spread: int = _env_int("SMR_AGMM_PUSH_SPREAD", 0)
     timeout_ms: int = _env_int("SMR_TIMEOUT_MS", 10000)
 
 
@@ -303,7 +307,8 @@ def all_gather_matmul(a_shard: torch.Tensor, b: torch.Tensor, a_out: Optional[to
         _check_gather_geometry(rec.notes, (aout_offset, M, K, a_shard.dtype))
         C.ag_matmul(a_shard, b, c_out, 2, None, 0, hdl.native, aout_offset, a_out, None,
                     bn, sms, n_copy, t_ns, config.cta_pair, _tail_buffer(a_shard.device, config), epi,
-                    _l2_hints(config, a_shard.dtype, epi), trace, config.lead)
+                    _l2_hints(config, a_shard.dtype, epi), trace, config.lead, config.push_ahead,
+                    config.push_spread)
         return c_out
     if config.plain_a_out == "push_copy":
         staged = gather_buffer(M, K, a_shard.device, group, a_shard.dtype)

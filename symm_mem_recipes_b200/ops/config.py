@@ -37,8 +37,13 @@ class AllReduceConfig:
     multimem_nvls_barrier: int = _env_int("SMR_AR_NVLS_BARRIER", 0)
     # multimem kernel: in-switch reductions in flight per thread (4, 8 or 16)
     multimem_unroll: int = _env_int("SMR_AR_MULTIMEM_UNROLL", 8)
-    # one-shot: rank r starts its peer loads at rank r+1 (0 = every rank starts at rank 0, as upstream)
-    one_shot_stagger: int = _env_int("SMR_AR_ONE_SHOT_STAGGER", 1)
+    # one-shot kernel: threads per CTA (128, 256, 512), 16-byte vectors per thread and iteration (1, 2, 4),
+    # barrier (0 = CAS protocol as upstream, 1 = the same with split sender / waiter threads, 2 = epoch
+    # barrier), and whether rank r starts its walk over the buffer at r / WS of it
+    one_shot_threads: int = _env_int("SMR_AR_ONE_SHOT_THREADS", 512)
+    one_shot_unroll: int = _env_int("SMR_AR_ONE_SHOT_UNROLL", 1)
+    one_shot_barrier: int = _env_int("SMR_AR_ONE_SHOT_BARRIER", 0)
+    one_shot_rotate: int = _env_int("SMR_AR_ONE_SHOT_ROTATE", 0)
     timeout_ms: int = _env_int("SMR_TIMEOUT_MS", 10000)
 
 

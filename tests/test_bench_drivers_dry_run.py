@@ -112,7 +112,8 @@ def _agmm_worker(rank, world_size, out_path):
     from symm_mem_recipes_b200.bench import all_gather_matmul
 
     _run(all_gather_matmul.main, ["--M", "512", "--N", "256", "--K", "128", "--warmup", "1", "--iters", "1",
-                                  "--copy-ctas", "4", "--with-push-copy"], rank, out_path)
+                                  "--copy-ctas", "4", "--with-push-copy", "--per-rank", "--leads", "1,2"],
+         rank, out_path)
 
 
 def _gemv_worker(rank, world_size, out_path):
@@ -181,7 +182,8 @@ def test_all_gather_matmul_driver(tmp_path):
     recs = _records(out)
     impls = [(r["impl"], r.get("gather")) for r in recs]
     assert impls == [("cublas_mm_only", None), ("smr_mm_only", None), ("cublas_plus_nccl", None),
-                     ("nccl_all_gather_only", None), ("smr_fused", "push"), ("smr_fused", "pull"),
+                     ("nccl_all_gather_only", None), ("smr_fused", "push"), ("smr_fused", "push"),
+                     ("smr_fused", "push"), ("smr_fused", "pull"),
                      ("smr_fused", "push_copy")]
 
 
@@ -198,6 +200,22 @@ def _all_reduce_worker(rank, world_size, out_path):
 
     _run(all_reduce.main, ["--min-bytes", "4096", "--max-bytes", "65536", "--warmup", "1", "--iters", "1"],
          rank, out_path)
+
+
+def _one_shot_sweep_worker(rank, world_size, out_path):
+    _prepare(rank, world_size)
+    from symm_mem_recipes_b200.bench import all_reduce
+
+    _run(all_reduce.main, ["--one-shot-sweep", "--max-bytes", "1048576"], rank, out_path)
+
+
+def test_one_shot_sweep_driver(tmp_path):
+    out = tmp_path / "sweep.txt"
+    spawn_ranks(_one_shot_sweep_worker, 2, "gloo", (str(out),), timeout_s=180.0)
+    recs = [r for r in _records(out) if r["op"] == "all_reduce_one_shot_sweep"]
+    ours = [r for r in recs if r["impl"] == "one_shot"]
+    assert {r["bytes"] for r in ours} == {4096, 65536, 1 << 20} and all(r["same_bits_as_default"] for r in ours)
+    assert {"barrier", "max_blocks"} <= set(ours[0]) and any(r["impl"] == "nccl" for r in recs)
 
 
 def test_all_reduce_driver(tmp_path):
