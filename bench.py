@@ -19,9 +19,17 @@ synchronize on both sides of the timed region; maximum over ranks.
 the host-to-device copy of the step's A shard from pinned memory and a
 device-to-host read of a checksum of C.  `same_box_baseline` is the library
 composition (NCCL all-gather + cuBLAS) timed the same way in the same run.
-`--e2e-pipelined` adds `e2e_pipelined`: the same end-to-end step fed the way a
-serving loop feeds it, the next step's host-to-device copy running on a copy
-stream under the current step's kernel (two shard buffers).
+`e2e` is that step fed the way a serving loop feeds it: two shard buffers, the
+next step's host-to-device copy on a copy stream under the current step's
+kernel; `e2e_serial` is the same step with copy, kernel and read-back strictly
+one after the other.
+
+At N > 1 the line also carries the other half of the metric (extra keys, each
+gated by its own check against NCCL): `all_reduce` (µs and bus GB/s at 4 KiB,
+64 KiB, 1 MiB and 64 MiB for `all_reduce(auto)`, `one_shot_all_reduce`, NCCL and
+the upstream Triton one-shot kernel, unmodified, where it loads) and
+`gemv_all_reduce` (fused GEMV + all-reduce against cuBLAS + NCCL at batch 1, 4
+and 16, Llama-3-70B down-projection shard).  `--no-extras` leaves them out.
 """
 from __future__ import annotations
 
@@ -45,11 +53,115 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--e2e-pipelined", action="store_true",
-                    help="also time the end-to-end step with the next step's host-to-device copy running on a "
-                         "copy stream under the current step's kernel (two shard buffers); reported as "
-                         "e2e_pipelined beside the serial e2e")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="N > 1: skip the all-reduce and GEMV + all-reduce sections")
     return ap.parse_args()
+
+
+def all_reduce_section(world, rank, dev):
+    """µs (device time, maximum over ranks) and bus GB/s of the all-reduce kernels at four sizes,
+    beside NCCL and the upstream Triton kernel on the same box.  Graph replay up to 1 MiB (the
+    eager number would be CPU launch cost), CUDA events at 64 MiB."""
+    import symm_mem_recipes_b200 as smr
+    from symm_mem_recipes_b200.parallel import symm_mem
+    from symm_mem_recipes_b200.utils.benchmark import benchmark_with_event, benchmark_with_graph
+
+    sizes = [4096, 65536, 1 << 20, 64 << 20]
+    buf = symm_mem.empty(sizes[-1] // 2, dtype=torch.bfloat16, device=dev)
+    hdl = symm_mem.rendezvous(buf)
+    torch.manual_seed(1234 + rank)
+    plain = torch.randn(sizes[-1] // 2, device=dev).to(torch.bfloat16)
+    ref_fn = ref_buf = None
+    ref_note = None
+    try:
+        sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+        from baseline.reference_triton import load_reference_one_shot
+        ref_fn, ref_alloc = load_reference_one_shot()
+        ref_buf = ref_alloc((8 << 20) // 2, dev)
+        ref_buf.normal_()
+    except Exception as e:  # noqa: BLE001 - the section goes on without that column
+        ref_fn, ref_note = None, f"{type(e).__name__}: {e}"
+    out = {"unit": "us", "bus_gbs": "2 (N-1)/N * bytes / time", "sizes": {}}
+    if ref_note:
+        out["reference_triton_unavailable"] = ref_note
+    for nbytes in sizes:
+        numel = nbytes // 2
+        t = buf[:numel]
+        # check: the dispatcher's result against NCCL on the same input
+        t.copy_(plain[:numel])
+        want = plain[:numel].clone()
+        dist.all_reduce(want)
+        hdl.barrier()
+        smr.all_reduce(t)
+        hdl.barrier()
+        symm_mem.check_status(dev)
+        scale = float(want.float().abs().max()) or 1.0
+        err = float((t.float() - want.float()).abs().max()) / scale
+        ok = max_all(0.0 if err < 2e-2 else 1.0, dev) == 0.0
+        t.copy_(plain[:numel])
+        hdl.barrier()
+        one_out = torch.empty_like(t)
+        impls = {"auto": lambda: smr.all_reduce(t), "nccl": lambda: dist.all_reduce(plain[:numel])}
+        if nbytes <= (8 << 20):
+            impls["one_shot"] = lambda: smr.one_shot_all_reduce(t, out=one_out)
+            if ref_fn is not None:
+                rt = ref_buf[:numel]
+                impls["reference_triton"] = lambda: ref_fn(rt)
+        row = {"matches_nccl": ok, "algo": smr.ops.choose_algo(nbytes, world, hdl.has_multicast)}
+        for name, fn in impls.items():
+            if nbytes <= (4 << 20):
+                us = benchmark_with_graph(fn, calls_per_graph=20, warmup_iters=5, replays=10)
+            else:
+                us = benchmark_with_event(fn, 5, 20, flush_l2=False)
+            row[name] = {"us": round(us, 2), "bus_gbs": round(2 * (world - 1) / world * nbytes / us / 1e3, 1)}
+            buf.normal_()
+            plain.normal_()
+        symm_mem.check_status(dev)
+        out["sizes"][str(nbytes)] = row
+    return out
+
+
+def gemv_section(world, rank, dev):
+    """Fused GEMV + all-reduce against cuBLAS + NCCL at the Llama-3-70B down-projection decode
+    shape (x [b, 3584], W [3584, 8192] per rank), device time per call from graph replay over
+    four weight copies (224 MB, more than the L2 holds), maximum over ranks."""
+    import symm_mem_recipes_b200 as smr
+    from symm_mem_recipes_b200.parallel import symm_mem
+    from symm_mem_recipes_b200.utils.benchmark import benchmark_with_graph
+
+    K, N = 3584, 8192
+    torch.manual_seed(77 + rank)
+    weights = [(torch.randn(K, N, device=dev) * 0.02).to(torch.bfloat16) for _ in range(4)]
+    out = {"unit": "us", "shape": {"K_per_rank": K, "N": N}, "batches": {}}
+    for b in (1, 4, 16):
+        x = (torch.randn(b, K, device=dev) * 0.02).to(torch.bfloat16)
+        y = torch.empty(b, N, dtype=torch.bfloat16, device=dev)
+        smr.gemv_all_reduce(x, weights[0], y)
+        symm_mem.check_status(dev)
+        want = smr.reference_gemv_all_reduce(x, weights[0])
+        ok = bool(torch.allclose(y.float(), want.float(), rtol=2e-2, atol=2e-2))
+        ok = max_all(0.0 if ok else 1.0, dev) == 0.0
+        state = {"i": 0}
+
+        def fused():
+            state["i"] = (state["i"] + 1) % 4
+            smr.gemv_all_reduce(x, weights[state["i"]], y)
+
+        def lib():
+            state["i"] = (state["i"] + 1) % 4
+            smr.reference_gemv_all_reduce(x, weights[state["i"]])
+
+        us = benchmark_with_graph(fused, calls_per_graph=20, replays=10)
+        us_lib = benchmark_with_graph(lib, calls_per_graph=20, replays=10)
+        symm_mem.check_status(dev)
+        out["batches"][str(b)] = {"matches_library": ok, "fused_us": round(us, 2),
+                                  "cublas_plus_nccl_us": round(us_lib, 2), "speedup": round(us_lib / us, 3)}
+    return out
+
+
+def max_all(value, dev):
+    from symm_mem_recipes_b200.utils.benchmark import max_over_ranks
+    return max_over_ranks(value, dev)
 
 
 def reference_arm(args) -> int:
@@ -70,9 +182,51 @@ def reference_arm(args) -> int:
         except Exception as e:  # noqa: BLE001
             reason = (f"unmodified reference cannot be imported on this image: {type(e).__name__}: {e} "
                       "(symm_mem_recipes/triton_all_gather_matmul.py:8 uses a Triton API removed before 3.6)")
+    line = {"impl": "reference", "unavailable": reason}
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1:
+        # The all-reduce half of the metric does run unmodified on this image (with a stub for the
+        # missing `expecttest` module): upstream's own kernel, wrapper and timing helper
+        # (symm_mem_recipes/triton_one_shot_all_reduce.py:96-125, 156-160), at four message sizes.
+        try:
+            line["all_reduce"] = reference_all_reduce(world, rank)
+        except Exception as e:  # noqa: BLE001
+            line["all_reduce"] = {"unavailable": f"{type(e).__name__}: {e}"}
     if rank == 0:
-        print(json.dumps({"impl": "reference", "unavailable": reason}))
+        print(json.dumps(line))
     return 0
+
+
+def reference_all_reduce(world, rank):
+    """Median kernel time (µs, rank 0, torch.profiler) of upstream's one-shot all-reduce on torch's
+    own symmetric memory, measured with upstream's `benchmark_with_profiler` as its driver does."""
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    dist.init_process_group("nccl", device_id=dev)
+    try:
+        sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+        from baseline.reference_triton import load_reference_one_shot
+        one_shot, alloc = load_reference_one_shot()
+        from symm_mem_recipes.utils import benchmark_with_profiler
+        sizes = [4096, 65536, 1 << 20, 8 << 20]
+        buf = alloc(sizes[-1] // 2, dev)
+        buf.fill_(1)
+        res = {"unit": "us", "how": "upstream one_shot_all_reduce timed by upstream benchmark_with_profiler "
+                                    "(median kernel time on rank 0, 200 iterations)", "sizes": {}}
+        ok = bool(one_shot(buf[:8192]).eq(world).all())           # upstream's own check (:153-154)
+        res["output_equals_world_size"] = ok
+        for nbytes in sizes:
+            t = buf[:nbytes // 2]
+            us = benchmark_with_profiler(lambda: one_shot(t), "one_shot_all_reduce_kernel", benchmark_iters=200)
+            res["sizes"][str(nbytes)] = {"us": round(float(us), 2),
+                                         "bus_gbs": round(2 * (world - 1) / world * nbytes / us / 1e3, 1) if us else None}
+        return res
+    finally:
+        torch.cuda.synchronize()
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 def main() -> int:
@@ -191,43 +345,41 @@ def main() -> int:
     #      on a copy stream while the kernel of step i runs; every step still copies its input from pinned
     #      memory and reads its checksum back.  One event pair around all K steps; no L2 flush inside
     #      (a step reads the gathered A and B, 314 MB, more than the L2 holds). ----
-    pipelined_ms = None
-    if args.e2e_pipelined:
-        copy_stream = torch.cuda.Stream(dev)
-        main = torch.cuda.current_stream()
-        shards = [torch.empty_like(a_shard) for _ in range(2)]      # push mode reads the shard locally only
-        ready = [torch.cuda.Event() for _ in range(2)]
-        consumed = [torch.cuda.Event() for _ in range(2)]
+    copy_stream = torch.cuda.Stream(dev)
+    main = torch.cuda.current_stream()
+    shards = [torch.empty_like(a_shard) for _ in range(2)]      # push mode reads the shard locally only
+    ready = [torch.cuda.Event() for _ in range(2)]
+    consumed = [torch.cuda.Event() for _ in range(2)]
 
-        def feed(j):
-            copy_stream.wait_event(consumed[j])
-            with torch.cuda.stream(copy_stream):
-                shards[j].copy_(a_host, non_blocking=True)
-                ready[j].record(copy_stream)
+    def feed(j):
+        copy_stream.wait_event(consumed[j])
+        with torch.cuda.stream(copy_stream):
+            shards[j].copy_(a_host, non_blocking=True)
+            ready[j].record(copy_stream)
 
-        def pipelined(steps):
-            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            for ev in consumed:
-                ev.record(main)
-            sync_all()
-            begin.record(main)
-            feed(0)
-            for i in range(steps):
-                j = i % 2
-                if i + 1 < steps:
-                    feed(1 - j)
-                main.wait_event(ready[j])
-                smr.all_gather_matmul(shards[j], b, a_out, c_out)
-                consumed[j].record(main)
-                checksum_host.copy_(c_out[:, :8].float().sum().reshape(1), non_blocking=True)
-                main.synchronize()                                   # the host has this step's result
-            end.record(main)
-            sync_all()
-            return max_over_ranks(begin.elapsed_time(end) / steps, dev)
+    def pipelined(steps):
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for ev in consumed:
+            ev.record(main)
+        sync_all()
+        begin.record(main)
+        feed(0)
+        for i in range(steps):
+            j = i % 2
+            if i + 1 < steps:
+                feed(1 - j)
+            main.wait_event(ready[j])
+            smr.all_gather_matmul(shards[j], b, a_out, c_out)
+            consumed[j].record(main)
+            checksum_host.copy_(c_out[:, :8].float().sum().reshape(1), non_blocking=True)
+            main.synchronize()                                   # the host has this step's result
+        end.record(main)
+        sync_all()
+        return max_over_ranks(begin.elapsed_time(end) / steps, dev)
 
-        pipelined(3)
-        pipelined_ms = pipelined(args.steps)
-        symm_mem.check_status(dev)
+    pipelined(3)
+    pipelined_ms = pipelined(args.steps)
+    symm_mem.check_status(dev)
 
     per_gpu_tflops = flops / (ms_per_step * 1e-3) / 1e12
     e2e_tflops = flops / (e2e_ms * 1e-3) / 1e12 * world
@@ -253,9 +405,16 @@ def main() -> int:
             "baseline": f"published fused {PUBLISHED_FUSED_US_H100} us on 8xH100 = "
                         f"{PUBLISHED_TFLOPS_PER_GPU:.1f} TFLOPS per GPU; vs_baseline is per-GPU",
         },
-        "e2e": {"value": round(e2e_tflops, 2), "unit": "TFLOPS (aggregate over GPUs)",
-                "ms_per_step": round(e2e_ms, 5),
-                "h2d_bytes_per_step": a_host.numel() * 2, "d2h_bytes_per_step": 4},
+        "e2e": {"value": round(flops / (pipelined_ms * 1e-3) / 1e12 * world, 2),
+                "unit": "TFLOPS (aggregate over GPUs)", "ms_per_step": round(pipelined_ms, 5),
+                "h2d_bytes_per_step": a_host.numel() * 2, "d2h_bytes_per_step": 4,
+                "how": "public API; every step copies its A shard from pinned host memory (on a copy stream, under "
+                       "the previous step's kernel: two shard buffers) and reads a checksum of C back to the host",
+                "l2": "no flush between steps: a step reads 314 MB (gathered A and B)"},
+        "e2e_serial": {"value": round(e2e_tflops, 2), "unit": "TFLOPS (aggregate over GPUs)",
+                       "ms_per_step": round(e2e_ms, 5),
+                       "h2d_bytes_per_step": a_host.numel() * 2, "d2h_bytes_per_step": 4,
+                       "how": "copy, kernel and read-back one after the other on one stream, L2 flushed per step"},
         "same_box_baseline": {
             "what": "NCCL all_gather_into_tensor + cuBLAS torch.matmul" if distributed else
                     "cuBLAS torch.matmul alone (nothing to gather at one GPU)",
@@ -264,11 +423,14 @@ def main() -> int:
         "clocks": clocks.summary(),
         "wall_s_timed_region": round(wall, 4),
     }
-    if pipelined_ms is not None:
-        out["e2e_pipelined"] = {"value": round(flops / (pipelined_ms * 1e-3) / 1e12 * world, 2),
-                                "unit": "TFLOPS (aggregate over GPUs)", "ms_per_step": round(pipelined_ms, 5),
-                                "h2d_bytes_per_step": a_host.numel() * 2, "d2h_bytes_per_step": 4,
-                                "l2": "no flush between steps: a step reads 314 MB (gathered A and B)"}
+    if distributed and not args.no_extras:
+        # the other half of the metric; a section that fails is reported, not fatal to the headline
+        for key, section in (("all_reduce", all_reduce_section), ("gemv_all_reduce", gemv_section)):
+            try:
+                out[key] = section(world, rank, dev)
+            except Exception as e:  # noqa: BLE001
+                out[key] = {"failed": f"{type(e).__name__}: {e}"}
+                break          # the ranks may no longer be in step: skip what follows
     if rank == 0:
         print(json.dumps(out))
     symm_mem.shutdown()

@@ -12,7 +12,7 @@ from .ops import (all_reduce, barrier_test, low_latency_all_reduce, multimem_all
                   one_shot_all_reduce, two_shot_all_reduce_)
 
 from .ops import all_gather_matmul, matmul, reference_all_gather_matmul  # noqa: F401,E402
-from .ops import gemv_all_reduce, reference_gemv_all_reduce  # noqa: F401,E402
+from .ops import gemv, gemv_all_reduce, reference_gemv_all_reduce  # noqa: F401,E402
 from .ops import matmul_reduce_scatter, reference_matmul_reduce_scatter  # noqa: F401,E402
 from .ops import matmul_all_reduce, reference_matmul_all_reduce  # noqa: F401,E402
 

@@ -137,15 +137,13 @@ def main(argv=None, standalone: bool = True) -> int:
 
         def variants(nbytes):
             if nbytes <= 64 * 1024:          # latency: the barrier and the CTA shape
-                for barrier, threads in itertools.product((0, 1, 2), (256, 512)):
-                    yield dict(one_shot_barrier=barrier, one_shot_threads=threads, one_shot_max_blocks=32)
+                for barrier, threads in itertools.product((0, 2), (256, 512)):
+                    yield dict(one_shot_barrier=barrier, one_shot_threads=threads, one_shot_max_blocks=32,
+                               one_shot_unroll=1)
             else:                            # bandwidth: loads in flight
-                for barrier, blocks, unroll, rotate in itertools.product((0, 2), (24, 32, 64, 128), (1, 2), (0, 1)):
+                for barrier, blocks, unroll, rotate in itertools.product((0, 2), (32, 64, 128), (1, 2), (0, 1)):
                     yield dict(one_shot_barrier=barrier, one_shot_max_blocks=blocks, one_shot_unroll=unroll,
                                one_shot_rotate=rotate, one_shot_threads=512)
-                for blocks, unroll in itertools.product((64, 128, 192), (1, 2)):
-                    yield dict(one_shot_barrier=0, one_shot_max_blocks=blocks, one_shot_unroll=unroll,
-                               one_shot_rotate=1, one_shot_threads=256)
 
         for nbytes in (4096, 65536, 1 << 20, 8 << 20):
             if nbytes > args.max_bytes:
@@ -191,13 +189,13 @@ def main(argv=None, standalone: bool = True) -> int:
 
     if args.multimem_sweep:
         if world > 1 and hdl.has_multicast:
-            for nbytes in (16 << 20, 64 << 20, 256 << 20):
+            for nbytes in (1 << 20, 64 << 20, 256 << 20):
                 if nbytes > args.max_bytes:
                     continue
                 t = buf[:nbytes // 2]
                 for nvls in (0, 1):
-                    for blocks in (8, 12, 16, 24, 32):
-                        for unroll in (4, 8, 16):
+                    for blocks in (8, 12, 16, 24):
+                        for unroll in (8, 16):
                             def one(blocks=blocks, unroll=unroll, nvls=nvls, t=t, nbytes=nbytes):
                                 c = AllReduceConfig(multimem_max_blocks=blocks, multimem_unroll=unroll,
                                                     multimem_nvls_barrier=nvls)

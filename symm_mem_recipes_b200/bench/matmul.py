@@ -24,6 +24,9 @@ def main() -> int:
     ap.add_argument("--variant", default="bf16", choices=["bf16", "fp8", "swiglu"],
                     help="matmul: float8_e4m3fn operands and output, or the SwiGLU epilogue (N = 2 x FFN width)")
     ap.add_argument("--gemv-algo", default=None, help="gemv: tc, tc_tagged or simt")
+    ap.add_argument("--weights-nk", action="store_true",
+                    help="gemv: weights stored [N, K] (the column-parallel projections of a decode step: "
+                         "--N 1280 --K 8192 is QKV, --N 7168 --K 8192 gate / up at TP8)")
     ap.add_argument("--M", type=int, default=16384)
     ap.add_argument("--N", type=int, default=3584)
     ap.add_argument("--K", type=int, default=8192)
@@ -77,27 +80,29 @@ def main() -> int:
             K = args.K if args.K != 8192 or args.N != 3584 else 3584
             N = args.N if args.K != 8192 or args.N != 3584 else 8192
             x = (torch.randn(args.batch, K, device=dev) * 0.02).to(torch.bfloat16)
-            ws_ = [(torch.randn(K, N, device=dev) * 0.02).to(torch.bfloat16) for _ in range(4)]
+            wshape = (N, K) if args.weights_nk else (K, N)
+            n_copies = max(4, -(-256 * 1024 * 1024 // (K * N * 2)))      # cycled copies: more than the L2 holds
+            ws_ = [(torch.randn(*wshape, device=dev) * 0.02).to(torch.bfloat16) for _ in range(n_copies)]
             y = torch.empty(args.batch, N, dtype=torch.bfloat16, device=dev)
             state = {"i": 0}
 
             def fused():
-                state["i"] = (state["i"] + 1) % 4
-                smr.gemv_all_reduce(x, ws_[state["i"]], y, algo=args.gemv_algo)
+                state["i"] = (state["i"] + 1) % n_copies
+                smr.gemv_all_reduce(x, ws_[state["i"]], y, algo=args.gemv_algo, weights_nk=args.weights_nk)
 
             def lib():
-                state["i"] = (state["i"] + 1) % 4
-                torch.matmul(x, ws_[state["i"]])
+                state["i"] = (state["i"] + 1) % n_copies
+                torch.matmul(x, ws_[state["i"]].t() if args.weights_nk else ws_[state["i"]])
 
             fused()
             if args.eager:
                 us = benchmark_with_event(fused, **bench)
             else:
-                us = benchmark_with_graph(fused, calls_per_graph=20, replays=10, all_ranks_max=False)
+                us = benchmark_with_graph(fused, calls_per_graph=2 * n_copies, replays=10, all_ranks_max=False)
             out.update(batch=args.batch, K=K, N=N, smr_us=round(us, 2), timing="event" if args.eager else "graph",
                        weight_gbs=round(K * N * 2 / us / 1e3, 1))
             if not args.no_cublas and not args.eager:
-                us2 = benchmark_with_graph(lib, calls_per_graph=20, replays=10, all_ranks_max=False)
+                us2 = benchmark_with_graph(lib, calls_per_graph=2 * n_copies, replays=10, all_ranks_max=False)
                 out.update(cublas_us=round(us2, 2))
         elif args.op == "glue":
             # the layer-glue kernels at the decoder layer's per-rank sizes: T tokens, hidden 8192,

@@ -469,7 +469,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                         c10::optional<torch::Tensor> a_out, c10::optional<torch::Tensor> flags,
                         int block_n, int num_sms, int n_copy, uint64_t timeout_ns, bool cta_pair,
                         c10::optional<torch::Tensor> tail_scratch, int epilogue, int l2_hints,
-                        c10::optional<torch::Tensor> trace, int lead, int push_ahead, int push_spread) {
+                        c10::optional<torch::Tensor> trace, int lead, int push_ahead, int push_spread,
+                        bool push_plain_stores) {
     const auto dtype = a.scalar_type();
     const bool fp8 = dtype == at::kFloat8_e4m3fn;
     TORCH_CHECK(fp8 || dtype == torch::kBFloat16, "a must be bfloat16 or float8_e4m3fn");
@@ -551,6 +552,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     args.lead = lead;
     args.push_ahead = push_ahead;
     args.push_spread = push_spread;
+    args.push_plain_stores = push_plain_stores ? 1 : 0;
     if (trace.has_value()) {
       TORCH_CHECK(cta_pair && mode != 1, "the timing record belongs to the CTA-pair kernel");
       TORCH_CHECK(trace->is_cuda() && trace->get_device() == dev && trace->is_contiguous() &&
@@ -565,7 +567,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
      py::arg("flags"), py::arg("block_n"), py::arg("num_sms"), py::arg("n_copy"), py::arg("timeout_ns"),
      py::arg("cta_pair") = false, py::arg("tail_scratch") = py::none(), py::arg("epilogue") = 0,
      py::arg("l2_hints") = 0, py::arg("trace") = py::none(), py::arg("lead") = -1,
-     py::arg("push_ahead") = 0, py::arg("push_spread") = 0);
+     py::arg("push_ahead") = 0, py::arg("push_spread") = 0, py::arg("push_plain_stores") = false);
 
   m.def("check_push_schedule", &check_push_schedule);
   m.def("check_pair_work", &check_pair_work);

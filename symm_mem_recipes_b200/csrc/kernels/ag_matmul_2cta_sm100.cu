@@ -590,7 +590,7 @@ int launch_ag_matmul_2cta(const AgMatmulArgs& a, cudaStream_t stream) {
   if (comm) {
     p.lead = p.blocks_per_rank < 4 ? p.blocks_per_rank : 4;
     if (a.lead >= 0) p.lead = a.lead < p.blocks_per_rank ? a.lead : p.blocks_per_rank;
-    p.push_ahead = a.push_ahead > 0 ? a.push_ahead : 2;
+    p.push_ahead = a.push_ahead > 0 ? a.push_ahead : 1;
     size_t block_vecs = (size_t)kBM * a.K * es / 16;
     p.pieces = block_vecs >= 8192 ? 16 : (block_vecs >= 1024 ? 4 : 1);
   }
@@ -599,7 +599,7 @@ int launch_ag_matmul_2cta(const AgMatmulArgs& a, cudaStream_t stream) {
   p.header = comm ? a.local_pad + kFlagSlotsBase : nullptr;
   p.a_local = static_cast<const char*>(a.a_local);
   p.aout_buffers = a.aout_buffers;
-  p.aout_mc = a.aout_mc;
+  p.aout_mc = a.push_plain_stores ? nullptr : a.aout_mc;
   p.aout_offset = a.aout_offset;
   p.a_out = static_cast<char*>(a.a_out);
   p.pads = a.pads;
@@ -625,8 +625,10 @@ int launch_ag_matmul_2cta(const AgMatmulArgs& a, cudaStream_t stream) {
   const int grid = 2 * pairs;
   if (comm) {
     const int n_rounds = (total_tiles + pairs - 1) / pairs;
-    // by default the whole shard is on the wire by the middle of the kernel
-    p.push_spread = a.push_spread > 0 ? a.push_spread : (n_rounds / 2 > 1 ? n_rounds / 2 : 1);
+    // by default no faster than the schedule needs: pushes beyond that only compete with the GEMM's own
+    // loads (measured on two ranks); a positive push_spread sends the whole shard within that many rounds
+    (void)n_rounds;
+    p.push_spread = a.push_spread > 0 ? a.push_spread : 0;
   }
   // the entry barrier of CTA i uses block slot (barrier_block_base + i): it must stay inside the block-slot region
   if (comm && ((size_t)a.barrier_block_base + grid) * a.world_size > kBlockSlots) return cudaErrorInvalidValue;

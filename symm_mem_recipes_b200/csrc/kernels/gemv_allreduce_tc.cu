@@ -455,8 +455,8 @@ int launch_gemv_all_reduce_tc(const GemvArgs& a, int num_sms, cudaStream_t strea
 // ---------------------------------------------------------------------------
 // Allocation-free C entry point (see gemv_noalloc.h).  The scratch that the
 // kernel above normally finds in a symmetric workspace lives in this array;
-// offset 0 holds the one-entry "workspace base of every rank" table, the
-// workspace itself starts at offset 256.
+// offset 0 holds the one-entry "workspace base of every rank" table, offset 64 the
+// 32-byte Status record of the last calls, the workspace itself starts at offset 256.
 // ---------------------------------------------------------------------------
 #include <mutex>
 #include <stdio.h>
@@ -471,6 +471,9 @@ constexpr int kMaxDevices = 64;
 std::mutex g_noalloc_mu;
 unsigned char* g_noalloc_base[kMaxDevices] = {};   // device address of the array, per device
 int g_noalloc_sms[kMaxDevices] = {};
+int g_noalloc_last_n[kMaxDevices] = {};            // shape of the previous call: the flag layout follows it
+int g_noalloc_last_k[kMaxDevices] = {};
+constexpr size_t kNoallocStatusOffset = 64;
 
 int noalloc_fail(int code, char* err, int err_len, const char* what, const char* detail = "") {
   if (err != nullptr && err_len > 0) snprintf(err, (size_t)err_len, "smr_gemv_bf16_noalloc: %s%s", what, detail);
@@ -517,6 +520,13 @@ extern "C" int smr_gemv_bf16_noalloc(const void* x, const void* w, void* out, in
     base = g_noalloc_base[dev];
     sms = g_noalloc_sms[dev];
   }
+  bool new_layout;
+  {
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    new_layout = g_noalloc_last_n[dev] != N || g_noalloc_last_k[dev] != K;
+    g_noalloc_last_n[dev] = N;
+    g_noalloc_last_k[dev] = K;
+  }
 
   GemvTcParams p{};
   p.out = static_cast<__nv_bfloat16*>(out);
@@ -524,7 +534,7 @@ extern "C" int smr_gemv_bf16_noalloc(const void* x, const void* w, void* out, in
   p.rank = 0; p.world_size = 1;
   p.buffers = reinterpret_cast<void* const*>(base);
   p.timeout_ns = 2000000000ull;
-  p.status = nullptr;
+  p.status = reinterpret_cast<Status*>(base + kNoallocStatusOffset);
   size_t need = gemv_tc_workspace_bytes(N, K, 1, sms, &p.flags_offset, &p.inbox_offset, &p.tiles, &p.ksplit, false);
   if (need + 256 > (size_t)SMR_GEMV_NOALLOC_SCRATCH_BYTES)
     return noalloc_fail(1, err, err_len, "this shape needs more scratch than the static array holds");
@@ -538,10 +548,47 @@ extern "C" int smr_gemv_bf16_noalloc(const void* x, const void* w, void* out, in
   // "CTAs done" must read zero when the kernel starts; an aborted earlier call may have left it set
   e = cudaMemsetAsync(base + 256 + 4, 0, 4, stream);
   if (e != cudaSuccess) return noalloc_fail(3, err, err_len, "cudaMemsetAsync: ", cudaGetErrorString(e));
+  if (new_layout) {
+    // Where the arrival flags sit depends on N and K: after a call of another shape their slots hold
+    // that call's partial sums.  A flag is "set" when it equals the call number, so zeros are safe.
+    e = cudaMemsetAsync(base + 256 + p.flags_offset, 0, p.inbox_offset - p.flags_offset, stream);
+    if (e != cudaSuccess) return noalloc_fail(3, err, err_len, "cudaMemsetAsync(flags): ", cudaGetErrorString(e));
+  }
   e = cudaFuncSetAttribute(gemv_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTotal);
   if (e != cudaSuccess) return noalloc_fail(3, err, err_len, "cudaFuncSetAttribute: ", cudaGetErrorString(e));
   gemv_tc_kernel<false><<<p.tiles * p.ksplit, kThreads, kSmemTotal, stream>>>(tw, tx, p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return noalloc_fail(3, err, err_len, "kernel launch: ", cudaGetErrorString(e));
   return 0;
+}
+
+extern "C" int smr_gemv_bf16_noalloc_status(void* stream_ptr, unsigned int record[6], char* err, int err_len) {
+  using namespace smr;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return noalloc_fail(3, err, err_len, "cudaGetDevice: ", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return noalloc_fail(3, err, err_len, "device ordinal out of range");
+  unsigned char* base;
+  {
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    base = g_noalloc_base[dev];
+  }
+  if (record != nullptr)
+    for (int i = 0; i < 6; ++i) record[i] = 0u;
+  if (base == nullptr) return 0;                 // no call on this device yet: nothing can have failed
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  e = cudaStreamSynchronize(stream);
+  if (e != cudaSuccess) return noalloc_fail(3, err, err_len, "cudaStreamSynchronize: ", cudaGetErrorString(e));
+  Status st{};
+  e = cudaMemcpy(&st, base + kNoallocStatusOffset, sizeof(Status), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return noalloc_fail(3, err, err_len, "cudaMemcpy(status): ", cudaGetErrorString(e));
+  if (record != nullptr) {
+    record[0] = st.code; record[1] = st.rank; record[2] = st.block;
+    record[3] = st.peer; record[4] = st.where; record[5] = st.aux;
+  }
+  if (st.code == kOk) return 0;
+  e = cudaMemset(base + kNoallocStatusOffset, 0, sizeof(Status));    // reported once
+  if (e != cudaSuccess) return noalloc_fail(3, err, err_len, "cudaMemset(status): ", cudaGetErrorString(e));
+  return noalloc_fail(4, err, err_len, "a wait inside an earlier call ran out after 2 s (the CTAs of the kernel were "
+                                       "not all resident at once?); that call left `out` unwritten");
 }

@@ -33,10 +33,19 @@
 //  * No call allocates: no cudaMalloc, no cudaFree, no framework allocator.
 //  * All calls on a device share the one scratch array, which keeps whatever
 //    the previous call left in it.  The kernel's own bookkeeping tolerates
-//    that (and the entry point clears the one counter that must start at
-//    zero), but two calls that overlap in time on the same GPU — different
-//    streams, or two host threads — race on it and produce garbage.  Order
-//    them on one stream or with events.
+//    that (the entry point clears the one counter that must start at zero,
+//    and the arrival flags whenever N or K differ from the previous call on
+//    the device, because their place in the array follows the shape), but two
+//    calls that overlap in time on the same GPU — different streams, or two
+//    host threads — race on it and produce garbage.  Order them on one stream
+//    or with events.
+//  * A return value of 0 means "enqueued", not "done".  The CTAs of the kernel
+//    wait for one another (the K splits of a column tile meet in the scratch),
+//    each wait bounded at 2 s.  If a wait runs out — in practice only when the
+//    kernel's CTAs cannot all be resident because something else holds the
+//    SMs — the kernel records why in a status word inside the same array and
+//    returns with `out` UNWRITTEN.  smr_gemv_bf16_noalloc_status() reads that
+//    word; call it wherever you would otherwise synchronise.
 //
 // Returns 0 when the kernel was enqueued, otherwise:
 //   1 a size is outside the limits above      2 a pointer is null or misaligned
@@ -56,6 +65,13 @@ extern "C" {
 // `err`/`err_len`: optional buffer that receives a NUL-terminated message on failure.
 int smr_gemv_bf16_noalloc(const void* x, const void* w, void* out, int batch, int K, int N,
                           void* stream, char* err, int err_len);
+
+// Waits for `stream` (cudaStreamSynchronize), then reads the status word of the current
+// device's scratch array: 0 = every call since the last query ran to its end; 4 = a bounded
+// wait ran out in one of them and that call left `out` unwritten (the word is cleared, so the
+// failure is reported once); 3 = a CUDA call failed.  `record` (optional, 6 words) receives
+// {code, rank, block, peer, where, aux} of the kernel's Status record.  Allocates nothing.
+int smr_gemv_bf16_noalloc_status(void* stream, unsigned int record[6], char* err, int err_len);
 
 #ifdef __cplusplus
 }

@@ -117,6 +117,10 @@ struct AgMatmulArgs {
   // first need, and the number of rounds over which the whole shard is broadcast at the latest
   int push_ahead;
   int push_spread;
+  // push mode: 0 = broadcast the shard with multimem.st when the allocation has a multicast mapping
+  // (the shard leaves this GPU once; every rank, the sender included, receives it from the switch),
+  // 1 = plain stores to every peer and a local copy (nothing loops back through the switch)
+  int push_plain_stores;
 };
 int launch_ag_matmul(const AgMatmulArgs& args, cudaStream_t stream);
 // Same contract on CTA pairs (tcgen05 cta_group::2, 256 x BN tiles); modes 0 and 2 only.

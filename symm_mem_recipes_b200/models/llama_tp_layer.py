@@ -336,6 +336,13 @@ class LlamaTPDecoderLayer:
             return ops.gemv_all_reduce(act, w, group=self.group, weights_nk=nk)
         return ops.reference_gemv_all_reduce(act, w, group=self.group, weights_nk=nk)
 
+    def _column_parallel_decode(self, h: torch.Tensor, w_nk: torch.Tensor, fused: bool) -> torch.Tensor:
+        """h [B, H] times this rank's rows of a column-parallel weight ([N_local, H]); nothing to reduce.
+        On the package's tcgen05 GEMV (the weight streamed once by TMA) when `fused`, else cuBLAS."""
+        if fused and h.is_cuda and h.shape[0] <= 16:
+            return ops.gemv(h, w_nk, weights_nk=True)
+        return h @ w_nk.t()
+
     def _decode_norm(self, t: torch.Tensor, w: torch.Tensor, glue: bool) -> torch.Tensor:
         return ops.rms_norm(t, w, self.cfg.eps) if glue else _rms_norm(t, w, self.cfg.eps)
 
@@ -348,7 +355,7 @@ class LlamaTPDecoderLayer:
         else:
             x1 = x + o_proj
             h2 = _rms_norm(x1, self.norm2, self.cfg.eps)
-        gu = h2 @ self.w_gate_up.t()
+        gu = self._column_parallel_decode(h2, self.w_gate_up, glue)
         act = ops.silu_mul(gu) if glue else LlamaTPDecoderLayer._mlp_act_torch(gu, self.ffn_local)
         down = self._row_parallel_decode(act, "down", fused)
         return (down, x1) if defer_residual else x1 + down
@@ -360,7 +367,7 @@ class LlamaTPDecoderLayer:
         cfg = self.cfg
         B, D, hq, hkv = x.shape[0], cfg.head_dim, self.hq, self.hkv
         glue = fused and self.fused_glue
-        qkv = self._decode_norm(x, self.norm1, glue) @ self.w_qkv.t()
+        qkv = self._column_parallel_decode(self._decode_norm(x, self.norm1, glue), self.w_qkv, glue)
         if glue:
             # ONE kernel rotates the new Q and K, writes the caches and attends over positions 0..pos
             attn = ops.decode_attention_(qkv, k_cache, v_cache, hq, pos, rope_theta=cfg.rope_theta)
@@ -404,7 +411,7 @@ class LlamaTPDecoderLayer:
             h1, x = ops.rms_norm(x, self.norm1, cfg.eps, residual=pending_residual)    # x = previous x1 + down
         else:
             h1 = self._decode_norm(x, self.norm1, glue)
-        qkv = h1 @ self.w_qkv.t()
+        qkv = self._column_parallel_decode(h1, self.w_qkv, glue)
         if glue:
             attn = ops.decode_attention_(qkv, k_cache, v_cache, hq, pos, rope_theta=cfg.rope_theta)
             return self._decode_mlp(x, self._row_parallel_decode(attn, "o", fused), fused, glue, defer_residual)

@@ -62,6 +62,8 @@ class AgMatmulConfig:
     # first need, and rounds over which the whole shard is on the wire at the latest
     push_ahead: int = _env_int("SMR_AGMM_PUSH_AHEAD", 0)
     push_spread: int = _env_int("SMR_AGMM_PUSH_SPREAD", 0)
+    # push gather by plain stores to every peer even where a multicast mapping exists (-1 = decide by world size)
+    push_plain_stores: int = _env_int("SMR_AGMM_PUSH_PLAIN_STORES", -1)
     timeout_ms: int = _env_int("SMR_TIMEOUT_MS", 10000)
 
 
@@ -93,6 +95,14 @@ def _l2_hints(config: "AgMatmulConfig", dtype: torch.dtype, epi: int) -> int:
     if not config.cta_pair or dtype != torch.bfloat16 or epi:
         return 0
     return int(config.l2_hints)
+
+
+def _push_plain_stores(config: "AgMatmulConfig", world_size: int) -> bool:
+    """A multimem.st comes back to its sender too: at two ranks that doubles the bytes every GPU
+    receives, so the broadcast through the switch is used from four ranks on."""
+    if config.push_plain_stores >= 0:
+        return bool(config.push_plain_stores)
+    return world_size < 4
 
 
 def _num_sms(device: torch.device) -> int:
@@ -308,7 +318,7 @@ def all_gather_matmul(a_shard: torch.Tensor, b: torch.Tensor, a_out: Optional[to
         C.ag_matmul(a_shard, b, c_out, 2, None, 0, hdl.native, aout_offset, a_out, None,
                     bn, sms, n_copy, t_ns, config.cta_pair, _tail_buffer(a_shard.device, config), epi,
                     _l2_hints(config, a_shard.dtype, epi), trace, config.lead, config.push_ahead,
-                    config.push_spread)
+                    config.push_spread, _push_plain_stores(config, ws))
         return c_out
     if config.plain_a_out == "push_copy":
         staged = gather_buffer(M, K, a_shard.device, group, a_shard.dtype)

@@ -23,6 +23,7 @@ from ..utils.trace import traced
 from .ag_matmul import _num_sms
 
 _workspaces: dict[tuple, torch.Tensor] = {}
+_LOCAL = "local"          # in place of a group: the workspace of the rank-local GEMV (a world of one)
 _TIMEOUT_MS = int(os.environ.get("SMR_TIMEOUT_MS", "10000"))
 
 
@@ -31,8 +32,9 @@ def _workspace(batch_tile: int, N: int, K: int, device: torch.device, group, ten
     """Symmetric scratch (inboxes, flags, epoch) for one (kernel, batch tile,
     N, K): allocated and rendezvoused at the first call, which is therefore
     collective; all ranks must make the same sequence of first calls."""
-    ws = dist.get_world_size(group) if dist.is_initialized() else 1
-    key = (tensor_core, tagged, batch_tile, N, K, device.index, symm_mem._group_key(group))
+    local = group is _LOCAL
+    ws = 1 if local or not dist.is_initialized() else dist.get_world_size(group)
+    key = (tensor_core, tagged, batch_tile, N, K, device.index, _LOCAL if local else symm_mem._group_key(group))
     t = _workspaces.get(key)
     if t is None:
         if tensor_core:
@@ -40,7 +42,10 @@ def _workspace(batch_tile: int, N: int, K: int, device: torch.device, group, ten
         else:
             nbytes = C.gemv_workspace_bytes(batch_tile, N, ws)
         t = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
-        symm_mem.rendezvous(t, group)
+        if local:
+            symm_mem.rendezvous_local(t)
+        else:
+            symm_mem.rendezvous(t, group)
         _workspaces[key] = t
     return t
 
@@ -83,10 +88,19 @@ def gemv_all_reduce(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor
     sms = _num_sms(x.device)
     bt = 16 if tensor_core else C.gemv_batch_tile(B)
     wsp = _workspace(bt, N, x.shape[1], x.device, group, tensor_core, sms, tagged)
-    hdl = symm_mem.rendezvous(wsp, group)
+    hdl = symm_mem.rendezvous_local(wsp) if group is _LOCAL else symm_mem.rendezvous(wsp, group)
     C.gemv_all_reduce(x.contiguous(), w, out, hdl.native, 0, int(timeout_ms) * 1_000_000, tensor_core, sms, tagged,
                       bool(weights_nk))
     return out
+
+
+def gemv(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, weights_nk: bool = False,
+         timeout_ms: int = _TIMEOUT_MS) -> torch.Tensor:
+    """Rank-local `x @ w` for a decode batch (1..16 rows) on the same kernels as `gemv_all_reduce`, with
+    nobody to reduce with: the column-parallel projections of a decode step (QKV, gate / up), whose
+    weights are streamed once from HBM.  `weights_nk=True`: `w` is [N, K], the layout of the prefill
+    GEMMs' B operand.  Not collective; its scratch is a private world of one."""
+    return gemv_all_reduce(x, w, out, group=_LOCAL, timeout_ms=timeout_ms, weights_nk=weights_nk)
 
 
 def reference_gemv_all_reduce(x: torch.Tensor, w: torch.Tensor, group=None,

@@ -375,6 +375,25 @@ def rendezvous(t: torch.Tensor, group=None) -> SymmetricMemory:
     return rec.handle
 
 
+def rendezvous_local(t: torch.Tensor) -> SymmetricMemory:
+    """A world of one for `t`'s allocation, whatever process group exists: nothing is exchanged and
+    the handle's only rank is this process.  For scratch that a kernel of the library needs in the
+    layout of a symmetric workspace while no peer takes part (the rank-local GEMV of a
+    column-parallel projection).  Not collective."""
+    rec, _ = _find_record(t)
+    if rec.handle is not None:
+        if rec.handle.world_size != 1:
+            raise SymmMemError("this allocation is already rendezvoused with peers")
+        return rec.handle
+    if rec.kind == "cuda":
+        rec.alloc.begin_rendezvous(0, 1)
+        rec.alloc.finish_rendezvous()
+    else:
+        rec.alloc.rendezvous(0, [rec.alloc.shm_name])
+    rec.handle = SymmetricMemory(rec, None)
+    return rec.handle
+
+
 def _setup_multicast(alloc, st: _GroupState) -> None:
     """All-or-nothing: if any rank fails a phase, every rank drops multicast
     and the P2P paths remain."""

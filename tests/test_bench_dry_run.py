@@ -121,7 +121,7 @@ def _load_bench(monkeypatch, shape):
     return bench
 
 
-@pytest.mark.parametrize("extra", [[], ["--e2e-pipelined"]])
+@pytest.mark.parametrize("extra", [[], ["--no-extras"]])
 def test_bench_runs_to_its_json_line(monkeypatch, capsys, extra):
     bench = _load_bench(monkeypatch, (256, 64, 128))
     monkeypatch.delenv("WORLD_SIZE", raising=False)
@@ -144,7 +144,7 @@ def test_bench_runs_to_its_json_line(monkeypatch, capsys, extra):
     # value = flops / time, aggregated over the GPUs; 0.5 ms per step by construction
     flops = 2.0 * 256 * 64 * 128
     assert rec["ms_per_step"] == 0.5 and abs(rec["value"] - round(flops / 0.5e-3 / 1e12, 2)) < 1e-9
-    assert ("e2e_pipelined" in rec) == bool(extra)
+    assert {"ms_per_step", "h2d_bytes_per_step", "how"} <= set(rec["e2e_serial"]) and "how" in rec["e2e"]
     assert rec["same_box_baseline"]["ms_per_step"] == 0.5
 
 
@@ -160,7 +160,7 @@ def _two_rank_worker(rank, world_size, out_path):
         mp.setattr(dist, "init_process_group", lambda *a, **k: None)          # the harness has formed the gloo group
         mp.setattr(dist, "destroy_process_group", lambda *a, **k: None)
         mp.setattr(sys, "argv", ["bench.py", "--gpus", str(world_size), "--steps", "2", "--warmup", "1",
-                                 "--e2e-pipelined"])
+                                 "--no-extras"])
         import io
         buf = io.StringIO()
         with contextlib.redirect_stdout(buf):
@@ -185,4 +185,4 @@ def test_bench_two_ranks_over_gloo(tmp_path):
     rec = json.loads(lines[0])
     assert REQUIRED <= set(rec) and rec["n_gpus"] == 2 and rec["config"]["parallelism"] == "tp2"
     assert rec["config"]["a_shard_rows"] == 128
-    assert "NCCL" in rec["same_box_baseline"]["what"] and "e2e_pipelined" in rec
+    assert "NCCL" in rec["same_box_baseline"]["what"] and "e2e_serial" in rec

@@ -115,3 +115,36 @@ def test_gemv_weights_nk_world_of_one(B, K, N, algo):
 @pytest.mark.multigpu(2)
 def test_gemv_weights_nk_2gpu():
     spawn_ranks(_gemv_nk_worker, 2, "nccl", (4, 3584, 8192, "tc"))
+
+
+def _local_gemv_worker(rank, world_size):
+    """`ops.gemv` inside a job with peers: every rank multiplies its own operands, nothing is
+    exchanged, and the fused op still works beside it on the same shapes."""
+    import symm_mem_recipes_b200 as smr
+    from symm_mem_recipes_b200.parallel import symm_mem
+
+    dev = torch.device("cuda", rank)
+    for B, K, N in [(1, 8192, 1280), (16, 8192, 7168), (3, 1000, 328)]:
+        g = torch.Generator().manual_seed(7 + rank)
+        x = (torch.randn(B, K, generator=g) * 0.5).to(torch.bfloat16).to(dev)
+        w_nk = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).to(dev)
+        for _ in range(3):
+            y = smr.gemv(x, w_nk, weights_nk=True)
+        symm_mem.check_status(dev)
+        ref = x.double() @ w_nk.double().t()
+        assert bool(((y.double() - ref).abs() <= ref.abs() * 2.0 ** -7 + 2e-2).all()), (B, K, N)
+    if world_size > 1:
+        _gemv_worker(rank, world_size, 4, 1000, 328)
+    torch.cuda.synchronize()
+
+
+@pytest.mark.gpu
+def test_local_gemv_one_gpu():
+    torch.cuda.set_device(0)
+    _local_gemv_worker(0, 1)
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu(2)
+def test_local_gemv_beside_peers_2gpu():
+    spawn_ranks(_local_gemv_worker, 2, "nccl")

@@ -26,6 +26,19 @@ def _entry():
     return fn
 
 
+def _status():
+    from symm_mem_recipes_b200._ext import C
+
+    lib = ctypes.CDLL(C.__file__)
+    fn = lib.smr_gemv_bf16_noalloc_status
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_uint * 6), ctypes.c_char_p, ctypes.c_int]
+    record = (ctypes.c_uint * 6)()
+    err = ctypes.create_string_buffer(256)
+    rc = fn(torch.cuda.current_stream().cuda_stream, ctypes.byref(record), err, 256)
+    return rc, list(record), err.value.decode()
+
+
 def _call(fn, x, w, out):
     err = ctypes.create_string_buffer(256)
     rc = fn(x.data_ptr(), w.data_ptr(), out.data_ptr(), x.shape[0], x.shape[1], w.shape[1],
@@ -51,6 +64,8 @@ def test_noalloc_gemv_matches_the_allocating_op_twice(B, K, N):
         assert rc == 0, msg
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == before      # nothing taken from the framework's allocator
+        rc, record, msg = _status()                         # the kernel ran to its end: no wait ran out
+        assert rc == 0 and record[0] == 0, (rc, record, msg)
         expect = smr.gemv_all_reduce(x, w)                  # world of one: the plain product
         torch.cuda.synchronize()
         ref = x.double() @ w.double()
@@ -74,3 +89,22 @@ def test_noalloc_gemv_refuses_what_does_not_fit():
     rc, msg = _call(fn, x17, w2, out2)
     assert rc == 1 and "batch" in msg
     torch.cuda.synchronize()
+
+
+@pytest.mark.gpu
+def test_noalloc_gemv_after_a_call_of_another_shape():
+    """The flags of a wide call sit where a narrow call keeps partial sums: the entry point clears
+    them when the shape changes, so alternating shapes stay correct."""
+    torch.cuda.set_device(0)
+    fn = _entry()
+    g = torch.Generator().manual_seed(5)
+    for B, K, N in [(2, 512, 8192), (2, 512, 256), (2, 512, 8192), (16, 4096, 1024), (2, 512, 8192)]:
+        x = (torch.randn(B, K, generator=g) * 0.5).to(torch.bfloat16).cuda()
+        w = (torch.randn(K, N, generator=g) * 0.05).to(torch.bfloat16).cuda()
+        out = torch.full((B, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        rc, msg = _call(fn, x, w, out)
+        assert rc == 0, msg
+        rc, record, msg = _status()
+        assert rc == 0 and record[0] == 0, (rc, record, msg)
+        ref = x.double() @ w.double()
+        assert bool(((out.double() - ref).abs() <= ref.abs() * 2.0 ** -7 + 2e-2).all()), (B, K, N)
