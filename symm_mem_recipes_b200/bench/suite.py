@@ -3,6 +3,11 @@
 
     torchrun --nnodes 1 --nproc-per-node 8 --master-addr 127.0.0.1 \
         -m symm_mem_recipes_b200.bench.suite --out-dir results --tag ws8
+
+`--jobs` runs an explicit list instead: driver names with their own arguments,
+separated by ';', for example
+    --jobs "all_reduce --one-shot-sweep --max-bytes 8388608; gemv_all_reduce --extra-algos tc_tagged"
+A job that raises is reported and the next one starts from fresh symmetric memory.
 """
 from __future__ import annotations
 
@@ -22,14 +27,30 @@ def main() -> int:
                     help="also time the opt-in kernel variants: the layer with the single-pass glue kernels and the "
                          "SwiGLU epilogue, its phases, the prefill without sequence parallelism, the reduce-scatter "
                          "variants, the tagged GEMV exchange, decode from one CUDA graph")
+    ap.add_argument("--jobs", default="",
+                    help="';'-separated list of '<driver> <its arguments>' (drivers: barrier, all_reduce, "
+                         "all_gather_matmul, gemv_all_reduce, llama_layer) run in this order instead of --only")
     args = ap.parse_args()
     from symm_mem_recipes_b200.bench import (all_gather_matmul, all_reduce, barrier, gemv_all_reduce,
                                              llama_layer)
-    from symm_mem_recipes_b200.bench._common import finish, init_distributed
+    from symm_mem_recipes_b200.bench._common import attempt, finish, init_distributed
 
-    rank, _, world, _ = init_distributed()
+    rank, _, world, dev = init_distributed()
     tag = args.tag or f"ws{world}"
     only = set(args.only.split(","))
+    if args.jobs:
+        import json
+        import shlex
+        drivers = {"barrier": barrier, "all_reduce": all_reduce, "all_gather_matmul": all_gather_matmul,
+                   "gemv_all_reduce": gemv_all_reduce, "llama_layer": llama_layer}
+        for job in [j.strip() for j in args.jobs.split(";") if j.strip()]:
+            name, *argv = shlex.split(job)
+            if name not in drivers:
+                raise SystemExit(f"unknown driver {name!r}; known: {sorted(drivers)}")
+            attempt(job, lambda name=name, argv=argv: drivers[name].main(argv, standalone=False), dev,
+                    lambda rec: print(json.dumps(rec), flush=True) if rank == 0 else None)
+        finish()
+        return 0
 
     def out(name):
         return os.path.join(args.out_dir, f"{name}_{tag}.jsonl")

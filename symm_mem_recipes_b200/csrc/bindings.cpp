@@ -16,6 +16,7 @@
 #include "kernels/launch.h"
 #include "oracle/cpu_reference.h"
 #include "symm/allocator.h"
+#include "symm/driver_api.h"
 #include "symm/host_backend.h"
 #include "symm/ipc.h"
 
@@ -221,6 +222,20 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("finish_rendezvous", &CudaSymmAllocation::finish_rendezvous)
       .def("release", &CudaSymmAllocation::release)
       .def_static("multicast_supported", &CudaSymmAllocation::multicast_supported);
+  // flags[offset] = value, ordered after the work already queued on the current stream and preceded by a
+  // system-scope fence (cuStreamWriteValue32: what upstream's host-driven all-gather publishes progress
+  // with, symm_mem_recipes/triton_all_gather_matmul.py:51-55).  False when the driver lacks the call.
+  m.def("stream_write_value32", [](torch::Tensor flags, int64_t offset, uint32_t value) {
+    TORCH_CHECK(flags.is_cuda() && flags.is_contiguous() && flags.element_size() == 4 &&
+                offset >= 0 && offset < flags.numel(), "need a contiguous 32-bit CUDA tensor and an offset inside it");
+    const DriverApi& d = DriverApi::get();
+    if (d.cuStreamWriteValue32 == nullptr) return false;
+    int dev = flags.get_device();
+    c10::cuda::CUDAGuard guard(dev);
+    CUdeviceptr addr = reinterpret_cast<CUdeviceptr>(flags.data_ptr()) + (CUdeviceptr)offset * 4;
+    SMR_CU_CHECK(d.cuStreamWriteValue32(current_stream(dev), addr, value, CU_STREAM_WRITE_VALUE_DEFAULT));
+    return true;
+  });
   m.def("cuda_view", &cuda_view, py::arg("alloc"), py::arg("rank"), py::arg("sizes"), py::arg("dtype"),
         py::arg("offset_bytes"), py::arg("multicast") = false);
   m.def("cuda_pad_view", &cuda_pad_view);

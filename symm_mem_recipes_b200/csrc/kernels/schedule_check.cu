@@ -16,8 +16,8 @@ using namespace agmm;
 //  1 the M schedule is not a permutation of the blocks / `local` is wrong
 //  2 a tile could wait for a piece that no CTA has been told to push yet
 //  3 not every piece is pushed by the end
-int check_push_schedule(int world_size, int rank, int blocks_per_rank, int n_tiles_n, int n_units,
-                        int pos_per_tile, int pieces) {
+static int check_push_schedule_with_lead(int world_size, int rank, int blocks_per_rank, int n_tiles_n, int n_units,
+                                         int pos_per_tile, int pieces, int lead) {
   AgMatmulParams p{};
   p.mode = 2;
   p.world_size = world_size;
@@ -25,7 +25,7 @@ int check_push_schedule(int world_size, int rank, int blocks_per_rank, int n_til
   p.blocks_per_rank = blocks_per_rank;
   p.n_blocks_m = world_size * blocks_per_rank;
   p.n_tiles_n = n_tiles_n;
-  p.lead = blocks_per_rank < 4 ? blocks_per_rank : 4;
+  p.lead = lead;
   p.pieces = pieces;
   // 1. permutation + locality
   std::vector<int> seen(p.n_blocks_m, 0);
@@ -57,6 +57,21 @@ int check_push_schedule(int world_size, int rank, int blocks_per_rank, int n_til
   }
   // 3. the last limit covers the whole shard
   if (pieces_needed_through_round(p, rounds, n_units, pos_per_tile) < blocks_per_rank * pieces) return 3;
+  return 0;
+}
+
+// Every number of own blocks scheduled first that a launcher may pick: none, a few, the first round of
+// tiles (the default), the whole shard.
+int check_push_schedule(int world_size, int rank, int blocks_per_rank, int n_tiles_n, int n_units,
+                        int pos_per_tile, int pieces) {
+  const int first_round = pos_per_tile * ((n_units + n_tiles_n - 1) / n_tiles_n);
+  const int leads[4] = {0, blocks_per_rank < 4 ? blocks_per_rank : 4,
+                        first_round < blocks_per_rank ? first_round : blocks_per_rank, blocks_per_rank};
+  for (int lead : leads) {
+    int rc = check_push_schedule_with_lead(world_size, rank, blocks_per_rank, n_tiles_n, n_units, pos_per_tile,
+                                           pieces, lead);
+    if (rc != 0) return rc;
+  }
   return 0;
 }
 

@@ -47,6 +47,9 @@ void load() {
   SMR_LOAD(cuMulticastGetGranularity)
   SMR_LOAD(cuTensorMapEncodeTiled)
 #undef SMR_LOAD
+  // cuda.h maps the name to its _v2 entry point (per-stream memory-operation ordering)
+  g_api.cuStreamWriteValue32 =
+      reinterpret_cast<decltype(g_api.cuStreamWriteValue32)>(dlsym(lib, "cuStreamWriteValue32_v2"));
 }
 }  // namespace
 

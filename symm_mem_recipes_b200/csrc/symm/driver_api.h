@@ -34,6 +34,8 @@ struct DriverApi {
   SMR_DRIVER_FN(cuMulticastUnbind)
   SMR_DRIVER_FN(cuMulticastGetGranularity)
   SMR_DRIVER_FN(cuTensorMapEncodeTiled)
+  // optional (nullptr when the driver lacks it): stream-ordered 32-bit write with a system-scope fence before it
+  SMR_DRIVER_FN(cuStreamWriteValue32)
 #undef SMR_DRIVER_FN
   // Throws std::runtime_error when no driver library can be loaded.
   static const DriverApi& get();

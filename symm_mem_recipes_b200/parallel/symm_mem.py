@@ -300,9 +300,16 @@ class SymmetricMemory:
     @staticmethod
     def stream_write_value32(flags: torch.Tensor, offset: int, value: int) -> None:
         """`flags[offset] = value`, ordered after everything already queued on
-        the current stream (the role cuStreamWriteValue32 plays upstream,
-        symm_mem_recipes/triton_all_gather_matmul.py:51-55)."""
-        flags.view(-1)[int(offset):int(offset) + 1].fill_(int(value))
+        the current stream, by the driver's stream memory operation
+        (cuStreamWriteValue32, a system-scope fence before the write: what
+        upstream publishes the progress of its copy-engine all-gather with,
+        symm_mem_recipes/triton_all_gather_matmul.py:51-55).  A CPU tensor, or
+        a driver without the call, gets a one-element fill instead."""
+        flat = flags.view(-1)
+        if flat.is_cuda and flat.element_size() == 4 and flat.is_contiguous():
+            if C.stream_write_value32(flat, int(offset), int(value) & 0xFFFFFFFF):
+                return
+        flat[int(offset):int(offset) + 1].fill_(int(value))
 
     @property
     def buffer_ptrs(self) -> list:

@@ -57,26 +57,39 @@ def max_over_ranks(value: float, device=None) -> float:
 def benchmark_with_event(target_fn: Callable[[], None], warmup_iters: int = 200,
                          benchmark_iters: int = 25, profile_ranks: Optional[Sequence[int]] = None,
                          flush_l2: bool = False, reduce: str = "median",
-                         all_ranks_max: bool = True) -> float:
+                         all_ranks_max: bool = True, trace_handler=None) -> float:
     """Median (or mean/min) microseconds per call of `target_fn`, timed with CUDA
     events on the current stream.  With `all_ranks_max` the per-rank result is
-    replaced by the maximum over ranks.  `profile_ranks` is accepted for
-    signature parity; profiling is what `benchmark_with_profiler` is for."""
-    del profile_ranks
+    replaced by the maximum over ranks.
+
+    `profile_ranks`: ranks on which the timed loop also runs under
+    `torch.profiler` (CPU and CUDA activities), `trace_handler(prof)` being its
+    `on_trace_ready` callback, as upstream does (utils.py:108-131; there the
+    default is rank 0 and the handler an optional importable module).  Here the
+    default is no profiler: its bookkeeping shows in event-timed microsecond
+    numbers."""
     flush = globals()["flush_l2"] if flush_l2 else None
+    rank = dist.get_rank() if dist.is_initialized() else 0
     for _ in range(warmup_iters):
         target_fn()
     _barrier()
     torch.cuda.synchronize()
     begins = [torch.cuda.Event(enable_timing=True) for _ in range(benchmark_iters)]
     ends = [torch.cuda.Event(enable_timing=True) for _ in range(benchmark_iters)]
-    for i in range(benchmark_iters):
-        if flush is not None:
-            flush()
-        begins[i].record()
-        target_fn()
-        ends[i].record()
-    torch.cuda.synchronize()
+    if profile_ranks is not None and rank in profile_ranks:
+        from torch.profiler import ProfilerActivity, profile
+        prof = profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA], on_trace_ready=trace_handler)
+    else:
+        import contextlib
+        prof = contextlib.nullcontext()
+    with prof:
+        for i in range(benchmark_iters):
+            if flush is not None:
+                flush()
+            begins[i].record()
+            target_fn()
+            ends[i].record()
+        torch.cuda.synchronize()
     times = [b.elapsed_time(e) * 1000.0 for b, e in zip(begins, ends)]
     if reduce == "median":
         us = statistics.median(times)

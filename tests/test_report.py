@@ -142,6 +142,40 @@ def test_suite_hands_each_benchmark_arguments_its_parser_accepts(monkeypatch, tm
     assert seen["all_reduce"][0].with_reference_triton and seen["all_reduce"][0].out.endswith("all_reduce_ws8.jsonl")
 
 
+def test_suite_runs_an_explicit_job_list(monkeypatch, tmp_path, capsys):
+    """`--jobs`: every job's arguments go through its driver's own parser; a job that raises is
+    reported and the next one still runs."""
+    import sys
+
+    import torch
+
+    from symm_mem_recipes_b200.bench import (_common, all_gather_matmul, all_reduce, barrier, gemv_all_reduce,
+                                             llama_layer, suite)
+
+    seen = []
+    for mod in (all_gather_matmul, all_reduce, barrier, gemv_all_reduce, llama_layer):
+        def fake_main(argv=None, standalone=True, _mod=mod):
+            ns = _mod.build_parser().parse_args(argv)
+            seen.append((_mod.__name__.rsplit(".", 1)[1], ns))
+            if _mod is gemv_all_reduce:
+                raise RuntimeError("boom")
+            return 0
+        monkeypatch.setattr(mod, "main", fake_main)
+    monkeypatch.setattr(_common, "init_distributed", lambda: (0, 0, 8, torch.device("cpu")))
+    monkeypatch.setattr(_common, "finish", lambda: None)
+    jobs = ("all_gather_matmul --M 16384 --N 3584 --K 8192 --warmup 10 --iters 25 --trace --per-rank "
+            "--pacings 1:0:12:0,1:0:4:1,1:0:12:1,2:0:12:0 --out x.jsonl; "
+            "gemv_all_reduce --extra-algos tc_tagged; "
+            "all_reduce --one-shot-sweep --with-reference-triton --max-bytes 8388608; "
+            "all_reduce --multimem-sweep --max-bytes 268435456; "
+            "llama_layer --skip-layer --rs-variants cta_pair,deep_strips,thread_stores,cta_pair+thread_stores")
+    monkeypatch.setattr(sys, "argv", ["suite", "--jobs", jobs])
+    assert suite.main() == 0
+    assert [n for n, _ in seen] == ["all_gather_matmul", "gemv_all_reduce", "all_reduce", "all_reduce", "llama_layer"]
+    assert seen[0][1].trace and seen[0][1].pacings.count(",") == 3 and seen[2][1].one_shot_sweep
+    assert '"section_failed"' in capsys.readouterr().out          # the job that raised
+
+
 def test_ncu_summary_from_raw_csv():
     """The raw-page CSV of Nsight Compute (header row, unit row, one row per launch) into the
     Markdown summary kept under profiles/, with the derived roofline figures."""
