@@ -12,17 +12,28 @@
 // descriptor says MN-major (8-row k groups 1024 B apart, 64-column n groups
 // 8192 B apart).  x is the K-major B operand, one [16 x 64] box per k step.
 // One thread streams the weights through an 8-stage TMA ring (144 KB in
-// flight per SM) — the op is bound by HBM, the MMA work is negligible.
+// flight per SM) — the op is bound by HBM, the MMA work is negligible.  The
+// first ring of loads is issued before the CTA's set-up barrier, so the weight
+// stream starts while tensor memory is still being allocated.
 //
-// Grid = (N / 128 column tiles) x (K splits), chosen to fill the SMs.  Every
-// CTA pushes its fp32 partial [b, 128] into the inbox slot (rank, split) of
-// every rank, raises that slot's flag for its tile (st.release.sys), waits
-// (bounded) for all WS x splits flags of the tile and reduces its share of the
-// tile's columns in slot order, so every rank produces the same bits.
-// Epoch / parity handling as in gemv_allreduce.cu: nothing is reset between
-// calls and the kernel can be replayed from a CUDA graph.
+// Grid = (N / 128 column tiles) x (K splits), chosen to fill the SMs; the K
+// splits of a tile form a thread-block CLUSTER.  Each CTA parks its fp32
+// partial [16 b x 128 n] in its own shared memory, the cluster meets, and CTA
+// kh sums the partials of its share of the tile's columns (128 / splits) over
+// the cluster's shared memories (distributed shared memory, split order): the
+// K reduction never touches global memory.  With one rank that sum is the
+// result.  With several, the CTA pushes it into slot `rank` of every rank's
+// inbox for those columns, raises the slot's flag (st.release.sys), waits
+// (bounded) for the WS flags of its columns and adds the slots in rank order,
+// so every rank produces the same bits.
 //
-// Tagged variant (kTagged, meant for batch <= 4): the partials travel as 8-byte
+// Nothing is reset between calls and the kernel can be replayed from a CUDA
+// graph: inbox and flags are double-buffered by the parity of a call number,
+// and every CTA keeps its own call counter in the workspace (read when it
+// starts, written when it ends; all CTAs of all ranks make the same calls, so
+// the counters agree without an atomic or a fence at the kernel's end).
+//
+// Tagged variant (kTagged, meant for batch <= 4): the sums travel as 8-byte
 // words {fp32 value, call number}, the protocol of the low-latency all-reduce
 // in all_reduce.cu.  No flag and no release fence (which has to wait for the
 // acknowledgements of all pushes): the reducer polls the words themselves
@@ -39,6 +50,7 @@
 #include "../device/vec.cuh"
 #include "../symm/driver_api.h"
 #include "launch.h"
+#include "residency.h"
 
 namespace smr {
 
@@ -65,10 +77,11 @@ struct GemvTcParams {
   __nv_bfloat16* out;     // [batch, N]
   int batch, K, N;
   int rank, world_size;
-  int ksplit;
+  int ksplit;             // K splits of a column tile = CTAs of a cluster
   void* const* buffers;   // workspace payload base of every rank
-  size_t flags_offset;    // [2 parity][tiles][kFlagStride] u32
-  size_t inbox_offset;    // [2 parity][WS * ksplit][16][N] fp32 (tagged: 8-byte words {fp32, call number})
+  size_t counters_offset; // [tiles * ksplit] u32: calls made so far, one counter per CTA
+  size_t flags_offset;    // [2 parity][tiles][kFlagStride] u32, flag of (tile, kh, source rank) at kh * WS + rank
+  size_t inbox_offset;    // [2 parity][WS][16][N] fp32 (tagged: 8-byte words {fp32, call number})
   int tiles;
   uint64_t timeout_ns;
   Status* status;
@@ -98,6 +111,21 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)
 
 __device__ __forceinline__ void group_sync_128() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
+// Cluster-wide barrier (every thread of every CTA of the cluster) and a 16-byte load from the
+// shared memory of CTA `cta` of the cluster at the same offset as `local_smem_addr`.
+__device__ __forceinline__ void cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float4 ld_dsmem_f4(uint32_t local_smem_addr, uint32_t cta) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem_addr), "r"(cta));
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+  return v;
+}
+
 // kWeightsNK: W is stored [N, K] (K contiguous), the layout the prefill GEMMs use, so that one
 // copy of a row-parallel weight serves prefill and decode.  The A operand is then K-major: one
 // [128 n x 64 k] TMA box per stage and the K-major descriptor of the GEMM kernels.
@@ -106,6 +134,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemv_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                const GemvTcParams p) {
   extern __shared__ uint8_t smem_raw[];
+  // the same offset in every CTA of the cluster: the dynamic window starts at the same shared address
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kBarOffset);
   uint64_t* full_bar = bars;
@@ -115,16 +144,17 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   __shared__ int flags_ok;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile = (int)blockIdx.x / p.ksplit, kh = (int)blockIdx.x % p.ksplit;
+  const int tile = (int)blockIdx.x / p.ksplit, kh = (int)blockIdx.x % p.ksplit;   // kh = rank in the cluster
   const int n0 = tile * kTileN;
   const int rank = p.rank, ws = p.world_size;
-  const int slots = ws * p.ksplit;                       // partials per output element
-  const int my_slot = rank * p.ksplit + kh;
 
   char* my_ws = static_cast<char*>(p.buffers[rank]);
-  uint32_t* header = reinterpret_cast<uint32_t*>(my_ws);   // [0] epoch, [1] CTAs done
-  const uint32_t epoch = ld_relaxed_gpu(&header[0]) + 1u;
-  const uint32_t parity = epoch & 1u;
+  uint32_t* my_counter = reinterpret_cast<uint32_t*>(my_ws + p.counters_offset) + blockIdx.x;
+  uint32_t epoch = 0, parity = 0;
+  if (ws > 1) {                          // a world of one exchanges nothing: no call number needed
+    epoch = ld_relaxed_gpu(my_counter) + 1u;
+    parity = epoch & 1u;
+  }
 
   const int kb_total = (p.K + kBK - 1) / kBK;
   const int kb_per = (kb_total + p.ksplit - 1) / p.ksplit;
@@ -132,6 +162,20 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   const int kb1 = kb0 + kb_per < kb_total ? kb0 + kb_per : kb_total;
   const int n_kb = kb1 > kb0 ? kb1 - kb0 : 0;
 
+  auto load_stage = [&](int i, uint32_t stage) {
+    const int kb = kb0 + i;
+    uint8_t* sw = smem + (size_t)stage * kStageBytes;
+    mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
+    if constexpr (kWeightsNK) {
+      tma_load_2d(sw, &tmap_w, &full_bar[stage], kb * kBK, n0);             // [128 n x 64 k], 16 KB
+    } else {
+      tma_load_2d(sw, &tmap_w, &full_bar[stage], n0, kb * kBK);               // n 0..63
+      tma_load_2d(sw + 8192, &tmap_w, &full_bar[stage], n0 + 64, kb * kBK);   // n 64..127
+    }
+    tma_load_2d(sw + kWBytes, &tmap_x, &full_bar[stage], kb * kBK, 0);
+  };
+
+  const int n_first = n_kb < kStages ? n_kb : kStages;     // loads that need no free-stage wait
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&full_bar[s], 1);
@@ -139,9 +183,9 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     }
     mbar_init(tmem_full, 1);
     mbar_fence_init();
-    tma_prefetch_desc(&tmap_w);
-    tma_prefetch_desc(&tmap_x);
     flags_ok = 1;
+    // the weight stream starts now, under the rest of the set-up
+    for (int i = 0; i < n_first; ++i) load_stage(i, (uint32_t)i);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, kTmemCols);
@@ -153,25 +197,22 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   const uint32_t tmem_base = *tmem_slot;
   bool failed = false;
 
+  float* part = reinterpret_cast<float*>(smem);          // [16][128] fp32 partial of this CTA (ring idle by then)
+  const int share = kTileN / p.ksplit;                   // columns of the tile this CTA finishes
+  const int c_share0 = kh * share;                       // first of them, inside the tile
+  const int quarter = warp & 3;
+  const int etid = (int)threadIdx.x - 64;
+
   if (warp == 0) {
     if (lane == 0) {
-      uint32_t stage = 0, phase = 0;
-      for (int i = 0; i < n_kb; ++i) {
-        const int kb = kb0 + i;
+      uint32_t stage = (uint32_t)(n_first % kStages), phase = n_first == kStages ? 1u : 0u;
+      for (int i = n_first; i < n_kb; ++i) {
         if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.timeout_ns)) {
           report_status(p.status, kTimeoutMbarrier, rank, blockIdx.x, stage, kWhereGemmEmpty);
           failed = true;
           break;
         }
-        uint8_t* sw = smem + (size_t)stage * kStageBytes;
-        mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
-        if constexpr (kWeightsNK) {
-          tma_load_2d(sw, &tmap_w, &full_bar[stage], kb * kBK, n0);             // [128 n x 64 k], 16 KB
-        } else {
-          tma_load_2d(sw, &tmap_w, &full_bar[stage], n0, kb * kBK);               // n 0..63
-          tma_load_2d(sw + 8192, &tmap_w, &full_bar[stage], n0 + 64, kb * kBK);   // n 64..127
-        }
-        tma_load_2d(sw + kWBytes, &tmap_x, &full_bar[stage], kb * kBK, 0);
+        load_stage(i, stage);
         if (++stage == kStages) { stage = 0; phase ^= 1; }
       }
     }
@@ -202,9 +243,7 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
       if (!failed) umma_commit(tmem_full);
     }
   } else {
-    // ---------------- epilogue + all-reduce (warps 2..5, 128 threads) ----------------
-    const int quarter = warp & 3;
-    const int etid = (int)threadIdx.x - 64;
+    // ---------------- epilogue, part 1 (warps 2..5): accumulator -> this CTA's shared memory ----------------
     const int col = quarter * 32 + lane;                 // column of the tile owned by this thread
     uint32_t acc[16];
     if (n_kb > 0) {
@@ -220,41 +259,80 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
 #pragma unroll
       for (int b = 0; b < 16; ++b) acc[b] = 0u;
     }
-    const size_t slot_stride = (size_t)kBatchN * p.N;                   // floats per slot
-    const size_t parity_off = (size_t)parity * slots * slot_stride;
-    // transpose through shared memory (the ring is idle once the last MMA has
-    // completed) so that the pushes are 16-byte stores of 4 consecutive columns
-    float* part = reinterpret_cast<float*>(smem);                       // [16][128]
+    if (failed) {
+#pragma unroll
+      for (int b = 0; b < 16; ++b) acc[b] = 0u;
+    }
 #pragma unroll
     for (int b = 0; b < 16; ++b) part[b * kTileN + col] = __uint_as_float(acc[b]);
-    group_sync_128();
-    if constexpr (kTagged) {
-      // ---- push {value, call number} words; then poll the own inbox for every slot's words ----
-      if (!failed) {
-        const size_t off = parity_off + (size_t)my_slot * slot_stride + n0;          // in words
-        for (int item = etid; item < p.batch * (kTileN / 4); item += 128) {
-          const int b = item / (kTileN / 4), c4 = (item % (kTileN / 4)) * 4;
-          if (n0 + c4 >= p.N) continue;
-          const Vec16 v = *reinterpret_cast<const Vec16*>(&part[b * kTileN + c4]);
-          const Vec16 w0{v.x, epoch, v.y, epoch}, w1{v.z, epoch, v.w, epoch};
+  }
+
+  // ---- every partial of the tile is in its CTA's shared memory ----
+  __syncwarp();
+  cluster_barrier();
+
+  if (warp >= 2) {
+    // ---------------- epilogue, part 2: K reduction over the cluster, then the ranks ----------------
+    // item = (batch row b, four consecutive columns of this CTA's share); at most 16 * 32 items
+    const int n_items = p.batch * (share / 4);
+    const uint32_t part_addr = smem_u32(part);
+    if (ws == 1) {
+      for (int item = etid; item < n_items; item += 128) {
+        const int b = item / (share / 4), c = c_share0 + (item % (share / 4)) * 4;
+        if (n0 + c >= p.N) continue;                                      // N % 8 == 0
+        float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int j = 0; j < p.ksplit; ++j) {                              // split order: deterministic
+          const float4 v = ld_dsmem_f4(part_addr + (uint32_t)(b * kTileN + c) * 4u, (uint32_t)j);
+          s4.x += v.x; s4.y += v.y; s4.z += v.z; s4.w += v.w;
+        }
+        uint2 o;
+        o.x = pack_bf16x2(s4.x, s4.y);
+        o.y = pack_bf16x2(s4.z, s4.w);
+        *reinterpret_cast<uint2*>(p.out + (size_t)b * p.N + n0 + c) = o;
+      }
+    } else {
+      const size_t slot_stride = (size_t)kBatchN * p.N;                   // floats (or words) per slot
+      const size_t parity_off = (size_t)parity * ws * slot_stride;
+      // ---- push this rank's sum of the share into slot `rank` of every rank's inbox ----
+      for (int item = etid; item < n_items && !failed; item += 128) {
+        const int b = item / (share / 4), c = c_share0 + (item % (share / 4)) * 4;
+        if (n0 + c >= p.N) continue;
+        float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int j = 0; j < p.ksplit; ++j) {
+          const float4 v = ld_dsmem_f4(part_addr + (uint32_t)(b * kTileN + c) * 4u, (uint32_t)j);
+          s4.x += v.x; s4.y += v.y; s4.z += v.z; s4.w += v.w;
+        }
+        const size_t off = parity_off + (size_t)rank * slot_stride + (size_t)b * p.N + n0 + c;
+        if constexpr (kTagged) {
+          const Vec16 w0{__float_as_uint(s4.x), epoch, __float_as_uint(s4.y), epoch};
+          const Vec16 w1{__float_as_uint(s4.z), epoch, __float_as_uint(s4.w), epoch};
           for (int j = 1; j <= ws; ++j) {                                 // own inbox last
             int peer = rank + j;
             if (peer >= ws) peer -= ws;
-            char* dst = static_cast<char*>(p.buffers[peer]) + p.inbox_offset + (off + (size_t)b * p.N + c4) * 8;
+            char* dst = static_cast<char*>(p.buffers[peer]) + p.inbox_offset + off * 8;
             st_16(dst, w0);
             st_16(dst + 16, w1);
           }
+        } else {
+          const Vec16 v{__float_as_uint(s4.x), __float_as_uint(s4.y), __float_as_uint(s4.z), __float_as_uint(s4.w)};
+          for (int j = 1; j <= ws; ++j) {
+            int peer = rank + j;
+            if (peer >= ws) peer -= ws;
+            float* inbox = reinterpret_cast<float*>(static_cast<char*>(p.buffers[peer]) + p.inbox_offset);
+            st_16(inbox + off, v);
+          }
         }
-        const int share = kTileN / p.ksplit;
-        const int c0 = n0 + kh * share;
+      }
+      if constexpr (kTagged) {
+        // ---- poll the own inbox until every rank's words for an item carry this call's number ----
         const char* inbox = my_ws + p.inbox_offset;
-        for (int item = etid; item < p.batch * (share / 4) && flags_ok; item += 128) {
-          const int b = item / (share / 4), c = c0 + (item % (share / 4)) * 4;
-          if (c >= p.N) continue;
+        for (int item = etid; item < n_items && !failed && flags_ok; item += 128) {
+          const int b = item / (share / 4), c = c_share0 + (item % (share / 4)) * 4;
+          if (n0 + c >= p.N) continue;
           float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
           Deadline d(p.timeout_ns);
-          for (int sl = 0; sl < slots; ++sl) {                            // slot order: same bits on every rank
-            const char* src = inbox + (parity_off + (size_t)sl * slot_stride + (size_t)b * p.N + c) * 8;
+          for (int sl = 0; sl < ws; ++sl) {                               // rank order: same bits on every rank
+            const char* src = inbox + (parity_off + (size_t)sl * slot_stride + (size_t)b * p.N + n0 + c) * 8;
             Vec16 a, g;
             bool got = false;
             while (!got) {
@@ -277,71 +355,54 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
           uint2 o;
           o.x = pack_bf16x2(s4.x, s4.y);
           o.y = pack_bf16x2(s4.z, s4.w);
-          *reinterpret_cast<uint2*>(p.out + (size_t)b * p.N + c) = o;
+          *reinterpret_cast<uint2*>(p.out + (size_t)b * p.N + n0 + c) = o;
         }
-      }
-    } else {
-    if (!failed) {
-      const size_t off = parity_off + (size_t)my_slot * slot_stride + n0;
-      for (int item = etid; item < p.batch * (kTileN / 4); item += 128) {
-        const int b = item / (kTileN / 4), c4 = (item % (kTileN / 4)) * 4;
-        if (n0 + c4 >= p.N) continue;                                   // N % 8 == 0
-        const Vec16 v = *reinterpret_cast<const Vec16*>(&part[b * kTileN + c4]);
-        for (int j = 1; j <= ws; ++j) {                                 // own inbox last
-          int peer = rank + j;
-          if (peer >= ws) peer -= ws;
-          float* inbox = reinterpret_cast<float*>(static_cast<char*>(p.buffers[peer]) + p.inbox_offset);
-          st_16(inbox + off + (size_t)b * p.N + c4, v);
+      } else {
+        group_sync_128();   // the group's pushes precede the releases below
+        const size_t flag_idx = ((size_t)parity * p.tiles + tile) * kFlagStride + (size_t)kh * ws;
+        if (etid < ws && !failed) {
+          uint32_t* peer_flags = reinterpret_cast<uint32_t*>(static_cast<char*>(p.buffers[etid]) + p.flags_offset);
+          st_release_sys(peer_flags + flag_idx + rank, epoch);
         }
-      }
-    }
-    group_sync_128();   // the group's pushes precede the releases below
-    const size_t flag_idx = ((size_t)parity * p.tiles + tile) * kFlagStride;
-    if (etid < ws && !failed) {
-      uint32_t* peer_flags = reinterpret_cast<uint32_t*>(static_cast<char*>(p.buffers[etid]) + p.flags_offset);
-      st_release_sys(peer_flags + flag_idx + my_slot, epoch);
-    }
-    if (etid < slots) {
-      const uint32_t* mine = reinterpret_cast<const uint32_t*>(my_ws + p.flags_offset) + flag_idx + etid;
-      Deadline d(p.timeout_ns);
-      while (ld_acquire_sys(mine) != epoch) {
-        if (!d.alive()) {
-          report_status(p.status, kTimeoutFlag, rank, tile, etid, kWhereGemvArrive, epoch);
-          flags_ok = 0;
-          break;
-        }
-      }
-    }
-    group_sync_128();
-    if (flags_ok && !failed) {
-      // this CTA reduces its share of the tile's columns: 128 / ksplit of them
-      const int share = kTileN / p.ksplit;
-      const int c0 = n0 + kh * share;
-      const float* inbox = reinterpret_cast<const float*>(my_ws + p.inbox_offset) + parity_off;
-      for (int item = etid; item < p.batch * (share / 4); item += 128) {
-        const int b = item / (share / 4), c = c0 + (item % (share / 4)) * 4;
-        if (c >= p.N) continue;
-        const float* src = inbox + (size_t)b * p.N + c;
-        float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int sl0 = 0; sl0 < slots; sl0 += 8) {                      // 8 independent loads in flight
-          Vec16 v[8];
-#pragma unroll
-          for (int u = 0; u < 8; ++u)
-            if (sl0 + u < slots) v[u] = ld_16_stream(src + (size_t)(sl0 + u) * slot_stride);
-#pragma unroll
-          for (int u = 0; u < 8; ++u)
-            if (sl0 + u < slots) {
-              s4.x += __uint_as_float(v[u].x); s4.y += __uint_as_float(v[u].y);
-              s4.z += __uint_as_float(v[u].z); s4.w += __uint_as_float(v[u].w);
+        if (etid < ws) {
+          const uint32_t* mine = reinterpret_cast<const uint32_t*>(my_ws + p.flags_offset) + flag_idx + etid;
+          Deadline d(p.timeout_ns);
+          while (ld_acquire_sys(mine) != epoch) {
+            if (!d.alive()) {
+              report_status(p.status, kTimeoutFlag, rank, tile, etid, kWhereGemvArrive, epoch);
+              flags_ok = 0;
+              break;
             }
+          }
         }
-        uint2 o;
-        o.x = pack_bf16x2(s4.x, s4.y);
-        o.y = pack_bf16x2(s4.z, s4.w);
-        *reinterpret_cast<uint2*>(p.out + (size_t)b * p.N + c) = o;
+        group_sync_128();
+        if (flags_ok && !failed) {
+          const float* inbox = reinterpret_cast<const float*>(my_ws + p.inbox_offset) + parity_off;
+          for (int item = etid; item < n_items; item += 128) {
+            const int b = item / (share / 4), c = c_share0 + (item % (share / 4)) * 4;
+            if (n0 + c >= p.N) continue;
+            const float* src = inbox + (size_t)b * p.N + n0 + c;
+            float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int sl0 = 0; sl0 < ws; sl0 += 8) {                       // 8 independent loads in flight
+              Vec16 v[8];
+#pragma unroll
+              for (int u = 0; u < 8; ++u)
+                if (sl0 + u < ws) v[u] = ld_16_stream(src + (size_t)(sl0 + u) * slot_stride);
+#pragma unroll
+              for (int u = 0; u < 8; ++u)
+                if (sl0 + u < ws) {
+                  s4.x += __uint_as_float(v[u].x); s4.y += __uint_as_float(v[u].y);
+                  s4.z += __uint_as_float(v[u].z); s4.w += __uint_as_float(v[u].w);
+                }
+            }
+            uint2 o;
+            o.x = pack_bf16x2(s4.x, s4.y);
+            o.y = pack_bf16x2(s4.z, s4.w);
+            *reinterpret_cast<uint2*>(p.out + (size_t)b * p.N + n0 + c) = o;
+          }
+        }
       }
     }
-    }   // flagged exchange
   }
 
   if (__any_sync(0xffffffffu, failed)) {
@@ -351,15 +412,10 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   __syncthreads();
   tcgen05_fence_after_thread_sync();
   if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
-  if (threadIdx.x == 0) {
-    __threadfence();
-    uint32_t done = atomicAdd(&header[1], 1u);
-    if (done == gridDim.x - 1) {
-      header[1] = 0u;
-      __threadfence();
-      st_release_gpu(&header[0], epoch);
-    }
-  }
+  if (ws > 1 && threadIdx.x == 0) *my_counter = epoch;   // this CTA has made its call; read by its next launch
+  // no CTA of the cluster leaves while another may still read its shared memory
+  __syncwarp();
+  cluster_barrier();
 }
 
 int encode(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint32_t box_inner,
@@ -376,25 +432,63 @@ int encode(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, u
   return r == CUDA_SUCCESS ? 0 : 1;
 }
 
-int pick_ksplit(int N, int K, int num_sms) {
+// K splits per column tile = cluster size: 1, 2, 4 or 8 (a share of 128 / ksplit columns per CTA).
+int pick_ksplit(int N, int K, int num_sms, int world_size) {
   int tiles = (N + kTileN - 1) / kTileN;
   int ks = num_sms / tiles;
-  if (ks < 1) ks = 1;
-  if (ks > 4) ks = 4;
-  while (ks > 1 && (kTileN % ks != 0 || (K + kBK - 1) / kBK < ks)) --ks;
+  ks = ks >= 8 ? 8 : (ks >= 4 ? 4 : (ks >= 2 ? 2 : 1));           // 8 = the portable cluster size
+  while (ks > 1 && ((K + kBK - 1) / kBK < ks || world_size * ks > kFlagStride)) ks >>= 1;
   return ks;
+}
+
+// One launch: the K splits of a tile are the CTAs of a cluster (the attribute is set per launch because the
+// split count depends on the shape).
+template <class Kernel>
+int launch_gemv_tc(Kernel kernel, const CUtensorMap& tw, const CUtensorMap& tx, GemvTcParams p,
+                   cudaStream_t stream) {
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTotal);
+  if (e != cudaSuccess) return (int)e;
+  // The largest split (cluster size) not above the planned one whose clusters are all resident at
+  // once: one wave streams the weights fastest, and with several ranks it is required, because the
+  // CTAs of a tile wait for the same tile's CTAs on the peers (every rank arrives at the same split:
+  // same shape, same GPU).  A world of one whose tiles alone exceed the GPU runs in waves.
+  int ks = p.ksplit;
+  while (ks > 1 && check_co_resident(kernel, p.tiles * ks, kThreads, kSmemTotal, ks) != 0) ks >>= 1;
+  if (p.world_size > 1) {
+    if (int rc = check_co_resident(kernel, p.tiles * ks, kThreads, kSmemTotal, ks)) return rc;
+  }
+  p.ksplit = ks;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)(p.tiles * p.ksplit), 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = kSmemTotal;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)p.ksplit;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  e = cudaLaunchKernelEx(&cfg, kernel, tw, tx, p);
+  if (e != cudaSuccess) return (int)e;
+  return (int)cudaGetLastError();
 }
 
 }  // namespace
 
 size_t gemv_tc_workspace_bytes(int N, int K, int world_size, int num_sms, size_t* flags_offset,
-                               size_t* inbox_offset, int* tiles, int* ksplit, bool tagged) {
+                               size_t* inbox_offset, int* tiles, int* ksplit, bool tagged,
+                               size_t* counters_offset) {
   int t = (N + kTileN - 1) / kTileN;
-  int ks = pick_ksplit(N, K, num_sms);
-  size_t flags_off = 256;
+  int ks = pick_ksplit(N, K, num_sms, world_size);
+  size_t counters_off = 256;
+  size_t counters_bytes = (size_t)t * ks * 4;
+  size_t flags_off = (counters_off + counters_bytes + 255) & ~(size_t)255;
   size_t flags_bytes = (size_t)2 * t * kFlagStride * 4;
   size_t inbox_off = (flags_off + flags_bytes + 255) & ~(size_t)255;
-  size_t inbox_bytes = (size_t)2 * world_size * ks * kBatchN * N * (tagged ? 8 : 4);
+  size_t inbox_bytes = (size_t)2 * world_size * kBatchN * N * (tagged ? 8 : 4);
+  if (counters_offset) *counters_offset = counters_off;
   if (flags_offset) *flags_offset = flags_off;
   if (inbox_offset) *inbox_offset = inbox_off;
   if (tiles) *tiles = t;
@@ -413,7 +507,7 @@ int launch_gemv_all_reduce_tc(const GemvArgs& a, int num_sms, cudaStream_t strea
   p.timeout_ns = a.timeout_ns;
   p.status = a.status;
   gemv_tc_workspace_bytes(a.N, a.K, a.pv.world_size, num_sms, &p.flags_offset, &p.inbox_offset, &p.tiles,
-                          &p.ksplit, tagged);
+                          &p.ksplit, tagged, &p.counters_offset);
   if (p.world_size * p.ksplit > kFlagStride) return cudaErrorInvalidValue;
   CUtensorMap tw, tx;
   if (weights_nk) {
@@ -422,41 +516,22 @@ int launch_gemv_all_reduce_tc(const GemvArgs& a, int num_sms, cudaStream_t strea
     if (encode(&tw, a.w, (uint64_t)a.N, (uint64_t)a.K, 64, kBK)) return cudaErrorInvalidValue;       // [K, N]
   }
   if (encode(&tx, a.x, (uint64_t)a.K, (uint64_t)a.batch, kBK, kBatchN)) return cudaErrorInvalidValue;
-  if (weights_nk) {
-    if (tagged) {
-      cudaError_t e = cudaFuncSetAttribute(gemv_tc_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           (int)kSmemTotal);
-      if (e != cudaSuccess) return (int)e;
-      gemv_tc_kernel<true, true><<<p.tiles * p.ksplit, kThreads, kSmemTotal, stream>>>(tw, tx, p);
-    } else {
-      cudaError_t e = cudaFuncSetAttribute(gemv_tc_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           (int)kSmemTotal);
-      if (e != cudaSuccess) return (int)e;
-      gemv_tc_kernel<false, true><<<p.tiles * p.ksplit, kThreads, kSmemTotal, stream>>>(tw, tx, p);
-    }
-    return (int)cudaGetLastError();
-  }
-  if (tagged) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)kSmemTotal);
-    if (e != cudaSuccess) return (int)e;
-    gemv_tc_kernel<true><<<p.tiles * p.ksplit, kThreads, kSmemTotal, stream>>>(tw, tx, p);
-    return (int)cudaGetLastError();
-  }
-  cudaError_t e = cudaFuncSetAttribute(gemv_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)kSmemTotal);
-  if (e != cudaSuccess) return (int)e;
-  gemv_tc_kernel<false><<<p.tiles * p.ksplit, kThreads, kSmemTotal, stream>>>(tw, tx, p);
-  return (int)cudaGetLastError();
+  if (weights_nk)
+    return tagged ? launch_gemv_tc(gemv_tc_kernel<true, true>, tw, tx, p, stream)
+                  : launch_gemv_tc(gemv_tc_kernel<false, true>, tw, tx, p, stream);
+  return tagged ? launch_gemv_tc(gemv_tc_kernel<true>, tw, tx, p, stream)
+                : launch_gemv_tc(gemv_tc_kernel<false>, tw, tx, p, stream);
 }
 
 }  // namespace smr
 
 // ---------------------------------------------------------------------------
-// Allocation-free C entry point (see gemv_noalloc.h).  The scratch that the
-// kernel above normally finds in a symmetric workspace lives in this array;
-// offset 0 holds the one-entry "workspace base of every rank" table, offset 64 the
-// 32-byte Status record of the last calls, the workspace itself starts at offset 256.
+// Allocation-free C entry point (see gemv_noalloc.h).  The global memory that the
+// kernel above needs besides its operands lives in this array: offset 0 holds the
+// one-entry "workspace base of every rank" table the kernel reads, offset 64 the
+// 32-byte Status record its bounded waits report into; a (here unused) workspace
+// would start at offset 256.  In a world of one the K splits of a tile meet in
+// shared memory, so nothing else is kept in global memory between or during calls.
 // ---------------------------------------------------------------------------
 #include <mutex>
 #include <stdio.h>
@@ -471,8 +546,6 @@ constexpr int kMaxDevices = 64;
 std::mutex g_noalloc_mu;
 unsigned char* g_noalloc_base[kMaxDevices] = {};   // device address of the array, per device
 int g_noalloc_sms[kMaxDevices] = {};
-int g_noalloc_last_n[kMaxDevices] = {};            // shape of the previous call: the flag layout follows it
-int g_noalloc_last_k[kMaxDevices] = {};
 constexpr size_t kNoallocStatusOffset = 64;
 
 int noalloc_fail(int code, char* err, int err_len, const char* what, const char* detail = "") {
@@ -488,7 +561,7 @@ extern "C" int smr_gemv_bf16_noalloc(const void* x, const void* w, void* out, in
   if (batch < 1 || batch > SMR_GEMV_NOALLOC_MAX_BATCH)
     return noalloc_fail(1, err, err_len, "batch must be between 1 and 16");
   if (N < 8 || N > SMR_GEMV_NOALLOC_MAX_N || N % 8 != 0)
-    return noalloc_fail(1, err, err_len, "N must be a multiple of 8 and at most 8192 (the scratch array is sized for that)");
+    return noalloc_fail(1, err, err_len, "N must be a multiple of 8 and at most 8192 (the limit of this entry point)");
   if (K < 8 || K % 8 != 0) return noalloc_fail(1, err, err_len, "K must be a positive multiple of 8");
   if (x == nullptr || w == nullptr || out == nullptr || ((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) % 16 != 0)
     return noalloc_fail(2, err, err_len, "x, w and out must be non-null and 16-byte aligned");
@@ -520,13 +593,6 @@ extern "C" int smr_gemv_bf16_noalloc(const void* x, const void* w, void* out, in
     base = g_noalloc_base[dev];
     sms = g_noalloc_sms[dev];
   }
-  bool new_layout;
-  {
-    std::lock_guard<std::mutex> lock(g_noalloc_mu);
-    new_layout = g_noalloc_last_n[dev] != N || g_noalloc_last_k[dev] != K;
-    g_noalloc_last_n[dev] = N;
-    g_noalloc_last_k[dev] = K;
-  }
 
   GemvTcParams p{};
   p.out = static_cast<__nv_bfloat16*>(out);
@@ -535,9 +601,9 @@ extern "C" int smr_gemv_bf16_noalloc(const void* x, const void* w, void* out, in
   p.buffers = reinterpret_cast<void* const*>(base);
   p.timeout_ns = 2000000000ull;
   p.status = reinterpret_cast<Status*>(base + kNoallocStatusOffset);
-  size_t need = gemv_tc_workspace_bytes(N, K, 1, sms, &p.flags_offset, &p.inbox_offset, &p.tiles, &p.ksplit, false);
-  if (need + 256 > (size_t)SMR_GEMV_NOALLOC_SCRATCH_BYTES)
-    return noalloc_fail(1, err, err_len, "this shape needs more scratch than the static array holds");
+  // tiles and K splits of this shape; the offsets describe a workspace that a world of one never touches
+  gemv_tc_workspace_bytes(N, K, 1, sms, &p.flags_offset, &p.inbox_offset, &p.tiles, &p.ksplit, false,
+                          &p.counters_offset);
   CUtensorMap tw, tx;
   try {
     if (encode(&tw, w, (uint64_t)N, (uint64_t)K, 64, kBK) || encode(&tx, x, (uint64_t)K, (uint64_t)batch, kBK, kBatchN))
@@ -545,20 +611,8 @@ extern "C" int smr_gemv_bf16_noalloc(const void* x, const void* w, void* out, in
   } catch (const std::exception& ex) {
     return noalloc_fail(3, err, err_len, "CUDA driver: ", ex.what());
   }
-  // "CTAs done" must read zero when the kernel starts; an aborted earlier call may have left it set
-  e = cudaMemsetAsync(base + 256 + 4, 0, 4, stream);
-  if (e != cudaSuccess) return noalloc_fail(3, err, err_len, "cudaMemsetAsync: ", cudaGetErrorString(e));
-  if (new_layout) {
-    // Where the arrival flags sit depends on N and K: after a call of another shape their slots hold
-    // that call's partial sums.  A flag is "set" when it equals the call number, so zeros are safe.
-    e = cudaMemsetAsync(base + 256 + p.flags_offset, 0, p.inbox_offset - p.flags_offset, stream);
-    if (e != cudaSuccess) return noalloc_fail(3, err, err_len, "cudaMemsetAsync(flags): ", cudaGetErrorString(e));
-  }
-  e = cudaFuncSetAttribute(gemv_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTotal);
-  if (e != cudaSuccess) return noalloc_fail(3, err, err_len, "cudaFuncSetAttribute: ", cudaGetErrorString(e));
-  gemv_tc_kernel<false><<<p.tiles * p.ksplit, kThreads, kSmemTotal, stream>>>(tw, tx, p);
-  e = cudaGetLastError();
-  if (e != cudaSuccess) return noalloc_fail(3, err, err_len, "kernel launch: ", cudaGetErrorString(e));
+  int rc = launch_gemv_tc(gemv_tc_kernel<false>, tw, tx, p, stream);
+  if (rc != 0) return noalloc_fail(3, err, err_len, "kernel launch: ", cudaGetErrorString((cudaError_t)rc));
   return 0;
 }
 

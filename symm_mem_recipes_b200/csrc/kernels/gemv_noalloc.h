@@ -7,16 +7,18 @@
 // process that may not touch that process's allocator, or code running between
 // the begin and end of a region where allocation would synchronise the device.
 // Such a caller cannot create the symmetric workspace that `gemv_all_reduce`
-// sets up on first use, so the library carries the workspace itself.
+// sets up on first use, so the library carries what the kernel needs itself.
 //
 //     out[b, n] = sum_k x[b, k] * w[k, n]      bf16 in, fp32 accumulate, bf16 out
 //
 // on ONE GPU (a world of one: nothing crosses NVLink), computed by the same
-// tcgen05 kernel as `gemv_all_reduce`.  That kernel splits K over several CTAs
-// per column tile and combines the partial sums through scratch memory; here
-// the scratch is a file-scope `static __device__` array of
-// SMR_GEMV_NOALLOC_SCRATCH_BYTES (about 4 MiB) that every GPU loading the
-// library holds until the process exits.
+// tcgen05 kernel as `gemv_all_reduce`.  The global memory that kernel needs
+// besides its operands — the table through which it finds its workspace and
+// the status record its bounded waits report into — sits in a file-scope
+// `static __device__` array of SMR_GEMV_NOALLOC_SCRATCH_BYTES (4 KiB) that
+// every GPU loading the library holds until the process exits.  (The K splits
+// of a column tile meet in shared memory; with one rank nothing else is parked
+// in global memory.)
 //
 // What the caller must know:
 //  * Limits: 1 <= batch <= SMR_GEMV_NOALLOC_MAX_BATCH, N <= SMR_GEMV_NOALLOC_MAX_N,
@@ -25,27 +27,23 @@
 //    launched.
 //  * x is [batch, K], w is [K, N], out is [batch, N]; contiguous bf16 in device
 //    memory of the current device, 16-byte aligned.  The caller owns them.
-//  * The first call on each device resolves the device address of the scratch
-//    array (cudaGetSymbolAddress) and writes one pointer into it with a
-//    blocking copy.  Make that first call before any stream capture and outside
-//    any region that must not synchronise.  Later calls only enqueue work on
+//  * The first call on each device resolves the device address of the array
+//    (cudaGetSymbolAddress) and writes one pointer into it with a blocking
+//    copy.  Make that first call before any stream capture and outside any
+//    region that must not synchronise.  Later calls only enqueue work on
 //    `stream`.
 //  * No call allocates: no cudaMalloc, no cudaFree, no framework allocator.
-//  * All calls on a device share the one scratch array, which keeps whatever
-//    the previous call left in it.  The kernel's own bookkeeping tolerates
-//    that (the entry point clears the one counter that must start at zero,
-//    and the arrival flags whenever N or K differ from the previous call on
-//    the device, because their place in the array follows the shape), but two
-//    calls that overlap in time on the same GPU — different streams, or two
-//    host threads — race on it and produce garbage.  Order them on one stream
-//    or with events.
+//  * All calls on a device share the one array, which keeps whatever the
+//    previous call left in it (the pointer table, and the status record of a
+//    failed call until it is queried).  Two calls that overlap in time on the
+//    same GPU — different streams, or two host threads — would share the status
+//    record; order them on one stream or with events.
 //  * A return value of 0 means "enqueued", not "done".  The CTAs of the kernel
-//    wait for one another (the K splits of a column tile meet in the scratch),
-//    each wait bounded at 2 s.  If a wait runs out — in practice only when the
-//    kernel's CTAs cannot all be resident because something else holds the
-//    SMs — the kernel records why in a status word inside the same array and
-//    returns with `out` UNWRITTEN.  smr_gemv_bf16_noalloc_status() reads that
-//    word; call it wherever you would otherwise synchronise.
+//    wait for one another (the K splits of a column tile form a cluster), each
+//    wait bounded at 2 s.  If a wait runs out the kernel records why in the
+//    status record and returns with `out` UNWRITTEN.
+//    smr_gemv_bf16_noalloc_status() reads that record; call it wherever you
+//    would otherwise synchronise.
 //
 // Returns 0 when the kernel was enqueued, otherwise:
 //   1 a size is outside the limits above      2 a pointer is null or misaligned
@@ -55,7 +53,7 @@
 
 #define SMR_GEMV_NOALLOC_MAX_BATCH 16
 #define SMR_GEMV_NOALLOC_MAX_N 8192
-#define SMR_GEMV_NOALLOC_SCRATCH_BYTES (256 + 16640 + 2 * 4 * 16 * SMR_GEMV_NOALLOC_MAX_N * 4)
+#define SMR_GEMV_NOALLOC_SCRATCH_BYTES 4096
 
 #ifdef __cplusplus
 extern "C" {

@@ -152,7 +152,8 @@ int launch_gemv_all_reduce(const GemvArgs& args, cudaStream_t stream);
 // `tagged`: partials travel as {fp32, call number} words and are polled directly (no flags, no
 // release fence); twice the inbox.  Meant for batch <= 4.
 size_t gemv_tc_workspace_bytes(int N, int K, int world_size, int num_sms, size_t* flags_offset,
-                               size_t* inbox_offset, int* tiles, int* ksplit, bool tagged = false);
+                               size_t* inbox_offset, int* tiles, int* ksplit, bool tagged = false,
+                               size_t* counters_offset = nullptr);
 // `weights_nk`: `args.w` is [N, K] (K contiguous), the layout of the prefill GEMMs' B operand.
 int launch_gemv_all_reduce_tc(const GemvArgs& args, int num_sms, cudaStream_t stream, bool tagged = false,
                               bool weights_nk = false);

@@ -27,11 +27,13 @@ The upstream recipes stop at the single fused op; this module is how the ops
 compose in the workload they were written for (Llama-3-70B at TP8: hidden
 8192, 64 query / 8 KV heads of 128, FFN 28672).  Attention is PyTorch's
 scaled_dot_product_attention (rank-local).  Norms, RoPE and the activation are
-PyTorch compositions by default; `fused_glue=True` (or SMR_FUSED_GLUE=1) swaps
-in the single-pass kernels of `ops.layer_glue`: RMSNorm writes straight into
-the symmetric buffer the next all_gather_matmul reads (and folds in the
-residual add before it), RoPE rotates Q and K in place inside the QKV buffer,
-SiLU(gate) * up is one pass.  `fused_swiglu=True` (SMR_FUSED_SWIGLU=1) goes one
+the single-pass kernels of `ops.layer_glue` (`fused_glue`, on by default;
+SMR_FUSED_GLUE=0 or `fused_glue=False` falls back to PyTorch compositions):
+RMSNorm writes straight into the symmetric buffer the next all_gather_matmul
+reads (and folds in the residual add before it), RoPE rotates Q and K in place
+inside the QKV buffer, SiLU(gate) * up is one pass; in a decode step the
+column-parallel projections run on the package's tcgen05 GEMV and the
+attention of the new token is one kernel.  `fused_swiglu=True` (SMR_FUSED_SWIGLU=1) goes one
 step further for prefill: the gate and up weights are interleaved so that the
 activation is applied to the accumulators inside the all_gather_matmul epilogue.
 """
@@ -107,7 +109,7 @@ class LlamaTPDecoderLayer:
                  dtype: torch.dtype = torch.bfloat16, fused_glue: Optional[bool] = None,
                  fused_swiglu: Optional[bool] = None, shared_row_weights: Optional[bool] = None):
         self.cfg, self.device, self.group = cfg, device, group
-        self.fused_glue = (os.environ.get("SMR_FUSED_GLUE", "0") == "1") if fused_glue is None else bool(fused_glue)
+        self.fused_glue = (os.environ.get("SMR_FUSED_GLUE", "1") == "1") if fused_glue is None else bool(fused_glue)
         # SiLU(gate) * up inside the epilogue of the gate/up all_gather_matmul (prefill only)
         self.fused_swiglu = ((os.environ.get("SMR_FUSED_SWIGLU", "0") == "1") if fused_swiglu is None
                              else bool(fused_swiglu))

@@ -3,7 +3,7 @@
 Some hosts cannot allocate device memory where they need a GEMV: a serving
 loop whose memory all belongs to a pool, a plugin inside another process, a
 region that must not synchronise.  `smr_gemv_bf16_noalloc` serves them from a
-scratch array compiled into the library.  This test loads the exported C
+small array compiled into the library.  This test loads the exported C
 symbol with ctypes (no Python binding in between), runs it twice in a row and
 compares each result with the library's regular op, which allocates its
 workspace through `symm_mem`.  It is collected last so that a failure here
@@ -93,8 +93,8 @@ def test_noalloc_gemv_refuses_what_does_not_fit():
 
 @pytest.mark.gpu
 def test_noalloc_gemv_after_a_call_of_another_shape():
-    """The flags of a wide call sit where a narrow call keeps partial sums: the entry point clears
-    them when the shape changes, so alternating shapes stay correct."""
+    """Calls of different shapes (different tile counts and K splits) share the one static array:
+    alternating them stays correct and the status record stays clear."""
     torch.cuda.set_device(0)
     fn = _entry()
     g = torch.Generator().manual_seed(5)
