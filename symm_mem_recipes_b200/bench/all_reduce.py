@@ -43,9 +43,9 @@ def build_parser() -> argparse.ArgumentParser:
                     help="instead of the size sweep: the multimem kernel over CTA counts, unroll factors and both "
                          "barrier kinds at 16, 64 and 256 MiB (clamped to --max-bytes), one start-up")
     ap.add_argument("--one-shot-sweep", action="store_true",
-                    help="instead of the size sweep: the one-shot kernel over its launch knobs (CTAs, threads, "
-                         "vectors per thread, barrier kind, rotated walk) at 4 KiB, 64 KiB, 1 MiB and 8 MiB, each "
-                         "variant first compared bit for bit with the default one")
+                    help="instead of the size sweep: the one-shot kernel over its CTA cap at 4 KiB, 64 KiB, 1 MiB and "
+                         "8 MiB beside NCCL and the upstream Triton kernel, each first compared bit for bit with the "
+                         "default launch")
     return ap
 
 
@@ -136,14 +136,9 @@ def main(argv=None, standalone: bool = True) -> int:
         import itertools
 
         def variants(nbytes):
-            if nbytes <= 64 * 1024:          # latency: the barrier and the CTA shape
-                for barrier, threads in itertools.product((0, 2), (256, 512)):
-                    yield dict(one_shot_barrier=barrier, one_shot_threads=threads, one_shot_max_blocks=32,
-                               one_shot_unroll=1)
-            else:                            # bandwidth: loads in flight
-                for barrier, blocks, unroll, rotate in itertools.product((0, 2), (32, 64, 128), (1, 2), (0, 1)):
-                    yield dict(one_shot_barrier=barrier, one_shot_max_blocks=blocks, one_shot_unroll=unroll,
-                               one_shot_rotate=rotate, one_shot_threads=512)
+            for blocks in (24, 32, 64, 128, 192):
+                if blocks == 32 or blocks * 512 * 16 <= nbytes:      # more CTAs than there is work: the same launch
+                    yield dict(one_shot_max_blocks=blocks)
 
         for nbytes in (4096, 65536, 1 << 20, 8 << 20):
             if nbytes > args.max_bytes:

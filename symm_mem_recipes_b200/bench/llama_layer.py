@@ -36,9 +36,6 @@ def build_parser() -> argparse.ArgumentParser:
                          "both: time the two; all: also with SiLU-mul inside the gate/up epilogue; "
                          "env: SMR_FUSED_GLUE / SMR_FUSED_SWIGLU")
     ap.add_argument("--breakdown", action="store_true", help="also print the device time of every phase of the layer")
-    ap.add_argument("--rs-variants", default="",
-                    help="comma-separated kernel variants of matmul_reduce_scatter to time besides the default: "
-                         "cta_pair, deep_strips, thread_stores, cta_pair+thread_stores")
     ap.add_argument("--tp", action="store_true",
                     help="also time the prefill without sequence parallelism (replicated activations, "
                          "matmul_all_reduce endings) against cuBLAS + NCCL all-reduce")
@@ -116,21 +113,6 @@ def main(argv=None, standalone: bool = True) -> int:
 
         if not section(f"matmul_reduce_scatter {name}", default_kernel):
             continue
-        for variant in [v for v in args.rs_variants.split(",") if v]:
-            def one_variant(variant=variant, name=name, k_local=k_local, a=a, b=b, shared=shared, wire=wire):
-                kw = {k: True for k in variant.split("+")}
-                got = smr.matmul_reduce_scatter(a, b, **kw)
-                symm_mem.check_status(dev)
-                # against the library composition (the default kernel's output may be gone after a reset)
-                same = bool(torch.allclose(got.float(), shared["ref"].float(), rtol=5e-2, atol=5e-2))
-                us_v = benchmark_with_event(lambda: smr.matmul_reduce_scatter(a, b, got, **kw), **bench)
-                symm_mem.check_status(dev)
-                emit({"op": "matmul_reduce_scatter_variant", "shape": name, "variant": variant, "world_size": world,
-                      "M": T, "N": cfg.hidden, "K_local": k_local, "matches_library": same,
-                      "smr_fused_us": round(us_v, 1), "cublas_plus_nccl_us": round(shared["us_r"], 1),
-                      "wire_gbs": round(wire / us_v / 1e3, 1), "speedup": round(shared["us_r"] / us_v, 3)})
-
-            section(f"matmul_reduce_scatter {name} variant {variant}", one_variant)
         del a, b, shared
     # ---- whole layer ----
     if not args.skip_layer:

@@ -25,8 +25,8 @@ def main() -> int:
     ap.add_argument("--ar-max-bytes", type=int, default=256 * 1024 * 1024)
     ap.add_argument("--layer-detail", action="store_true",
                     help="also time the opt-in kernel variants: the layer with the single-pass glue kernels and the "
-                         "SwiGLU epilogue, its phases, the prefill without sequence parallelism, the reduce-scatter "
-                         "variants, the tagged GEMV exchange, decode from one CUDA graph")
+                         "SwiGLU epilogue, its phases, the prefill without sequence parallelism, the tagged GEMV "
+                         "exchange, decode from one CUDA graph")
     ap.add_argument("--jobs", default="",
                     help="';'-separated list of '<driver> <its arguments>' (drivers: barrier, all_reduce, "
                          "all_gather_matmul, gemv_all_reduce, llama_layer) run in this order instead of --only")
@@ -71,8 +71,7 @@ def main() -> int:
         gemv_all_reduce.main(["--out", out("gemv")] + (["--extra-algos", "tc_tagged"] if args.layer_detail else []),
                              standalone=False)
     if "layer" in only:
-        llama_layer.main(["--out", out("layer")] + (["--fused-glue", "all", "--breakdown", "--tp", "--rs-variants",
-                                                     "cta_pair,deep_strips,thread_stores,cta_pair+thread_stores",
+        llama_layer.main(["--out", out("layer")] + (["--fused-glue", "all", "--breakdown", "--tp",
                                                      "--decode-graph", "2"]
                                                     if args.layer_detail
                                                     else []), standalone=False)

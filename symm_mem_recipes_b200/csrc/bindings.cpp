@@ -70,6 +70,17 @@ PeerView view_of(const CudaSymmAllocation& a) {
   return pv;
 }
 
+PeerPtrs ptrs_of(const CudaSymmAllocation& a) {
+  TORCH_CHECK(a.rendezvoused(), "symmetric allocation has not been rendezvoused");
+  TORCH_CHECK(a.world_size() <= 8, "this kernel takes its peers by value: at most 8 ranks");
+  PeerPtrs p{};
+  for (int r = 0; r < a.world_size(); ++r) {
+    p.buffers[r] = a.peer_ptr(r);
+    p.pads[r] = a.peer_pad(r);
+  }
+  return p;
+}
+
 torch::Tensor cuda_view(const std::shared_ptr<CudaSymmAllocation>& a, int rank,
                         std::vector<int64_t> sizes, torch::ScalarType dtype, int64_t offset_bytes,
                         bool multicast) {
@@ -425,23 +436,16 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   });
   m.def("one_shot_all_reduce", [](const std::shared_ptr<CudaSymmAllocation>& a, int64_t offset_bytes,
                                   torch::Tensor out, int64_t numel, int max_blocks, bool exit_barrier,
-                                  uint64_t timeout_ns, bool write_back, int threads, int unroll, int barrier,
-                                  bool rotate) {
+                                  uint64_t timeout_ns, bool write_back) {
     TORCH_CHECK(out.is_cuda() && out.is_contiguous() && out.scalar_type() == torch::kBFloat16 &&
                 out.numel() == numel, "bad output tensor");
     c10::cuda::CUDAGuard guard(a->device());
-    OneShotTuning tune;
-    tune.threads = threads;
-    tune.unroll = unroll;
-    tune.barrier = barrier;
-    tune.rotate = rotate;
-    rt_check(launch_one_shot_all_reduce(view_of(*a), (size_t)offset_bytes, out.data_ptr(), (size_t)numel,
-                                        max_blocks, exit_barrier, write_back, tune, timeout_ns,
+    rt_check(launch_one_shot_all_reduce(view_of(*a), ptrs_of(*a), (size_t)offset_bytes, out.data_ptr(),
+                                        (size_t)numel, max_blocks, exit_barrier, write_back, timeout_ns,
                                         status_for(a->device()), current_stream(a->device())),
              "one_shot_all_reduce");
   }, py::arg("alloc"), py::arg("offset_bytes"), py::arg("out"), py::arg("numel"), py::arg("max_blocks"),
-     py::arg("exit_barrier"), py::arg("timeout_ns"), py::arg("write_back") = false,
-     py::arg("threads") = 512, py::arg("unroll") = 1, py::arg("barrier") = 0, py::arg("rotate") = false);
+     py::arg("exit_barrier"), py::arg("timeout_ns"), py::arg("write_back") = false);
   m.def("ll_all_reduce_workspace_bytes", &ll_all_reduce_workspace_bytes);
   m.def("ll_all_reduce", [](const std::shared_ptr<CudaSymmAllocation>& workspace, torch::Tensor in,
                             torch::Tensor out, int64_t capacity_numel, int max_blocks, uint64_t timeout_ns) {
@@ -485,7 +489,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                         int block_n, int num_sms, int n_copy, uint64_t timeout_ns, bool cta_pair,
                         c10::optional<torch::Tensor> tail_scratch, int epilogue, int l2_hints,
                         c10::optional<torch::Tensor> trace, int lead, int push_ahead, int push_spread,
-                        bool push_plain_stores) {
+                        bool push_plain_stores, int push_pieces) {
     const auto dtype = a.scalar_type();
     const bool fp8 = dtype == at::kFloat8_e4m3fn;
     TORCH_CHECK(fp8 || dtype == torch::kBFloat16, "a must be bfloat16 or float8_e4m3fn");
@@ -568,6 +572,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     args.push_ahead = push_ahead;
     args.push_spread = push_spread;
     args.push_plain_stores = push_plain_stores ? 1 : 0;
+    args.push_pieces = push_pieces;
     if (trace.has_value()) {
       TORCH_CHECK(cta_pair && mode != 1, "the timing record belongs to the CTA-pair kernel");
       TORCH_CHECK(trace->is_cuda() && trace->get_device() == dev && trace->is_contiguous() &&
@@ -582,7 +587,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
      py::arg("flags"), py::arg("block_n"), py::arg("num_sms"), py::arg("n_copy"), py::arg("timeout_ns"),
      py::arg("cta_pair") = false, py::arg("tail_scratch") = py::none(), py::arg("epilogue") = 0,
      py::arg("l2_hints") = 0, py::arg("trace") = py::none(), py::arg("lead") = -1,
-     py::arg("push_ahead") = 0, py::arg("push_spread") = 0, py::arg("push_plain_stores") = false);
+     py::arg("push_ahead") = 0, py::arg("push_spread") = 0, py::arg("push_plain_stores") = false,
+     py::arg("push_pieces") = 0);
 
   m.def("check_push_schedule", &check_push_schedule);
   m.def("check_pair_work", &check_pair_work);
@@ -640,8 +646,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("matmul_rs_workspace_bytes", &matmul_rs_workspace_bytes);
   m.def("matmul_reduce_scatter", [](torch::Tensor a, torch::Tensor b, torch::Tensor out,
                                     const std::shared_ptr<CudaSymmAllocation>& workspace, int num_sms,
-                                    uint64_t timeout_ns, c10::optional<torch::Tensor> trace, bool deep_strips,
-                                    bool cta_pair, bool thread_stores) {
+                                    uint64_t timeout_ns, c10::optional<torch::Tensor> trace) {
     auto ok2d = [](const torch::Tensor& t) {
       return t.is_cuda() && t.dim() == 2 && t.is_contiguous() && t.scalar_type() == torch::kBFloat16;
     };
@@ -672,19 +677,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                   "trace must be an int64 CUDA tensor of at least 4 * num_sms elements");
       args.trace = reinterpret_cast<uint64_t*>(trace->data_ptr());
     }
-    args.deep_strips = deep_strips;
-    args.cta_pair = cta_pair;
-    args.thread_stores = thread_stores;
     rt_check(launch_matmul_reduce_scatter(args, current_stream(dev)), "matmul_reduce_scatter");
   }, py::arg("a"), py::arg("b"), py::arg("out"), py::arg("workspace"), py::arg("num_sms"),
-     py::arg("timeout_ns"), py::arg("trace") = py::none(), py::arg("deep_strips") = false,
-     py::arg("cta_pair") = false, py::arg("thread_stores") = false);
+     py::arg("timeout_ns"), py::arg("trace") = py::none());
 
   // all-reduce form: `out` [M, N] lives in the symmetric allocation `out_alloc` at `out_offset`
   m.def("matmul_all_reduce", [](torch::Tensor a, torch::Tensor b, torch::Tensor out,
                                 const std::shared_ptr<CudaSymmAllocation>& out_alloc, int64_t out_offset,
                                 const std::shared_ptr<CudaSymmAllocation>& workspace, int num_sms,
-                                uint64_t timeout_ns, bool cta_pair) {
+                                uint64_t timeout_ns) {
     auto ok2d = [](const torch::Tensor& t) {
       return t.is_cuda() && t.dim() == 2 && t.is_contiguous() && t.scalar_type() == torch::kBFloat16;
     };
@@ -714,14 +715,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     args.num_sms = num_sms;
     args.timeout_ns = timeout_ns;
     args.status = status_for(dev);
-    args.cta_pair = cta_pair;
     args.all_reduce = true;
     args.ar_peers = ov.buffers;
     args.ar_mc = ov.multicast;
     args.ar_offset = (size_t)out_offset;
     rt_check(launch_matmul_reduce_scatter(args, current_stream(dev)), "matmul_all_reduce");
   }, py::arg("a"), py::arg("b"), py::arg("out"), py::arg("out_alloc"), py::arg("out_offset"), py::arg("workspace"),
-     py::arg("num_sms"), py::arg("timeout_ns"), py::arg("cta_pair") = false);
+     py::arg("num_sms"), py::arg("timeout_ns"));
 
   // ---- rank-local layer glue ----
   m.def("rms_norm", [](torch::Tensor x, c10::optional<torch::Tensor> residual, torch::Tensor w,

@@ -78,44 +78,6 @@ __device__ __forceinline__ bool blockwise_barrier(uint32_t* const* pads, uint32_
   return __syncthreads_and(ok) != 0;
 }
 
-// The same protocol on the same slots with the two halves on different threads: thread t < WS
-// sends to peer t while thread 32 + t (another warp) already waits for peer t, so the wait does
-// not start one NVLink round trip late; the wait spins on a relaxed CAS and is followed by ONE
-// acquire fence (as upstream spins: triton_barrier.py:127), instead of an acquire per attempt.
-// Needs at least 64 threads in the CTA; interoperates with blockwise_barrier on the peers.
-__device__ __forceinline__ bool blockwise_barrier_split(uint32_t* const* pads, uint32_t block_id,
-                                                        int rank, int world_size,
-                                                        uint64_t timeout_ns, Status* st, uint32_t where) {
-  __syncthreads();  // the CTA's earlier writes precede the release
-  bool ok = true;
-  const uint32_t tid = flat_tid();
-  const uint32_t slot_base = block_id * (uint32_t)world_size;
-  if (tid < (uint32_t)world_size) {
-    uint32_t* send = pads[tid] + slot_base + rank;
-    Deadline d(timeout_ns);
-    while (cas_release_sys(send, 0u, 1u) != 0u) {
-      if (!d.alive()) {
-        report_status(st, kTimeoutBarrierSend, rank, block_id, tid, where);
-        ok = false;
-        break;
-      }
-    }
-  } else if (tid >= 32u && tid < 32u + (uint32_t)world_size) {
-    const uint32_t peer = tid - 32u;
-    uint32_t* wait = pads[rank] + slot_base + peer;
-    Deadline d(timeout_ns);
-    while (cas_relaxed_sys(wait, 1u, 0u) != 1u) {
-      if (!d.alive()) {
-        report_status(st, kTimeoutBarrierWait, rank, block_id, peer, where);
-        ok = false;
-        break;
-      }
-    }
-    fence_acq_rel_sys();
-  }
-  return __syncthreads_and(ok) != 0;
-}
-
 // ---------------------------------------------------------------------------
 // Epoch barrier: the low-latency barrier of the all-reduce kernels.
 //

@@ -67,12 +67,6 @@ __device__ __forceinline__ uint32_t cas_acquire_sys(uint32_t* p, uint32_t cmp, u
                : "=r"(old) : "l"(p), "r"(cmp), "r"(val) : "memory");
   return old;
 }
-__device__ __forceinline__ uint32_t cas_relaxed_sys(uint32_t* p, uint32_t cmp, uint32_t val) {
-  uint32_t old;
-  asm volatile("atom.global.relaxed.sys.cas.b32 %0, [%1], %2, %3;"
-               : "=r"(old) : "l"(p), "r"(cmp), "r"(val) : "memory");
-  return old;
-}
 __device__ __forceinline__ void fence_acq_rel_sys() {
   asm volatile("fence.acq_rel.sys;" ::: "memory");
 }
@@ -124,6 +118,16 @@ __device__ __forceinline__ bool wait_ge_acquire_sys(const uint32_t* p, uint32_t 
                                                     uint64_t timeout_ns) {
   Deadline d(timeout_ns);
   while (ld_acquire_sys(p) < target) {
+    if (!d.alive()) return false;
+  }
+  return true;
+}
+// The same for a counter that only grows and may wrap: waits until it has reached `target`
+// (difference taken modulo 2^32; the counter is never more than 2^31 ahead or behind).
+__device__ __forceinline__ bool wait_reached_acquire_sys(const uint32_t* p, uint32_t target,
+                                                         uint64_t timeout_ns) {
+  Deadline d(timeout_ns);
+  while ((int32_t)(ld_acquire_sys(p) - target) < 0) {
     if (!d.alive()) return false;
   }
   return true;

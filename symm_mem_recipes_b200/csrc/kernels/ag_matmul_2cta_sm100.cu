@@ -95,7 +95,7 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
   uint32_t epoch = 0, flag_target = p.flag_target;
   if (p.mode == 2) {
     epoch = ld_relaxed_gpu(&p.header[0]) + 1u;
-    flag_target = epoch * (uint32_t)p.pieces;
+    flag_target = epoch * kArrivalUnits;
   }
 
   if (threadIdx.x == 0) {
@@ -163,7 +163,7 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
           }
           if (!local) {
             const uint64_t t0 = tr ? globaltimer_ns() : 0;
-            if (!wait_ge_acquire_sys(&p.flags[mblk], flag_target, p.timeout_ns)) {
+            if (!wait_reached_acquire_sys(&p.flags[mblk], flag_target, p.timeout_ns)) {
               report_status(p.status, kTimeoutFlag, p.rank, blockIdx.x, mblk, kWhereGemmProgress);
               failed = true;
               break;
@@ -593,6 +593,11 @@ int launch_ag_matmul_2cta(const AgMatmulArgs& a, cudaStream_t stream) {
     p.push_ahead = a.push_ahead > 0 ? a.push_ahead : 1;
     size_t block_vecs = (size_t)kBM * a.K * es / 16;
     p.pieces = block_vecs >= 8192 ? 16 : (block_vecs >= 1024 ? 4 : 1);
+    if (a.push_pieces > 0) {
+      if ((a.push_pieces & (a.push_pieces - 1)) != 0 || (uint32_t)a.push_pieces > kArrivalUnits) return cudaErrorInvalidValue;
+      p.pieces = a.push_pieces;
+      while (p.pieces > 1 && (size_t)p.pieces * 128 > block_vecs) p.pieces >>= 1;   // a piece feeds 128 threads at least once
+    }
   }
   p.flags = comm ? a.local_pad + kFlagSlotsBase + 2 : nullptr;
   p.flag_target = 1u;

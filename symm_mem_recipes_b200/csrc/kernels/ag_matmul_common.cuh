@@ -33,6 +33,9 @@ constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kCopyChunk = 16384;   // bytes per bulk copy
 constexpr int kStoreLag = 2;             // bulk stores allowed to still read smem
 constexpr int kFlagLag = 6;              // chunks after which a block's writes are drained
+// Push mode: a block's arrival counter grows by kArrivalUnits per call whatever the number of pieces
+// (each piece adds kArrivalUnits / pieces), so calls with different piece counts can share an allocation.
+constexpr uint32_t kArrivalUnits = 256;  // pieces: a power of two up to this
 
 struct AgMatmulParams {
   __nv_bfloat16* c;      // [M, N]; one byte per element when elem_bytes == 1
@@ -163,7 +166,7 @@ __device__ inline int push_pieces(const AgMatmulParams& p, int next, int n_ctas,
     }
     epilogue_group_sync();   // the group's stores precede the releases below
     if (etid < p.world_size)
-      red_add_release_sys(p.pads[etid] + kFlagSlotsBase + 2 + gblk, 1u);
+      red_add_release_sys(p.pads[etid] + kFlagSlotsBase + 2 + gblk, kArrivalUnits / (uint32_t)p.pieces);
   }
   return piece;
 }

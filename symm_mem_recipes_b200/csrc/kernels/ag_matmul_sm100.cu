@@ -192,7 +192,7 @@ ag_matmul_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
   uint32_t epoch = 0, flag_target = p.flag_target;
   if (p.mode == 2) {
     epoch = ld_relaxed_gpu(&p.header[0]) + 1u;
-    flag_target = epoch * (uint32_t)p.pieces;
+    flag_target = epoch * kArrivalUnits;
   }
 
   // ======================= copier CTAs (pull mode only) =======================
@@ -259,7 +259,7 @@ ag_matmul_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
           row0 -= p.rank * rows_per_rank;
         }
         if (!local) {
-          if (!wait_ge_acquire_sys(&p.flags[mblk], flag_target, p.timeout_ns)) {
+          if (!wait_reached_acquire_sys(&p.flags[mblk], flag_target, p.timeout_ns)) {
             report_status(p.status, kTimeoutFlag, p.rank, blockIdx.x, mblk, kWhereGemmProgress);
             failed = true;
             break;

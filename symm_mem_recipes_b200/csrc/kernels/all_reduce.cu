@@ -100,79 +100,55 @@ __device__ __forceinline__ Vec16 ld_16_relaxed_sys(const void* p) {
   return v;
 }
 
-// The barrier of the one-shot kernel, chosen at launch: 0 = blockwise_barrier (CAS protocol,
-// upstream's), 1 = the same protocol with sender and waiter on different threads and a relaxed
-// spin, 2 = epoch barrier (one store per peer, counts that only grow).
-struct OneShotBarrier {
-  int kind;
-  EpochBarrier epoch;
-  __device__ __forceinline__ OneShotBarrier(const PeerView& pv, int kind_)
-      : kind(kind_), epoch(pv.pads, kind_ == 2 ? blockIdx.x : 0u, pv.rank, pv.world_size) {}
-  __device__ __forceinline__ bool sync(const PeerView& pv, uint64_t timeout_ns, Status* st, uint32_t where) {
-    if (kind == 2) return epoch.sync(timeout_ns, st, where);
-    if (kind == 1) return blockwise_barrier_split(pv.pads, blockIdx.x, pv.rank, pv.world_size, timeout_ns, st, where);
-    return blockwise_barrier(pv.pads, blockIdx.x, pv.rank, pv.world_size, timeout_ns, st, where);
-  }
-  __device__ __forceinline__ void finish() {
-    if (kind == 2) epoch.finish();
-  }
-};
-
-// U elements (16-byte vectors) per thread and iteration: U x WS peer loads in flight per thread.
-// `rotate`: rank r walks the vectors starting at r * n_vec / WS (wrapping), so that at any moment
-// the ranks read different regions of every peer's buffer; the sum of an element is rank-ordered
-// either way (same bits on every rank, symm_mem_recipes/triton_one_shot_all_reduce.py:84-89).
+// U elements (16-byte vectors) per thread and iteration: U x WS peer loads in flight per thread,
+// up to 128 CTAs (measured on 2 and 4 GPUs: 32 CTAs with one element per thread leave the links
+// two to four times under-used).  The peers' addresses arrive by value in the kernel's parameters,
+// not through the device table: no dependent load sits in front of the barrier's first store.
+// Epoch barrier (one release store per peer) on entry; the sum of an element is rank-ordered:
+// same bits on every rank (symm_mem_recipes/triton_one_shot_all_reduce.py:84-89).
 template <int WS, int U>
 __global__ void __launch_bounds__(kArThreads)
-one_shot_all_reduce_kernel(PeerView pv, size_t offset_bytes, Vec16* __restrict__ out,
-                           size_t n_vec, bool exit_barrier, bool write_back, int barrier_kind, bool rotate,
-                           uint64_t timeout_ns, Status* st) {
-  // the pointer table is read before the barrier: those loads overlap the barrier's round trip
+one_shot_all_reduce_kernel(PeerPtrs ptrs, int rank, size_t offset_bytes, Vec16* __restrict__ out,
+                           size_t n_vec, bool exit_barrier, bool write_back, uint64_t timeout_ns, Status* st) {
+  EpochBarrier bar(ptrs.pads, blockIdx.x, rank, WS);
+  if (!bar.sync(timeout_ns, st, kWhereOneShotEntry)) return;
+
   const Vec16* src[WS];
 #pragma unroll
   for (int r = 0; r < WS; ++r)
-    src[r] = reinterpret_cast<const Vec16*>(static_cast<const char*>(pv.buffers[r]) + offset_bytes);
-  OneShotBarrier bar(pv, barrier_kind);
-  if (!bar.sync(pv, timeout_ns, st, kWhereOneShotEntry)) return;
+    src[r] = reinterpret_cast<const Vec16*>(static_cast<const char*>(ptrs.buffers[r]) + offset_bytes);
 
   const size_t stride = (size_t)gridDim.x * blockDim.x;
-  const size_t rot = rotate ? ((n_vec / WS) * (size_t)pv.rank) & ~(size_t)31 : 0;
   for (size_t k = (size_t)blockIdx.x * blockDim.x + threadIdx.x; k < n_vec; k += (size_t)U * stride) {
     Vec16 v[U][WS];
-    size_t idx[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const size_t ku = k + (size_t)u * stride;
-      size_t i = ku + rot;
-      if (i >= n_vec) i -= n_vec;
-      idx[u] = ku < n_vec ? i : n_vec;
-      if (ku < n_vec) {
+      const size_t i = k + (size_t)u * stride;
+      if (i < n_vec) {
 #pragma unroll
         for (int r = 0; r < WS; ++r) v[u][r] = ld_16(src[r] + i);
       }
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      if (idx[u] < n_vec) {
+      const size_t i = k + (size_t)u * stride;
+      if (i < n_vec) {
         Vec16 acc = {0u, 0u, 0u, 0u};
 #pragma unroll
         for (int r = 0; r < WS; ++r) acc = add_bf16x8(acc, v[u][r]);
-        st_16(out + idx[u], acc);
+        st_16(out + i, acc);
       }
     }
   }
 
   if (exit_barrier) {
     // proves that every peer has finished reading this rank's buffer
-    if (bar.sync(pv, timeout_ns, st, kWhereOneShotExit) && write_back) {
+    if (bar.sync(timeout_ns, st, kWhereOneShotExit) && write_back) {
       // in-place form: now the sum may replace this rank's input; every thread
       // copies back exactly the vectors it produced above
-      Vec16* self = reinterpret_cast<Vec16*>(static_cast<char*>(pv.buffers[pv.rank]) + offset_bytes);
-      for (size_t k = (size_t)blockIdx.x * blockDim.x + threadIdx.x; k < n_vec; k += stride) {
-        size_t i = k + rot;
-        if (i >= n_vec) i -= n_vec;
+      Vec16* self = reinterpret_cast<Vec16*>(static_cast<char*>(ptrs.buffers[rank]) + offset_bytes);
+      for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += stride)
         st_16(self + i, ld_16(out + i));
-      }
     }
   }
   bar.finish();
@@ -392,38 +368,33 @@ int launch_wait_flag(const uint32_t* flag, uint32_t target, uint64_t timeout_ns,
     default: return cudaErrorInvalidValue;                                                      \
   }
 
-int launch_one_shot_all_reduce(const PeerView& pv, size_t offset_bytes, void* out, size_t numel,
-                               int max_blocks, bool exit_barrier, bool write_back, const OneShotTuning& tune,
+int launch_one_shot_all_reduce(const PeerView& pv, const PeerPtrs& ptrs, size_t offset_bytes, void* out,
+                               size_t numel, int max_blocks, bool exit_barrier, bool write_back,
                                uint64_t timeout_ns, Status* status, cudaStream_t stream) {
   if (write_back && !exit_barrier) return cudaErrorInvalidValue;
   if (numel % 8 != 0 || offset_bytes % 16 != 0) return cudaErrorInvalidValue;
-  if (tune.barrier < 0 || tune.barrier > 2) return cudaErrorInvalidValue;
-  int threads = tune.threads;
-  if (threads != 128 && threads != 256 && threads != 512) return cudaErrorInvalidValue;
   size_t n_vec = numel / 8;
-  if ((uint32_t)max_blocks * pv.world_size > kBlockSlots) max_blocks = kBlockSlots / pv.world_size;
-  if (tune.barrier == 2 && (uint32_t)max_blocks > kArMaxBlocks) max_blocks = (int)kArMaxBlocks;
-  // U x WS vectors of 16 bytes live in registers per thread: at most 16
-  int unroll = tune.unroll;
-  while (unroll > 1 && unroll * pv.world_size > 16) unroll >>= 1;
-  if (unroll != 1 && unroll != 2 && unroll != 4) return cudaErrorInvalidValue;
-  size_t per_block = (size_t)threads * unroll;
+  if (max_blocks < 1) max_blocks = 1;
+  if ((uint32_t)max_blocks > kArMaxBlocks) max_blocks = (int)kArMaxBlocks;     // one epoch-barrier group per CTA
+  // two vectors per thread once the message is worth it (U x WS vectors live in registers: at most 16)
+  const int unroll = (pv.world_size <= 8 && n_vec >= (size_t)2 * kArThreads * 8) ? 2 : 1;
+  size_t per_block = (size_t)kArThreads * unroll;
   size_t want = (n_vec + per_block - 1) / per_block;
   int blocks = (int)(want < 1 ? 1 : (want > (size_t)max_blocks ? (size_t)max_blocks : want));
-#define SMR_ONE_SHOT(WS_, U_)                                                                       \
-  one_shot_all_reduce_kernel<WS_, U_><<<blocks, threads, 0, stream>>>(                              \
-      pv, offset_bytes, static_cast<Vec16*>(out), n_vec, exit_barrier, write_back, tune.barrier,    \
-      tune.rotate, timeout_ns, status)
-#define SMR_ONE_SHOT_U(WS_)                                                                         \
-  if (unroll == 4) SMR_ONE_SHOT(WS_, 4); else if (unroll == 2) SMR_ONE_SHOT(WS_, 2); else SMR_ONE_SHOT(WS_, 1)
+#define SMR_ONE_SHOT(WS_)                                                                                    \
+  if (unroll == 2)                                                                                           \
+    one_shot_all_reduce_kernel<WS_, 2><<<blocks, kArThreads, 0, stream>>>(                                   \
+        ptrs, pv.rank, offset_bytes, static_cast<Vec16*>(out), n_vec, exit_barrier, write_back, timeout_ns, status); \
+  else                                                                                                       \
+    one_shot_all_reduce_kernel<WS_, 1><<<blocks, kArThreads, 0, stream>>>(                                   \
+        ptrs, pv.rank, offset_bytes, static_cast<Vec16*>(out), n_vec, exit_barrier, write_back, timeout_ns, status)
   switch (pv.world_size) {
-    case 1: SMR_ONE_SHOT_U(1); break;
-    case 2: SMR_ONE_SHOT_U(2); break;
-    case 4: SMR_ONE_SHOT_U(4); break;
-    case 8: if (unroll == 2) SMR_ONE_SHOT(8, 2); else SMR_ONE_SHOT(8, 1); break;
+    case 1: SMR_ONE_SHOT(1); break;
+    case 2: SMR_ONE_SHOT(2); break;
+    case 4: SMR_ONE_SHOT(4); break;
+    case 8: SMR_ONE_SHOT(8); break;
     default: return cudaErrorInvalidValue;
   }
-#undef SMR_ONE_SHOT_U
 #undef SMR_ONE_SHOT
   return last_error();
 }

@@ -18,6 +18,13 @@ struct PeerView {
   int world_size;
 };
 
+// The same addresses by value (kernel parameters), for latency-bound kernels that cannot afford a
+// dependent load from the tables before their first remote access; worlds of up to 8 ranks.
+struct PeerPtrs {
+  void* buffers[8];
+  uint32_t* pads[8];
+};
+
 // ---- barrier ---------------------------------------------------------------
 // `kind`: 0 = blockwise_barrier (CAS protocol, pad returns to zero), 1 = epoch barrier (one store per
 // peer, counters only grow), 2 = NVLS barrier (one multimem.red per rank; needs a multicast mapping).
@@ -41,14 +48,8 @@ int launch_wait_flag(const uint32_t* flag, uint32_t target, uint64_t timeout_ns,
 // `offset_bytes` is the offset of the tensor inside the symmetric payload.
 // `write_back` (needs exit_barrier): after the exit barrier the sum also replaces this
 // rank's symmetric input, i.e. the in-place form used by the dispatcher.
-struct OneShotTuning {
-  int threads = 512;    // per CTA: 128, 256 or 512
-  int unroll = 1;       // 16-byte vectors per thread and iteration (1, 2, 4; unroll x WS <= 16)
-  int barrier = 0;      // 0 CAS (upstream's protocol), 1 CAS with split sender / waiter threads, 2 epoch barrier
-  bool rotate = false;  // rank r starts its walk at r / WS of the buffer
-};
-int launch_one_shot_all_reduce(const PeerView& pv, size_t offset_bytes, void* out, size_t numel,
-                               int max_blocks, bool exit_barrier, bool write_back, const OneShotTuning& tune,
+int launch_one_shot_all_reduce(const PeerView& pv, const PeerPtrs& ptrs, size_t offset_bytes, void* out,
+                               size_t numel, int max_blocks, bool exit_barrier, bool write_back,
                                uint64_t timeout_ns, Status* status, cudaStream_t stream);
 // Low-latency (push, tagged words) all-reduce for small messages.  `pv` is the view of a
 // symmetric workspace of ll_all_reduce_workspace_bytes(capacity_numel, WS); `in` / `out` are
@@ -121,6 +122,9 @@ struct AgMatmulArgs {
   // (the shard leaves this GPU once; every rank, the sender included, receives it from the switch),
   // 1 = plain stores to every peer and a local copy (nothing loops back through the switch)
   int push_plain_stores;
+  // push mode: pieces a 128-row block is cut into for the broadcast (0 = the launcher's choice); a block
+  // has arrived when all of its pieces have, each pushed by another CTA
+  int push_pieces;
 };
 int launch_ag_matmul(const AgMatmulArgs& args, cudaStream_t stream);
 // Same contract on CTA pairs (tcgen05 cta_group::2, 256 x BN tiles); modes 0 and 2 only.
@@ -172,9 +176,6 @@ struct MatmulRsArgs {
   uint64_t timeout_ns;
   Status* status;
   uint64_t* trace;     // optional [num_sms][4] %globaltimer stamps per CTA (start, entered, GEMM done, reduced)
-  bool deep_strips;    // 3-stage ring and five epilogue strips on the wire instead of 4 stages and two
-  bool cta_pair;       // tcgen05 cta_group::2 main loop (256 x 256 tiles on CTA pairs), 5 stages, four strips
-  bool thread_stores;  // 1-CTA kernel: strips leave shared memory by coalesced stores of the epilogue threads
   // all-reduce form: every rank ends up with the whole [M, N] sum in a SYMMETRIC output (`out` is unused);
   // each rank reduces its rows and broadcasts them (multimem.st when `ar_mc`, else stores to every peer)
   bool all_reduce;
@@ -183,9 +184,7 @@ struct MatmulRsArgs {
   size_t ar_offset;        // offset of the output tensor inside that payload
 };
 size_t matmul_rs_workspace_bytes(int M, int N);
-// Dispatches on `cta_pair` / `deep_strips`; same workspace layout and result bits for every variant.
 int launch_matmul_reduce_scatter(const MatmulRsArgs& args, cudaStream_t stream);
-int launch_matmul_reduce_scatter_2cta(const MatmulRsArgs& args, cudaStream_t stream);
 
 // ---- rank-local layer glue (layer_glue.cu): bf16 data, fp32 math, one pass each ----
 // out[rows, H] = RMSNorm(x (+ residual)) * w.  With `residual`, `sum_out` (optional) receives

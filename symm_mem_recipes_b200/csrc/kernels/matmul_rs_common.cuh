@@ -1,5 +1,5 @@
-// Pieces shared by the 1-CTA and the CTA-pair forms of the fused GEMM +
-// reduce-scatter kernel: tile geometry, the strip-major inbox layout, the
+// Pieces of the fused GEMM + reduce-scatter kernel that its launcher and the host-side
+// schedule checks share: tile geometry, the strip-major inbox layout, the
 // kernel parameters, the ordered reduction of arrived partials and the
 // tensor-map builder.
 #pragma once

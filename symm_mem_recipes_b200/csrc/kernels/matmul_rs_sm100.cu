@@ -2,31 +2,41 @@
 //     out_r[M/WS, N] = sum over ranks s of ( A_s[M, K_s] * B_s[N, K_s]^T )[rows of rank r]
 // No upstream counterpart (the upstream package has the all-gather half only).
 //
-//  * The GEMM is the tcgen05 / TMEM pipeline of ag_matmul_sm100.cu (TMA
-//    producer warp, MMA warp, four epilogue warps, two TMEM accumulators).
-//  * Tiles are visited by destination rank: rank+1 first, ..., own rows last,
-//    so the links are busy from the first tile and nothing waits on the wire
-//    at the end.
-//  * Epilogue: accumulator -> bf16 -> a shared-memory strip of [128 rows x 64
-//    columns] (16 KB, 16-byte chunks XOR-swizzled by row so that the writes do
-//    not collide on banks) -> ONE bulk copy (cp.async.bulk, shared -> global)
-//    of 16 contiguous KB into the DESTINATION rank's inbox.  The inbox is
-//    internal scratch, so it is laid out strip by strip,
-//    [src][row block][N tile][strip][16 KB], exactly as the strips sit in
-//    shared memory: every store is one long contiguous write over NVLink (a
-//    row-major inbox would turn it into 128-byte fragments 16 KB apart, which
-//    measured 400 GB/s).  Two strips alternate, so the next one is converted
-//    while the previous one is on the wire.  A tile's arrival counter on the
-//    destination gets +1 (red.release.sys) once the tile's stores have
-//    completed, which is checked one tile later so the epilogue never waits
-//    for the wire.
-//  * Reduce: after its GEMM tiles every CTA takes output tiles of its own rank,
-//    waits (bounded) until WS partials have arrived, sums them in rank order in
-//    fp32 and writes bf16.  All ranks thus produce identical bits.
-//  * An entry barrier over the signal pad proves that every rank has finished
-//    reducing the previous call before its inbox is overwritten.  Counters
-//    count calls (epoch word in the pad), so nothing is reset between calls.
+//  * Main loop on CTA pairs (tcgen05 `cta_group::2`), as in ag_matmul_2cta_sm100.cu: two CTAs
+//    on neighbouring SMs multiply one [256 x 256] tile, each staging its own 128 rows of A and
+//    its own half of the B tile (ordinary TMA loads, no multicast qualifier); the leader's MMA
+//    thread issues one MMA per 16 elements of K and each CTA finds its 128 accumulator rows in
+//    its own TMEM.  Six 32 KB stages.
+//  * Row blocks are visited by destination rank: rank+1 first, ..., own rows last, so the links
+//    are busy from the first tile and nothing waits on the wire at the end.  The two row blocks
+//    of a pair are consecutive entries of that list, so they may belong to different
+//    destinations; each CTA converts, ships and signals its own block.  With an odd number of
+//    row blocks the last pair's second CTA multiplies zero rows (out-of-range TMA coordinates
+//    read as zero) and ships nothing.
+//  * Epilogue: accumulator -> bf16 -> a shared-memory strip of [128 rows x 64 columns] (16 KB,
+//    16-byte chunks XOR-swizzled by row so that the writes do not collide on banks) -> the
+//    128 epilogue threads copy it with coalesced 16-byte stores (512 contiguous bytes per warp
+//    instruction) into the DESTINATION rank's inbox.  The inbox is internal scratch, so it is
+//    laid out strip by strip, [src][row block][N tile][strip][16 KB], exactly as the strips sit
+//    in shared memory: every strip is one contiguous 16 KB write over NVLink.  Two strip
+//    buffers alternate.  A tile's arrival counter on the destination gets +1 (red.release.sys)
+//    after its last strip.  Measured on 4 GPUs against the other forms this kernel has had
+//    (one CTA per tile; strips leaving by bulk copies, two to five in flight): 1.21x cuBLAS +
+//    NCCL at the down-projection shape where those reached 0.82x to 1.17x, and within 3 % of
+//    the best of them at the o-projection shape.
+//  * Reduce: after its GEMM tiles every CTA takes output tiles of its own rank, waits (bounded)
+//    until WS partials have arrived, sums them in rank order in fp32 and writes bf16.
+//  * An entry barrier over the signal pad proves that every rank has finished reducing the
+//    previous call before its inbox is overwritten.  Counters count calls (epoch word in the
+//    pad), so nothing is reset between calls.
+//  * All-reduce form (kAllReduce): each rank reduces its rows and broadcasts them into a
+//    symmetric [M, N] output on every rank; an exit barrier proves that all rows have landed.
+//
+// Barriers inside the pair: full[] on the leader, empty[] / tmem_full[] by multicast commit,
+// tmem_empty[] on the leader with 8 arrivals.
+#include "../device/tcgen05_pair.cuh"
 #include "matmul_rs_common.cuh"
+#include "residency.h"
 
 namespace smr {
 
@@ -34,54 +44,43 @@ using namespace rs;
 
 namespace {
 
-template <int kStages, int kNStrips>
-struct RsSmem {
+constexpr int kStages = 6;
+constexpr int kNStrips = 2;
+
+struct PairRsSmem {
   static constexpr uint32_t kABytes = kBM * kBK * 2;
-  static constexpr uint32_t kBBytes = kBN * kBK * 2;
+  static constexpr uint32_t kBBytes = (kBN / 2) * kBK * 2;       // this CTA's half of the B tile
   static constexpr uint32_t kStageBytes = kABytes + kBBytes;
   static constexpr uint32_t kRingBytes = kStageBytes * kStages;
   static constexpr uint32_t kStripOffset = kRingBytes;
-  static constexpr uint32_t kStripBytes = kNStrips * kStripBytesOne;   // strips in flight on the wire
+  static constexpr uint32_t kStripBytes = kNStrips * kStripBytesOne;
   static constexpr uint32_t kBarOffset = kStripOffset + kStripBytes;
   static constexpr uint32_t kNumBars = 2 * kStages + 4;
   static constexpr uint32_t kMiscOffset = kBarOffset + 8 * kNumBars;
   static constexpr uint32_t kTotal = kMiscOffset + 16 + 1024;
+  static_assert(kStageBytes % 1024 == 0, "stage bases must stay 1024-byte aligned");
 };
-static_assert(RsSmem<4, 2>::kTotal <= 232448 && RsSmem<3, 5>::kTotal <= 232448, "shared memory limit exceeded");
+static_assert(PairRsSmem::kTotal <= 232448, "shared memory limit exceeded");
 
-// tile index -> destination rank, 128-row block inside the destination, N tile
-__device__ __forceinline__ void tile_coords(const RsParams& p, int t, int& dest, int& mb, int& ni) {
-  const int per_dest = p.blocks_per_rank * p.n_tiles_n;
-  int step = t / per_dest, rem = t - step * per_dest;
-  dest = p.rank + 1 + step;
-  if (dest >= p.world_size) dest -= p.world_size;
-  mb = rem / p.n_tiles_n;
-  ni = rem - mb * p.n_tiles_n;
-}
-
-// kStages: depth of the operand ring; kNStrips: epilogue strips that may be on the wire at once.
-// <4, 2> is the default; <3, 5> trades a stage for three more strips in flight (short-K shapes,
-// where the wire, not the main loop, is the limit).
-// kThreadStores: a strip leaves shared memory by coalesced 16-byte loads and stores of the 128
-// epilogue threads (512 contiguous bytes per warp instruction) instead of one bulk store by one
-// thread.  Stores issued by threads are not capped at kNStrips per SM on the wire, the buffer is
-// free as soon as it has been read, and the tile's counter is bumped right after its last strip.
-template <int kStages, int kNStrips, bool kAllReduce = false, bool kThreadStores = false>
-__global__ void __launch_bounds__(kThreads, 1)
+template <bool kAllReduce = false>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 matmul_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const RsParams p) {
-  using Smem = RsSmem<kStages, kNStrips>;
+                      const RsParams p) {
+  using L = PairRsSmem;
   extern __shared__ uint8_t smem_raw[];
+  // same offset in both CTAs: the dynamic window starts at the same shared address
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint8_t* strip = smem + Smem::kStripOffset;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Smem::kBarOffset);
+  uint8_t* strip = smem + L::kStripOffset;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + kStages;
   uint64_t* tmem_full = bars + 2 * kStages;
   uint64_t* tmem_empty = bars + 2 * kStages + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Smem::kMiscOffset);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kMiscOffset);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t cta_rank = cluster_ctarank();
+  const bool leader = cta_rank == 0;
   uint32_t* header = p.local_pad + kFlagSlotsBase;        // [0] epoch, [1] CTAs done
   const uint32_t epoch = ld_relaxed_gpu(&header[0]) + 1u;
   const uint32_t target = epoch * (uint32_t)p.world_size;
@@ -94,15 +93,15 @@ matmul_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tmem_full[b], 1);
-      mbar_init(&tmem_empty[b], 4);
+      mbar_init(&tmem_empty[b], 8);   // 4 epilogue warps x 2 CTAs (used in the leader)
     }
     mbar_fence_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, kTmemCols);
-    tmem_relinquish_alloc_permit();
+    tmem_alloc_pair(tmem_slot, kTmemCols);
+    tmem_relinquish_pair();
   }
   if (p.trace != nullptr && threadIdx.x == 0) p.trace[blockIdx.x * 4 + 0] = globaltimer_ns();
   // every rank has entered this call: its reduce of the previous call is done
@@ -111,40 +110,52 @@ matmul_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   if (p.trace != nullptr && threadIdx.x == 0) p.trace[blockIdx.x * 4 + 1] = globaltimer_ns();
   tcgen05_fence_before_thread_sync();
   __syncthreads();
+  cluster_sync_all();                 // barriers of both CTAs initialised, TMEM allocated
   tcgen05_fence_after_thread_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int total_tiles = p.world_size * p.blocks_per_rank * p.n_tiles_n;
+  const int pair = (int)blockIdx.x >> 1;
+  const int n_pairs = (int)gridDim.x >> 1;
+  const int n_rb = p.world_size * p.blocks_per_rank;       // 128-row blocks over all destinations
+  const int total_tiles = ((n_rb + 1) >> 1) * p.n_tiles_n;
   const int k_blocks = (p.K + kBK - 1) / kBK;
   const int rows_per_rank = p.blocks_per_rank * kBM;
   bool failed = !entered;
 
   if (warp == 0) {
+    // ---------------- TMA producer (both CTAs) ----------------
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
-      for (int t = blockIdx.x; t < total_tiles && !failed; t += gridDim.x) {
-        int dest, mb, ni;
-        tile_coords(p, t, dest, mb, ni);
-        const int row0 = dest * rows_per_rank + mb * kBM;
+      for (int t = pair; t < total_tiles && !failed; t += n_pairs) {
+        const int pr = t / p.n_tiles_n, ni = t - pr * p.n_tiles_n;
+        const int rb = 2 * pr + (int)cta_rank;
+        int row0 = p.M;                                    // past the end: reads as zero
+        if (rb < n_rb) {
+          int dest, mb;
+          row_block_coords(p, rb, dest, mb);
+          row0 = dest * rows_per_rank + mb * kBM;
+        }
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.timeout_ns)) {
             report_status(p.status, kTimeoutMbarrier, p.rank, blockIdx.x, stage, kWhereGemmEmpty);
             failed = true;
             break;
           }
-          uint8_t* sa = smem + (size_t)stage * Smem::kStageBytes;
-          mbar_arrive_expect_tx(&full_bar[stage], Smem::kStageBytes);
-          tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * kBK, row0);
-          tma_load_2d(sa + Smem::kABytes, &tmap_b, &full_bar[stage], kb * kBK, ni * kBN);
+          uint8_t* sa = smem + (size_t)stage * L::kStageBytes;
+          if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2u * L::kStageBytes);
+          const uint32_t full_leader = map_to_cta(smem_u32(&full_bar[stage]), 0);
+          tma_load_2d_pair(sa, &tmap_a, full_leader, kb * kBK, row0);
+          tma_load_2d_pair(sa + L::kABytes, &tmap_b, full_leader, kb * kBK, ni * kBN + (int)cta_rank * (kBN / 2));
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16_f32(kBM, kBN);
+    // ---------------- MMA issuer (leader CTA only) ----------------
+    if (leader && lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16_f32(2 * kBM, kBN);
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
-      for (int t = blockIdx.x; t < total_tiles && !failed; t += gridDim.x) {
+      for (int t = pair; t < total_tiles && !failed; t += n_pairs) {
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, p.timeout_ns)) {
           report_status(p.status, kTimeoutMbarrier, p.rank, blockIdx.x, acc, kWhereGemmTmemEmpty);
           failed = true;
@@ -159,32 +170,34 @@ matmul_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             break;
           }
           tcgen05_fence_after_thread_sync();
-          const uint32_t sa = smem_u32(smem + (size_t)stage * Smem::kStageBytes);
+          const uint32_t sa = smem_u32(smem + (size_t)stage * L::kStageBytes);
           const uint64_t da = umma_smem_desc_sw128(sa);
-          const uint64_t db = umma_smem_desc_sw128(sa + Smem::kABytes);
+          const uint64_t db = umma_smem_desc_sw128(sa + L::kABytes);
 #pragma unroll
           for (int k = 0; k < kBK / kUmmaK; ++k)
-            umma_bf16_ss(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc,
-                         (kb | k) != 0 ? 1u : 0u);
-          umma_commit(&empty_bar[stage]);
+            umma_bf16_ss_pair(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc,
+                              (kb | k) != 0 ? 1u : 0u);
+          umma_commit_pair(&empty_bar[stage]);
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
         if (failed) break;
-        umma_commit(&tmem_full[acc]);
+        umma_commit_pair(&tmem_full[acc]);
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1;
       }
     }
   } else {
-    // ---------------- epilogue: TMEM -> bf16 strip -> TMA store into the destination ----------------
+    // ------- epilogue (warps 2..5 of both CTAs): TMEM -> bf16 strip -> coalesced stores into the destination -------
     const int quarter = warp & 3;
     const int etid = (int)threadIdx.x - 64;
-    const int r = quarter * 32 + lane;                  // row of the tile owned by this thread
+    const int r = quarter * 32 + lane;                  // row of this CTA's block owned by this thread
     uint32_t acc = 0, acc_phase = 0, strip_ctr = 0;
-    uint32_t* prev_counter = nullptr;                   // tile whose stores are issued but not yet signalled
-    for (int t = blockIdx.x; t < total_tiles && !failed; t += gridDim.x) {
-      int dest, mb, ni;
-      tile_coords(p, t, dest, mb, ni);
+    for (int t = pair; t < total_tiles && !failed; t += n_pairs) {
+      const int pr = t / p.n_tiles_n, ni = t - pr * p.n_tiles_n;
+      const int rb = 2 * pr + (int)cta_rank;
+      const bool valid = rb < n_rb;
+      int dest = 0, mb = 0;
+      if (valid) row_block_coords(p, rb, dest, mb);
       if (!mbar_wait(&tmem_full[acc], acc_phase, p.timeout_ns)) {
         if (lane == 0)
           report_status(p.status, kTimeoutMbarrier, p.rank, blockIdx.x, acc, kWhereGemmTmemFull);
@@ -194,66 +207,36 @@ matmul_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       tcgen05_fence_after_thread_sync();
       const uint32_t taddr = tmem_base + acc * 256u + ((uint32_t)(quarter * 32) << 16);
       int strips = 0;
+      if (valid) {
 #pragma unroll 1
-      for (int sidx = 0; sidx < kBN / kStripCols; ++sidx) {
-        const int col0 = ni * kBN + sidx * kStripCols;
-        if (col0 >= p.N) break;                          // uniform over the CTA
-        uint32_t v0[32], v1[32];
-        tmem_ld_32x32b_x32(taddr + (uint32_t)(sidx * kStripCols), v0);
-        tmem_ld_32x32b_x32(taddr + (uint32_t)(sidx * kStripCols + 32), v1);
-        tmem_ld_wait();
-        // the store issued two strips ago has finished reading the buffer we are about to fill
-        if constexpr (!kThreadStores) {
-          if (etid == 0) bulk_wait_group_read<kNStrips - 1>();
-        }
-        epilogue_sync();
-        uint8_t* buf = strip + (size_t)(strip_ctr % (uint32_t)kNStrips) * kStripBytesOne;
-        strip_row_to_smem(buf, r, v0, v1);
-        if constexpr (kThreadStores) {
-          epilogue_sync();                               // the strip is complete in shared memory
+        for (int sidx = 0; sidx < kStripsPerTile; ++sidx) {
+          const int col0 = ni * kBN + sidx * kStripCols;
+          if (col0 >= p.N) break;                          // uniform over the CTA
+          uint32_t v0[32], v1[32];
+          tmem_ld_32x32b_x32(taddr + (uint32_t)(sidx * kStripCols), v0);
+          tmem_ld_32x32b_x32(taddr + (uint32_t)(sidx * kStripCols + 32), v1);
+          tmem_ld_wait();
+          // every thread has copied the strip before last out of the buffer we are about to fill
+          epilogue_sync();
+          uint8_t* buf = strip + (size_t)(strip_ctr % (uint32_t)kNStrips) * kStripBytesOne;
+          strip_row_to_smem(buf, r, v0, v1);
+          epilogue_sync();                                 // the strip is complete in shared memory
           char* dst = static_cast<char*>(p.buffers[dest]) + p.inbox_offset +
                       strip_offset(p.rank, mb, ni, sidx, p.blocks_per_rank, p.n_tiles_n);
           strip_copy_out(dst, buf, etid);
-        } else {
-        fence_proxy_async();                             // generic writes to smem, async-proxy read
-        epilogue_sync();
-        if (etid == 0) {
-          char* dst = static_cast<char*>(p.buffers[dest]) + p.inbox_offset +
-                      strip_offset(p.rank, mb, ni, sidx, p.blocks_per_rank, p.n_tiles_n);
-          bulk_store(dst, buf, kStripBytesOne);
-          bulk_commit_group();
+          ++strip_ctr;
+          ++strips;
         }
-        }
-        ++strip_ctr;
-        ++strips;
       }
-      // the accumulator has been read: hand it back
+      // the accumulator has been read (or holds nothing to ship): hand it back to the leader's MMA thread
       tcgen05_fence_before_thread_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
-      if constexpr (kThreadStores) {
-        epilogue_sync();                                 // every thread has issued its stores of this tile
-        if (etid == 0 && strips > 0)
-          red_add_release_sys(p.pads[dest] + kFlagSlotsBase + 2 + mb * p.n_tiles_n + ni, 1u);
-      } else if (etid == 0) {
-        if (prev_counter != nullptr) {
-          // everything older than this tile's groups has completed
-          if (strips == 4) bulk_wait_group<4>();
-          else bulk_wait_group<0>();
-          fence_proxy_async();
-          red_add_release_sys(prev_counter, 1u);
-        }
-        prev_counter = p.pads[dest] + kFlagSlotsBase + 2 + mb * p.n_tiles_n + ni;
-      }
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc]), 0));
+      epilogue_sync();                                   // every thread has issued its stores of this tile
+      if (etid == 0 && strips > 0)
+        red_add_release_sys(p.pads[dest] + kFlagSlotsBase + 2 + mb * p.n_tiles_n + ni, 1u);
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
-    }
-    if (etid == 0) {
-      bulk_wait_group<0>();
-      if (prev_counter != nullptr && !failed) {
-        fence_proxy_async();
-        red_add_release_sys(prev_counter, 1u);
-      }
     }
   }
 
@@ -263,11 +246,12 @@ matmul_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   }
   tcgen05_fence_before_thread_sync();
   failed = __syncthreads_or(failed) != 0;
+  cluster_sync_all();   // the peer may still read this CTA's smem / signal its barriers until here
   tcgen05_fence_after_thread_sync();
-  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+  if (warp == 1) tmem_dealloc_pair(tmem_base, kTmemCols);
   if (p.trace != nullptr && threadIdx.x == 0) p.trace[blockIdx.x * 4 + 2] = globaltimer_ns();
 
-  // ---------------- reduce the tiles of this rank ----------------
+  // ---------------- reduce the tiles of this rank (every CTA on its own) ----------------
   if (!failed) {
     const int my_tiles = p.blocks_per_rank * p.n_tiles_n;
     const char* inbox = static_cast<const char*>(p.buffers[p.rank]) + p.inbox_offset;
@@ -315,7 +299,6 @@ size_t matmul_rs_workspace_bytes(int M, int N) {
 }
 
 int launch_matmul_reduce_scatter(const MatmulRsArgs& a, cudaStream_t stream) {
-  if (a.cta_pair) return launch_matmul_reduce_scatter_2cta(a, stream);
   const int ws = a.pv.world_size;
   if (a.M <= 0 || a.N % 8 != 0 || a.K % 8 != 0 || a.M % (ws * kBM) != 0) return cudaErrorInvalidValue;
   RsParams p{};
@@ -333,7 +316,7 @@ int launch_matmul_reduce_scatter(const MatmulRsArgs& a, cudaStream_t stream) {
   p.status = a.status;
   p.trace = a.trace;
   if (a.all_reduce) {
-    if (a.ar_peers == nullptr || a.deep_strips || a.ar_offset % 16 != 0) return cudaErrorInvalidValue;
+    if (a.ar_peers == nullptr || a.ar_offset % 16 != 0) return cudaErrorInvalidValue;
     p.ar_peers = a.ar_peers;
     p.ar_mc = a.ar_mc;
     p.ar_offset = a.ar_offset;
@@ -342,35 +325,28 @@ int launch_matmul_reduce_scatter(const MatmulRsArgs& a, cudaStream_t stream) {
   }
   CUtensorMap ta, tb;
   if (make_tmap(&ta, a.a, (uint64_t)a.M, (uint64_t)a.K, kBM)) return cudaErrorInvalidValue;
-  if (make_tmap(&tb, a.b, (uint64_t)a.N, (uint64_t)a.K, kBN)) return cudaErrorInvalidValue;
-  int total_tiles = ws * p.blocks_per_rank * p.n_tiles_n;
-  int grid = a.num_sms < total_tiles ? a.num_sms : total_tiles;
-  if (grid < 1 || (uint32_t)(1024 + grid) * (uint32_t)ws > kBlockSlots) return cudaErrorInvalidValue;
-  if (a.deep_strips) {
-    auto kern = matmul_rs_kernel<3, 5>;
-    constexpr int smem = (int)RsSmem<3, 5>::kTotal;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (make_tmap(&tb, a.b, (uint64_t)a.N, (uint64_t)a.K, kBN / 2)) return cudaErrorInvalidValue;
+  const int n_rb = ws * p.blocks_per_rank;
+  const int total_tiles = ((n_rb + 1) / 2) * p.n_tiles_n;
+  int pairs = a.num_sms / 2;
+  if (pairs > total_tiles) pairs = total_tiles;
+  if (pairs < 1) return cudaErrorInvalidValue;
+  const int grid = 2 * pairs;
+  if ((uint32_t)(1024 + grid) * (uint32_t)ws > kBlockSlots) return cudaErrorInvalidValue;
+  if (a.all_reduce) {
+    auto kern = matmul_rs_kernel<true>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PairRsSmem::kTotal);
     if (e != cudaSuccess) return (int)e;
-    kern<<<grid, kThreads, smem, stream>>>(ta, tb, p);
-  } else if (a.thread_stores && !a.all_reduce) {
-    auto kern = matmul_rs_kernel<4, 2, false, true>;
-    constexpr int smem = (int)RsSmem<4, 2>::kTotal;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return (int)e;
-    kern<<<grid, kThreads, smem, stream>>>(ta, tb, p);
-  } else if (a.all_reduce) {
-    auto kern = matmul_rs_kernel<4, 2, true>;
-    constexpr int smem = (int)RsSmem<4, 2>::kTotal;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return (int)e;
-    kern<<<grid, kThreads, smem, stream>>>(ta, tb, p);
-  } else {
-    auto kern = matmul_rs_kernel<4, 2>;
-    constexpr int smem = (int)RsSmem<4, 2>::kTotal;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return (int)e;
-    kern<<<grid, kThreads, smem, stream>>>(ta, tb, p);
+    // the CTAs of a rank wait for the same CTAs of the peers (entry barrier, arrival counters)
+    if (int rc = check_co_resident(kern, grid, kThreads, PairRsSmem::kTotal, 2)) return rc;
+    kern<<<grid, kThreads, PairRsSmem::kTotal, stream>>>(ta, tb, p);
+    return (int)cudaGetLastError();
   }
+  auto kern = matmul_rs_kernel<false>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PairRsSmem::kTotal);
+  if (e != cudaSuccess) return (int)e;
+  if (int rc = check_co_resident(kern, grid, kThreads, PairRsSmem::kTotal, 2)) return rc;
+  kern<<<grid, kThreads, PairRsSmem::kTotal, stream>>>(ta, tb, p);
   return (int)cudaGetLastError();
 }
 

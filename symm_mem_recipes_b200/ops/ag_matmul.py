@@ -64,6 +64,8 @@ class AgMatmulConfig:
     push_spread: int = _env_int("SMR_AGMM_PUSH_SPREAD", 0)
     # push gather by plain stores to every peer even where a multicast mapping exists (-1 = decide by world size)
     push_plain_stores: int = _env_int("SMR_AGMM_PUSH_PLAIN_STORES", -1)
+    # pieces a 128-row block is cut into for the broadcast (0 = the launcher's choice)
+    push_pieces: int = _env_int("SMR_AGMM_PUSH_PIECES", 0)
     timeout_ms: int = _env_int("SMR_TIMEOUT_MS", 10000)
 
 
@@ -318,7 +320,7 @@ def all_gather_matmul(a_shard: torch.Tensor, b: torch.Tensor, a_out: Optional[to
         C.ag_matmul(a_shard, b, c_out, 2, None, 0, hdl.native, aout_offset, a_out, None,
                     bn, sms, n_copy, t_ns, config.cta_pair, _tail_buffer(a_shard.device, config), epi,
                     _l2_hints(config, a_shard.dtype, epi), trace, config.lead, config.push_ahead,
-                    config.push_spread, _push_plain_stores(config, ws))
+                    config.push_spread, _push_plain_stores(config, ws), config.push_pieces)
         return c_out
     if config.plain_a_out == "push_copy":
         staged = gather_buffer(M, K, a_shard.device, group, a_shard.dtype)

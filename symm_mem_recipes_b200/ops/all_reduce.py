@@ -55,8 +55,7 @@ def one_shot_all_reduce(t: torch.Tensor, *, exit_barrier: bool = False,
     exit_barrier = exit_barrier or write_back
     if hdl.kind == "cuda":
         C.one_shot_all_reduce(hdl.native, offset, out, t.numel(), config.one_shot_max_blocks,
-                              exit_barrier, t_ns, write_back, config.one_shot_threads, config.one_shot_unroll,
-                              config.one_shot_barrier, bool(config.one_shot_rotate))
+                              exit_barrier, t_ns, write_back)
     else:
         raise_for_status(C.host_all_reduce(hdl.native, offset, out, t.numel(), 0, t_ns))
         if exit_barrier:

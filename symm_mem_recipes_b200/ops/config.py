@@ -30,20 +30,13 @@ class AllReduceConfig:
     # Above one-shot: multimem when a multicast mapping exists, else two-shot.
     # CTA caps.  Upstream caps its one-shot kernel at 24 CTAs of 512 threads
     # (triton_one_shot_all_reduce.py:97-109); large messages want more.
-    one_shot_max_blocks: int = _env_int("SMR_AR_ONE_SHOT_MAX_BLOCKS", 32)
+    one_shot_max_blocks: int = _env_int("SMR_AR_ONE_SHOT_MAX_BLOCKS", 128)
     two_shot_max_blocks: int = _env_int("SMR_AR_TWO_SHOT_MAX_BLOCKS", 128)
     multimem_max_blocks: int = _env_int("SMR_AR_MULTIMEM_MAX_BLOCKS", 16)
     # multimem kernel: entry / exit barriers by one multimem.red per rank (NVLS) instead of per-peer stores
     multimem_nvls_barrier: int = _env_int("SMR_AR_NVLS_BARRIER", 0)
     # multimem kernel: in-switch reductions in flight per thread (4, 8 or 16)
     multimem_unroll: int = _env_int("SMR_AR_MULTIMEM_UNROLL", 8)
-    # one-shot kernel: threads per CTA (128, 256, 512), 16-byte vectors per thread and iteration (1, 2, 4),
-    # barrier (0 = CAS protocol as upstream, 1 = the same with split sender / waiter threads, 2 = epoch
-    # barrier), and whether rank r starts its walk over the buffer at r / WS of it
-    one_shot_threads: int = _env_int("SMR_AR_ONE_SHOT_THREADS", 512)
-    one_shot_unroll: int = _env_int("SMR_AR_ONE_SHOT_UNROLL", 1)
-    one_shot_barrier: int = _env_int("SMR_AR_ONE_SHOT_BARRIER", 0)
-    one_shot_rotate: int = _env_int("SMR_AR_ONE_SHOT_ROTATE", 0)
     timeout_ms: int = _env_int("SMR_TIMEOUT_MS", 10000)
 
 

@@ -57,15 +57,18 @@ def gemv_all_reduce(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor
     """`x` [B, K] and `w` [K, N] are this rank's (ordinary) tensors; returns the
     all-reduced [B, N] in bf16, bitwise identical on every rank.
 
-    `algo`: "tc" = tcgen05 kernel (weights streamed by TMA, swap-A/B MMA);
-    "simt" = CUDA-core kernel; "tc_tagged" = the tcgen05 kernel exchanging its
-    partials as {value, call number} words that the reducer polls directly
-    (no flags, no release fence; meant for batch <= 4; built, not yet run on a
-    GPU).  Default from SMR_GEMV_ALGO, else "tc".
+    `algo`: "tc" = tcgen05 kernel (weights streamed by TMA, swap-A/B MMA),
+    partial sums exchanged through inboxes and flags; "tc_tagged" = the same
+    kernel exchanging its sums as {value, call number} words that the reducer
+    polls directly (no flags, no release fence: one NVLink crossing on the
+    critical path, twice the bytes); "simt" = CUDA-core kernel.  Default from
+    SMR_GEMV_ALGO, else "tc_tagged" up to batch 8 and "tc" above (measured on 2
+    and 4 GPUs: the tagged exchange is 2 to 9 µs faster up to batch 4 and 1.4 µs
+    slower at batch 16).
 
     `weights_nk=True`: `w` is [N, K] (K contiguous), the layout
     `matmul_reduce_scatter` takes, so that one copy of a row-parallel weight
-    serves prefill and decode (tcgen05 kernels only; built, not yet run)."""
+    serves prefill and decode (tcgen05 kernels only)."""
     k_dim, n_dim = (1, 0) if weights_nk else (0, 1)
     if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[k_dim]:
         raise SymmMemError("need x[B, K] and w[K, N]" + (" given as [N, K]" if weights_nk else ""))
@@ -76,7 +79,7 @@ def gemv_all_reduce(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor
         raise SymmMemError("N must be a multiple of 8")
     if out is None:
         out = torch.empty(B, N, dtype=torch.bfloat16, device=x.device)
-    algo = algo or os.environ.get("SMR_GEMV_ALGO", "tc")
+    algo = algo or os.environ.get("SMR_GEMV_ALGO") or ("tc_tagged" if B <= 8 and x.shape[1] % 8 == 0 else "tc")
     if algo not in ("tc", "simt", "tc_tagged"):
         raise SymmMemError('algo must be "tc", "tc_tagged" or "simt"')
     if algo == "tc_tagged" and x.shape[1] % 8:

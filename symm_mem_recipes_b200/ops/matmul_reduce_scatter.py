@@ -3,9 +3,9 @@ tensor-parallel block at prefill time (o-proj, down-proj).
 
     out_r[M/WS, N] = ( sum over ranks s of  A_s[M, K_s] @ B_s[N, K_s]^T ) [rows of rank r]
 
-One tcgen05 kernel multiplies, ships every tile straight from its epilogue to
-the rank that owns those rows, and reduces what arrives; see
-csrc/kernels/matmul_rs_sm100.cu.  Together with `all_gather_matmul` it keeps
+One tcgen05 kernel (CTA pairs, `cta_group::2`) multiplies, ships every tile
+straight from its epilogue to the rank that owns those rows, and reduces what
+arrives; see csrc/kernels/matmul_rs_sm100.cu.  Together with `all_gather_matmul` it keeps
 activations sharded on tokens between the layers (sequence parallelism).  The
 upstream package has no reduce-scatter half; the library baseline is
 `reference_matmul_reduce_scatter` (cuBLAS + NCCL).
@@ -43,8 +43,7 @@ def _workspace(M: int, N: int, device: torch.device, group) -> torch.Tensor:
 @traced("smr.matmul_reduce_scatter")
 def matmul_reduce_scatter(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None,
                           group=None, num_sms: int = 0, timeout_ms: int = _TIMEOUT_MS,
-                          trace: Optional[torch.Tensor] = None, deep_strips: Optional[bool] = None,
-                          cta_pair: Optional[bool] = None, thread_stores: Optional[bool] = None) -> torch.Tensor:
+                          trace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """`a` [M, K_local] (all tokens, this rank's slice of the reduction
     dimension), `b` [N, K_local]; returns this rank's [M/WS, N] rows of the sum
     over ranks, bitwise identical to what any other summation site would get
@@ -52,23 +51,7 @@ def matmul_reduce_scatter(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.
 
     `trace`: optional int64 CUDA tensor [num_sms, 4]; every CTA writes its
     %globaltimer (ns) at kernel start, after the entry barrier, when its GEMM
-    tiles are pushed, and when its share of the reduction is done.
-
-    `deep_strips` (default from SMR_RS_DEEP_STRIPS, off): variant of the kernel
-    with a 3-stage operand ring and five 16 KB epilogue strips in flight instead
-    of 4 stages and two, meant for short reduction dimensions where the wire is
-    the limit.  Built, not yet measured on a GPU.
-
-    `cta_pair` (default from SMR_RS_CTA_PAIR, off): the main loop on CTA pairs
-    (tcgen05 cta_group::2, 256 x 256 tiles, 5 stages, four strips in flight;
-    csrc/kernels/matmul_rs_2cta_sm100.cu).  Same inbox layout and the same
-    result bits.  Built, not yet run on a GPU.
-
-    `thread_stores` (default from SMR_RS_THREAD_STORES, off): the epilogue
-    strips are copied out of shared memory by coalesced stores of the 128
-    epilogue threads instead of one bulk store each: no cap on the strips an SM
-    has on the wire.  Combines with `cta_pair` (then six operand stages).  Same
-    inbox, same bits.  Built, not yet run."""
+    tiles are pushed, and when its share of the reduction is done."""
     if a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[1]:
         raise SymmMemError("need a[M, K] and b[N, K]")
     ws = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -82,18 +65,8 @@ def matmul_reduce_scatter(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.
         out = torch.empty(M // ws, N, dtype=torch.bfloat16, device=a.device)
     wsp = _workspace(M, N, a.device, group)
     hdl = symm_mem.rendezvous(wsp, group)
-    if deep_strips is None:
-        deep_strips = os.environ.get("SMR_RS_DEEP_STRIPS", "0") == "1"
-    if cta_pair is None:
-        cta_pair = os.environ.get("SMR_RS_CTA_PAIR", "0") == "1"
-    if thread_stores is None:
-        thread_stores = os.environ.get("SMR_RS_THREAD_STORES", "0") == "1"
-    if deep_strips and (cta_pair or thread_stores):
-        raise SymmMemError("deep_strips is a variant of the 1-CTA bulk-store kernel: it does not combine with "
-                           "cta_pair or thread_stores")
     C.matmul_reduce_scatter(a, b, out, hdl.native, num_sms or _num_sms(a.device),
-                            int(timeout_ms) * 1_000_000, trace, bool(deep_strips), bool(cta_pair),
-                            bool(thread_stores))
+                            int(timeout_ms) * 1_000_000, trace)
     return out
 
 
@@ -102,7 +75,7 @@ _ar_outputs: dict[tuple, torch.Tensor] = {}
 
 @traced("smr.matmul_all_reduce")
 def matmul_all_reduce(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, group=None,
-                      num_sms: int = 0, timeout_ms: int = _TIMEOUT_MS, cta_pair: Optional[bool] = None) -> torch.Tensor:
+                      num_sms: int = 0, timeout_ms: int = _TIMEOUT_MS) -> torch.Tensor:
     """The same kernel with an all-reduce ending, for tensor parallelism without
     sequence parallelism: every rank gets the whole [M, N] sum.  Rank r reduces
     its M/WS rows as in `matmul_reduce_scatter` and then broadcasts them into
@@ -112,8 +85,7 @@ def matmul_all_reduce(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tens
 
     `out` must live in symmetric memory (peers write into it).  With
     `out=None` an internal symmetric [M, N] buffer per shape is used and
-    returned: it is overwritten by the next call of that shape.
-    Built, not yet run on a GPU."""
+    returned: it is overwritten by the next call of that shape."""
     if a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[1]:
         raise SymmMemError("need a[M, K] and b[N, K]")
     ws = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -136,10 +108,8 @@ def matmul_all_reduce(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tens
     out_hdl = symm_mem.rendezvous(out, group)
     wsp = _workspace(M, N, a.device, group)
     hdl = symm_mem.rendezvous(wsp, group)
-    if cta_pair is None:
-        cta_pair = os.environ.get("SMR_RS_CTA_PAIR", "0") == "1"
     C.matmul_all_reduce(a, b, out, out_hdl.native, out_offset, hdl.native, num_sms or _num_sms(a.device),
-                        int(timeout_ms) * 1_000_000, bool(cta_pair))
+                        int(timeout_ms) * 1_000_000)
     return out
 
 

@@ -203,10 +203,7 @@ def build_checks(world: int, rank: int, dev: torch.device) -> list:
         return fn
 
     add("matmul_reduce_scatter", "default", row_parallel("rs"))
-    for variant in ("cta_pair", "deep_strips", "thread_stores", "cta_pair+thread_stores"):
-        add("matmul_reduce_scatter", variant, row_parallel("rs", **{k: True for k in variant.split("+")}), True)
-    add("matmul_all_reduce", "default", row_parallel("ar"), True)
-    add("matmul_all_reduce", "cta_pair", row_parallel("ar", cta_pair=True), True)
+    add("matmul_all_reduce", "default", row_parallel("ar"))
 
     # ------------------------------------------------------------------ GEMV + all-reduce
     def gemv(algo, B, nk=False):

@@ -26,7 +26,7 @@ def _install_host_kernels():
         @staticmethod
         def ag_matmul(a, b, c, mode, shard_alloc, shard_offset, aout_alloc, aout_offset, a_out, flags, block_n,
                       num_sms, n_copy, timeout_ns, cta_pair=False, tail_scratch=None, epilogue=0, l2_hints=0, trace=None, lead=-1, push_ahead=0,
-                  push_spread=0, push_plain_stores=False):
+                  push_spread=0, push_plain_stores=False, push_pieces=0):
             calls.append(mode)
             if mode == 2:
                 ws, rank = dist.get_world_size(), dist.get_rank()
@@ -145,16 +145,15 @@ def _row_parallel_flow_worker(rank, world_size):
             return getattr(real, name)
 
         @staticmethod
-        def matmul_reduce_scatter(a, b, out, workspace, num_sms, timeout_ns, trace=None, deep_strips=False,
-                                  cta_pair=False, thread_stores=False):
-            seen["rs"] = (deep_strips, cta_pair, workspace.payload_bytes, thread_stores)
+        def matmul_reduce_scatter(a, b, out, workspace, num_sms, timeout_ns, trace=None):
+            seen["rs"] = workspace.payload_bytes
             rows = out.shape[0]
             out.copy_(summed(a, b)[rank * rows:(rank + 1) * rows].to(out.dtype))
 
         @staticmethod
-        def matmul_all_reduce(a, b, out, out_alloc, out_offset, workspace, num_sms, timeout_ns, cta_pair=False):
+        def matmul_all_reduce(a, b, out, out_alloc, out_offset, workspace, num_sms, timeout_ns):
             assert out.data_ptr() == real.host_view(out_alloc, -1, [1], torch.uint8, out_offset).data_ptr()
-            seen["ar"] = cta_pair
+            seen["ar"] = True
             out.copy_(summed(a, b).to(out.dtype))
 
         @staticmethod
@@ -179,19 +178,11 @@ def _row_parallel_flow_worker(rank, world_size):
 
     out = smr.matmul_reduce_scatter(a, b)
     assert out.shape == (rows, N) and torch.allclose(out.float(), want[rank * rows:(rank + 1) * rows], atol=0.02)
-    assert seen["rs"][:2] == (False, False) and seen["rs"][2] >= real.matmul_rs_workspace_bytes(M, N)
-    smr.matmul_reduce_scatter(a, b, cta_pair=True)
-    assert seen["rs"][:2] == (False, True)
-    smr.matmul_reduce_scatter(a, b, deep_strips=True)
-    assert seen["rs"][:2] == (True, False)
-    smr.matmul_reduce_scatter(a, b, thread_stores=True)
-    assert seen["rs"][:2] == (False, False) and seen["rs"][3] is True
-    with pytest.raises(SymmMemError, match="does not combine"):
-        smr.matmul_reduce_scatter(a, b, deep_strips=True, thread_stores=True)
+    assert seen["rs"] >= real.matmul_rs_workspace_bytes(M, N)
 
     full = smr.matmul_all_reduce(a, b)                       # internal symmetric output, cached per shape
     assert symm_mem.is_symm_mem_tensor(full) and torch.allclose(full.float(), want, atol=0.02)
-    assert smr.matmul_all_reduce(a, b, cta_pair=True).data_ptr() == full.data_ptr() and seen["ar"] is True
+    assert smr.matmul_all_reduce(a, b).data_ptr() == full.data_ptr() and seen["ar"] is True
     with pytest.raises(SymmMemError, match="symmetric"):
         smr.matmul_all_reduce(a, b, out=torch.empty(M, N, dtype=torch.bfloat16))
     with pytest.raises(SymmMemError, match="multiple of 128"):
@@ -240,15 +231,14 @@ def _install_row_parallel_and_glue_stand_ins():
             return getattr(real, name)
 
         @staticmethod
-        def matmul_reduce_scatter(a, b, out, workspace, num_sms, timeout_ns, trace=None, deep_strips=False,
-                                  cta_pair=False, thread_stores=False):
+        def matmul_reduce_scatter(a, b, out, workspace, num_sms, timeout_ns, trace=None):
             rank, rows = dist.get_rank(), out.shape[0]
             out.copy_(summed(a, b)[rank * rows:(rank + 1) * rows].to(out.dtype))
             if trace is not None:                                # [CTA][start, entered, GEMM done, reduced] in ns
                 trace.view(-1, 4)[:2] = torch.tensor([[1000, 2000, 9000, 12000], [1100, 2100, 9500, 12500]])
 
         @staticmethod
-        def matmul_all_reduce(a, b, out, out_alloc, out_offset, workspace, num_sms, timeout_ns, cta_pair=False):
+        def matmul_all_reduce(a, b, out, out_alloc, out_offset, workspace, num_sms, timeout_ns):
             out.copy_(summed(a, b).to(out.dtype))
 
         @staticmethod

@@ -104,8 +104,7 @@ WORKERS = [
     ("test_gpu_gemv", "_gemv_nk_worker", (1, 2), (3, 256, 512, "tc_tagged")),
     ("test_gpu_matmul_fp8", "_mm_worker", (1,), (256, 512, 256, 256, 0, True)),
     ("test_gpu_matmul_fp8", "_agmm_worker", (2,), (128, 256, 256)),
-    ("test_gpu_matmul_rs", "_rs_worker", (2,), (256, 256, 128, "cta_pair,thread_stores")),
-    ("test_gpu_matmul_rs", "_ar_worker", (2,), (256, 256, 128, True)),
+    ("test_gpu_matmul_rs", "_ar_worker", (2,), (256, 256, 128)),
     ("test_gpu_llama_layer", "_layer_worker", (1, 2), ()),
     ("test_gpu_llama_layer", "_layer_tp_worker", (2,), (True, True)),
     ("test_gpu_llama_layer", "_decode_graph_worker", (1, 2), (True,)),

@@ -46,6 +46,34 @@ def test_all_reduce_gloo_ws4():
     spawn_ranks(_all_reduce_worker, 4, "gloo", ("one_shot",))
 
 
+def _sub_group_worker(rank, world_size):
+    """Two sub-groups of two ranks each, reducing at the same time: `all_reduce(auto)` on a tensor
+    that was rendezvoused on a sub-group must reduce over that sub-group only, small messages
+    (the low-latency inbox, a workspace per group) included."""
+    import torch.distributed as dist
+
+    import symm_mem_recipes_b200 as smr
+    from symm_mem_recipes_b200._ext import C
+    from symm_mem_recipes_b200.parallel import symm_mem
+
+    groups = [dist.new_group([0, 1]), dist.new_group([2, 3])]      # every rank creates both
+    mine = groups[rank // 2]
+    members = [0, 1] if rank < 2 else [2, 3]
+    for numel in (1024, 8192, 1 << 18):                            # low-latency sizes and one beyond them
+        t = symm_mem.empty(numel, dtype=torch.bfloat16, device="cpu")
+        t.copy_(seeded_normal_bf16(numel, rank))
+        hdl = symm_mem.rendezvous(t, mine)
+        assert hdl.world_size == 2 and hdl.rank == rank % 2
+        out = smr.all_reduce(t, algo="auto")
+        ref = C.oracle_ordered_sum_bf16([seeded_normal_bf16(numel, r) for r in members])
+        assert torch.equal(out.view(torch.int16), ref.view(torch.int16)), numel
+    dist.barrier()
+
+
+def test_all_reduce_on_sub_groups():
+    spawn_ranks(_sub_group_worker, 4, "gloo")
+
+
 def _low_latency_worker(rank, world_size):
     """The tagged-word protocol over shared memory: sizes change from call to
     call, parities alternate, the last call is in place."""

@@ -137,7 +137,6 @@ def test_suite_hands_each_benchmark_arguments_its_parser_accepts(monkeypatch, tm
     assert len(seen["all_gather_matmul"]) == 2 and seen["all_gather_matmul"][1].upstream_table
     layer = seen["llama_layer"][0]
     assert layer.fused_glue == "all" and layer.breakdown and layer.tp and layer.decode_graph == 2
-    assert layer.rs_variants.split(",") == ["cta_pair", "deep_strips", "thread_stores", "cta_pair+thread_stores"]
     assert seen["gemv_all_reduce"][0].extra_algos == "tc_tagged"
     assert seen["all_reduce"][0].with_reference_triton and seen["all_reduce"][0].out.endswith("all_reduce_ws8.jsonl")
 
@@ -168,7 +167,7 @@ def test_suite_runs_an_explicit_job_list(monkeypatch, tmp_path, capsys):
             "gemv_all_reduce --extra-algos tc_tagged; "
             "all_reduce --one-shot-sweep --with-reference-triton --max-bytes 8388608; "
             "all_reduce --multimem-sweep --max-bytes 268435456; "
-            "llama_layer --skip-layer --rs-variants cta_pair,deep_strips,thread_stores,cta_pair+thread_stores")
+            "llama_layer --skip-layer")
     monkeypatch.setattr(sys, "argv", ["suite", "--jobs", jobs])
     assert suite.main() == 0
     assert [n for n, _ in seen] == ["all_gather_matmul", "gemv_all_reduce", "all_reduce", "all_reduce", "llama_layer"]
