@@ -37,11 +37,9 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--out", default=None, help="also append the JSON lines to this file")
     ap.add_argument("--multimem-blocks", type=int, default=0,
                     help="CTAs of the multimem kernel (0: configured default)")
-    ap.add_argument("--multimem-unroll", type=int, default=0, help="4, 8 or 16 reductions in flight per thread")
-    ap.add_argument("--nvls-barrier", action="store_true", help="multimem kernel: barriers by multimem.red")
     ap.add_argument("--multimem-sweep", action="store_true",
-                    help="instead of the size sweep: the multimem kernel over CTA counts, unroll factors and both "
-                         "barrier kinds at 16, 64 and 256 MiB (clamped to --max-bytes), one start-up")
+                    help="instead of the size sweep: the multimem kernel over CTA counts at 1, 64 and 256 MiB "
+                         "(clamped to --max-bytes), one start-up")
     ap.add_argument("--one-shot-sweep", action="store_true",
                     help="instead of the size sweep: the one-shot kernel over its CTA cap at 4 KiB, 64 KiB, 1 MiB and "
                          "8 MiB beside NCCL and the upstream Triton kernel, each first compared bit for bit with the "
@@ -70,10 +68,6 @@ def main(argv=None, standalone: bool = True) -> int:
     cfg = AllReduceConfig()
     if args.multimem_blocks:
         cfg.multimem_max_blocks = args.multimem_blocks
-    if args.multimem_unroll:
-        cfg.multimem_unroll = args.multimem_unroll
-    if args.nvls_barrier:
-        cfg.multimem_nvls_barrier = 1
     ref_fn = ref_buf = None
     if args.with_reference_triton:
         try:
@@ -188,31 +182,30 @@ def main(argv=None, standalone: bool = True) -> int:
                 if nbytes > args.max_bytes:
                     continue
                 t = buf[:nbytes // 2]
-                for nvls in (0, 1):
-                    for blocks in (8, 12, 16, 24):
-                        for unroll in (8, 16):
-                            def one(blocks=blocks, unroll=unroll, nvls=nvls, t=t, nbytes=nbytes):
-                                c = AllReduceConfig(multimem_max_blocks=blocks, multimem_unroll=unroll,
-                                                    multimem_nvls_barrier=nvls)
-                                us = benchmark_with_event(lambda: smr.multimem_all_reduce_(t, config=c), 5, 15,
-                                                          flush_l2=False)
-                                hdl.check()
-                                buf.normal_()
-                                emit({"op": "all_reduce_multimem_sweep", "world_size": world, "bytes": nbytes,
-                                      "blocks": blocks, "unroll": unroll, "nvls_barrier": bool(nvls),
-                                      "us": round(us, 2),
-                                      "bus_gbs": round(2 * (world - 1) / world * nbytes / us / 1e3, 1)})
+                for blocks in (4, 6, 8, 12, 16, 24):
+                    def one(blocks=blocks, t=t, nbytes=nbytes):
+                        c = AllReduceConfig(multimem_max_blocks=blocks)
+                        if nbytes <= (4 << 20):
+                            us = benchmark_with_graph(lambda: smr.multimem_all_reduce_(t, config=c),
+                                                      calls_per_graph=20, warmup_iters=5, replays=10)
+                        else:
+                            us = benchmark_with_event(lambda: smr.multimem_all_reduce_(t, config=c), 5, 15,
+                                                      flush_l2=False)
+                        hdl.check()
+                        buf.normal_()
+                        emit({"op": "all_reduce_multimem_sweep", "world_size": world, "bytes": nbytes,
+                              "blocks": blocks, "us": round(us, 2),
+                              "bus_gbs": round(2 * (world - 1) / world * nbytes / us / 1e3, 1)})
 
-                            if not attempt(f"multimem sweep: {nbytes} bytes, {blocks} CTAs, unroll {unroll}, "
-                                           f"nvls_barrier {nvls}", one, dev, emit):
-                                # after a device-side timeout the buffer itself is gone (reset): stop the sweep
-                                if not symm_mem.is_symm_mem_tensor(buf):
-                                    if args.out and rank == 0:
-                                        with open(args.out, "a") as f:
-                                            f.write("\n".join(lines) + "\n")
-                                    if standalone:
-                                        finish()
-                                    return 1
+                    if not attempt(f"multimem sweep: {nbytes} bytes, {blocks} CTAs", one, dev, emit):
+                        # after a device-side timeout the buffer itself is gone (reset): stop the sweep
+                        if not symm_mem.is_symm_mem_tensor(buf):
+                            if args.out and rank == 0:
+                                with open(args.out, "a") as f:
+                                    f.write("\n".join(lines) + "\n")
+                            if standalone:
+                                finish()
+                            return 1
         if args.out and rank == 0:
             with open(args.out, "a") as f:
                 f.write("\n".join(lines) + "\n")
@@ -258,8 +251,7 @@ def main(argv=None, standalone: bool = True) -> int:
             buf.normal_()   # in-place algorithms grow the values; refresh
             extra = {}
             if name == "multimem":
-                extra = {"multimem_blocks": cfg.multimem_max_blocks, "multimem_unroll": cfg.multimem_unroll,
-                         "nvls_barrier": bool(cfg.multimem_nvls_barrier)}
+                extra = {"multimem_blocks": cfg.multimem_max_blocks}
             emit({"op": "all_reduce", "impl": name, "world_size": world, "bytes": nbytes, "timing": how, **extra,
                   "us": round(us, 2), "alg_gbs": round(nbytes / us / 1e3, 2),
                   "bus_gbs": round(2 * (world - 1) / world * nbytes / us / 1e3, 2)})

@@ -470,14 +470,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                                         current_stream(a->device())), "two_shot_all_reduce");
   });
   m.def("multimem_all_reduce", [](const std::shared_ptr<CudaSymmAllocation>& a, int64_t offset_bytes,
-                                  int64_t numel, int max_blocks, uint64_t timeout_ns, bool nvls_barrier,
-                                  int unroll) {
+                                  int64_t numel, int max_blocks, uint64_t timeout_ns) {
     c10::cuda::CUDAGuard guard(a->device());
     rt_check(launch_multimem_all_reduce(view_of(*a), (size_t)offset_bytes, (size_t)numel, max_blocks,
                                         timeout_ns, status_for(a->device()),
-                                        current_stream(a->device()), nvls_barrier, unroll), "multimem_all_reduce");
-  }, py::arg("alloc"), py::arg("offset_bytes"), py::arg("numel"), py::arg("max_blocks"), py::arg("timeout_ns"),
-     py::arg("nvls_barrier") = false, py::arg("unroll") = 8);
+                                        current_stream(a->device())), "multimem_all_reduce");
+  }, py::arg("alloc"), py::arg("offset_bytes"), py::arg("numel"), py::arg("max_blocks"), py::arg("timeout_ns"));
 
   // a: own shard (or all of A when mode == 0), b: [N, K], c: [M, N]
   // mode 1 (pull): `shard_alloc` holds a; a_out is an ordinary tensor.

@@ -199,19 +199,20 @@ two_shot_all_reduce_kernel(PeerView pv, size_t offset_bytes, size_t n_vec, uint6
   bar.finish();
 }
 
-template <class Bar, int U = 8>
+// Eight independent in-switch reductions in flight per thread and few CTAs (eight to sixteen: more
+// measured slower at every size on 4 and 8 GPUs, and so did barriers by multimem.red).
 __global__ void __launch_bounds__(kArThreads)
 multimem_all_reduce_kernel(PeerView pv, size_t offset_bytes, size_t n_vec, uint64_t timeout_ns,
                            Status* st) {
+  constexpr int U = 8;
   const int rank = pv.rank, ws = pv.world_size;
-  Bar bar(pv, blockIdx.x);
+  EpochBar bar(pv, blockIdx.x);
   if (!bar.sync(timeout_ns, st, kWhereMultimemEntry)) return;
   Vec16* mc = reinterpret_cast<Vec16*>(static_cast<char*>(pv.multicast) + offset_bytes);
   size_t begin, end;
   slice_of(n_vec, ws, rank, begin, end);
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   size_t i = begin + (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  // U (eight by default) independent in-switch reductions in flight per thread
   for (; i + (U - 1) * stride < end; i += U * stride) {
     Vec16 v[U];
 #pragma unroll
@@ -436,25 +437,14 @@ int launch_two_shot_all_reduce(const PeerView& pv, size_t offset_bytes, size_t n
 
 int launch_multimem_all_reduce(const PeerView& pv, size_t offset_bytes, size_t numel,
                                int max_blocks, uint64_t timeout_ns, Status* status,
-                               cudaStream_t stream, bool nvls_barrier, int unroll) {
+                               cudaStream_t stream) {
   if (numel % 8 != 0 || offset_bytes % 16 != 0) return cudaErrorInvalidValue;
   if (pv.multicast == nullptr) return cudaErrorNotSupported;
   size_t n_vec = numel / 8;
+  if (max_blocks < 1) max_blocks = 1;
   if ((uint32_t)max_blocks > kArMaxBlocks) max_blocks = (int)kArMaxBlocks;
   int blocks = blocks_for((n_vec + pv.world_size - 1) / pv.world_size, max_blocks);
-#define SMR_MULTIMEM_LAUNCH(BAR, UNROLL) \
-  multimem_all_reduce_kernel<BAR, UNROLL><<<blocks, kArThreads, 0, stream>>>(pv, offset_bytes, n_vec, timeout_ns, status)
-  if (unroll != 4 && unroll != 8 && unroll != 16) return cudaErrorInvalidValue;
-  if (nvls_barrier) {
-    if (unroll == 4) SMR_MULTIMEM_LAUNCH(NvlsBar, 4);
-    else if (unroll == 16) SMR_MULTIMEM_LAUNCH(NvlsBar, 16);
-    else SMR_MULTIMEM_LAUNCH(NvlsBar, 8);
-  } else {
-    if (unroll == 4) SMR_MULTIMEM_LAUNCH(EpochBar, 4);
-    else if (unroll == 16) SMR_MULTIMEM_LAUNCH(EpochBar, 16);
-    else SMR_MULTIMEM_LAUNCH(EpochBar, 8);
-  }
-#undef SMR_MULTIMEM_LAUNCH
+  multimem_all_reduce_kernel<<<blocks, kArThreads, 0, stream>>>(pv, offset_bytes, n_vec, timeout_ns, status);
   return last_error();
 }
 

@@ -60,11 +60,9 @@ int launch_ll_all_reduce(const PeerView& pv, const void* in, void* out, size_t n
 int launch_two_shot_all_reduce(const PeerView& pv, size_t offset_bytes, size_t numel,
                                int max_blocks, uint64_t timeout_ns, Status* status,
                                cudaStream_t stream);
-// `nvls_barrier`: entry / exit barriers by multimem.red instead of per-peer stores.
 int launch_multimem_all_reduce(const PeerView& pv, size_t offset_bytes, size_t numel,
                                int max_blocks, uint64_t timeout_ns, Status* status,
-                               cudaStream_t stream, bool nvls_barrier = false, int unroll = 8);
-// `unroll` (4, 8 or 16): in-switch reductions in flight per thread.
+                               cudaStream_t stream);
 
 // ---- all_gather_matmul (tcgen05 GEMM + in-kernel all-gather) ---------------
 struct AgMatmulArgs {

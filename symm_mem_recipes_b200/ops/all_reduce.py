@@ -132,8 +132,7 @@ def multimem_all_reduce_(t: torch.Tensor, *, config: AllReduceConfig = DEFAULT_A
             return t
         if not hdl.has_multicast:
             raise SymmMemError("this allocation has no multicast mapping (NVLS unavailable)")
-        C.multimem_all_reduce(hdl.native, offset, t.numel(), config.multimem_max_blocks, t_ns,
-                              bool(config.multimem_nvls_barrier), int(config.multimem_unroll))
+        C.multimem_all_reduce(hdl.native, offset, t.numel(), config.multimem_max_blocks, t_ns)
     else:
         raise_for_status(C.host_all_reduce(hdl.native, offset, t, t.numel(), 2, t_ns))
     return t

@@ -33,10 +33,6 @@ class AllReduceConfig:
     one_shot_max_blocks: int = _env_int("SMR_AR_ONE_SHOT_MAX_BLOCKS", 128)
     two_shot_max_blocks: int = _env_int("SMR_AR_TWO_SHOT_MAX_BLOCKS", 128)
     multimem_max_blocks: int = _env_int("SMR_AR_MULTIMEM_MAX_BLOCKS", 16)
-    # multimem kernel: entry / exit barriers by one multimem.red per rank (NVLS) instead of per-peer stores
-    multimem_nvls_barrier: int = _env_int("SMR_AR_NVLS_BARRIER", 0)
-    # multimem kernel: in-switch reductions in flight per thread (4, 8 or 16)
-    multimem_unroll: int = _env_int("SMR_AR_MULTIMEM_UNROLL", 8)
     timeout_ms: int = _env_int("SMR_TIMEOUT_MS", 10000)
 
 

@@ -99,8 +99,7 @@ def build_checks(world: int, rank: int, dev: torch.device) -> list:
     add("all_reduce", "auto", ar("auto"))
     if multi:
         add("all_reduce", "multimem", ar("multimem"))
-        add("all_reduce", "multimem, NVLS barriers", ar("multimem", AllReduceConfig(multimem_nvls_barrier=1)), True)
-        add("all_reduce", "multimem, 16 reductions in flight", ar("multimem", AllReduceConfig(multimem_unroll=16)),
+        add("all_reduce", "multimem, 8 CTAs", ar("multimem", AllReduceConfig(multimem_max_blocks=8)),
             True)
 
     def barriers(kind):

@@ -167,7 +167,7 @@ def test_all_reduce_8gpu():
 
 def _counting_barriers_worker(rank, world_size, numel):
     """The epoch barrier and the NVLS (multimem.red) barrier as kernels of their
-    own, then the multimem all-reduce with NVLS barriers against the default."""
+    own, then the multimem all-reduce on the same pad."""
     import symm_mem_recipes_b200 as smr
     from symm_mem_recipes_b200.ops.config import AllReduceConfig
     from symm_mem_recipes_b200.parallel import symm_mem
@@ -186,18 +186,18 @@ def _counting_barriers_worker(rank, world_size, numel):
     if hdl.has_multicast:
         srcs = [seeded_normal_bf16(numel, r) for r in range(world_size)]
         results = []
-        for nvls in (0, 1, 1, 0):            # alternating kinds share the pad without disturbing each other
+        for blocks in (16, 4, 8, 16):        # after the barrier tests, at several CTA counts
             hdl.barrier()
             t.copy_(srcs[rank].to(dev))
             hdl.barrier()
-            smr.multimem_all_reduce_(t, config=AllReduceConfig(multimem_nvls_barrier=nvls, timeout_ms=2000))
+            smr.multimem_all_reduce_(t, config=AllReduceConfig(multimem_max_blocks=blocks, timeout_ms=2000))
             hdl.check()
             results.append(t.clone())
         ref = results[0].float()
         for r in results[1:]:
             # the switch's summation order is its own: within one bf16 ulp
             if not bool(((r.float() - ref).abs() <= ref.abs() * 2.0 ** -7 + 1e-6).all()):
-                failures.append("multimem all-reduce with NVLS barriers differs from the default")
+                failures.append("multimem all-reduce differs between CTA counts")
     elif world_size > 1:
         failures.append("no multicast mapping on an NVSwitch machine")
     torch.cuda.synchronize()
