@@ -7,7 +7,6 @@ and of the world-of-one GEMV and all-reduce kernels.  Also the program that
     python -m symm_mem_recipes_b200.bench.matmul --op gemv --batch 16
     python -m symm_mem_recipes_b200.bench.matmul --op glue --M 32768          # RMSNorm, RoPE, SiLU-mul kernels
     python -m symm_mem_recipes_b200.bench.matmul --op matmul --variant fp8    # or swiglu
-    python -m symm_mem_recipes_b200.bench.matmul --l2-hints sweep             # L2 eviction hint levels 0..3
 """
 from __future__ import annotations
 
@@ -31,8 +30,6 @@ def main() -> int:
     ap.add_argument("--N", type=int, default=3584)
     ap.add_argument("--K", type=int, default=8192)
     ap.add_argument("--block-n", type=int, default=0)
-    ap.add_argument("--l2-hints", default="0",
-                    help="matmul, bf16: L2 eviction hint level of the CTA-pair kernel (0..3), or 'sweep' for all four")
     ap.add_argument("--batch", type=int, default=16)
     ap.add_argument("--bytes", type=int, default=64 * 1024 * 1024)
     ap.add_argument("--warmup", type=int, default=5)
@@ -61,15 +58,11 @@ def main() -> int:
             b = (torch.randn(N, K, device=dev) * 0.02).to(dt)
             epilogue = "swiglu" if args.variant == "swiglu" else None
             c = torch.empty(M, N // 2 if epilogue else N, dtype=dt, device=dev)
-            levels = [0, 1, 2, 3] if args.l2_hints == "sweep" else [int(args.l2_hints)]
             flops = 2.0 * M * N * K
-            for level in levels:
-                cfg = AgMatmulConfig(block_n=args.block_n, l2_hints=level if args.variant == "bf16" else 0)
-                us = benchmark_with_event(lambda: smr.matmul(a, b, c, cfg, epilogue), **bench)
-                key = "smr" if level == levels[0] else f"smr_l2_hints_{level}"
-                out.update({f"{key}_us": round(us, 1), f"{key}_tflops": round(flops / us / 1e6, 1)})
-            out.update(M=M, N=N, K=K, variant=args.variant, block_n=args.block_n or choose_block_n(M, N, 148),
-                       l2_hints=levels[0])
+            cfg = AgMatmulConfig(block_n=args.block_n)
+            us = benchmark_with_event(lambda: smr.matmul(a, b, c, cfg, epilogue), **bench)
+            out.update(smr_us=round(us, 1), smr_tflops=round(flops / us / 1e6, 1))
+            out.update(M=M, N=N, K=K, variant=args.variant, block_n=args.block_n or choose_block_n(M, N, 148))
             if not args.no_cublas and args.variant == "bf16":
                 bt = b.t()
                 us2 = benchmark_with_event(lambda: torch.matmul(a, bt, out=c), **bench)

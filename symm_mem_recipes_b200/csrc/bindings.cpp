@@ -485,7 +485,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                         std::shared_ptr<CudaSymmAllocation> aout_alloc, int64_t aout_offset,
                         c10::optional<torch::Tensor> a_out, c10::optional<torch::Tensor> flags,
                         int block_n, int num_sms, int n_copy, uint64_t timeout_ns, bool cta_pair,
-                        c10::optional<torch::Tensor> tail_scratch, int epilogue, int l2_hints,
+                        c10::optional<torch::Tensor> tail_scratch, int epilogue,
                         c10::optional<torch::Tensor> trace, int lead, int push_ahead, int push_spread,
                         bool push_plain_stores, int push_pieces) {
     const auto dtype = a.scalar_type();
@@ -510,9 +510,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     args.K = (int)a.size(1);
     args.elem_bytes = fp8 ? 1 : 2;
     args.epilogue = epilogue;
-    args.l2_hints = l2_hints;
-    TORCH_CHECK(l2_hints == 0 || (l2_hints >= 1 && l2_hints <= 3 && cta_pair && mode != 1 && !fp8 && epilogue == 0),
-                "L2 eviction hints (1..3) exist on the bf16 CTA-pair kernel with the plain epilogue");
     TORCH_CHECK(epilogue == 0 || (epilogue == 1 && cta_pair && mode != 1 && !fp8),
                 "the SwiGLU epilogue runs on the bf16 CTA-pair kernel (a_out symmetric or absent)");
     args.block_n = block_n;
@@ -584,7 +581,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
      py::arg("shard_offset"), py::arg("aout_alloc"), py::arg("aout_offset"), py::arg("a_out"),
      py::arg("flags"), py::arg("block_n"), py::arg("num_sms"), py::arg("n_copy"), py::arg("timeout_ns"),
      py::arg("cta_pair") = false, py::arg("tail_scratch") = py::none(), py::arg("epilogue") = 0,
-     py::arg("l2_hints") = 0, py::arg("trace") = py::none(), py::arg("lead") = -1,
+     py::arg("trace") = py::none(), py::arg("lead") = -1,
      py::arg("push_ahead") = 0, py::arg("push_spread") = 0, py::arg("push_plain_stores") = false,
      py::arg("push_pieces") = 0);
 

@@ -48,17 +48,6 @@ __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorM
         "r"(x), "r"(y)
       : "memory");
 }
-// The same load with an L2 eviction policy (from l2_policy_*) attached to the lines it brings in.
-__device__ __forceinline__ void tma_load_2d_pair_hint(void* smem_dst, const CUtensorMap* map,
-                                                      uint32_t bar_cluster_addr, int32_t x, int32_t y,
-                                                      uint64_t policy) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint"
-      " [%0], [%1, {%3, %4}], [%2], %5;"
-      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr),
-        "r"(x), "r"(y), "l"(policy)
-      : "memory");
-}
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_dst, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
                ::"r"(smem_u32(smem_dst)), "r"(ncols) : "memory");

@@ -70,28 +70,6 @@ __device__ __forceinline__ uint32_t pack_e4m3x4(float f0, float f1, float f2, fl
   asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(f3), "f"(f2));
   return (uint32_t)lo | ((uint32_t)hi << 16);
 }
-// L2 eviction policies for loads / stores that carry a cache hint: lines brought in under
-// evict_last are the last candidates for replacement (an operand every CTA re-reads), lines
-// under evict_first the first (data read or written once).
-__device__ __forceinline__ uint64_t l2_policy_evict_last() {
-  uint64_t pol;
-  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
-  return pol;
-}
-__device__ __forceinline__ uint64_t l2_policy_evict_first() {
-  uint64_t pol;
-  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
-  return pol;
-}
-__device__ __forceinline__ uint64_t l2_policy_evict_normal() {
-  uint64_t pol;
-  asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(pol));
-  return pol;
-}
-__device__ __forceinline__ void st_16_hint(void* p, const Vec16& v, uint64_t policy) {
-  asm volatile("st.global.L2::cache_hint.v4.u32 [%0], {%1,%2,%3,%4}, %5;"
-               ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "l"(policy) : "memory");
-}
 __device__ __forceinline__ void st_8(void* p, uint32_t a, uint32_t b) {
   asm volatile("st.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(a), "r"(b) : "memory");
 }

@@ -69,7 +69,7 @@ struct PairSmem {
 // the epilogue writes SiLU(gate) * up, i.e. C is [M, N / 2] and tile ni covers its
 // columns [128 ni, 128 ni + 128).  The activation never makes a round trip through
 // memory and C is half as wide.  The split-K tail is not used with it.
-template <int BN, int STAGES, bool kFp8, bool kSwiGlu = false, bool kL2Hints = false>
+template <int BN, int STAGES, bool kFp8, bool kSwiGlu = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
                       const __grid_constant__ CUtensorMap tmap_a_out,
@@ -142,12 +142,6 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
       PairWork w;
       uint64_t t_flag = 0, t_stage = 0, t_first = 0;
       bool first_remote = true;
-      // B is re-read by every wave of tiles: keep it; A passes through once
-      [[maybe_unused]] uint64_t pol_a = 0, pol_b = 0;
-      if constexpr (kL2Hints) {
-        pol_b = l2_policy_evict_last();
-        pol_a = p.l2_hints >= 2 ? l2_policy_evict_first() : l2_policy_evict_normal();
-      }
       for (int wi = 0; !failed && pair_work(p, pair, n_pairs, total_tiles, k_blocks, wi, w); ++wi) {
         const int t = w.tile;
         const int mi = (t / p.n_tiles_n) * 2 + (int)cta_rank, ni = t % p.n_tiles_n;
@@ -192,13 +186,8 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
           uint8_t* sb = sa + L::kABytes;
           if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2u * L::kStageBytes);
           const uint32_t full_leader = map_to_cta(smem_u32(&full_bar[stage]), 0);
-          if constexpr (kL2Hints) {
-            tma_load_2d_pair_hint(sa, amap, full_leader, kb * kBKE, row0, pol_a);
-            tma_load_2d_pair_hint(sb, &tmap_b, full_leader, kb * kBKE, ni * BN + (int)cta_rank * (BN / 2), pol_b);
-          } else {
-            tma_load_2d_pair(sa, amap, full_leader, kb * kBKE, row0);
-            tma_load_2d_pair(sb, &tmap_b, full_leader, kb * kBKE, ni * BN + (int)cta_rank * (BN / 2));
-          }
+          tma_load_2d_pair(sa, amap, full_leader, kb * kBKE, row0);
+          tma_load_2d_pair(sb, &tmap_b, full_leader, kb * kBKE, ni * BN + (int)cta_rank * (BN / 2));
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -270,8 +259,6 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
     const int etid = (int)threadIdx.x - 64;
     int next_piece = (int)blockIdx.x, round = 0;
     const int all_pieces = p.blocks_per_rank * p.pieces;
-    [[maybe_unused]] uint64_t pol_c = 0;               // C is written once and not read again by this kernel
-    if constexpr (kL2Hints) pol_c = l2_policy_evict_first();
     [[maybe_unused]] int out_box = 0;                  // which of this warp's two output boxes is filled next
     if (p.mode == 2 && !push_entry_barrier(p, (int)blockIdx.x, etid)) failed = true;
     const bool trt = tr && etid == 0;
@@ -442,12 +429,7 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
           if (lane == 0) {
             if (store_ok && ni * BN + c * 64 < p.N) {
               uint8_t* src = smem + L::kOutOffset + ((size_t)quarter * 2 + out_box) * L::kOutBoxBytes;
-              if constexpr (kL2Hints) {
-                if (p.l2_hints >= 3) tma_store_2d_hint(&tmap_c, src, ni * BN + c * 64, mblk * kBM + quarter * 32, pol_c);
-                else tma_store_2d(&tmap_c, src, ni * BN + c * 64, mblk * kBM + quarter * 32);
-              } else {
-                tma_store_2d(&tmap_c, src, ni * BN + c * 64, mblk * kBM + quarter * 32);
-              }
+              tma_store_2d(&tmap_c, src, ni * BN + c * 64, mblk * kBM + quarter * 32);
             }
             bulk_commit_group();
           }
@@ -539,12 +521,12 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
   }
 }
 
-template <int BN, int STAGES, bool kFp8, bool kSwiGlu = false, bool kL2Hints = false>
+template <int BN, int STAGES, bool kFp8, bool kSwiGlu = false>
 int launch_pair_variant(const CUtensorMap& ta_shard, const CUtensorMap& ta_out, const CUtensorMap& tb,
                         const CUtensorMap& tc, const AgMatmulParams& p, int grid, cudaStream_t stream) {
   using L = PairSmem<BN, STAGES, pair_tma_store<BN, kFp8, kSwiGlu>()>;
   static_assert(L::kTotal <= 232448, "shared memory limit exceeded");
-  auto kern = ag_matmul_2cta_kernel<BN, STAGES, kFp8, kSwiGlu, kL2Hints>;
+  auto kern = ag_matmul_2cta_kernel<BN, STAGES, kFp8, kSwiGlu>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::kTotal);
   if (e != cudaSuccess) return (int)e;
   kern<<<grid, kGemmThreads, L::kTotal, stream>>>(ta_shard, ta_out, tb, tc, p);
@@ -661,16 +643,6 @@ int launch_ag_matmul_2cta(const AgMatmulArgs& a, cudaStream_t stream) {
       p.tail_counters = a.tail_counters;
       cudaError_t me = cudaMemsetAsync(a.tail_counters, 0, sizeof(uint32_t) * rem * 2, stream);
       if (me != cudaSuccess) return (int)me;
-    }
-  }
-  if (a.l2_hints < 0 || a.l2_hints > 3 || (a.l2_hints != 0 && (fp8 || swiglu))) return cudaErrorInvalidValue;
-  p.l2_hints = a.l2_hints;
-  if (a.l2_hints != 0) {
-    switch (bn) {
-      case 128: return launch_pair_variant<128, 8, false, false, true>(ta_shard, ta_out, tb, tc, p, grid, stream);
-      case 192: return launch_pair_variant<192, 6, false, false, true>(ta_shard, ta_out, tb, tc, p, grid, stream);
-      case 224: return launch_pair_variant<224, 7, false, false, true>(ta_shard, ta_out, tb, tc, p, grid, stream);
-      default:  return launch_pair_variant<256, 6, false, false, true>(ta_shard, ta_out, tb, tc, p, grid, stream);
     }
   }
   if (swiglu) return launch_pair_variant<256, 6, false, true>(ta_shard, ta_out, tb, tc, p, grid, stream);

@@ -71,9 +71,6 @@ struct AgMatmulParams {
   int tail_splits;       // K parts per such tile (2, 4 or 8)
   float* tail_scratch;   // [tail_tiles][tail_splits][2 CTAs][128 x BN] fp32 partial accumulators
   uint32_t* tail_counters;   // [tail_tiles][2] arrivals, zeroed before the launch
-  // L2 eviction hints (2-CTA kernel, bf16, hinted instantiation only): 1 = B tiles evict_last,
-  // 2 = also A tiles evict_first, 3 = also the stores of C evict_first
-  int l2_hints;
   // optional per-CTA %globaltimer record (2-CTA kernel), kTraceSlots words per CTA; see ag_trace::
   uint64_t* trace;
 };

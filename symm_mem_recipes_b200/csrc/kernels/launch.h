@@ -105,9 +105,6 @@ struct AgMatmulArgs {
   size_t tail_scratch_bytes;
   uint32_t* tail_counters;
   size_t tail_counter_slots;
-  // 2-CTA kernel, bf16, plain epilogue: L2 eviction hints on the operand loads (0 = none;
-  // 1 = B evict_last; 2 = also A evict_first; 3 = also the stores of C evict_first)
-  int l2_hints;
   // 2-CTA kernel: optional [num_sms][12] words of per-CTA timing (ag_trace:: in ag_matmul_common.cuh)
   uint64_t* trace;
   // push mode: own 128-row blocks multiplied before the first remote one (-1 = chosen by the launcher)

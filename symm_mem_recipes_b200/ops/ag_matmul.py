@@ -52,10 +52,6 @@ class AgMatmulConfig:
     # shards with copier CTAs; "push_copy" = gather by push into the internal symmetric buffer on the CTA-pair
     # kernel, then one device-to-device copy into a_out
     plain_a_out: str = os.environ.get("SMR_AGMM_PLAIN_A_OUT", "pull")
-    # L2 eviction hints on the CTA-pair kernel (bf16, plain epilogue): 0 none; 1 = B tiles evict_last (every
-    # wave of tiles re-reads B); 2 = also A tiles evict_first (A passes through once); 3 = also the stores
-    # of C evict_first
-    l2_hints: int = _env_int("SMR_AGMM_L2_HINTS", 0)
     # push gather: own 128-row blocks multiplied before the first remote one (-1 = the launcher's choice)
     lead: int = _env_int("SMR_AGMM_LEAD", -1)
     # push gather pacing (0 = the launcher's choice): rounds of tiles by which the broadcast runs ahead of the
@@ -87,16 +83,6 @@ def _tail_buffer(device: torch.device, config: "AgMatmulConfig"):
     return t
 
 _flags: dict[int, torch.Tensor] = {}
-
-
-def _l2_hints(config: "AgMatmulConfig", dtype: torch.dtype, epi: int) -> int:
-    """The hint level the kernel gets: the hinted instantiations exist for bf16
-    with the plain epilogue on the CTA-pair kernel; elsewhere the knob is ignored."""
-    if not 0 <= config.l2_hints <= 3:
-        raise SymmMemError("AgMatmulConfig.l2_hints must be 0, 1, 2 or 3")
-    if not config.cta_pair or dtype != torch.bfloat16 or epi:
-        return 0
-    return int(config.l2_hints)
 
 
 def _push_plain_stores(config: "AgMatmulConfig", world_size: int) -> bool:
@@ -217,7 +203,7 @@ def matmul(a: torch.Tensor, b: torch.Tensor, c_out: Optional[torch.Tensor] = Non
     sms = config.num_sms or _num_sms(a.device)
     bn = 256 if epi else (config.block_n or choose_block_n(M, N, sms, config.cta_pair))
     C.ag_matmul(a, b, c_out, 0, None, 0, None, 0, None, None, bn, sms, 0, config.timeout_ms * 1_000_000,
-                config.cta_pair, _tail_buffer(a.device, config), epi, _l2_hints(config, a.dtype, epi), trace)
+                config.cta_pair, _tail_buffer(a.device, config), epi, trace)
     return c_out
 
 
@@ -319,7 +305,7 @@ def all_gather_matmul(a_shard: torch.Tensor, b: torch.Tensor, a_out: Optional[to
         _check_gather_geometry(rec.notes, (aout_offset, M, K, a_shard.dtype))
         C.ag_matmul(a_shard, b, c_out, 2, None, 0, hdl.native, aout_offset, a_out, None,
                     bn, sms, n_copy, t_ns, config.cta_pair, _tail_buffer(a_shard.device, config), epi,
-                    _l2_hints(config, a_shard.dtype, epi), trace, config.lead, config.push_ahead,
+                    trace, config.lead, config.push_ahead,
                     config.push_spread, _push_plain_stores(config, ws), config.push_pieces)
         return c_out
     if config.plain_a_out == "push_copy":

@@ -177,8 +177,6 @@ def build_checks(world: int, rank: int, dev: torch.device) -> list:
             "push_copy", cfg=AgMatmulConfig(timeout_ms=5000, plain_a_out="push_copy")), True)
     add("all_gather_matmul", "float8_e4m3fn", agmm("push", dtype=torch.float8_e4m3fn), True)
     add("all_gather_matmul", "SwiGLU epilogue", agmm("push", epilogue="swiglu"), True)
-    add("all_gather_matmul", "L2 eviction hints (level 3)", agmm(
-        "push", cfg=AgMatmulConfig(timeout_ms=5000, l2_hints=3)), True)
 
     # ------------------------------------------------------------------ row-parallel GEMMs
     def row_parallel(op, **kw):

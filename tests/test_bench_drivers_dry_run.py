@@ -254,7 +254,7 @@ class _FakeTorchOneGpu:
 
 
 @pytest.mark.parametrize("argv", [
-    ["--M", "256", "--N", "512", "--K", "128", "--l2-hints", "sweep"],
+    ["--M", "256", "--N", "512", "--K", "128"],
     ["--M", "256", "--N", "512", "--K", "128", "--variant", "fp8"],
     ["--M", "256", "--N", "512", "--K", "128", "--variant", "swiglu"],
     ["--op", "gemv", "--batch", "4", "--K", "256", "--N", "512", "--gemv-algo", "tc_tagged"],
@@ -325,8 +325,6 @@ def test_single_gpu_driver(monkeypatch, capsys, argv):
         symm_mem.reset()
     rec = json.loads([ln for ln in capsys.readouterr().out.splitlines() if ln.startswith("{")][-1])
     assert rec["op"] == (argv[1] if argv[0] == "--op" else "matmul") and "clocks" in rec
-    if "--l2-hints" in argv:
-        assert {"smr_us", "smr_l2_hints_1_us", "smr_l2_hints_2_us", "smr_l2_hints_3_us"} <= set(rec)
 
 
 def test_barrier_driver(tmp_path):

@@ -38,27 +38,6 @@ def test_matmul_small(block_n, shape, cta_pair):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("level", [1, 2, 3])
-@pytest.mark.parametrize("block_n,shape", [(256, (640, 1000, 1024)), (224, (200, 328, 96)), (128, (2048, 3584, 512))])
-def test_matmul_l2_hints_change_nothing_but_the_cache_policy(level, block_n, shape):
-    """Same bits as the kernel without hints: the hinted instantiation differs
-    only in the eviction policy attached to its loads and stores."""
-    from symm_mem_recipes_b200.ops.ag_matmul import AgMatmulConfig, matmul
-    from symm_mem_recipes_b200.parallel import symm_mem
-
-    M, N, K = shape
-    torch.manual_seed(M + N + K)
-    a = (torch.randn(M, K, device="cuda") * 0.5).to(torch.bfloat16)
-    b = (torch.randn(N, K, device="cuda") * 0.5).to(torch.bfloat16)
-    plain = matmul(a, b, None, AgMatmulConfig(block_n=block_n, timeout_ms=2000))
-    c, intact = guarded_empty((M, N), torch.bfloat16, "cuda")
-    c.fill_(float("nan"))
-    matmul(a, b, c, AgMatmulConfig(block_n=block_n, timeout_ms=2000, l2_hints=level))
-    symm_mem.check_status("cuda")
-    assert torch.equal(c.view(torch.int16), plain.view(torch.int16)) and intact()
-
-
-@pytest.mark.gpu
 @pytest.mark.parametrize("shape,num_sms", [((768, 768, 1024), 8), ((1280, 512, 512), 8), ((768, 768, 4096), 8),
                                            ((16384, 3584, 1024), 0)])
 def test_matmul_split_k_tail(shape, num_sms):

@@ -136,8 +136,6 @@ FUNCTIONS = [
     ("test_gpu_layer_glue", "test_silu_mul", {"rows": 19, "F": 48}),
     ("test_gpu_layer_glue", "test_decode_attention", {"B": 3, "hq": 4, "hkv": 2, "D": 64, "s_max": 40,
                                                       "positions": (0, 7, 39)}),
-    ("test_gpu_matmul", "test_matmul_l2_hints_change_nothing_but_the_cache_policy",
-     {"level": 3, "block_n": 256, "shape": (256, 512, 128)}),
     ("test_gpu_matmul", "test_matmul_small", {"block_n": 224, "shape": (200, 328, 96), "cta_pair": True}),
     ("test_gpu_layer_glue", "test_layer_with_fused_glue_matches_fp32", {}),
     ("test_gpu_layer_glue", "test_layer_with_fused_swiglu_matches_fp32", {}),
