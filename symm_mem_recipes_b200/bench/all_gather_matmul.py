@@ -43,12 +43,12 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--GROUP_SIZE_M", type=int, default=1, help="ignored: tiles are scheduled N-fastest")
     ap.add_argument("--num_stages", type=int, default=0, help="ignored: follows from the tile (4-8 stages)")
     ap.add_argument("--num_warps", type=int, default=6, help="fixed: TMA, MMA and four epilogue warps")
-    ap.add_argument("--copy-ctas", default="", help="pull mode: comma-separated copier-CTA counts to time")
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--iters", type=int, default=25)
     ap.add_argument("--out", default=None)
-    ap.add_argument("--with-push-copy", action="store_true",
-                    help="also time an ordinary a_out served by the push kernel plus one local copy")
+    ap.add_argument("--with-plain-a-out", "--with-push-copy", dest="with_plain_a_out", action="store_true",
+                    help="also time the upstream calling convention: an ordinary (non-symmetric) a_out, served "
+                         "through the internal symmetric buffer plus one local copy")
     ap.add_argument("--leads", default="", help="push mode: comma-separated counts of own 128-row blocks multiplied "
                                                 "before the first remote one, each timed")
     ap.add_argument("--pacings", default="", help="push mode: comma-separated AHEAD:SPREAD[:LEAD[:PLAIN[:PIECES]]] settings, each timed "
@@ -105,7 +105,7 @@ def _one_shape(args, M, N, K, rank, world, dev, lines) -> None:
     bt = b.t()
     c = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
     a_out = symm_mem.empty(M, K, dtype=torch.bfloat16, device=dev)       # push (broadcast) path
-    a_out_plain = torch.empty(M, K, dtype=torch.bfloat16, device=dev)    # pull path
+    a_out_plain = torch.empty(M, K, dtype=torch.bfloat16, device=dev)    # the upstream calling convention
     symm_mem.rendezvous(a_shard)
     symm_mem.rendezvous(a_out)
     flops = 2.0 * M * N * K
@@ -197,22 +197,16 @@ def _one_shape(args, M, N, K, rank, world, dev, lines) -> None:
                     print(line, flush=True)
                     lines.append(line)
         symm_mem.check_status(dev)
-    for n_copy in [int(x) for x in args.copy_ctas.split(",") if x]:
-        cfg = AgMatmulConfig(block_n=args.block_n, n_copy=n_copy)
-        us = benchmark_with_event(lambda: smr.all_gather_matmul(a_shard, b, a_out_plain, c, cfg), **bench)
-        emit("smr_fused", us, copy_ctas=n_copy, gather="pull")
-        symm_mem.check_status(dev)
-    if args.with_push_copy:
-        def push_copy():
-            cfgp = AgMatmulConfig(block_n=args.block_n, plain_a_out="push_copy")
-            us = benchmark_with_event(lambda: smr.all_gather_matmul(a_shard, b, a_out_plain, c, cfgp), **bench)
+    if args.with_plain_a_out:
+        def plain_a_out():
+            us = benchmark_with_event(lambda: smr.all_gather_matmul(a_shard, b, a_out_plain, c, cfg0), **bench)
             symm_mem.check_status(dev)
             if not torch.allclose(c0.float(), c.float(), rtol=2e-2, atol=2e-3):
-                raise RuntimeError("push_copy result differs from NCCL + cuBLAS")
+                raise RuntimeError("the result with an ordinary a_out differs from NCCL + cuBLAS")
             emit("smr_fused", us, gather="push_copy")
 
         from symm_mem_recipes_b200.bench._common import attempt
-        attempt("all_gather_matmul with an ordinary a_out by push and copy", push_copy, dev,
+        attempt("all_gather_matmul with an ordinary a_out", plain_a_out, dev,
                 lambda rec: (print(json.dumps(rec), flush=True), lines.append(json.dumps(rec))) if rank == 0 else None)
 
 

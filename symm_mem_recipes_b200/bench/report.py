@@ -105,8 +105,7 @@ def ag_matmul_table(recs: list[dict], peaks: Optional[dict]) -> Optional[str]:
             continue
         name = r["impl"]
         if name == "smr_fused":
-            copiers = f", {r['copy_ctas']} copy CTAs" if "copy_ctas" in r else ""
-            name = f"smr_fused ({r.get('gather', 'push')}{copiers})"
+            name = f"smr_fused ({r.get('gather', 'push')})"
         groups.setdefault((r["world_size"], r["M"], r["N"], r["K"]), {})[name] = r
     if not groups:
         return None

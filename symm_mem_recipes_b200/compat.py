@@ -48,8 +48,9 @@ def all_gather_matmul_tma_persistent(a_shard: torch.Tensor, b: torch.Tensor, a_o
                                      c_out: torch.Tensor, configs: Optional[dict] = None,
                                      mm_only: bool = False) -> torch.Tensor:
     """Upstream signature (triton_all_gather_matmul.py:219-226) on the fused kernel of this
-    package.  `a_out` may be an ordinary tensor, as upstream allocates it (:376); a symmetric
-    one (`symm_mem.empty`) selects the faster push gather."""
+    package.  `a_out` may be an ordinary tensor, as upstream allocates it (:376): the gather then
+    goes through an internal symmetric buffer and one copy; a symmetric one (`symm_mem.empty`)
+    is gathered into directly."""
     return all_gather_matmul(a_shard, b, a_out, c_out, _config_from_dict(configs), mm_only)
 
 

@@ -478,13 +478,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   }, py::arg("alloc"), py::arg("offset_bytes"), py::arg("numel"), py::arg("max_blocks"), py::arg("timeout_ns"));
 
   // a: own shard (or all of A when mode == 0), b: [N, K], c: [M, N]
-  // mode 1 (pull): `shard_alloc` holds a; a_out is an ordinary tensor.
   // mode 2 (push): `aout_alloc` holds a_out; a is any CUDA tensor.
   m.def("ag_matmul", [](torch::Tensor a, torch::Tensor b, torch::Tensor c, int mode,
-                        std::shared_ptr<CudaSymmAllocation> shard_alloc, int64_t shard_offset,
                         std::shared_ptr<CudaSymmAllocation> aout_alloc, int64_t aout_offset,
-                        c10::optional<torch::Tensor> a_out, c10::optional<torch::Tensor> flags,
-                        int block_n, int num_sms, int n_copy, uint64_t timeout_ns, bool cta_pair,
+                        c10::optional<torch::Tensor> a_out, int block_n, int num_sms, uint64_t timeout_ns,
                         c10::optional<torch::Tensor> tail_scratch, int epilogue,
                         c10::optional<torch::Tensor> trace, int lead, int push_ahead, int push_spread,
                         bool push_plain_stores, int push_pieces) {
@@ -496,8 +493,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     };
     TORCH_CHECK(ok2d(a) && ok2d(b) && ok2d(c), "a, b, c must be contiguous 2-D CUDA tensors of one dtype");
     TORCH_CHECK(a.size(1) == b.size(1), "A[*, K] and B[N, K] disagree on K");
-    TORCH_CHECK(!fp8 || (cta_pair && mode != 1),
-                "float8_e4m3fn runs on the CTA-pair kernel: a_out must be symmetric memory (push) or absent");
     int dev = a.get_device();
     TORCH_CHECK(b.get_device() == dev && c.get_device() == dev, "a, b and c must live on one GPU");
     c10::cuda::CUDAGuard guard(dev);
@@ -510,19 +505,16 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     args.K = (int)a.size(1);
     args.elem_bytes = fp8 ? 1 : 2;
     args.epilogue = epilogue;
-    TORCH_CHECK(epilogue == 0 || (epilogue == 1 && cta_pair && mode != 1 && !fp8),
-                "the SwiGLU epilogue runs on the bf16 CTA-pair kernel (a_out symmetric or absent)");
+    TORCH_CHECK(epilogue == 0 || (epilogue == 1 && !fp8), "the SwiGLU epilogue is a bfloat16 epilogue");
     args.block_n = block_n;
     args.num_sms = num_sms;
     args.timeout_ns = timeout_ns;
     args.status = status_for(dev);
     args.mode = mode;
     if (mode != 0) {
-      TORCH_CHECK(mode == 1 || mode == 2, "mode must be 0, 1 or 2");
-      const CudaSymmAllocation* sym = mode == 1 ? shard_alloc.get() : aout_alloc.get();
-      TORCH_CHECK(sym != nullptr && a_out.has_value(), "communication needs a symmetric allocation and a_out");
-      PeerView pv = view_of(*sym);
-      args.n_copy = n_copy;
+      TORCH_CHECK(mode == 2, "mode must be 0 (no gather) or 2 (push)");
+      TORCH_CHECK(aout_alloc != nullptr && a_out.has_value(), "the gather needs a symmetric a_out");
+      PeerView pv = view_of(*aout_alloc);
       args.rank = pv.rank;
       args.world_size = pv.world_size;
       args.rows_per_rank = (int)a.size(0);
@@ -531,29 +523,18 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       args.barrier_block_base = 1024;
       TORCH_CHECK(ok2d(*a_out) && a_out->size(0) == args.M && a_out->size(1) == args.K, "a_out must be [M, K] of a's dtype");
       args.a_out = a_out->data_ptr();
-      int n_blocks = (args.M + 127) / 128;
-      if (mode == 1) {
-        TORCH_CHECK(flags.has_value() && flags->is_cuda() && flags->element_size() == 4 &&
-                    flags->numel() >= n_blocks, "flags too small");
-        args.buffers = pv.buffers;
-        args.shard_offset = (size_t)shard_offset;
-        args.flags = reinterpret_cast<uint32_t*>(flags->data_ptr());
-        rt_check(cudaMemsetAsync(args.flags, 0, sizeof(uint32_t) * n_blocks, stream), "cudaMemsetAsync(flags)");
-      } else {
-        TORCH_CHECK((char*)a_out->data_ptr() == (char*)aout_alloc->local_ptr() + aout_offset,
-                    "a_out does not sit at aout_offset of its allocation");
-        args.aout_buffers = pv.buffers;
-        args.aout_mc = pv.multicast;
-        args.aout_offset = (size_t)aout_offset;
-        args.local_pad = aout_alloc->peer_pad(pv.rank);
-      }
+      TORCH_CHECK((char*)a_out->data_ptr() == (char*)aout_alloc->local_ptr() + aout_offset,
+                  "a_out does not sit at aout_offset of its allocation");
+      args.aout_buffers = pv.buffers;
+      args.aout_mc = pv.multicast;
+      args.aout_offset = (size_t)aout_offset;
+      args.local_pad = aout_alloc->peer_pad(pv.rank);
     } else {
-      args.n_copy = 0;
       args.M = (int)a.size(0);
     }
     TORCH_CHECK(c.size(0) == args.M && c.size(1) == (epilogue == 1 ? args.N / 2 : args.N),
                 "c must be [M, N] ([M, N / 2] with the SwiGLU epilogue)");
-    if (tail_scratch.has_value() && cta_pair) {
+    if (tail_scratch.has_value()) {
       // first 4 KiB: arrival counters; the rest: fp32 partial accumulators
       TORCH_CHECK(tail_scratch->is_cuda() && tail_scratch->is_contiguous() && tail_scratch->nbytes() > 8192,
                   "tail_scratch must be a contiguous CUDA tensor");
@@ -569,18 +550,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     args.push_plain_stores = push_plain_stores ? 1 : 0;
     args.push_pieces = push_pieces;
     if (trace.has_value()) {
-      TORCH_CHECK(cta_pair && mode != 1, "the timing record belongs to the CTA-pair kernel");
       TORCH_CHECK(trace->is_cuda() && trace->get_device() == dev && trace->is_contiguous() &&
                   trace->scalar_type() == torch::kInt64 && trace->numel() >= (int64_t)num_sms * 12,
                   "trace must be a contiguous int64 CUDA tensor of num_sms x 12 words");
       args.trace = reinterpret_cast<uint64_t*>(trace->data_ptr());
     }
-    rt_check(cta_pair && mode != 1 ? launch_ag_matmul_2cta(args, stream) : launch_ag_matmul(args, stream),
-             "ag_matmul");
-  }, py::arg("a"), py::arg("b"), py::arg("c"), py::arg("mode"), py::arg("shard_alloc"),
-     py::arg("shard_offset"), py::arg("aout_alloc"), py::arg("aout_offset"), py::arg("a_out"),
-     py::arg("flags"), py::arg("block_n"), py::arg("num_sms"), py::arg("n_copy"), py::arg("timeout_ns"),
-     py::arg("cta_pair") = false, py::arg("tail_scratch") = py::none(), py::arg("epilogue") = 0,
+    rt_check(launch_ag_matmul_2cta(args, stream), "ag_matmul");
+  }, py::arg("a"), py::arg("b"), py::arg("c"), py::arg("mode"), py::arg("aout_alloc"), py::arg("aout_offset"),
+     py::arg("a_out"), py::arg("block_n"), py::arg("num_sms"), py::arg("timeout_ns"),
+     py::arg("tail_scratch") = py::none(), py::arg("epilogue") = 0,
      py::arg("trace") = py::none(), py::arg("lead") = -1,
      py::arg("push_ahead") = 0, py::arg("push_spread") = 0, py::arg("push_plain_stores") = false,
      py::arg("push_pieces") = 0);

@@ -1,6 +1,6 @@
-// Pieces shared by the 1-CTA and the 2-CTA (cta_group::2) all_gather_matmul
-// kernels: parameters, the M schedule, the epilogue-warp push of the own shard
-// and the tensor-map builder.
+// Pieces of the all_gather_matmul kernel (ag_matmul_2cta_sm100.cu) that its launcher and the
+// host-side schedule checks share: parameters, the M schedule, the epilogue-warp push of the
+// own shard and the tensor-map builder.
 //
 // Upstream counterparts (symm_mem_recipes/triton_all_gather_matmul.py):
 //   push_pieces + arrival counters   <->  all_gather_with_progress, :20-56 (copy
@@ -30,9 +30,6 @@ constexpr int kUmmaK = 16;
 constexpr int kGemmThreads = 192; // 6 warps
 constexpr int kEpiWarp0 = 2;
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kCopyChunk = 16384;   // bytes per bulk copy
-constexpr int kStoreLag = 2;             // bulk stores allowed to still read smem
-constexpr int kFlagLag = 6;              // chunks after which a block's writes are drained
 // Push mode: a block's arrival counter grows by kArrivalUnits per call whatever the number of pieces
 // (each piece adds kArrivalUnits / pieces), so calls with different piece counts can share an allocation.
 constexpr uint32_t kArrivalUnits = 256;  // pieces: a power of two up to this
@@ -40,30 +37,27 @@ constexpr uint32_t kArrivalUnits = 256;  // pieces: a power of two up to this
 struct AgMatmulParams {
   __nv_bfloat16* c;      // [M, N]; one byte per element when elem_bytes == 1
   int M, N, K;
-  int elem_bytes;        // 2 = bf16 in and out; 1 = fp8 e4m3 in and out (2-CTA kernel only)
+  int elem_bytes;        // 2 = bf16 in and out; 1 = fp8 e4m3 in and out
   int n_tiles_n;         // ceil(N / BN)
   int n_blocks_m;        // ceil(M / 128)
   // gather
   int rank, world_size;
   int blocks_per_rank;   // 128-row blocks per shard
-  int n_copy;            // copier CTAs (0 = no communication)
-  int mode;              // 0 none, 1 pull, 2 push
+  int mode;              // 0 none, 2 push
   int lead;              // own blocks scheduled before the first remote one
   int pieces;            // push: pieces per 128-row block (arrivals per block and call)
   int push_ahead;        // push: rounds of tiles by which the broadcast runs ahead of the first need (>= 1)
   int push_spread;       // push: rounds over which the whole shard is broadcast at the latest
   uint32_t* flags;       // [n_blocks_m] arrival flags read by the GEMM CTAs (local memory)
-  uint32_t flag_target;  // pull: 1 (flags zeroed before launch); push: filled from the epoch
+  uint32_t flag_target;  // filled from the call number in the kernel
   uint32_t* header;      // push: [0] epoch, [1] CTAs done (local, in the a_out signal pad)
   const char* a_local;   // own shard
   void* const* aout_buffers;   // push: payload base of the a_out allocation on every rank
   void* aout_mc;         // push: multicast payload base of the a_out allocation, or nullptr
   size_t aout_offset;    // push: offset of a_out inside that payload
-  void* const* buffers;  // device table [WS]: symmetric payload base of every rank (peer-mapped)
-  size_t shard_offset;   // offset of the A shard inside the payload
   char* a_out;           // local gathered A [M, K]
-  uint32_t* const* pads; // signal pads (entry / exit barrier of the copiers)
-  uint32_t barrier_block_base;     // first blockwise-barrier slot id used by copiers
+  uint32_t* const* pads; // signal pads (entry barrier of the push)
+  uint32_t barrier_block_base;     // first blockwise-barrier slot id used by it
   uint64_t timeout_ns;
   Status* status;
   // split-K tail (2-CTA kernel): the tiles of the last, partly filled wave are cut along K

@@ -64,35 +64,27 @@ int launch_multimem_all_reduce(const PeerView& pv, size_t offset_bytes, size_t n
                                int max_blocks, uint64_t timeout_ns, Status* status,
                                cudaStream_t stream);
 
-// ---- all_gather_matmul (tcgen05 GEMM + in-kernel all-gather) ---------------
+// ---- all_gather_matmul (tcgen05 GEMM on CTA pairs + in-kernel all-gather) ---
 struct AgMatmulArgs {
-  const void* a_local;   // own A shard [rows_per_rank, K] (or all of A [M, K] when n_copy == 0)
+  const void* a_local;   // own A shard [rows_per_rank, K] (all of A [M, K] when mode == 0)
   const void* b;         // [N, K] bf16, K-major
   void* c;               // [M, N] bf16
   int M, N, K;
   // 0 or 2: bf16.  1: A, B, C and a_out hold fp8 e4m3 (fp32 accumulation, no scale factors,
-  // as upstream's FP8_OUTPUT path); 2-CTA kernel, modes 0 and 2; N and K multiples of 16.
+  // as upstream's FP8_OUTPUT path); N and K multiples of 16.
   int elem_bytes;
-  // 0: C[M, N] = A B^T.  1 (2-CTA kernel, bf16, block_n 256, N % 256 == 0): B's rows are interleaved
+  // 0: C[M, N] = A B^T.  1 (bf16, block_n 256, N % 256 == 0): B's rows are interleaved
   // in groups of 128 (gate rows, then the matching up rows) and C[M, N / 2] = SiLU(gate) * up.
   int epilogue;
   int block_n;           // 128, 192, 224 or 256
-  int num_sms;           // CTAs to launch at most (copiers included)
-  // communication: mode 0 = none (GEMM over a_local only),
-  //   1 = pull (a_out ordinary memory; the A shards are symmetric and copier
-  //       CTAs fetch the peers' shards),
-  //   2 = push (a_out symmetric; copier CTAs broadcast the own shard).
+  int num_sms;           // CTAs to launch at most
+  // communication: mode 0 = none (GEMM over a_local only), 2 = push (a_out symmetric; the
+  // epilogue warps of the GEMM CTAs broadcast the own shard into every rank's a_out)
   int mode;
-  int n_copy;            // copier CTAs
   int rank, world_size;
   int rows_per_rank;     // multiple of 128
   void* a_out;           // local gathered A [M, K]
-  uint32_t* const* pads; // signal pads of the symmetric allocation in use
-  // pull
-  void* const* buffers;  // device table: payload base of the A-shard allocation on every rank
-  size_t shard_offset;   // offset of the A shard inside that payload
-  uint32_t* flags;       // local [ceil(M/128)], zeroed (stream-ordered) before the launch
-  // push
+  uint32_t* const* pads; // signal pads of the a_out allocation
   void* const* aout_buffers;  // device table: payload base of the a_out allocation on every rank
   void* aout_mc;              // its multicast base or nullptr
   size_t aout_offset;         // offset of a_out inside that payload
@@ -100,12 +92,12 @@ struct AgMatmulArgs {
   uint32_t barrier_block_base;
   uint64_t timeout_ns;
   Status* status;
-  // optional scratch of the 2-CTA kernel's split-K tail (nullptr = never split)
+  // optional scratch of the split-K tail (nullptr = never split)
   void* tail_scratch;
   size_t tail_scratch_bytes;
   uint32_t* tail_counters;
   size_t tail_counter_slots;
-  // 2-CTA kernel: optional [num_sms][12] words of per-CTA timing (ag_trace:: in ag_matmul_common.cuh)
+  // optional [num_sms][12] words of per-CTA timing (ag_trace:: in ag_matmul_common.cuh)
   uint64_t* trace;
   // push mode: own 128-row blocks multiplied before the first remote one (-1 = chosen by the launcher)
   int lead;
@@ -121,8 +113,6 @@ struct AgMatmulArgs {
   // has arrived when all of its pieces have, each pushed by another CTA
   int push_pieces;
 };
-int launch_ag_matmul(const AgMatmulArgs& args, cudaStream_t stream);
-// Same contract on CTA pairs (tcgen05 cta_group::2, 256 x BN tiles); modes 0 and 2 only.
 int launch_ag_matmul_2cta(const AgMatmulArgs& args, cudaStream_t stream);
 
 // Host-side checks of the kernels' scheduling arithmetic (schedule_check.cu); 0 = invariants hold.

@@ -93,88 +93,107 @@ __host__ __device__ __forceinline__ void row_block_coords(const RsParams& p, int
   if (dest >= p.world_size) dest -= p.world_size;
 }
 
-// Ordered fp32 sum of the WS partials of one [128 x 256] output tile, read from the
-// strip-major inbox (un-doing the row XOR of the 16-byte chunks) and written row-major.
-// 16 independent 16-byte loads are in flight per thread (the phase is bound by memory
-// latency otherwise): 16 / WS output vectors at a time.  WS = 0: generic loop.
-// kAllReduce: instead of the local [M/WS, N] output, the tile goes to rows
-// [rank * M/WS + ...] of the symmetric [M, N] output of EVERY rank (one multimem.st, or WS stores).
+// Epilogue of a tile of the rank's own rows, one thread per row `r` of the CTA's 128-row block:
+// the row's accumulator (TMEM) and the peers' bf16 partials of the same row (strip-major inbox,
+// 16-byte chunks XOR-swizzled by row) are added in rank order in fp32, the own value rounded to
+// bf16 first as if it had crossed the wire, and the bf16 result is written row-major.  CH x 8
+// columns at a time (32 up to four ranks, 16 at eight: the loaded vectors live in registers):
+// (WS - 1) x CH independent 16-byte loads in flight per thread.  WS = 0: generic loop.
+// kAllReduce: instead of the local [M/WS, N] output, the row goes to rows [rank * M/WS + ...] of
+// the symmetric [M, N] output of EVERY rank (one multimem.st per 16 bytes, or WS stores).
+__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+
 template <int WS, bool kAllReduce = false>
-__device__ __forceinline__ void reduce_tile(const RsParams& p, const char* inbox, int mb, int ni) {
+__device__ __forceinline__ void reduce_own_tile(const RsParams& p, uint32_t taddr, int mb, int ni, int r) {
+  constexpr int CH = (WS == 0 || WS > 4) ? 2 : 4;           // 16-byte chunks (8 columns each) per step
+  constexpr int COLS = CH * 8;
   const int n0 = ni * kBN;
-  const int strips = min(kStripsPerTile, (p.N - n0 + kStripCols - 1) / kStripCols);
-  const int total = strips * kBM * 8;                       // 16-byte vectors of the tile
+  const char* inbox = static_cast<const char*>(p.buffers[p.rank]) + p.inbox_offset;
   const size_t src_stride = (size_t)p.blocks_per_rank * p.n_tiles_n * kStripsPerTile * kStripBytesOne;
-  const char* tile_base = inbox + strip_offset(0, mb, ni, 0, p.blocks_per_rank, p.n_tiles_n);
-  // vector idx -> (strip, row, chunk): consecutive idx walk a strip's bytes in order (coalesced)
-  auto locate = [&](int idx, size_t& in_off, size_t& out_off, bool& in_range) {
-    const int sidx = idx / (kBM * 8), rem = idx - sidx * (kBM * 8);
-    const int row = rem >> 3, pos = rem & 7;                // pos: position inside the swizzled row
-    const int c = pos ^ (row & 7);                          // logical 16-byte chunk
-    in_off = (size_t)sidx * kStripBytesOne + (size_t)rem * 16;
-    const int col = n0 + sidx * kStripCols + c * 8;
-    in_range = col < p.N;
-    out_off = (size_t)(mb * kBM + row) * p.N + col;
-  };
-  constexpr int U = WS == 0 ? 1 : 16 / WS;
-  for (int idx0 = threadIdx.x; idx0 < total; idx0 += kThreads * U) {
-    Vec16 v[U][WS == 0 ? 1 : WS];
-    size_t out_off[U];
-    bool live[U];
-    float s[U][8];
+  const int ws = WS == 0 ? p.world_size : WS;
+  const size_t out_row = (size_t)(mb * kBM + r);
+#pragma unroll 1
+  for (int h = 0; h < kBN / COLS; ++h) {
+    const int col0 = n0 + h * COLS;
+    if (col0 >= p.N) break;                                 // uniform over the CTA
+    const int sidx = (h * COLS) / kStripCols, c0 = ((h * COLS) % kStripCols) / 8;   // strip, first logical chunk in it
+    uint32_t own[COLS];
+    if constexpr (CH == 4) tmem_ld_32x32b_x32(taddr + (uint32_t)(h * COLS), own);
+    else tmem_ld_32x32b_x16(taddr + (uint32_t)(h * COLS), own);
+    const char* row_base = inbox + strip_offset(0, mb, ni, sidx, p.blocks_per_rank, p.n_tiles_n) + (size_t)r * 128;
+    float s[COLS];
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int idx = idx0 + u * kThreads;
-      size_t in_off = 0;
-      live[u] = false;
-      if (idx < total) locate(idx, in_off, out_off[u], live[u]);
+    for (int q = 0; q < COLS; ++q) s[q] = 0.f;
+    auto add_vec = [&](int c, const Vec16& w) {
+      s[c * 8 + 0] += bf16lo_to_f32(w.x); s[c * 8 + 1] += bf16hi_to_f32(w.x);
+      s[c * 8 + 2] += bf16lo_to_f32(w.y); s[c * 8 + 3] += bf16hi_to_f32(w.y);
+      s[c * 8 + 4] += bf16lo_to_f32(w.z); s[c * 8 + 5] += bf16hi_to_f32(w.z);
+      s[c * 8 + 6] += bf16lo_to_f32(w.w); s[c * 8 + 7] += bf16hi_to_f32(w.w);
+    };
+    auto own_vec = [&](int c) {
+      Vec16 w;
+      w.x = pack_bf16x2(__uint_as_float(own[c * 8 + 0]), __uint_as_float(own[c * 8 + 1]));
+      w.y = pack_bf16x2(__uint_as_float(own[c * 8 + 2]), __uint_as_float(own[c * 8 + 3]));
+      w.z = pack_bf16x2(__uint_as_float(own[c * 8 + 4]), __uint_as_float(own[c * 8 + 5]));
+      w.w = pack_bf16x2(__uint_as_float(own[c * 8 + 6]), __uint_as_float(own[c * 8 + 7]));
+      return w;
+    };
+    if constexpr (WS == 0) {
+      tmem_ld_wait();
+      for (int src = 0; src < ws; ++src) {
 #pragma unroll
-      for (int q = 0; q < 8; ++q) s[u][q] = 0.f;
-      if (live[u]) {
-        if constexpr (WS == 0) {
-          for (int src = 0; src < p.world_size; ++src) {
-            const Vec16 w = ld_16_stream(tile_base + (size_t)src * src_stride + in_off);
-            s[u][0] += bf16lo_to_f32(w.x); s[u][1] += bf16hi_to_f32(w.x);
-            s[u][2] += bf16lo_to_f32(w.y); s[u][3] += bf16hi_to_f32(w.y);
-            s[u][4] += bf16lo_to_f32(w.z); s[u][5] += bf16hi_to_f32(w.z);
-            s[u][6] += bf16lo_to_f32(w.w); s[u][7] += bf16hi_to_f32(w.w);
-          }
-        } else {
-#pragma unroll
-          for (int src = 0; src < WS; ++src) v[u][src] = ld_16_stream(tile_base + (size_t)src * src_stride + in_off);
+        for (int c = 0; c < CH; ++c) {
+          const Vec16 w = src == p.rank ? own_vec(c)
+                                        : ld_16_stream(row_base + (size_t)src * src_stride + (((c0 + c) ^ (r & 7)) << 4));
+          add_vec(c, w);
         }
+      }
+    } else {
+      Vec16 v[WS][CH];
+#pragma unroll
+      for (int src = 0; src < WS; ++src) {
+        if (src != p.rank) {
+#pragma unroll
+          for (int c = 0; c < CH; ++c)
+            v[src][c] = ld_16_stream(row_base + (size_t)src * src_stride + (((c0 + c) ^ (r & 7)) << 4));
+        }
+      }
+      tmem_ld_wait();
+#pragma unroll
+      for (int src = 0; src < WS; ++src) {
+#pragma unroll
+        for (int c = 0; c < CH; ++c) add_vec(c, src == p.rank ? own_vec(c) : v[src][c]);
       }
     }
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      if (!live[u]) continue;
-      if constexpr (WS != 0) {
-#pragma unroll
-        for (int src = 0; src < WS; ++src) {
-          const Vec16& w = v[u][src];
-          s[u][0] += bf16lo_to_f32(w.x); s[u][1] += bf16hi_to_f32(w.x);
-          s[u][2] += bf16lo_to_f32(w.y); s[u][3] += bf16hi_to_f32(w.y);
-          s[u][4] += bf16lo_to_f32(w.z); s[u][5] += bf16hi_to_f32(w.z);
-          s[u][6] += bf16lo_to_f32(w.w); s[u][7] += bf16hi_to_f32(w.w);
-        }
-      }
+    for (int c = 0; c < CH; ++c) {
+      const int col = col0 + c * 8;
+      if (col >= p.N) break;                                // N % 8 == 0
       Vec16 o;
-      o.x = pack_bf16x2(s[u][0], s[u][1]); o.y = pack_bf16x2(s[u][2], s[u][3]);
-      o.z = pack_bf16x2(s[u][4], s[u][5]); o.w = pack_bf16x2(s[u][6], s[u][7]);
+      o.x = pack_bf16x2(s[c * 8 + 0], s[c * 8 + 1]); o.y = pack_bf16x2(s[c * 8 + 2], s[c * 8 + 3]);
+      o.z = pack_bf16x2(s[c * 8 + 4], s[c * 8 + 5]); o.w = pack_bf16x2(s[c * 8 + 6], s[c * 8 + 7]);
       if constexpr (kAllReduce) {
         const size_t off = p.ar_offset +
-                           ((size_t)p.rank * p.blocks_per_rank * kBM * p.N + out_off[u]) * sizeof(__nv_bfloat16);
+                           (((size_t)p.rank * p.blocks_per_rank * kBM + out_row) * p.N + col) * sizeof(__nv_bfloat16);
         if (p.ar_mc != nullptr) {
           multimem_st_16(static_cast<char*>(p.ar_mc) + off, o);
         } else {
-          for (int s2 = 1; s2 <= p.world_size; ++s2) {            // own copy last
+          for (int s2 = 1; s2 <= p.world_size; ++s2) {      // own copy last
             int peer = p.rank + s2;
             if (peer >= p.world_size) peer -= p.world_size;
             st_16(static_cast<char*>(p.ar_peers[peer]) + off, o);
           }
         }
       } else {
-        st_16(p.out + out_off[u], o);
+        st_16(p.out + out_row * p.N + col, o);
       }
     }
   }

@@ -24,8 +24,13 @@
 //    (one CTA per tile; strips leaving by bulk copies, two to five in flight): 1.21x cuBLAS +
 //    NCCL at the down-projection shape where those reached 0.82x to 1.17x, and within 3 % of
 //    the best of them at the o-projection shape.
-//  * Reduce: after its GEMM tiles every CTA takes output tiles of its own rank, waits (bounded)
-//    until WS partials have arrived, sums them in rank order in fp32 and writes bf16.
+//  * Reduce: the tiles of the rank's OWN rows come last in the visiting order, when the peers'
+//    partials for them have long arrived.  Their epilogue does not ship the accumulator: it waits
+//    (bounded) for the tile's WS - 1 arrivals, reads the peers' bf16 partials out of the inbox
+//    (row by row, 28 independent 16-byte loads in flight per thread), adds them and its own
+//    accumulator (rounded to bf16 as if it had travelled) in rank order in fp32, and writes the
+//    final bf16 rows.  There is no separate reduction pass and the own partial never touches
+//    memory.
 //  * An entry barrier over the signal pad proves that every rank has finished reducing the
 //    previous call before its inbox is overwritten.  Counters count calls (epoch word in the
 //    pad), so nothing is reset between calls.
@@ -83,7 +88,7 @@ matmul_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const bool leader = cta_rank == 0;
   uint32_t* header = p.local_pad + kFlagSlotsBase;        // [0] epoch, [1] CTAs done
   const uint32_t epoch = ld_relaxed_gpu(&header[0]) + 1u;
-  const uint32_t target = epoch * (uint32_t)p.world_size;
+  const uint32_t target = epoch * (uint32_t)(p.world_size - 1);   // arrivals from the peers, per call
   uint32_t* my_counters = p.local_pad + kFlagSlotsBase + 2;
 
   if (threadIdx.x == 0) {
@@ -192,6 +197,7 @@ matmul_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int etid = (int)threadIdx.x - 64;
     const int r = quarter * 32 + lane;                  // row of this CTA's block owned by this thread
     uint32_t acc = 0, acc_phase = 0, strip_ctr = 0;
+    __shared__ int own_ok;
     for (int t = pair; t < total_tiles && !failed; t += n_pairs) {
       const int pr = t / p.n_tiles_n, ni = t - pr * p.n_tiles_n;
       const int rb = 2 * pr + (int)cta_rank;
@@ -207,7 +213,24 @@ matmul_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       tcgen05_fence_after_thread_sync();
       const uint32_t taddr = tmem_base + acc * 256u + ((uint32_t)(quarter * 32) << 16);
       int strips = 0;
-      if (valid) {
+      if (valid && dest == p.rank) {
+        // ---- own rows: every peer's partial of this tile is (about to be) in the inbox ----
+        if (etid == 0) {
+          own_ok = 1;
+          if (!wait_reached_acquire_sys(&my_counters[mb * p.n_tiles_n + ni], target, p.timeout_ns)) {
+            report_status(p.status, kTimeoutFlag, p.rank, blockIdx.x, mb * p.n_tiles_n + ni, kWhereRsArrive, target);
+            own_ok = 0;
+          }
+        }
+        epilogue_sync();
+        if (!own_ok) { failed = true; break; }
+        switch (p.world_size) {
+          case 2: reduce_own_tile<2, kAllReduce>(p, taddr, mb, ni, r); break;
+          case 4: reduce_own_tile<4, kAllReduce>(p, taddr, mb, ni, r); break;
+          case 8: reduce_own_tile<8, kAllReduce>(p, taddr, mb, ni, r); break;
+          default: reduce_own_tile<0, kAllReduce>(p, taddr, mb, ni, r); break;
+        }
+      } else if (valid) {
 #pragma unroll 1
         for (int sidx = 0; sidx < kStripsPerTile; ++sidx) {
           const int col0 = ni * kBN + sidx * kStripCols;
@@ -233,7 +256,7 @@ matmul_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc]), 0));
       epilogue_sync();                                   // every thread has issued its stores of this tile
-      if (etid == 0 && strips > 0)
+      if (etid == 0 && strips > 0)                       // (own tiles ship nothing: strips stays 0)
         red_add_release_sys(p.pads[dest] + kFlagSlotsBase + 2 + mb * p.n_tiles_n + ni, 1u);
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
@@ -250,27 +273,6 @@ matmul_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   tcgen05_fence_after_thread_sync();
   if (warp == 1) tmem_dealloc_pair(tmem_base, kTmemCols);
   if (p.trace != nullptr && threadIdx.x == 0) p.trace[blockIdx.x * 4 + 2] = globaltimer_ns();
-
-  // ---------------- reduce the tiles of this rank (every CTA on its own) ----------------
-  if (!failed) {
-    const int my_tiles = p.blocks_per_rank * p.n_tiles_n;
-    const char* inbox = static_cast<const char*>(p.buffers[p.rank]) + p.inbox_offset;
-    for (int t = blockIdx.x; t < my_tiles; t += gridDim.x) {
-      const int mb = t / p.n_tiles_n, ni = t - mb * p.n_tiles_n;
-      bool ok = true;
-      if (threadIdx.x == 0 && !wait_ge_acquire_sys(&my_counters[t], target, p.timeout_ns)) {
-        report_status(p.status, kTimeoutFlag, p.rank, blockIdx.x, t, kWhereRsArrive, target);
-        ok = false;
-      }
-      if (!__syncthreads_and(ok)) break;
-      switch (p.world_size) {
-        case 2: reduce_tile<2, kAllReduce>(p, inbox, mb, ni); break;
-        case 4: reduce_tile<4, kAllReduce>(p, inbox, mb, ni); break;
-        case 8: reduce_tile<8, kAllReduce>(p, inbox, mb, ni); break;
-        default: reduce_tile<0, kAllReduce>(p, inbox, mb, ni); break;
-      }
-    }
-  }
 
   if constexpr (kAllReduce) {
     // CTA i of every rank has finished broadcasting its rows: when all CTAs of this rank have passed

@@ -152,7 +152,7 @@ def build_checks(world: int, rank: int, dev: torch.device) -> list:
                 symm_mem.rendezvous(a_shard)
             if mode == "push":
                 a_out = symm_mem.empty(M, K, dtype=dtype, device=dev)
-            elif mode in ("pull", "push_copy"):
+            elif mode == "plain":
                 a_out = torch.zeros(M, K, dtype=dtype, device=dev)
             else:
                 a_out = None
@@ -172,9 +172,7 @@ def build_checks(world: int, rank: int, dev: torch.device) -> list:
     add("all_gather_matmul", "push (symmetric a_out)", agmm("push"))
     add("all_gather_matmul", "internal buffer", agmm("internal"))
     if multi:
-        add("all_gather_matmul", "pull (ordinary a_out)", agmm("pull"))
-        add("all_gather_matmul", "ordinary a_out by push and copy", agmm(
-            "push_copy", cfg=AgMatmulConfig(timeout_ms=5000, plain_a_out="push_copy")), True)
+        add("all_gather_matmul", "ordinary a_out (gather into the internal buffer, one copy)", agmm("plain"))
     add("all_gather_matmul", "float8_e4m3fn", agmm("push", dtype=torch.float8_e4m3fn), True)
     add("all_gather_matmul", "SwiGLU epilogue", agmm("push", epilogue="swiglu"), True)
 

@@ -55,7 +55,7 @@ def test_epilogue_and_tile_choices():
     with pytest.raises(SymmMemError):
         _epilogue_code("swiglu", torch.float8_e4m3fn, 7168, cfg)
     with pytest.raises(SymmMemError):
-        _epilogue_code("swiglu", torch.bfloat16, 7168, AgMatmulConfig(cta_pair=False))
+        _epilogue_code("swiglu", torch.bfloat16, 7168, AgMatmulConfig(block_n=128))
     assert choose_block_n(4096, 100, 148) == 128 and choose_block_n(4096, 200, 148) == 224
     assert choose_block_n(4096, 3584, 148) == 256
 

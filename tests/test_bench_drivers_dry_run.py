@@ -114,7 +114,7 @@ def _agmm_worker(rank, world_size, out_path):
     from symm_mem_recipes_b200.bench import all_gather_matmul
 
     _run(all_gather_matmul.main, ["--M", "512", "--N", "256", "--K", "128", "--warmup", "1", "--iters", "1",
-                                  "--copy-ctas", "4", "--with-push-copy", "--per-rank", "--leads", "1,2"],
+                                  "--with-plain-a-out", "--per-rank", "--leads", "1,2"],
          rank, out_path)
 
 
@@ -184,8 +184,7 @@ def test_all_gather_matmul_driver(tmp_path):
     impls = [(r["impl"], r.get("gather")) for r in recs]
     assert impls == [("cublas_mm_only", None), ("smr_mm_only", None), ("cublas_plus_nccl", None),
                      ("nccl_all_gather_only", None), ("smr_fused", "push"), ("smr_fused", "push"),
-                     ("smr_fused", "push"), ("smr_fused", "pull"),
-                     ("smr_fused", "push_copy")]
+                     ("smr_fused", "push"), ("smr_fused", "push_copy")]
 
 
 def test_gemv_driver(tmp_path):

@@ -143,7 +143,7 @@ def test_build_targets_sm_100a_only_and_covers_every_source():
     assert flags.count("-gencode") == 1                      # one architecture, no fallback targets
     cu, cpp = _build.sources()
     names = {p.name for p in cu}
-    for must in ("all_reduce.cu", "ag_matmul_2cta_sm100.cu", "ag_matmul_sm100.cu", "gemv_allreduce_tc.cu",
+    for must in ("all_reduce.cu", "ag_matmul_2cta_sm100.cu", "gemv_allreduce_tc.cu",
                  "matmul_rs_sm100.cu", "layer_glue.cu"):
         assert must in names, must
     ninja = _build.write_ninja().read_text()

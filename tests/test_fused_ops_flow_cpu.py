@@ -24,9 +24,9 @@ def _install_host_kernels():
             return getattr(real, name)
 
         @staticmethod
-        def ag_matmul(a, b, c, mode, shard_alloc, shard_offset, aout_alloc, aout_offset, a_out, flags, block_n,
-                      num_sms, n_copy, timeout_ns, cta_pair=False, tail_scratch=None, epilogue=0, trace=None, lead=-1, push_ahead=0,
-                  push_spread=0, push_plain_stores=False, push_pieces=0):
+        def ag_matmul(a, b, c, mode, aout_alloc, aout_offset, a_out, block_n, num_sms, timeout_ns, tail_scratch=None,
+                      epilogue=0, trace=None, lead=-1, push_ahead=0, push_spread=0, push_plain_stores=False,
+                      push_pieces=0):
             calls.append(mode)
             if mode == 2:
                 ws, rank = dist.get_world_size(), dist.get_rank()
@@ -64,7 +64,7 @@ def _agmm_flow_worker(rank, world_size):
 
     import symm_mem_recipes_b200 as smr
     from symm_mem_recipes_b200.errors import SymmMemError
-    from symm_mem_recipes_b200.ops.ag_matmul import AgMatmulConfig, interleave_gate_up
+    from symm_mem_recipes_b200.ops.ag_matmul import interleave_gate_up
     from symm_mem_recipes_b200.parallel import symm_mem
 
     calls = _install_host_kernels()
@@ -94,9 +94,9 @@ def _agmm_flow_worker(rank, world_size):
         smr.all_gather_matmul(a_shard, wg, big[: M * K].view(M, K))
     dist.barrier()
 
-    # 3. an ordinary a_out served by push into the internal buffer plus one copy
+    # 3. an ordinary a_out: gathered into the internal buffer, then one copy
     plain = torch.zeros(M, K, dtype=torch.bfloat16)
-    c3 = smr.all_gather_matmul(a_shard, wg, plain, config=AgMatmulConfig(plain_a_out="push_copy"))
+    c3 = smr.all_gather_matmul(a_shard, wg, plain)
     assert calls[-1] == 2 and torch.equal(plain, full_a) and torch.equal(c3, c)
 
     # 4. SwiGLU epilogue over the gather
@@ -191,9 +191,11 @@ def _row_parallel_flow_worker(rank, world_size):
     x = (torch.randn(4, K, generator=g) * 0.3).to(torch.bfloat16)
     w = (torch.randn(K, N, generator=g) * 0.3).to(torch.bfloat16)
     y = smr.gemv_all_reduce(x, w)
-    assert seen["gemv"] == (True, False) and y.shape == (4, N)
-    smr.gemv_all_reduce(x, w, algo="tc_tagged")
-    assert seen["gemv"] == (True, True)
+    assert seen["gemv"] == (True, True) and y.shape == (4, N)                 # up to batch 8: the tagged exchange
+    smr.gemv_all_reduce(torch.cat([x] * 4), w)
+    assert seen["gemv"] == (True, False)                                       # batch 16: inboxes and flags
+    smr.gemv_all_reduce(x, w, algo="tc")
+    assert seen["gemv"] == (True, False)
     smr.gemv_all_reduce(x, w, algo="simt")
     assert seen["gemv"] == (False, False)
     y_nk = smr.gemv_all_reduce(x, w.t().contiguous(), weights_nk=True)       # [N, K] weights: same product
@@ -321,26 +323,6 @@ def _install_all_stand_ins():
     _install_row_parallel_and_glue_stand_ins()
     ag_mod = importlib.import_module("symm_mem_recipes_b200.ops.ag_matmul")
     gemv_mod = importlib.import_module("symm_mem_recipes_b200.ops.gemv_all_reduce")
-    push_fake = ag_mod.C
-
-    class AgFake:                                     # adds the pull mode to the push / plain stand-in
-        def __getattr__(self, name):
-            return getattr(push_fake, name)
-
-        @staticmethod
-        def ag_matmul(a, b, c, mode, shard_alloc, shard_offset, *rest, **kw):
-            if mode != 1:
-                return push_fake.ag_matmul(a, b, c, mode, shard_alloc, shard_offset, *rest, **kw)
-            a_out = rest[2]
-            rows, K = a.shape
-            dist.barrier()
-            for r in range(dist.get_world_size()):
-                a_out[r * rows:(r + 1) * rows].copy_(real.host_view(shard_alloc, r, [rows, K], a.dtype, shard_offset))
-            dist.barrier()
-            c.copy_((a_out.float() @ b.float().t()).to(c.dtype))
-
-    ag_mod.C = AgFake()
-
     class GemvFake:
         def __getattr__(self, name):
             return getattr(real, name)
@@ -379,7 +361,7 @@ def _selfcheck_worker(rank, world_size):
     results, recoveries, stopped = selfcheck.run_checks(checks, rank, torch.device("cpu"))
     failures = [f"{r['group']}: {r['check']}: {r['detail']}" for r in results if not r["ok"]]
     assert not failures, failures
-    assert len(results) >= 30 and recoveries == 0 and not stopped, (len(results), recoveries)
+    assert len(results) >= 25 and recoveries == 0 and not stopped, (len(results), recoveries)
     dist.barrier()
 
 

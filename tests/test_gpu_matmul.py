@@ -17,10 +17,9 @@ def _close(c, ref, K):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("cta_pair", [False, True])
 @pytest.mark.parametrize("block_n", [128, 192, 224, 256])
 @pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 256), (200, 328, 96), (640, 1000, 1024)])
-def test_matmul_small(block_n, shape, cta_pair):
+def test_matmul_small(block_n, shape):
     from symm_mem_recipes_b200.ops.ag_matmul import AgMatmulConfig, matmul
     from symm_mem_recipes_b200.parallel import symm_mem
 
@@ -30,7 +29,7 @@ def test_matmul_small(block_n, shape, cta_pair):
     b = (torch.randn(N, K, device="cuda") * 0.5).to(torch.bfloat16)
     c, intact = guarded_empty((M, N), torch.bfloat16, "cuda")    # canaries before and after the output
     c.fill_(float("nan"))
-    matmul(a, b, c, AgMatmulConfig(block_n=block_n, timeout_ms=2000, cta_pair=cta_pair))
+    matmul(a, b, c, AgMatmulConfig(block_n=block_n, timeout_ms=2000))
     symm_mem.check_status("cuda")
     ok, err = _close(c, _ref(a, b), K)
     assert ok, f"max abs error {err}"
@@ -65,8 +64,7 @@ def test_matmul_split_k_tail(shape, num_sms):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("cta_pair", [False, True])
-def test_matmul_llama70b_shape_vs_cublas(cta_pair):
+def test_matmul_llama70b_shape_vs_cublas():
     from symm_mem_recipes_b200.ops.ag_matmul import AgMatmulConfig, matmul
     from symm_mem_recipes_b200.parallel import symm_mem
 
@@ -74,13 +72,13 @@ def test_matmul_llama70b_shape_vs_cublas(cta_pair):
     torch.manual_seed(0)
     a = (torch.randn(M, K, device="cuda") * 0.02).to(torch.bfloat16)
     b = (torch.randn(N, K, device="cuda") * 0.02).to(torch.bfloat16)
-    c = matmul(a, b, config=AgMatmulConfig(cta_pair=cta_pair, timeout_ms=2000))
+    c = matmul(a, b, config=AgMatmulConfig(timeout_ms=2000))
     symm_mem.check_status("cuda")
     ref = torch.matmul(a, b.t())
     assert torch.allclose(c.float(), ref.float(), rtol=2e-2, atol=2e-3)
 
 
-def _agmm_worker(rank, world_size, rows, N, K, n_copy, mode, cta_pair=False):
+def _agmm_worker(rank, world_size, rows, N, K, mode):
     import symm_mem_recipes_b200 as smr
     from symm_mem_recipes_b200.ops.ag_matmul import AgMatmulConfig
     from symm_mem_recipes_b200.parallel import symm_mem
@@ -92,17 +90,16 @@ def _agmm_worker(rank, world_size, rows, N, K, n_copy, mode, cta_pair=False):
     torch.manual_seed(7)
     b = (torch.randn(N, K, device=dev) * 0.02).to(torch.bfloat16)
     M = rows * world_size
-    if mode == "push":          # gathered A lands in symmetric memory: shards are broadcast
+    if mode in ("push", "push_multicast", "push_plain"):   # gathered A lands in symmetric memory
         a_out = symm_mem.empty(M, K, dtype=torch.bfloat16, device=dev)
-    elif mode in ("pull", "push_copy"):   # ordinary a_out, as in the upstream API
+    elif mode == "plain":       # ordinary a_out, as in the upstream API: internal buffer plus one copy
         a_out = torch.zeros(M, K, dtype=torch.bfloat16, device=dev)
     else:                       # internal symmetric buffer
         from symm_mem_recipes_b200.ops.ag_matmul import gather_buffer
         a_out = None
     c_out = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
-    cfg = AgMatmulConfig(n_copy=n_copy, timeout_ms=5000, cta_pair=cta_pair)
-    if mode == "push_copy":     # ordinary a_out served by the push kernel plus one local copy
-        cfg = AgMatmulConfig(timeout_ms=5000, plain_a_out="push_copy")
+    # the broadcast through the switch (multimem.st) and the plain peer stores, whatever the world size picks
+    cfg = AgMatmulConfig(timeout_ms=5000, push_plain_stores={"push_multicast": 0, "push_plain": 1}.get(mode, -1))
     failures = []
     for it in range(3):
         smr.all_gather_matmul(a_shard, b, a_out, c_out, cfg)
@@ -134,34 +131,20 @@ def _agmm_worker(rank, world_size, rows, N, K, n_copy, mode, cta_pair=False):
 
 @pytest.mark.gpu
 @pytest.mark.multigpu(2)
-@pytest.mark.parametrize("mode", ["push", "pull", "internal"])
-@pytest.mark.parametrize("rows,N,K,n_copy", [(128, 256, 256, 1), (256, 512, 1024, 3), (2048, 3584, 8192, 4)])
-def test_all_gather_matmul_2gpu(rows, N, K, n_copy, mode):
-    spawn_ranks(_agmm_worker, 2, "nccl", (rows, N, K, n_copy, mode))
-
-
-@pytest.mark.gpu
-@pytest.mark.multigpu(2)
+@pytest.mark.parametrize("mode", ["push_multicast", "push_plain", "internal", "plain"])
 @pytest.mark.parametrize("rows,N,K", [(128, 256, 256), (384, 512, 1024), (2048, 3584, 8192)])
-def test_all_gather_matmul_cta_pair_2gpu(rows, N, K):
-    spawn_ranks(_agmm_worker, 2, "nccl", (rows, N, K, 0, "push", True))
+def test_all_gather_matmul_2gpu(rows, N, K, mode):
+    spawn_ranks(_agmm_worker, 2, "nccl", (rows, N, K, mode))
 
 
 @pytest.mark.gpu
 @pytest.mark.multigpu(2)
 def test_all_gather_matmul_push_without_multicast(monkeypatch):
     monkeypatch.setenv("SMR_DISABLE_MULTICAST", "1")     # plain peer stores instead of multimem.st
-    spawn_ranks(_agmm_worker, 2, "nccl", (256, 512, 1024, 2, "push"))
+    spawn_ranks(_agmm_worker, 2, "nccl", (256, 512, 1024, "push"))
 
 
 @pytest.mark.gpu
 @pytest.mark.multigpu(8)
 def test_all_gather_matmul_8gpu():
-    spawn_ranks(_agmm_worker, 8, "nccl", (2048, 3584, 8192, 4, "push"))
-
-
-@pytest.mark.gpu
-@pytest.mark.multigpu(2)
-@pytest.mark.parametrize("rows,N,K", [(256, 512, 1024), (2048, 3584, 8192)])
-def test_all_gather_matmul_plain_a_out_by_push_and_copy_2gpu(rows, N, K):
-    spawn_ranks(_agmm_worker, 2, "nccl", (rows, N, K, 0, "push_copy"))
+    spawn_ranks(_agmm_worker, 8, "nccl", (2048, 3584, 8192, "push"))

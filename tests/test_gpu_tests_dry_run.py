@@ -111,11 +111,10 @@ WORKERS = [
     ("test_gpu_llama_layer", "_stack_worker", (1, 2), ()),
     ("test_gpu_symm_mem", "_signals_gpu_worker", (2,), ()),
     ("test_gpu_symm_mem", "_compat_gpu_worker", (2,), ()),
-    ("test_gpu_matmul", "_agmm_worker", (2,), (128, 256, 256, 1, "push_copy")),
-    ("test_gpu_matmul", "_agmm_worker", (2,), (128, 256, 256, 2, "pull")),
-    ("test_gpu_matmul", "_agmm_worker", (2,), (128, 256, 256, 0, "internal", True)),
+    ("test_gpu_matmul", "_agmm_worker", (2,), (128, 256, 256, "plain")),
+    ("test_gpu_matmul", "_agmm_worker", (2,), (128, 256, 256, "internal")),
     # the default forms of the multi-GPU tests
-    ("test_gpu_matmul", "_agmm_worker", (2,), (128, 256, 256, 1, "push")),
+    ("test_gpu_matmul", "_agmm_worker", (2,), (128, 256, 256, "push_plain")),
     ("test_gpu_gemv", "_gemv_worker", (2,), (4, 256, 512, "tc")),
     ("test_gpu_matmul_rs", "_rs_worker", (2,), (256, 256, 128)),
 ]
@@ -136,7 +135,7 @@ FUNCTIONS = [
     ("test_gpu_layer_glue", "test_silu_mul", {"rows": 19, "F": 48}),
     ("test_gpu_layer_glue", "test_decode_attention", {"B": 3, "hq": 4, "hkv": 2, "D": 64, "s_max": 40,
                                                       "positions": (0, 7, 39)}),
-    ("test_gpu_matmul", "test_matmul_small", {"block_n": 224, "shape": (200, 328, 96), "cta_pair": True}),
+    ("test_gpu_matmul", "test_matmul_small", {"block_n": 224, "shape": (200, 328, 96)}),
     ("test_gpu_layer_glue", "test_layer_with_fused_glue_matches_fp32", {}),
     ("test_gpu_layer_glue", "test_layer_with_fused_swiglu_matches_fp32", {}),
     ("test_gpu_layer_glue", "test_matmul_with_swiglu_epilogue", {"M": 200, "F": 384, "K": 96}),
