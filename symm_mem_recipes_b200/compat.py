@@ -58,8 +58,11 @@ def all_gather_with_progress(output: torch.Tensor, inp: torch.Tensor, progress: 
                              splits_per_rank: int) -> None:
     """Host-driven all-gather of the symmetric tensor `inp` into `output` with one flag per
     chunk: chunks are copied from the peers nearest neighbour first and own shard last, and
-    `progress[chunk]` becomes 1, in stream order, once its copy is complete; a barrier at the
-    end keeps any rank from overwriting `inp` while a peer still reads it.  Same contract as
+    `progress[chunk]` becomes 1, in stream order (the driver's stream memory operation on a
+    32-bit CUDA tensor, a one-element fill otherwise), once its copy is complete; a barrier at
+    the end keeps any rank from overwriting `inp` while a peer still reads it.  Everything is
+    queued on the CURRENT stream: a caller that wants the gather beside a kernel enters
+    `torch.cuda.stream(side)` around the call, as upstream does.  Same contract as
     upstream (triton_all_gather_matmul.py:20-56), where a kernel on another stream polls the
     flags.  The fused kernel of this package does not use it (its gather runs inside the
     GEMM); it is here for code that consumes the flags itself."""
@@ -82,5 +85,5 @@ def all_gather_with_progress(output: torch.Tensor, inp: torch.Tensor, progress: 
         for split in range(splits_per_rank):
             idx = src * splits_per_rank + split
             chunks[idx].copy_(hdl.get_buffer(src, chunks[0].shape, inp.dtype, base + chunk_numel * split))
-            flags[idx : idx + 1].fill_(1)        # ordered after the copy on the current stream
+            hdl.stream_write_value32(flags, idx, 1)   # ordered after the copy on the current stream
     hdl.barrier()

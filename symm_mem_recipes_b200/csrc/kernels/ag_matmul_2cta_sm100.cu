@@ -41,6 +41,7 @@
 // kernel through the internal symmetric buffer plus one local copy.
 #include "../device/tcgen05_pair.cuh"
 #include "ag_matmul_common.cuh"
+#include "residency.h"
 
 namespace smr {
 
@@ -540,6 +541,8 @@ int launch_pair_variant(const CUtensorMap& ta_shard, const CUtensorMap& ta_out, 
   auto kern = ag_matmul_2cta_kernel<BN, STAGES, kFp8, kSwiGlu>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::kTotal);
   if (e != cudaSuccess) return (int)e;
+  // The pairs wait for one another (pieces of the gather, parts of the split-K tail): all of them must be resident.
+  if (int rc = check_co_resident(kern, grid, kGemmThreads, L::kTotal, 2)) return rc;
   kern<<<grid, kGemmThreads, L::kTotal, stream>>>(ta_shard, ta_out, tb, tc, p);
   return (int)cudaGetLastError();
 }

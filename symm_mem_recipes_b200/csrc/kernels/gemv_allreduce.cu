@@ -18,6 +18,7 @@
 #include "../device/barrier.cuh"
 #include "../device/vec.cuh"
 #include "launch.h"
+#include "residency.h"
 
 namespace smr {
 
@@ -200,6 +201,10 @@ int launch_variant(const GemvParams& p, int tiles, cudaStream_t stream) {
   if (smem > 227 * 1024) return cudaErrorInvalidValue;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
+  // A tile waits for the same tile of every peer: with peers, all tiles must be resident at once.
+  if (p.world_size > 1) {
+    if (int rc = check_co_resident(kern, tiles, THREADS, smem)) return rc;
+  }
   kern<<<tiles, THREADS, smem, stream>>>(p);
   return (int)cudaGetLastError();
 }

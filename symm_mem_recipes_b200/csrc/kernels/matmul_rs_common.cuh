@@ -93,107 +93,132 @@ __host__ __device__ __forceinline__ void row_block_coords(const RsParams& p, int
   if (dest >= p.world_size) dest -= p.world_size;
 }
 
-// Epilogue of a tile of the rank's own rows, one thread per row `r` of the CTA's 128-row block:
-// the row's accumulator (TMEM) and the peers' bf16 partials of the same row (strip-major inbox,
-// 16-byte chunks XOR-swizzled by row) are added in rank order in fp32, the own value rounded to
-// bf16 first as if it had crossed the wire, and the bf16 result is written row-major.  CH x 8
-// columns at a time (32 up to four ranks, 16 at eight: the loaded vectors live in registers):
-// (WS - 1) x CH independent 16-byte loads in flight per thread.  WS = 0: generic loop.
+// Epilogue of a tile of the rank's own rows.  Each 64-column strip of the accumulator is staged in
+// shared memory as bf16 exactly as if it were to be shipped (so the own partial is rounded like the
+// peers' partials that crossed the wire); then the 128 epilogue threads walk the strip in the order it
+// has in memory, 16 bytes per thread and 512 contiguous bytes per warp instruction: the strips of the
+// peers in the inbox have the same layout, so their loads are fully coalesced, and a warp's stores
+// fill four whole 128-byte rows of the output.  The sum is fp32, in rank order from +0, rounded once.
+// The peers' vectors of the next batch (JB vectors per peer) are loaded before the current batch is
+// added, also across the TMEM read and staging of the next strip: 2 x (WS - 1) x JB 16-byte loads in
+// flight per thread.  WS = 0: generic loop for other world sizes.
 // kAllReduce: instead of the local [M/WS, N] output, the row goes to rows [rank * M/WS + ...] of
 // the symmetric [M, N] output of EVERY rank (one multimem.st per 16 bytes, or WS stores).
-__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
-}
-
 template <int WS, bool kAllReduce = false>
-__device__ __forceinline__ void reduce_own_tile(const RsParams& p, uint32_t taddr, int mb, int ni, int r) {
-  constexpr int CH = (WS == 0 || WS > 4) ? 2 : 4;           // 16-byte chunks (8 columns each) per step
-  constexpr int COLS = CH * 8;
+__device__ __forceinline__ void reduce_own_tile(const RsParams& p, uint32_t taddr, int mb, int ni, int r, int etid,
+                                                uint8_t* strip, int n_strip_bufs, uint32_t& strip_ctr) {
+  constexpr int NP = WS > 0 ? WS - 1 : 1;                   // peers
+  constexpr int JB = WS == 0 ? 4 : (WS <= 2 ? 8 : (WS <= 4 ? 4 : 2));   // 16-byte vectors per thread and batch
+  constexpr int NB = 8 / JB;                                // batches per strip (a strip is 8 vectors per thread)
+  constexpr size_t kVecStep = 128 * 16;                     // distance between a thread's vectors j and j + 1
   const int n0 = ni * kBN;
-  const char* inbox = static_cast<const char*>(p.buffers[p.rank]) + p.inbox_offset;
   const size_t src_stride = (size_t)p.blocks_per_rank * p.n_tiles_n * kStripsPerTile * kStripBytesOne;
-  const int ws = WS == 0 ? p.world_size : WS;
-  const size_t out_row = (size_t)(mb * kBM + r);
-#pragma unroll 1
-  for (int h = 0; h < kBN / COLS; ++h) {
-    const int col0 = n0 + h * COLS;
-    if (col0 >= p.N) break;                                 // uniform over the CTA
-    const int sidx = (h * COLS) / kStripCols, c0 = ((h * COLS) % kStripCols) / 8;   // strip, first logical chunk in it
-    uint32_t own[COLS];
-    if constexpr (CH == 4) tmem_ld_32x32b_x32(taddr + (uint32_t)(h * COLS), own);
-    else tmem_ld_32x32b_x16(taddr + (uint32_t)(h * COLS), own);
-    const char* row_base = inbox + strip_offset(0, mb, ni, sidx, p.blocks_per_rank, p.n_tiles_n) + (size_t)r * 128;
-    float s[COLS];
-#pragma unroll
-    for (int q = 0; q < COLS; ++q) s[q] = 0.f;
-    auto add_vec = [&](int c, const Vec16& w) {
-      s[c * 8 + 0] += bf16lo_to_f32(w.x); s[c * 8 + 1] += bf16hi_to_f32(w.x);
-      s[c * 8 + 2] += bf16lo_to_f32(w.y); s[c * 8 + 3] += bf16hi_to_f32(w.y);
-      s[c * 8 + 4] += bf16lo_to_f32(w.z); s[c * 8 + 5] += bf16hi_to_f32(w.z);
-      s[c * 8 + 6] += bf16lo_to_f32(w.w); s[c * 8 + 7] += bf16hi_to_f32(w.w);
-    };
-    auto own_vec = [&](int c) {
-      Vec16 w;
-      w.x = pack_bf16x2(__uint_as_float(own[c * 8 + 0]), __uint_as_float(own[c * 8 + 1]));
-      w.y = pack_bf16x2(__uint_as_float(own[c * 8 + 2]), __uint_as_float(own[c * 8 + 3]));
-      w.z = pack_bf16x2(__uint_as_float(own[c * 8 + 4]), __uint_as_float(own[c * 8 + 5]));
-      w.w = pack_bf16x2(__uint_as_float(own[c * 8 + 6]), __uint_as_float(own[c * 8 + 7]));
-      return w;
-    };
-    if constexpr (WS == 0) {
-      tmem_ld_wait();
-      for (int src = 0; src < ws; ++src) {
-#pragma unroll
-        for (int c = 0; c < CH; ++c) {
-          const Vec16 w = src == p.rank ? own_vec(c)
-                                        : ld_16_stream(row_base + (size_t)src * src_stride + (((c0 + c) ^ (r & 7)) << 4));
-          add_vec(c, w);
+  const char* tile_base = static_cast<const char*>(p.buffers[p.rank]) + p.inbox_offset +
+                          strip_offset(0, mb, ni, 0, p.blocks_per_rank, p.n_tiles_n) + (size_t)etid * 16;
+  auto add_vec = [](float (&s)[8], const Vec16& w) {
+    s[0] += bf16lo_to_f32(w.x); s[1] += bf16hi_to_f32(w.x);
+    s[2] += bf16lo_to_f32(w.y); s[3] += bf16hi_to_f32(w.y);
+    s[4] += bf16lo_to_f32(w.z); s[5] += bf16hi_to_f32(w.z);
+    s[6] += bf16lo_to_f32(w.w); s[7] += bf16hi_to_f32(w.w);
+  };
+  auto write_out = [&](int idx, int col0, const float (&s)[8]) {
+    const int row = idx >> 3;
+    const int col = col0 + (((idx & 7) ^ (row & 7)) << 3);  // undo the strip's swizzle
+    if (col >= p.N) return;                                 // N % 8 == 0
+    Vec16 o;
+    o.x = pack_bf16x2(s[0], s[1]); o.y = pack_bf16x2(s[2], s[3]);
+    o.z = pack_bf16x2(s[4], s[5]); o.w = pack_bf16x2(s[6], s[7]);
+    const size_t out_row = (size_t)(mb * kBM + row);
+    if constexpr (kAllReduce) {
+      const size_t off = p.ar_offset +
+                         (((size_t)p.rank * p.blocks_per_rank * kBM + out_row) * p.N + col) * sizeof(__nv_bfloat16);
+      if (p.ar_mc != nullptr) {
+        multimem_st_16(static_cast<char*>(p.ar_mc) + off, o);
+      } else {
+        for (int s2 = 1; s2 <= p.world_size; ++s2) {        // own copy last
+          int peer = p.rank + s2;
+          if (peer >= p.world_size) peer -= p.world_size;
+          st_16(static_cast<char*>(p.ar_peers[peer]) + off, o);
         }
       }
     } else {
-      Vec16 v[WS][CH];
-#pragma unroll
-      for (int src = 0; src < WS; ++src) {
-        if (src != p.rank) {
-#pragma unroll
-          for (int c = 0; c < CH; ++c)
-            v[src][c] = ld_16_stream(row_base + (size_t)src * src_stride + (((c0 + c) ^ (r & 7)) << 4));
-        }
-      }
-      tmem_ld_wait();
-#pragma unroll
-      for (int src = 0; src < WS; ++src) {
-#pragma unroll
-        for (int c = 0; c < CH; ++c) add_vec(c, src == p.rank ? own_vec(c) : v[src][c]);
-      }
+      st_16(p.out + out_row * p.N + col, o);
     }
+  };
+  auto load_batch = [&](Vec16 (&v)[NP][JB], int sidx, int b) {
 #pragma unroll
-    for (int c = 0; c < CH; ++c) {
-      const int col = col0 + c * 8;
-      if (col >= p.N) break;                                // N % 8 == 0
-      Vec16 o;
-      o.x = pack_bf16x2(s[c * 8 + 0], s[c * 8 + 1]); o.y = pack_bf16x2(s[c * 8 + 2], s[c * 8 + 3]);
-      o.z = pack_bf16x2(s[c * 8 + 4], s[c * 8 + 5]); o.w = pack_bf16x2(s[c * 8 + 6], s[c * 8 + 7]);
-      if constexpr (kAllReduce) {
-        const size_t off = p.ar_offset +
-                           (((size_t)p.rank * p.blocks_per_rank * kBM + out_row) * p.N + col) * sizeof(__nv_bfloat16);
-        if (p.ar_mc != nullptr) {
-          multimem_st_16(static_cast<char*>(p.ar_mc) + off, o);
-        } else {
-          for (int s2 = 1; s2 <= p.world_size; ++s2) {      // own copy last
-            int peer = p.rank + s2;
-            if (peer >= p.world_size) peer -= p.world_size;
-            st_16(static_cast<char*>(p.ar_peers[peer]) + off, o);
+    for (int q = 0; q < NP; ++q) {
+      const int src = q < p.rank ? q : q + 1;
+      const char* base = tile_base + (size_t)src * src_stride + (size_t)sidx * kStripBytesOne + (size_t)(b * JB) * kVecStep;
+#pragma unroll
+      for (int j = 0; j < JB; ++j) v[q][j] = ld_16_stream(base + (size_t)j * kVecStep);
+    }
+  };
+
+  Vec16 nxt[NP][JB];
+  if constexpr (WS > 0) load_batch(nxt, 0, 0);
+#pragma unroll 1
+  for (int sidx = 0; sidx < kStripsPerTile; ++sidx) {
+    const int col0 = n0 + sidx * kStripCols;
+    if (col0 >= p.N) break;                                 // uniform over the CTA
+    uint8_t* buf = strip + (size_t)(strip_ctr % (uint32_t)n_strip_bufs) * kStripBytesOne;
+    {
+      uint32_t v0[32], v1[32];
+      tmem_ld_32x32b_x32(taddr + (uint32_t)(sidx * kStripCols), v0);
+      tmem_ld_32x32b_x32(taddr + (uint32_t)(sidx * kStripCols + 32), v1);
+      tmem_ld_wait();
+      epilogue_sync();                                      // nobody reads the buffer we are about to fill any more
+      strip_row_to_smem(buf, r, v0, v1);
+    }
+    epilogue_sync();                                        // the own strip is complete in shared memory
+    ++strip_ctr;
+    const bool more = sidx + 1 < kStripsPerTile && col0 + kStripCols < p.N;
+    if constexpr (WS == 0) {
+#pragma unroll 1
+      for (int b = 0; b < NB; ++b) {
+        float s[JB][8];
+#pragma unroll
+        for (int j = 0; j < JB; ++j)
+#pragma unroll
+          for (int e = 0; e < 8; ++e) s[j][e] = 0.f;
+        for (int src = 0; src < p.world_size; ++src) {
+#pragma unroll
+          for (int j = 0; j < JB; ++j) {
+            const size_t voff = (size_t)(b * JB + j) * kVecStep;
+            const Vec16 w = src == p.rank
+                                ? *reinterpret_cast<const Vec16*>(buf + (size_t)etid * 16 + voff)
+                                : ld_16_stream(tile_base + (size_t)src * src_stride + (size_t)sidx * kStripBytesOne + voff);
+            add_vec(s[j], w);
           }
         }
-      } else {
-        st_16(p.out + out_row * p.N + col, o);
+#pragma unroll
+        for (int j = 0; j < JB; ++j) write_out(etid + (b * JB + j) * 128, col0, s[j]);
+      }
+    } else {
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
+        Vec16 cur[NP][JB];
+#pragma unroll
+        for (int q = 0; q < NP; ++q)
+#pragma unroll
+          for (int j = 0; j < JB; ++j) cur[q][j] = nxt[q][j];
+        if (b + 1 < NB) load_batch(nxt, sidx, b + 1);
+        else if (more) load_batch(nxt, sidx + 1, 0);
+#pragma unroll
+        for (int j = 0; j < JB; ++j) {
+          const int idx = etid + (b * JB + j) * 128;
+          const Vec16 own = *reinterpret_cast<const Vec16*>(buf + (size_t)idx * 16);
+          float s[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) s[e] = 0.f;
+#pragma unroll
+          for (int q = 0; q < NP; ++q) {
+            if (q == p.rank) add_vec(s, own);
+            add_vec(s, cur[q][j]);
+          }
+          if (p.rank == NP) add_vec(s, own);
+          write_out(idx, col0, s);
+        }
       }
     }
   }

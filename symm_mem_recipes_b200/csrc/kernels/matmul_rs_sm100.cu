@@ -225,10 +225,10 @@ matmul_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         epilogue_sync();
         if (!own_ok) { failed = true; break; }
         switch (p.world_size) {
-          case 2: reduce_own_tile<2, kAllReduce>(p, taddr, mb, ni, r); break;
-          case 4: reduce_own_tile<4, kAllReduce>(p, taddr, mb, ni, r); break;
-          case 8: reduce_own_tile<8, kAllReduce>(p, taddr, mb, ni, r); break;
-          default: reduce_own_tile<0, kAllReduce>(p, taddr, mb, ni, r); break;
+          case 2: reduce_own_tile<2, kAllReduce>(p, taddr, mb, ni, r, etid, strip, kNStrips, strip_ctr); break;
+          case 4: reduce_own_tile<4, kAllReduce>(p, taddr, mb, ni, r, etid, strip, kNStrips, strip_ctr); break;
+          case 8: reduce_own_tile<8, kAllReduce>(p, taddr, mb, ni, r, etid, strip, kNStrips, strip_ctr); break;
+          default: reduce_own_tile<0, kAllReduce>(p, taddr, mb, ni, r, etid, strip, kNStrips, strip_ctr); break;
         }
       } else if (valid) {
 #pragma unroll 1
