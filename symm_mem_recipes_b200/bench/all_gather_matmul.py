@@ -54,6 +54,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--pacings", default="", help="push mode: comma-separated AHEAD:SPREAD[:LEAD[:PLAIN[:PIECES]]] settings, each timed "
                                                   "(rounds of lookahead of the broadcast; rounds over which the whole "
                                                   "shard is sent at the latest, 0 = half of the kernel; own blocks first)")
+    ap.add_argument("--panels", default="", help="comma-separated column-panel widths of the tile order (N tiles per "
+                                                 "panel), each timed for the GEMM alone and for the fused op")
     ap.add_argument("--trace", action="store_true",
                     help="print the per-CTA timing record of one fused call and one GEMM-only call, per rank")
     ap.add_argument("--per-rank", action="store_true", help="also print every rank's own median beside the maximum")
@@ -160,6 +162,28 @@ def _one_shape(args, M, N, K, rank, world, dev, lines) -> None:
         us, extra = timed(lambda: smr.all_gather_matmul(a_shard, b, a_out, c, cfgl))
         emit("smr_fused", us, gather="push", lead=lead, **extra)
         symm_mem.check_status(dev)
+    widths = [int(x) for x in args.panels.split(",") if x]
+    if widths:
+        # the GPU's clock drifts by several per cent over a run of this length, so the candidates are
+        # timed in turns (three cycles over all of them) and the median of a candidate's cycles is reported
+        import statistics
+
+        short = dict(warmup_iters=2, benchmark_iters=max(3, args.iters // 3), flush_l2=True)
+        runs = {}
+        for cycle in range(3):
+            for pw in widths:
+                cfgw = AgMatmulConfig(block_n=args.block_n, panel_w=pw)
+                for what, fn in (("cublas_mm_only", lambda: torch.matmul(a, bt, out=c)),
+                                 ("smr_mm_only", lambda: smr.matmul(a, b, c, cfgw)),
+                                 ("smr_fused", lambda: smr.all_gather_matmul(a_shard, b, a_out, c, cfgw))):
+                    if what == "cublas_mm_only" and pw != widths[0]:
+                        continue
+                    own = benchmark_with_event(fn, all_ranks_max=True, **short)
+                    runs.setdefault((what, pw), []).append(round(own, 1))
+                symm_mem.check_status(dev)
+        for (what, pw), vals in runs.items():
+            extra = {} if what == "cublas_mm_only" else {"panel_w": pw}
+            emit(what, statistics.median(vals), timing="three interleaved cycles", cycles_us=vals, **extra)
     for spec in [x for x in args.pacings.split(",") if x]:
         parts = [int(v) for v in spec.split(":")]
         cfgp = AgMatmulConfig(block_n=args.block_n, push_ahead=parts[0], push_spread=parts[1] if len(parts) > 1 else 0,

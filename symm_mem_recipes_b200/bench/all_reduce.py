@@ -251,7 +251,7 @@ def main(argv=None, standalone: bool = True) -> int:
             buf.normal_()   # in-place algorithms grow the values; refresh
             extra = {}
             if name == "multimem":
-                extra = {"multimem_blocks": cfg.multimem_max_blocks}
+                extra = {"multimem_blocks": cfg.multimem_blocks(world)}
             emit({"op": "all_reduce", "impl": name, "world_size": world, "bytes": nbytes, "timing": how, **extra,
                   "us": round(us, 2), "alg_gbs": round(nbytes / us / 1e3, 2),
                   "bus_gbs": round(2 * (world - 1) / world * nbytes / us / 1e3, 2)})

@@ -30,6 +30,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--rs-panels", default="", help="matmul_reduce_scatter: comma-separated column-panel widths of the "
+                                                    "tile order (N tiles of 256 columns per panel), each timed")
     ap.add_argument("--skip-layer", action="store_true")
     ap.add_argument("--fused-glue", default="env", choices=["env", "0", "1", "both", "all"],
                     help="norms / RoPE / SiLU-mul as single-pass kernels (1) or PyTorch compositions (0); "
@@ -110,6 +112,22 @@ def main(argv=None, standalone: bool = True) -> int:
                   "fused_tflops": round(flops / us_f / 1e6, 1), "wire_gbs": round(wire / us_f / 1e3, 1),
                   "speedup": round(us_r / us_f, 3), "phases": {k: round(v, 1) for k, v in phases.items()}})
             shared.update(ref=ref, us_r=us_r)
+            widths = [int(v) for v in args.rs_panels.split(",") if v]
+            if widths:
+                # candidates timed in turns (three cycles): the GPU's clock drifts by several per cent over the run
+                import statistics
+
+                short = dict(warmup_iters=2, benchmark_iters=max(3, args.iters // 3), flush_l2=True)
+                runs, okay = {}, {}
+                for cycle in range(3):
+                    for pw in widths:
+                        us_p = benchmark_with_event(lambda: smr.matmul_reduce_scatter(a, b, out, panel_w=pw), **short)
+                        symm_mem.check_status(dev)
+                        runs.setdefault(pw, []).append(round(us_p, 1))
+                        okay[pw] = bool(torch.allclose(out.float(), ref.float(), rtol=5e-2, atol=5e-2))
+                for pw, vals in runs.items():
+                    emit({"op": "matmul_reduce_scatter", "shape": name, "world_size": world, "panel_w": pw,
+                          "smr_fused_us": statistics.median(vals), "cycles_us": vals, "matches_library": okay[pw]})
 
         if not section(f"matmul_reduce_scatter {name}", default_kernel):
             continue

@@ -484,7 +484,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                         c10::optional<torch::Tensor> a_out, int block_n, int num_sms, uint64_t timeout_ns,
                         c10::optional<torch::Tensor> tail_scratch, int epilogue,
                         c10::optional<torch::Tensor> trace, int lead, int push_ahead, int push_spread,
-                        bool push_plain_stores, int push_pieces) {
+                        bool push_plain_stores, int push_pieces, int panel_w) {
     const auto dtype = a.scalar_type();
     const bool fp8 = dtype == at::kFloat8_e4m3fn;
     TORCH_CHECK(fp8 || dtype == torch::kBFloat16, "a must be bfloat16 or float8_e4m3fn");
@@ -549,6 +549,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     args.push_spread = push_spread;
     args.push_plain_stores = push_plain_stores ? 1 : 0;
     args.push_pieces = push_pieces;
+    args.panel_w = panel_w;
     if (trace.has_value()) {
       TORCH_CHECK(trace->is_cuda() && trace->get_device() == dev && trace->is_contiguous() &&
                   trace->scalar_type() == torch::kInt64 && trace->numel() >= (int64_t)num_sms * 12,
@@ -561,7 +562,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
      py::arg("tail_scratch") = py::none(), py::arg("epilogue") = 0,
      py::arg("trace") = py::none(), py::arg("lead") = -1,
      py::arg("push_ahead") = 0, py::arg("push_spread") = 0, py::arg("push_plain_stores") = false,
-     py::arg("push_pieces") = 0);
+     py::arg("push_pieces") = 0, py::arg("panel_w") = 0);
 
   m.def("check_push_schedule", &check_push_schedule);
   m.def("check_pair_work", &check_pair_work);
@@ -619,7 +620,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("matmul_rs_workspace_bytes", &matmul_rs_workspace_bytes);
   m.def("matmul_reduce_scatter", [](torch::Tensor a, torch::Tensor b, torch::Tensor out,
                                     const std::shared_ptr<CudaSymmAllocation>& workspace, int num_sms,
-                                    uint64_t timeout_ns, c10::optional<torch::Tensor> trace) {
+                                    uint64_t timeout_ns, c10::optional<torch::Tensor> trace, int panel_w) {
     auto ok2d = [](const torch::Tensor& t) {
       return t.is_cuda() && t.dim() == 2 && t.is_contiguous() && t.scalar_type() == torch::kBFloat16;
     };
@@ -645,6 +646,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     args.num_sms = num_sms;
     args.timeout_ns = timeout_ns;
     args.status = status_for(dev);
+    args.panel_w = panel_w;
     if (trace.has_value()) {
       TORCH_CHECK(trace->is_cuda() && trace->scalar_type() == torch::kInt64 && trace->numel() >= 4 * num_sms,
                   "trace must be an int64 CUDA tensor of at least 4 * num_sms elements");
@@ -652,13 +654,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     }
     rt_check(launch_matmul_reduce_scatter(args, current_stream(dev)), "matmul_reduce_scatter");
   }, py::arg("a"), py::arg("b"), py::arg("out"), py::arg("workspace"), py::arg("num_sms"),
-     py::arg("timeout_ns"), py::arg("trace") = py::none());
+     py::arg("timeout_ns"), py::arg("trace") = py::none(), py::arg("panel_w") = 0);
 
   // all-reduce form: `out` [M, N] lives in the symmetric allocation `out_alloc` at `out_offset`
   m.def("matmul_all_reduce", [](torch::Tensor a, torch::Tensor b, torch::Tensor out,
                                 const std::shared_ptr<CudaSymmAllocation>& out_alloc, int64_t out_offset,
                                 const std::shared_ptr<CudaSymmAllocation>& workspace, int num_sms,
-                                uint64_t timeout_ns) {
+                                uint64_t timeout_ns, int panel_w) {
     auto ok2d = [](const torch::Tensor& t) {
       return t.is_cuda() && t.dim() == 2 && t.is_contiguous() && t.scalar_type() == torch::kBFloat16;
     };
@@ -689,12 +691,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     args.timeout_ns = timeout_ns;
     args.status = status_for(dev);
     args.all_reduce = true;
+    args.panel_w = panel_w;
     args.ar_peers = ov.buffers;
     args.ar_mc = ov.multicast;
     args.ar_offset = (size_t)out_offset;
     rt_check(launch_matmul_reduce_scatter(args, current_stream(dev)), "matmul_all_reduce");
   }, py::arg("a"), py::arg("b"), py::arg("out"), py::arg("out_alloc"), py::arg("out_offset"), py::arg("workspace"),
-     py::arg("num_sms"), py::arg("timeout_ns"));
+     py::arg("num_sms"), py::arg("timeout_ns"), py::arg("panel_w") = 0);
 
   // ---- rank-local layer glue ----
   m.def("rms_norm", [](torch::Tensor x, c10::optional<torch::Tensor> residual, torch::Tensor w,

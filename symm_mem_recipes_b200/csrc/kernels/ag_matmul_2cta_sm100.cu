@@ -156,7 +156,9 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
       bool first_remote = true;
       for (int wi = 0; !failed && pair_work(p, pair, n_pairs, total_tiles, k_blocks, wi, w); ++wi) {
         const int t = w.tile;
-        const int mi = (t / p.n_tiles_n) * 2 + (int)cta_rank, ni = t % p.n_tiles_n;
+        int prow, ni;
+        tile_coords(p, n_pair_rows, t, prow, ni);
+        const int mi = prow * 2 + (int)cta_rank;
         bool local = true;
         const CUtensorMap* amap = &tmap_a_out;
         int row0;
@@ -280,7 +282,9 @@ ag_matmul_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a_shard,
     PairWork w;
     for (int wi = 0; !failed && pair_work(p, pair, n_pairs, total_tiles, k_blocks, wi, w); ++wi) {
       const int t = w.tile;
-      const int mi = (t / p.n_tiles_n) * 2 + (int)cta_rank, ni = t % p.n_tiles_n;
+      int prow, ni;
+      tile_coords(p, n_pair_rows, t, prow, ni);
+      const int mi = prow * 2 + (int)cta_rank;
       bool local_unused;
       const bool valid = mi < p.n_blocks_m;
       const int mblk = valid ? scheduled_block(p, mi, local_unused) : 0;
@@ -575,6 +579,8 @@ int launch_ag_matmul_2cta(const AgMatmulArgs& a, cudaStream_t stream) {
   p.M = a.M; p.N = a.N; p.K = a.K;
   p.elem_bytes = es;
   p.n_tiles_n = (a.N + bn - 1) / bn;
+  p.panel_w = a.panel_w > 0 ? (a.panel_w < p.n_tiles_n ? a.panel_w : p.n_tiles_n)
+                            : pick_panel_w(p.n_tiles_n, (size_t)bn * a.K * es);
   p.n_blocks_m = (a.M + kBM - 1) / kBM;
   p.rank = comm ? a.rank : 0;
   p.world_size = comm ? a.world_size : 1;
@@ -627,7 +633,7 @@ int launch_ag_matmul_2cta(const AgMatmulArgs& a, cudaStream_t stream) {
     if (a.lead < 0) {
       // own blocks first for as long as the first round of tiles lasts: no CTA then starts the kernel
       // waiting for a peer (measured on two ranks: 693 µs with 12 own blocks first, 734 µs with 4)
-      const int first_round = 2 * ((pairs + p.n_tiles_n - 1) / p.n_tiles_n);
+      const int first_round = 2 * ((pairs + p.panel_w - 1) / p.panel_w);
       p.lead = first_round < p.blocks_per_rank ? first_round : p.blocks_per_rank;
     }
     const int n_rounds = (total_tiles + pairs - 1) / pairs;

@@ -20,6 +20,7 @@
 #include "../device/vec.cuh"
 #include "../symm/driver_api.h"
 #include "launch.h"
+#include "tile_order.h"
 
 namespace smr {
 namespace agmm {
@@ -39,6 +40,7 @@ struct AgMatmulParams {
   int M, N, K;
   int elem_bytes;        // 2 = bf16 in and out; 1 = fp8 e4m3 in and out
   int n_tiles_n;         // ceil(N / BN)
+  int panel_w;           // N tiles per column panel of the tile order (n_tiles_n: one panel)
   int n_blocks_m;        // ceil(M / 128)
   // gather
   int rank, world_size;
@@ -203,7 +205,8 @@ __host__ __device__ __forceinline__ int pieces_needed_through_round(const AgMatm
                                                            int n_units, int pos_per_tile = 1) {
   const int ws = p.world_size, bpr = p.blocks_per_rank;
   long long tiles = (long long)(round + 1) * n_units;
-  int mi_end = (int)((tiles + p.n_tiles_n - 1) / p.n_tiles_n) * pos_per_tile;   // positions touched: [0, mi_end)
+  // the first column panel walks every row block; later panels find them all arrived
+  int mi_end = (int)((tiles + p.panel_w - 1) / p.panel_w) * pos_per_tile;       // positions touched: [0, mi_end)
   if (mi_end > p.n_blocks_m) mi_end = p.n_blocks_m;
   if (mi_end <= p.lead) return 0;
   int q = mi_end - 1 - p.lead;
@@ -227,6 +230,10 @@ __host__ __device__ __forceinline__ int pieces_due(const AgMatmulParams& p, int 
     if (even > due) due = (int)even;
   }
   return due < all_pieces ? due : all_pieces;
+}
+
+__host__ __device__ __forceinline__ void tile_coords(const AgMatmulParams& p, int n_rows, int t, int& row, int& ni) {
+  panel_tile_coords(p.n_tiles_n, p.panel_w, n_rows, t, row, ni);
 }
 
 // The i-th piece of work of a CTA pair in the 2-CTA kernel: a whole tile, or

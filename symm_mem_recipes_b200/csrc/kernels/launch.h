@@ -112,6 +112,9 @@ struct AgMatmulArgs {
   // push mode: pieces a 128-row block is cut into for the broadcast (0 = the launcher's choice); a block
   // has arrived when all of its pieces have, each pushed by another CTA
   int push_pieces;
+  // N tiles per column panel of the tile order (0 = the launcher's choice: the widest even split of the
+  // N tiles whose rows of B stay in L2)
+  int panel_w;
 };
 int launch_ag_matmul_2cta(const AgMatmulArgs& args, cudaStream_t stream);
 
@@ -167,6 +170,8 @@ struct MatmulRsArgs {
   void* const* ar_peers;   // device table: payload base of the output allocation on every rank
   void* ar_mc;             // its multicast base or nullptr
   size_t ar_offset;        // offset of the output tensor inside that payload
+  // N tiles per column panel of the tile order (0 = the widest even split whose rows of B stay in L2)
+  int panel_w;
 };
 size_t matmul_rs_workspace_bytes(int M, int N);
 int launch_matmul_reduce_scatter(const MatmulRsArgs& args, cudaStream_t stream);

@@ -170,13 +170,15 @@ __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloa
 // with an online softmax for the G = hq / hkv query heads that share the KV head: a lane owns VEC of
 // the D = 32 * VEC dimensions, so one K or V row is one coalesced warp load.  The warps of a CTA
 // merge their (max, sum, weighted V) through shared memory into one partial per CTA in scratch; the
-// last CTA of a (b, kv head) to arrive merges those and writes bf16.  The new token's key and value
+// last CTA of a (b, kv head) to arrive merges those (one warp per head weighs the splits, then all
+// threads add them up) and writes bf16.  The new token's key and value
 // come from the QKV row (split 0 also writes them into the caches), so no CTA depends on another's
 // cache write.  The position may come from device memory and the grid does not depend on it: a
 // captured graph serves every position.
 constexpr int kAttnWarps = 8;
 constexpr int kAttnMaxG = 8;
 constexpr int kAttnBatch = 4;            // positions whose rows are loaded before any is used
+constexpr int kAttnMaxSplit = 64;        // CTAs per (sequence, KV head) at most
 // "No position seen yet" as a running maximum.  A finite stand-in for minus infinity: a warp or a CTA
 // may see no position at all (pos + 1 < units), and exp(-inf - (-inf)) would be NaN in the merges,
 // while exp(kNoScore - kNoScore) = 1 weights a sum and a vector that are both zero.
@@ -212,34 +214,36 @@ __device__ __forceinline__ void copy_bf16_vec(__nv_bfloat16* dst, const __nv_bfl
   else *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(src);
 }
 
-// Merges `n` partials of query head g, dimension d: partial i has its max at m[i * m_stride], its sum
-// at l[i * m_stride] and its weighted V at a[i * a_stride].  Returns the merged weighted V, max, sum.
-// kGlobal: the partials were written by other CTAs (read past L1).
-template <bool kGlobal>
-__device__ __forceinline__ void merge_partials(const float* m, const float* l, const float* a, int n, int m_stride,
-                                               int a_stride, float& out_a, float& out_m, float& out_l) {
-  auto ld = [](const float* p) { return kGlobal ? __ldcg(p) : *p; };
+// Merges the `n` partials that the warps of a CTA left in shared memory for query head g, dimension d:
+// partial i has its max at m[i * stride], its sum at l[i * stride] and its weighted V at a[i * stride].
+// Returns the merged weighted V, max, sum.
+__device__ __forceinline__ void merge_partials(const float* m, const float* l, const float* a, int n, int stride,
+                                               float& out_a, float& out_m, float& out_l) {
   float big = kNoScore;
 #pragma unroll 8
-  for (int i = 0; i < n; ++i) big = fmaxf(big, ld(m + (size_t)i * m_stride));
+  for (int i = 0; i < n; ++i) big = fmaxf(big, m[(size_t)i * stride]);
   float sum = 0.f, acc = 0.f;
 #pragma unroll 8
   for (int i = 0; i < n; ++i) {
-    const float w = __expf(ld(m + (size_t)i * m_stride) - big);   // 0 for a partial that saw no position while another did
-    sum += w * ld(l + (size_t)i * m_stride);
-    acc += w * ld(a + (size_t)i * a_stride);
+    const float w = __expf(m[(size_t)i * stride] - big);   // 0 for a partial that saw no position while another did
+    sum += w * l[(size_t)i * stride];
+    acc += w * a[(size_t)i * stride];
   }
   out_a = acc; out_m = big; out_l = sum;
 }
 
 template <int VEC>
-__global__ void __launch_bounds__(kAttnWarps * 32)
+__global__ void __launch_bounds__(kAttnWarps * 32, 2)
 decode_attention_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* k_cache, __nv_bfloat16* v_cache,
                         __nv_bfloat16* __restrict__ out, float* scratch, unsigned int* counters, int hq, int hkv,
                         int s_max, int pos0, const int* __restrict__ pos_dev, float scale, float log2_theta) {
   constexpr int D = 32 * VEC;
   constexpr int kRow = D + 2;                                  // D weighted-V sums, then max and sum
   __shared__ float sm[kAttnWarps][kAttnMaxG][kRow];
+  __shared__ __align__(16) float wsm[kAttnWarps][kAttnBatch * kAttnMaxG];   // a batch's softmax weights, per warp
+  __shared__ __align__(16) float csm[kAttnWarps][kAttnMaxG];                // and its rescaling of the running sums
+  __shared__ float split_w[kAttnMaxG][kAttnMaxSplit];   // the last CTA's weights of the splits, per head
+  __shared__ float head_sum[kAttnMaxG];
   __shared__ int is_last;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bh = blockIdx.x, b = bh / hkv, kvh = bh - b * hkv;
@@ -278,11 +282,9 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* k_
   load_bf16_vec<VEC>(v_new, v_tok);
   if (rotate) rope(k_tok);
 
-  float q[kAttnMaxG][VEC], acc[kAttnMaxG][VEC], m[kAttnMaxG], l[kAttnMaxG];
+  float q[kAttnMaxG][VEC], acc[kAttnMaxG][VEC];
 #pragma unroll
   for (int g = 0; g < kAttnMaxG; ++g) {
-    m[g] = kNoScore;
-    l[g] = 0.f;
 #pragma unroll
     for (int j = 0; j < VEC; ++j) acc[g][j] = q[g][j] = 0.f;
     if (g < G) {
@@ -292,11 +294,18 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* k_
       for (int j = 0; j < VEC; ++j) q[g][j] *= scale;
     }
   }
+  // After the reduction below, lane L owns the score of position slot L >> 3 of the batch and query
+  // head L & 7, and keeps the running maximum of that head (the same value in the four lanes of a
+  // head) and its own slot's share of the running sum.
+  const int my_slot = lane >> 3, my_g = lane & 7;
+  float m_run = kNoScore, l_run = 0.f;
   for (int p0 = unit; p0 <= pos; p0 += kAttnBatch * n_units) {
     float k[kAttnBatch][VEC], v[kAttnBatch][VEC];
 #pragma unroll
     for (int i = 0; i < kAttnBatch; ++i) {                      // all loads of the batch before any use
       const int p = p0 + i * n_units;
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) k[i][j] = v[i][j] = 0.f;
       if (p < pos) {
         const size_t off = (((size_t)b * s_max + p) * hkv + kvh) * D + lane * VEC;
         load_bf16_vec<VEC>(k_cache + off, k[i]);
@@ -309,28 +318,61 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* k_
         }
       }
     }
+    // this lane's share of the 4 x 8 dot products, then a halving exchange: 31 shuffles leave the
+    // complete sum of product (slot, head) in lane slot * 8 + head (a shuffle tree per product
+    // would take 160)
+    float val[kAttnBatch * kAttnMaxG];
 #pragma unroll
-    for (int i = 0; i < kAttnBatch; ++i) {
-      if (p0 + i * n_units <= pos) {                            // uniform over the warp
+    for (int i = 0; i < kAttnBatch; ++i)
 #pragma unroll
-        for (int g = 0; g < kAttnMaxG; ++g) {
-          if (g < G) {
-            float s = 0.f;
+      for (int g = 0; g < kAttnMaxG; ++g) {
+        float d = 0.f;
 #pragma unroll
-            for (int j = 0; j < VEC; ++j) s += q[g][j] * k[i][j];
+        for (int j = 0; j < VEC; ++j) d += q[g][j] * k[i][j];
+        val[i * kAttnMaxG + g] = d;
+      }
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-            const float m_new = fmaxf(m[g], s);
-            const float corr = __expf(m[g] - m_new), w = __expf(s - m_new);
-            l[g] = l[g] * corr + w;
+    for (int sft = 16, n = 32; sft >= 1; sft >>= 1, n >>= 1) {
+      const bool upper = (lane & sft) != 0;
 #pragma unroll
-            for (int j = 0; j < VEC; ++j) acc[g][j] = acc[g][j] * corr + w * v[i][j];
-            m[g] = m_new;
-          }
-        }
+      for (int t = 0; t < n / 2; ++t) {
+        const float send = upper ? val[t] : val[t + n / 2];
+        const float keep = upper ? val[t + n / 2] : val[t];
+        val[t] = keep + __shfl_xor_sync(0xffffffffu, send, sft);
       }
     }
+    const bool valid = my_g < G && p0 + my_slot * n_units <= pos;
+    const float sc = valid ? val[0] : kNoScore;
+    float mb = fmaxf(sc, __shfl_xor_sync(0xffffffffu, sc, 8));
+    mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, 16));
+    const float m_new = fmaxf(m_run, mb);
+    const float corr = __expf(m_run - m_new);                  // 1 while the head has seen no position
+    const float w = valid ? __expf(sc - m_new) : 0.f;
+    l_run = l_run * corr + w;
+    m_run = m_new;
+    // every lane needs all 32 weights and the 8 corrections: through shared memory (broadcast reads)
+    wsm[warp][lane] = w;
+    if (lane < kAttnMaxG) csm[warp][lane] = corr;
+    __syncwarp();
+#pragma unroll
+    for (int g = 0; g < kAttnMaxG; ++g) {
+      const float c = csm[warp][g];
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) acc[g][j] *= c;
+    }
+#pragma unroll
+    for (int i = 0; i < kAttnBatch; ++i)
+#pragma unroll
+      for (int g = 0; g < kAttnMaxG; ++g) {
+        const float wv = wsm[warp][i * kAttnMaxG + g];
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) acc[g][j] += wv * v[i][j];
+      }
+    __syncwarp();                                               // all lanes have read before the next batch writes
   }
+  // the head's sum: add the four slots' shares (its maximum is already the same in the four lanes)
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 8);
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 16);
   if (split == 0 && warp == 0) {                      // the new token's key and value enter the caches
     const size_t off = (((size_t)b * s_max + pos) * hkv + kvh) * D + lane * VEC;
     store_bf16_vec<VEC>(k_cache + off, k_tok);
@@ -342,19 +384,18 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* k_
     if (g < G) {
 #pragma unroll
       for (int j = 0; j < VEC; ++j) sm[warp][g][lane * VEC + j] = acc[g][j];
-      if (lane == 0) {
-        sm[warp][g][D] = m[g];
-        sm[warp][g][D + 1] = l[g];
-      }
     }
+  }
+  if (lane < kAttnMaxG) {                               // lane g holds head g's maximum and sum
+    sm[warp][lane][D] = m_run;
+    sm[warp][lane][D + 1] = l_run;
   }
   __syncthreads();
   float* mine = scratch + ((size_t)bh * n_split + split) * kAttnMaxG * kRow;
   for (int item = threadIdx.x; item < G * D; item += kAttnWarps * 32) {
     const int g = item / D, d = item - g * D;
     float a, mm, ll;
-    merge_partials<false>(&sm[0][g][D], &sm[0][g][D + 1], &sm[0][g][d], kAttnWarps, kAttnMaxG * kRow,
-                          kAttnMaxG * kRow, a, mm, ll);
+    merge_partials(&sm[0][g][D], &sm[0][g][D + 1], &sm[0][g][d], kAttnWarps, kAttnMaxG * kRow, a, mm, ll);
     mine[g * kRow + d] = a;
     if (d == 0) {
       mine[g * kRow + D] = mm;
@@ -367,14 +408,60 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* k_
   __syncthreads();
   if (!is_last) return;
   // ---- the last CTA of this (b, kv head) merges the CTAs' partials ----
+  // Warp g first turns head g's maxima and sums of the splits into one weight per split (a lane
+  // takes up to two splits) and the head's total; then every thread adds up its (head, dimension)
+  // items over the splits with those weights, eight splits' loads in flight for each of its items.
   __threadfence();
+  static_assert(kAttnWarps >= kAttnMaxG && kAttnMaxSplit <= 64, "a warp per head, two splits per lane");
   const float* all = scratch + (size_t)bh * n_split * kAttnMaxG * kRow;
-  for (int item = threadIdx.x; item < G * D; item += kAttnWarps * 32) {
-    const int g = item / D, d = item - g * D;
-    float a, mm, ll;
-    merge_partials<true>(all + g * kRow + D, all + g * kRow + D + 1, all + g * kRow + d, n_split, kAttnMaxG * kRow,
-                         kAttnMaxG * kRow, a, mm, ll);
-    out[((size_t)b * hq + kvh * G + g) * D + d] = __float2bfloat16_rn(a / ll);
+  if (warp < G) {
+    const int g = warp;
+    float mv[2], lv[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int i = lane + 32 * u;
+      const float* rec = all + ((size_t)i * kAttnMaxG + g) * kRow + D;
+      mv[u] = i < n_split ? __ldcg(rec) : kNoScore;
+      lv[u] = i < n_split ? __ldcg(rec + 1) : 0.f;
+    }
+    float big = fmaxf(mv[0], mv[1]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) big = fmaxf(big, __shfl_xor_sync(0xffffffffu, big, o));
+    float total = 0.f;
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int i = lane + 32 * u;
+      const float w = i < n_split ? __expf(mv[u] - big) : 0.f;   // 0 for a split that saw no position while another did
+      split_w[g][i] = w;
+      total += w * lv[u];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+    if (lane == 0) head_sum[g] = total;
+  }
+  __syncthreads();
+  constexpr int kItems = kAttnMaxG * D / (kAttnWarps * 32);   // (head, dimension) items per thread at most
+  float tot[kItems];
+#pragma unroll
+  for (int t = 0; t < kItems; ++t) tot[t] = 0.f;
+#pragma unroll 8
+  for (int i = 0; i < n_split; ++i) {
+#pragma unroll
+    for (int t = 0; t < kItems; ++t) {
+      const int item = threadIdx.x + t * kAttnWarps * 32;
+      if (item < G * D) {
+        const int g = item / D, d = item - g * D;
+        tot[t] += split_w[g][i] * __ldcg(all + ((size_t)i * kAttnMaxG + g) * kRow + d);
+      }
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < kItems; ++t) {
+    const int item = threadIdx.x + t * kAttnWarps * 32;
+    if (item < G * D) {
+      const int g = item / D, d = item - g * D;
+      out[((size_t)b * hq + kvh * G + g) * D + d] = __float2bfloat16_rn(tot[t] / head_sum[g]);
+    }
   }
   if (threadIdx.x == 0) counters[bh] = 0u;            // ready for the next launch
 }
@@ -427,9 +514,15 @@ int launch_silu_mul(const void* gate_up, void* out, long long rows, int F, int n
 }
 
 size_t decode_attention_scratch_bytes(int batch, int hkv, int head_dim, int s_max, int* n_split_out) {
-  // enough units to spread a long cache over the SMs, few enough for one CTA to combine them
-  int n_split = (s_max + 255) / 256;
-  n_split = n_split < 1 ? 1 : (n_split > 32 ? 32 : n_split);
+  // about two CTAs per SM over all (b, kv head); a CTA's eight warps take four positions at a time, so
+  // a split shorter than 64 positions is not worth a CTA; few enough splits for one CTA to combine them
+  // (rounded down: 296 CTAs of 256 threads and 128 registers are what 148 SMs hold at once, and a few
+  // CTAs left for a second wave would double the kernel's time)
+  const int rows = batch * hkv > 0 ? batch * hkv : 1;
+  int n_split = 296 / rows;
+  const int by_length = (s_max + 63) / 64;
+  if (n_split > by_length) n_split = by_length;
+  n_split = n_split < 1 ? 1 : (n_split > kAttnMaxSplit ? kAttnMaxSplit : n_split);
   if (n_split_out) *n_split_out = n_split;
   const size_t partials = (size_t)batch * hkv * n_split * kAttnMaxG * (head_dim + 2) * sizeof(float);
   return 256 + ((size_t)batch * hkv * sizeof(unsigned int) + 255) / 256 * 256 + partials;

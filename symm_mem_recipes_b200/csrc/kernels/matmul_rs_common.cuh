@@ -14,6 +14,7 @@
 #include "../device/vec.cuh"
 #include "../symm/driver_api.h"
 #include "launch.h"
+#include "tile_order.h"
 
 namespace smr {
 namespace rs {
@@ -39,6 +40,7 @@ struct RsParams {
   int rank, world_size;
   int blocks_per_rank;       // 128-row blocks per destination
   int n_tiles_n;
+  int panel_w;               // N tiles per column panel of the tile order (n_tiles_n: one panel)
   void* const* buffers;      // workspace payload base of every rank
   size_t inbox_offset;       // inbox [WS src][M/WS][N] bf16 inside the payload
   uint32_t* const* pads;

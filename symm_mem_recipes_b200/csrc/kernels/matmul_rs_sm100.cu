@@ -122,7 +122,8 @@ matmul_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int pair = (int)blockIdx.x >> 1;
   const int n_pairs = (int)gridDim.x >> 1;
   const int n_rb = p.world_size * p.blocks_per_rank;       // 128-row blocks over all destinations
-  const int total_tiles = ((n_rb + 1) >> 1) * p.n_tiles_n;
+  const int n_pair_rows = (n_rb + 1) >> 1;
+  const int total_tiles = n_pair_rows * p.n_tiles_n;
   const int k_blocks = (p.K + kBK - 1) / kBK;
   const int rows_per_rank = p.blocks_per_rank * kBM;
   bool failed = !entered;
@@ -132,7 +133,8 @@ matmul_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       for (int t = pair; t < total_tiles && !failed; t += n_pairs) {
-        const int pr = t / p.n_tiles_n, ni = t - pr * p.n_tiles_n;
+        int pr, ni;
+        panel_tile_coords(p.n_tiles_n, p.panel_w, n_pair_rows, t, pr, ni);
         const int rb = 2 * pr + (int)cta_rank;
         int row0 = p.M;                                    // past the end: reads as zero
         if (rb < n_rb) {
@@ -199,7 +201,8 @@ matmul_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint32_t acc = 0, acc_phase = 0, strip_ctr = 0;
     __shared__ int own_ok;
     for (int t = pair; t < total_tiles && !failed; t += n_pairs) {
-      const int pr = t / p.n_tiles_n, ni = t - pr * p.n_tiles_n;
+      int pr, ni;
+      panel_tile_coords(p.n_tiles_n, p.panel_w, n_pair_rows, t, pr, ni);
       const int rb = 2 * pr + (int)cta_rank;
       const bool valid = rb < n_rb;
       int dest = 0, mb = 0;
@@ -308,6 +311,10 @@ int launch_matmul_reduce_scatter(const MatmulRsArgs& a, cudaStream_t stream) {
   p.rank = a.pv.rank; p.world_size = ws;
   p.blocks_per_rank = a.M / ws / kBM;
   p.n_tiles_n = (a.N + kBN - 1) / kBN;
+  // column panels only for a B beyond the L2: timed in turns on four GPUs (down-projection, B = 117 MB), one
+  // panel took 2785 µs and panels of 16 / 11 / 8 tiles 2935 / 2999 / 3002 µs
+  p.panel_w = a.panel_w > 0 ? (a.panel_w < p.n_tiles_n ? a.panel_w : p.n_tiles_n)
+                            : pick_panel_w(p.n_tiles_n, (size_t)kBN * a.K * 2, kPanelBudgetL2);
   if ((uint32_t)(p.blocks_per_rank * p.n_tiles_n) + 2u > kFusedFlagSlots) return cudaErrorInvalidValue;
   p.buffers = a.pv.buffers;
   p.inbox_offset = a.inbox_offset;

@@ -16,8 +16,9 @@ using namespace agmm;
 //  1 the M schedule is not a permutation of the blocks / `local` is wrong
 //  2 a tile could wait for a piece that no CTA has been told to push yet
 //  3 not every piece is pushed by the end
+//  4 the column-panel tile order does not visit every tile exactly once
 static int check_push_schedule_with_lead(int world_size, int rank, int blocks_per_rank, int n_tiles_n, int n_units,
-                                         int pos_per_tile, int pieces, int lead) {
+                                         int pos_per_tile, int pieces, int lead, int panel_w) {
   AgMatmulParams p{};
   p.mode = 2;
   p.world_size = world_size;
@@ -25,6 +26,7 @@ static int check_push_schedule_with_lead(int world_size, int rank, int blocks_pe
   p.blocks_per_rank = blocks_per_rank;
   p.n_blocks_m = world_size * blocks_per_rank;
   p.n_tiles_n = n_tiles_n;
+  p.panel_w = panel_w;
   p.lead = lead;
   p.pieces = pieces;
   // 1. permutation + locality
@@ -40,12 +42,22 @@ static int check_push_schedule_with_lead(int world_size, int rank, int blocks_pe
   const int m_tiles = (p.n_blocks_m + pos_per_tile - 1) / pos_per_tile;
   const int total_tiles = m_tiles * n_tiles_n;
   const int rounds = (total_tiles + n_units - 1) / n_units;
+  {
+    std::vector<int> visited((size_t)total_tiles, 0);
+    for (int t = 0; t < total_tiles; ++t) {
+      int row, ni;
+      tile_coords(p, m_tiles, t, row, ni);
+      if (row < 0 || row >= m_tiles || ni < 0 || ni >= n_tiles_n || visited[(size_t)row * n_tiles_n + ni]++) return 4;
+    }
+  }
   for (int j = 0; j < rounds; ++j) {
     const int limit = pieces_needed_through_round(p, j + 1, n_units, pos_per_tile);
     const long long t_end = (long long)(j + 1) * n_units;
     for (int t = 0; t < total_tiles && t < t_end; ++t) {
       for (int c = 0; c < pos_per_tile; ++c) {
-        const int mi = (t / n_tiles_n) * pos_per_tile + c;
+        int row, ni;
+        tile_coords(p, m_tiles, t, row, ni);
+        const int mi = row * pos_per_tile + c;
         if (mi >= p.n_blocks_m) continue;
         bool local = false;
         const int blk = scheduled_block(p, mi, local);
@@ -60,17 +72,21 @@ static int check_push_schedule_with_lead(int world_size, int rank, int blocks_pe
   return 0;
 }
 
-// Every number of own blocks scheduled first that a launcher may pick: none, a few, the first round of
-// tiles (the default), the whole shard.
+// Every number of own blocks scheduled first that a launcher may pick (none, a few, the first round of
+// tiles (the default), the whole shard), for one column panel and for narrower ones (an even split in
+// two, an uneven one with a narrow last panel, single-tile panels).
 int check_push_schedule(int world_size, int rank, int blocks_per_rank, int n_tiles_n, int n_units,
                         int pos_per_tile, int pieces) {
-  const int first_round = pos_per_tile * ((n_units + n_tiles_n - 1) / n_tiles_n);
-  const int leads[4] = {0, blocks_per_rank < 4 ? blocks_per_rank : 4,
-                        first_round < blocks_per_rank ? first_round : blocks_per_rank, blocks_per_rank};
-  for (int lead : leads) {
-    int rc = check_push_schedule_with_lead(world_size, rank, blocks_per_rank, n_tiles_n, n_units, pos_per_tile,
-                                           pieces, lead);
-    if (rc != 0) return rc;
+  const int widths[4] = {n_tiles_n, (n_tiles_n + 1) / 2, n_tiles_n > 3 ? n_tiles_n - n_tiles_n / 3 : n_tiles_n, 1};
+  for (int panel_w : widths) {
+    const int first_round = pos_per_tile * ((n_units + panel_w - 1) / panel_w);
+    const int leads[4] = {0, blocks_per_rank < 4 ? blocks_per_rank : 4,
+                          first_round < blocks_per_rank ? first_round : blocks_per_rank, blocks_per_rank};
+    for (int lead : leads) {
+      int rc = check_push_schedule_with_lead(world_size, rank, blocks_per_rank, n_tiles_n, n_units, pos_per_tile,
+                                             pieces, lead, panel_w);
+      if (rc != 0) return rc;
+    }
   }
   return 0;
 }
@@ -97,10 +113,23 @@ int check_pair_work(int total_tiles, int n_pairs, int k_blocks, int tail_tiles, 
 }
 
 // CTA-pair reduce-scatter kernel: over all pairs, both CTAs and all tiles, every (destination, row
-// block, N tile) is produced exactly once, own rows last; entries past the end are skipped.
-// 0 = holds; 1 = a tile is missing or doubled; 2 = a destination other than the own one follows it.
+// block, N tile) is produced exactly once, own rows last inside every column panel (a tile of the own
+// rows waits for the peers' tiles of the same panel, which therefore all come earlier in every
+// rank's order); entries past the end are skipped.
+// 0 = holds; 1 = a tile is missing or doubled; 2 = inside a panel, a destination other than the own one
+// follows it.
+static int check_rs_pair_schedule_panel(int world_size, int rank, int blocks_per_rank, int n_tiles_n, int n_pairs,
+                                        int panel_w);
 int check_rs_pair_schedule(int world_size, int rank, int blocks_per_rank, int n_tiles_n, int n_pairs) {
+  const int widths[4] = {n_tiles_n, (n_tiles_n + 1) / 2, n_tiles_n > 3 ? n_tiles_n - n_tiles_n / 3 : n_tiles_n, 1};
+  for (int w : widths)
+    if (int rc = check_rs_pair_schedule_panel(world_size, rank, blocks_per_rank, n_tiles_n, n_pairs, w)) return rc;
+  return 0;
+}
+static int check_rs_pair_schedule_panel(int world_size, int rank, int blocks_per_rank, int n_tiles_n, int n_pairs,
+                                        int panel_w) {
   rs::RsParams p{};
+  p.panel_w = panel_w;
   p.world_size = world_size;
   p.rank = rank;
   p.blocks_per_rank = blocks_per_rank;
@@ -111,8 +140,14 @@ int check_rs_pair_schedule(int world_size, int rank, int blocks_per_rank, int n_
   for (int pair = 0; pair < n_pairs; ++pair)
     for (int cta = 0; cta < 2; ++cta) {
       bool own_seen = false;
+      int last_panel = -1;
       for (int t = pair; t < total_tiles; t += n_pairs) {
-        const int pr = t / n_tiles_n, ni = t - pr * n_tiles_n;
+        int pr, ni;
+        panel_tile_coords(n_tiles_n, panel_w, (n_rb + 1) / 2, t, pr, ni);
+        if (ni / panel_w != last_panel) {
+          last_panel = ni / panel_w;
+          own_seen = false;
+        }
         const int rb = 2 * pr + cta;
         if (rb >= n_rb) continue;
         int dest, mb;

@@ -53,6 +53,8 @@ class AgMatmulConfig:
     push_plain_stores: int = _env_int("SMR_AGMM_PUSH_PLAIN_STORES", -1)
     # pieces a 128-row block is cut into for the broadcast (0 = the launcher's choice)
     push_pieces: int = _env_int("SMR_AGMM_PUSH_PIECES", 0)
+    # N tiles per column panel of the tile order (0 = the widest even split whose rows of B stay in L2)
+    panel_w: int = _env_int("SMR_AGMM_PANEL_W", 0)
     timeout_ms: int = _env_int("SMR_TIMEOUT_MS", 10000)
 
 
@@ -186,7 +188,7 @@ def matmul(a: torch.Tensor, b: torch.Tensor, c_out: Optional[torch.Tensor] = Non
     sms = config.num_sms or _num_sms(a.device)
     bn = 256 if epi else (config.block_n or choose_block_n(M, N, sms))
     C.ag_matmul(a, b, c_out, 0, None, 0, None, bn, sms, config.timeout_ms * 1_000_000,
-                _tail_buffer(a.device, config), epi, trace)
+                _tail_buffer(a.device, config), epi, trace, panel_w=config.panel_w)
     return c_out
 
 
@@ -291,7 +293,7 @@ def all_gather_matmul(a_shard: torch.Tensor, b: torch.Tensor, a_out: Optional[to
     _check_gather_geometry(rec.notes, (aout_offset, M, K, a_shard.dtype))
     C.ag_matmul(a_shard, b, c_out, 2, hdl.native, aout_offset, a_out, bn, sms, t_ns,
                 _tail_buffer(a_shard.device, config), epi, trace, config.lead, config.push_ahead,
-                config.push_spread, _push_plain_stores(config, ws), config.push_pieces)
+                config.push_spread, _push_plain_stores(config, ws), config.push_pieces, config.panel_w)
     return c_out
 
 

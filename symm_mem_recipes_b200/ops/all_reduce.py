@@ -132,7 +132,7 @@ def multimem_all_reduce_(t: torch.Tensor, *, config: AllReduceConfig = DEFAULT_A
             return t
         if not hdl.has_multicast:
             raise SymmMemError("this allocation has no multicast mapping (NVLS unavailable)")
-        C.multimem_all_reduce(hdl.native, offset, t.numel(), config.multimem_max_blocks, t_ns)
+        C.multimem_all_reduce(hdl.native, offset, t.numel(), config.multimem_blocks(hdl.world_size), t_ns)
     else:
         raise_for_status(C.host_all_reduce(hdl.native, offset, t, t.numel(), 2, t_ns))
     return t
@@ -155,7 +155,7 @@ def choose_algo(nbytes: int, world_size: int, has_multicast: bool,
         return "multimem"
     if nbytes <= min(config.ll_max_bytes, _LL_CAPACITY_NUMEL * 2):
         return "low_latency"
-    if nbytes <= config.one_shot_max_bytes:
+    if nbytes <= config.one_shot_limit(world_size):
         return "one_shot"
     return "multimem" if has_multicast else "two_shot"
 

@@ -25,16 +25,38 @@ class AllReduceConfig:
     # low-latency push kernel (tagged words, no barrier) up to this size ...
     ll_max_bytes: int = _env_int("SMR_AR_LL_MAX_BYTES", 256 * 1024)
     ll_max_blocks: int = _env_int("SMR_AR_LL_MAX_BLOCKS", 128)
-    # ... then one-shot (peer loads) up to this size (only when larger than ll_max_bytes)
-    one_shot_max_bytes: int = _env_int("SMR_AR_ONE_SHOT_MAX_BYTES", 0)
+    # ... then one-shot (peer loads) up to this size (only when larger than ll_max_bytes);
+    # -1 = by world size (`one_shot_limit`)
+    one_shot_max_bytes: int = _env_int("SMR_AR_ONE_SHOT_MAX_BYTES", -1)
     # Above one-shot: multimem when a multicast mapping exists, else two-shot.
     # CTA caps.  Upstream caps its one-shot kernel at 24 CTAs of 512 threads
     # (triton_one_shot_all_reduce.py:97-109); large messages want more.
     one_shot_max_blocks: int = _env_int("SMR_AR_ONE_SHOT_MAX_BLOCKS", 128)
     two_shot_max_blocks: int = _env_int("SMR_AR_TWO_SHOT_MAX_BLOCKS", 128)
-    multimem_max_blocks: int = _env_int("SMR_AR_MULTIMEM_MAX_BLOCKS", 16)
+    # 0 = by world size (`multimem_blocks`)
+    multimem_max_blocks: int = _env_int("SMR_AR_MULTIMEM_MAX_BLOCKS", 0)
     timeout_ms: int = _env_int("SMR_TIMEOUT_MS", 10000)
 
+    def one_shot_limit(self, world_size: int) -> int:
+        """Largest message for which `algo="auto"` takes the one-shot kernel.  One-shot makes every
+        rank read all of every peer's buffer, so its range shrinks as the world grows.  Measured
+        on B200s: with two ranks it moves no more bytes than any other algorithm and has one
+        barrier less; with four it wins up to 1 MiB and is within 5 % of the best at 2 MiB
+        (14.1 µs against 16.3 two-shot and 17.6 multimem at 1 MiB); with eight the in-switch
+        reduction wins from 512 KiB on, i.e. right above the low-latency kernel's range."""
+        if self.one_shot_max_bytes >= 0:
+            return self.one_shot_max_bytes
+        if world_size <= 2:
+            return 1 << 62
+        return 2 * 1024 * 1024 if world_size <= 4 else 0
+
+    def multimem_blocks(self, world_size: int) -> int:
+        """CTAs of the multimem kernel: a few CTAs with eight reductions in flight per thread
+        saturate the NVSwitch port; more only add barrier traffic.  Measured at 64 MiB on four
+        ranks: 605 GB/s bus bandwidth with 8 CTAs, 598 with 16, 577 with 24, 539 with 4."""
+        if self.multimem_max_blocks > 0:
+            return self.multimem_max_blocks
+        return 8 if world_size <= 4 else 16
 
     @staticmethod
     def from_tuning(path: str, world_size: int = 0) -> "AllReduceConfig":

@@ -26,6 +26,7 @@ from .ag_matmul import _num_sms, matmul
 
 _workspaces: dict[tuple, torch.Tensor] = {}
 _TIMEOUT_MS = int(os.environ.get("SMR_TIMEOUT_MS", "10000"))
+_PANEL_W = int(os.environ.get("SMR_RS_PANEL_W", "0"))
 
 
 def _workspace(M: int, N: int, device: torch.device, group) -> torch.Tensor:
@@ -43,7 +44,7 @@ def _workspace(M: int, N: int, device: torch.device, group) -> torch.Tensor:
 @traced("smr.matmul_reduce_scatter")
 def matmul_reduce_scatter(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None,
                           group=None, num_sms: int = 0, timeout_ms: int = _TIMEOUT_MS,
-                          trace: Optional[torch.Tensor] = None) -> torch.Tensor:
+                          trace: Optional[torch.Tensor] = None, panel_w: int = _PANEL_W) -> torch.Tensor:
     """`a` [M, K_local] (all tokens, this rank's slice of the reduction
     dimension), `b` [N, K_local]; returns this rank's [M/WS, N] rows of the sum
     over ranks, bitwise identical to what any other summation site would get
@@ -51,7 +52,9 @@ def matmul_reduce_scatter(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.
 
     `trace`: optional int64 CUDA tensor [num_sms, 4]; every CTA writes its
     %globaltimer (ns) at kernel start, after the entry barrier, when its GEMM
-    tiles are pushed, and when its share of the reduction is done."""
+    tiles are pushed, and when its share of the reduction is done.
+    `panel_w`: N tiles (of 256 columns) per column panel of the tile order; 0
+    lets the launcher keep a panel's rows of `b` within the L2."""
     if a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[1]:
         raise SymmMemError("need a[M, K] and b[N, K]")
     ws = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -66,7 +69,7 @@ def matmul_reduce_scatter(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.
     wsp = _workspace(M, N, a.device, group)
     hdl = symm_mem.rendezvous(wsp, group)
     C.matmul_reduce_scatter(a, b, out, hdl.native, num_sms or _num_sms(a.device),
-                            int(timeout_ms) * 1_000_000, trace)
+                            int(timeout_ms) * 1_000_000, trace, int(panel_w))
     return out
 
 
@@ -109,7 +112,7 @@ def matmul_all_reduce(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tens
     wsp = _workspace(M, N, a.device, group)
     hdl = symm_mem.rendezvous(wsp, group)
     C.matmul_all_reduce(a, b, out, out_hdl.native, out_offset, hdl.native, num_sms or _num_sms(a.device),
-                        int(timeout_ms) * 1_000_000)
+                        int(timeout_ms) * 1_000_000, _PANEL_W)
     return out
 
 

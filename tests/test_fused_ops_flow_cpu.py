@@ -26,7 +26,7 @@ def _install_host_kernels():
         @staticmethod
         def ag_matmul(a, b, c, mode, aout_alloc, aout_offset, a_out, block_n, num_sms, timeout_ns, tail_scratch=None,
                       epilogue=0, trace=None, lead=-1, push_ahead=0, push_spread=0, push_plain_stores=False,
-                      push_pieces=0):
+                      push_pieces=0, panel_w=0):
             calls.append(mode)
             if mode == 2:
                 ws, rank = dist.get_world_size(), dist.get_rank()
@@ -145,13 +145,13 @@ def _row_parallel_flow_worker(rank, world_size):
             return getattr(real, name)
 
         @staticmethod
-        def matmul_reduce_scatter(a, b, out, workspace, num_sms, timeout_ns, trace=None):
+        def matmul_reduce_scatter(a, b, out, workspace, num_sms, timeout_ns, trace=None, panel_w=0):
             seen["rs"] = workspace.payload_bytes
             rows = out.shape[0]
             out.copy_(summed(a, b)[rank * rows:(rank + 1) * rows].to(out.dtype))
 
         @staticmethod
-        def matmul_all_reduce(a, b, out, out_alloc, out_offset, workspace, num_sms, timeout_ns):
+        def matmul_all_reduce(a, b, out, out_alloc, out_offset, workspace, num_sms, timeout_ns, panel_w=0):
             assert out.data_ptr() == real.host_view(out_alloc, -1, [1], torch.uint8, out_offset).data_ptr()
             seen["ar"] = True
             out.copy_(summed(a, b).to(out.dtype))
@@ -233,14 +233,14 @@ def _install_row_parallel_and_glue_stand_ins():
             return getattr(real, name)
 
         @staticmethod
-        def matmul_reduce_scatter(a, b, out, workspace, num_sms, timeout_ns, trace=None):
+        def matmul_reduce_scatter(a, b, out, workspace, num_sms, timeout_ns, trace=None, panel_w=0):
             rank, rows = dist.get_rank(), out.shape[0]
             out.copy_(summed(a, b)[rank * rows:(rank + 1) * rows].to(out.dtype))
             if trace is not None:                                # [CTA][start, entered, GEMM done, reduced] in ns
                 trace.view(-1, 4)[:2] = torch.tensor([[1000, 2000, 9000, 12000], [1100, 2100, 9500, 12500]])
 
         @staticmethod
-        def matmul_all_reduce(a, b, out, out_alloc, out_offset, workspace, num_sms, timeout_ns):
+        def matmul_all_reduce(a, b, out, out_alloc, out_offset, workspace, num_sms, timeout_ns, panel_w=0):
             out.copy_(summed(a, b).to(out.dtype))
 
         @staticmethod
