@@ -157,6 +157,8 @@ def choose_algo(nbytes: int, world_size: int, has_multicast: bool,
         return "low_latency"
     if nbytes <= config.one_shot_limit(world_size):
         return "one_shot"
+    if nbytes <= config.two_shot_limit(world_size):
+        return "two_shot"
     return "multimem" if has_multicast else "two_shot"
 
 

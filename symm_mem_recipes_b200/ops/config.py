@@ -28,7 +28,9 @@ class AllReduceConfig:
     # ... then one-shot (peer loads) up to this size (only when larger than ll_max_bytes);
     # -1 = by world size (`one_shot_limit`)
     one_shot_max_bytes: int = _env_int("SMR_AR_ONE_SHOT_MAX_BYTES", -1)
-    # Above one-shot: multimem when a multicast mapping exists, else two-shot.
+    # ... then two-shot up to this size; -1 = by world size (`two_shot_limit`)
+    two_shot_max_bytes: int = _env_int("SMR_AR_TWO_SHOT_MAX_BYTES", -1)
+    # Above that: multimem when a multicast mapping exists, else two-shot.
     # CTA caps.  Upstream caps its one-shot kernel at 24 CTAs of 512 threads
     # (triton_one_shot_all_reduce.py:97-109); large messages want more.
     one_shot_max_blocks: int = _env_int("SMR_AR_ONE_SHOT_MAX_BLOCKS", 128)
@@ -38,17 +40,28 @@ class AllReduceConfig:
     timeout_ms: int = _env_int("SMR_TIMEOUT_MS", 10000)
 
     def one_shot_limit(self, world_size: int) -> int:
-        """Largest message for which `algo="auto"` takes the one-shot kernel.  One-shot makes every
-        rank read all of every peer's buffer, so its range shrinks as the world grows.  Measured
-        on B200s: with two ranks it moves no more bytes than any other algorithm and has one
-        barrier less; with four it wins up to 1 MiB and is within 5 % of the best at 2 MiB
-        (14.1 µs against 16.3 two-shot and 17.6 multimem at 1 MiB); with eight the in-switch
-        reduction wins from 512 KiB on, i.e. right above the low-latency kernel's range."""
-        if self.one_shot_max_bytes >= 0:
-            return self.one_shot_max_bytes
+        """Largest message for which `algo="auto"` takes the one-shot kernel.  `all_reduce` works
+        in place, and one-shot must then wait for every peer to have read the input before it
+        may overwrite it: a second barrier and a second pass, about 5.5 µs.  Measured on two and
+        four B200s, the one-shot kernel alone beats two-shot from 256 KiB to 1 MiB (12.2 against
+        15.3 µs at 512 KiB on four ranks) but loses with that write-back (17.7 µs), so by default
+        the dispatcher never picks it; callers that can take the sum in a new tensor call
+        `one_shot_all_reduce` themselves."""
+        return self.one_shot_max_bytes if self.one_shot_max_bytes >= 0 else 0
+
+    def two_shot_limit(self, world_size: int) -> int:
+        """Largest message for which `algo="auto"` prefers the two-shot kernel (peer loads, peer
+        stores) to the in-switch reduction.  Measured: with two ranks the switch has nothing to
+        save and its broadcast also returns to the sender (119 against 193 µs at 64 MiB, 15.1
+        against 13.4-17.0 at 1 MiB); with four ranks two-shot wins up to 1 MiB (15.3 against
+        15.4-18.4 µs at 512 KiB, 16.3 against 17.6-19.9 at 1 MiB) and the two are within noise of
+        each other up to 4 MiB, from where multimem wins (35.3 against 41.3 µs at 8 MiB); with
+        eight ranks multimem won at every size above the low-latency kernel's range."""
+        if self.two_shot_max_bytes >= 0:
+            return self.two_shot_max_bytes
         if world_size <= 2:
             return 1 << 62
-        return 2 * 1024 * 1024 if world_size <= 4 else 0
+        return 1024 * 1024 if world_size <= 4 else 0
 
     def multimem_blocks(self, world_size: int) -> int:
         """CTAs of the multimem kernel: a few CTAs with eight reductions in flight per thread

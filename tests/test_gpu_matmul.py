@@ -37,6 +37,33 @@ def test_matmul_small(block_n, shape):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("panel_w", [1, 2, 3, 5])
+@pytest.mark.parametrize("shape", [(640, 1280, 256), (1152, 1000, 512)])
+def test_matmul_column_panels(panel_w, shape):
+    """The tile order in column panels (whole, uneven and single-tile panels, with and without the
+    split-K tail) computes every tile exactly once: same bits as the one-panel order."""
+    from symm_mem_recipes_b200.ops.ag_matmul import AgMatmulConfig, matmul
+    from symm_mem_recipes_b200.parallel import symm_mem
+
+    M, N, K = shape
+    torch.manual_seed(M + N + K)
+    a = (torch.randn(M, K, device="cuda") * 0.5).to(torch.bfloat16)
+    b = (torch.randn(N, K, device="cuda") * 0.5).to(torch.bfloat16)
+    for split in (False, True):
+        want = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        matmul(a, b, want, AgMatmulConfig(block_n=256, num_sms=8, split_k_tail=split, panel_w=1000, timeout_ms=2000))
+        c, intact = guarded_empty((M, N), torch.bfloat16, "cuda")
+        c.fill_(float("nan"))
+        matmul(a, b, c, AgMatmulConfig(block_n=256, num_sms=8, split_k_tail=split, panel_w=panel_w, timeout_ms=2000))
+        symm_mem.check_status("cuda")
+        ok, err = _close(c, _ref(a, b), K)
+        assert ok, f"max abs error {err}"
+        assert intact(), "the kernel stored outside its output"
+        if not split:
+            assert torch.equal(c, want), "whole tiles: the order of the tiles must not change a bit"
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("shape,num_sms", [((768, 768, 1024), 8), ((1280, 512, 512), 8), ((768, 768, 4096), 8),
                                            ((16384, 3584, 1024), 0)])
 def test_matmul_split_k_tail(shape, num_sms):
@@ -90,7 +117,7 @@ def _agmm_worker(rank, world_size, rows, N, K, mode):
     torch.manual_seed(7)
     b = (torch.randn(N, K, device=dev) * 0.02).to(torch.bfloat16)
     M = rows * world_size
-    if mode in ("push", "push_multicast", "push_plain"):   # gathered A lands in symmetric memory
+    if mode in ("push", "push_multicast", "push_plain", "push_panels"):   # gathered A lands in symmetric memory
         a_out = symm_mem.empty(M, K, dtype=torch.bfloat16, device=dev)
     elif mode == "plain":       # ordinary a_out, as in the upstream API: internal buffer plus one copy
         a_out = torch.zeros(M, K, dtype=torch.bfloat16, device=dev)
@@ -99,7 +126,8 @@ def _agmm_worker(rank, world_size, rows, N, K, mode):
         a_out = None
     c_out = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
     # the broadcast through the switch (multimem.st) and the plain peer stores, whatever the world size picks
-    cfg = AgMatmulConfig(timeout_ms=5000, push_plain_stores={"push_multicast": 0, "push_plain": 1}.get(mode, -1))
+    cfg = AgMatmulConfig(timeout_ms=5000, push_plain_stores={"push_multicast": 0, "push_plain": 1}.get(mode, -1),
+                         panel_w=1 if mode == "push_panels" else 0)
     failures = []
     for it in range(3):
         smr.all_gather_matmul(a_shard, b, a_out, c_out, cfg)
@@ -131,7 +159,7 @@ def _agmm_worker(rank, world_size, rows, N, K, mode):
 
 @pytest.mark.gpu
 @pytest.mark.multigpu(2)
-@pytest.mark.parametrize("mode", ["push_multicast", "push_plain", "internal", "plain"])
+@pytest.mark.parametrize("mode", ["push_multicast", "push_plain", "push_panels", "internal", "plain"])
 @pytest.mark.parametrize("rows,N,K", [(128, 256, 256), (384, 512, 1024), (2048, 3584, 8192)])
 def test_all_gather_matmul_2gpu(rows, N, K, mode):
     spawn_ranks(_agmm_worker, 2, "nccl", (rows, N, K, mode))

@@ -5,7 +5,7 @@ import torch
 from symm_mem_recipes_b200.utils.testing import spawn_ranks
 
 
-def _rs_worker(rank, world_size, M, N, K):
+def _rs_worker(rank, world_size, M, N, K, panel_w=0):
     import symm_mem_recipes_b200 as smr
     from symm_mem_recipes_b200.parallel import symm_mem
 
@@ -21,7 +21,7 @@ def _rs_worker(rank, world_size, M, N, K):
             b_r = (torch.randn(N, K, generator=gens[r]) * 0.05).to(torch.bfloat16)
             parts.append((a_r, b_r))
         a, b = parts[rank][0].to(dev), parts[rank][1].to(dev)
-        out = smr.matmul_reduce_scatter(a, b)
+        out = smr.matmul_reduce_scatter(a, b, panel_w=panel_w)
         symm_mem.check_status(dev)
         ref = torch.zeros(rows, N, dtype=torch.float32)
         for a_r, b_r in parts:
@@ -45,6 +45,15 @@ def _rs_worker(rank, world_size, M, N, K):
 @pytest.mark.parametrize("M,N,K", [(256, 256, 128), (512, 328, 192), (768, 328, 192), (4096, 8192, 1024)])
 def test_matmul_reduce_scatter_2gpu(M, N, K):
     spawn_ranks(_rs_worker, 2, "nccl", (M, N, K))
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu(2)
+@pytest.mark.parametrize("panel_w", [1, 3])
+def test_matmul_reduce_scatter_column_panels_2gpu(panel_w):
+    """Tiles walked in column panels: the own rows come last inside every panel, and their tiles wait
+    for the peers' tiles of the same panel."""
+    spawn_ranks(_rs_worker, 2, "nccl", (1024, 1280, 256, panel_w))
 
 
 @pytest.mark.gpu

@@ -126,11 +126,16 @@ def _ar_worker(rank, world_size, numel):
     hdl.barrier()
     t.copy_(srcs[rank].to(dev))
     hdl.barrier()
+    picked = smr.ops.choose_algo(numel * 2, world_size, hdl.has_multicast)
     smr.all_reduce(t, "auto")
     hdl.check()
-    tol = fp32.abs() * 2.0 ** -5 + 1e-2       # covers ordered-bf16 and in-switch fp32 summation
-    if not bool(((t.cpu().float() - fp32).abs() <= tol).all()):
-        failures.append("all_reduce(auto) is off")
+    if picked == "multimem":                  # in-switch fp32 summation, one rounding
+        tol = fp32.abs() * 2.0 ** -7 + 1e-6
+        if not bool(((t.cpu().float() - fp32).abs() <= tol).all()):
+            failures.append("all_reduce(auto) -> multimem is off")
+    elif not torch.equal(t.cpu().view(torch.int16), ordered.view(torch.int16)):
+        # every other kernel adds bf16 values in rank order: the oracle's bits
+        failures.append(f"all_reduce(auto) -> {picked} differs from the ordered-sum oracle")
 
     # barrier stress, 10^4 barriers over four grid sizes: the pad must be all zero afterwards
     for blocks in (1, 7, 32, 148):

@@ -39,8 +39,9 @@ def test_dispatcher_thresholds():
     assert choose_algo(1 << 26, 1, False, cfg) == "one_shot"   # nothing to reduce
     # the defaults depend on the world size: one-shot reads every peer's whole buffer
     dflt = AllReduceConfig(ll_max_bytes=256 * 1024, one_shot_max_bytes=-1, multimem_max_blocks=0)
-    assert [choose_algo(1 << 20, ws, True, dflt) for ws in (2, 4, 8)] == ["one_shot", "one_shot", "multimem"]
-    assert [choose_algo(1 << 23, ws, True, dflt) for ws in (2, 4, 8)] == ["one_shot", "multimem", "multimem"]
+    assert [choose_algo(1 << 20, ws, True, dflt) for ws in (2, 4, 8)] == ["two_shot", "two_shot", "multimem"]
+    assert [choose_algo(1 << 22, ws, True, dflt) for ws in (2, 4, 8)] == ["two_shot", "multimem", "multimem"]
+    assert [choose_algo(1 << 26, ws, True, dflt) for ws in (2, 4, 8)] == ["two_shot", "multimem", "multimem"]
     assert choose_algo(1 << 23, 4, False, dflt) == "two_shot"
     assert (dflt.multimem_blocks(4), dflt.multimem_blocks(8)) == (8, 16)
     assert AllReduceConfig(multimem_max_blocks=12).multimem_blocks(8) == 12
