@@ -65,11 +65,10 @@ class AllReduceConfig:
 
     def multimem_blocks(self, world_size: int) -> int:
         """CTAs of the multimem kernel: a few CTAs with eight reductions in flight per thread
-        saturate the NVSwitch port; more only add barrier traffic.  Measured at 64 MiB on four
-        ranks: 605 GB/s bus bandwidth with 8 CTAs, 598 with 16, 577 with 24, 539 with 4."""
-        if self.multimem_max_blocks > 0:
-            return self.multimem_max_blocks
-        return 8 if world_size <= 4 else 16
+        saturate the NVSwitch port; more only add barrier traffic.  Measured at 64 MiB, bus
+        bandwidth with 4 / 8 / 16 / 24 CTAs: 733 / 741 / 707 / 689 GB/s on eight ranks, 539 / 605 /
+        598 / 577 GB/s on four; at 1 MiB 8 and 16 CTAs tie (16.9 / 16.8 µs on eight ranks)."""
+        return self.multimem_max_blocks if self.multimem_max_blocks > 0 else 8
 
     @staticmethod
     def from_tuning(path: str, world_size: int = 0) -> "AllReduceConfig":

@@ -99,7 +99,7 @@ def build_checks(world: int, rank: int, dev: torch.device) -> list:
     add("all_reduce", "auto", ar("auto"))
     if multi:
         add("all_reduce", "multimem", ar("multimem"))
-        add("all_reduce", "multimem, 8 CTAs", ar("multimem", AllReduceConfig(multimem_max_blocks=8)),
+        add("all_reduce", "multimem, 16 CTAs", ar("multimem", AllReduceConfig(multimem_max_blocks=16)),
             True)
 
     def barriers(kind):

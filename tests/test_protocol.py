@@ -43,7 +43,7 @@ def test_dispatcher_thresholds():
     assert [choose_algo(1 << 22, ws, True, dflt) for ws in (2, 4, 8)] == ["two_shot", "multimem", "multimem"]
     assert [choose_algo(1 << 26, ws, True, dflt) for ws in (2, 4, 8)] == ["two_shot", "multimem", "multimem"]
     assert choose_algo(1 << 23, 4, False, dflt) == "two_shot"
-    assert (dflt.multimem_blocks(4), dflt.multimem_blocks(8)) == (8, 16)
+    assert (dflt.multimem_blocks(4), dflt.multimem_blocks(8)) == (8, 8)
     assert AllReduceConfig(multimem_max_blocks=12).multimem_blocks(8) == 12
 
 
