@@ -32,6 +32,8 @@ def main() -> int:
     ap.add_argument("--block-n", type=int, default=0)
     ap.add_argument("--batch", type=int, default=16)
     ap.add_argument("--bytes", type=int, default=64 * 1024 * 1024)
+    ap.add_argument("--ar-algo", default="one_shot", choices=["one_shot", "low_latency"],
+                    help="all_reduce: the kernel to time in a world of one")
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-cublas", action="store_true")
@@ -132,9 +134,13 @@ def main() -> int:
             t = symm_mem.empty(numel, dtype=torch.bfloat16, device=dev)
             t.normal_()
             o = torch.empty_like(t)
-            us = benchmark_with_event(lambda: smr.one_shot_all_reduce(t, out=o), **bench)
-            out.update(bytes=args.bytes, one_shot_us=round(us, 2),
-                       read_write_gbs=round(2 * args.bytes / us / 1e3, 1))
+            if args.ar_algo == "low_latency":
+                us = benchmark_with_event(lambda: smr.low_latency_all_reduce(t, out=o), **bench)
+                out.update(bytes=args.bytes, low_latency_us=round(us, 2))
+            else:
+                us = benchmark_with_event(lambda: smr.one_shot_all_reduce(t, out=o), **bench)
+                out.update(bytes=args.bytes, one_shot_us=round(us, 2),
+                           read_write_gbs=round(2 * args.bytes / us / 1e3, 1))
         symm_mem.check_status(dev)
     out["clocks"] = clocks.summary()
     print(json.dumps(out))
