@@ -594,6 +594,14 @@ int launch_ag_matmul_2cta(const AgMatmulArgs& a, cudaStream_t stream) {
     p.push_ahead = a.push_ahead > 0 ? a.push_ahead : 1;
     size_t block_vecs = (size_t)kBM * a.K * es / 16;
     p.pieces = block_vecs >= 8192 ? 16 : (block_vecs >= 1024 ? 4 : 1);
+    // A CTA's epilogue warps take 40-60 µs to broadcast 128 KB, about one round of tiles, which is all the
+    // lead the schedule gives a piece once the own blocks are used up: with eight ranks (16 blocks per rank,
+    // 1.7 pieces of 128 KB per CTA) the CTAs waited 165 µs per call for remote blocks.  So the smaller the
+    // shard, the finer the pieces: about six per CTA over the whole shard (64 per block at eight ranks of
+    // the headline shape, 32 at four, 16 at two; on four ranks 64 measured 10-29 µs faster than 16).
+    while (p.pieces < 256 && (size_t)p.blocks_per_rank * p.pieces < (size_t)6 * a.num_sms &&
+           (size_t)(2 * p.pieces) * 128 <= block_vecs)
+      p.pieces *= 2;
     if (a.push_pieces > 0) {
       if ((a.push_pieces & (a.push_pieces - 1)) != 0 || (uint32_t)a.push_pieces > kArrivalUnits) return cudaErrorInvalidValue;
       p.pieces = a.push_pieces;
