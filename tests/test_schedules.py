@@ -46,6 +46,14 @@ def test_decoder_layer_shapes():
             assert C.check_push_schedule(8, rank, 32, n_tiles_n, 74, 2, 16) == 0
 
 
+@pytest.mark.parametrize("ws,pieces", [(2, 16), (4, 32), (8, 64), (8, 256)])
+def test_push_schedule_fine_pieces(ws, pieces):
+    """The piece counts the launcher picks for small shards (about six pieces per CTA over the shard)."""
+    bpr = 16384 // ws // 128
+    for rank in range(ws):
+        assert C.check_push_schedule(ws, rank, bpr, 14, 74, 2, pieces) == 0
+
+
 def test_split_k_tail_covers_every_tile_once():
     # headline: 896 pair tiles on 74 pairs -> 8 tail tiles cut in 8
     assert C.check_pair_work(896, 74, 128, 8, 8) == 0
