@@ -21,6 +21,10 @@ CSRC = PKG_DIR / "csrc"
 BUILD_DIR = ROOT / "build" / "smr"
 MODULE_NAME = "_C"
 
+# --use_fast_math: flush-to-zero and the approximate exp / rsqrt / division in the glue kernels (RMSNorm,
+# RoPE, SiLU, attention softmax).  Their GPU tests compare with the IEEE fp32 CPU oracles within a bf16
+# ulp of the output, which the approximations stay well inside; the GEMM, GEMV and all-reduce kernels do
+# no fp32 arithmetic that the flag changes (tensor-core MMAs and packed bf16 adds).
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17", "--use_fast_math",
