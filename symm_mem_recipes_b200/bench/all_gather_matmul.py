@@ -51,9 +51,9 @@ def build_parser() -> argparse.ArgumentParser:
                          "through the internal symmetric buffer plus one local copy")
     ap.add_argument("--leads", default="", help="push mode: comma-separated counts of own 128-row blocks multiplied "
                                                 "before the first remote one, each timed")
-    ap.add_argument("--pacings", default="", help="push mode: comma-separated AHEAD:SPREAD[:LEAD[:PLAIN[:PIECES]]] settings, each timed "
-                                                  "(rounds of lookahead of the broadcast; rounds over which the whole "
-                                                  "shard is sent at the latest, 0 = half of the kernel; own blocks first)")
+    ap.add_argument("--pacings", default="", help="push mode: comma-separated AHEAD[:LEAD[:PLAIN[:PIECES]]] settings, each timed "
+                                                  "(rounds of lookahead of the broadcast; own blocks first, -1 = default; "
+                                                  "1 = plain peer stores, 0 = multimem, -1 = by world size; pieces per block)")
     ap.add_argument("--panels", default="", help="comma-separated column-panel widths of the tile order (N tiles per "
                                                  "panel), each timed for the GEMM alone and for the fused op")
     ap.add_argument("--trace", action="store_true",
@@ -186,10 +186,10 @@ def _one_shape(args, M, N, K, rank, world, dev, lines) -> None:
             emit(what, statistics.median(vals), timing="three interleaved cycles", cycles_us=vals, **extra)
     for spec in [x for x in args.pacings.split(",") if x]:
         parts = [int(v) for v in spec.split(":")]
-        cfgp = AgMatmulConfig(block_n=args.block_n, push_ahead=parts[0], push_spread=parts[1] if len(parts) > 1 else 0,
-                              lead=parts[2] if len(parts) > 2 else -1,
-                              push_plain_stores=parts[3] if len(parts) > 3 else -1,
-                              push_pieces=parts[4] if len(parts) > 4 else 0)
+        cfgp = AgMatmulConfig(block_n=args.block_n, push_ahead=parts[0],
+                              lead=parts[1] if len(parts) > 1 else -1,
+                              push_plain_stores=parts[2] if len(parts) > 2 else -1,
+                              push_pieces=parts[3] if len(parts) > 3 else 0)
         us, extra = timed(lambda: smr.all_gather_matmul(a_shard, b, a_out, c, cfgp))
         emit("smr_fused", us, gather="push", pacing=spec, **extra)
         symm_mem.check_status(dev)

@@ -483,7 +483,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                         std::shared_ptr<CudaSymmAllocation> aout_alloc, int64_t aout_offset,
                         c10::optional<torch::Tensor> a_out, int block_n, int num_sms, uint64_t timeout_ns,
                         c10::optional<torch::Tensor> tail_scratch, int epilogue,
-                        c10::optional<torch::Tensor> trace, int lead, int push_ahead, int push_spread,
+                        c10::optional<torch::Tensor> trace, int lead, int push_ahead,
                         bool push_plain_stores, int push_pieces, int panel_w) {
     const auto dtype = a.scalar_type();
     const bool fp8 = dtype == at::kFloat8_e4m3fn;
@@ -546,7 +546,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     }
     args.lead = lead;
     args.push_ahead = push_ahead;
-    args.push_spread = push_spread;
     args.push_plain_stores = push_plain_stores ? 1 : 0;
     args.push_pieces = push_pieces;
     args.panel_w = panel_w;
@@ -561,7 +560,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
      py::arg("a_out"), py::arg("block_n"), py::arg("num_sms"), py::arg("timeout_ns"),
      py::arg("tail_scratch") = py::none(), py::arg("epilogue") = 0,
      py::arg("trace") = py::none(), py::arg("lead") = -1,
-     py::arg("push_ahead") = 0, py::arg("push_spread") = 0, py::arg("push_plain_stores") = false,
+     py::arg("push_ahead") = 0, py::arg("push_plain_stores") = false,
      py::arg("push_pieces") = 0, py::arg("panel_w") = 0);
 
   m.def("check_push_schedule", &check_push_schedule);

@@ -644,11 +644,6 @@ int launch_ag_matmul_2cta(const AgMatmulArgs& a, cudaStream_t stream) {
       const int first_round = 2 * ((pairs + p.panel_w - 1) / p.panel_w);
       p.lead = first_round < p.blocks_per_rank ? first_round : p.blocks_per_rank;
     }
-    const int n_rounds = (total_tiles + pairs - 1) / pairs;
-    // by default no faster than the schedule needs: pushes beyond that only compete with the GEMM's own
-    // loads (measured on two ranks); a positive push_spread sends the whole shard within that many rounds
-    (void)n_rounds;
-    p.push_spread = a.push_spread > 0 ? a.push_spread : 0;
   }
   // the entry barrier of CTA i uses block slot (barrier_block_base + i): it must stay inside the block-slot region
   if (comm && ((size_t)a.barrier_block_base + grid) * a.world_size > kBlockSlots) return cudaErrorInvalidValue;

@@ -49,7 +49,6 @@ struct AgMatmulParams {
   int lead;              // own blocks scheduled before the first remote one
   int pieces;            // push: pieces per 128-row block (arrivals per block and call)
   int push_ahead;        // push: rounds of tiles by which the broadcast runs ahead of the first need (>= 1)
-  int push_spread;       // push: rounds over which the whole shard is broadcast at the latest
   uint32_t* flags;       // [n_blocks_m] arrival flags read by the GEMM CTAs (local memory)
   uint32_t flag_target;  // filled from the call number in the kernel
   uint32_t* header;      // push: [0] epoch, [1] CTAs done (local, in the a_out signal pad)
@@ -218,17 +217,12 @@ __host__ __device__ __forceinline__ int pieces_needed_through_round(const AgMatm
 
 // Pieces of the own shard that should be on the wire once round `round` begins.  Never less
 // than the schedule needs (`pieces_needed_through_round(round + 1)`: nobody can then block on a
-// piece that a blocked CTA still holds), and beyond that ahead of the need: `push_ahead` rounds
-// of lookahead absorb a rank that entered the kernel late, and an even spread over
-// `push_spread` rounds keeps the epilogue warps' share of every round short when the shard is
-// large (few ranks).
+// piece that a blocked CTA still holds); `push_ahead` > 1 asks for that many rounds of lookahead
+// instead of one.  (Spreading the whole shard evenly over the first rounds of the kernel was
+// measured too: 40-190 µs slower, eager stores compete with the GEMM's own loads.)
 __host__ __device__ __forceinline__ int pieces_due(const AgMatmulParams& p, int round, int n_units,
                                                    int pos_per_tile, int all_pieces) {
   int due = pieces_needed_through_round(p, round + (p.push_ahead > 1 ? p.push_ahead : 1), n_units, pos_per_tile);
-  if (p.push_spread > 0) {
-    long long even = ((long long)(round + 1) * all_pieces + p.push_spread - 1) / p.push_spread;
-    if (even > due) due = (int)even;
-  }
   return due < all_pieces ? due : all_pieces;
 }
 

@@ -101,10 +101,8 @@ struct AgMatmulArgs {
   uint64_t* trace;
   // push mode: own 128-row blocks multiplied before the first remote one (-1 = chosen by the launcher)
   int lead;
-  // push mode pacing (0 = the launcher's choice): rounds of lookahead of the broadcast over the
-  // first need, and the number of rounds over which the whole shard is broadcast at the latest
+  // push mode pacing (0 = the launcher's choice): rounds of lookahead of the broadcast over the first need
   int push_ahead;
-  int push_spread;
   // push mode: 0 = broadcast the shard with multimem.st when the allocation has a multicast mapping
   // (the shard leaves this GPU once; every rank, the sender included, receives it from the switch),
   // 1 = plain stores to every peer and a local copy (nothing loops back through the switch)

@@ -46,9 +46,8 @@ class AgMatmulConfig:
     # push gather: own 128-row blocks multiplied before the first remote one (-1 = the launcher's choice)
     lead: int = _env_int("SMR_AGMM_LEAD", -1)
     # push gather pacing (0 = the launcher's choice): rounds of tiles by which the broadcast runs ahead of the
-    # first need, and rounds over which the whole shard is on the wire at the latest
+    # first need
     push_ahead: int = _env_int("SMR_AGMM_PUSH_AHEAD", 0)
-    push_spread: int = _env_int("SMR_AGMM_PUSH_SPREAD", 0)
     # push gather by plain stores to every peer even where a multicast mapping exists (-1 = decide by world size)
     push_plain_stores: int = _env_int("SMR_AGMM_PUSH_PLAIN_STORES", -1)
     # pieces a 128-row block is cut into for the broadcast (0 = the launcher's choice)
@@ -293,7 +292,7 @@ def all_gather_matmul(a_shard: torch.Tensor, b: torch.Tensor, a_out: Optional[to
     _check_gather_geometry(rec.notes, (aout_offset, M, K, a_shard.dtype))
     C.ag_matmul(a_shard, b, c_out, 2, hdl.native, aout_offset, a_out, bn, sms, t_ns,
                 _tail_buffer(a_shard.device, config), epi, trace, config.lead, config.push_ahead,
-                config.push_spread, _push_plain_stores(config, ws), config.push_pieces, config.panel_w)
+                _push_plain_stores(config, ws), config.push_pieces, config.panel_w)
     return c_out
 
 

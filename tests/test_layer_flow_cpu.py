@@ -19,7 +19,7 @@ class _FakeC:
 
     @staticmethod
     def ag_matmul(a, b, c, mode, aout_alloc, aout_offset, a_out, block_n, num_sms, timeout_ns, tail_scratch=None,
-                  epilogue=0, trace=None, lead=-1, push_ahead=0, push_spread=0, push_plain_stores=False,
+                  epilogue=0, trace=None, lead=-1, push_ahead=0, push_plain_stores=False,
                   push_pieces=0, panel_w=0):
         assert mode == 0, "world of one: no gather"
         full = a.float() @ b.float().t()

@@ -109,7 +109,7 @@ def test_every_native_call_site_fits_its_binding():
 
 @pytest.mark.parametrize("name,expected", [
     ("ag_matmul", ["a", "b", "c", "mode", "aout_alloc", "aout_offset", "a_out", "block_n", "num_sms", "timeout_ns",
-                   "tail_scratch", "epilogue", "trace", "lead", "push_ahead", "push_spread", "push_plain_stores",
+                   "tail_scratch", "epilogue", "trace", "lead", "push_ahead", "push_plain_stores",
                    "push_pieces", "panel_w"]),
     ("matmul_reduce_scatter", ["a", "b", "out", "workspace", "num_sms", "timeout_ns", "trace", "panel_w"]),
     ("matmul_all_reduce", ["a", "b", "out", "out_alloc", "out_offset", "workspace", "num_sms", "timeout_ns",

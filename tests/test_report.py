@@ -163,7 +163,7 @@ def test_suite_runs_an_explicit_job_list(monkeypatch, tmp_path, capsys):
     monkeypatch.setattr(_common, "init_distributed", lambda: (0, 0, 8, torch.device("cpu")))
     monkeypatch.setattr(_common, "finish", lambda: None)
     jobs = ("all_gather_matmul --M 16384 --N 3584 --K 8192 --warmup 10 --iters 25 --trace --per-rank "
-            "--pacings 1:0:12:0,1:0:4:1,1:0:12:1,2:0:12:0 --out x.jsonl; "
+            "--pacings 1:12:0,1:4:1,1:12:1,2:12:0 --out x.jsonl; "
             "gemv_all_reduce --extra-algos tc_tagged; "
             "all_reduce --one-shot-sweep --with-reference-triton --max-bytes 8388608; "
             "all_reduce --multimem-sweep --max-bytes 268435456; "
