@@ -566,6 +566,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("check_push_schedule", &check_push_schedule);
   m.def("check_pair_work", &check_pair_work);
   m.def("check_rs_pair_schedule", &check_rs_pair_schedule);
+  m.def("check_rs_progress", &check_rs_progress);
   m.def("gemv_batch_tile", &gemv_batch_tile);
   m.def("gemv_workspace_bytes", [](int batch_tile, int N, int world_size) {
     return gemv_workspace_bytes(batch_tile, N, world_size, nullptr, nullptr, nullptr);

@@ -121,6 +121,7 @@ int check_push_schedule(int world_size, int rank, int blocks_per_rank, int n_til
                         int pos_per_tile, int pieces);
 int check_pair_work(int total_tiles, int n_pairs, int k_blocks, int tail_tiles, int tail_splits);
 int check_rs_pair_schedule(int world_size, int rank, int blocks_per_rank, int n_tiles_n, int n_pairs);
+int check_rs_progress(int world_size, int blocks_per_rank, int n_tiles_n, int n_pairs, int panel_w);
 
 // ---- fused GEMV + all-reduce (decode) -------------------------------------
 struct GemvArgs {

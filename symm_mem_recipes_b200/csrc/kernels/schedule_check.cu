@@ -163,4 +163,66 @@ static int check_rs_pair_schedule_panel(int world_size, int rank, int blocks_per
   return 0;
 }
 
+// Progress of the reduce-scatter kernel over all ranks at once, under a model that is stricter than the
+// kernel: a CTA pair moves to its next tile only when both of its CTAs have finished the current one (the
+// kernel lets the MMA run one tile ahead); a tile of another rank's rows ships at once, a tile of the own
+// rows finishes when all peers have shipped their tile of the same (row block, N tile).  Every pair of
+// every rank is assumed resident (the launcher checks that).  0 = every tile of every rank finishes;
+// 1 = the ranks end up waiting for one another (a cycle of waits).
+int check_rs_progress(int world_size, int blocks_per_rank, int n_tiles_n, int n_pairs, int panel_w) {
+  const int n_rb = world_size * blocks_per_rank;
+  const int n_rows = (n_rb + 1) / 2;
+  const int total_tiles = n_rows * n_tiles_n;
+  if (panel_w < 1 || panel_w > n_tiles_n) panel_w = n_tiles_n;
+  std::vector<rs::RsParams> params(world_size);
+  for (int r = 0; r < world_size; ++r) {
+    params[r].world_size = world_size;
+    params[r].rank = r;
+    params[r].blocks_per_rank = blocks_per_rank;
+    params[r].n_tiles_n = n_tiles_n;
+    params[r].panel_w = panel_w;
+  }
+  std::vector<int> arrived((size_t)world_size * blocks_per_rank * n_tiles_n, 0);
+  std::vector<int> next((size_t)world_size * n_pairs, 0);          // index of the pair's current tile in its own order
+  std::vector<char> done((size_t)world_size * n_pairs * 2, 0);     // CTA c of the pair has finished the current tile
+  bool moved = true;
+  while (moved) {
+    moved = false;
+    for (int r = 0; r < world_size; ++r)
+      for (int pair = 0; pair < n_pairs; ++pair) {
+        const size_t slot = (size_t)r * n_pairs + pair;
+        for (;;) {
+          const int t = pair + next[slot] * n_pairs;
+          if (t >= total_tiles) break;
+          int pr, ni;
+          panel_tile_coords(n_tiles_n, panel_w, n_rows, t, pr, ni);
+          for (int c = 0; c < 2; ++c) {
+            if (done[slot * 2 + c]) continue;
+            const int rb = 2 * pr + c;
+            if (rb >= n_rb) { done[slot * 2 + c] = 1; moved = true; continue; }
+            int dest, mb;
+            rs::row_block_coords(params[r], rb, dest, mb);
+            int& count = arrived[((size_t)dest * blocks_per_rank + mb) * n_tiles_n + ni];
+            if (dest != r) {
+              ++count;                                             // shipped
+              done[slot * 2 + c] = 1;
+              moved = true;
+            } else if (count == world_size - 1) {
+              done[slot * 2 + c] = 1;                              // all partials are in: reduced
+              moved = true;
+            }
+          }
+          if (!(done[slot * 2] && done[slot * 2 + 1])) break;
+          done[slot * 2] = done[slot * 2 + 1] = 0;
+          ++next[slot];
+          moved = true;
+        }
+      }
+  }
+  for (int r = 0; r < world_size; ++r)
+    for (int pair = 0; pair < n_pairs; ++pair)
+      if (pair + next[(size_t)r * n_pairs + pair] * n_pairs < total_tiles) return 1;
+  return 0;
+}
+
 }  // namespace smr

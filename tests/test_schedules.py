@@ -87,3 +87,15 @@ def test_reduce_scatter_pair_schedule_covers_every_tile_once():
             if rc != 0:
                 bad.append((ws, rank, bpr, n_tiles_n, pairs, rc))
     assert not bad, bad[:10]
+
+
+def test_reduce_scatter_progress_with_column_panels():
+    """All ranks simulated together: with the own rows last inside every column panel no cycle of waits
+    can form, whatever the panel width, also when a CTA pair straddles two destinations (odd blocks per
+    rank) and when there are fewer pairs than tiles in a panel."""
+    bad = []
+    for ws, bpr, n_tiles_n, pairs in itertools.product((2, 3, 4, 8), (1, 2, 3, 32), (1, 5, 32), (1, 3, 74)):
+        for panel_w in {n_tiles_n, (n_tiles_n + 1) // 2, 1}:
+            if C.check_rs_progress(ws, bpr, n_tiles_n, pairs, panel_w) != 0:
+                bad.append((ws, bpr, n_tiles_n, pairs, panel_w))
+    assert not bad, bad[:10]
