@@ -74,10 +74,11 @@ def test_all_reduce_thresholds_from_a_sweep(tmp_path, monkeypatch):
         # 4 KiB, 8 KiB: low_latency wins; 16 KiB: one_shot wins; 32 KiB on: multimem wins
         rec("nccl", 4096, 1.0), rec("low_latency", 4096, 5), rec("one_shot", 4096, 12), rec("multimem", 4096, 10),
         rec("low_latency", 8192, 6), rec("one_shot", 8192, 12), rec("multimem", 8192, 10),
-        rec("low_latency", 16384, 14), rec("one_shot", 16384, 9), rec("two_shot", 16384, 13),
-        rec("multimem", 16384, 10),
-        rec("one_shot", 32768, 20), rec("multimem", 32768, 11),
-        rec("low_latency", 65536, 1), rec("multimem", 65536, 12),     # past the break: must not reopen the range
+        rec("low_latency", 16384, 14), rec("one_shot", 16384, 4), rec("two_shot", 16384, 13),
+        rec("multimem", 16384, 10),                                    # one-shot: 4 + 5.5 for its write-back < 10
+        rec("one_shot", 32768, 9), rec("two_shot", 32768, 10.5), rec("multimem", 32768, 11),   # 9 + 5.5 loses
+        rec("two_shot", 49152, 13), rec("multimem", 49152, 12),
+        rec("low_latency", 65536, 1), rec("two_shot", 65536, 1), rec("multimem", 65536, 12),   # past the breaks: ranges must not reopen
         rec("low_latency", 4096, 5, ws=2), rec("two_shot", 4096, 9, ws=2),
     ]
     f = tmp_path / "sweep.jsonl"
@@ -85,14 +86,15 @@ def test_all_reduce_thresholds_from_a_sweep(tmp_path, monkeypatch):
     out = tmp_path / "tuning.json"
     assert tune_all_reduce.main([str(f), "--out", str(out)]) == 0
     table = json.loads(out.read_text())["by_world_size"]
-    assert table["8"] == {"ll_max_bytes": 8192, "one_shot_max_bytes": 16384}
-    assert table["2"] == {"ll_max_bytes": 4096, "one_shot_max_bytes": 0}
+    assert table["8"] == {"ll_max_bytes": 8192, "one_shot_max_bytes": 16384, "two_shot_max_bytes": 32768}
+    assert table["2"] == {"ll_max_bytes": 4096, "one_shot_max_bytes": 0}    # two-shot never met multimem: no entry
     cfg = AllReduceConfig.from_tuning(str(out), world_size=8)
     assert (cfg.ll_max_bytes, cfg.one_shot_max_bytes) == (8192, 16384)
     assert AllReduceConfig.from_tuning(str(out)).ll_max_bytes == 8192           # largest world size in the file
     from symm_mem_recipes_b200.ops.all_reduce import choose_algo
-    assert [choose_algo(n, 8, True, cfg) for n in (4096, 16384, 32768)] == ["low_latency", "one_shot", "multimem"]
-    assert choose_algo(32768, 8, False, cfg) == "two_shot"
+    assert [choose_algo(n, 8, True, cfg) for n in (4096, 16384, 32768, 49152)] == [
+        "low_latency", "one_shot", "two_shot", "multimem"]
+    assert choose_algo(49152, 8, False, cfg) == "two_shot"
 
 
 def test_roofline_expectations():
